@@ -1,0 +1,471 @@
+#!/usr/bin/env python
+"""Benchmark of the attention hot path on B200: one full-attention layer decode step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--no-sweep] [--impl reference]
+
+A step = one launch of the fused decode-attention kernel (partial RoPE on q/k, KV append, paged GQA attention with
+split-K over pages, sigmoid gate) over a batch of B sequences with contexts drawn uniform in [512, 4096] (seed 1):
+8 Q heads, 2 KV heads, head_dim 256, 16-token pages, random page table, bf16 ~N(0,1) data, RoPE on the first 64 dims
+with theta 1e7.  Synthetic data throughout.
+
+Reported on one JSON line:
+  value      achieved HBM GB/s = ALGORITHMIC bytes per step / device time (CUDA events), inputs resident in HBM
+  e2e        same metric through the public Python operator with HOST inputs: per step q/k_new/v_new/gate are copied
+             from pinned host memory and the [B,2048] output is copied back (the KV cache is device-resident state,
+             as it is in the engine)
+  roofline   the fused kernel against the measured copy bandwidth of this pool's B200s
+  cpu_baseline  the CPU oracle (a port of the reference operators' math, eager PyTorch on the host cores)
+  sweep      us/layer and GB/s for B in {1,4,16,32,64,256}, random and fixed-32768 contexts, plus the drop-in
+             3-launch chain and the Gated-DeltaNet decode state update (not part of `value`)
+`--impl reference` times the reference operators' CPU math (the oracle port; the Triton reference itself cannot
+travel to the box) on a bounded sample of the same workload.
+Under torchrun each rank runs its own replica (weak scaling, no data-path collective); the time is the max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+PKG = ROOT / "qwen3_5-triton-inference-engine_b200"
+for _p in (str(ROOT), str(PKG), str(ROOT / "tests")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+PAGE, HQ, HKV, D, ROT = 16, 8, 2, 256, 64
+L2_BYTES = 126 * 1024 * 1024
+METRIC = "paged_gqa_decode_attention_hbm_gbs"
+FALLBACK_HBM_GBS = 6650.0
+# dram bytes / algorithmic bytes of the fused kernel, from the ncu capture summarised under profiles/
+# (None until a capture exists)
+NCU_TRAFFIC_RATIO = None
+
+
+def cdiv(a, b):
+    return (a + b - 1) // b
+
+
+def draw_lengths(batch: int, mode: str, seed: int = 1) -> list[int]:
+    if mode == "fixed32768":
+        return [32768] * batch
+    gen = torch.Generator().manual_seed(seed)
+    return torch.randint(512, 4097, (batch,), generator=gen).tolist()
+
+
+def algorithmic_bytes(lengths: list[int]) -> int:
+    """K+V rows of every cached token incl. the appended one, q/gate/out rows, new-kv read + cache write,
+    page-table entries and positions.  Split-K scratch is NOT algorithmic."""
+    b = len(lengths)
+    return (sum(2048 * (n + 1) for n in lengths) + b * (4096 + 4096 + 4096 + 2048 + 2048)
+            + sum(4 * cdiv(n + 1, PAGE) for n in lengths) + 8 * b)
+
+
+def gdn_decode_bytes(batch: int, heads: int = 16) -> int:
+    return batch * (2 * heads * 128 * 128 * 4 + 3 * heads * 128 * 2 + heads * 128 * 2 + 2 * heads * 4)
+
+
+class Workload:
+    """`sets` independent copies of the layer state so that consecutive timed steps never find their pages in L2."""
+
+    def __init__(self, lengths, device, seed=1, min_total_bytes=3 * L2_BYTES, max_sets=64, pin_host=False):
+        self.lengths = lengths
+        self.batch = b = len(lengths)
+        self.device = device
+        self.bytes = algorithmic_bytes(lengths)
+        self.sets = max(1, min(max_sets, cdiv(min_total_bytes, self.bytes)))
+        gen = torch.Generator().manual_seed(seed)
+        pages_per_seq = [cdiv(n + 1, PAGE) for n in lengths]
+        max_pages = max(pages_per_seq)
+        used = sum(pages_per_seq)
+        num_pages = used + 8
+        self.inv_freq = (1.0 / (1e7 ** (torch.arange(0, ROT, 2, dtype=torch.float32) / ROT))).to(device)
+        self.pos = torch.tensor(lengths, dtype=torch.int64, device=device)
+        self.k_caches, self.v_caches, self.tables = [], [], []
+        for _ in range(self.sets):
+            perm = torch.randperm(num_pages, generator=gen)
+            table = torch.zeros(b, max_pages, dtype=torch.int32)
+            off = 0
+            for i, n in enumerate(pages_per_seq):
+                table[i, :n] = perm[off:off + n].to(torch.int32)
+                off += n
+            self.tables.append(table.to(device))
+            self.k_caches.append(torch.randn(num_pages, HKV, PAGE, D, dtype=torch.bfloat16, device=device))
+            self.v_caches.append(torch.randn(num_pages, HKV, PAGE, D, dtype=torch.bfloat16, device=device))
+        host = dict(
+            q=torch.randn(b, HQ, D, generator=gen).to(torch.bfloat16),
+            k_new=torch.randn(b, HKV, D, generator=gen).to(torch.bfloat16),
+            v_new=torch.randn(b, HKV, D, generator=gen).to(torch.bfloat16),
+            gate=torch.randn(b, HQ * D, generator=gen).to(torch.bfloat16),
+        )
+        self.host = {k: (v.pin_memory() if pin_host else v) for k, v in host.items()}
+        self.dev = {k: v.to(device) for k, v in host.items()}
+        self.out = torch.empty(b, HQ * D, dtype=torch.bfloat16, device=device)
+        self.out_host = torch.empty(b, HQ * D, dtype=torch.bfloat16).pin_memory() if pin_host else None
+
+
+def time_steps(fn, steps: int, warmup: int) -> float:
+    """ms per step with CUDA events on the current (launching) stream."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(steps):
+        fn(warmup + i)
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / steps
+
+
+def fused_step(ops, w: Workload, ws):
+    d = w.dev
+
+    def fn(i):
+        s = i % w.sets
+        ops.fused_decode_attention(d["q"], d["k_new"], d["v_new"], d["gate"], w.k_caches[s], w.v_caches[s], w.tables[s],
+                                   w.pos, w.inv_freq, ROT, ws, out=w.out)
+    return fn
+
+
+def chain_step(ops, w: Workload, scratch):
+    """The reference's launch structure with our drop-in operators: rope x2, append, split, combine, gate-pack."""
+    d = w.dev
+    b = w.batch
+    ids = w.pos.view(b, 1)
+
+    def fn(i):
+        s = i % w.sets
+        q4 = ops.partial_rope(d["q"].unsqueeze(2), ids, w.inv_freq, ROT)
+        k4 = ops.partial_rope(d["k_new"].unsqueeze(2), ids, w.inv_freq, ROT)
+        ctx = ops.call_paged_gqa_attention_decode_triton(q4[:, :, 0, :], k4[:, :, 0, :], d["v_new"], w.k_caches[s],
+                                                         w.v_caches[s], w.tables[s], w.pos, scratch)
+        gate4 = d["gate"].view(b, HQ, D).permute(1, 0, 2).unsqueeze(0)
+        ops.attention_gate_pack(ctx.permute(1, 0, 2).unsqueeze(0), gate4)
+    return fn
+
+
+def e2e_step(ops, w: Workload, ws):
+    h = w.host
+    dev = w.device
+
+    def fn(i):
+        s = i % w.sets
+        q = h["q"].to(dev, non_blocking=True)
+        k = h["k_new"].to(dev, non_blocking=True)
+        v = h["v_new"].to(dev, non_blocking=True)
+        g = h["gate"].to(dev, non_blocking=True)
+        out = ops.fused_decode_attention(q, k, v, g, w.k_caches[s], w.v_caches[s], w.tables[s], w.pos, w.inv_freq, ROT, ws)
+        w.out_host.copy_(out, non_blocking=True)
+    return fn
+
+
+# --------------------------------------------------------------------------- CPU oracle timing
+def cpu_reference_step(lengths, sample: int, seed: int = 1):
+    """Returns (seconds, algorithmic bytes) of one oracle pass over the first `sample` sequences of the workload."""
+    from oracle import reference_ops as O
+
+    lens = lengths[:sample]
+    gen = torch.Generator().manual_seed(seed)
+    b = len(lens)
+    pps = [cdiv(n + 1, PAGE) for n in lens]
+    num_pages = sum(pps) + 8
+    perm = torch.randperm(num_pages, generator=gen)
+    table = torch.zeros(b, max(pps), dtype=torch.int32)
+    off = 0
+    for i, n in enumerate(pps):
+        table[i, :n] = perm[off:off + n].to(torch.int32)
+        off += n
+    kc = torch.randn(num_pages, HKV, PAGE, D, generator=gen).to(torch.bfloat16)
+    vc = torch.randn(num_pages, HKV, PAGE, D, generator=gen).to(torch.bfloat16)
+    q = torch.randn(b, HQ, D, generator=gen).to(torch.bfloat16)
+    kn = torch.randn(b, HKV, D, generator=gen).to(torch.bfloat16)
+    vn = torch.randn(b, HKV, D, generator=gen).to(torch.bfloat16)
+    gate = torch.randn(b, HQ * D, generator=gen).to(torch.bfloat16)
+    pos = torch.tensor(lens, dtype=torch.int64)
+    inv = 1.0 / (1e7 ** (torch.arange(0, ROT, 2, dtype=torch.float32) / ROT))
+    t0 = time.perf_counter()
+    O.fused_decode_attention(q, kn, vn, gate, kc, vc, table, pos, inv, ROT, exact=True)
+    return time.perf_counter() - t0, algorithmic_bytes(lens)
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def __enter__(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def hbm_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+# --------------------------------------------------------------------------- main
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    lengths = draw_lengths(args.batch, "random")
+    threads = torch.get_num_threads()
+    sample = min(args.batch, args.cpu_sample)
+    for _ in range(args.warmup):
+        cpu_reference_step(lengths, min(sample, 8))
+    times, nbytes = [], 0
+    for _ in range(args.steps):
+        t, nbytes = cpu_reference_step(lengths, sample)
+        times.append(t)
+    sec = sum(times) / len(times)
+    value = nbytes / sec / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"decode attention layer step, B={args.batch}, ctx~U[512,4096] seed 1, 8q/2kv heads, "
+                               f"d=256, page 16, rope 64 theta 1e7, sigmoid gate"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"first {sample} of {args.batch} sequences per step, eager PyTorch fp32 on the host"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--cpu-sample", type=int, default=256)
+    ap.add_argument("--sweep-steps", type=int, default=20)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path (use --impl reference for the CPU oracle)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+
+    from b200attn import ops
+
+    ws = ops.fused_decode_workspace(device)
+    peak, peak_kind = hbm_peak()
+    lengths = draw_lengths(args.batch, "random", seed=1 + rank)
+    w = Workload(lengths, device, seed=1 + rank, pin_host=True)
+    step = fused_step(ops, w, ws)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    # ---- headline: device-resident inputs
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for i in range(args.steps):
+            step(args.warmup + i)
+        end.record()
+        barrier()
+        ms_total = start.elapsed_time(end)
+        # keep the sampler alive for a moment on very short runs so that it sees the load
+        if ms_total < 400:
+            t_end = time.time() + 0.5
+            j = 0
+            while time.time() < t_end:
+                step(j)
+                j += 1
+            torch.cuda.synchronize()
+    clock_info = clocks.summary()
+    if dist is not None:
+        t = torch.tensor([ms_total], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+        tb = torch.tensor([float(w.bytes)], device=device, dtype=torch.float64)
+        dist.all_reduce(tb)
+        total_bytes = float(tb.item())
+    else:
+        total_bytes = float(w.bytes)
+    ms_per_step = ms_total / args.steps
+    value = total_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- e2e: host inputs and output through the public operator
+    e2e = e2e_step(ops, w, ws)
+    for i in range(args.warmup):
+        e2e(i)
+    barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    start.record()
+    for i in range(args.steps):
+        e2e(args.warmup + i)
+    end.record()
+    barrier()
+    e2e_ms = max(start.elapsed_time(end), (time.perf_counter() - t0) * 1e3)
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = total_bytes / (e2e_ms / args.steps * 1e-3) / 1e9
+    h2d = args.batch * (4096 + 1024 + 1024 + 4096)
+    d2h = args.batch * 4096
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {
+            "workload": f"decode attention layer step, B={args.batch} per GPU, ctx~U[512,4096] seed 1, 8q/2kv heads, "
+                        f"d=256, page 16, rope 64 theta 1e7, sigmoid gate",
+            "l2_policy": f"inputs larger than L2: {w.sets} rotating cache sets x {w.bytes / 1e6:.0f} MB per step",
+            "parallelism": f"replicas x{world} (no data-path collective)",
+            "us_per_layer": ms_per_step * 1e3,
+        },
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": args.steps,
+        "clocks": clock_info,
+    }
+
+    if rank == 0:
+        per_gpu = w.bytes / (ms_per_step * 1e-3) / 1e9
+        line["roofline"] = {
+            "bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
+            "traffic": (None if NCU_TRAFFIC_RATIO is None else NCU_TRAFFIC_RATIO * w.bytes),
+            "peak_kind": f"of {peak_kind}", "kernel": "fused_decode_kernel",
+            "algorithmic_bytes_per_launch": w.bytes,
+        }
+    if world == 1:
+        # ---- CPU baseline on a bounded sample (rank 0, N=1 only)
+        sample = min(args.batch, args.cpu_sample)
+        cpu_reference_step(lengths, min(sample, 8))
+        secs, nbytes = [], 0
+        t_budget = time.time() + 20
+        while len(secs) < 3 and time.time() < t_budget:
+            s, nbytes = cpu_reference_step(lengths, sample)
+            secs.append(s)
+        cpu_val = nbytes / (sum(secs) / len(secs)) / 1e9
+        line["cpu_baseline"] = {"value": cpu_val, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": f"first {sample} of {args.batch} sequences, {len(secs)} passes, eager PyTorch fp32"}
+        if not args.no_sweep:
+            line["sweep"] = run_sweep(ops, ws, device, peak, args.sweep_steps)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_sweep(ops, ws, device, peak, steps):
+    rows = []
+    for mode in ("random", "fixed32768"):
+        for b in (1, 4, 16, 32, 64, 256):
+            lengths = draw_lengths(b, mode)
+            w = Workload(lengths, device, max_sets=32)
+            ms = time_steps(fused_step(ops, w, ws), steps, 3)
+            row = {"op": "fused_decode", "B": b, "ctx": mode, "us_per_layer": ms * 1e3,
+                   "gbs": w.bytes / (ms * 1e-3) / 1e9}
+            row["frac"] = row["gbs"] / peak
+            if mode == "random" or b <= 32:
+                scratch = ops.allocate_split_scratch(HQ, D, batch=b, device=device)
+                ms_c = time_steps(chain_step(ops, w, scratch), steps, 3)
+                row["chain_us_per_layer"] = ms_c * 1e3
+                row["chain_gbs"] = w.bytes / (ms_c * 1e-3) / 1e9
+                del scratch
+            rows.append(row)
+            del w
+            torch.cuda.empty_cache()
+    # Gated-DeltaNet decode: fp32 state [B,16,128,128] streamed in and out once per step
+    for b in (1, 32, 256):
+        nbytes = gdn_decode_bytes(b)
+        sets = max(1, min(32, cdiv(3 * L2_BYTES, nbytes)))
+        states = [torch.zeros(b, 16, 128, 128, device=device) for _ in range(sets)]
+        gen = torch.Generator().manual_seed(3)
+        q = torch.nn.functional.normalize(torch.randn(b, 16, 128, generator=gen), dim=-1).to(torch.bfloat16).to(device)
+        k = torch.nn.functional.normalize(torch.randn(b, 16, 128, generator=gen), dim=-1).to(torch.bfloat16).to(device)
+        v = torch.randn(b, 16, 128, generator=gen).to(torch.bfloat16).to(device)
+        beta = torch.sigmoid(torch.randn(b, 16, generator=gen)).to(device)
+        g = (-torch.nn.functional.softplus(torch.randn(b, 16, generator=gen))).to(device)
+        ms = time_steps(lambda i: ops.gdn_recurrent_decode(q, k, v, beta, g, states[i % sets]), steps, 3)
+        rows.append({"op": "gdn_recurrent_decode", "B": b, "us_per_layer": ms * 1e3, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                     "frac": nbytes / (ms * 1e-3) / 1e9 / peak})
+        del states
+        torch.cuda.empty_cache()
+    return rows
+
+
+if __name__ == "__main__":
+    main()

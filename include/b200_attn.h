@@ -1,0 +1,147 @@
+/*
+ * b200_attn.h -- C ABI of libb200attn.so: hand-written sm_100a CUDA kernels for the attention /
+ * Gated-DeltaNet hot path of a Qwen3.5-style decoder.
+ *
+ * Every entry point replaces one operator of the reference engine (cited as file:line inside the
+ * reference project) and keeps its argument meaning.  Conventions:
+ *   - All pointers are DEVICE pointers unless a comment says "host".  bf16 tensors are passed as
+ *     `void*`, fp32 as `float*`, page tables / cu_seqlens as `int32_t*`, positions as `int64_t*`.
+ *   - Strides are in ELEMENTS.  The innermost dimension of every tensor must have stride 1.
+ *   - `stream` is the cudaStream_t to launch on (0 = legacy default stream).
+ *   - Return value: 0 = kernel launched; non-zero = nothing was launched, b200_last_error() says why.
+ *   - No entry point synchronises, allocates device memory, or reads device data on the host, so all of
+ *     them may be captured into a CUDA graph (exceptions are marked "host-synchronous").
+ *   - Kernels do no bounds checks on page ids or positions: sizing the page table is the caller's job,
+ *     exactly as in the reference (triton_kernels/gqa_attention_decode_paged.py:225-226).
+ */
+#ifndef B200_ATTN_H_
+#define B200_ATTN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_ABI_VERSION 1
+
+/* Model constants the tensor-core kernels are specialised for (other values are rejected). */
+#define B200_PAGE_SIZE 16   /* triton_kernels/gqa_attention_decode_paged.py:91  PAGE_SIZE  */
+#define B200_MAX_SPLITS 128 /* triton_kernels/gqa_attention_decode_paged.py:95  MAX_SPLITS */
+#define B200_HEAD_DIM 256
+#define B200_GROUP 4
+#define B200_GDN_DIM 128
+#define B200_GDN_CHUNK 64
+
+typedef void* b200_stream_t; /* cudaStream_t */
+
+/* ------------------------------------------------------------------------------------------ utilities */
+const char* b200_last_error(void); /* host string describing the last non-zero return */
+int b200_abi_version(void);
+/* host-synchronous: 1 if a kernel on the current device gave up a bounded wait on a staged copy since the
+ * last call (the flag is cleared), 0 if not, -1 on a runtime error.  For tests and debugging. */
+int b200_wait_timed_out(void);
+
+/* ------------------------------------------------------------------------------------------ paged KV cache */
+/* cache[block_table[b, pos[b]/16], h, pos[b]%16, :] = new[b, h, :] for K and V.
+ * Replaces wy_lib::paged_kv_append, triton_kernels/gqa_attention_decode_paged.py:254-305 (kernel :175-250).
+ * caches [num_pages, H_kv, 16, D] bf16; k_new/v_new [B, H_kv, D] bf16; block_table [B, max_pages]; pos [B]. */
+int b200_paged_kv_append(void* k_cache, void* v_cache, int64_t kc_stride_p, int64_t kc_stride_h, int64_t kc_stride_s,
+                         int64_t vc_stride_p, int64_t vc_stride_h, int64_t vc_stride_s, const void* k_new,
+                         int64_t kn_stride_b, int64_t kn_stride_h, const void* v_new, int64_t vn_stride_b,
+                         int64_t vn_stride_h, const int32_t* block_table, int64_t bt_stride_b, const int64_t* pos,
+                         int32_t batch, int32_t num_kv_heads, int32_t head_dim, b200_stream_t stream);
+
+/* Scatter packed K/V [H_kv, T, D] (any h/t strides) into each sequence's pages; slots past a sequence's end
+ * keep their bytes.  max_seqlen (host) only sizes the grid.
+ * Replaces wy_lib::paged_kv_fill_varlen, triton_kernels/gqa_attention_decode_paged.py:492-561 (kernel :397-489). */
+int b200_paged_kv_fill_varlen(void* k_cache, void* v_cache, int64_t kc_stride_p, int64_t kc_stride_h,
+                              int64_t kc_stride_s, int64_t vc_stride_p, int64_t vc_stride_h, int64_t vc_stride_s,
+                              const void* k_packed, int64_t kp_stride_h, int64_t kp_stride_t, const void* v_packed,
+                              int64_t vp_stride_h, int64_t vp_stride_t, const int32_t* block_table,
+                              int64_t bt_stride_b, const int32_t* cu_seqlens, int32_t batch, int32_t num_kv_heads,
+                              int32_t head_dim, int32_t max_seqlen, b200_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------ paged decode attention */
+/* Split-K partial attention with the reference's page partition; writes all 128 (m, l, acc) partials.
+ * q [B, H_q, 256] bf16; m_partial/l_partial [B, H_q, 128] fp32, acc_partial [B, H_q, 128, 256] fp32, contiguous.
+ * Replaces wy_lib::paged_gqa_attention_decode_split, triton_kernels/gqa_attention_decode_paged.py:822-891
+ * (kernel :622-733). */
+int b200_paged_decode_split(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_cache,
+                            const void* v_cache, int64_t kc_stride_p, int64_t kc_stride_h, int64_t kc_stride_s,
+                            int64_t vc_stride_p, int64_t vc_stride_h, int64_t vc_stride_s, const int32_t* block_table,
+                            int64_t bt_stride_b, float* m_partial, float* l_partial, float* acc_partial,
+                            const int64_t* pos, int32_t batch, int32_t num_q_heads, int32_t num_kv_heads,
+                            int32_t head_dim, b200_stream_t stream);
+
+/* Merge the active partials into out [B, H_q, 256] bf16 (contiguous).
+ * Replaces wy_lib::paged_gqa_attention_decode_combine, triton_kernels/gqa_attention_decode_paged.py:901-939
+ * (kernel :745-817). */
+int b200_paged_decode_combine(const float* m_partial, const float* l_partial, const float* acc_partial,
+                              const int64_t* pos, void* out, int32_t batch, int32_t num_q_heads, int32_t head_dim,
+                              b200_stream_t stream);
+
+/* Fused decode attention layer core: partial RoPE on q and k_new at position pos[b], append of the rotated
+ * k_new and of v_new to the paged cache, attention over the pos[b]+1 cached tokens, sigmoid output gate.
+ * One launch replaces the chain partial_rope x2 -> paged_kv_append -> split -> combine -> attention_gate_pack of
+ * engine/runner.py:482-517 (call_paged_gqa_attention_decode_triton, gqa_attention_decode_paged.py:963-994).
+ * q [B,H_q,256], k_new/v_new [B,H_kv,256], gate [B, H_q*256] (row stride gate_stride_b), out [B, H_q*256] bf16
+ * contiguous; inv_freq [rotary_dim/2] fp32; rotary_dim is 64 (the model's) or 0 = no rotation.
+ * workspace: b200_fused_decode_workspace_bytes() bytes of device memory, 256-byte aligned, zero-filled ONCE by
+ * the caller before the first use (the kernel leaves it zeroed again); calls sharing a workspace must not
+ * overlap on the device. */
+int64_t b200_fused_decode_workspace_bytes(void);
+int b200_fused_decode_attention(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_new,
+                                int64_t kn_stride_b, int64_t kn_stride_h, const void* v_new, int64_t vn_stride_b,
+                                int64_t vn_stride_h, const void* gate, int64_t gate_stride_b, void* k_cache,
+                                void* v_cache, int64_t kc_stride_p, int64_t kc_stride_h, int64_t kc_stride_s,
+                                int64_t vc_stride_p, int64_t vc_stride_h, int64_t vc_stride_s,
+                                const int32_t* block_table, int64_t bt_stride_b, const int64_t* pos,
+                                const float* inv_freq, int32_t rotary_dim, void* out, void* workspace, int32_t batch,
+                                int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, b200_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------ rope / gate */
+/* Half-split rotation of the first rotary_dim dims of x [B,H,T,D] bf16 (dims >= rotary_dim copied).
+ * position_ids [B,T] int32 or int64.  Replaces wy_lib::partial_rope, triton_kernels/partial_rope.py:145-198
+ * (kernel :27-132). */
+int b200_partial_rope(const void* x, int64_t x_stride_b, int64_t x_stride_h, int64_t x_stride_t, void* out,
+                      int64_t out_stride_b, int64_t out_stride_h, int64_t out_stride_t, const void* position_ids,
+                      int32_t ids_are_int64, int64_t ids_stride_b, int64_t ids_stride_t, const float* inv_freq,
+                      int32_t batch, int32_t num_heads, int32_t num_tokens, int32_t head_dim, int32_t rotary_dim,
+                      b200_stream_t stream);
+
+/* out[t, h*D + d] = bf16(x[h,t,d] * sigmoid(gate[h,t,d])); x, gate are [1,H,T,D] views, out [T, H*D] contiguous.
+ * Replaces wy_lib::attention_gate_pack, triton_kernels/attention_gate_pack.py:77-126 (kernel :15-64). */
+int b200_attention_gate_pack(const void* x, int64_t x_stride_h, int64_t x_stride_t, const void* gate,
+                             int64_t gate_stride_h, int64_t gate_stride_t, void* out, int32_t num_heads,
+                             int32_t num_tokens, int32_t head_dim, b200_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------ Gated DeltaNet */
+/* One delta-rule step per sequence; state [B,H,128,128] fp32 updated in place (inner two dims contiguous).
+ * q,k [B,H,128] bf16, v [B,H,128] bf16 (any b/h strides), beta,g [B,H] fp32, out [B,H,128] bf16.
+ * Replaces wy_lib::gdn_recurrent_decode, triton_kernels/gdn_recurrent_prefill.py:1185-1259 (kernel :145-246). */
+int b200_gdn_recurrent_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k,
+                              int64_t k_stride_b, int64_t k_stride_h, const void* v, int64_t v_stride_b,
+                              int64_t v_stride_h, const float* beta, int64_t beta_stride_b, int64_t beta_stride_h,
+                              const float* g, int64_t g_stride_b, int64_t g_stride_h, float* state,
+                              int64_t state_stride_b, int64_t state_stride_h, void* out, int64_t out_stride_b,
+                              int64_t out_stride_h, int32_t batch, int32_t num_heads, int32_t key_dim,
+                              int32_t value_dim, b200_stream_t stream);
+
+/* Token-serial recurrence over a packed buffer, zero state at every cu_seqlens[b]; cu_seqlens may be NULL
+ * (one sequence of total_tokens).  state [batch,H,128,128] fp32 contiguous (written), out [T,H,128] bf16.
+ * Replaces wy_lib::gdn_recurrent_prefill_sequential, triton_kernels/gdn_recurrent_prefill.py:1050-1145
+ * (kernel :47-143). */
+int b200_gdn_recurrent_prefill_sequential(const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k,
+                                          int64_t k_stride_t, int64_t k_stride_h, const void* v, int64_t v_stride_t,
+                                          int64_t v_stride_h, const float* beta, int64_t beta_stride_t,
+                                          int64_t beta_stride_h, const float* g, int64_t g_stride_t,
+                                          int64_t g_stride_h, const int32_t* cu_seqlens, int32_t batch,
+                                          int32_t total_tokens, float* state, void* out, int64_t out_stride_t,
+                                          int64_t out_stride_h, int32_t num_heads, int32_t key_dim, int32_t value_dim,
+                                          b200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_ATTN_H_ */

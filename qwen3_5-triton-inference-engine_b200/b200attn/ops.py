@@ -1,0 +1,367 @@
+"""torch.library operators `wy_lib::*` backed by libb200attn.so.
+
+Same operator names, schemas, argument meaning and assert-before-launch behaviour as the reference's
+`triton_kernels/*.py` wrappers (each function cites the one it replaces), so `engine/runner.py`, `cache.py` and
+`paging.py` of the reference can import them unchanged through the `triton_kernels` shim package next to this one.
+Outputs are allocated with torch on the inputs' device; caches, state and scratch are caller-owned and
+mutated in place.  Everything launches on `torch.cuda.current_stream()`; nothing synchronises.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+
+PAGE_SIZE = 16     # triton_kernels/gqa_attention_decode_paged.py:91
+MAX_SPLITS = 128   # triton_kernels/gqa_attention_decode_paged.py:95
+GDN_CHUNK = 64
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def _inner_contiguous(t: torch.Tensor) -> torch.Tensor:
+    """The C ABI wants unit stride on the last dim; anything else is materialised (never the case in the engine)."""
+    return t if t.stride(-1) == 1 else t.contiguous()
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None:
+            assert t.is_cuda, "b200attn operators run on CUDA tensors only (there is no CPU fallback)"
+
+
+# =========================================================================== paged KV cache
+@torch.library.custom_op("wy_lib::paged_kv_append", mutates_args=("k_cache", "v_cache"), device_types="cuda")
+def paged_kv_append(k_cache: torch.Tensor, v_cache: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
+                    block_table: torch.Tensor, pos: torch.Tensor) -> None:
+    """Replaces triton_kernels/gqa_attention_decode_paged.py:254-305."""
+    batch, num_kv_heads, head_dim = k_new.shape
+    assert k_cache.shape[1] == num_kv_heads and k_cache.shape[3] == head_dim
+    assert k_cache.shape[2] == PAGE_SIZE
+    assert v_cache.shape == k_cache.shape
+    assert k_new.shape == v_new.shape
+    assert k_cache.dtype == v_cache.dtype == torch.bfloat16
+    assert k_new.dtype == v_new.dtype == torch.bfloat16
+    assert block_table.dtype == torch.int32 and block_table.shape[0] == batch
+    assert pos.dtype == torch.int64 and pos.shape == (batch,)
+    assert k_cache.stride(3) == 1 and v_cache.stride(3) == 1 and block_table.stride(1) == 1
+    _require_cuda(k_cache, v_cache, k_new, v_new, block_table, pos)
+    k_new, v_new, pos = _inner_contiguous(k_new), _inner_contiguous(v_new), pos.contiguous()
+    _lib.call("b200_paged_kv_append", _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), k_cache.stride(1),
+              k_cache.stride(2), v_cache.stride(0), v_cache.stride(1), v_cache.stride(2), _ptr(k_new), k_new.stride(0),
+              k_new.stride(1), _ptr(v_new), v_new.stride(0), v_new.stride(1), _ptr(block_table), block_table.stride(0),
+              _ptr(pos), batch, num_kv_heads, head_dim, _stream())
+
+
+@paged_kv_append.register_fake
+def _(k_cache, v_cache, k_new, v_new, block_table, pos) -> None:
+    return None
+
+
+@torch.library.custom_op("wy_lib::paged_kv_fill_varlen", mutates_args=("k_cache", "v_cache"), device_types="cuda")
+def paged_kv_fill_varlen(k_cache: torch.Tensor, v_cache: torch.Tensor, k_packed: torch.Tensor, v_packed: torch.Tensor,
+                         block_table: torch.Tensor, cu_seqlens: torch.Tensor, max_seqlen: int) -> None:
+    """Replaces triton_kernels/gqa_attention_decode_paged.py:492-561.  k_packed/v_packed are [H_kv, T, D] views."""
+    num_kv_heads, total_tokens, head_dim = k_packed.shape
+    assert v_packed.shape == k_packed.shape
+    assert k_cache.shape[1] == num_kv_heads and k_cache.shape[3] == head_dim
+    assert k_cache.shape[2] == PAGE_SIZE
+    assert v_cache.shape == k_cache.shape
+    assert k_cache.dtype == v_cache.dtype == torch.bfloat16
+    assert k_packed.dtype == v_packed.dtype == torch.bfloat16
+    assert block_table.dtype == torch.int32 and block_table.ndim == 2
+    assert cu_seqlens.dtype == torch.int32 and cu_seqlens.ndim == 1
+    batch = cu_seqlens.shape[0] - 1
+    assert block_table.shape[0] == batch, (
+        f"block_table has {block_table.shape[0]} rows but cu_seqlens describes {batch} sequences")
+    assert block_table.shape[1] >= (max_seqlen + PAGE_SIZE - 1) // PAGE_SIZE, (
+        f"page table rows hold {block_table.shape[1]} pages, too few for {max_seqlen} tokens")
+    assert k_cache.stride(3) == 1 and v_cache.stride(3) == 1 and block_table.stride(1) == 1
+    _require_cuda(k_cache, v_cache, k_packed, v_packed, block_table, cu_seqlens)
+    k_packed, v_packed = _inner_contiguous(k_packed), _inner_contiguous(v_packed)
+    cu_seqlens = cu_seqlens.contiguous()
+    _lib.call("b200_paged_kv_fill_varlen", _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), k_cache.stride(1),
+              k_cache.stride(2), v_cache.stride(0), v_cache.stride(1), v_cache.stride(2), _ptr(k_packed),
+              k_packed.stride(0), k_packed.stride(1), _ptr(v_packed), v_packed.stride(0), v_packed.stride(1),
+              _ptr(block_table), block_table.stride(0), _ptr(cu_seqlens), batch, num_kv_heads, head_dim,
+              int(max_seqlen), _stream())
+
+
+@paged_kv_fill_varlen.register_fake
+def _(k_cache, v_cache, k_packed, v_packed, block_table, cu_seqlens, max_seqlen) -> None:
+    return None
+
+
+# =========================================================================== paged decode attention
+@torch.library.custom_op("wy_lib::paged_gqa_attention_decode_split",
+                         mutates_args=("m_partial", "l_partial", "acc_partial"), device_types="cuda")
+def paged_gqa_attention_decode_split(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                                     block_table: torch.Tensor, m_partial: torch.Tensor, l_partial: torch.Tensor,
+                                     acc_partial: torch.Tensor, pos: torch.Tensor, seq_bucket: int) -> None:
+    """Replaces triton_kernels/gqa_attention_decode_paged.py:822-891.  `seq_bucket` only keyed the reference's
+    autotuner and is ignored."""
+    batch, num_q_heads, head_dim = q.shape
+    num_pages, num_kv_heads, page, cache_dim = k_cache.shape
+    assert page == PAGE_SIZE and cache_dim == head_dim
+    assert v_cache.shape == k_cache.shape
+    assert q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+    assert block_table.dtype == torch.int32 and block_table.shape[0] == batch
+    assert m_partial.shape == (batch, num_q_heads, MAX_SPLITS)
+    assert l_partial.shape == (batch, num_q_heads, MAX_SPLITS)
+    assert acc_partial.shape == (batch, num_q_heads, MAX_SPLITS, head_dim)
+    assert m_partial.dtype == l_partial.dtype == acc_partial.dtype == torch.float32
+    assert m_partial.is_contiguous() and l_partial.is_contiguous() and acc_partial.is_contiguous()
+    assert pos.dtype == torch.int64 and pos.shape == (batch,)
+    assert num_q_heads % num_kv_heads == 0
+    assert k_cache.stride(3) == 1 and v_cache.stride(3) == 1 and block_table.stride(1) == 1
+    _require_cuda(q, k_cache, v_cache, block_table, m_partial, l_partial, acc_partial, pos)
+    q, pos = _inner_contiguous(q), pos.contiguous()
+    _lib.call("b200_paged_decode_split", _ptr(q), q.stride(0), q.stride(1), _ptr(k_cache), _ptr(v_cache),
+              k_cache.stride(0), k_cache.stride(1), k_cache.stride(2), v_cache.stride(0), v_cache.stride(1),
+              v_cache.stride(2), _ptr(block_table), block_table.stride(0), _ptr(m_partial), _ptr(l_partial),
+              _ptr(acc_partial), _ptr(pos), batch, num_q_heads, num_kv_heads, head_dim, _stream())
+
+
+@paged_gqa_attention_decode_split.register_fake
+def _(q, k_cache, v_cache, block_table, m_partial, l_partial, acc_partial, pos, seq_bucket) -> None:
+    return None
+
+
+@torch.library.custom_op("wy_lib::paged_gqa_attention_decode_combine", mutates_args=(), device_types="cuda")
+def paged_gqa_attention_decode_combine(m_partial: torch.Tensor, l_partial: torch.Tensor, acc_partial: torch.Tensor,
+                                       pos: torch.Tensor) -> torch.Tensor:
+    """Replaces triton_kernels/gqa_attention_decode_paged.py:901-939."""
+    batch, num_q_heads, _, head_dim = acc_partial.shape
+    assert m_partial.is_contiguous() and l_partial.is_contiguous() and acc_partial.is_contiguous()
+    assert pos.dtype == torch.int64 and pos.shape == (batch,)
+    _require_cuda(m_partial, l_partial, acc_partial, pos)
+    out = torch.empty((batch, num_q_heads, head_dim), dtype=torch.bfloat16, device=acc_partial.device)
+    _lib.call("b200_paged_decode_combine", _ptr(m_partial), _ptr(l_partial), _ptr(acc_partial), _ptr(pos.contiguous()),
+              _ptr(out), batch, num_q_heads, head_dim, _stream())
+    return out
+
+
+@paged_gqa_attention_decode_combine.register_fake
+def _(m_partial, l_partial, acc_partial, pos) -> torch.Tensor:
+    batch, num_q_heads, _, head_dim = acc_partial.shape
+    return torch.empty((batch, num_q_heads, head_dim), dtype=torch.bfloat16, device=acc_partial.device)
+
+
+def allocate_paged_kv_cache(num_pages: int, num_kv_heads: int, head_dim: int, *, device="cuda"):
+    """`[num_pages, H_kv, PAGE, D]` bf16 K and V pools.  triton_kernels/gqa_attention_decode_paged.py:100-111."""
+    shape = (num_pages, num_kv_heads, PAGE_SIZE, head_dim)
+    return (torch.zeros(shape, dtype=torch.bfloat16, device=device),
+            torch.zeros(shape, dtype=torch.bfloat16, device=device))
+
+
+def allocate_split_scratch(num_q_heads: int, head_dim: int, *, batch: int = 1, device="cuda"):
+    """(m, l, acc) split-K scratch shared by all layers.  triton_kernels/gqa_attention_decode_paged.py:591-609."""
+    m = torch.zeros((batch, num_q_heads, MAX_SPLITS), dtype=torch.float32, device=device)
+    l = torch.zeros((batch, num_q_heads, MAX_SPLITS), dtype=torch.float32, device=device)
+    acc = torch.zeros((batch, num_q_heads, MAX_SPLITS, head_dim), dtype=torch.float32, device=device)
+    return m, l, acc
+
+
+def physical_rows(block_table: torch.Tensor, token_index: torch.Tensor, num_kv_heads: int) -> torch.Tensor:
+    """row(t,h) = (block_table[t // PAGE] * H + h) * PAGE + t % PAGE, [T, H], all on the device.
+    triton_kernels/gqa_attention_decode_paged.py:127-144."""
+    logical_page = token_index // PAGE_SIZE
+    slot = token_index % PAGE_SIZE
+    phys = block_table.index_select(0, logical_page.to(torch.int32)).to(torch.int64)
+    heads = torch.arange(num_kv_heads, device=block_table.device, dtype=torch.int64)
+    return (phys[:, None] * num_kv_heads + heads[None, :]) * PAGE_SIZE + slot[:, None]
+
+
+def paged_kv_fill(k_cache, v_cache, k_prefill, v_prefill, block_table) -> None:
+    """Single-sequence scatter of `[H, T, D]` K/V (block_table is that sequence's row).
+    triton_kernels/gqa_attention_decode_paged.py:355-375; served by the varlen kernel with cu_seqlens=[0, T]."""
+    num_kv_heads, token_num, head_dim = k_prefill.shape
+    assert v_prefill.shape == k_prefill.shape
+    cu = torch.tensor([0, token_num], dtype=torch.int32, device=k_cache.device)
+    paged_kv_fill_varlen(k_cache, v_cache, k_prefill, v_prefill, block_table.reshape(1, -1), cu, token_num)
+
+
+def call_paged_gqa_attention_decode_triton(q, k_new, v_new, k_cache, v_cache, block_table, pos, scratch=None):
+    """append -> split -> combine, the symbol engine/runner.py:508-510 calls.
+    triton_kernels/gqa_attention_decode_paged.py:963-994 (the name is kept for drop-in use; no Triton is involved)."""
+    if scratch is None:
+        scratch = allocate_split_scratch(q.shape[1], q.shape[2], batch=q.shape[0], device=q.device)
+    m_partial, l_partial, acc_partial = scratch
+    paged_kv_append(k_cache, v_cache, k_new, v_new, block_table, pos)
+    hint = k_cache.shape[0] * PAGE_SIZE
+    paged_gqa_attention_decode_split(q, k_cache, v_cache, block_table, m_partial, l_partial, acc_partial, pos, hint)
+    return paged_gqa_attention_decode_combine(m_partial, l_partial, acc_partial, pos)
+
+
+# --------------------------------------------------------------------------- fused decode (new entry point)
+def fused_decode_workspace(device="cuda") -> torch.Tensor:
+    """Zero-filled workspace for `fused_decode_attention` (one per stream of calls; shared by all layers)."""
+    nbytes = _lib.load().b200_fused_decode_workspace_bytes()
+    return torch.zeros(nbytes, dtype=torch.uint8, device=device)
+
+
+def fused_decode_attention(q, k_new, v_new, gate, k_cache, v_cache, block_table, pos, inv_freq, rotary_dim,
+                           workspace, out=None) -> torch.Tensor:
+    """RoPE(q, k_new) + append + paged attention + sigmoid gate in one launch -> [B, H_q*D] bf16.
+    q [B,H_q,D], k_new/v_new [B,H_kv,D] are the post-norm, PRE-RoPE projections; gate [B, H_q*D]."""
+    batch, num_q_heads, head_dim = q.shape
+    num_kv_heads = k_new.shape[1]
+    assert k_new.shape == v_new.shape == (batch, num_kv_heads, head_dim)
+    assert gate.shape == (batch, num_q_heads * head_dim)
+    assert q.dtype == k_new.dtype == v_new.dtype == gate.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
+    assert k_cache.shape[1:] == (num_kv_heads, PAGE_SIZE, head_dim) and v_cache.shape == k_cache.shape
+    assert block_table.dtype == torch.int32 and block_table.shape[0] == batch and block_table.stride(1) == 1
+    assert pos.dtype == torch.int64 and pos.shape == (batch,) and pos.is_contiguous()
+    assert inv_freq.dtype == torch.float32 and inv_freq.shape == (rotary_dim // 2,) and inv_freq.is_contiguous()
+    assert k_cache.stride(3) == 1 and v_cache.stride(3) == 1
+    _require_cuda(q, k_new, v_new, gate, k_cache, v_cache, block_table, pos, inv_freq, workspace)
+    q, k_new, v_new, gate = map(_inner_contiguous, (q, k_new, v_new, gate))
+    if out is None:
+        out = torch.empty((batch, num_q_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    assert out.is_contiguous() and out.shape == (batch, num_q_heads * head_dim)
+    _lib.call("b200_fused_decode_attention", _ptr(q), q.stride(0), q.stride(1), _ptr(k_new), k_new.stride(0),
+              k_new.stride(1), _ptr(v_new), v_new.stride(0), v_new.stride(1), _ptr(gate), gate.stride(0),
+              _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), k_cache.stride(1), k_cache.stride(2), v_cache.stride(0),
+              v_cache.stride(1), v_cache.stride(2), _ptr(block_table), block_table.stride(0), _ptr(pos),
+              _ptr(inv_freq), int(rotary_dim), _ptr(out), _ptr(workspace), batch, num_q_heads, num_kv_heads, head_dim,
+              _stream())
+    return out
+
+
+# =========================================================================== rope / gate
+@torch.library.custom_op("wy_lib::partial_rope", mutates_args=(), device_types="cuda")
+def partial_rope(x: torch.Tensor, position_ids: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int) -> torch.Tensor:
+    """Replaces triton_kernels/partial_rope.py:145-198."""
+    assert x.ndim == 4
+    assert x.dtype == torch.bfloat16
+    assert position_ids.ndim == 2
+    assert position_ids.dtype in (torch.int32, torch.int64)
+    assert inv_freq.ndim == 1 and inv_freq.dtype == torch.float32
+    assert x.device == position_ids.device == inv_freq.device
+    batch_size, num_heads, token_num, head_dim = x.shape
+    assert position_ids.shape == (batch_size, token_num)
+    assert rotary_dim > 0 and rotary_dim <= head_dim and rotary_dim % 2 == 0
+    assert inv_freq.shape == (rotary_dim // 2,)
+    _require_cuda(x)
+    x = _inner_contiguous(x)
+    out = torch.empty_like(x)
+    assert out.stride(3) == 1
+    _lib.call("b200_partial_rope", _ptr(x), x.stride(0), x.stride(1), x.stride(2), _ptr(out), out.stride(0),
+              out.stride(1), out.stride(2), _ptr(position_ids), int(position_ids.dtype == torch.int64),
+              position_ids.stride(0), position_ids.stride(1), _ptr(inv_freq.contiguous()), batch_size, num_heads,
+              token_num, head_dim, int(rotary_dim), _stream())
+    return out
+
+
+@partial_rope.register_fake
+def _(x, position_ids, inv_freq, rotary_dim) -> torch.Tensor:
+    return torch.empty_like(x)
+
+
+@torch.library.custom_op("wy_lib::attention_gate_pack", mutates_args=(), device_types="cuda")
+def attention_gate_pack(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """Replaces triton_kernels/attention_gate_pack.py:77-126."""
+    assert x.ndim == 4 and gate.ndim == 4
+    assert x.shape == gate.shape
+    assert x.dtype == torch.bfloat16 and gate.dtype == torch.bfloat16
+    assert x.device == gate.device
+    batch_size, num_heads, token_num, head_dim = x.shape
+    assert batch_size == 1
+    assert token_num > 0
+    assert head_dim > 0
+    _require_cuda(x, gate)
+    x, gate = _inner_contiguous(x), _inner_contiguous(gate)
+    out = torch.empty((token_num, num_heads * head_dim), dtype=x.dtype, device=x.device)
+    _lib.call("b200_attention_gate_pack", _ptr(x), x.stride(1), x.stride(2), _ptr(gate), gate.stride(1), gate.stride(2),
+              _ptr(out), num_heads, token_num, head_dim, _stream())
+    return out
+
+
+@attention_gate_pack.register_fake
+def _(x, gate) -> torch.Tensor:
+    return torch.empty((x.shape[2], x.shape[1] * x.shape[3]), dtype=x.dtype, device=x.device)
+
+
+# =========================================================================== Gated DeltaNet
+def _check_gdn(q, k, v, beta, g):
+    assert q.ndim == 3 and k.ndim == 3 and v.ndim == 3
+    assert q.shape == k.shape
+    assert q.shape[:2] == v.shape[:2]
+    assert beta.ndim == 2 and g.ndim == 2
+    assert beta.shape == g.shape == q.shape[:2]
+    assert q.dtype == torch.bfloat16
+    assert k.dtype == torch.bfloat16
+    assert v.dtype == torch.bfloat16
+    assert beta.dtype == torch.float32 and g.dtype == torch.float32
+    assert q.device == k.device == v.device == beta.device == g.device
+    _require_cuda(q)
+
+
+@torch.library.custom_op("wy_lib::gdn_recurrent_decode", mutates_args=("state",), device_types="cuda")
+def gdn_recurrent_decode(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, g: torch.Tensor,
+                         state: torch.Tensor) -> torch.Tensor:
+    """Replaces triton_kernels/gdn_recurrent_prefill.py:1185-1259.  `state` [B,H,DK,DV] fp32 is updated in place."""
+    _check_gdn(q, k, v, beta, g)
+    assert state.dtype == torch.float32 and state.device == q.device
+    batch, num_heads, key_dim = q.shape
+    value_dim = v.shape[-1]
+    assert state.shape == (batch, num_heads, key_dim, value_dim), (
+        f"state must be [B,H,DK,DV]={(batch, num_heads, key_dim, value_dim)}, got {tuple(state.shape)}")
+    assert state.stride(3) == 1 and state.stride(2) == value_dim
+    q, k, v = map(_inner_contiguous, (q, k, v))
+    out = torch.empty_like(v)
+    assert out.stride(2) == 1
+    _lib.call("b200_gdn_recurrent_decode", _ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1),
+              _ptr(v), v.stride(0), v.stride(1), _ptr(beta), beta.stride(0), beta.stride(1), _ptr(g), g.stride(0),
+              g.stride(1), _ptr(state), state.stride(0), state.stride(1), _ptr(out), out.stride(0), out.stride(1),
+              batch, num_heads, key_dim, value_dim, _stream())
+    return out
+
+
+@gdn_recurrent_decode.register_fake
+def _(q, k, v, beta, g, state) -> torch.Tensor:
+    return torch.empty_like(v)
+
+
+@torch.library.custom_op("wy_lib::gdn_recurrent_prefill_sequential", mutates_args=(), device_types="cuda")
+def gdn_recurrent_prefill_sequential(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor,
+                                     g: torch.Tensor,
+                                     cu_seqlens: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """Replaces triton_kernels/gdn_recurrent_prefill.py:1050-1145.  Returns (out [T,H,DV] bf16, state); state is
+    [B,H,DK,DV] with cu_seqlens, [H,DK,DV] without."""
+    _check_gdn(q, k, v, beta, g)
+    token_num, num_heads, key_dim = q.shape
+    value_dim = v.shape[-1]
+    assert token_num > 0 and num_heads > 0
+    if cu_seqlens is None:
+        squeeze_state, batch = True, 1
+    else:
+        assert cu_seqlens.dtype == torch.int32 and cu_seqlens.ndim == 1
+        assert int(cu_seqlens[-1]) == token_num, (
+            f"cu_seqlens[-1]={int(cu_seqlens[-1])} does not match the {token_num} packed tokens")
+        squeeze_state, batch = False, cu_seqlens.numel() - 1
+        cu_seqlens = cu_seqlens.contiguous()
+    q, k, v = map(_inner_contiguous, (q, k, v))
+    out = torch.empty_like(v)
+    assert out.stride(2) == 1
+    state = torch.empty((batch, num_heads, key_dim, value_dim), dtype=torch.float32, device=q.device)
+    _lib.call("b200_gdn_recurrent_prefill_sequential", _ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0),
+              k.stride(1), _ptr(v), v.stride(0), v.stride(1), _ptr(beta), beta.stride(0), beta.stride(1), _ptr(g),
+              g.stride(0), g.stride(1), _ptr(cu_seqlens), batch, token_num, _ptr(state), _ptr(out), out.stride(0),
+              out.stride(1), num_heads, key_dim, value_dim, _stream())
+    return out, (state[0] if squeeze_state else state)
+
+
+@gdn_recurrent_prefill_sequential.register_fake
+def _(q, k, v, beta, g, cu_seqlens=None):
+    num_heads, key_dim, value_dim = q.shape[1], q.shape[2], v.shape[2]
+    shape = (num_heads, key_dim, value_dim) if cu_seqlens is None else (cu_seqlens.numel() - 1, num_heads, key_dim, value_dim)
+    return torch.empty_like(v), torch.empty(shape, dtype=torch.float32, device=q.device)

@@ -1,0 +1,443 @@
+// Fused paged GQA decode attention for one layer step:
+//   partial RoPE(q, k_new) at pos[b]  ->  append(k_new, v_new)  ->  attention over pos[b]+1 tokens  ->  sigmoid gate
+// in ONE launch.  It replaces the operator chain of engine/runner.py:482-517 in the reference
+// (partial_rope x2, paged_kv_append, paged_gqa_attention_decode_split, ..._combine, attention_gate_pack; the
+// attention part is call_paged_gqa_attention_decode_triton, triton_kernels/gqa_attention_decode_paged.py:963-994).
+//
+// Work decomposition ("stream-K over pages").  A unit is one KV page of one (sequence, kv head) segment, plus
+// one extra unit per segment for the token being appended.  All units of all segments form one line that is
+// cut into equal ranges, one per CTA; the grid is one CTA per SM whatever the batch or the context lengths,
+// and the cut is recomputed on the device from pos[], so the launch is static and CUDA-graph safe.  Inside a
+// CTA the four warps take the units of a segment piece round-robin, each with a private 3-stage ring of
+// TMA-staged pages (decode_core.cuh), then merge their online-softmax states through shared memory.
+//   - A segment that lies inside one CTA's range is finished there: normalise, round to bf16, multiply by
+//     sigmoid(gate), store.
+//   - A segment cut by a range boundary leaves one partial (m, l, acc[4][256]) per CTA in the workspace; the
+//     last CTA to arrive (a counter per segment) merges them and finishes the segment.  No CTA ever waits for
+//     another one, so nothing depends on co-residency.
+// The appended token never takes the cross-CTA write-then-read path that makes the reference keep the append
+// in its own launch (gqa_attention_decode_paged.py:332-334): its K/V rows are built in shared memory by the warp
+// that owns the segment's extra unit and stored to the cache from there; page readers mask that slot.
+#include "b200_attn.h"
+#include "decode_core.cuh"
+
+namespace b200 {
+
+constexpr int FD_WARPS = 4;
+constexpr int FD_THREADS = FD_WARPS * 32;
+constexpr int FD_STAGES = 3;
+constexpr int FD_MAX_BATCH = 1024;                     // prefix table lives in shared memory
+constexpr int FD_MAX_SEGMENTS = 2048;                  // counters in the workspace
+constexpr int FD_MAX_CTAS = 256;                       // partial slots in the workspace
+constexpr int FD_TILE_FLOATS = GROUP * HEAD_DIM;       // 1024 accumulator floats per partial
+constexpr int FD_PARTIAL_FLOATS = FD_TILE_FLOATS + 8;  // + m[4], l[4]
+constexpr int64_t FD_COUNTER_BYTES = FD_MAX_SEGMENTS * 4;
+constexpr int64_t FD_WORKSPACE_BYTES = FD_COUNTER_BYTES + int64_t(FD_MAX_CTAS) * 2 * FD_PARTIAL_FLOATS * 4;
+
+constexpr int FD_SMEM_STAGES = FD_WARPS * FD_STAGES * STAGE_BYTES;
+constexpr int FD_SMEM_MERGE = FD_WARPS * FD_PARTIAL_FLOATS * 4;
+constexpr int FD_SMEM_CUM = ((FD_MAX_BATCH + 1) * 4 + 15) / 16 * 16;
+constexpr int FD_SMEM_TOTAL = FD_SMEM_STAGES + FD_SMEM_MERGE + FD_SMEM_CUM + 128;
+
+struct FusedDecodeParams {
+  const __nv_bfloat16 *q, *k_new, *v_new, *gate;
+  __nv_bfloat16 *k_cache, *v_cache, *out;
+  int64_t q_b, q_h, kn_b, kn_h, vn_b, vn_h, gate_b;
+  int64_t kc_p, kc_h, kc_s, vc_p, vc_h, vc_s, bt_b;
+  const int32_t* block_table;
+  const int64_t* pos;
+  const float* inv_freq;
+  float* partials;
+  int* counters;
+  int* err;
+  int batch, num_kv_heads, rotary_half;
+  float scale;
+};
+
+// Position of a (sequence, kv head) segment on the unit line.  units = old pages + 1 (the appended token).
+struct Segment {
+  int b, h, start, end;
+};
+
+__device__ __forceinline__ Segment segment_of_unit(int u, const int* cum, int batch, int heads) {
+  int lo = 0, hi = batch - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (heads * cum[mid] <= u) lo = mid; else hi = mid - 1;
+  }
+  Segment s;
+  s.b = lo;
+  const int units = cum[lo + 1] - cum[lo];
+  s.h = (u - heads * cum[lo]) / units;
+  s.start = heads * cum[lo] + s.h * units;
+  s.end = s.start + units;
+  return s;
+}
+__device__ __forceinline__ void segment_advance(Segment& s, const int* cum, int batch, int heads) {
+  s.start = s.end;
+  if (++s.h == heads) {
+    s.h = 0;
+    ++s.b;
+  }
+  if (s.b < batch) s.end = s.start + (cum[s.b + 1] - cum[s.b]);
+}
+
+// Rotate the Q fragments in place: dims [0, half) pair with [half, 2*half); both partners of a pair sit in the
+// same lane, `half/16` fragment steps apart.  Angles = float(pos) * inv_freq[d], fp32, full-range sincosf, result
+// rounded to bf16 -- the arithmetic of triton_kernels/partial_rope.py:65-113.
+template <int HALF>
+__device__ __forceinline__ void rope_q_fragments(DecodeWarpState& st, const float* __restrict__ inv_freq, float posf,
+                                                 int lane) {
+  const int kk = (lane & 3) * 2;
+  constexpr int steps = HALF / 16;
+#pragma unroll
+  for (int ks = 0; ks < steps; ++ks) {
+    {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int d = ks * 16 + r * 8 + kk;
+        float s0, c0, s1, c1;
+        sincosf(posf * inv_freq[d], &s0, &c0);
+        sincosf(posf * inv_freq[d + 1], &s1, &c1);
+        const uint32_t a = st.qb[ks][r], b = st.qb[ks + steps][r];
+        const float a0 = bf16_lo(a), a1 = bf16_hi(a), b0 = bf16_lo(b), b1 = bf16_hi(b);
+        float f0, g0, f1, g1;
+        rope_pair(a0, b0, s0, c0, f0, g0);
+        rope_pair(a1, b1, s1, c1, f1, g1);
+        st.qb[ks][r] = pack_bf16(f0, f1);
+        st.qb[ks + steps][r] = pack_bf16(g0, g1);
+      }
+    }
+  }
+}
+
+// The appended token as a one-row page: rotated k_new and v_new go to row 0 of the stage and to their slot
+// in the cache.  Each lane owns 8 consecutive dims.
+__device__ __forceinline__ void stage_new_token(uint8_t* stage, const FusedDecodeParams& p, int b, int h, int64_t pos_b,
+                                                int lane) {
+  const uint4 kraw = *reinterpret_cast<const uint4*>(p.k_new + b * p.kn_b + h * p.kn_h + lane * 8);
+  const uint4 vraw = *reinterpret_cast<const uint4*>(p.v_new + b * p.vn_b + h * p.vn_h + lane * 8);
+  uint32_t kw[4] = {kraw.x, kraw.y, kraw.z, kraw.w};
+  const int half = p.rotary_half;
+  if (half > 0) {
+    const int lanes_half = half / 8;  // lanes [0, lanes_half) hold the first halves, the next lanes_half the second
+    const bool in_rot = lane < 2 * lanes_half;
+    const bool first = lane < lanes_half;
+    const int partner = first ? lane + lanes_half : lane - lanes_half;
+    uint32_t other[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) other[i] = __shfl_sync(0xffffffffu, kw[i], in_rot ? partner : lane);
+    if (in_rot) {
+      const float posf = static_cast<float>(pos_b);
+      const int dbase = (first ? lane : partner) * 8;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float s0, c0, s1, c1;
+        sincosf(posf * p.inv_freq[dbase + 2 * i], &s0, &c0);
+        sincosf(posf * p.inv_freq[dbase + 2 * i + 1], &s1, &c1);
+        const uint32_t fa = first ? kw[i] : other[i];  // first-half values
+        const uint32_t fb = first ? other[i] : kw[i];  // second-half values
+        const float a0 = bf16_lo(fa), a1 = bf16_hi(fa), b0 = bf16_lo(fb), b1 = bf16_hi(fb);
+        float f0, g0, f1, g1;
+        rope_pair(a0, b0, s0, c0, f0, g0);
+        rope_pair(a1, b1, s1, c1, f1, g1);
+        kw[i] = first ? pack_bf16(f0, f1) : pack_bf16(g0, g1);
+      }
+    }
+  }
+  const uint4 krot = make_uint4(kw[0], kw[1], kw[2], kw[3]);
+  *reinterpret_cast<uint4*>(stage + lane * 16) = krot;
+  *reinterpret_cast<uint4*>(stage + TILE_BYTES + lane * 16) = vraw;
+  const int64_t phys = p.block_table[b * p.bt_b + pos_b / PAGE];
+  const int64_t slot = pos_b % PAGE;
+  *reinterpret_cast<uint4*>(p.k_cache + phys * p.kc_p + h * p.kc_h + slot * p.kc_s + lane * 8) = krot;
+  *reinterpret_cast<uint4*>(p.v_cache + phys * p.vc_p + h * p.vc_h + slot * p.vc_s + lane * 8) = vraw;
+}
+
+// out = bf16( bf16(acc / l) * sigmoid(gate) ), 8 consecutive dims of one head per thread.
+__device__ __forceinline__ void finish_store(const FusedDecodeParams& p, int b, int hq, int d0, const float (&acc)[8],
+                                             float l) {
+  const int64_t col = static_cast<int64_t>(hq) * HEAD_DIM + d0;
+  const uint4 gv = *reinterpret_cast<const uint4*>(p.gate + b * p.gate_b + col);
+  const uint32_t gs[4] = {gv.x, gv.y, gv.z, gv.w};
+  const float inv_l = 1.f / l;
+  uint32_t os[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float x0 = round_bf16(acc[2 * j] * inv_l), x1 = round_bf16(acc[2 * j + 1] * inv_l);
+    const float g0 = 1.f / (1.f + __expf(-bf16_lo(gs[j]))), g1 = 1.f / (1.f + __expf(-bf16_hi(gs[j])));
+    os[j] = pack_bf16(x0 * g0, x1 * g1);
+  }
+  const int64_t row = static_cast<int64_t>(p.num_kv_heads) * GROUP * HEAD_DIM;
+  *reinterpret_cast<uint4*>(p.out + b * row + col) = make_uint4(os[0], os[1], os[2], os[3]);
+}
+
+__global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __grid_constant__ FusedDecodeParams p) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  __shared__ uint64_t bars[FD_WARPS][FD_STAGES];
+  __shared__ int s_last;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  float* merge = reinterpret_cast<float*>(smem + FD_SMEM_STAGES);
+  int* cum = reinterpret_cast<int*>(smem + FD_SMEM_STAGES + FD_SMEM_MERGE);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int heads = p.num_kv_heads, batch = p.batch;
+  uint8_t* my_stages = smem + warp * FD_STAGES * STAGE_BYTES;
+  if (lane == 0) {
+    for (int s = 0; s < FD_STAGES; ++s) mbar_init(&bars[warp][s], 1);
+    mbar_fence_init();
+  }
+
+  // ---- exclusive prefix of units per sequence: units_b = cdiv(pos[b], 16) + 1
+  for (int b = tid; b < batch; b += FD_THREADS) {
+    const int pb = static_cast<int>(p.pos[b]);
+    cum[b + 1] = (pb + PAGE - 1) / PAGE + 1;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int carry = 0;
+    for (int base = 0; base < batch; base += 32) {
+      const int idx = base + lane;
+      int v = (idx < batch) ? cum[idx + 1] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += n;
+      }
+      if (idx < batch) cum[idx + 1] = v + carry;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+    if (lane == 0) cum[0] = 0;
+  }
+  __syncthreads();
+
+  const int total = heads * cum[batch];
+  const int chunk = (total + gridDim.x - 1) / gridDim.x;
+  const int r0 = blockIdx.x * chunk;
+  const int r1 = min(r0 + chunk, total);
+  if (r0 >= r1) return;
+
+  // ---- per-warp issue cursor (runs FD_STAGES units ahead of the consumer)
+  Segment iseg = segment_of_unit(r0, cum, batch, heads);
+  int iu = r0 + warp;          // next unit this warp will issue
+  int issued = 0, consumed = 0;  // ring positions
+  uint32_t phase_bits = 0;
+  bool dead = false;
+
+  auto issue_next = [&]() {
+    for (;;) {
+      const int hi = min(iseg.end, r1);
+      if (iu < hi) {
+        const int j = iu - iseg.start;
+        const int np = iseg.end - iseg.start - 1;
+        const int slot = issued % FD_STAGES;
+        if (j < np) {
+          const int64_t phys = p.block_table[iseg.b * p.bt_b + j];
+          decode_issue_page(my_stages + slot * STAGE_BYTES, &bars[warp][slot],
+                            p.k_cache + phys * p.kc_p + iseg.h * p.kc_h, p.v_cache + phys * p.vc_p + iseg.h * p.vc_h,
+                            p.kc_s, p.vc_s, lane);
+        }
+        ++issued;
+        iu += FD_WARPS;
+        return;
+      }
+      if (iseg.end >= r1) return;  // nothing left in this CTA's range
+      segment_advance(iseg, cum, batch, heads);
+      iu = iseg.start + warp;
+    }
+  };
+  __syncwarp();
+  for (int s = 0; s < FD_STAGES; ++s) issue_next();
+
+  // ---- consumer: CTA-uniform loop over the pieces of this range
+  Segment seg = segment_of_unit(r0, cum, batch, heads);
+  const int hh = tid >> 5, d0 = (tid & 31) * 8;  // element mapping of the merge / finish steps
+  while (seg.start < r1) {
+    const int lo = max(seg.start, r0), hi = min(seg.end, r1);
+    const int np = seg.end - seg.start - 1;
+    const int64_t pos_b = p.pos[seg.b];
+    DecodeWarpState st;
+    decode_state_init(st);
+    if (lo + warp < hi) {
+      decode_load_q(st, p.q + seg.b * p.q_b + (seg.h * GROUP) * p.q_h, p.q_h, lane);
+      if (p.rotary_half == 32) rope_q_fragments<32>(st, p.inv_freq, static_cast<float>(pos_b), lane);
+    }
+    for (int u = lo + warp; u < hi; u += FD_WARPS) {
+      const int j = u - seg.start;
+      const int slot = consumed % FD_STAGES;
+      uint8_t* stage = my_stages + slot * STAGE_BYTES;
+      if (j < np) {
+        if (!dead) {
+          if (mbar_wait_bounded(&bars[warp][slot], (phase_bits >> slot) & 1u)) {
+            phase_bits ^= (1u << slot);
+            decode_consume_page(st, stage, min(PAGE, static_cast<int>(pos_b) - j * PAGE), p.scale, lane);
+          } else {
+            dead = true;
+            if (lane == 0) atomicExch(p.err, 1);
+          }
+        }
+      } else {
+        stage_new_token(stage, p, seg.b, seg.h, pos_b, lane);
+        __syncwarp();
+        decode_consume_page(st, stage, 1, p.scale, lane);
+      }
+      ++consumed;
+      fence_proxy_async();  // generic-proxy writes to this stage (row clears, the appended token) before the next bulk copy
+      __syncwarp();
+      if (!dead) issue_next();
+    }
+
+    // ---- merge the four warps' states
+    float* mine = merge + warp * FD_PARTIAL_FLOATS;
+    if (lane < 2) {
+      mine[lane * 2] = st.m[0];
+      mine[lane * 2 + 1] = st.m[1];
+      mine[4 + lane * 2] = st.l[0];
+      mine[4 + lane * 2 + 1] = st.l[1];
+    }
+    decode_store_acc_smem(st, mine + 8, lane);
+    __syncthreads();
+    float wgt[FD_WARPS], m_all = -INFINITY, l_all = 0.f;
+#pragma unroll
+    for (int w = 0; w < FD_WARPS; ++w) m_all = fmaxf(m_all, merge[w * FD_PARTIAL_FLOATS + hh]);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int w = 0; w < FD_WARPS; ++w) {
+      const float* src = merge + w * FD_PARTIAL_FLOATS;
+      wgt[w] = (src[hh] == -INFINITY) ? 0.f : __expf(src[hh] - m_all);
+      l_all += wgt[w] * src[4 + hh];
+      const float4 x0 = *reinterpret_cast<const float4*>(src + 8 + hh * HEAD_DIM + d0);
+      const float4 x1 = *reinterpret_cast<const float4*>(src + 8 + hh * HEAD_DIM + d0 + 4);
+      acc[0] += wgt[w] * x0.x; acc[1] += wgt[w] * x0.y; acc[2] += wgt[w] * x0.z; acc[3] += wgt[w] * x0.w;
+      acc[4] += wgt[w] * x1.x; acc[5] += wgt[w] * x1.y; acc[6] += wgt[w] * x1.z; acc[7] += wgt[w] * x1.w;
+    }
+    __syncthreads();  // merge buffer free again
+
+    const bool whole = (lo == seg.start) && (hi == seg.end);
+    if (whole) {
+      finish_store(p, seg.b, seg.h * GROUP + hh, d0, acc, l_all);
+    } else {
+      // ---- leave a partial; the last CTA to arrive on this segment merges all of them
+      const int which = (seg.start < r0) ? 0 : 1;
+      float* dst = p.partials + (static_cast<int64_t>(blockIdx.x) * 2 + which) * FD_PARTIAL_FLOATS;
+      if ((tid & 31) == 0) {
+        dst[hh] = m_all;
+        dst[4 + hh] = l_all;
+      }
+      *reinterpret_cast<float4*>(dst + 8 + hh * HEAD_DIM + d0) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      *reinterpret_cast<float4*>(dst + 8 + hh * HEAD_DIM + d0 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      __threadfence();
+      __syncthreads();
+      const int c_first = seg.start / chunk, c_last = (seg.end - 1) / chunk;
+      const int seg_id = seg.b * heads + seg.h;
+      if (tid == 0) {
+        const int old = atomicAdd(p.counters + seg_id, 1);
+        const int last = (old == c_last - c_first);
+        if (last) p.counters[seg_id] = 0;  // ready for the next launch
+        s_last = last;
+      }
+      __syncthreads();
+      if (s_last) {
+        __threadfence();
+        float m_fin = -INFINITY;
+        for (int c = c_first; c <= c_last; ++c) {
+          const float* src = p.partials + (static_cast<int64_t>(c) * 2 + (c == c_first ? 1 : 0)) * FD_PARTIAL_FLOATS;
+          m_fin = fmaxf(m_fin, __ldcg(src + hh));
+        }
+        float l_fin = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+        for (int c = c_first; c <= c_last; ++c) {
+          const float* src = p.partials + (static_cast<int64_t>(c) * 2 + (c == c_first ? 1 : 0)) * FD_PARTIAL_FLOATS;
+          const float wc = __expf(__ldcg(src + hh) - m_fin);
+          l_fin += wc * __ldcg(src + 4 + hh);
+          const float4 x0 = __ldcg(reinterpret_cast<const float4*>(src + 8 + hh * HEAD_DIM + d0));
+          const float4 x1 = __ldcg(reinterpret_cast<const float4*>(src + 8 + hh * HEAD_DIM + d0 + 4));
+          acc[0] += wc * x0.x; acc[1] += wc * x0.y; acc[2] += wc * x0.z; acc[3] += wc * x0.w;
+          acc[4] += wc * x1.x; acc[5] += wc * x1.y; acc[6] += wc * x1.z; acc[7] += wc * x1.w;
+        }
+        finish_store(p, seg.b, seg.h * GROUP + hh, d0, acc, l_fin);
+      }
+      __syncthreads();  // s_last is reused by the next piece
+    }
+    segment_advance(seg, cum, batch, heads);
+  }
+  if (dead) {
+    for (int s = 0; s < FD_STAGES; ++s) mbar_wait_bounded(&bars[warp][s], (phase_bits >> s) & 1u, 1u << 16);
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int64_t b200_fused_decode_workspace_bytes(void) { return FD_WORKSPACE_BYTES; }
+
+extern "C" int b200_fused_decode_attention(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_new,
+                                           int64_t kn_stride_b, int64_t kn_stride_h, const void* v_new,
+                                           int64_t vn_stride_b, int64_t vn_stride_h, const void* gate,
+                                           int64_t gate_stride_b, void* k_cache, void* v_cache, int64_t kc_stride_p,
+                                           int64_t kc_stride_h, int64_t kc_stride_s, int64_t vc_stride_p,
+                                           int64_t vc_stride_h, int64_t vc_stride_s, const int32_t* block_table,
+                                           int64_t bt_stride_b, const int64_t* pos, const float* inv_freq,
+                                           int32_t rotary_dim, void* out, void* workspace, int32_t batch,
+                                           int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                                           b200_stream_t stream) {
+  B200_REQUIRE(batch > 0 && batch <= FD_MAX_BATCH, "fused_decode_attention: batch must be in [1, %d] (got %d)",
+               FD_MAX_BATCH, batch);
+  B200_REQUIRE(head_dim == HEAD_DIM, "fused_decode_attention: head_dim must be %d (got %d)", HEAD_DIM, head_dim);
+  B200_REQUIRE(num_kv_heads > 0 && num_q_heads == num_kv_heads * GROUP && batch * num_kv_heads <= FD_MAX_SEGMENTS,
+               "fused_decode_attention: needs %d Q heads per KV head and batch*H_kv <= %d", GROUP, FD_MAX_SEGMENTS);
+  B200_REQUIRE(rotary_dim == 0 || rotary_dim == 64, "fused_decode_attention: rotary_dim must be 64 or 0 (got %d)",
+               rotary_dim);
+  B200_REQUIRE(rotary_dim == 0 || inv_freq != nullptr, "fused_decode_attention: inv_freq is NULL");
+  B200_REQUIRE(workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) % 256 == 0),
+               "fused_decode_attention: workspace must be 256-byte aligned");
+  const bool strides_ok = (q_stride_b % 8 == 0) && (q_stride_h % 8 == 0) && (kn_stride_b % 8 == 0) &&
+                          (kn_stride_h % 8 == 0) && (vn_stride_b % 8 == 0) && (vn_stride_h % 8 == 0) &&
+                          (gate_stride_b % 8 == 0) && (kc_stride_p % 8 == 0) && (kc_stride_h % 8 == 0) &&
+                          (kc_stride_s % 8 == 0) && (vc_stride_p % 8 == 0) && (vc_stride_h % 8 == 0) &&
+                          (vc_stride_s % 8 == 0);
+  B200_REQUIRE(strides_ok && aligned16(q) && aligned16(k_new) && aligned16(v_new) && aligned16(gate) &&
+                   aligned16(k_cache) && aligned16(v_cache) && aligned16(out),
+               "fused_decode_attention: tensors must be 16-byte aligned with strides that are multiples of 8");
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(fused_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FD_SMEM_TOTAL) !=
+        cudaSuccess)
+      return fail(ERR_RUNTIME, "fused_decode_attention: cannot raise dynamic shared memory to %d", FD_SMEM_TOTAL);
+    configured[dev] = true;
+  }
+  FusedDecodeParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k_new = static_cast<const __nv_bfloat16*>(k_new);
+  p.v_new = static_cast<const __nv_bfloat16*>(v_new);
+  p.gate = static_cast<const __nv_bfloat16*>(gate);
+  p.k_cache = static_cast<__nv_bfloat16*>(k_cache);
+  p.v_cache = static_cast<__nv_bfloat16*>(v_cache);
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.q_b = q_stride_b; p.q_h = q_stride_h;
+  p.kn_b = kn_stride_b; p.kn_h = kn_stride_h;
+  p.vn_b = vn_stride_b; p.vn_h = vn_stride_h;
+  p.gate_b = gate_stride_b;
+  p.kc_p = kc_stride_p; p.kc_h = kc_stride_h; p.kc_s = kc_stride_s;
+  p.vc_p = vc_stride_p; p.vc_h = vc_stride_h; p.vc_s = vc_stride_s;
+  p.bt_b = bt_stride_b;
+  p.block_table = block_table;
+  p.pos = pos;
+  p.inv_freq = inv_freq;
+  p.counters = static_cast<int*>(workspace);
+  p.partials = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + FD_COUNTER_BYTES);
+  p.err = wait_timeout_flag();
+  if (!p.err) return fail(ERR_RUNTIME, "fused_decode_attention: no error flag");
+  p.batch = batch;
+  p.num_kv_heads = num_kv_heads;
+  p.rotary_half = rotary_dim / 2;
+  p.scale = 1.0f / sqrtf(static_cast<float>(head_dim));
+  int grid = sm_count();
+  if (grid > FD_MAX_CTAS) grid = FD_MAX_CTAS;
+  fused_decode_kernel<<<grid, FD_THREADS, FD_SMEM_TOTAL, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  return check_launch("fused_decode_attention");
+}

@@ -1,0 +1,199 @@
+// Reference-compatible split-K pair for paged GQA decode attention:
+//   b200_paged_decode_split   <->  triton_kernels/gqa_attention_decode_paged.py:622-733 (+ op :822-891)
+//   b200_paged_decode_combine <->  triton_kernels/gqa_attention_decode_paged.py:745-817 (+ op :901-939)
+// The page partition (pages_per_split = cdiv(pages_used, 128), split s owns pages
+// [s*pps, min((s+1)*pps, pages_used))) and the scratch layout are the reference's, so either half can be
+// mixed with the reference's other half.  All 128 partials are written, empty ones as (-inf, 0, 0).
+#include "b200_attn.h"
+#include "decode_core.cuh"
+
+namespace b200 {
+
+constexpr int SPLIT_WARPS = 4;
+constexpr int SPLIT_STAGES = 2;
+constexpr int SPLIT_SMEM = SPLIT_WARPS * SPLIT_STAGES * STAGE_BYTES + 128;
+
+// One warp per (sequence, kv head, split).  grid.x = B * H_kv * 128 / SPLIT_WARPS: static in B, so the launch
+// is CUDA-graph safe; everything length-dependent comes from pos[] on the device.
+__global__ void __launch_bounds__(SPLIT_WARPS * 32)
+paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_b, int64_t q_h,
+                          const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+                          int64_t kc_p, int64_t kc_h, int64_t kc_s, int64_t vc_p, int64_t vc_h, int64_t vc_s,
+                          const int32_t* __restrict__ block_table, int64_t bt_b, float* __restrict__ m_partial,
+                          float* __restrict__ l_partial, float* __restrict__ acc_partial,
+                          const int64_t* __restrict__ pos, int num_kv_heads, float scale, int* __restrict__ err) {
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  __shared__ uint64_t bars[SPLIT_WARPS][SPLIT_STAGES];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  uint8_t* my_stages = smem + warp * SPLIT_STAGES * STAGE_BYTES;
+  if (lane == 0) {
+    for (int s = 0; s < SPLIT_STAGES; ++s) mbar_init(&bars[warp][s], 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+
+  const int item = blockIdx.x * SPLIT_WARPS + warp;
+  const int split = item % MAX_SPLITS;
+  const int h = (item / MAX_SPLITS) % num_kv_heads;
+  const int b = item / (MAX_SPLITS * num_kv_heads);
+  const int num_q_heads = num_kv_heads * GROUP;
+
+  const int seq_len = static_cast<int>(pos[b]) + 1;
+  const int pages_used = (seq_len + PAGE - 1) / PAGE;
+  const int pps = (pages_used + MAX_SPLITS - 1) / MAX_SPLITS;
+  const int page_start = split * pps;
+  const int page_end = min(page_start + pps, pages_used);
+  const int n_pages = max(page_end - page_start, 0);
+
+  DecodeWarpState st;
+  decode_state_init(st);
+  const int32_t* table = block_table + b * bt_b;
+  const __nv_bfloat16* kh = k_cache + h * kc_h;
+  const __nv_bfloat16* vh = v_cache + h * vc_h;
+
+  if (n_pages > 0) {
+    decode_load_q(st, q + b * q_b + (h * GROUP) * q_h, q_h, lane);
+    // prologue: fill the ring
+    for (int i = 0; i < min(n_pages, SPLIT_STAGES); ++i) {
+      const int64_t phys = table[page_start + i];
+      decode_issue_page(my_stages + i * STAGE_BYTES, &bars[warp][i], kh + phys * kc_p, vh + phys * vc_p, kc_s, vc_s,
+                        lane);
+    }
+    bool ok = true;
+    for (int i = 0; i < n_pages; ++i) {
+      const int stage = i % SPLIT_STAGES;
+      const uint32_t parity = (i / SPLIT_STAGES) & 1;
+      if (!mbar_wait_bounded(&bars[warp][stage], parity)) {
+        ok = false;
+        break;
+      }
+      const int lp = page_start + i;
+      const int valid = min(PAGE, seq_len - lp * PAGE);
+      decode_consume_page(st, my_stages + stage * STAGE_BYTES, valid, scale, lane);
+      __syncwarp();
+      if (i + SPLIT_STAGES < n_pages) {
+        const int64_t phys = table[lp + SPLIT_STAGES];
+        decode_issue_page(my_stages + stage * STAGE_BYTES, &bars[warp][stage], kh + phys * kc_p, vh + phys * vc_p,
+                          kc_s, vc_s, lane);
+      }
+    }
+    if (!ok) {
+      if (lane == 0) atomicExch(err, 1);
+      // copies may still be in flight into this CTA's shared memory: give them a bounded time to land
+      for (int s = 0; s < SPLIT_STAGES; ++s) mbar_wait_bounded(&bars[warp][s], 0, 1u << 16);
+      return;
+    }
+  }
+
+  // ---- store the partial: m, l per head; acc through shared memory for 16-byte coalesced stores
+  const int hq0 = h * GROUP;
+  if (lane < 2) {
+    const int64_t base = (static_cast<int64_t>(b) * num_q_heads + hq0 + lane * 2) * MAX_SPLITS + split;
+    m_partial[base] = st.m[0];
+    m_partial[base + MAX_SPLITS] = st.m[1];
+    l_partial[base] = st.l[0];
+    l_partial[base + MAX_SPLITS] = st.l[1];
+  }
+  float* tile = reinterpret_cast<float*>(my_stages);
+  __syncwarp();
+  decode_store_acc_smem(st, tile, lane);
+  __syncwarp();
+#pragma unroll
+  for (int j = 0; j < GROUP * HEAD_DIM / 4 / 32; ++j) {
+    const int idx = j * 32 + lane;  // float4 index inside the [4][256] tile
+    const int head = idx / (HEAD_DIM / 4), c = idx % (HEAD_DIM / 4);
+    float4 v = reinterpret_cast<const float4*>(tile)[idx];
+    float* dst = acc_partial + ((static_cast<int64_t>(b) * num_q_heads + hq0 + head) * MAX_SPLITS + split) * HEAD_DIM;
+    reinterpret_cast<float4*>(dst)[c] = v;
+  }
+}
+
+// One CTA per (sequence, q head), one thread per output dim.
+__global__ void __launch_bounds__(HEAD_DIM)
+paged_decode_combine_kernel(const float* __restrict__ m_partial, const float* __restrict__ l_partial,
+                            const float* __restrict__ acc_partial, const int64_t* __restrict__ pos,
+                            __nv_bfloat16* __restrict__ out, int num_q_heads) {
+  const int b = blockIdx.x, hq = blockIdx.y, d = threadIdx.x;
+  const int seq_len = static_cast<int>(pos[b]) + 1;
+  const int pages_used = (seq_len + PAGE - 1) / PAGE;
+  const int pps = (pages_used + MAX_SPLITS - 1) / MAX_SPLITS;
+  const int num_active = (pages_used + pps - 1) / pps;
+  const int64_t row = static_cast<int64_t>(b) * num_q_heads + hq;
+  const float* m = m_partial + row * MAX_SPLITS;
+  const float* l = l_partial + row * MAX_SPLITS;
+  const float* acc = acc_partial + row * MAX_SPLITS * HEAD_DIM;
+  __shared__ float alpha_s[MAX_SPLITS];
+  __shared__ float red[2];
+  // warp 0: global max and the rescaled sum of l
+  if (d < 32) {
+    float mx = -INFINITY;
+    for (int s = d; s < num_active; s += 32) mx = fmaxf(mx, m[s]);
+    mx = warp_max(mx);
+    float lsum = 0.f;
+    for (int s = d; s < num_active; s += 32) {
+      const float a = __expf(m[s] - mx);
+      alpha_s[s] = a;
+      lsum += l[s] * a;
+    }
+    lsum = warp_sum(lsum);
+    if (d == 0) red[0] = lsum;
+  }
+  __syncthreads();
+  float sum = 0.f;
+  for (int s = 0; s < num_active; ++s) sum += acc[s * HEAD_DIM + d] * alpha_s[s];
+  out[row * HEAD_DIM + d] = __float2bfloat16_rn(sum / red[0]);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_paged_decode_split(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_cache,
+                                       const void* v_cache, int64_t kc_stride_p, int64_t kc_stride_h,
+                                       int64_t kc_stride_s, int64_t vc_stride_p, int64_t vc_stride_h,
+                                       int64_t vc_stride_s, const int32_t* block_table, int64_t bt_stride_b,
+                                       float* m_partial, float* l_partial, float* acc_partial, const int64_t* pos,
+                                       int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                                       b200_stream_t stream) {
+  B200_REQUIRE(batch > 0, "paged_decode_split: batch must be positive");
+  B200_REQUIRE(head_dim == HEAD_DIM, "paged_decode_split: head_dim must be %d (got %d)", HEAD_DIM, head_dim);
+  B200_REQUIRE(num_kv_heads > 0 && num_q_heads == num_kv_heads * GROUP,
+               "paged_decode_split: needs %d Q heads per KV head (got %d/%d)", GROUP, num_q_heads, num_kv_heads);
+  B200_REQUIRE(aligned16(k_cache) && aligned16(v_cache) && aligned16(acc_partial) && (kc_stride_s % 8 == 0) &&
+                   (vc_stride_s % 8 == 0) && (kc_stride_p % 8 == 0) && (vc_stride_p % 8 == 0) &&
+                   (kc_stride_h % 8 == 0) && (vc_stride_h % 8 == 0),
+               "paged_decode_split: caches and scratch must be 16-byte aligned with strides that are multiples of 8");
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(q) % 4 == 0) && (q_stride_b % 2 == 0) && (q_stride_h % 2 == 0),
+               "paged_decode_split: q must be 4-byte aligned with even strides");
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(paged_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SPLIT_SMEM) !=
+        cudaSuccess)
+      return fail(ERR_RUNTIME, "paged_decode_split: cannot raise dynamic shared memory to %d", SPLIT_SMEM);
+    configured[dev] = true;
+  }
+  int* err = wait_timeout_flag();
+  if (!err) return fail(ERR_RUNTIME, "paged_decode_split: no error flag");
+  const int64_t items = static_cast<int64_t>(batch) * num_kv_heads * MAX_SPLITS;
+  const unsigned grid = static_cast<unsigned>(items / SPLIT_WARPS);
+  paged_decode_split_kernel<<<grid, SPLIT_WARPS * 32, SPLIT_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(q), q_stride_b, q_stride_h, static_cast<const __nv_bfloat16*>(k_cache),
+      static_cast<const __nv_bfloat16*>(v_cache), kc_stride_p, kc_stride_h, kc_stride_s, vc_stride_p, vc_stride_h,
+      vc_stride_s, block_table, bt_stride_b, m_partial, l_partial, acc_partial, pos, num_kv_heads,
+      1.0f / sqrtf(static_cast<float>(head_dim)), err);
+  return check_launch("paged_decode_split");
+}
+
+extern "C" int b200_paged_decode_combine(const float* m_partial, const float* l_partial, const float* acc_partial,
+                                         const int64_t* pos, void* out, int32_t batch, int32_t num_q_heads,
+                                         int32_t head_dim, b200_stream_t stream) {
+  B200_REQUIRE(batch > 0 && num_q_heads > 0 && num_q_heads <= 65535, "paged_decode_combine: bad shape");
+  B200_REQUIRE(head_dim == HEAD_DIM, "paged_decode_combine: head_dim must be %d (got %d)", HEAD_DIM, head_dim);
+  paged_decode_combine_kernel<<<dim3(batch, num_q_heads), HEAD_DIM, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      m_partial, l_partial, acc_partial, pos, static_cast<__nv_bfloat16*>(out), num_q_heads);
+  return check_launch("paged_decode_combine");
+}
+

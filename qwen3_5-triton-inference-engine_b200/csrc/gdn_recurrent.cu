@@ -1,0 +1,164 @@
+// Gated-DeltaNet delta-rule recurrence, token-serial forms (fp32 state [128 x 128] per head):
+//   b200_gdn_recurrent_decode              <-> triton_kernels/gdn_recurrent_prefill.py:145-246 (+ op :1185-1259)
+//   b200_gdn_recurrent_prefill_sequential  <-> triton_kernels/gdn_recurrent_prefill.py:47-143  (+ op :1050-1145)
+// Per token:  S *= exp(g);  mem = k^T S;  delta = beta (v - mem);  S += k (x) delta;  out = q^T S.
+//
+// Layout: one CTA per (sequence, head), one thread per value column.  A thread keeps its whole column
+// S[0..127][v] in registers, so both column reductions (k^T S and q^T S) are thread-local: no shuffles and
+// no block barriers inside a token.  Global accesses are coalesced along v (a warp touches 128 contiguous
+// bytes per state row).  Decode streams the 64 KiB state once in and once out (HBM-bound); prefill keeps it
+// in registers across the whole sequence (fp32-FMA-bound).
+#include "b200_attn.h"
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int GDN_THREADS = GDN_D;  // one thread per value column
+
+// k and q of one token as fp32 in shared memory, read back as broadcast float4.
+__device__ __forceinline__ void gdn_token_update(float (&s)[GDN_D], const float* __restrict__ kf,
+                                                 const float* __restrict__ qf, float eg, float beta, float v,
+                                                 float& out) {
+  float mem0 = 0.f, mem1 = 0.f, mem2 = 0.f, mem3 = 0.f;
+#pragma unroll
+  for (int i = 0; i < GDN_D; i += 4) {
+    const float4 k4 = *reinterpret_cast<const float4*>(kf + i);
+    s[i] *= eg;
+    s[i + 1] *= eg;
+    s[i + 2] *= eg;
+    s[i + 3] *= eg;
+    mem0 = fmaf(k4.x, s[i], mem0);
+    mem1 = fmaf(k4.y, s[i + 1], mem1);
+    mem2 = fmaf(k4.z, s[i + 2], mem2);
+    mem3 = fmaf(k4.w, s[i + 3], mem3);
+  }
+  const float delta = beta * (v - ((mem0 + mem1) + (mem2 + mem3)));
+  float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+  for (int i = 0; i < GDN_D; i += 4) {
+    const float4 k4 = *reinterpret_cast<const float4*>(kf + i);
+    const float4 q4 = *reinterpret_cast<const float4*>(qf + i);
+    s[i] = fmaf(k4.x, delta, s[i]);
+    s[i + 1] = fmaf(k4.y, delta, s[i + 1]);
+    s[i + 2] = fmaf(k4.z, delta, s[i + 2]);
+    s[i + 3] = fmaf(k4.w, delta, s[i + 3]);
+    o0 = fmaf(q4.x, s[i], o0);
+    o1 = fmaf(q4.y, s[i + 1], o1);
+    o2 = fmaf(q4.z, s[i + 2], o2);
+    o3 = fmaf(q4.w, s[i + 3], o3);
+  }
+  out = (o0 + o1) + (o2 + o3);
+}
+
+__global__ void __launch_bounds__(GDN_THREADS)
+gdn_decode_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_b, int64_t q_h, const __nv_bfloat16* __restrict__ k,
+                  int64_t k_b, int64_t k_h, const __nv_bfloat16* __restrict__ v, int64_t v_b, int64_t v_h,
+                  const float* __restrict__ beta, int64_t be_b, int64_t be_h, const float* __restrict__ g, int64_t g_b,
+                  int64_t g_h, float* __restrict__ state, int64_t s_b, int64_t s_h, __nv_bfloat16* __restrict__ out,
+                  int64_t o_b, int64_t o_h, int heads) {
+  __shared__ __align__(16) float kf[GDN_D];
+  __shared__ __align__(16) float qf[GDN_D];
+  const int b = blockIdx.x / heads, h = blockIdx.x % heads, col = threadIdx.x;
+  float* sp = state + b * s_b + h * s_h + col;
+  float s[GDN_D];
+#pragma unroll
+  for (int i = 0; i < GDN_D; ++i) s[i] = __ldcs(sp + i * GDN_D);  // streamed once: evict-first
+  kf[col] = __bfloat162float(k[b * k_b + h * k_h + col]);
+  qf[col] = __bfloat162float(q[b * q_b + h * q_h + col]);
+  const float eg = __expf(g[b * g_b + h * g_h]);
+  const float bt = beta[b * be_b + h * be_h];
+  const float vv = __bfloat162float(v[b * v_b + h * v_h + col]);
+  __syncthreads();
+  float o;
+  gdn_token_update(s, kf, qf, eg, bt, vv, o);
+  out[b * o_b + h * o_h + col] = __float2bfloat16_rn(o);
+#pragma unroll
+  for (int i = 0; i < GDN_D; ++i) __stcs(sp + i * GDN_D, s[i]);
+}
+
+constexpr int SEQ_TILE = 16;  // tokens staged in shared memory per step of the prefill loop
+
+__global__ void __launch_bounds__(GDN_THREADS)
+gdn_sequential_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_t, int64_t q_h,
+                      const __nv_bfloat16* __restrict__ k, int64_t k_t, int64_t k_h,
+                      const __nv_bfloat16* __restrict__ v, int64_t v_t, int64_t v_h, const float* __restrict__ beta,
+                      int64_t be_t, int64_t be_h, const float* __restrict__ g, int64_t g_t, int64_t g_h,
+                      const int32_t* __restrict__ cu_seqlens, int total_tokens, float* __restrict__ state,
+                      __nv_bfloat16* __restrict__ out, int64_t o_t, int64_t o_h, int heads) {
+  __shared__ __align__(16) float kf[SEQ_TILE][GDN_D];
+  __shared__ __align__(16) float qf[SEQ_TILE][GDN_D];
+  __shared__ float vf[SEQ_TILE][GDN_D];
+  __shared__ float egf[SEQ_TILE], btf[SEQ_TILE];
+  const int b = blockIdx.x / heads, h = blockIdx.x % heads, col = threadIdx.x;
+  const int seq_start = cu_seqlens ? cu_seqlens[b] : 0;
+  const int seq_len = (cu_seqlens ? cu_seqlens[b + 1] : total_tokens) - seq_start;
+  float s[GDN_D];
+#pragma unroll
+  for (int i = 0; i < GDN_D; ++i) s[i] = 0.f;
+
+  for (int t0 = 0; t0 < seq_len; t0 += SEQ_TILE) {
+    const int nt = min(SEQ_TILE, seq_len - t0);
+    __syncthreads();  // previous tile fully consumed
+    for (int j = 0; j < nt; ++j) {
+      const int64_t t = seq_start + t0 + j;
+      kf[j][col] = __bfloat162float(k[t * k_t + h * k_h + col]);
+      qf[j][col] = __bfloat162float(q[t * q_t + h * q_h + col]);
+      vf[j][col] = __bfloat162float(v[t * v_t + h * v_h + col]);
+    }
+    if (col < nt) {
+      const int64_t t = seq_start + t0 + col;
+      egf[col] = __expf(g[t * g_t + h * g_h]);
+      btf[col] = beta[t * be_t + h * be_h];
+    }
+    __syncthreads();
+    for (int j = 0; j < nt; ++j) {
+      float o;
+      gdn_token_update(s, kf[j], qf[j], egf[j], btf[j], vf[j][col], o);
+      out[(seq_start + t0 + j) * o_t + h * o_h + col] = __float2bfloat16_rn(o);
+    }
+  }
+  float* sp = state + (static_cast<int64_t>(b) * heads + h) * GDN_D * GDN_D + col;
+#pragma unroll
+  for (int i = 0; i < GDN_D; ++i) sp[i * GDN_D] = s[i];
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_gdn_recurrent_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k,
+                                         int64_t k_stride_b, int64_t k_stride_h, const void* v, int64_t v_stride_b,
+                                         int64_t v_stride_h, const float* beta, int64_t beta_stride_b,
+                                         int64_t beta_stride_h, const float* g, int64_t g_stride_b, int64_t g_stride_h,
+                                         float* state, int64_t state_stride_b, int64_t state_stride_h, void* out,
+                                         int64_t out_stride_b, int64_t out_stride_h, int32_t batch, int32_t num_heads,
+                                         int32_t key_dim, int32_t value_dim, b200_stream_t stream) {
+  B200_REQUIRE(batch > 0 && num_heads > 0, "gdn_recurrent_decode: empty shape");
+  B200_REQUIRE(key_dim == GDN_D && value_dim == GDN_D, "gdn_recurrent_decode: key/value dim must be %d (got %d/%d)",
+               GDN_D, key_dim, value_dim);
+  gdn_decode_kernel<<<static_cast<unsigned>(batch) * num_heads, GDN_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(q), q_stride_b, q_stride_h, static_cast<const __nv_bfloat16*>(k), k_stride_b,
+      k_stride_h, static_cast<const __nv_bfloat16*>(v), v_stride_b, v_stride_h, beta, beta_stride_b, beta_stride_h, g,
+      g_stride_b, g_stride_h, state, state_stride_b, state_stride_h, static_cast<__nv_bfloat16*>(out), out_stride_b,
+      out_stride_h, num_heads);
+  return check_launch("gdn_recurrent_decode");
+}
+
+extern "C" int b200_gdn_recurrent_prefill_sequential(
+    const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k, int64_t k_stride_t, int64_t k_stride_h,
+    const void* v, int64_t v_stride_t, int64_t v_stride_h, const float* beta, int64_t beta_stride_t,
+    int64_t beta_stride_h, const float* g, int64_t g_stride_t, int64_t g_stride_h, const int32_t* cu_seqlens,
+    int32_t batch, int32_t total_tokens, float* state, void* out, int64_t out_stride_t, int64_t out_stride_h,
+    int32_t num_heads, int32_t key_dim, int32_t value_dim, b200_stream_t stream) {
+  B200_REQUIRE(batch > 0 && num_heads > 0 && total_tokens > 0, "gdn_recurrent_prefill_sequential: empty shape");
+  B200_REQUIRE(key_dim == GDN_D && value_dim == GDN_D,
+               "gdn_recurrent_prefill_sequential: key/value dim must be %d (got %d/%d)", GDN_D, key_dim, value_dim);
+  B200_REQUIRE(cu_seqlens != nullptr || batch == 1, "gdn_recurrent_prefill_sequential: batch > 1 needs cu_seqlens");
+  gdn_sequential_kernel<<<static_cast<unsigned>(batch) * num_heads, GDN_THREADS, 0,
+                          reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(q), q_stride_t, q_stride_h, static_cast<const __nv_bfloat16*>(k), k_stride_t,
+      k_stride_h, static_cast<const __nv_bfloat16*>(v), v_stride_t, v_stride_h, beta, beta_stride_t, beta_stride_h, g,
+      g_stride_t, g_stride_h, cu_seqlens, total_tokens, state, static_cast<__nv_bfloat16*>(out), out_stride_t,
+      out_stride_h, num_heads);
+  return check_launch("gdn_recurrent_prefill_sequential");
+}
