@@ -242,9 +242,10 @@ def test_decode_under_cuda_graph(ops):
     out_s = torch.empty(3, 2048, dtype=torch.bfloat16, device=DEV)
     kc, vc = d["k_cache"].clone(), d["v_cache"].clone()
     pos0, kc0, vc0 = pos.clone(), kc.clone(), vc.clone()
+    inv_d = inv.to(DEV)
 
     def step():
-        ops.fused_decode_attention(q_s, k_s, v_s, d["gate"], kc, vc, d["block_table"], pos, inv.to(DEV), 64, ws, out=out_s)
+        ops.fused_decode_attention(q_s, k_s, v_s, d["gate"], kc, vc, d["block_table"], pos, inv_d, 64, ws, out=out_s)
         pos.add_(1)
 
     side = torch.cuda.Stream()
