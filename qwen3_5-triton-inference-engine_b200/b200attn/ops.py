@@ -365,3 +365,76 @@ def _(q, k, v, beta, g, cu_seqlens=None):
     num_heads, key_dim, value_dim = q.shape[1], q.shape[2], v.shape[2]
     shape = (num_heads, key_dim, value_dim) if cu_seqlens is None else (cu_seqlens.numel() - 1, num_heads, key_dim, value_dim)
     return torch.empty_like(v), torch.empty(shape, dtype=torch.float32, device=q.device)
+
+
+# =========================================================================== varlen causal prefill attention
+@torch.library.custom_op("wy_lib::gqa_attention_varlen_causal", mutates_args=(), device_types="cuda")
+def gqa_attention_varlen_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor,
+                                max_seqlen: int) -> torch.Tensor:
+    """Replaces triton_kernels/gqa_attention_varlen_causal.py:214-278.  q [T,H_q,D], k/v [T,H_kv,D] bf16 packed;
+    `max_seqlen` is a host int that only sizes the grid."""
+    assert q.dtype == torch.bfloat16 and k.dtype == v.dtype == torch.bfloat16
+    assert q.ndim == 3 and k.ndim == 3 and v.ndim == 3
+    assert cu_seqlens.dtype == torch.int32 and cu_seqlens.ndim == 1
+    total_tokens, num_q_head, d_model = q.shape
+    assert k.shape == v.shape
+    assert k.shape[0] == total_tokens and k.shape[2] == d_model
+    num_kv_head = k.shape[1]
+    assert num_q_head % num_kv_head == 0
+    batch = cu_seqlens.numel() - 1
+    assert batch >= 1
+    _require_cuda(q, k, v, cu_seqlens)
+    q, k, v = map(_inner_contiguous, (q, k, v))
+    out = torch.empty_like(q)
+    assert out.stride(2) == 1
+    _lib.call("b200_gqa_varlen_causal", _ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1), _ptr(v),
+              v.stride(0), v.stride(1), _ptr(out), out.stride(0), out.stride(1), _ptr(cu_seqlens.contiguous()), batch,
+              int(max_seqlen), num_q_head, num_kv_head, d_model, _stream())
+    return out
+
+
+@gqa_attention_varlen_causal.register_fake
+def _(q, k, v, cu_seqlens, max_seqlen) -> torch.Tensor:
+    return torch.empty_like(q)
+
+
+def build_cu_seqlens(lengths, *, device="cuda"):
+    """Length list -> (cu_seqlens [B+1] int32, max_seqlen).  triton_kernels/gqa_attention_varlen_causal.py:288-298."""
+    cu = [0]
+    for n in lengths:
+        cu.append(cu[-1] + n)
+    return torch.tensor(cu, dtype=torch.int32, device=device), (max(lengths) if lengths else 0)
+
+
+def fused_prefill_attention(q, k, v, gate, k_cache, v_cache, block_table, cu_seqlens, position_ids, inv_freq,
+                            rotary_dim, max_seqlen, out=None) -> torch.Tensor:
+    """RoPE(q, k) + packed causal attention + sigmoid gate + paged KV scatter (two launches) -> [T, H_q*D] bf16.
+    q [T,H_q,D], k/v [T,H_kv,D] are the post-norm, PRE-RoPE projections (any token/head strides); gate [T, H_q*D];
+    position_ids [1,T] or [T] int32/int64, restarting at every sequence."""
+    total, num_q_heads, head_dim = q.shape
+    num_kv_heads = k.shape[1]
+    assert k.shape == v.shape == (total, num_kv_heads, head_dim)
+    assert gate.shape == (total, num_q_heads * head_dim)
+    assert q.dtype == k.dtype == v.dtype == gate.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
+    assert k_cache.shape[1:] == (num_kv_heads, PAGE_SIZE, head_dim) and v_cache.shape == k_cache.shape
+    assert cu_seqlens.dtype == torch.int32 and cu_seqlens.ndim == 1 and cu_seqlens.is_contiguous()
+    batch = cu_seqlens.numel() - 1
+    assert block_table.dtype == torch.int32 and block_table.shape[0] == batch and block_table.stride(1) == 1
+    assert block_table.shape[1] >= (max_seqlen + PAGE_SIZE - 1) // PAGE_SIZE
+    position_ids = position_ids.reshape(-1)
+    assert position_ids.numel() == total and position_ids.dtype in (torch.int32, torch.int64)
+    assert position_ids.is_contiguous()
+    assert inv_freq.dtype == torch.float32 and inv_freq.shape == (rotary_dim // 2,) and inv_freq.is_contiguous()
+    assert k_cache.stride(3) == 1 and v_cache.stride(3) == 1
+    _require_cuda(q, k, v, gate, k_cache, v_cache, block_table, cu_seqlens, position_ids, inv_freq)
+    q, k, v, gate = map(_inner_contiguous, (q, k, v, gate))
+    if out is None:
+        out = torch.empty((total, num_q_heads * head_dim), dtype=torch.bfloat16, device=q.device)
+    assert out.is_contiguous() and out.shape == (total, num_q_heads * head_dim)
+    _lib.call("b200_fused_prefill_attention", _ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1),
+              _ptr(v), v.stride(0), v.stride(1), _ptr(gate), gate.stride(0), _ptr(k_cache), _ptr(v_cache),
+              k_cache.stride(0), k_cache.stride(1), k_cache.stride(2), v_cache.stride(0), v_cache.stride(1),
+              v_cache.stride(2), _ptr(block_table), block_table.stride(0), _ptr(cu_seqlens), _ptr(position_ids),
+              int(position_ids.dtype == torch.int64), _ptr(inv_freq), int(rotary_dim), _ptr(out), batch,
+              int(max_seqlen), num_q_heads, num_kv_heads, head_dim, _stream())
+    return out

@@ -8,8 +8,8 @@
 // one extra unit per segment for the token being appended.  All units of all segments form one line that is
 // cut into equal ranges, one per CTA; the grid is one CTA per SM whatever the batch or the context lengths,
 // and the cut is recomputed on the device from pos[], so the launch is static and CUDA-graph safe.  Inside a
-// CTA the four warps take the units of a segment piece round-robin, each with a private 3-stage ring of
-// TMA-staged pages (decode_core.cuh), then merge their online-softmax states through shared memory.
+// CTA the eight warps take the units of a segment piece round-robin, each with a private ring of three
+// TMA-staged K/V tiles (decode_core.cuh), then merge their online-softmax states through shared memory.
 //   - A segment that lies inside one CTA's range is finished there: normalise, round to bf16, multiply by
 //     sigmoid(gate), store.
 //   - A segment cut by a range boundary leaves one partial (m, l, acc[4][256]) per CTA in the workspace; the
@@ -23,9 +23,10 @@
 
 namespace b200 {
 
-constexpr int FD_WARPS = 4;
+constexpr int FD_WARPS = 8;
 constexpr int FD_THREADS = FD_WARPS * 32;
-constexpr int FD_STAGES = 3;
+constexpr int FD_RING = 3;                             // K/V tiles per warp
+constexpr int FD_MERGE_SLOTS = 4;                      // warps merge in two rounds of four
 constexpr int FD_MAX_BATCH = 1024;                     // prefix table lives in shared memory
 constexpr int FD_MAX_SEGMENTS = 2048;                  // counters in the workspace
 constexpr int FD_MAX_CTAS = 256;                       // partial slots in the workspace
@@ -34,10 +35,10 @@ constexpr int FD_PARTIAL_FLOATS = FD_TILE_FLOATS + 8;  // + m[4], l[4]
 constexpr int64_t FD_COUNTER_BYTES = FD_MAX_SEGMENTS * 4;
 constexpr int64_t FD_WORKSPACE_BYTES = FD_COUNTER_BYTES + int64_t(FD_MAX_CTAS) * 2 * FD_PARTIAL_FLOATS * 4;
 
-constexpr int FD_SMEM_STAGES = FD_WARPS * FD_STAGES * STAGE_BYTES;
-constexpr int FD_SMEM_MERGE = FD_WARPS * FD_PARTIAL_FLOATS * 4;
+constexpr int FD_SMEM_RING = FD_WARPS * FD_RING * TILE_BYTES;
+constexpr int FD_SMEM_MERGE = FD_MERGE_SLOTS * FD_PARTIAL_FLOATS * 4;
 constexpr int FD_SMEM_CUM = ((FD_MAX_BATCH + 1) * 4 + 15) / 16 * 16;
-constexpr int FD_SMEM_TOTAL = FD_SMEM_STAGES + FD_SMEM_MERGE + FD_SMEM_CUM + 128;
+constexpr int FD_SMEM_TOTAL = FD_SMEM_RING + FD_SMEM_MERGE + FD_SMEM_CUM + 128;
 
 struct FusedDecodeParams {
   const __nv_bfloat16 *q, *k_new, *v_new, *gate;
@@ -82,8 +83,8 @@ __device__ __forceinline__ void segment_advance(Segment& s, const int* cum, int 
   if (s.b < batch) s.end = s.start + (cum[s.b + 1] - cum[s.b]);
 }
 
-// Rotate the Q fragments in place: dims [0, half) pair with [half, 2*half); both partners of a pair sit in the
-// same lane, `half/16` fragment steps apart.  Angles = float(pos) * inv_freq[d], fp32, full-range sincosf, result
+// Rotate the Q fragments in place: dims [0, HALF) pair with [HALF, 2*HALF); both partners of a pair sit in the
+// same lane, HALF/16 fragment steps apart.  Angles = float(pos) * inv_freq[d], fp32, full-range sincosf, result
 // rounded to bf16 -- the arithmetic of triton_kernels/partial_rope.py:65-113.
 template <int HALF>
 __device__ __forceinline__ void rope_q_fragments(DecodeWarpState& st, const float* __restrict__ inv_freq, float posf,
@@ -92,31 +93,27 @@ __device__ __forceinline__ void rope_q_fragments(DecodeWarpState& st, const floa
   constexpr int steps = HALF / 16;
 #pragma unroll
   for (int ks = 0; ks < steps; ++ks) {
-    {
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        const int d = ks * 16 + r * 8 + kk;
-        float s0, c0, s1, c1;
-        sincosf(posf * inv_freq[d], &s0, &c0);
-        sincosf(posf * inv_freq[d + 1], &s1, &c1);
-        const uint32_t a = st.qb[ks][r], b = st.qb[ks + steps][r];
-        const float a0 = bf16_lo(a), a1 = bf16_hi(a), b0 = bf16_lo(b), b1 = bf16_hi(b);
-        float f0, g0, f1, g1;
-        rope_pair(a0, b0, s0, c0, f0, g0);
-        rope_pair(a1, b1, s1, c1, f1, g1);
-        st.qb[ks][r] = pack_bf16(f0, f1);
-        st.qb[ks + steps][r] = pack_bf16(g0, g1);
-      }
+    for (int r = 0; r < 2; ++r) {
+      const int d = ks * 16 + r * 8 + kk;
+      float s0, c0, s1, c1;
+      sincosf(posf * inv_freq[d], &s0, &c0);
+      sincosf(posf * inv_freq[d + 1], &s1, &c1);
+      const uint32_t a = st.qb[ks][r], b = st.qb[ks + steps][r];
+      float f0, g0, f1, g1;
+      rope_pair(bf16_lo(a), bf16_lo(b), s0, c0, f0, g0);
+      rope_pair(bf16_hi(a), bf16_hi(b), s1, c1, f1, g1);
+      st.qb[ks][r] = pack_bf16(f0, f1);
+      st.qb[ks + steps][r] = pack_bf16(g0, g1);
     }
   }
 }
 
-// The appended token as a one-row page: rotated k_new and v_new go to row 0 of the stage and to their slot
-// in the cache.  Each lane owns 8 consecutive dims.
-__device__ __forceinline__ void stage_new_token(uint8_t* stage, const FusedDecodeParams& p, int b, int h, int64_t pos_b,
-                                                int lane) {
+// The appended token as a one-row page: the rotated k_new goes to row 0 of `k_tile` and to its slot in the
+// cache.  Each lane owns 8 consecutive dims.
+__device__ __forceinline__ void stage_new_k(uint8_t* k_tile, const FusedDecodeParams& p, int b, int h, int64_t pos_b,
+                                            int lane) {
   const uint4 kraw = *reinterpret_cast<const uint4*>(p.k_new + b * p.kn_b + h * p.kn_h + lane * 8);
-  const uint4 vraw = *reinterpret_cast<const uint4*>(p.v_new + b * p.vn_b + h * p.vn_h + lane * 8);
   uint32_t kw[4] = {kraw.x, kraw.y, kraw.z, kraw.w};
   const int half = p.rotary_half;
   if (half > 0) {
@@ -137,54 +134,68 @@ __device__ __forceinline__ void stage_new_token(uint8_t* stage, const FusedDecod
         sincosf(posf * p.inv_freq[dbase + 2 * i + 1], &s1, &c1);
         const uint32_t fa = first ? kw[i] : other[i];  // first-half values
         const uint32_t fb = first ? other[i] : kw[i];  // second-half values
-        const float a0 = bf16_lo(fa), a1 = bf16_hi(fa), b0 = bf16_lo(fb), b1 = bf16_hi(fb);
         float f0, g0, f1, g1;
-        rope_pair(a0, b0, s0, c0, f0, g0);
-        rope_pair(a1, b1, s1, c1, f1, g1);
+        rope_pair(bf16_lo(fa), bf16_lo(fb), s0, c0, f0, g0);
+        rope_pair(bf16_hi(fa), bf16_hi(fb), s1, c1, f1, g1);
         kw[i] = first ? pack_bf16(f0, f1) : pack_bf16(g0, g1);
       }
     }
   }
   const uint4 krot = make_uint4(kw[0], kw[1], kw[2], kw[3]);
-  *reinterpret_cast<uint4*>(stage + lane * 16) = krot;
-  *reinterpret_cast<uint4*>(stage + TILE_BYTES + lane * 16) = vraw;
+  *reinterpret_cast<uint4*>(k_tile + lane * 16) = krot;
   const int64_t phys = p.block_table[b * p.bt_b + pos_b / PAGE];
-  const int64_t slot = pos_b % PAGE;
-  *reinterpret_cast<uint4*>(p.k_cache + phys * p.kc_p + h * p.kc_h + slot * p.kc_s + lane * 8) = krot;
-  *reinterpret_cast<uint4*>(p.v_cache + phys * p.vc_p + h * p.vc_h + slot * p.vc_s + lane * 8) = vraw;
+  *reinterpret_cast<uint4*>(p.k_cache + phys * p.kc_p + h * p.kc_h + (pos_b % PAGE) * p.kc_s + lane * 8) = krot;
+}
+__device__ __forceinline__ void stage_new_v(uint8_t* v_tile, const FusedDecodeParams& p, int b, int h, int64_t pos_b,
+                                            int lane) {
+  const uint4 vraw = *reinterpret_cast<const uint4*>(p.v_new + b * p.vn_b + h * p.vn_h + lane * 8);
+  *reinterpret_cast<uint4*>(v_tile + lane * 16) = vraw;
+  const int64_t phys = p.block_table[b * p.bt_b + pos_b / PAGE];
+  *reinterpret_cast<uint4*>(p.v_cache + phys * p.vc_p + h * p.vc_h + (pos_b % PAGE) * p.vc_s + lane * 8) = vraw;
 }
 
-// out = bf16( bf16(acc / l) * sigmoid(gate) ), 8 consecutive dims of one head per thread.
-__device__ __forceinline__ void finish_store(const FusedDecodeParams& p, int b, int hq, int d0, const float (&acc)[8],
+// out = bf16( bf16(acc / l) * sigmoid(gate) ), 4 consecutive dims of one head per thread.
+__device__ __forceinline__ void finish_store(const FusedDecodeParams& p, int b, int hq, int d0, const float (&acc)[4],
                                              float l) {
   const int64_t col = static_cast<int64_t>(hq) * HEAD_DIM + d0;
-  const uint4 gv = *reinterpret_cast<const uint4*>(p.gate + b * p.gate_b + col);
-  const uint32_t gs[4] = {gv.x, gv.y, gv.z, gv.w};
+  const uint2 gv = *reinterpret_cast<const uint2*>(p.gate + b * p.gate_b + col);
   const float inv_l = 1.f / l;
-  uint32_t os[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float x0 = round_bf16(acc[2 * j] * inv_l), x1 = round_bf16(acc[2 * j + 1] * inv_l);
-    const float g0 = 1.f / (1.f + __expf(-bf16_lo(gs[j]))), g1 = 1.f / (1.f + __expf(-bf16_hi(gs[j])));
-    os[j] = pack_bf16(x0 * g0, x1 * g1);
-  }
+  const float x0 = round_bf16(acc[0] * inv_l), x1 = round_bf16(acc[1] * inv_l);
+  const float x2 = round_bf16(acc[2] * inv_l), x3 = round_bf16(acc[3] * inv_l);
+  const float g0 = 1.f / (1.f + __expf(-bf16_lo(gv.x))), g1 = 1.f / (1.f + __expf(-bf16_hi(gv.x)));
+  const float g2 = 1.f / (1.f + __expf(-bf16_lo(gv.y))), g3 = 1.f / (1.f + __expf(-bf16_hi(gv.y)));
   const int64_t row = static_cast<int64_t>(p.num_kv_heads) * GROUP * HEAD_DIM;
-  *reinterpret_cast<uint4*>(p.out + b * row + col) = make_uint4(os[0], os[1], os[2], os[3]);
+  *reinterpret_cast<uint2*>(p.out + b * row + col) = make_uint2(pack_bf16(x0 * g0, x1 * g1), pack_bf16(x2 * g2, x3 * g3));
+}
+
+// Fold one exported state (m, l, acc) into a running one with the usual max-rescaling.
+__device__ __forceinline__ void merge_state(float& m_run, float& l_run, float (&acc)[4], float m_in, float l_in,
+                                            const float4& x) {
+  if (m_in == -INFINITY) return;  // empty contribution
+  const float m_new = fmaxf(m_run, m_in);
+  const float s_old = (m_run == -INFINITY) ? 0.f : __expf(m_run - m_new);
+  const float s_in = __expf(m_in - m_new);
+  l_run = l_run * s_old + l_in * s_in;
+  acc[0] = acc[0] * s_old + x.x * s_in;
+  acc[1] = acc[1] * s_old + x.y * s_in;
+  acc[2] = acc[2] * s_old + x.z * s_in;
+  acc[3] = acc[3] * s_old + x.w * s_in;
+  m_run = m_new;
 }
 
 __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __grid_constant__ FusedDecodeParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  __shared__ uint64_t bars[FD_WARPS][FD_STAGES];
+  __shared__ uint64_t bars[FD_WARPS][FD_RING];
   __shared__ int s_last;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
-  float* merge = reinterpret_cast<float*>(smem + FD_SMEM_STAGES);
-  int* cum = reinterpret_cast<int*>(smem + FD_SMEM_STAGES + FD_SMEM_MERGE);
+  float* merge = reinterpret_cast<float*>(smem + FD_SMEM_RING);
+  int* cum = reinterpret_cast<int*>(smem + FD_SMEM_RING + FD_SMEM_MERGE);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int heads = p.num_kv_heads, batch = p.batch;
-  uint8_t* my_stages = smem + warp * FD_STAGES * STAGE_BYTES;
+  uint8_t* ring = smem + warp * FD_RING * TILE_BYTES;
   if (lane == 0) {
-    for (int s = 0; s < FD_STAGES; ++s) mbar_init(&bars[warp][s], 1);
+    for (int s = 0; s < FD_RING; ++s) mbar_init(&bars[warp][s], 1);
     mbar_fence_init();
   }
 
@@ -211,16 +222,24 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
   }
   __syncthreads();
 
+  // equal ranges of units per CTA, but never less than one unit per warp: tiny problems use fewer CTAs and leave
+  // fewer partials to merge
   const int total = heads * cum[batch];
-  const int chunk = (total + gridDim.x - 1) / gridDim.x;
+  const int chunk = max((total + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x), FD_WARPS);
   const int r0 = blockIdx.x * chunk;
   const int r1 = min(r0 + chunk, total);
   if (r0 >= r1) return;
 
-  // ---- per-warp issue cursor (runs FD_STAGES units ahead of the consumer)
+  // ---- per-warp issue cursor: walks the same unit sequence as the consumer, FD_RING tiles ahead.
+  // Tile sequence of a warp: K(u0), V(u0), K(u1), V(u1), ...; tile n lives in ring slot n % FD_RING.
   Segment iseg = segment_of_unit(r0, cum, batch, heads);
-  int iu = r0 + warp;          // next unit this warp will issue
-  int issued = 0, consumed = 0;  // ring positions
+  int iu = r0 + warp;        // unit whose tiles are issued next
+  bool i_is_v = false;       // next tile to issue is the V tile of unit iu
+  int ii = 0;                // index of unit iu among this warp's units of the current piece
+  int win_base = -1;         // first ii covered by the page-id window (-1 = none loaded)
+  int win_phys = 0;          // lane L holds the physical page of this warp's (win_base + L)-th unit of the piece
+  int cur_phys = 0;
+  int issued = 0, consumed = 0;
   uint32_t phase_bits = 0;
   bool dead = false;
 
@@ -230,28 +249,46 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
       if (iu < hi) {
         const int j = iu - iseg.start;
         const int np = iseg.end - iseg.start - 1;
-        const int slot = issued % FD_STAGES;
+        const int slot = issued % FD_RING;
         if (j < np) {
-          const int64_t phys = p.block_table[iseg.b * p.bt_b + j];
-          decode_issue_page(my_stages + slot * STAGE_BYTES, &bars[warp][slot],
-                            p.k_cache + phys * p.kc_p + iseg.h * p.kc_h, p.v_cache + phys * p.vc_p + iseg.h * p.vc_h,
-                            p.kc_s, p.vc_s, lane);
+          if (!i_is_v) {
+            if (win_base < 0 || ii - win_base >= 32) {
+              // one gather of the next 32 page ids of this warp (stride FD_WARPS in the table row)
+              win_base = ii;
+              const int jl = j + lane * FD_WARPS;
+              win_phys = (iu + lane * FD_WARPS < hi && jl < np) ? p.block_table[iseg.b * p.bt_b + jl] : 0;
+            }
+            cur_phys = __shfl_sync(0xffffffffu, win_phys, ii - win_base);
+          }
+          const int64_t phys = cur_phys;
+          if (i_is_v)
+            decode_issue_tile(ring + slot * TILE_BYTES, &bars[warp][slot], p.v_cache + phys * p.vc_p + iseg.h * p.vc_h,
+                              p.vc_s, lane);
+          else
+            decode_issue_tile(ring + slot * TILE_BYTES, &bars[warp][slot], p.k_cache + phys * p.kc_p + iseg.h * p.kc_h,
+                              p.kc_s, lane);
         }
         ++issued;
-        iu += FD_WARPS;
+        if (i_is_v) {
+          iu += FD_WARPS;
+          ++ii;
+        }
+        i_is_v = !i_is_v;
         return;
       }
       if (iseg.end >= r1) return;  // nothing left in this CTA's range
       segment_advance(iseg, cum, batch, heads);
       iu = iseg.start + warp;
+      ii = 0;
+      win_base = -1;
     }
   };
   __syncwarp();
-  for (int s = 0; s < FD_STAGES; ++s) issue_next();
+  for (int s = 0; s < FD_RING; ++s) issue_next();
 
   // ---- consumer: CTA-uniform loop over the pieces of this range
   Segment seg = segment_of_unit(r0, cum, batch, heads);
-  const int hh = tid >> 5, d0 = (tid & 31) * 8;  // element mapping of the merge / finish steps
+  const int hh = tid >> 6, d0 = (tid & 63) * 4;  // element mapping of the merge / finish steps
   while (seg.start < r1) {
     const int lo = max(seg.start, r0), hi = min(seg.end, r1);
     const int np = seg.end - seg.start - 1;
@@ -264,54 +301,66 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
     }
     for (int u = lo + warp; u < hi; u += FD_WARPS) {
       const int j = u - seg.start;
-      const int slot = consumed % FD_STAGES;
-      uint8_t* stage = my_stages + slot * STAGE_BYTES;
-      if (j < np) {
-        if (!dead) {
-          if (mbar_wait_bounded(&bars[warp][slot], (phase_bits >> slot) & 1u)) {
-            phase_bits ^= (1u << slot);
-            decode_consume_page(st, stage, min(PAGE, static_cast<int>(pos_b) - j * PAGE), p.scale, lane);
-          } else {
-            dead = true;
-            if (lane == 0) atomicExch(p.err, 1);
+      const bool is_page = j < np;
+      const int valid = is_page ? min(PAGE, static_cast<int>(pos_b) - j * PAGE) : 1;
+      uint32_t b0 = 0, b1 = 0;
+      float alpha0 = 1.f, alpha1 = 1.f;
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        const int slot = consumed % FD_RING;
+        uint8_t* tile = ring + slot * TILE_BYTES;
+        bool ready = !dead;
+        if (is_page) {
+          if (ready) {
+            if (mbar_wait_bounded(&bars[warp][slot], (phase_bits >> slot) & 1u)) {
+              phase_bits ^= (1u << slot);
+            } else {
+              dead = true;
+              ready = false;
+              if (lane == 0) atomicExch(p.err, 1);
+            }
           }
+        } else {
+          if (part == 0) stage_new_k(tile, p, seg.b, seg.h, pos_b, lane);
+          else stage_new_v(tile, p, seg.b, seg.h, pos_b, lane);
+          __syncwarp();
         }
-      } else {
-        stage_new_token(stage, p, seg.b, seg.h, pos_b, lane);
+        if (ready) {
+          if (part == 0) decode_scores(st, tile, valid, p.scale, lane, b0, b1, alpha0, alpha1);
+          else decode_accumulate(st, tile, valid, b0, b1, alpha0, alpha1, lane);
+        }
+        ++consumed;
+        fence_proxy_async();  // generic-proxy writes to this slot (row clears, the appended token) before the next bulk copy
         __syncwarp();
-        decode_consume_page(st, stage, 1, p.scale, lane);
+        if (!dead) issue_next();
       }
-      ++consumed;
-      fence_proxy_async();  // generic-proxy writes to this stage (row clears, the appended token) before the next bulk copy
-      __syncwarp();
-      if (!dead) issue_next();
     }
+    decode_reduce_l(st);
 
-    // ---- merge the four warps' states
-    float* mine = merge + warp * FD_PARTIAL_FLOATS;
-    if (lane < 2) {
-      mine[lane * 2] = st.m[0];
-      mine[lane * 2 + 1] = st.m[1];
-      mine[4 + lane * 2] = st.l[0];
-      mine[4 + lane * 2 + 1] = st.l[1];
-    }
-    decode_store_acc_smem(st, mine + 8, lane);
-    __syncthreads();
-    float wgt[FD_WARPS], m_all = -INFINITY, l_all = 0.f;
+    // ---- merge the eight warps' states, four at a time
+    float m_all = -INFINITY, l_all = 0.f;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int w = 0; w < FD_WARPS; ++w) m_all = fmaxf(m_all, merge[w * FD_PARTIAL_FLOATS + hh]);
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int round = 0; round < FD_WARPS / FD_MERGE_SLOTS; ++round) {
+      if ((warp / FD_MERGE_SLOTS) == round) {
+        float* mine = merge + (warp % FD_MERGE_SLOTS) * FD_PARTIAL_FLOATS;
+        if (lane < 2) {
+          mine[lane * 2] = st.m[0];
+          mine[lane * 2 + 1] = st.m[1];
+          mine[4 + lane * 2] = st.l[0];
+          mine[4 + lane * 2 + 1] = st.l[1];
+        }
+        decode_store_acc_smem(st, mine + 8, lane);
+      }
+      __syncthreads();
 #pragma unroll
-    for (int w = 0; w < FD_WARPS; ++w) {
-      const float* src = merge + w * FD_PARTIAL_FLOATS;
-      wgt[w] = (src[hh] == -INFINITY) ? 0.f : __expf(src[hh] - m_all);
-      l_all += wgt[w] * src[4 + hh];
-      const float4 x0 = *reinterpret_cast<const float4*>(src + 8 + hh * HEAD_DIM + d0);
-      const float4 x1 = *reinterpret_cast<const float4*>(src + 8 + hh * HEAD_DIM + d0 + 4);
-      acc[0] += wgt[w] * x0.x; acc[1] += wgt[w] * x0.y; acc[2] += wgt[w] * x0.z; acc[3] += wgt[w] * x0.w;
-      acc[4] += wgt[w] * x1.x; acc[5] += wgt[w] * x1.y; acc[6] += wgt[w] * x1.z; acc[7] += wgt[w] * x1.w;
+      for (int w = 0; w < FD_MERGE_SLOTS; ++w) {
+        const float* src = merge + w * FD_PARTIAL_FLOATS;
+        merge_state(m_all, l_all, acc, src[hh], src[4 + hh],
+                    *reinterpret_cast<const float4*>(src + 8 + hh * HEAD_DIM + d0));
+      }
+      __syncthreads();  // merge buffer free again
     }
-    __syncthreads();  // merge buffer free again
 
     const bool whole = (lo == seg.start) && (hi == seg.end);
     if (whole) {
@@ -320,12 +369,11 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
       // ---- leave a partial; the last CTA to arrive on this segment merges all of them
       const int which = (seg.start < r0) ? 0 : 1;
       float* dst = p.partials + (static_cast<int64_t>(blockIdx.x) * 2 + which) * FD_PARTIAL_FLOATS;
-      if ((tid & 31) == 0) {
+      if ((tid & 63) == 0) {
         dst[hh] = m_all;
         dst[4 + hh] = l_all;
       }
       *reinterpret_cast<float4*>(dst + 8 + hh * HEAD_DIM + d0) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-      *reinterpret_cast<float4*>(dst + 8 + hh * HEAD_DIM + d0 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
       __threadfence();
       __syncthreads();
       const int c_first = seg.start / chunk, c_last = (seg.end - 1) / chunk;
@@ -339,31 +387,22 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
       __syncthreads();
       if (s_last) {
         __threadfence();
-        float m_fin = -INFINITY;
+        m_all = -INFINITY;
+        l_all = 0.f;
+        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
         for (int c = c_first; c <= c_last; ++c) {
           const float* src = p.partials + (static_cast<int64_t>(c) * 2 + (c == c_first ? 1 : 0)) * FD_PARTIAL_FLOATS;
-          m_fin = fmaxf(m_fin, __ldcg(src + hh));
+          const float4 x = __ldcg(reinterpret_cast<const float4*>(src + 8 + hh * HEAD_DIM + d0));
+          merge_state(m_all, l_all, acc, __ldcg(src + hh), __ldcg(src + 4 + hh), x);
         }
-        float l_fin = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-        for (int c = c_first; c <= c_last; ++c) {
-          const float* src = p.partials + (static_cast<int64_t>(c) * 2 + (c == c_first ? 1 : 0)) * FD_PARTIAL_FLOATS;
-          const float wc = __expf(__ldcg(src + hh) - m_fin);
-          l_fin += wc * __ldcg(src + 4 + hh);
-          const float4 x0 = __ldcg(reinterpret_cast<const float4*>(src + 8 + hh * HEAD_DIM + d0));
-          const float4 x1 = __ldcg(reinterpret_cast<const float4*>(src + 8 + hh * HEAD_DIM + d0 + 4));
-          acc[0] += wc * x0.x; acc[1] += wc * x0.y; acc[2] += wc * x0.z; acc[3] += wc * x0.w;
-          acc[4] += wc * x1.x; acc[5] += wc * x1.y; acc[6] += wc * x1.z; acc[7] += wc * x1.w;
-        }
-        finish_store(p, seg.b, seg.h * GROUP + hh, d0, acc, l_fin);
+        finish_store(p, seg.b, seg.h * GROUP + hh, d0, acc, l_all);
       }
       __syncthreads();  // s_last is reused by the next piece
     }
     segment_advance(seg, cum, batch, heads);
   }
   if (dead) {
-    for (int s = 0; s < FD_STAGES; ++s) mbar_wait_bounded(&bars[warp][s], (phase_bits >> s) & 1u, 1u << 16);
+    for (int s = 0; s < FD_RING; ++s) mbar_wait_bounded(&bars[warp][s], (phase_bits >> s) & 1u, 1u << 12);
   }
 }
 

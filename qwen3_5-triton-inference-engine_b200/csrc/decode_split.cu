@@ -10,8 +10,8 @@
 namespace b200 {
 
 constexpr int SPLIT_WARPS = 4;
-constexpr int SPLIT_STAGES = 2;
-constexpr int SPLIT_SMEM = SPLIT_WARPS * SPLIT_STAGES * STAGE_BYTES + 128;
+constexpr int SPLIT_TILES = 4;  // ring of K/V tiles per warp (two pages)
+constexpr int SPLIT_SMEM = SPLIT_WARPS * SPLIT_TILES * TILE_BYTES + 128;
 
 // One warp per (sequence, kv head, split).  grid.x = B * H_kv * 128 / SPLIT_WARPS: static in B, so the launch
 // is CUDA-graph safe; everything length-dependent comes from pos[] on the device.
@@ -23,12 +23,12 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_b, int6
                           float* __restrict__ l_partial, float* __restrict__ acc_partial,
                           const int64_t* __restrict__ pos, int num_kv_heads, float scale, int* __restrict__ err) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  __shared__ uint64_t bars[SPLIT_WARPS][SPLIT_STAGES];
+  __shared__ uint64_t bars[SPLIT_WARPS][SPLIT_TILES];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
-  uint8_t* my_stages = smem + warp * SPLIT_STAGES * STAGE_BYTES;
+  uint8_t* ring = smem + warp * SPLIT_TILES * TILE_BYTES;
   if (lane == 0) {
-    for (int s = 0; s < SPLIT_STAGES; ++s) mbar_init(&bars[warp][s], 1);
+    for (int s = 0; s < SPLIT_TILES; ++s) mbar_init(&bars[warp][s], 1);
     mbar_fence_init();
   }
   __syncwarp();
@@ -54,36 +54,43 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_b, int6
 
   if (n_pages > 0) {
     decode_load_q(st, q + b * q_b + (h * GROUP) * q_h, q_h, lane);
-    // prologue: fill the ring
-    for (int i = 0; i < min(n_pages, SPLIT_STAGES); ++i) {
-      const int64_t phys = table[page_start + i];
-      decode_issue_page(my_stages + i * STAGE_BYTES, &bars[warp][i], kh + phys * kc_p, vh + phys * vc_p, kc_s, vc_s,
-                        lane);
-    }
+    // tile t = K (even) or V (odd) of page t/2, staged in ring slot t % SPLIT_TILES
+    auto issue = [&](int t) {
+      const int64_t phys = table[page_start + (t >> 1)];
+      const int slot = t % SPLIT_TILES;
+      if (t & 1) decode_issue_tile(ring + slot * TILE_BYTES, &bars[warp][slot], vh + phys * vc_p, vc_s, lane);
+      else decode_issue_tile(ring + slot * TILE_BYTES, &bars[warp][slot], kh + phys * kc_p, kc_s, lane);
+    };
+    const int n_tiles = 2 * n_pages;
+    for (int t = 0; t < min(n_tiles, SPLIT_TILES); ++t) issue(t);
     bool ok = true;
-    for (int i = 0; i < n_pages; ++i) {
-      const int stage = i % SPLIT_STAGES;
-      const uint32_t parity = (i / SPLIT_STAGES) & 1;
-      if (!mbar_wait_bounded(&bars[warp][stage], parity)) {
-        ok = false;
-        break;
-      }
-      const int lp = page_start + i;
-      const int valid = min(PAGE, seq_len - lp * PAGE);
-      decode_consume_page(st, my_stages + stage * STAGE_BYTES, valid, scale, lane);
-      __syncwarp();
-      if (i + SPLIT_STAGES < n_pages) {
-        const int64_t phys = table[lp + SPLIT_STAGES];
-        decode_issue_page(my_stages + stage * STAGE_BYTES, &bars[warp][stage], kh + phys * kc_p, vh + phys * vc_p,
-                          kc_s, vc_s, lane);
+    for (int i = 0; i < n_pages && ok; ++i) {
+      const int valid = min(PAGE, seq_len - (page_start + i) * PAGE);
+      uint32_t b0 = 0, b1 = 0;
+      float alpha0 = 1.f, alpha1 = 1.f;
+#pragma unroll
+      for (int part = 0; part < 2; ++part) {
+        const int t = 2 * i + part;
+        const int slot = t % SPLIT_TILES;
+        if (!mbar_wait_bounded(&bars[warp][slot], (t / SPLIT_TILES) & 1)) {
+          ok = false;
+          break;
+        }
+        uint8_t* tile = ring + slot * TILE_BYTES;
+        if (part == 0) decode_scores(st, tile, valid, scale, lane, b0, b1, alpha0, alpha1);
+        else decode_accumulate(st, tile, valid, b0, b1, alpha0, alpha1, lane);
+        fence_proxy_async();  // row clears (generic proxy) before the next bulk copy into this slot
+        __syncwarp();
+        if (t + SPLIT_TILES < n_tiles) issue(t + SPLIT_TILES);
       }
     }
     if (!ok) {
       if (lane == 0) atomicExch(err, 1);
       // copies may still be in flight into this CTA's shared memory: give them a bounded time to land
-      for (int s = 0; s < SPLIT_STAGES; ++s) mbar_wait_bounded(&bars[warp][s], 0, 1u << 16);
+      for (int s = 0; s < SPLIT_TILES; ++s) mbar_wait_bounded(&bars[warp][s], 0, 1u << 12);
       return;
     }
+    decode_reduce_l(st);
   }
 
   // ---- store the partial: m, l per head; acc through shared memory for 16-byte coalesced stores
@@ -95,7 +102,7 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_b, int6
     l_partial[base] = st.l[0];
     l_partial[base + MAX_SPLITS] = st.l[1];
   }
-  float* tile = reinterpret_cast<float*>(my_stages);
+  float* tile = reinterpret_cast<float*>(ring);
   __syncwarp();
   decode_store_acc_smem(st, tile, lane);
   __syncwarp();
