@@ -168,6 +168,28 @@ int b200_gdn_recurrent_prefill_sequential(const void* q, int64_t q_stride_t, int
                                           int64_t out_stride_h, int32_t num_heads, int32_t key_dim, int32_t value_dim,
                                           b200_stream_t stream);
 
+/* Chunk-64 form of the recurrence for ONE sequence of token_num tokens, as the reference's three operators with
+ * their fp32 intermediates (N = cdiv(token_num, 64); every output is contiguous):
+ *   prepare_wy: w [N,H,64,128], u_base [N,H,64,128], g_cumsum [N,H,64]
+ *               replaces wy_lib::gdn_chunk_prepare_wy, triton_kernels/gdn_recurrent_prefill.py:703-784 (kernel :248-396)
+ *   state:      delta [N,H,64,128], chunk_state [N,H,128,128] (state ENTERING each chunk), final_state [H,128,128]
+ *               replaces wy_lib::gdn_chunk_state, triton_kernels/gdn_recurrent_prefill.py:825-909 (kernel :404-537)
+ *   output:     out [T,H,128] bf16
+ *               replaces wy_lib::gdn_chunk_output, triton_kernels/gdn_recurrent_prefill.py:935-1006 (kernel :563-690) */
+int b200_gdn_chunk_prepare_wy(const void* k, int64_t k_stride_t, int64_t k_stride_h, const void* v, int64_t v_stride_t,
+                              int64_t v_stride_h, const float* beta, int64_t beta_stride_t, int64_t beta_stride_h,
+                              const float* g, int64_t g_stride_t, int64_t g_stride_h, float* w, float* u_base,
+                              float* g_cumsum, int32_t token_num, int32_t num_heads, int32_t key_dim,
+                              int32_t value_dim, b200_stream_t stream);
+int b200_gdn_chunk_state(const void* k, int64_t k_stride_t, int64_t k_stride_h, const float* w, const float* u_base,
+                         const float* g_cumsum, float* delta, float* chunk_state, float* final_state,
+                         int32_t token_num, int32_t num_heads, int32_t key_dim, int32_t value_dim,
+                         b200_stream_t stream);
+int b200_gdn_chunk_output(const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k, int64_t k_stride_t,
+                          int64_t k_stride_h, const float* delta, const float* g_cumsum, const float* chunk_state,
+                          void* out, int64_t out_stride_t, int64_t out_stride_h, int32_t token_num, int32_t num_heads,
+                          int32_t key_dim, int32_t value_dim, b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -32,6 +32,9 @@ SIGNATURES: dict[str, list] = {
                                   P, I64, I64, I32, I32, I32, I32, P],
     "b200_gdn_recurrent_prefill_sequential": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P,
                                               I32, I32, P, P, I64, I64, I32, I32, I32, P],
+    "b200_gdn_chunk_prepare_wy": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, P, P, I32, I32, I32, I32, P],
+    "b200_gdn_chunk_state": [P, I64, I64, P, P, P, P, P, P, I32, I32, I32, I32, P],
+    "b200_gdn_chunk_output": [P, I64, I64, P, I64, I64, P, P, P, P, I64, I64, I32, I32, I32, I32, P],
 }
 OTHER = {
     "b200_last_error": ([], c_char_p),

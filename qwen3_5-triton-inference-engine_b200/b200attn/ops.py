@@ -438,3 +438,118 @@ def fused_prefill_attention(q, k, v, gate, k_cache, v_cache, block_table, cu_seq
               int(position_ids.dtype == torch.int64), _ptr(inv_freq), int(rotary_dim), _ptr(out), batch,
               int(max_seqlen), num_q_heads, num_kv_heads, head_dim, _stream())
     return out
+
+
+# =========================================================================== Gated DeltaNet, chunk-64 form
+@torch.library.custom_op("wy_lib::gdn_chunk_prepare_wy", mutates_args=(), device_types="cuda")
+def gdn_chunk_prepare_wy(k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor,
+                         g: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Replaces triton_kernels/gdn_recurrent_prefill.py:703-784.  Returns (w [N,H,64,DK], u_base [N,H,64,DV],
+    g_cumsum [N,H,64]) in fp32 for ONE sequence of T tokens, N = cdiv(T, 64)."""
+    assert k.ndim == 3 and v.ndim == 3
+    assert k.shape[:2] == v.shape[:2]
+    assert beta.ndim == 2 and g.ndim == 2
+    assert beta.shape == g.shape == k.shape[:2]
+    assert k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16
+    assert beta.dtype == torch.float32 and g.dtype == torch.float32
+    assert k.device == v.device == beta.device == g.device
+    token_num, num_heads, key_dim = k.shape
+    value_dim = v.shape[-1]
+    assert token_num > 0 and num_heads > 0
+    _require_cuda(k)
+    k, v = _inner_contiguous(k), _inner_contiguous(v)
+    num_chunks = (token_num + GDN_CHUNK - 1) // GDN_CHUNK
+    w = torch.empty((num_chunks, num_heads, GDN_CHUNK, key_dim), dtype=torch.float32, device=k.device)
+    u_base = torch.empty((num_chunks, num_heads, GDN_CHUNK, value_dim), dtype=torch.float32, device=k.device)
+    g_cumsum = torch.empty((num_chunks, num_heads, GDN_CHUNK), dtype=torch.float32, device=k.device)
+    _lib.call("b200_gdn_chunk_prepare_wy", _ptr(k), k.stride(0), k.stride(1), _ptr(v), v.stride(0), v.stride(1),
+              _ptr(beta), beta.stride(0), beta.stride(1), _ptr(g), g.stride(0), g.stride(1), _ptr(w), _ptr(u_base),
+              _ptr(g_cumsum), token_num, num_heads, key_dim, value_dim, _stream())
+    return w, u_base, g_cumsum
+
+
+@gdn_chunk_prepare_wy.register_fake
+def _(k, v, beta, g):
+    token_num, num_heads, key_dim = k.shape
+    n = (token_num + GDN_CHUNK - 1) // GDN_CHUNK
+    return (torch.empty((n, num_heads, GDN_CHUNK, key_dim), dtype=torch.float32, device=k.device),
+            torch.empty((n, num_heads, GDN_CHUNK, v.shape[-1]), dtype=torch.float32, device=k.device),
+            torch.empty((n, num_heads, GDN_CHUNK), dtype=torch.float32, device=k.device))
+
+
+@torch.library.custom_op("wy_lib::gdn_chunk_state", mutates_args=(), device_types="cuda")
+def gdn_chunk_state(k: torch.Tensor, w: torch.Tensor, u_base: torch.Tensor,
+                    g_cumsum: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Replaces triton_kernels/gdn_recurrent_prefill.py:825-909.  Returns (delta [N,H,64,DV], chunk_state
+    [N,H,DK,DV] = state ENTERING each chunk, final_state [H,DK,DV])."""
+    assert k.ndim == 3 and k.dtype == torch.bfloat16
+    assert w.ndim == 4 and u_base.ndim == 4 and g_cumsum.ndim == 3
+    assert w.dtype == u_base.dtype == g_cumsum.dtype == torch.float32
+    assert k.device == w.device == u_base.device == g_cumsum.device
+    token_num, num_heads, key_dim = k.shape
+    num_chunks, state_heads, chunk_size, state_key_dim = w.shape
+    value_dim = u_base.shape[-1]
+    assert token_num > 0
+    assert state_heads == num_heads and state_key_dim == key_dim
+    assert chunk_size == GDN_CHUNK
+    assert u_base.shape == (num_chunks, num_heads, chunk_size, value_dim)
+    assert g_cumsum.shape == (num_chunks, num_heads, chunk_size)
+    assert num_chunks == (token_num + GDN_CHUNK - 1) // GDN_CHUNK
+    _require_cuda(k)
+    k, w, u_base, g_cumsum = _inner_contiguous(k), w.contiguous(), u_base.contiguous(), g_cumsum.contiguous()
+    delta = torch.empty_like(u_base)
+    chunk_state = torch.empty((num_chunks, num_heads, key_dim, value_dim), dtype=torch.float32, device=k.device)
+    final_state = torch.empty((num_heads, key_dim, value_dim), dtype=torch.float32, device=k.device)
+    _lib.call("b200_gdn_chunk_state", _ptr(k), k.stride(0), k.stride(1), _ptr(w), _ptr(u_base), _ptr(g_cumsum),
+              _ptr(delta), _ptr(chunk_state), _ptr(final_state), token_num, num_heads, key_dim, value_dim, _stream())
+    return delta, chunk_state, final_state
+
+
+@gdn_chunk_state.register_fake
+def _(k, w, u_base, g_cumsum):
+    _, num_heads, key_dim = k.shape
+    num_chunks, _, _, value_dim = u_base.shape
+    return (torch.empty_like(u_base),
+            torch.empty((num_chunks, num_heads, key_dim, value_dim), dtype=torch.float32, device=k.device),
+            torch.empty((num_heads, key_dim, value_dim), dtype=torch.float32, device=k.device))
+
+
+@torch.library.custom_op("wy_lib::gdn_chunk_output", mutates_args=(), device_types="cuda")
+def gdn_chunk_output(q: torch.Tensor, k: torch.Tensor, delta: torch.Tensor, g_cumsum: torch.Tensor,
+                     chunk_state: torch.Tensor) -> torch.Tensor:
+    """Replaces triton_kernels/gdn_recurrent_prefill.py:935-1006.  Returns out [T,H,DV] bf16."""
+    assert q.ndim == 3 and k.ndim == 3 and q.shape == k.shape
+    assert q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16
+    assert delta.ndim == 4 and delta.dtype == torch.float32
+    assert g_cumsum.ndim == 3 and g_cumsum.dtype == torch.float32
+    assert chunk_state.ndim == 4 and chunk_state.dtype == torch.float32
+    assert q.device == k.device == delta.device == g_cumsum.device == chunk_state.device
+    token_num, num_heads, key_dim = q.shape
+    num_chunks, delta_heads, chunk_size, value_dim = delta.shape
+    assert token_num > 0 and delta_heads == num_heads
+    assert chunk_size == GDN_CHUNK
+    assert num_chunks == (token_num + GDN_CHUNK - 1) // GDN_CHUNK
+    assert g_cumsum.shape == (num_chunks, num_heads, chunk_size)
+    assert chunk_state.shape == (num_chunks, num_heads, key_dim, value_dim)
+    _require_cuda(q)
+    q, k = _inner_contiguous(q), _inner_contiguous(k)
+    delta, g_cumsum, chunk_state = delta.contiguous(), g_cumsum.contiguous(), chunk_state.contiguous()
+    out = torch.empty((token_num, num_heads, value_dim), dtype=q.dtype, device=q.device)
+    _lib.call("b200_gdn_chunk_output", _ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1), _ptr(delta),
+              _ptr(g_cumsum), _ptr(chunk_state), _ptr(out), out.stride(0), out.stride(1), token_num, num_heads, key_dim,
+              value_dim, _stream())
+    return out
+
+
+@gdn_chunk_output.register_fake
+def _(q, k, delta, g_cumsum, chunk_state):
+    return torch.empty((q.shape[0], q.shape[1], delta.shape[-1]), dtype=q.dtype, device=q.device)
+
+
+def call_gdn_recurrent_prefill_chunked_triton(q, k, v, beta, g):
+    """prepare_wy -> chunk_state -> chunk_output for one sequence; returns (out, final_state).
+    triton_kernels/gdn_recurrent_prefill.py:1026-1047 (name kept for drop-in use; no Triton is involved)."""
+    w, u_base, g_cumsum = gdn_chunk_prepare_wy(k, v, beta, g)
+    delta, chunk_state, final_state = gdn_chunk_state(k, w, u_base, g_cumsum)
+    out = gdn_chunk_output(q, k, delta, g_cumsum, chunk_state)
+    return out, final_state

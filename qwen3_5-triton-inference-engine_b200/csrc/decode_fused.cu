@@ -27,7 +27,7 @@ constexpr int FD_WARPS = 8;
 constexpr int FD_THREADS = FD_WARPS * 32;
 constexpr int FD_RING = 3;                             // K/V tiles per warp
 constexpr int FD_MERGE_SLOTS = 4;                      // warps merge in two rounds of four
-constexpr int FD_MAX_BATCH = 1024;                     // prefix table lives in shared memory
+constexpr int FD_MAX_BATCH = 512;                      // prefix table and positions live in shared memory
 constexpr int FD_MAX_SEGMENTS = 2048;                  // counters in the workspace
 constexpr int FD_MAX_CTAS = 256;                       // partial slots in the workspace
 constexpr int FD_TILE_FLOATS = GROUP * HEAD_DIM;       // 1024 accumulator floats per partial
@@ -37,8 +37,11 @@ constexpr int64_t FD_WORKSPACE_BYTES = FD_COUNTER_BYTES + int64_t(FD_MAX_CTAS) *
 
 constexpr int FD_SMEM_RING = FD_WARPS * FD_RING * TILE_BYTES;
 constexpr int FD_SMEM_MERGE = FD_MERGE_SLOTS * FD_PARTIAL_FLOATS * 4;
-constexpr int FD_SMEM_CUM = ((FD_MAX_BATCH + 1) * 4 + 15) / 16 * 16;
-constexpr int FD_SMEM_TOTAL = FD_SMEM_RING + FD_SMEM_MERGE + FD_SMEM_CUM + 128;
+constexpr int FD_SMEM_CUM = ((FD_MAX_BATCH + 1) * 4 + 15) / 16 * 16;   // exclusive prefix of units
+constexpr int FD_SMEM_POS = FD_MAX_BATCH * 4;                           // pos[] as int32
+constexpr int FD_Q_PITCH = HEAD_DIM + 8;                                // bf16 elements per staged Q row
+constexpr int FD_SMEM_Q = 2 * GROUP * FD_Q_PITCH * 2;                   // rotated Q of this piece and of the next
+constexpr int FD_SMEM_TOTAL = FD_SMEM_RING + FD_SMEM_MERGE + FD_SMEM_CUM + FD_SMEM_POS + FD_SMEM_Q + 128;
 
 struct FusedDecodeParams {
   const __nv_bfloat16 *q, *k_new, *v_new, *gate;
@@ -83,28 +86,29 @@ __device__ __forceinline__ void segment_advance(Segment& s, const int* cum, int 
   if (s.b < batch) s.end = s.start + (cum[s.b + 1] - cum[s.b]);
 }
 
-// Rotate the Q fragments in place: dims [0, HALF) pair with [HALF, 2*HALF); both partners of a pair sit in the
-// same lane, HALF/16 fragment steps apart.  Angles = float(pos) * inv_freq[d], fp32, full-range sincosf, result
-// rounded to bf16 -- the arithmetic of triton_kernels/partial_rope.py:65-113.
-template <int HALF>
-__device__ __forceinline__ void rope_q_fragments(DecodeWarpState& st, const float* __restrict__ inv_freq, float posf,
-                                                 int lane) {
-  const int kk = (lane & 3) * 2;
-  constexpr int steps = HALF / 16;
-#pragma unroll
-  for (int ks = 0; ks < steps; ++ks) {
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      const int d = ks * 16 + r * 8 + kk;
-      float s0, c0, s1, c1;
-      sincosf(posf * inv_freq[d], &s0, &c0);
-      sincosf(posf * inv_freq[d + 1], &s1, &c1);
-      const uint32_t a = st.qb[ks][r], b = st.qb[ks + steps][r];
-      float f0, g0, f1, g1;
-      rope_pair(bf16_lo(a), bf16_lo(b), s0, c0, f0, g0);
-      rope_pair(bf16_hi(a), bf16_hi(b), s1, c1, f1, g1);
-      st.qb[ks][r] = pack_bf16(f0, f1);
-      st.qb[ks + steps][r] = pack_bf16(g0, g1);
+// Stage the 4 Q heads of one segment in shared memory, rotated: dims [0, half) pair with [half, 2*half),
+// angles = float(pos) * inv_freq[d] in fp32, full-range sincosf, result rounded to bf16 -- the arithmetic of
+// triton_kernels/partial_rope.py:65-113.  Cooperative over the CTA's 256 threads; the caller synchronises.
+__device__ __forceinline__ void stage_q(__nv_bfloat16* buf, const FusedDecodeParams& p, int b, int h, int pos_b, int tid) {
+  const int half = p.rotary_half;
+  const __nv_bfloat16* q4 = p.q + b * p.q_b + (h * GROUP) * p.q_h;
+  if (tid < GROUP * 32) {
+    // rotary pairs: at most 32 per head (rotary_dim <= 64)
+    const int head = tid >> 5, j = tid & 31;
+    if (j < half) {
+      const float a = __bfloat162float(q4[head * p.q_h + j]), bb = __bfloat162float(q4[head * p.q_h + j + half]);
+      float sn, cs, f, g;
+      sincosf(static_cast<float>(pos_b) * p.inv_freq[j], &sn, &cs);
+      rope_pair(a, bb, sn, cs, f, g);
+      buf[head * FD_Q_PITCH + j] = __float2bfloat16_rn(f);
+      buf[head * FD_Q_PITCH + j + half] = __float2bfloat16_rn(g);
+    }
+  } else {
+    // pass-through dims [2*half, 256) in 16-byte pieces
+    const int per_head = (HEAD_DIM - 2 * half) / 8;
+    for (int i = tid - GROUP * 32; i < GROUP * per_head; i += FD_THREADS - GROUP * 32) {
+      const int head = i / per_head, d = 2 * half + (i % per_head) * 8;
+      *reinterpret_cast<uint4*>(buf + head * FD_Q_PITCH + d) = *reinterpret_cast<const uint4*>(q4 + head * p.q_h + d);
     }
   }
 }
@@ -156,9 +160,8 @@ __device__ __forceinline__ void stage_new_v(uint8_t* v_tile, const FusedDecodePa
 
 // out = bf16( bf16(acc / l) * sigmoid(gate) ), 4 consecutive dims of one head per thread.
 __device__ __forceinline__ void finish_store(const FusedDecodeParams& p, int b, int hq, int d0, const float (&acc)[4],
-                                             float l) {
+                                             float l, uint2 gv) {
   const int64_t col = static_cast<int64_t>(hq) * HEAD_DIM + d0;
-  const uint2 gv = *reinterpret_cast<const uint2*>(p.gate + b * p.gate_b + col);
   const float inv_l = 1.f / l;
   const float x0 = round_bf16(acc[0] * inv_l), x1 = round_bf16(acc[1] * inv_l);
   const float x2 = round_bf16(acc[2] * inv_l), x3 = round_bf16(acc[3] * inv_l);
@@ -190,6 +193,8 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   float* merge = reinterpret_cast<float*>(smem + FD_SMEM_RING);
   int* cum = reinterpret_cast<int*>(smem + FD_SMEM_RING + FD_SMEM_MERGE);
+  int* pos_s = reinterpret_cast<int*>(smem + FD_SMEM_RING + FD_SMEM_MERGE + FD_SMEM_CUM);
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem + FD_SMEM_RING + FD_SMEM_MERGE + FD_SMEM_CUM + FD_SMEM_POS);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int heads = p.num_kv_heads, batch = p.batch;
@@ -202,6 +207,7 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
   // ---- exclusive prefix of units per sequence: units_b = cdiv(pos[b], 16) + 1
   for (int b = tid; b < batch; b += FD_THREADS) {
     const int pb = static_cast<int>(p.pos[b]);
+    pos_s[b] = pb;
     cum[b + 1] = (pb + PAGE - 1) / PAGE + 1;
   }
   __syncthreads();
@@ -289,16 +295,25 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
   // ---- consumer: CTA-uniform loop over the pieces of this range
   Segment seg = segment_of_unit(r0, cum, batch, heads);
   const int hh = tid >> 6, d0 = (tid & 63) * 4;  // element mapping of the merge / finish steps
+  int piece = 0;
+  stage_q(q_s, p, seg.b, seg.h, pos_s[seg.b], tid);
+  __syncthreads();
   while (seg.start < r1) {
     const int lo = max(seg.start, r0), hi = min(seg.end, r1);
     const int np = seg.end - seg.start - 1;
-    const int64_t pos_b = p.pos[seg.b];
+    const int64_t pos_b = pos_s[seg.b];
+    // the gate row of this segment is only needed at the very end: fetch it now, off the critical path
+    const uint2 gate_pf = *reinterpret_cast<const uint2*>(p.gate + seg.b * p.gate_b +
+                                                           static_cast<int64_t>(seg.h * GROUP + hh) * HEAD_DIM + d0);
+    // rotated Q of the NEXT piece goes to the other buffer while this piece streams (published by the merge barriers)
+    if (seg.end < r1) {
+      Segment nxt = seg;
+      segment_advance(nxt, cum, batch, heads);
+      stage_q(q_s + ((piece + 1) & 1) * GROUP * FD_Q_PITCH, p, nxt.b, nxt.h, pos_s[nxt.b], tid);
+    }
     DecodeWarpState st;
     decode_state_init(st);
-    if (lo + warp < hi) {
-      decode_load_q(st, p.q + seg.b * p.q_b + (seg.h * GROUP) * p.q_h, p.q_h, lane);
-      if (p.rotary_half == 32) rope_q_fragments<32>(st, p.inv_freq, static_cast<float>(pos_b), lane);
-    }
+    if (lo + warp < hi) decode_load_q(st, q_s + (piece & 1) * GROUP * FD_Q_PITCH, FD_Q_PITCH, lane);
     for (int u = lo + warp; u < hi; u += FD_WARPS) {
       const int j = u - seg.start;
       const bool is_page = j < np;
@@ -364,7 +379,7 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
 
     const bool whole = (lo == seg.start) && (hi == seg.end);
     if (whole) {
-      finish_store(p, seg.b, seg.h * GROUP + hh, d0, acc, l_all);
+      finish_store(p, seg.b, seg.h * GROUP + hh, d0, acc, l_all, gate_pf);
     } else {
       // ---- leave a partial; the last CTA to arrive on this segment merges all of them
       const int which = (seg.start < r0) ? 0 : 1;
@@ -390,16 +405,28 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
         m_all = -INFINITY;
         l_all = 0.f;
         acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-        for (int c = c_first; c <= c_last; ++c) {
-          const float* src = p.partials + (static_cast<int64_t>(c) * 2 + (c == c_first ? 1 : 0)) * FD_PARTIAL_FLOATS;
-          const float4 x = __ldcg(reinterpret_cast<const float4*>(src + 8 + hh * HEAD_DIM + d0));
-          merge_state(m_all, l_all, acc, __ldcg(src + hh), __ldcg(src + 4 + hh), x);
+        // eight contributors per round: all their loads are in flight before the first dependent merge
+        for (int c0 = c_first; c0 <= c_last; c0 += 8) {
+          float mm[8], ll[8];
+          float4 xx[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int c = min(c0 + i, c_last);
+            const float* src = p.partials + (static_cast<int64_t>(c) * 2 + (c == c_first ? 1 : 0)) * FD_PARTIAL_FLOATS;
+            mm[i] = __ldcg(src + hh);
+            ll[i] = __ldcg(src + 4 + hh);
+            xx[i] = __ldcg(reinterpret_cast<const float4*>(src + 8 + hh * HEAD_DIM + d0));
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (c0 + i <= c_last) merge_state(m_all, l_all, acc, mm[i], ll[i], xx[i]);
         }
-        finish_store(p, seg.b, seg.h * GROUP + hh, d0, acc, l_all);
+        finish_store(p, seg.b, seg.h * GROUP + hh, d0, acc, l_all, gate_pf);
       }
       __syncthreads();  // s_last is reused by the next piece
     }
     segment_advance(seg, cum, batch, heads);
+    ++piece;
   }
   if (dead) {
     for (int s = 0; s < FD_RING; ++s) mbar_wait_bounded(&bars[warp][s], (phase_bits >> s) & 1u, 1u << 12);
