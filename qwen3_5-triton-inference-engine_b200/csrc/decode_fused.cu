@@ -296,6 +296,33 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
   Segment seg = segment_of_unit(r0, cum, batch, heads);
   const int hh = tid >> 6, d0 = (tid & 63) * 4;  // element mapping of the merge / finish steps
   int piece = 0;
+  bool have_pending = false;
+  Segment pend_seg = seg;
+  int pend_first = 0, pend_last = 0;
+  uint2 pend_gate = make_uint2(0, 0);
+  // merge the partials CTAs [c_first, c_last] left for segment `sg` and finish it
+  auto combine_and_finish = [&](const Segment& sg, int c_first, int c_last, uint2 gate_bits) {
+    __threadfence();
+    float m_fin = -INFINITY, l_fin = 0.f;
+    float a4[4] = {0.f, 0.f, 0.f, 0.f};
+    // eight contributors per round: all their loads are in flight before the first dependent merge
+    for (int c0 = c_first; c0 <= c_last; c0 += 8) {
+      float mm[8], ll[8];
+      float4 xx[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int c = min(c0 + i, c_last);
+        const float* src = p.partials + (static_cast<int64_t>(c) * 2 + (c == c_first ? 1 : 0)) * FD_PARTIAL_FLOATS;
+        mm[i] = __ldcg(src + hh);
+        ll[i] = __ldcg(src + 4 + hh);
+        xx[i] = __ldcg(reinterpret_cast<const float4*>(src + 8 + hh * HEAD_DIM + d0));
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (c0 + i <= c_last) merge_state(m_fin, l_fin, a4, mm[i], ll[i], xx[i]);
+    }
+    finish_store(p, sg.b, sg.h * GROUP + hh, d0, a4, l_fin, gate_bits);
+  };
   stage_q(q_s, p, seg.b, seg.h, pos_s[seg.b], tid);
   __syncthreads();
   while (seg.start < r1) {
@@ -377,11 +404,17 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
       __syncthreads();  // merge buffer free again
     }
 
+    // a partial left by the previous piece: its arrival ticket was taken by thread 0 while this piece streamed
+    if (have_pending) {
+      if (s_last) combine_and_finish(pend_seg, pend_first, pend_last, pend_gate);
+      have_pending = false;
+    }
     const bool whole = (lo == seg.start) && (hi == seg.end);
     if (whole) {
       finish_store(p, seg.b, seg.h * GROUP + hh, d0, acc, l_all, gate_pf);
     } else {
-      // ---- leave a partial; the last CTA to arrive on this segment merges all of them
+      // ---- leave a partial; the last CTA to arrive on this segment merges all of them.  Nobody waits for the
+      // ticket here: the result is looked at after the next piece's merge barriers (or after the loop).
       const int which = (seg.start < r0) ? 0 : 1;
       float* dst = p.partials + (static_cast<int64_t>(blockIdx.x) * 2 + which) * FD_PARTIAL_FLOATS;
       if ((tid & 63) == 0) {
@@ -389,44 +422,27 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
         dst[4 + hh] = l_all;
       }
       *reinterpret_cast<float4*>(dst + 8 + hh * HEAD_DIM + d0) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-      __threadfence();
-      __syncthreads();
-      const int c_first = seg.start / chunk, c_last = (seg.end - 1) / chunk;
-      const int seg_id = seg.b * heads + seg.h;
+      pend_seg = seg;
+      pend_first = seg.start / chunk;
+      pend_last = (seg.end - 1) / chunk;
+      pend_gate = gate_pf;
+      have_pending = true;
+      __syncthreads();  // every thread's partial stores happen-before thread 0's release below
       if (tid == 0) {
+        __threadfence();
+        const int seg_id = seg.b * heads + seg.h;
         const int old = atomicAdd(p.counters + seg_id, 1);
-        const int last = (old == c_last - c_first);
+        const int last = (old == pend_last - pend_first);
         if (last) p.counters[seg_id] = 0;  // ready for the next launch
         s_last = last;
       }
-      __syncthreads();
-      if (s_last) {
-        __threadfence();
-        m_all = -INFINITY;
-        l_all = 0.f;
-        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-        // eight contributors per round: all their loads are in flight before the first dependent merge
-        for (int c0 = c_first; c0 <= c_last; c0 += 8) {
-          float mm[8], ll[8];
-          float4 xx[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int c = min(c0 + i, c_last);
-            const float* src = p.partials + (static_cast<int64_t>(c) * 2 + (c == c_first ? 1 : 0)) * FD_PARTIAL_FLOATS;
-            mm[i] = __ldcg(src + hh);
-            ll[i] = __ldcg(src + 4 + hh);
-            xx[i] = __ldcg(reinterpret_cast<const float4*>(src + 8 + hh * HEAD_DIM + d0));
-          }
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            if (c0 + i <= c_last) merge_state(m_all, l_all, acc, mm[i], ll[i], xx[i]);
-        }
-        finish_store(p, seg.b, seg.h * GROUP + hh, d0, acc, l_all, gate_pf);
-      }
-      __syncthreads();  // s_last is reused by the next piece
     }
     segment_advance(seg, cum, batch, heads);
     ++piece;
+  }
+  if (have_pending) {
+    __syncthreads();
+    if (s_last) combine_and_finish(pend_seg, pend_first, pend_last, pend_gate);
   }
   if (dead) {
     for (int s = 0; s < FD_RING; ++s) mbar_wait_bounded(&bars[warp][s], (phase_bits >> s) & 1u, 1u << 12);
