@@ -100,6 +100,25 @@ int b200_fused_decode_attention(const void* q, int64_t q_stride_b, int64_t q_str
                                 const float* inv_freq, int32_t rotary_dim, void* out, void* workspace, int32_t batch,
                                 int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, b200_stream_t stream);
 
+/* The same fused decode step for callers that cannot allocate device memory (a host that owns the whole GPU and
+ * forbids cudaMalloc after start-up, a plugin inside another process, code running under stream capture).  This
+ * entry point has NO counterpart in the reference.  Arguments are those of b200_fused_decode_attention without
+ * `workspace`: the workspace is a fixed ~2 MB array inside the library's device image (present on every GPU that
+ * loads the library, until the process exits).  Nothing is allocated, here or in anything it calls.
+ *   - Limits: batch <= 512 and batch * num_kv_heads <= 2048; larger calls return non-zero and launch nothing.
+ *   - The first call on a device also resolves the array's device address: make it before any stream capture.
+ *   - All calls on a device share the array; it is re-initialised on `stream` at the start of each call, so calls
+ *     that overlap on the GPU race and must be serialised by the caller. */
+int b200_fused_decode_attention_static(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_new,
+                                       int64_t kn_stride_b, int64_t kn_stride_h, const void* v_new,
+                                       int64_t vn_stride_b, int64_t vn_stride_h, const void* gate,
+                                       int64_t gate_stride_b, void* k_cache, void* v_cache, int64_t kc_stride_p,
+                                       int64_t kc_stride_h, int64_t kc_stride_s, int64_t vc_stride_p,
+                                       int64_t vc_stride_h, int64_t vc_stride_s, const int32_t* block_table,
+                                       int64_t bt_stride_b, const int64_t* pos, const float* inv_freq,
+                                       int32_t rotary_dim, void* out, int32_t batch, int32_t num_q_heads,
+                                       int32_t num_kv_heads, int32_t head_dim, b200_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------ varlen causal prefill attention */
 /* Block-diagonal causal GQA over a packed batch: q [T,H_q,256], k/v [T,H_kv,256] bf16 (any t/h strides),
  * cu_seqlens [B+1] int32, out [T,H_q,256] bf16.  max_seqlen (host) only sizes the grid.

@@ -523,3 +523,71 @@ extern "C" int b200_fused_decode_attention(const void* q, int64_t q_stride_b, in
   fused_decode_kernel<<<grid, FD_THREADS, FD_SMEM_TOTAL, reinterpret_cast<cudaStream_t>(stream)>>>(p);
   return check_launch("fused_decode_attention");
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Variant for callers that cannot allocate device memory.
+//
+// Some hosts of this library hand out no allocator at all: a runtime that has already carved up the whole GPU and
+// forbids cudaMalloc after start-up, a plugin loaded into somebody else's process that must not touch the caching
+// allocator, or code running between the begin and end of a stream capture where an allocation is an error.  For
+// them the fused decode step needs a workspace that exists without anyone asking for it.  It lives here, in a
+// fixed-size array in the library's own device image: every GPU that loads the library carries these ~2 MB until the
+// process exits, whether or not this entry point is ever called.
+//
+// The array's NAME is only meaningful to device code.  On the host the same identifier is a shadow object whose
+// address is a host address, so it must never be handed to a kernel; the device address is asked for once per
+// device with cudaGetSymbolAddress() while that device is current.
+static __device__ __align__(256) unsigned char g_fused_decode_static_workspace[FD_WORKSPACE_BYTES];
+
+static void* static_workspace_for_current_device() {
+  static void* cached[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (cached[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_fused_decode_static_workspace) != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();  // leave no sticky error behind for the caller's next launch check
+      return nullptr;
+    }
+    cached[dev] = ptr;
+  }
+  return cached[dev];
+}
+
+// Same computation and arguments as b200_fused_decode_attention, minus the workspace.
+//  - Nothing is allocated: no cudaMalloc / cudaFree, no allocating library call; the workspace is the static array.
+//  - The FIRST call on each device looks up the array's device address (and raises the kernel's shared-memory
+//    limit); make that first call outside any stream capture.  Later calls only enqueue work on `stream`.
+//  - Limits (fixed by the array's size): batch <= 512 and batch * num_kv_heads <= 2048; larger calls are refused with
+//    an error message and launch nothing.
+//  - All calls on a device share the one array and it keeps what the previous call left in it.  The part that has
+//    to start at zero (the per-segment arrival counters) is cleared on `stream` before each launch; the rest is
+//    overwritten before it is read.  Two calls that overlap on the GPU (different streams, or graphs replayed
+//    concurrently) would race on the array: serialise them.
+extern "C" int b200_fused_decode_attention_static(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                                                  const void* k_new, int64_t kn_stride_b, int64_t kn_stride_h,
+                                                  const void* v_new, int64_t vn_stride_b, int64_t vn_stride_h,
+                                                  const void* gate, int64_t gate_stride_b, void* k_cache,
+                                                  void* v_cache, int64_t kc_stride_p, int64_t kc_stride_h,
+                                                  int64_t kc_stride_s, int64_t vc_stride_p, int64_t vc_stride_h,
+                                                  int64_t vc_stride_s, const int32_t* block_table,
+                                                  int64_t bt_stride_b, const int64_t* pos, const float* inv_freq,
+                                                  int32_t rotary_dim, void* out, int32_t batch, int32_t num_q_heads,
+                                                  int32_t num_kv_heads, int32_t head_dim, b200_stream_t stream) {
+  if (batch < 1 || batch > FD_MAX_BATCH || num_kv_heads < 1 ||
+      static_cast<int64_t>(batch) * num_kv_heads > FD_MAX_SEGMENTS)
+    return fail(ERR_LIMIT,
+                "fused_decode_attention_static: the built-in workspace holds at most batch=%d and batch*H_kv=%d "
+                "(got batch=%d, H_kv=%d); use b200_fused_decode_attention with a caller-provided workspace",
+                FD_MAX_BATCH, FD_MAX_SEGMENTS, batch, num_kv_heads);
+  void* workspace = static_workspace_for_current_device();
+  if (workspace == nullptr)
+    return fail(ERR_RUNTIME, "fused_decode_attention_static: cudaGetSymbolAddress failed for the built-in workspace");
+  if (cudaMemsetAsync(workspace, 0, FD_COUNTER_BYTES, reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess)
+    return fail(ERR_RUNTIME, "fused_decode_attention_static: cannot clear the arrival counters");
+  return b200_fused_decode_attention(q, q_stride_b, q_stride_h, k_new, kn_stride_b, kn_stride_h, v_new, vn_stride_b,
+                                     vn_stride_h, gate, gate_stride_b, k_cache, v_cache, kc_stride_p, kc_stride_h,
+                                     kc_stride_s, vc_stride_p, vc_stride_h, vc_stride_s, block_table, bt_stride_b, pos,
+                                     inv_freq, rotary_dim, out, workspace, batch, num_q_heads, num_kv_heads, head_dim,
+                                     stream);
+}
