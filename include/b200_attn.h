@@ -9,8 +9,9 @@
  *   - Strides are in ELEMENTS.  The innermost dimension of every tensor must have stride 1.
  *   - `stream` is the cudaStream_t to launch on (0 = legacy default stream).
  *   - Return value: 0 = kernel launched; non-zero = nothing was launched, b200_last_error() says why.
- *   - No entry point synchronises, allocates device memory, or reads device data on the host, so all of
- *     them may be captured into a CUDA graph (exceptions are marked "host-synchronous").
+ *   - The entry points that replace a reference operator, and the two fused attention steps, neither synchronise,
+ *     nor allocate device memory, nor read device data on the host, so they may be captured into a CUDA graph
+ *     (exceptions are marked "host-synchronous").
  *   - Kernels do no bounds checks on page ids or positions: sizing the page table is the caller's job,
  *     exactly as in the reference (triton_kernels/gqa_attention_decode_paged.py:225-226).
  */
