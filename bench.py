@@ -506,7 +506,94 @@ def run_sweep(ops, ws, device, peak, steps):
                      "frac": nbytes / (ms * 1e-3) / 1e9 / peak})
         del states
         torch.cuda.empty_cache()
+    rows += run_prefill_sweep(ops, device, steps)
     return rows
+
+
+def run_prefill_sweep(ops, device, steps):
+    """Prefill-side operators at the BASELINE shapes: packed varlen causal attention (config 3: B=32, lengths
+    ~U[16,512] seed 2, plus a long-prompt shape where the tensor bound applies) and the GDN prefill forms (config 4:
+    32 prompts x 128 tokens).  Reported against both rooflines; inputs are regenerated per call site, not rotated
+    (every call reads each input once, outputs are larger than the reuse L2 could give)."""
+    rows = []
+    tf_peak = 1649.6
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            tf_peak = float(json.loads(p.read_text())["bf16_tflops"])
+        except Exception:
+            pass
+    hbm, _ = hbm_peak()
+    gen = torch.Generator().manual_seed(2)
+    for tag, lengths in (("cfg3 B=32 L~U[16,512]", torch.randint(16, 513, (32,), generator=gen).tolist()),
+                         ("long B=8 L=4096", [4096] * 8)):
+        total = sum(lengths)
+        q = torch.randn(total, HQ, D, device=device, dtype=torch.bfloat16)
+        k = torch.randn(total, HKV, D, device=device, dtype=torch.bfloat16)
+        v = torch.randn(total, HKV, D, device=device, dtype=torch.bfloat16)
+        gate = torch.randn(total, HQ * D, device=device, dtype=torch.bfloat16)
+        cu, max_len = ops.build_cu_seqlens(lengths, device=device)
+        flops = 4096 * sum(n * (n + 1) for n in lengths)
+        nbytes = total * (4096 + 1024 + 1024 + 4096)
+        ms = time_steps(lambda i: ops.gqa_attention_varlen_causal(q, k, v, cu, max_len), steps, 3)
+        rows.append({"op": "gqa_attention_varlen_causal", "shape": tag, "tokens": total, "us": ms * 1e3,
+                     "tflops": flops / (ms * 1e-3) / 1e12, "frac_tensor": flops / (ms * 1e-3) / 1e12 / tf_peak,
+                     "gbs": nbytes / (ms * 1e-3) / 1e9, "frac_hbm": nbytes / (ms * 1e-3) / 1e9 / hbm})
+        pps = [cdiv(n, PAGE) for n in lengths]
+        table = torch.zeros(len(lengths), max(pps), dtype=torch.int32)
+        perm = torch.randperm(sum(pps), generator=gen)
+        off = 0
+        for i, n in enumerate(pps):
+            table[i, :n] = perm[off:off + n].to(torch.int32)
+            off += n
+        table = table.to(device)
+        kc, vc = ops.allocate_paged_kv_cache(sum(pps), HKV, D, device=device)
+        ids = torch.cat([torch.arange(n) for n in lengths]).to(torch.int32).to(device)
+        inv = (1.0 / (1e7 ** (torch.arange(0, ROT, 2, dtype=torch.float32) / ROT))).to(device)
+        out = torch.empty(total, HQ * D, dtype=torch.bfloat16, device=device)
+        ms = time_steps(lambda i: ops.fused_prefill_attention(q, k, v, gate, kc, vc, table, cu, ids, inv, ROT, max_len,
+                                                              out=out), steps, 3)
+        nbytes_f = nbytes + total * (4096 + 2048)
+        rows.append({"op": "fused_prefill_attention", "shape": tag, "tokens": total, "us": ms * 1e3,
+                     "tflops": flops / (ms * 1e-3) / 1e12, "frac_tensor": flops / (ms * 1e-3) / 1e12 / tf_peak,
+                     "gbs": nbytes_f / (ms * 1e-3) / 1e9, "frac_hbm": nbytes_f / (ms * 1e-3) / 1e9 / hbm})
+        del q, k, v, gate, kc, vc, out
+        torch.cuda.empty_cache()
+    # GDN prefill, config 4: 32 prompts x 128 tokens, 16 heads
+    heads, lengths = 16, [128] * 32
+    total = sum(lengths)
+    gq = torch.nn.functional.normalize(torch.randn(total, heads, 128, generator=gen), dim=-1) * 128 ** -0.5
+    gk = torch.nn.functional.normalize(torch.randn(total, heads, 128, generator=gen), dim=-1)
+    gq, gk = gq.to(torch.bfloat16).to(device), gk.to(torch.bfloat16).to(device)
+    gv = torch.randn(total, heads, 128, generator=gen).to(torch.bfloat16).to(device)
+    beta = torch.sigmoid(torch.randn(total, heads, generator=gen)).to(device)
+    g = (-torch.nn.functional.softplus(torch.randn(total, heads, generator=gen))
+         * torch.exp(torch.rand(heads, generator=gen) * 2.7)).to(device)
+    cu, _ = ops.build_cu_seqlens(lengths, device=device)
+    flops = total * heads * 7 * 128 * 128  # seven 128x128 fp32 multiply-adds-ish per token per head
+    nbytes = total * heads * 128 * 2 * 4 + len(lengths) * heads * 128 * 128 * 4
+    ms = time_steps(lambda i: _gdn_seq_nosync(ops, gq, gk, gv, beta, g, cu, len(lengths)), steps, 3)
+    rows.append({"op": "gdn_recurrent_prefill_sequential", "shape": "cfg4 B=32 x 128", "tokens": total, "us": ms * 1e3,
+                 "tflops_fp32": flops / (ms * 1e-3) / 1e12, "gbs": nbytes / (ms * 1e-3) / 1e9})
+    one = slice(0, 128)
+    ms = time_steps(lambda i: ops.call_gdn_recurrent_prefill_chunked_triton(gq[one], gk[one], gv[one], beta[one], g[one]),
+                    steps, 3)
+    rows.append({"op": "gdn chunk-64 pipeline (3 launches)", "shape": "1 sequence x 128", "tokens": 128, "us": ms * 1e3})
+    return rows
+
+
+def _gdn_seq_nosync(ops, q, k, v, beta, g, cu, batch):
+    """gdn_recurrent_prefill_sequential through the C ABI without the operator's host read of cu_seqlens[-1] (the
+    reference's assert), so that it can sit inside a CUDA graph."""
+    from b200attn import _lib
+    total, heads, dk = q.shape
+    out = torch.empty_like(v)
+    state = torch.empty(batch, heads, dk, v.shape[-1], dtype=torch.float32, device=q.device)
+    _lib.call("b200_gdn_recurrent_prefill_sequential", q.data_ptr(), q.stride(0), q.stride(1), k.data_ptr(), k.stride(0),
+              k.stride(1), v.data_ptr(), v.stride(0), v.stride(1), beta.data_ptr(), beta.stride(0), beta.stride(1),
+              g.data_ptr(), g.stride(0), g.stride(1), cu.data_ptr(), batch, total, state.data_ptr(), out.data_ptr(),
+              out.stride(0), out.stride(1), heads, dk, v.shape[-1], torch.cuda.current_stream().cuda_stream)
+    return out
 
 
 if __name__ == "__main__":
