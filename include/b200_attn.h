@@ -43,6 +43,12 @@ int b200_abi_version(void);
  * last call (the flag is cleared), 0 if not, -1 on a runtime error.  For tests and debugging. */
 int b200_wait_timed_out(void);
 
+/* Diagnostic: one CTA multiplies two bf16 tiles loaded by tensor-map TMA with tcgen05.mma (accumulator in tensor
+ * memory) and writes fp32 C.  mode 0: C[128x64] = A[128x256] . B[64x256]^T;  mode 1: C[128x256] = A[128x64] . B[64x256].
+ * All matrices row-major and contiguous.  No counterpart in the reference; it validates the sm_100a building blocks
+ * the prefill kernels use. */
+int b200_selftest_umma(int32_t mode, const void* a, const void* b, float* c, b200_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------ paged KV cache */
 /* cache[block_table[b, pos[b]/16], h, pos[b]%16, :] = new[b, h, :] for K and V.
  * Replaces wy_lib::paged_kv_append, triton_kernels/gqa_attention_decode_paged.py:254-305 (kernel :175-250).
