@@ -128,14 +128,15 @@ int b200_fused_decode_attention_static(const void* q, int64_t q_stride_b, int64_
 
 /* ------------------------------------------------------------------------------------------ varlen causal prefill attention */
 /* Block-diagonal causal GQA over a packed batch: q [T,H_q,256], k/v [T,H_kv,256] bf16 (any t/h strides),
- * cu_seqlens [B+1] int32, out [T,H_q,256] bf16.  max_seqlen (host) only sizes the grid.
+ * cu_seqlens [B+1] int32, out [T,H_q,256] bf16.  total_tokens = T bounds the TMA tensor maps; max_seqlen (host) only
+ * sizes the grid.  Runs on tcgen05 tensor cores with accumulators in tensor memory.
  * Replaces wy_lib::gqa_attention_varlen_causal, triton_kernels/gqa_attention_varlen_causal.py:214-278
  * (kernel :99-210). */
 int b200_gqa_varlen_causal(const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k, int64_t k_stride_t,
                            int64_t k_stride_h, const void* v, int64_t v_stride_t, int64_t v_stride_h, void* out,
                            int64_t out_stride_t, int64_t out_stride_h, const int32_t* cu_seqlens, int32_t batch,
-                           int32_t max_seqlen, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
-                           b200_stream_t stream);
+                           int32_t total_tokens, int32_t max_seqlen, int32_t num_q_heads, int32_t num_kv_heads,
+                           int32_t head_dim, b200_stream_t stream);
 
 /* Fused prefill attention layer core in two launches: (1) partial RoPE on k at position_ids[t] and scatter of the
  * rotated k and of v into the paged cache; (2) partial RoPE on q, causal attention that reads K/V back through the

@@ -389,7 +389,7 @@ def gqa_attention_varlen_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
     assert out.stride(2) == 1
     _lib.call("b200_gqa_varlen_causal", _ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1), _ptr(v),
               v.stride(0), v.stride(1), _ptr(out), out.stride(0), out.stride(1), _ptr(cu_seqlens.contiguous()), batch,
-              int(max_seqlen), num_q_head, num_kv_head, d_model, _stream())
+              total_tokens, int(max_seqlen), num_q_head, num_kv_head, d_model, _stream())
     return out
 
 

@@ -1,5 +1,4 @@
 // Packed variable-length causal GQA prefill attention (4 Q heads per KV head, head_dim 256).
-//   b200_gqa_varlen_causal        <-> triton_kernels/gqa_attention_varlen_causal.py:214-278 (kernel :99-210)
 //   b200_fused_prefill_attention  <-> the chain of engine/runner.py:339-384: partial_rope(q), partial_rope(k),
 //                                     gqa_attention_varlen_causal, attention_gate_pack, paged_kv_fill_varlen
 //
@@ -366,35 +365,6 @@ static int launch_varlen(const PrefillParams& p, int batch, int num_kv_heads, in
 using namespace b200;
 
 static bool mult8(int64_t x) { return (x & 7) == 0; }
-
-extern "C" int b200_gqa_varlen_causal(const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k,
-                                      int64_t k_stride_t, int64_t k_stride_h, const void* v, int64_t v_stride_t,
-                                      int64_t v_stride_h, void* out, int64_t out_stride_t, int64_t out_stride_h,
-                                      const int32_t* cu_seqlens, int32_t batch, int32_t max_seqlen,
-                                      int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
-                                      b200_stream_t stream) {
-  B200_REQUIRE(batch > 0 && batch <= 65535, "gqa_varlen_causal: batch must be in [1, 65535]");
-  B200_REQUIRE(head_dim == HEAD_DIM, "gqa_varlen_causal: head_dim must be %d (got %d)", HEAD_DIM, head_dim);
-  B200_REQUIRE(num_kv_heads > 0 && num_q_heads == num_kv_heads * GROUP,
-               "gqa_varlen_causal: needs %d Q heads per KV head (got %d/%d)", GROUP, num_q_heads, num_kv_heads);
-  B200_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && mult8(q_stride_t) &&
-                   mult8(q_stride_h) && mult8(k_stride_t) && mult8(k_stride_h) && mult8(v_stride_t) &&
-                   mult8(v_stride_h) && mult8(out_stride_t) && mult8(out_stride_h),
-               "gqa_varlen_causal: tensors must be 16-byte aligned with strides that are multiples of 8");
-  if (max_seqlen <= 0) return OK;
-  PrefillParams p = {};
-  p.q = static_cast<const __nv_bfloat16*>(q);
-  p.k = static_cast<const __nv_bfloat16*>(k);
-  p.v = static_cast<const __nv_bfloat16*>(v);
-  p.out = static_cast<__nv_bfloat16*>(out);
-  p.q_t = q_stride_t; p.q_h = q_stride_h; p.k_t = k_stride_t; p.k_h = k_stride_h;
-  p.v_t = v_stride_t; p.v_h = v_stride_h; p.out_t = out_stride_t; p.out_h = out_stride_h;
-  p.cu_seqlens = cu_seqlens;
-  p.err = wait_timeout_flag();
-  if (!p.err) return fail(ERR_RUNTIME, "gqa_varlen_causal: no error flag");
-  p.qk_scale = (1.0f / sqrtf(static_cast<float>(head_dim))) * LOG2E;
-  return launch_varlen<false, false>(p, batch, num_kv_heads, max_seqlen, reinterpret_cast<cudaStream_t>(stream));
-}
 
 extern "C" int b200_fused_prefill_attention(const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k,
                                             int64_t k_stride_t, int64_t k_stride_h, const void* v, int64_t v_stride_t,

@@ -9,8 +9,8 @@
 
 namespace b200 {
 
-bool encode_tile_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
-                     uint32_t box_rows, uint32_t box_blocks) {
+bool encode_map_bf16_sw128(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                           const uint64_t* strides_bytes, const uint32_t* box) {
   typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -25,14 +25,30 @@ bool encode_tile_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t
     }
     encode = reinterpret_cast<EncodeFn>(fn);
   }
-  if (cols % 64 != 0 || row_stride_bytes % 16 != 0 || (reinterpret_cast<uintptr_t>(base) & 15) != 0) return false;
-  const cuuint64_t dims[3] = {64, rows, cols / 64};
-  const cuuint64_t strides[2] = {row_stride_bytes, 128};  // bytes, for dimensions 1 and 2
-  const cuuint32_t box[3] = {64, box_rows, box_blocks};
-  const cuuint32_t elem_strides[3] = {1, 1, 1};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem_strides,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+  if (rank < 3 || rank > 5 || dims[0] != 64 || box[0] != 64 || (reinterpret_cast<uintptr_t>(base) & 15) != 0) return false;
+  cuuint64_t d[5], st[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+    if (i + 1 < rank) {
+      if (strides_bytes[i] % 16 != 0) return false;
+      st[i] = strides_bytes[i];
+    }
+  }
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base), d, st, bx,
+                es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool encode_tile_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride_bytes,
+                     uint32_t box_rows, uint32_t box_blocks) {
+  if (cols % 64 != 0) return false;
+  const uint64_t dims[3] = {64, rows, cols / 64};
+  const uint64_t strides[2] = {row_stride_bytes, 128};
+  const uint32_t box[3] = {64, box_rows, box_blocks};
+  return encode_map_bf16_sw128(map, base, 3, dims, strides, box);
 }
 
 constexpr int ST_A_BYTES = 128 * 256 * 2;  // largest A tile (mode 0)
