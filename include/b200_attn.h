@@ -138,12 +138,14 @@ int b200_gqa_varlen_causal(const void* q, int64_t q_stride_t, int64_t q_stride_h
                            int32_t total_tokens, int32_t max_seqlen, int32_t num_q_heads, int32_t num_kv_heads,
                            int32_t head_dim, b200_stream_t stream);
 
-/* Fused prefill attention layer core in two launches: (1) partial RoPE on k at position_ids[t] and scatter of the
- * rotated k and of v into the paged cache; (2) partial RoPE on q, causal attention that reads K/V back through the
- * page table, sigmoid output gate.  Replaces the chain partial_rope x2 -> gqa_attention_varlen_causal ->
- * attention_gate_pack -> paged_kv_fill_varlen of engine/runner.py:339-384.
+/* Fused prefill attention layer core in two launches: (1) partial RoPE on k at position_ids[t], scatter of the
+ * rotated k and of v into the paged cache, and a packed copy of the rotated k into k_rot_scratch; (2) partial RoPE on
+ * q in shared memory, causal attention on the tensor cores (tcgen05/TMEM), sigmoid output gate.  Replaces the chain
+ * partial_rope x2 -> gqa_attention_varlen_causal -> attention_gate_pack -> paged_kv_fill_varlen of
+ * engine/runner.py:339-384.
  * q [T,H_q,256], k/v [T,H_kv,256] are the post-norm PRE-RoPE projections; gate [T, H_q*256] (row stride
- * gate_stride_t); position_ids [T] int32/int64; out [T, H_q*256] bf16 contiguous; rotary_dim must be 64. */
+ * gate_stride_t); position_ids [T] int32/int64; k_rot_scratch: T*H_kv*256 bf16 of caller-owned device memory
+ * (contents undefined afterwards); out [T, H_q*256] bf16 contiguous; rotary_dim must be 64. */
 int b200_fused_prefill_attention(const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k,
                                  int64_t k_stride_t, int64_t k_stride_h, const void* v, int64_t v_stride_t,
                                  int64_t v_stride_h, const void* gate, int64_t gate_stride_t, void* k_cache,
@@ -151,8 +153,9 @@ int b200_fused_prefill_attention(const void* q, int64_t q_stride_t, int64_t q_st
                                  int64_t vc_stride_p, int64_t vc_stride_h, int64_t vc_stride_s,
                                  const int32_t* block_table, int64_t bt_stride_b, const int32_t* cu_seqlens,
                                  const void* position_ids, int32_t ids_are_int64, const float* inv_freq,
-                                 int32_t rotary_dim, void* out, int32_t batch, int32_t max_seqlen,
-                                 int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, b200_stream_t stream);
+                                 int32_t rotary_dim, void* k_rot_scratch, void* out, int32_t batch,
+                                 int32_t total_tokens, int32_t max_seqlen, int32_t num_q_heads, int32_t num_kv_heads,
+                                 int32_t head_dim, b200_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------ rope / gate */
 /* Half-split rotation of the first rotary_dim dims of x [B,H,T,D] bf16 (dims >= rotary_dim copied).

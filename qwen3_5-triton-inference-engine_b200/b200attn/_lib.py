@@ -28,7 +28,7 @@ SIGNATURES: dict[str, list] = {
     "b200_selftest_umma": [I32, P, P, P, P],
     "b200_gqa_varlen_causal": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I32, I32, I32, I32, I32, I32, P],
     "b200_fused_prefill_attention": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, P, P, I64, I64, I64, I64, I64, I64,
-                                     P, I64, P, P, I32, P, I32, P, I32, I32, I32, I32, I32, P],
+                                     P, I64, P, P, I32, P, I32, P, P, I32, I32, I32, I32, I32, I32, P],
     "b200_partial_rope": [P, I64, I64, I64, P, I64, I64, I64, P, I32, I64, I64, P, I32, I32, I32, I32, I32, P],
     "b200_attention_gate_pack": [P, I64, I64, P, I64, I64, P, I32, I32, I32, P],
     "b200_gdn_recurrent_decode": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64,

@@ -431,12 +431,13 @@ def fused_prefill_attention(q, k, v, gate, k_cache, v_cache, block_table, cu_seq
     if out is None:
         out = torch.empty((total, num_q_heads * head_dim), dtype=torch.bfloat16, device=q.device)
     assert out.is_contiguous() and out.shape == (total, num_q_heads * head_dim)
+    k_rot = torch.empty((total, num_kv_heads, head_dim), dtype=torch.bfloat16, device=q.device)  # rotated k, packed
     _lib.call("b200_fused_prefill_attention", _ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1),
               _ptr(v), v.stride(0), v.stride(1), _ptr(gate), gate.stride(0), _ptr(k_cache), _ptr(v_cache),
               k_cache.stride(0), k_cache.stride(1), k_cache.stride(2), v_cache.stride(0), v_cache.stride(1),
               v_cache.stride(2), _ptr(block_table), block_table.stride(0), _ptr(cu_seqlens), _ptr(position_ids),
-              int(position_ids.dtype == torch.int64), _ptr(inv_freq), int(rotary_dim), _ptr(out), batch,
-              int(max_seqlen), num_q_heads, num_kv_heads, head_dim, _stream())
+              int(position_ids.dtype == torch.int64), _ptr(inv_freq), int(rotary_dim), _ptr(k_rot), _ptr(out), batch,
+              total, int(max_seqlen), num_q_heads, num_kv_heads, head_dim, _stream())
     return out
 
 

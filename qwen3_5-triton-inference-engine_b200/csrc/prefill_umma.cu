@@ -1,5 +1,7 @@
 // Packed variable-length causal GQA prefill attention on the Blackwell tensor cores (tcgen05 + TMEM + tensor-map TMA).
-//   b200_gqa_varlen_causal <-> triton_kernels/gqa_attention_varlen_causal.py:214-278 (kernel :99-210)
+//   b200_gqa_varlen_causal       <-> triton_kernels/gqa_attention_varlen_causal.py:214-278 (kernel :99-210)
+//   b200_fused_prefill_attention <-> the chain of engine/runner.py:339-384: partial_rope(q), partial_rope(k),
+//                                    gqa_attention_varlen_causal, attention_gate_pack, paged_kv_fill_varlen
 //
 // One CTA = one (sequence, kv head, block of 32 query tokens).  The 4 Q heads of the group are stacked into the 128
 // rows of one MMA tile (row = token*4 + head, the stacking idea of gqa_attention_varlen_causal.py:151-160), so every
@@ -25,9 +27,9 @@ constexpr int PU_THREADS = 192;
 constexpr int PU_Q_BYTES = 128 * HEAD_DIM * 2;      // 64 KiB: 4 column blocks of [128 rows][64]
 constexpr int PU_P_BYTES = 128 * PU_TKV * 2;        // 16 KiB: [128 rows][64]
 constexpr int PU_KV_BYTES = PU_TKV * HEAD_DIM * 2;  // 32 KiB: 4 column blocks of [64 rows][64]
-constexpr int PU_SMEM = PU_Q_BYTES + PU_P_BYTES + 4 * PU_KV_BYTES + 1024;
+constexpr int PU_SMEM = PU_Q_BYTES + 2 * PU_P_BYTES + 4 * PU_KV_BYTES + 1024;
 constexpr int PU_OUT_PITCH = HEAD_DIM * 2 + 16;     // staging pitch of the epilogue (bytes)
-static_assert(128 * PU_OUT_PITCH <= PU_Q_BYTES + PU_P_BYTES, "output staging must fit in the Q + P region");
+static_assert(128 * PU_OUT_PITCH <= PU_Q_BYTES + 2 * PU_P_BYTES, "output staging must fit in the Q + P region");
 constexpr uint32_t PU_TMEM_COLS = 512;              // S0 [0,64) S1 [64,128) O [128,384)
 constexpr float PU_TAU = 8.0f;                      // lazy-rescale threshold (log2 domain)
 constexpr float PU_LOG2E = 1.4426950408889634f;
@@ -38,13 +40,80 @@ struct PrefillUmmaParams {
   const int32_t* cu_seqlens;
   int* err;
   float scale_log2;
+  // fused form only: rotary embedding of q in shared memory, sigmoid gate in the epilogue
+  const __nv_bfloat16* gate;
+  int64_t gate_t;
+  const void* position_ids;
+  int ids_are_int64;
+  const float* inv_freq;
 };
 
+// Fused path, first kernel: rotate K at its position, scatter K (rotated) and V into the paged cache and keep a
+// packed copy of the rotated K [T, H_kv, 256] for the attention kernel's TMA loads (so the rotation is computed once
+// per token, not once per consumer tile).  One warp per (token, kv head) row, each lane 8 consecutive dims;
+// grid = (pages of the longest sequence, H_kv, B).
+__global__ void __launch_bounds__(128)
+rope_scatter_kernel(const __nv_bfloat16* __restrict__ k, int64_t k_t, int64_t k_h, const __nv_bfloat16* __restrict__ v,
+                    int64_t v_t, int64_t v_h, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                    int64_t kc_p, int64_t kc_h, int64_t kc_s, int64_t vc_p, int64_t vc_h, int64_t vc_s,
+                    const int32_t* __restrict__ block_table, int64_t bt_b, const int32_t* __restrict__ cu_seqlens,
+                    const void* __restrict__ position_ids, int ids_are_int64, const float* __restrict__ inv_freq,
+                    int rotary_half, __nv_bfloat16* __restrict__ k_rot, int num_kv_heads) {
+  const int lp = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq_start = cu_seqlens[b];
+  const int seq_len = cu_seqlens[b + 1] - seq_start;
+  if (lp * PAGE >= seq_len) return;
+  const int64_t phys = block_table[b * bt_b + lp];
+  const int lanes_half = rotary_half / 8;
+  const bool in_rot = lane < 2 * lanes_half;
+  const bool first = lane < lanes_half;
+  const int partner = first ? lane + lanes_half : lane - lanes_half;
+  for (int slot = warp; slot < PAGE; slot += 4) {
+    const int tok = lp * PAGE + slot;
+    if (tok >= seq_len) break;
+    const int64_t t = seq_start + tok;
+    const uint4 kraw = *reinterpret_cast<const uint4*>(k + t * k_t + h * k_h + lane * 8);
+    const uint4 vraw = *reinterpret_cast<const uint4*>(v + t * v_t + h * v_h + lane * 8);
+    uint32_t kw[4] = {kraw.x, kraw.y, kraw.z, kraw.w};
+    if (rotary_half > 0) {
+      uint32_t other[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) other[i] = __shfl_sync(0xffffffffu, kw[i], in_rot ? partner : lane);
+      if (in_rot) {
+        const int64_t pid = ids_are_int64 ? static_cast<const int64_t*>(position_ids)[t]
+                                          : static_cast<int64_t>(static_cast<const int32_t*>(position_ids)[t]);
+        const float posf = static_cast<float>(pid);
+        const int dbase = (first ? lane : partner) * 8;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float s0, c0, s1, c1;
+          sincosf(posf * inv_freq[dbase + 2 * i], &s0, &c0);
+          sincosf(posf * inv_freq[dbase + 2 * i + 1], &s1, &c1);
+          const uint32_t fa = first ? kw[i] : other[i];
+          const uint32_t fb = first ? other[i] : kw[i];
+          float f0, g0, f1, g1;
+          rope_pair(bf16_lo(fa), bf16_lo(fb), s0, c0, f0, g0);
+          rope_pair(bf16_hi(fa), bf16_hi(fb), s1, c1, f1, g1);
+          kw[i] = first ? pack_bf16(f0, f1) : pack_bf16(g0, g1);
+        }
+      }
+    }
+    const uint4 krot = make_uint4(kw[0], kw[1], kw[2], kw[3]);
+    *reinterpret_cast<uint4*>(k_cache + phys * kc_p + h * kc_h + slot * kc_s + lane * 8) = krot;
+    *reinterpret_cast<uint4*>(k_rot + (t * num_kv_heads + h) * HEAD_DIM + lane * 8) = krot;
+    *reinterpret_cast<uint4*>(v_cache + phys * vc_p + h * vc_h + slot * vc_s + lane * 8) = vraw;
+  }
+}
+
+
+
+template <bool FUSED>
 __global__ void __launch_bounds__(PU_THREADS, 1)
 varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                           const __grid_constant__ CUtensorMap map_v, const __grid_constant__ PrefillUmmaParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ uint64_t bar_q, bar_k[2], bar_v[2], bar_s[2], bar_p[2], bar_pv[2];
+  __shared__ uint64_t bar_q, bar_qr, bar_k[2], bar_v[2], bar_s[2], bar_p[2], bar_pv[2];
   __shared__ uint32_t tmem_slot;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -60,12 +129,13 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_s = smem;
   uint8_t* p_s = smem + PU_Q_BYTES;
-  uint8_t* k_s = p_s + PU_P_BYTES;      // two stages
+  uint8_t* k_s = p_s + 2 * PU_P_BYTES;  // two stages (P is double-buffered too)
   uint8_t* v_s = k_s + 2 * PU_KV_BYTES;  // two stages
 
   if (warp == 0) tmem_alloc(&tmem_slot, PU_TMEM_COLS);
   if (tid == 0) {
     mbar_init(&bar_q, 1);
+    mbar_init(&bar_qr, 128);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar_k[i], 1);
       mbar_init(&bar_v[i], 1);
@@ -106,7 +176,7 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
       const uint32_t idesc_s = idesc_bf16_f32(128, PU_TKV, false, false);
       const uint32_t idesc_o = idesc_bf16_f32(128, HEAD_DIM, false, true);
       const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
-      bool ok = mbar_wait_bounded(&bar_q, 0);
+      bool ok = FUSED ? mbar_wait_bounded(&bar_qr, 0) : mbar_wait_bounded(&bar_q, 0);
       auto issue_pv = [&](int jj) {
         const int s = jj & 1;
         ok = ok && mbar_wait_bounded(&bar_p[s], (jj >> 1) & 1);
@@ -116,7 +186,7 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         const uint32_t v_addr = smem_u32(v_s + s * PU_KV_BYTES);
 #pragma unroll
         for (int kt = 0; kt < PU_TKV / 16; ++kt)
-          umma_ss(tmem_o, smem_desc_sw128(p_addr + kt * 32, 16, 1024),
+          umma_ss(tmem_o, smem_desc_sw128(p_addr + s * PU_P_BYTES + kt * 32, 16, 1024),
                   smem_desc_sw128(v_addr + kt * 2048, PU_TKV * 128, 1024), idesc_o, (jj > 0) || (kt > 0));
         umma_commit(&bar_pv[s]);
       };
@@ -143,6 +213,43 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
     float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
+    if (FUSED) {
+      // rotate this thread's Q row in place (dims j and j+32, j < 32, all inside column block 0 of the swizzled
+      // tile).  The 32 angles of a token are shared by its 4 heads = 4 adjacent lanes: each computes 8 of them.
+      const int tok = min(q_tok, seq_len - 1);
+      const int64_t t = seq_start + tok;
+      const int64_t pid = p.ids_are_int64 ? static_cast<const int64_t*>(p.position_ids)[t]
+                                          : static_cast<int64_t>(static_cast<const int32_t*>(p.position_ids)[t]);
+      const float posf = static_cast<float>(pid);
+      float cs[8], sn[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sincosf(posf * p.inv_freq[(lane & 3) * 8 + i], &sn[i], &cs[i]);
+      ok = mbar_wait_bounded(&bar_q, 0);
+      uint8_t* qrow = q_s + row * 128;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {  // chunk c holds dims [8c, 8c+8), chunk c+4 their partners [32+8c, 40+8c)
+        uint4* pa = reinterpret_cast<uint4*>(qrow + ((c ^ (row & 7)) << 4));
+        uint4* pb = reinterpret_cast<uint4*>(qrow + (((c + 4) ^ (row & 7)) << 4));
+        const uint4 va = *pa, vb = *pb;
+        uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          // angle index 8c + 2k (+1) lives in lane (quad base + c), register 2k (+1)
+          const int src = (lane & ~3) + c;
+          const float c0 = __shfl_sync(0xffffffffu, cs[2 * k], src), s0 = __shfl_sync(0xffffffffu, sn[2 * k], src);
+          const float c1 = __shfl_sync(0xffffffffu, cs[2 * k + 1], src), s1 = __shfl_sync(0xffffffffu, sn[2 * k + 1], src);
+          float f0, g0, f1, g1;
+          rope_pair(bf16_lo(wa[k]), bf16_lo(wb[k]), s0, c0, f0, g0);
+          rope_pair(bf16_hi(wa[k]), bf16_hi(wb[k]), s1, c1, f1, g1);
+          wa[k] = pack_bf16(f0, f1);
+          wb[k] = pack_bf16(g0, g1);
+        }
+        *pa = make_uint4(wa[0], wa[1], wa[2], wa[3]);
+        *pb = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+      }
+      fence_proxy_async();  // the rotated rows must be visible to the tensor core's reads
+      mbar_arrive(&bar_qr);
+    }
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int s = j & 1;
       ok = mbar_wait_bounded(&bar_s[s], (j >> 1) & 1);
@@ -168,12 +275,12 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
       if (j == 0) {
         m_ref = m_new;
       } else {
-        // the P buffer is still being read by PV of tile j-1, and O must be at rest before it is rescaled
-        ok = mbar_wait_bounded(&bar_pv[(j - 1) & 1], ((j - 1) >> 1) & 1);
-        if (!ok) break;
-        tc_fence_after_sync();
         const bool need = (m_new - m_ref) > PU_TAU;
         if (__any_sync(0xffffffffu, need)) {
+          // O must be at rest before it is rescaled: wait for the PV product of tile j-1
+          ok = mbar_wait_bounded(&bar_pv[(j - 1) & 1], ((j - 1) >> 1) & 1);
+          if (!ok) break;
+          tc_fence_after_sync();
           const float alpha = need ? exp2f(m_ref - m_new) : 1.f;
 #pragma unroll 1
           for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
@@ -188,10 +295,15 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
           l_run *= alpha;
           if (need) m_ref = m_new;
         }
+        if (j >= 2) {
+          // this tile's P buffer was last read by the PV product of tile j-2
+          ok = mbar_wait_bounded(&bar_pv[s], ((j - 2) >> 1) & 1);
+          if (!ok) break;
+        }
       }
       // p = exp2(s - m_ref): fp32 for l, bf16 for the PV product, written as row `row` of the swizzled P tile
       float sum = 0.f;
-      uint8_t* prow = p_s + row * 128;
+      uint8_t* prow = p_s + s * PU_P_BYTES + row * 128;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
         uint32_t w[4];
@@ -235,13 +347,40 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");  // the four softmax warps only
     if (ok) {
-      for (int i = tid; i < 128 * (HEAD_DIM / 8); i += 128) {
-        const int r = i >> 5, ch = i & 31;
-        const int tok = q0 + (r >> 2);
-        if (tok < seq_len) {
-          const uint4 v = *reinterpret_cast<const uint4*>(smem + r * PU_OUT_PITCH + ch * 16);
-          *reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(seq_start + tok) * p.out_t +
-                                    (h * GROUP + (r & 3)) * p.out_h + ch * 8) = v;
+      // 128 rows x 32 sixteen-byte chunks; a warp covers one 512-byte row per step.  The gate rows are fetched
+      // eight steps at a time so that their latency is paid once per batch, not once per chunk.
+      constexpr int STEPS = HEAD_DIM / 8;  // 32 iterations of 128 threads
+#pragma unroll 1
+      for (int i0 = 0; i0 < STEPS; i0 += 8) {
+        uint4 gv[8];
+        if (FUSED) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int i = (i0 + u) * 128 + tid, r = i >> 5, ch = i & 31;
+            const int tok = min(q0 + (r >> 2), seq_len - 1);
+            gv[u] = *reinterpret_cast<const uint4*>(p.gate + static_cast<int64_t>(seq_start + tok) * p.gate_t +
+                                                    (h * GROUP + (r & 3)) * HEAD_DIM + ch * 8);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = (i0 + u) * 128 + tid, r = i >> 5, ch = i & 31;
+          const int tok = q0 + (r >> 2);
+          if (tok < seq_len) {
+            uint4 v = *reinterpret_cast<const uint4*>(smem + r * PU_OUT_PITCH + ch * 16);
+            if (FUSED) {
+              uint32_t xs[4] = {v.x, v.y, v.z, v.w};
+              const uint32_t gs[4] = {gv[u].x, gv[u].y, gv[u].z, gv[u].w};
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const float g0 = 1.f / (1.f + __expf(-bf16_lo(gs[k]))), g1 = 1.f / (1.f + __expf(-bf16_hi(gs[k])));
+                xs[k] = pack_bf16(bf16_lo(xs[k]) * g0, bf16_hi(xs[k]) * g1);
+              }
+              v = make_uint4(xs[0], xs[1], xs[2], xs[3]);
+            }
+            *reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(seq_start + tok) * p.out_t +
+                                      (h * GROUP + (r & 3)) * p.out_h + ch * 8) = v;
+          }
         }
       }
     }
@@ -256,6 +395,49 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
 using namespace b200;
 
 static bool mult8(int64_t x) { return (x & 7) == 0; }
+
+// Encodes the tensor maps and launches the attention kernel (FUSED adds rope on q and the output gate).
+template <bool FUSED>
+static int launch_prefill_umma(const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k, int64_t k_stride_t,
+                               int64_t k_stride_h, const void* v, int64_t v_stride_t, int64_t v_stride_h,
+                               PrefillUmmaParams p, int batch, int total_tokens, int max_seqlen, int num_kv_heads,
+                               cudaStream_t stream, const char* what) {
+  CUtensorMap map_q, map_k, map_v;
+  const uint64_t T = static_cast<uint64_t>(total_tokens), H = static_cast<uint64_t>(num_kv_heads);
+  {
+    // q as {64 cols, 4 heads of a group, groups, tokens, 4 column blocks}; one load = 32 tokens of one group
+    const uint64_t dims[5] = {64, GROUP, H, T, HEAD_DIM / 64};
+    const uint64_t strides[4] = {static_cast<uint64_t>(q_stride_h) * 2, static_cast<uint64_t>(q_stride_h) * 2 * GROUP,
+                                 static_cast<uint64_t>(q_stride_t) * 2, 128};
+    const uint32_t box[5] = {64, GROUP, 1, PU_BQ, HEAD_DIM / 64};
+    if (!encode_map_bf16_sw128(&map_q, q, 5, dims, strides, box))
+      return fail(ERR_RUNTIME, "%s: cannot encode the tensor map of q", what);
+  }
+  {
+    // k, v as {64 cols, tokens, 4 column blocks, kv heads}; one load = 64 tokens of one head
+    const uint64_t dims[4] = {64, T, HEAD_DIM / 64, H};
+    const uint32_t box[4] = {64, PU_TKV, HEAD_DIM / 64, 1};
+    const uint64_t ks[3] = {static_cast<uint64_t>(k_stride_t) * 2, 128, static_cast<uint64_t>(k_stride_h) * 2};
+    const uint64_t vs[3] = {static_cast<uint64_t>(v_stride_t) * 2, 128, static_cast<uint64_t>(v_stride_h) * 2};
+    if (!encode_map_bf16_sw128(&map_k, k, 4, dims, ks, box) || !encode_map_bf16_sw128(&map_v, v, 4, dims, vs, box))
+      return fail(ERR_RUNTIME, "%s: cannot encode the tensor maps of k / v", what);
+  }
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(varlen_causal_umma_kernel<FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, PU_SMEM) !=
+        cudaSuccess)
+      return fail(ERR_RUNTIME, "%s: cannot raise dynamic shared memory to %d", what, PU_SMEM);
+    configured[dev] = true;
+  }
+  p.err = wait_timeout_flag();
+  if (!p.err) return fail(ERR_RUNTIME, "%s: no error flag", what);
+  p.scale_log2 = (1.0f / sqrtf(static_cast<float>(HEAD_DIM))) * PU_LOG2E;
+  const dim3 grid((max_seqlen + PU_BQ - 1) / PU_BQ, num_kv_heads, batch);
+  varlen_causal_umma_kernel<FUSED><<<grid, PU_THREADS, PU_SMEM, stream>>>(map_q, map_k, map_v, p);
+  return check_launch(what);
+}
 
 extern "C" int b200_gqa_varlen_causal(const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k,
                                       int64_t k_stride_t, int64_t k_stride_h, const void* v, int64_t v_stride_t,
@@ -273,44 +455,62 @@ extern "C" int b200_gqa_varlen_causal(const void* q, int64_t q_stride_t, int64_t
                    mult8(v_stride_h) && mult8(out_stride_t) && mult8(out_stride_h),
                "gqa_varlen_causal: tensors must be 16-byte aligned with strides that are multiples of 8");
   if (max_seqlen <= 0) return OK;
-  CUtensorMap map_q, map_k, map_v;
-  const uint64_t T = static_cast<uint64_t>(total_tokens), H = static_cast<uint64_t>(num_kv_heads);
-  {
-    // q as {64 cols, 4 heads of a group, groups, tokens, 4 column blocks}; one load = 32 tokens of one group
-    const uint64_t dims[5] = {64, GROUP, H, T, HEAD_DIM / 64};
-    const uint64_t strides[4] = {static_cast<uint64_t>(q_stride_h) * 2, static_cast<uint64_t>(q_stride_h) * 2 * GROUP,
-                                 static_cast<uint64_t>(q_stride_t) * 2, 128};
-    const uint32_t box[5] = {64, GROUP, 1, PU_BQ, HEAD_DIM / 64};
-    if (!encode_map_bf16_sw128(&map_q, q, 5, dims, strides, box))
-      return fail(ERR_RUNTIME, "gqa_varlen_causal: cannot encode the tensor map of q");
-  }
-  {
-    // k, v as {64 cols, tokens, 4 column blocks, kv heads}; one load = 64 tokens of one head
-    const uint64_t dims[4] = {64, T, HEAD_DIM / 64, H};
-    const uint32_t box[4] = {64, PU_TKV, HEAD_DIM / 64, 1};
-    const uint64_t ks[3] = {static_cast<uint64_t>(k_stride_t) * 2, 128, static_cast<uint64_t>(k_stride_h) * 2};
-    const uint64_t vs[3] = {static_cast<uint64_t>(v_stride_t) * 2, 128, static_cast<uint64_t>(v_stride_h) * 2};
-    if (!encode_map_bf16_sw128(&map_k, k, 4, dims, ks, box) || !encode_map_bf16_sw128(&map_v, v, 4, dims, vs, box))
-      return fail(ERR_RUNTIME, "gqa_varlen_causal: cannot encode the tensor maps of k / v");
-  }
-  static bool configured[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    if (cudaFuncSetAttribute(varlen_causal_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PU_SMEM) !=
-        cudaSuccess)
-      return fail(ERR_RUNTIME, "gqa_varlen_causal: cannot raise dynamic shared memory to %d", PU_SMEM);
-    configured[dev] = true;
-  }
-  PrefillUmmaParams p;
+  PrefillUmmaParams p = {};
   p.out = static_cast<__nv_bfloat16*>(out);
   p.out_t = out_stride_t;
   p.out_h = out_stride_h;
   p.cu_seqlens = cu_seqlens;
-  p.err = wait_timeout_flag();
-  if (!p.err) return fail(ERR_RUNTIME, "gqa_varlen_causal: no error flag");
-  p.scale_log2 = (1.0f / sqrtf(static_cast<float>(head_dim))) * PU_LOG2E;
-  const dim3 grid((max_seqlen + PU_BQ - 1) / PU_BQ, num_kv_heads, batch);
-  varlen_causal_umma_kernel<<<grid, PU_THREADS, PU_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(map_q, map_k, map_v, p);
-  return check_launch("gqa_varlen_causal");
+  return launch_prefill_umma<false>(q, q_stride_t, q_stride_h, k, k_stride_t, k_stride_h, v, v_stride_t, v_stride_h, p,
+                                    batch, total_tokens, max_seqlen, num_kv_heads,
+                                    reinterpret_cast<cudaStream_t>(stream), "gqa_varlen_causal");
+}
+
+extern "C" int b200_fused_prefill_attention(const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k,
+                                            int64_t k_stride_t, int64_t k_stride_h, const void* v, int64_t v_stride_t,
+                                            int64_t v_stride_h, const void* gate, int64_t gate_stride_t, void* k_cache,
+                                            void* v_cache, int64_t kc_stride_p, int64_t kc_stride_h,
+                                            int64_t kc_stride_s, int64_t vc_stride_p, int64_t vc_stride_h,
+                                            int64_t vc_stride_s, const int32_t* block_table, int64_t bt_stride_b,
+                                            const int32_t* cu_seqlens, const void* position_ids, int32_t ids_are_int64,
+                                            const float* inv_freq, int32_t rotary_dim, void* k_rot_scratch, void* out,
+                                            int32_t batch, int32_t total_tokens, int32_t max_seqlen,
+                                            int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                                            b200_stream_t stream) {
+  B200_REQUIRE(batch > 0 && batch <= 65535, "fused_prefill_attention: batch must be in [1, 65535]");
+  B200_REQUIRE(total_tokens > 0, "fused_prefill_attention: total_tokens must be positive");
+  B200_REQUIRE(head_dim == HEAD_DIM, "fused_prefill_attention: head_dim must be %d (got %d)", HEAD_DIM, head_dim);
+  B200_REQUIRE(num_kv_heads > 0 && num_q_heads == num_kv_heads * GROUP,
+               "fused_prefill_attention: needs %d Q heads per KV head (got %d/%d)", GROUP, num_q_heads, num_kv_heads);
+  B200_REQUIRE(rotary_dim == 64, "fused_prefill_attention: rotary_dim must be 64 (got %d)", rotary_dim);
+  B200_REQUIRE(inv_freq != nullptr && position_ids != nullptr && k_rot_scratch != nullptr,
+               "fused_prefill_attention: NULL rope inputs or scratch");
+  B200_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(out) && aligned16(gate) &&
+                   aligned16(k_cache) && aligned16(v_cache) && aligned16(k_rot_scratch) && mult8(q_stride_t) &&
+                   mult8(q_stride_h) && mult8(k_stride_t) && mult8(k_stride_h) && mult8(v_stride_t) &&
+                   mult8(v_stride_h) && mult8(gate_stride_t) && mult8(kc_stride_p) && mult8(kc_stride_h) &&
+                   mult8(kc_stride_s) && mult8(vc_stride_p) && mult8(vc_stride_h) && mult8(vc_stride_s),
+               "fused_prefill_attention: tensors must be 16-byte aligned with strides that are multiples of 8");
+  if (max_seqlen <= 0) return OK;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const dim3 grid((max_seqlen + PAGE - 1) / PAGE, num_kv_heads, batch);
+  rope_scatter_kernel<<<grid, 128, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(k), k_stride_t, k_stride_h, static_cast<const __nv_bfloat16*>(v), v_stride_t,
+      v_stride_h, static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), kc_stride_p, kc_stride_h,
+      kc_stride_s, vc_stride_p, vc_stride_h, vc_stride_s, block_table, bt_stride_b, cu_seqlens, position_ids,
+      ids_are_int64, inv_freq, rotary_dim / 2, static_cast<__nv_bfloat16*>(k_rot_scratch), num_kv_heads);
+  int rc = check_launch("fused_prefill_attention (rope + scatter)");
+  if (rc != OK) return rc;
+  PrefillUmmaParams p = {};
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.out_t = static_cast<int64_t>(num_q_heads) * HEAD_DIM;
+  p.out_h = HEAD_DIM;
+  p.cu_seqlens = cu_seqlens;
+  p.gate = static_cast<const __nv_bfloat16*>(gate);
+  p.gate_t = gate_stride_t;
+  p.position_ids = position_ids;
+  p.ids_are_int64 = ids_are_int64;
+  p.inv_freq = inv_freq;
+  return launch_prefill_umma<true>(q, q_stride_t, q_stride_h, k_rot_scratch, static_cast<int64_t>(num_kv_heads) * HEAD_DIM,
+                                   HEAD_DIM, v, v_stride_t, v_stride_h, p, batch, total_tokens, max_seqlen,
+                                   num_kv_heads, st, "fused_prefill_attention");
 }
