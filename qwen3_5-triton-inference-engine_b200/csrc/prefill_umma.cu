@@ -259,18 +259,25 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
       tmem_ld32(tmem + lane_base + s * PU_TKV, r0);
       tmem_ld32(tmem + lane_base + s * PU_TKV + 32, r1);
       tmem_ld_wait();
-      // scale to the log2 domain, mask (causal and inside the sequence), row maximum
+      // mask (causal and inside the sequence; only tiles on the diagonal or at the sequence end need it) and take
+      // the row maximum of the raw scores; the scale (> 0) is folded into the exponent below
       const int lim = min(q_tok, seq_len - 1) - j * PU_TKV;  // last valid column of this tile for this row
-      float m_tile = -INFINITY;
+      if (lim < PU_TKV - 1) {
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        float a = __uint_as_float(r0[c]) * p.scale_log2, bb = __uint_as_float(r1[c]) * p.scale_log2;
-        a = (c <= lim) ? a : -INFINITY;
-        bb = (c + 32 <= lim) ? bb : -INFINITY;
-        r0[c] = __float_as_uint(a);
-        r1[c] = __float_as_uint(bb);
-        m_tile = fmaxf(m_tile, fmaxf(a, bb));
+        for (int c = 0; c < 32; ++c) {
+          if (c > lim) r0[c] = 0xff800000u;       // -inf
+          if (c + 32 > lim) r1[c] = 0xff800000u;
+        }
       }
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 32; c += 2) {
+        mx0 = fmaxf(mx0, __uint_as_float(r0[c]));
+        mx1 = fmaxf(mx1, __uint_as_float(r0[c + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(r1[c]));
+        mx3 = fmaxf(mx3, __uint_as_float(r1[c + 1]));
+      }
+      const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
       const float m_new = fmaxf(m_ref, m_tile);
       if (j == 0) {
         m_ref = m_new;
@@ -281,7 +288,7 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
           ok = mbar_wait_bounded(&bar_pv[(j - 1) & 1], ((j - 1) >> 1) & 1);
           if (!ok) break;
           tc_fence_after_sync();
-          const float alpha = need ? exp2f(m_ref - m_new) : 1.f;
+          const float alpha = need ? ex2_fast(m_ref - m_new) : 1.f;
 #pragma unroll 1
           for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
             uint32_t o[32];
@@ -301,8 +308,9 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
           if (!ok) break;
         }
       }
-      // p = exp2(s - m_ref): fp32 for l, bf16 for the PV product, written as row `row` of the swizzled P tile
-      float sum = 0.f;
+      // p = 2^(s*scale - m_ref): fp32 for l, bf16 for the PV product, written as row `row` of the swizzled P tile
+      float sum0 = 0.f, sum1 = 0.f;
+      const float neg_m = -m_ref, sc = p.scale_log2;
       uint8_t* prow = p_s + s * PU_P_BYTES + row * 128;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
@@ -310,13 +318,15 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const int c = ch * 8 + k * 2;
-          const float x0 = exp2f(__uint_as_float(c < 32 ? r0[c] : r1[c - 32]) - m_ref);
-          const float x1 = exp2f(__uint_as_float(c + 1 < 32 ? r0[c + 1] : r1[c + 1 - 32]) - m_ref);
-          sum += x0 + x1;
+          const float x0 = ex2_fast(fmaf(__uint_as_float(c < 32 ? r0[c] : r1[c - 32]), sc, neg_m));
+          const float x1 = ex2_fast(fmaf(__uint_as_float(c + 1 < 32 ? r0[c + 1] : r1[c + 1 - 32]), sc, neg_m));
+          sum0 += x0;
+          sum1 += x1;
           w[k] = pack_bf16(x0, x1);
         }
         *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
+      const float sum = sum0 + sum1;
       l_run += sum;
       fence_proxy_async();      // generic-proxy stores to P before the tensor core (async proxy) reads them
       tc_fence_before_sync();   // this thread's TMEM loads/stores before the arrive
@@ -373,8 +383,8 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
               const uint32_t gs[4] = {gv[u].x, gv[u].y, gv[u].z, gv[u].w};
 #pragma unroll
               for (int k = 0; k < 4; ++k) {
-                const float g0 = 1.f / (1.f + __expf(-bf16_lo(gs[k]))), g1 = 1.f / (1.f + __expf(-bf16_hi(gs[k])));
-                xs[k] = pack_bf16(bf16_lo(xs[k]) * g0, bf16_hi(xs[k]) * g1);
+                xs[k] = pack_bf16(bf16_lo(xs[k]) * sigmoid_fast(bf16_lo(gs[k])),
+                                  bf16_hi(xs[k]) * sigmoid_fast(bf16_hi(gs[k])));
               }
               v = make_uint4(xs[0], xs[1], xs[2], xs[3]);
             }
