@@ -220,6 +220,22 @@ int b200_gdn_chunk_output(const void* q, int64_t q_stride_t, int64_t q_stride_h,
                           void* out, int64_t out_stride_t, int64_t out_stride_h, int32_t token_num, int32_t num_heads,
                           int32_t key_dim, int32_t value_dim, b200_stream_t stream);
 
+/* Chunk-64 prefill over a PACKED batch: the three stages above with the chunk grid restarting at every
+ * cu_seqlens[b] and a zero state at each sequence start; out [T,H,128] bf16, state [batch,H,128,128] fp32 (written).
+ * The reference's chunk path is single-sequence (engine/runner.py:263-267, README-EN.md:306-308); this packed form
+ * equals wy_lib::gdn_recurrent_prefill_sequential(..., cu_seqlens) up to fp32 rounding.  `workspace` is
+ * b200_gdn_chunked_prefill_packed_workspace_bytes(batch, total_tokens, num_heads) bytes of caller-owned device
+ * memory, 16-byte aligned (contents undefined afterwards); max_seqlen (host) only sizes the grid. */
+int64_t b200_gdn_chunked_prefill_packed_workspace_bytes(int32_t batch, int32_t total_tokens, int32_t num_heads);
+int b200_gdn_chunked_prefill_packed(const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k,
+                                    int64_t k_stride_t, int64_t k_stride_h, const void* v, int64_t v_stride_t,
+                                    int64_t v_stride_h, const float* beta, int64_t beta_stride_t,
+                                    int64_t beta_stride_h, const float* g, int64_t g_stride_t, int64_t g_stride_h,
+                                    const int32_t* cu_seqlens, int32_t batch, int32_t total_tokens, int32_t max_seqlen,
+                                    void* workspace, float* state, void* out, int64_t out_stride_t,
+                                    int64_t out_stride_h, int32_t num_heads, int32_t key_dim, int32_t value_dim,
+                                    b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

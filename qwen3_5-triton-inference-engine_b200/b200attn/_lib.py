@@ -38,12 +38,15 @@ SIGNATURES: dict[str, list] = {
     "b200_gdn_chunk_prepare_wy": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, P, P, I32, I32, I32, I32, P],
     "b200_gdn_chunk_state": [P, I64, I64, P, P, P, P, P, P, I32, I32, I32, I32, P],
     "b200_gdn_chunk_output": [P, I64, I64, P, I64, I64, P, P, P, P, I64, I64, I32, I32, I32, I32, P],
+    "b200_gdn_chunked_prefill_packed": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I32, I32, I32,
+                                        P, P, P, I64, I64, I32, I32, I32, P],
 }
 OTHER = {
     "b200_last_error": ([], c_char_p),
     "b200_abi_version": ([], c_int),
     "b200_wait_timed_out": ([], c_int),
     "b200_fused_decode_workspace_bytes": ([], c_int64),
+    "b200_gdn_chunked_prefill_packed_workspace_bytes": ([I32, I32, I32], c_int64),
 }
 
 _lib = None

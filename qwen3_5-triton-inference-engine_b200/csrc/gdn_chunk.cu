@@ -18,6 +18,35 @@ constexpr int GC_THREADS = 256;
 constexpr int GC_PITCH = GDN_D + 4;   // fp32 row pitch of [64][128] tiles (16-byte aligned rows, banks shifted by 4)
 constexpr int GC_LP = CHUNK + 1;      // pitch of [64][64] tiles
 
+// Where a CTA's chunk lives.  Single sequence (cu_seqlens == nullptr): chunk = blockIdx.x of `token_num` tokens.
+// Packed batch: blockIdx.z = sequence, blockIdx.x = chunk inside it; chunks of all sequences are numbered
+// consecutively (sequence after sequence), which is also how the intermediates are laid out.
+struct ChunkPos {
+  int chunk;      // global chunk index (row of the intermediates)
+  int t0;         // first token of the chunk in the packed buffer
+  int t_end;      // one past the last token of the sequence
+  bool valid;
+};
+__device__ __forceinline__ ChunkPos locate_chunk(const int32_t* cu_seqlens, int token_num) {
+  ChunkPos c;
+  if (cu_seqlens == nullptr) {
+    c.chunk = blockIdx.x;
+    c.t0 = blockIdx.x * CHUNK;
+    c.t_end = token_num;
+    c.valid = true;
+    return c;
+  }
+  const int b = blockIdx.z;
+  const int start = cu_seqlens[b], len = cu_seqlens[b + 1] - start;
+  int base = 0;
+  for (int i = 0; i < b; ++i) base += (cu_seqlens[i + 1] - cu_seqlens[i] + CHUNK - 1) / CHUNK;
+  c.chunk = base + blockIdx.x;
+  c.t0 = start + blockIdx.x * CHUNK;
+  c.t_end = start + len;
+  c.valid = blockIdx.x * CHUNK < len;
+  return c;
+}
+
 // ---------------------------------------------------------------------------------------------------- prepare_wy
 constexpr int PW_SMEM = (2 * CHUNK * GC_PITCH + 2 * CHUNK * GC_LP + 4 * CHUNK) * 4;
 
@@ -26,8 +55,12 @@ gdn_chunk_prepare_wy_kernel(const __nv_bfloat16* __restrict__ k, int64_t k_t, in
                             const __nv_bfloat16* __restrict__ v, int64_t v_t, int64_t v_h,
                             const float* __restrict__ beta, int64_t be_t, int64_t be_h, const float* __restrict__ g,
                             int64_t g_t, int64_t g_h, float* __restrict__ w, float* __restrict__ u_base,
-                            float* __restrict__ g_cumsum, int token_num, int heads) {
+                            float* __restrict__ g_cumsum, int token_num, int heads,
+                            const int32_t* __restrict__ cu_seqlens) {
   extern __shared__ __align__(16) float sm[];
+  const ChunkPos pos = locate_chunk(cu_seqlens, token_num);
+  if (!pos.valid) return;
+  token_num = pos.t_end;
   float* kf = sm;                            // [64][GC_PITCH]
   float* vf = kf + CHUNK * GC_PITCH;         // [64][GC_PITCH]
   float* lower = vf + CHUNK * GC_PITCH;      // [64][GC_LP]
@@ -35,8 +68,8 @@ gdn_chunk_prepare_wy_kernel(const __nv_bfloat16* __restrict__ k, int64_t k_t, in
   float* gs = inv + CHUNK * GC_LP;           // g, then G
   float* bs = gs + CHUNK;                    // beta
   float* es = bs + CHUNK;                    // exp(G)
-  const int chunk = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-  const int t0 = chunk * CHUNK;
+  const int chunk = pos.chunk, h = blockIdx.y, tid = threadIdx.x;
+  const int t0 = pos.t0;
 
   for (int i = tid; i < CHUNK * GDN_D; i += GC_THREADS) {
     const int r = i / GDN_D, c = i % GDN_D;
@@ -153,8 +186,17 @@ __global__ void __launch_bounds__(GC_THREADS)
 gdn_chunk_state_kernel(const __nv_bfloat16* __restrict__ k, int64_t k_t, int64_t k_h, const float* __restrict__ w,
                        const float* __restrict__ u_base, const float* __restrict__ g_cumsum, float* __restrict__ delta,
                        float* __restrict__ chunk_state, float* __restrict__ final_state, int token_num, int num_chunks,
-                       int heads) {
+                       int heads, const int32_t* __restrict__ cu_seqlens) {
   extern __shared__ __align__(16) float sm[];
+  // packed batch: blockIdx.z = sequence; its chunks are [chunk_base, chunk_base + num_chunks)
+  int chunk_base = 0, tok_base = 0;
+  if (cu_seqlens != nullptr) {
+    const int b = blockIdx.z;
+    for (int i = 0; i < b; ++i) chunk_base += (cu_seqlens[i + 1] - cu_seqlens[i] + CHUNK - 1) / CHUNK;
+    tok_base = cu_seqlens[b];
+    token_num = cu_seqlens[b + 1] - tok_base;
+    num_chunks = (token_num + CHUNK - 1) / CHUNK;
+  }
   float* wf = sm;                           // [64][GC_PITCH]
   float* kf = wf + CHUNK * GC_PITCH;        // [64][GC_PITCH]
   float* st = kf + CHUNK * GC_PITCH;        // [128][16]
@@ -167,7 +209,7 @@ gdn_chunk_state_kernel(const __nv_bfloat16* __restrict__ k, int64_t k_t, int64_t
   for (int i = tid; i < GDN_D * CS_BV; i += GC_THREADS) st[i] = 0.f;
   __syncthreads();
   for (int c = 0; c < num_chunks; ++c) {
-    const int64_t ch = static_cast<int64_t>(c) * heads + h;
+    const int64_t ch = static_cast<int64_t>(chunk_base + c) * heads + h;
     // state entering the chunk
     for (int i = tid; i < GDN_D * CS_BV / 4; i += GC_THREADS) {
       const int kk = i / (CS_BV / 4), q4 = i % (CS_BV / 4);
@@ -182,7 +224,7 @@ gdn_chunk_state_kernel(const __nv_bfloat16* __restrict__ k, int64_t k_t, int64_t
     for (int i = tid; i < CHUNK * GDN_D; i += GC_THREADS) {
       const int r = i / GDN_D, cc = i % GDN_D;
       const int64_t t = static_cast<int64_t>(c) * CHUNK + r;
-      kf[r * GC_PITCH + cc] = t < token_num ? __bfloat162float(k[t * k_t + h * k_h + cc]) : 0.f;
+      kf[r * GC_PITCH + cc] = t < token_num ? __bfloat162float(k[(tok_base + t) * k_t + h * k_h + cc]) : 0.f;
     }
     if (tid < CHUNK) gs[tid] = g_cumsum[ch * CHUNK + tid];
     __syncthreads();
@@ -233,7 +275,8 @@ gdn_chunk_state_kernel(const __nv_bfloat16* __restrict__ k, int64_t k_t, int64_t
   }
   for (int i = tid; i < GDN_D * CS_BV / 4; i += GC_THREADS) {
     const int kk = i / (CS_BV / 4), q4 = i % (CS_BV / 4);
-    *reinterpret_cast<float4*>(final_state + (static_cast<int64_t>(h) * GDN_D + kk) * GDN_D + v0 + q4 * 4) =
+    *reinterpret_cast<float4*>(final_state + ((static_cast<int64_t>(blockIdx.z) * heads + h) * GDN_D + kk) * GDN_D + v0 +
+                               q4 * 4) =
         *reinterpret_cast<const float4*>(st + kk * CS_BV + q4 * 4);
   }
 }
@@ -245,16 +288,20 @@ __global__ void __launch_bounds__(GC_THREADS)
 gdn_chunk_output_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_t, int64_t q_h,
                         const __nv_bfloat16* __restrict__ k, int64_t k_t, int64_t k_h, const float* __restrict__ delta,
                         const float* __restrict__ g_cumsum, const float* __restrict__ chunk_state,
-                        __nv_bfloat16* __restrict__ out, int64_t o_t, int64_t o_h, int token_num, int heads) {
+                        __nv_bfloat16* __restrict__ out, int64_t o_t, int64_t o_h, int token_num, int heads,
+                        const int32_t* __restrict__ cu_seqlens) {
   extern __shared__ __align__(16) float sm[];
+  const ChunkPos pos = locate_chunk(cu_seqlens, token_num);
+  if (!pos.valid) return;
+  token_num = pos.t_end;
   float* qf = sm;                           // [64][GC_PITCH]
   float* kd = qf + CHUNK * GC_PITCH;        // k, later delta [64][GC_PITCH]
   float* att = kd + CHUNK * GC_PITCH;       // [64][GC_LP]
   float* sf = att + CHUNK * GC_LP;          // state_in [128][GC_PITCH]
   float* gs = sf + GDN_D * GC_PITCH;        // G
   float* es = gs + CHUNK;                   // exp(G)
-  const int chunk = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-  const int t0 = chunk * CHUNK;
+  const int chunk = pos.chunk, h = blockIdx.y, tid = threadIdx.x;
+  const int t0 = pos.t0;
   const int64_t ch = static_cast<int64_t>(chunk) * heads + h;
 
   for (int i = tid; i < CHUNK * GDN_D; i += GC_THREADS) {
@@ -380,7 +427,7 @@ extern "C" int b200_gdn_chunk_prepare_wy(const void* k, int64_t k_stride_t, int6
   gdn_chunk_prepare_wy_kernel<<<dim3(chunks, num_heads), GC_THREADS, PW_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(k), k_stride_t, k_stride_h, static_cast<const __nv_bfloat16*>(v), v_stride_t,
       v_stride_h, beta, beta_stride_t, beta_stride_h, g, g_stride_t, g_stride_h, w, u_base, g_cumsum, token_num,
-      num_heads);
+      num_heads, nullptr);
   return check_launch("gdn_chunk_prepare_wy");
 }
 
@@ -397,7 +444,7 @@ extern "C" int b200_gdn_chunk_state(const void* k, int64_t k_stride_t, int64_t k
   const int chunks = (token_num + CHUNK - 1) / CHUNK;
   gdn_chunk_state_kernel<<<dim3(num_heads, GDN_D / CS_BV), GC_THREADS, CS_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(k), k_stride_t, k_stride_h, w, u_base, g_cumsum, delta, chunk_state,
-      final_state, token_num, chunks, num_heads);
+      final_state, token_num, chunks, num_heads, nullptr);
   return check_launch("gdn_chunk_state");
 }
 
@@ -418,6 +465,65 @@ extern "C" int b200_gdn_chunk_output(const void* q, int64_t q_stride_t, int64_t 
   gdn_chunk_output_kernel<<<dim3(chunks, num_heads), GC_THREADS, CO_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(q), q_stride_t, q_stride_h, static_cast<const __nv_bfloat16*>(k), k_stride_t,
       k_stride_h, delta, g_cumsum, chunk_state, static_cast<__nv_bfloat16*>(out), out_stride_t, out_stride_h, token_num,
-      num_heads);
+      num_heads, nullptr);
   return check_launch("gdn_chunk_output");
+}
+
+// Packed chunk-64 prefill: the three stages over a batch of sequences packed in one buffer, chunk grid restarting at
+// every cu_seqlens[b], zero state at each sequence start.  The reference has no such call (its chunk path is
+// single-sequence, engine/runner.py:263-267); it is the packed form BASELINE config 4 asks for.
+// Workspace layout (fp32): w | u_base | delta [Nmax,H,64,128] each, g_cumsum [Nmax,H,64], chunk_state [Nmax,H,128,128]
+// with Nmax = total_tokens / 64 + batch (an upper bound of the number of chunks that needs no device read).
+extern "C" int64_t b200_gdn_chunked_prefill_packed_workspace_bytes(int32_t batch, int32_t total_tokens, int32_t num_heads) {
+  const int64_t n = static_cast<int64_t>(total_tokens) / CHUNK + batch;
+  return n * num_heads * (3LL * CHUNK * GDN_D + CHUNK + static_cast<int64_t>(GDN_D) * GDN_D) * 4;
+}
+
+extern "C" int b200_gdn_chunked_prefill_packed(const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k,
+                                               int64_t k_stride_t, int64_t k_stride_h, const void* v,
+                                               int64_t v_stride_t, int64_t v_stride_h, const float* beta,
+                                               int64_t beta_stride_t, int64_t beta_stride_h, const float* g,
+                                               int64_t g_stride_t, int64_t g_stride_h, const int32_t* cu_seqlens,
+                                               int32_t batch, int32_t total_tokens, int32_t max_seqlen, void* workspace,
+                                               float* state, void* out, int64_t out_stride_t, int64_t out_stride_h,
+                                               int32_t num_heads, int32_t key_dim, int32_t value_dim,
+                                               b200_stream_t stream) {
+  B200_REQUIRE(batch > 0 && batch <= 65535 && total_tokens > 0 && num_heads > 0 && num_heads <= 65535,
+               "gdn_chunked_prefill_packed: bad shape");
+  B200_REQUIRE(key_dim == GDN_D && value_dim == GDN_D,
+               "gdn_chunked_prefill_packed: key/value dim must be %d (got %d/%d)", GDN_D, key_dim, value_dim);
+  B200_REQUIRE(cu_seqlens != nullptr && workspace != nullptr && aligned16(workspace),
+               "gdn_chunked_prefill_packed: cu_seqlens and a 16-byte aligned workspace are required");
+  B200_REQUIRE((reinterpret_cast<uintptr_t>(out) % 8 == 0) && out_stride_t % 4 == 0 && out_stride_h % 4 == 0,
+               "gdn_chunked_prefill_packed: out must be 8-byte aligned with strides that are multiples of 4");
+  if (max_seqlen <= 0) return OK;
+  static bool c1[64] = {false}, c2[64] = {false}, c3[64] = {false};
+  int rc = set_smem(gdn_chunk_prepare_wy_kernel, PW_SMEM, c1, "gdn_chunked_prefill_packed");
+  if (rc == OK) rc = set_smem(gdn_chunk_state_kernel, CS_SMEM, c2, "gdn_chunked_prefill_packed");
+  if (rc == OK) rc = set_smem(gdn_chunk_output_kernel, CO_SMEM, c3, "gdn_chunked_prefill_packed");
+  if (rc != OK) return rc;
+  const int64_t n = static_cast<int64_t>(total_tokens) / CHUNK + batch;
+  float* w = static_cast<float*>(workspace);
+  float* u = w + n * num_heads * CHUNK * GDN_D;
+  float* delta = u + n * num_heads * CHUNK * GDN_D;
+  float* gcs = delta + n * num_heads * CHUNK * GDN_D;
+  float* cstate = gcs + n * num_heads * CHUNK;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int chunks = (max_seqlen + CHUNK - 1) / CHUNK;
+  const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(q);
+  const __nv_bfloat16* kb = static_cast<const __nv_bfloat16*>(k);
+  const __nv_bfloat16* vb = static_cast<const __nv_bfloat16*>(v);
+  gdn_chunk_prepare_wy_kernel<<<dim3(chunks, num_heads, batch), GC_THREADS, PW_SMEM, st>>>(
+      kb, k_stride_t, k_stride_h, vb, v_stride_t, v_stride_h, beta, beta_stride_t, beta_stride_h, g, g_stride_t,
+      g_stride_h, w, u, gcs, total_tokens, num_heads, cu_seqlens);
+  rc = check_launch("gdn_chunked_prefill_packed (prepare_wy)");
+  if (rc != OK) return rc;
+  gdn_chunk_state_kernel<<<dim3(num_heads, GDN_D / CS_BV, batch), GC_THREADS, CS_SMEM, st>>>(
+      kb, k_stride_t, k_stride_h, w, u, gcs, delta, cstate, state, total_tokens, chunks, num_heads, cu_seqlens);
+  rc = check_launch("gdn_chunked_prefill_packed (state)");
+  if (rc != OK) return rc;
+  gdn_chunk_output_kernel<<<dim3(chunks, num_heads, batch), GC_THREADS, CO_SMEM, st>>>(
+      qb, q_stride_t, q_stride_h, kb, k_stride_t, k_stride_h, delta, gcs, cstate, static_cast<__nv_bfloat16*>(out),
+      out_stride_t, out_stride_h, total_tokens, num_heads, cu_seqlens);
+  return check_launch("gdn_chunked_prefill_packed (output)");
 }

@@ -4,6 +4,7 @@ from b200attn.ops import (  # noqa: F401
     gdn_chunk_output,
     gdn_chunk_prepare_wy,
     gdn_chunk_state,
+    gdn_chunked_prefill_packed,
     gdn_recurrent_decode,
     gdn_recurrent_prefill_sequential,
 )

@@ -65,3 +65,25 @@ def test_prepare_wy_vs_oracle(ops):
     rw, ru, rg = O.gdn_chunk_prepare_wy(k, v, beta, g)
     assert maxabs(gcs, rg) < 2e-6 * rg.abs().max().item()
     assert maxabs(w, rw) < 2e-4 and maxabs(u, ru) < 2e-4
+
+
+@pytest.mark.parametrize("lengths", [[128] * 4, [5, 64, 65, 1, 200], [130], [63, 300, 17]])
+def test_chunked_prefill_packed(ops, lengths):
+    """Packed chunk-64 prefill (the form BASELINE config 4 asks for, which the reference cannot run in one call):
+    pinned by (i) the token-serial kernel with cu_seqlens and (ii) the oracle's per-sequence chunk pipeline."""
+    gen = torch.Generator().manual_seed(1200 + sum(lengths))
+    heads, total = 16, sum(lengths)
+    q, k, v, beta, g = gdn_inputs(total, heads, gen, v_row_stride=3 * heads * 128)
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32)
+    storage = torch.zeros(total, 3 * heads * 128, dtype=torch.bfloat16, device=DEV)
+    storage[:, 2 * heads * 128:] = v.to(DEV).reshape(total, -1)
+    vd = storage[:, 2 * heads * 128:].view(total, heads, 128)
+    qd, kd, bd, gd, cud = q.to(DEV), k.to(DEV), beta.to(DEV), g.to(DEV), cu.to(DEV)
+    out_c, state_c = ops.gdn_chunked_prefill_packed(qd, kd, vd, bd, gd, cud, max(lengths))
+    out_s, state_s = ops.gdn_recurrent_prefill_sequential(qd, kd, vd, bd, gd, cud)
+    assert out_c.shape == out_s.shape and state_c.shape == state_s.shape == (len(lengths), heads, 128, 128)
+    assert torch.isfinite(out_c.float()).all() and torch.isfinite(state_c).all()
+    assert maxabs(out_c, out_s) <= 1e-2 and maxabs(state_c, state_s) <= 5e-4
+    if total <= 400:
+        ref_out, ref_state = O.gdn_chunked_prefill_packed(q, k, v, beta, g, cu)
+        assert maxabs(out_c, ref_out) <= 1e-2 and maxabs(state_c, ref_state) <= 5e-4
