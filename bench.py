@@ -323,6 +323,8 @@ def main():
     ap.add_argument("--sweep-steps", type=int, default=20)
     ap.add_argument("--kernel-only", action="store_true", help="headline timing only (for profiler captures)")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of one CUDA graph")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gdn"],
+                    help="with --kernel-only: which kernel family to run (profiler captures of the other families)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -343,6 +345,14 @@ def main():
         dist.init_process_group("nccl", device_id=device)
 
     from b200attn import ops
+
+    if args.kernel_only and args.workload != "decode":
+        rows = run_prefill_sweep(ops, device, args.steps, only=args.workload)
+        if rank == 0:
+            print(json.dumps({"kernel_only": True, "workload": args.workload, "rows": rows}), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
 
     ws = ops.fused_decode_workspace(device)
     peak, peak_kind = hbm_peak()
@@ -510,7 +520,7 @@ def run_sweep(ops, ws, device, peak, steps):
     return rows
 
 
-def run_prefill_sweep(ops, device, steps):
+def run_prefill_sweep(ops, device, steps, only=None):
     """Prefill-side operators at the BASELINE shapes: packed varlen causal attention (config 3: B=32, lengths
     ~U[16,512] seed 2, plus a long-prompt shape where the tensor bound applies) and the GDN prefill forms (config 4:
     32 prompts x 128 tokens).  Reported against both rooflines; inputs are regenerated per call site, not rotated
@@ -525,8 +535,13 @@ def run_prefill_sweep(ops, device, steps):
             pass
     hbm, _ = hbm_peak()
     gen = torch.Generator().manual_seed(2)
-    for tag, lengths in (("cfg3 B=32 L~U[16,512]", torch.randint(16, 513, (32,), generator=gen).tolist()),
-                         ("long B=8 L=4096", [4096] * 8)):
+    attn_shapes = (("cfg3 B=32 L~U[16,512]", torch.randint(16, 513, (32,), generator=gen).tolist()),
+                   ("long B=8 L=4096", [4096] * 8))
+    if only == "prefill":
+        attn_shapes = attn_shapes[1:]
+    elif only == "gdn":
+        attn_shapes = ()
+    for tag, lengths in attn_shapes:
         total = sum(lengths)
         q = torch.randn(total, HQ, D, device=device, dtype=torch.bfloat16)
         k = torch.randn(total, HKV, D, device=device, dtype=torch.bfloat16)
@@ -559,6 +574,8 @@ def run_prefill_sweep(ops, device, steps):
                      "gbs": nbytes_f / (ms * 1e-3) / 1e9, "frac_hbm": nbytes_f / (ms * 1e-3) / 1e9 / hbm})
         del q, k, v, gate, kc, vc, out
         torch.cuda.empty_cache()
+    if only == "prefill":
+        return rows
     # GDN prefill, config 4: 32 prompts x 128 tokens, 16 heads
     heads, lengths = 16, [128] * 32
     total = sum(lengths)
@@ -575,6 +592,9 @@ def run_prefill_sweep(ops, device, steps):
     ms = time_steps(lambda i: _gdn_seq_nosync(ops, gq, gk, gv, beta, g, cu, len(lengths)), steps, 3)
     rows.append({"op": "gdn_recurrent_prefill_sequential", "shape": "cfg4 B=32 x 128", "tokens": total, "us": ms * 1e3,
                  "tflops_fp32": flops / (ms * 1e-3) / 1e12, "gbs": nbytes / (ms * 1e-3) / 1e9})
+    ms = time_steps(lambda i: ops.gdn_chunked_prefill_packed(gq, gk, gv, beta, g, cu, 128), steps, 3)
+    rows.append({"op": "gdn_chunked_prefill_packed (3 launches)", "shape": "cfg4 B=32 x 128", "tokens": total,
+                 "us": ms * 1e3, "tflops_fp32": 12.1e6 * 2 * len(lengths) * heads / (ms * 1e-3) / 1e12})
     one = slice(0, 128)
     ms = time_steps(lambda i: ops.call_gdn_recurrent_prefill_chunked_triton(gq[one], gk[one], gv[one], beta[one], g[one]),
                     steps, 3)
