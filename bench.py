@@ -287,6 +287,10 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     lengths = draw_lengths(args.batch, "random")
+    try:  # torchrun exports OMP_NUM_THREADS=1: the CPU baseline is meant to use every host core it can
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    except Exception:
+        pass
     threads = torch.get_num_threads()
     sample = min(args.batch, args.cpu_sample)
     for _ in range(args.warmup):

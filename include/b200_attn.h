@@ -93,7 +93,8 @@ int b200_paged_decode_combine(const float* m_partial, const float* l_partial, co
  * One launch replaces the chain partial_rope x2 -> paged_kv_append -> split -> combine -> attention_gate_pack of
  * engine/runner.py:482-517 (call_paged_gqa_attention_decode_triton, gqa_attention_decode_paged.py:963-994).
  * q [B,H_q,256], k_new/v_new [B,H_kv,256], gate [B, H_q*256] (row stride gate_stride_b), out [B, H_q*256] bf16
- * contiguous; inv_freq [rotary_dim/2] fp32; rotary_dim is 64 (the model's) or 0 = no rotation.
+ * contiguous; inv_freq [rotary_dim/2] fp32; rotary_dim is 64 (the model's) or 0 = no rotation.  The pools must be
+ * the dense [num_pages, H_kv, 16, 256] layout (pages are fetched by tensor-map TMA, one 8 KiB box per page and head).
  * workspace: b200_fused_decode_workspace_bytes() bytes of device memory, 256-byte aligned, zero-filled ONCE by
  * the caller before the first use (the kernel leaves it zeroed again); calls sharing a workspace must not
  * overlap on the device. */
@@ -102,7 +103,7 @@ int b200_fused_decode_attention(const void* q, int64_t q_stride_b, int64_t q_str
                                 int64_t kn_stride_b, int64_t kn_stride_h, const void* v_new, int64_t vn_stride_b,
                                 int64_t vn_stride_h, const void* gate, int64_t gate_stride_b, void* k_cache,
                                 void* v_cache, int64_t kc_stride_p, int64_t kc_stride_h, int64_t kc_stride_s,
-                                int64_t vc_stride_p, int64_t vc_stride_h, int64_t vc_stride_s,
+                                int64_t vc_stride_p, int64_t vc_stride_h, int64_t vc_stride_s, int64_t num_pages,
                                 const int32_t* block_table, int64_t bt_stride_b, const int64_t* pos,
                                 const float* inv_freq, int32_t rotary_dim, void* out, void* workspace, int32_t batch,
                                 int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, b200_stream_t stream);
@@ -121,8 +122,9 @@ int b200_fused_decode_attention_static(const void* q, int64_t q_stride_b, int64_
                                        int64_t vn_stride_b, int64_t vn_stride_h, const void* gate,
                                        int64_t gate_stride_b, void* k_cache, void* v_cache, int64_t kc_stride_p,
                                        int64_t kc_stride_h, int64_t kc_stride_s, int64_t vc_stride_p,
-                                       int64_t vc_stride_h, int64_t vc_stride_s, const int32_t* block_table,
-                                       int64_t bt_stride_b, const int64_t* pos, const float* inv_freq,
+                                       int64_t vc_stride_h, int64_t vc_stride_s, int64_t num_pages,
+                                       const int32_t* block_table, int64_t bt_stride_b, const int64_t* pos,
+                                       const float* inv_freq,
                                        int32_t rotary_dim, void* out, int32_t batch, int32_t num_q_heads,
                                        int32_t num_kv_heads, int32_t head_dim, b200_stream_t stream);
 

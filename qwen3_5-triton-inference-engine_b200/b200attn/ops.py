@@ -221,7 +221,7 @@ def fused_decode_attention(q, k_new, v_new, gate, k_cache, v_cache, block_table,
     assert block_table.dtype == torch.int32 and block_table.shape[0] == batch and block_table.stride(1) == 1
     assert pos.dtype == torch.int64 and pos.shape == (batch,) and pos.is_contiguous()
     assert inv_freq.dtype == torch.float32 and inv_freq.shape == (rotary_dim // 2,) and inv_freq.is_contiguous()
-    assert k_cache.stride(3) == 1 and v_cache.stride(3) == 1
+    assert k_cache.is_contiguous() and v_cache.is_contiguous(), "the fused kernel reads pages by TMA: dense pools only"
     _require_cuda(q, k_new, v_new, gate, k_cache, v_cache, block_table, pos, inv_freq, workspace)
     q, k_new, v_new, gate = map(_inner_contiguous, (q, k_new, v_new, gate))
     if out is None:
@@ -230,7 +230,7 @@ def fused_decode_attention(q, k_new, v_new, gate, k_cache, v_cache, block_table,
     _lib.call("b200_fused_decode_attention", _ptr(q), q.stride(0), q.stride(1), _ptr(k_new), k_new.stride(0),
               k_new.stride(1), _ptr(v_new), v_new.stride(0), v_new.stride(1), _ptr(gate), gate.stride(0),
               _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), k_cache.stride(1), k_cache.stride(2), v_cache.stride(0),
-              v_cache.stride(1), v_cache.stride(2), _ptr(block_table), block_table.stride(0), _ptr(pos),
+              v_cache.stride(1), v_cache.stride(2), k_cache.shape[0], _ptr(block_table), block_table.stride(0), _ptr(pos),
               _ptr(inv_freq), int(rotary_dim), _ptr(out), _ptr(workspace), batch, num_q_heads, num_kv_heads, head_dim,
               _stream())
     return out

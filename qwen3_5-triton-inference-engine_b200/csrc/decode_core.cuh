@@ -16,9 +16,22 @@
 namespace b200 {
 
 constexpr int ROW_BYTES = HEAD_DIM * 2;                // 512: one token row of K or V
-constexpr int ROW_PITCH = ROW_BYTES + 16;              // 528: padded pitch in shared memory
-constexpr int TILE_BYTES = PAGE * ROW_PITCH;           // 8448: one staged K (or V) tile
+constexpr int ROW_PITCH = ROW_BYTES + 16;              // 528: padded pitch of the row-copy layout
+constexpr int TILE_BYTES = PAGE * ROW_PITCH;           // 8448: one staged K (or V) tile, row-copy layout
+constexpr int TILE_BYTES_SW = PAGE * ROW_BYTES;        // 8192: one staged tile, swizzled tensor-map layout
 constexpr uint32_t TILE_TX_BYTES = PAGE * ROW_BYTES;   // bytes an mbarrier expects per tile
+
+// Two shared-memory layouts of a [16 tokens][256 dims] bf16 tile:
+//   SW = false  rows copied one by one (cp.async.bulk, 512 B each) to a 528-byte pitch; any cache strides.
+//   SW = true   ONE tensor-map TMA box {64 dims, 16 rows, 4 column blocks} with the 128-byte swizzle: the tile is
+//               4 blocks of [16 rows][128 B], 16-byte chunk c of row r stored at position c ^ (r & 7); needs a
+//               dense cache and a 1024-byte aligned tile.  Both are conflict-free for ldmatrix.
+// `chunk` counts 16-byte pieces along the head dim (0..31).
+template <bool SW>
+__device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
+  if (SW) return static_cast<uint32_t>((chunk >> 3) * (PAGE * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+  return static_cast<uint32_t>(row * ROW_PITCH + chunk * 16);
+}
 
 struct DecodeWarpState {
   uint32_t qb[16][2];  // B fragments of Q^T, one pair per 16-wide slice of head_dim
@@ -61,6 +74,7 @@ __device__ __forceinline__ void decode_issue_tile(uint8_t* tile, uint64_t* bar, 
 
 // Scores and softmax statistics of one staged K tile.  `valid` = leading token rows that belong to the
 // sequence (1..16).  Returns the P^T operand fragments (b0, b1) and the rescale factors of the accumulators.
+template <bool SW = false>
 __device__ __forceinline__ void decode_scores(DecodeWarpState& st, const uint8_t* k_tile, int valid, float scale,
                                               int lane, uint32_t& b0, uint32_t& b1, float& alpha0, float& alpha1) {
   const uint32_t kbase = smem_u32(k_tile);
@@ -69,14 +83,14 @@ __device__ __forceinline__ void decode_scores(DecodeWarpState& st, const uint8_t
   float sc[4] = {0.f, 0.f, 0.f, 0.f}, sd[4] = {0.f, 0.f, 0.f, 0.f};
   {
     const int mi = lane >> 3, r = lane & 7;
-    const uint32_t a_addr = kbase + (r + (mi & 1) * 8) * ROW_PITCH + (mi >> 1) * 16;
+    const int arow = r + (mi & 1) * 8, acol = mi >> 1;  // this lane's row and chunk parity inside a 16-dim slice
 #pragma unroll
     for (int ks = 0; ks < 16; ks += 4) {
       uint32_t a0[4], a1[4], a2[4], a3[4];
-      ldmatrix_x4(a0, a_addr + ks * 32);
-      ldmatrix_x4(a1, a_addr + (ks + 1) * 32);
-      ldmatrix_x4(a2, a_addr + (ks + 2) * 32);
-      ldmatrix_x4(a3, a_addr + (ks + 3) * 32);
+      ldmatrix_x4(a0, kbase + tile_offset<SW>(arow, ks * 2 + acol));
+      ldmatrix_x4(a1, kbase + tile_offset<SW>(arow, (ks + 1) * 2 + acol));
+      ldmatrix_x4(a2, kbase + tile_offset<SW>(arow, (ks + 2) * 2 + acol));
+      ldmatrix_x4(a3, kbase + tile_offset<SW>(arow, (ks + 3) * 2 + acol));
       mma_bf16_16816(sa, a0, st.qb[ks][0], st.qb[ks][1]);
       mma_bf16_16816(sb, a1, st.qb[ks + 1][0], st.qb[ks + 1][1]);
       mma_bf16_16816(sc, a2, st.qb[ks + 2][0], st.qb[ks + 2][1]);
@@ -111,6 +125,7 @@ __device__ __forceinline__ void decode_scores(DecodeWarpState& st, const uint8_t
 }
 
 // O^T = alpha * O^T + V^T . P^T for one staged V tile.
+template <bool SW = false>
 __device__ __forceinline__ void decode_accumulate(DecodeWarpState& st, uint8_t* v_tile, int valid, uint32_t b0,
                                                   uint32_t b1, float alpha0, float alpha1, int lane) {
   if (valid < PAGE) {
@@ -118,13 +133,13 @@ __device__ __forceinline__ void decode_accumulate(DecodeWarpState& st, uint8_t* 
     // cannot poison the accumulators (K garbage is removed by the -inf mask on the scores)
     for (int i = lane; i < (PAGE - valid) * (ROW_BYTES / 16); i += 32) {
       const int r = valid + i / (ROW_BYTES / 16), c = i % (ROW_BYTES / 16);
-      *reinterpret_cast<uint4*>(v_tile + r * ROW_PITCH + c * 16) = make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(v_tile + tile_offset<SW>(r, c)) = make_uint4(0, 0, 0, 0);
     }
     __syncwarp();
   }
   const uint32_t vbase = smem_u32(v_tile);
   const int mi = lane >> 3, r = lane & 7;
-  const uint32_t a_addr = vbase + (r + (mi >> 1) * 8) * ROW_PITCH + (mi & 1) * 16;
+  const int vrow = r + (mi >> 1) * 8, vcol = mi & 1;
   // the running max changes rarely after the first pages: skip the 64 multiplies when no lane needs them
   const bool rescale = __any_sync(0xffffffffu, (alpha0 != 1.f) || (alpha1 != 1.f));
   if (rescale) {
@@ -139,7 +154,7 @@ __device__ __forceinline__ void decode_accumulate(DecodeWarpState& st, uint8_t* 
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     uint32_t a[4];
-    ldmatrix_x4_trans(a, a_addr + i * 32);
+    ldmatrix_x4_trans(a, vbase + tile_offset<SW>(vrow, i * 2 + vcol));
     mma_bf16_16816(st.o[i], a, b0, b1);
   }
 }

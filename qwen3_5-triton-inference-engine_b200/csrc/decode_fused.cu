@@ -9,7 +9,8 @@
 // cut into equal ranges, one per CTA; the grid is one CTA per SM whatever the batch or the context lengths,
 // and the cut is recomputed on the device from pos[], so the launch is static and CUDA-graph safe.  Inside a
 // CTA the eight warps take the units of a segment piece round-robin, each with a private ring of three
-// TMA-staged K/V tiles (decode_core.cuh), then merge their online-softmax states through shared memory.
+// K/V tiles, each tile filled by ONE tensor-map TMA copy (8 KiB box, 128-byte swizzle; decode_core.cuh), then merge
+// their online-softmax states through shared memory.
 //   - A segment that lies inside one CTA's range is finished there: normalise, round to bf16, multiply by
 //     sigmoid(gate), store.
 //   - A segment cut by a range boundary leaves one partial (m, l, acc[4][256]) per CTA in the workspace; the
@@ -20,6 +21,7 @@
 // that owns the segment's extra unit and stored to the cache from there; page readers mask that slot.
 #include "b200_attn.h"
 #include "decode_core.cuh"
+#include "umma.cuh"
 
 namespace b200 {
 
@@ -35,13 +37,13 @@ constexpr int FD_PARTIAL_FLOATS = FD_TILE_FLOATS + 8;  // + m[4], l[4]
 constexpr int64_t FD_COUNTER_BYTES = FD_MAX_SEGMENTS * 4;
 constexpr int64_t FD_WORKSPACE_BYTES = FD_COUNTER_BYTES + int64_t(FD_MAX_CTAS) * 2 * FD_PARTIAL_FLOATS * 4;
 
-constexpr int FD_SMEM_RING = FD_WARPS * FD_RING * TILE_BYTES;
+constexpr int FD_SMEM_RING = FD_WARPS * FD_RING * TILE_BYTES_SW;
 constexpr int FD_SMEM_MERGE = FD_MERGE_SLOTS * FD_PARTIAL_FLOATS * 4;
 constexpr int FD_SMEM_CUM = ((FD_MAX_BATCH + 1) * 4 + 15) / 16 * 16;   // exclusive prefix of units
 constexpr int FD_SMEM_POS = FD_MAX_BATCH * 4;                           // pos[] as int32
 constexpr int FD_Q_PITCH = HEAD_DIM + 8;                                // bf16 elements per staged Q row
 constexpr int FD_SMEM_Q = 2 * GROUP * FD_Q_PITCH * 2;                   // rotated Q of this piece and of the next
-constexpr int FD_SMEM_TOTAL = FD_SMEM_RING + FD_SMEM_MERGE + FD_SMEM_CUM + FD_SMEM_POS + FD_SMEM_Q + 128;
+constexpr int FD_SMEM_TOTAL = FD_SMEM_RING + FD_SMEM_MERGE + FD_SMEM_CUM + FD_SMEM_POS + FD_SMEM_Q + 1024;
 
 struct FusedDecodeParams {
   const __nv_bfloat16 *q, *k_new, *v_new, *gate;
@@ -146,14 +148,14 @@ __device__ __forceinline__ void stage_new_k(uint8_t* k_tile, const FusedDecodePa
     }
   }
   const uint4 krot = make_uint4(kw[0], kw[1], kw[2], kw[3]);
-  *reinterpret_cast<uint4*>(k_tile + lane * 16) = krot;
+  *reinterpret_cast<uint4*>(k_tile + tile_offset<true>(0, lane)) = krot;
   const int64_t phys = p.block_table[b * p.bt_b + pos_b / PAGE];
   *reinterpret_cast<uint4*>(p.k_cache + phys * p.kc_p + h * p.kc_h + (pos_b % PAGE) * p.kc_s + lane * 8) = krot;
 }
 __device__ __forceinline__ void stage_new_v(uint8_t* v_tile, const FusedDecodeParams& p, int b, int h, int64_t pos_b,
                                             int lane) {
   const uint4 vraw = *reinterpret_cast<const uint4*>(p.v_new + b * p.vn_b + h * p.vn_h + lane * 8);
-  *reinterpret_cast<uint4*>(v_tile + lane * 16) = vraw;
+  *reinterpret_cast<uint4*>(v_tile + tile_offset<true>(0, lane)) = vraw;
   const int64_t phys = p.block_table[b * p.bt_b + pos_b / PAGE];
   *reinterpret_cast<uint4*>(p.v_cache + phys * p.vc_p + h * p.vc_h + (pos_b % PAGE) * p.vc_s + lane * 8) = vraw;
 }
@@ -186,11 +188,13 @@ __device__ __forceinline__ void merge_state(float& m_run, float& l_run, float (&
   m_run = m_new;
 }
 
-__global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __grid_constant__ FusedDecodeParams p) {
-  extern __shared__ __align__(128) uint8_t smem_raw[];
+__global__ void __launch_bounds__(FD_THREADS, 1)
+fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ uint64_t bars[FD_WARPS][FD_RING];
   __shared__ int s_last;
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* merge = reinterpret_cast<float*>(smem + FD_SMEM_RING);
   int* cum = reinterpret_cast<int*>(smem + FD_SMEM_RING + FD_SMEM_MERGE);
   int* pos_s = reinterpret_cast<int*>(smem + FD_SMEM_RING + FD_SMEM_MERGE + FD_SMEM_CUM);
@@ -198,7 +202,7 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int heads = p.num_kv_heads, batch = p.batch;
-  uint8_t* ring = smem + warp * FD_RING * TILE_BYTES;
+  uint8_t* ring = smem + warp * FD_RING * TILE_BYTES_SW;
   if (lane == 0) {
     for (int s = 0; s < FD_RING; ++s) mbar_init(&bars[warp][s], 1);
     mbar_fence_init();
@@ -266,13 +270,12 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
             }
             cur_phys = __shfl_sync(0xffffffffu, win_phys, ii - win_base);
           }
-          const int64_t phys = cur_phys;
-          if (i_is_v)
-            decode_issue_tile(ring + slot * TILE_BYTES, &bars[warp][slot], p.v_cache + phys * p.vc_p + iseg.h * p.vc_h,
-                              p.vc_s, lane);
-          else
-            decode_issue_tile(ring + slot * TILE_BYTES, &bars[warp][slot], p.k_cache + phys * p.kc_p + iseg.h * p.kc_h,
-                              p.kc_s, lane);
+          // the cache as a matrix of token rows: row = (page * H_kv + head) * 16 + slot; one box = one page of one head
+          if (lane == 0) {
+            const int row0 = (cur_phys * heads + iseg.h) * PAGE;
+            mbar_expect_tx(&bars[warp][slot], TILE_TX_BYTES);
+            tma_load_3d(ring + slot * TILE_BYTES_SW, i_is_v ? &map_v : &map_k, 0, row0, 0, &bars[warp][slot]);
+          }
         }
         ++issued;
         if (i_is_v) {
@@ -350,7 +353,7 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
 #pragma unroll
       for (int part = 0; part < 2; ++part) {
         const int slot = consumed % FD_RING;
-        uint8_t* tile = ring + slot * TILE_BYTES;
+        uint8_t* tile = ring + slot * TILE_BYTES_SW;
         bool ready = !dead;
         if (is_page) {
           if (ready) {
@@ -368,8 +371,8 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
           __syncwarp();
         }
         if (ready) {
-          if (part == 0) decode_scores(st, tile, valid, p.scale, lane, b0, b1, alpha0, alpha1);
-          else decode_accumulate(st, tile, valid, b0, b1, alpha0, alpha1, lane);
+          if (part == 0) decode_scores<true>(st, tile, valid, p.scale, lane, b0, b1, alpha0, alpha1);
+          else decode_accumulate<true>(st, tile, valid, b0, b1, alpha0, alpha1, lane);
         }
         ++consumed;
         fence_proxy_async();  // generic-proxy writes to this slot (row clears, the appended token) before the next bulk copy
@@ -453,6 +456,33 @@ __global__ void __launch_bounds__(FD_THREADS, 1) fused_decode_kernel(const __gri
 
 using namespace b200;
 
+// Tensor maps of the KV pools seen as matrices of token rows [rows][256]; a box is one page of one head
+// ({64 dims, 16 rows, 4 column blocks}).  Encoding costs a few microseconds of host time, so the last few
+// (pointer, rows) pairs are remembered: a model has a fixed set of pools.
+static const CUtensorMap* cache_tile_map(const void* base, int64_t rows) {
+  struct Entry {
+    const void* base;
+    int64_t rows;
+    int dev;
+    CUtensorMap map;
+  };
+  constexpr int N = 32;
+  static Entry entries[N];
+  static int used = 0, next = 0;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  for (int i = 0; i < used; ++i)
+    if (entries[i].base == base && entries[i].rows == rows && entries[i].dev == dev) return &entries[i].map;
+  Entry& e = entries[next];
+  if (!encode_tile_map(&e.map, base, static_cast<uint64_t>(rows), HEAD_DIM, HEAD_DIM * 2, PAGE, HEAD_DIM / 64)) return nullptr;
+  e.base = base;
+  e.rows = rows;
+  e.dev = dev;
+  next = (next + 1) % N;
+  if (used < N) ++used;
+  return &e.map;
+}
+
 extern "C" int64_t b200_fused_decode_workspace_bytes(void) { return FD_WORKSPACE_BYTES; }
 
 extern "C" int b200_fused_decode_attention(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_new,
@@ -460,10 +490,10 @@ extern "C" int b200_fused_decode_attention(const void* q, int64_t q_stride_b, in
                                            int64_t vn_stride_b, int64_t vn_stride_h, const void* gate,
                                            int64_t gate_stride_b, void* k_cache, void* v_cache, int64_t kc_stride_p,
                                            int64_t kc_stride_h, int64_t kc_stride_s, int64_t vc_stride_p,
-                                           int64_t vc_stride_h, int64_t vc_stride_s, const int32_t* block_table,
-                                           int64_t bt_stride_b, const int64_t* pos, const float* inv_freq,
-                                           int32_t rotary_dim, void* out, void* workspace, int32_t batch,
-                                           int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                                           int64_t vc_stride_h, int64_t vc_stride_s, int64_t num_pages,
+                                           const int32_t* block_table, int64_t bt_stride_b, const int64_t* pos,
+                                           const float* inv_freq, int32_t rotary_dim, void* out, void* workspace,
+                                           int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
                                            b200_stream_t stream) {
   B200_REQUIRE(batch > 0 && batch <= FD_MAX_BATCH, "fused_decode_attention: batch must be in [1, %d] (got %d)",
                FD_MAX_BATCH, batch);
@@ -483,6 +513,15 @@ extern "C" int b200_fused_decode_attention(const void* q, int64_t q_stride_b, in
   B200_REQUIRE(strides_ok && aligned16(q) && aligned16(k_new) && aligned16(v_new) && aligned16(gate) &&
                    aligned16(k_cache) && aligned16(v_cache) && aligned16(out),
                "fused_decode_attention: tensors must be 16-byte aligned with strides that are multiples of 8");
+  // the pages are fetched with tensor-map TMA: the pools must be the dense [num_pages, H_kv, 16, 256] layout that
+  // the reference allocates (triton_kernels/gqa_attention_decode_paged.py:100-111)
+  const int64_t dense_h = static_cast<int64_t>(PAGE) * HEAD_DIM, dense_p = dense_h * num_kv_heads;
+  B200_REQUIRE(num_pages > 0 && kc_stride_s == HEAD_DIM && vc_stride_s == HEAD_DIM && kc_stride_h == dense_h &&
+                   vc_stride_h == dense_h && kc_stride_p == dense_p && vc_stride_p == dense_p,
+               "fused_decode_attention: k_cache / v_cache must be contiguous [num_pages, H_kv, 16, 256]");
+  const CUtensorMap* map_k = cache_tile_map(k_cache, num_pages * num_kv_heads * PAGE);
+  const CUtensorMap* map_v = cache_tile_map(v_cache, num_pages * num_kv_heads * PAGE);
+  if (!map_k || !map_v) return fail(ERR_RUNTIME, "fused_decode_attention: cannot encode the cache tensor maps");
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -520,7 +559,7 @@ extern "C" int b200_fused_decode_attention(const void* q, int64_t q_stride_b, in
   p.scale = 1.0f / sqrtf(static_cast<float>(head_dim));
   int grid = sm_count();
   if (grid > FD_MAX_CTAS) grid = FD_MAX_CTAS;
-  fused_decode_kernel<<<grid, FD_THREADS, FD_SMEM_TOTAL, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  fused_decode_kernel<<<grid, FD_THREADS, FD_SMEM_TOTAL, reinterpret_cast<cudaStream_t>(stream)>>>(p, *map_k, *map_v);
   return check_launch("fused_decode_attention");
 }
 
@@ -570,7 +609,7 @@ extern "C" int b200_fused_decode_attention_static(const void* q, int64_t q_strid
                                                   const void* gate, int64_t gate_stride_b, void* k_cache,
                                                   void* v_cache, int64_t kc_stride_p, int64_t kc_stride_h,
                                                   int64_t kc_stride_s, int64_t vc_stride_p, int64_t vc_stride_h,
-                                                  int64_t vc_stride_s, const int32_t* block_table,
+                                                  int64_t vc_stride_s, int64_t num_pages, const int32_t* block_table,
                                                   int64_t bt_stride_b, const int64_t* pos, const float* inv_freq,
                                                   int32_t rotary_dim, void* out, int32_t batch, int32_t num_q_heads,
                                                   int32_t num_kv_heads, int32_t head_dim, b200_stream_t stream) {
@@ -587,7 +626,7 @@ extern "C" int b200_fused_decode_attention_static(const void* q, int64_t q_strid
     return fail(ERR_RUNTIME, "fused_decode_attention_static: cannot clear the arrival counters");
   return b200_fused_decode_attention(q, q_stride_b, q_stride_h, k_new, kn_stride_b, kn_stride_h, v_new, vn_stride_b,
                                      vn_stride_h, gate, gate_stride_b, k_cache, v_cache, kc_stride_p, kc_stride_h,
-                                     kc_stride_s, vc_stride_p, vc_stride_h, vc_stride_s, block_table, bt_stride_b, pos,
-                                     inv_freq, rotary_dim, out, workspace, batch, num_q_heads, num_kv_heads, head_dim,
-                                     stream);
+                                     kc_stride_s, vc_stride_p, vc_stride_h, vc_stride_s, num_pages, block_table,
+                                     bt_stride_b, pos, inv_freq, rotary_dim, out, workspace, batch, num_q_heads,
+                                     num_kv_heads, head_dim, stream);
 }

@@ -23,7 +23,7 @@ def call_static(lib_call, t, kc, vc, inv, out):
     lib_call("b200_fused_decode_attention_static", q.data_ptr(), q.stride(0), q.stride(1), k_new.data_ptr(),
              k_new.stride(0), k_new.stride(1), v_new.data_ptr(), v_new.stride(0), v_new.stride(1), gate.data_ptr(),
              gate.stride(0), kc.data_ptr(), vc.data_ptr(), kc.stride(0), kc.stride(1), kc.stride(2), vc.stride(0),
-             vc.stride(1), vc.stride(2), bt.data_ptr(), bt.stride(0), pos.data_ptr(), inv.data_ptr(), 64,
+             vc.stride(1), vc.stride(2), kc.shape[0], bt.data_ptr(), bt.stride(0), pos.data_ptr(), inv.data_ptr(), 64,
              out.data_ptr(), batch, hq, k_new.shape[1], d, torch.cuda.current_stream().cuda_stream)
 
 
@@ -62,5 +62,5 @@ def test_static_workspace_rejects_oversized_batch():
     z = torch.zeros(1, device=DEV)
     with pytest.raises(_lib.B200Error, match="built-in workspace"):
         _lib.call("b200_fused_decode_attention_static", z.data_ptr(), 2048, 256, z.data_ptr(), 512, 256, z.data_ptr(),
-                  512, 256, z.data_ptr(), 2048, z.data_ptr(), z.data_ptr(), 8192, 4096, 256, 8192, 4096, 256,
+                  512, 256, z.data_ptr(), 2048, z.data_ptr(), z.data_ptr(), 8192, 4096, 256, 8192, 4096, 256, 4,
                   z.data_ptr(), 8, z.data_ptr(), z.data_ptr(), 64, z.data_ptr(), 513, 8, 2, 256, None)
