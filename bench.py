@@ -596,7 +596,15 @@ def run_prefill_sweep(ops, device, steps, only=None):
     ms = time_steps(lambda i: _gdn_seq_nosync(ops, gq, gk, gv, beta, g, cu, len(lengths)), steps, 3)
     rows.append({"op": "gdn_recurrent_prefill_sequential", "shape": "cfg4 B=32 x 128", "tokens": total, "us": ms * 1e3,
                  "tflops_fp32": flops / (ms * 1e-3) / 1e12, "gbs": nbytes / (ms * 1e-3) / 1e9})
-    ms = time_steps(lambda i: ops.gdn_chunked_prefill_packed(gq, gk, gv, beta, g, cu, 128), steps, 3)
+    # chunk-64 on the tensor cores: 12.1 MFLOP per (chunk, head) counting each product once; bytes = q, k, v read,
+    # out written (bf16), beta and g read, final state written
+    ms = time_steps(lambda i: ops.gdn_chunked_prefill_packed(gq, gk, gv, beta, g, cu), steps, 3)
+    cflops = 12.1e6 * 2 * len(lengths) * heads
+    cbytes = total * heads * (4 * 128 * 2 + 8) + len(lengths) * heads * 128 * 128 * 4
+    rows.append({"op": "gdn_chunked_prefill_fused (tcgen05, 1 launch)", "shape": "cfg4 B=32 x 128", "tokens": total,
+                 "us": ms * 1e3, "tflops": cflops / (ms * 1e-3) / 1e12, "frac_tensor": cflops / (ms * 1e-3) / 1e12 / tf_peak,
+                 "gbs": cbytes / (ms * 1e-3) / 1e9, "frac_hbm": cbytes / (ms * 1e-3) / 1e9 / hbm})
+    ms = time_steps(lambda i: ops.gdn_chunked_prefill_packed(gq, gk, gv, beta, g, cu, 128, fused=False), steps, 3)
     rows.append({"op": "gdn_chunked_prefill_packed (3 launches)", "shape": "cfg4 B=32 x 128", "tokens": total,
                  "us": ms * 1e3, "tflops_fp32": 12.1e6 * 2 * len(lengths) * heads / (ms * 1e-3) / 1e12})
     one = slice(0, 128)

@@ -238,6 +238,20 @@ int b200_gdn_chunked_prefill_packed(const void* q, int64_t q_stride_t, int64_t q
                                     int64_t out_stride_h, int32_t num_heads, int32_t key_dim, int32_t value_dim,
                                     b200_stream_t stream);
 
+/* The same packed chunk-64 prefill as ONE kernel on the tcgen05 tensor cores: one CTA per (sequence, head) keeps the
+ * state in tensor memory and walks the chunks; Q/K/V chunks arrive by tensor-map TMA, no workspace, no max_seqlen.
+ * q, k, v must be 16-byte aligned with token and head strides that are multiples of 8 elements.  No reference
+ * counterpart as a single call (it fuses triton_kernels/gdn_recurrent_prefill.py:703-784, :825-909, :935-1006 for a
+ * packed batch); results equal wy_lib::gdn_recurrent_prefill_sequential(..., cu_seqlens) within the reference's
+ * chunked-vs-sequential bars (out 1e-2, state 5e-4, gdn_recurrent_prefill.py:1520-1526). */
+int b200_gdn_chunked_prefill_fused(const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k,
+                                   int64_t k_stride_t, int64_t k_stride_h, const void* v, int64_t v_stride_t,
+                                   int64_t v_stride_h, const float* beta, int64_t beta_stride_t,
+                                   int64_t beta_stride_h, const float* g, int64_t g_stride_t, int64_t g_stride_h,
+                                   const int32_t* cu_seqlens, int32_t batch, int32_t total_tokens, float* state,
+                                   void* out, int64_t out_stride_t, int64_t out_stride_h, int32_t num_heads,
+                                   int32_t key_dim, int32_t value_dim, b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -40,6 +40,8 @@ SIGNATURES: dict[str, list] = {
     "b200_gdn_chunk_output": [P, I64, I64, P, I64, I64, P, P, P, P, I64, I64, I32, I32, I32, I32, P],
     "b200_gdn_chunked_prefill_packed": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I32, I32, I32,
                                         P, P, P, I64, I64, I32, I32, I32, P],
+    "b200_gdn_chunked_prefill_fused": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I32, I32,
+                                       P, P, I64, I64, I32, I32, I32, P],
 }
 OTHER = {
     "b200_last_error": ([], c_char_p),

@@ -556,21 +556,31 @@ def call_gdn_recurrent_prefill_chunked_triton(q, k, v, beta, g):
     return out, final_state
 
 
-def gdn_chunked_prefill_packed(q, k, v, beta, g, cu_seqlens, max_seqlen):
+def gdn_chunked_prefill_packed(q, k, v, beta, g, cu_seqlens, max_seqlen=None, fused=True):
     """Chunk-64 Gated-DeltaNet prefill over a PACKED batch (chunks restart at every cu_seqlens[b], zero state at each
     sequence start).  Returns (out [T,H,DV] bf16, state [B,H,DK,DV] fp32).  The reference's chunk path is
     single-sequence only (engine/runner.py:263-267); this is its packed form, equal to
-    gdn_recurrent_prefill_sequential(..., cu_seqlens) up to fp32 rounding.  `max_seqlen` is a host int (grid size)."""
+    gdn_recurrent_prefill_sequential(..., cu_seqlens) up to fp32 rounding.
+    fused=True: one tcgen05 kernel, state resident in tensor memory, no workspace (q/k/v need token and head strides
+    that are multiples of 8 elements).  fused=False: the three reference-shaped stages through a workspace;
+    `max_seqlen` (host int) sizes their grid."""
     _check_gdn(q, k, v, beta, g)
     assert cu_seqlens.dtype == torch.int32 and cu_seqlens.ndim == 1 and cu_seqlens.is_cuda
     token_num, num_heads, key_dim = q.shape
     value_dim = v.shape[-1]
     batch = cu_seqlens.numel() - 1
     q, k, v = map(_inner_contiguous, (q, k, v))
-    nbytes = _lib.load().b200_gdn_chunked_prefill_packed_workspace_bytes(batch, token_num, num_heads)
-    workspace = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
     state = torch.empty((batch, num_heads, key_dim, value_dim), dtype=torch.float32, device=q.device)
     out = torch.empty((token_num, num_heads, value_dim), dtype=q.dtype, device=q.device)
+    if fused:
+        _lib.call("b200_gdn_chunked_prefill_fused", _ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1),
+                  _ptr(v), v.stride(0), v.stride(1), _ptr(beta), beta.stride(0), beta.stride(1), _ptr(g), g.stride(0),
+                  g.stride(1), _ptr(cu_seqlens.contiguous()), batch, token_num, _ptr(state), _ptr(out), out.stride(0),
+                  out.stride(1), num_heads, key_dim, value_dim, _stream())
+        return out, state
+    assert max_seqlen is not None, "the three-stage path needs max_seqlen"
+    nbytes = _lib.load().b200_gdn_chunked_prefill_packed_workspace_bytes(batch, token_num, num_heads)
+    workspace = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
     _lib.call("b200_gdn_chunked_prefill_packed", _ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1),
               _ptr(v), v.stride(0), v.stride(1), _ptr(beta), beta.stride(0), beta.stride(1), _ptr(g), g.stride(0),
               g.stride(1), _ptr(cu_seqlens.contiguous()), batch, token_num, int(max_seqlen), _ptr(workspace), _ptr(state),

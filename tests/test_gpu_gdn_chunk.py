@@ -67,10 +67,12 @@ def test_prepare_wy_vs_oracle(ops):
     assert maxabs(w, rw) < 2e-4 and maxabs(u, ru) < 2e-4
 
 
+@pytest.mark.parametrize("fused", [True, False], ids=["tcgen05", "three-stage"])
 @pytest.mark.parametrize("lengths", [[128] * 4, [5, 64, 65, 1, 200], [130], [63, 300, 17]])
-def test_chunked_prefill_packed(ops, lengths):
-    """Packed chunk-64 prefill (the form BASELINE config 4 asks for, which the reference cannot run in one call):
-    pinned by (i) the token-serial kernel with cu_seqlens and (ii) the oracle's per-sequence chunk pipeline."""
+def test_chunked_prefill_packed(ops, lengths, fused):
+    """Packed chunk-64 prefill (32 prompts in one call, which the reference cannot run in one call), as the single
+    tcgen05 kernel and as the three reference-shaped stages: pinned by (i) the token-serial kernel with cu_seqlens
+    and (ii) the oracle's per-sequence chunk pipeline."""
     gen = torch.Generator().manual_seed(1200 + sum(lengths))
     heads, total = 16, sum(lengths)
     q, k, v, beta, g = gdn_inputs(total, heads, gen, v_row_stride=3 * heads * 128)
@@ -79,7 +81,7 @@ def test_chunked_prefill_packed(ops, lengths):
     storage[:, 2 * heads * 128:] = v.to(DEV).reshape(total, -1)
     vd = storage[:, 2 * heads * 128:].view(total, heads, 128)
     qd, kd, bd, gd, cud = q.to(DEV), k.to(DEV), beta.to(DEV), g.to(DEV), cu.to(DEV)
-    out_c, state_c = ops.gdn_chunked_prefill_packed(qd, kd, vd, bd, gd, cud, max(lengths))
+    out_c, state_c = ops.gdn_chunked_prefill_packed(qd, kd, vd, bd, gd, cud, max(lengths), fused=fused)
     out_s, state_s = ops.gdn_recurrent_prefill_sequential(qd, kd, vd, bd, gd, cud)
     assert out_c.shape == out_s.shape and state_c.shape == state_s.shape == (len(lengths), heads, 128, 128)
     assert torch.isfinite(out_c.float()).all() and torch.isfinite(state_c).all()
@@ -87,3 +89,21 @@ def test_chunked_prefill_packed(ops, lengths):
     if total <= 400:
         ref_out, ref_state = O.gdn_chunked_prefill_packed(q, k, v, beta, g, cu)
         assert maxabs(out_c, ref_out) <= 1e-2 and maxabs(state_c, ref_state) <= 5e-4
+
+
+@pytest.mark.parametrize("lengths", [[128] * 32, [1000, 513, 64, 2048]])
+def test_fused_chunk_prefill_long(ops, lengths):
+    """The tcgen05 chunk kernel at the batched-prompt size (32 x 128) and over many chunks per sequence (the state is
+    carried in tensor memory for up to 32 chunks) against the token-serial kernel; no bounded wait may run out."""
+    from b200attn import _lib
+    gen = torch.Generator().manual_seed(4242 + len(lengths))
+    heads, total = 16, sum(lengths)
+    q, k, v, beta, g = gdn_inputs(total, heads, gen)
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32)
+    qd, kd, vd, bd, gd, cud = (x.to(DEV) for x in (q, k, v, beta, g, cu))
+    out_c, state_c = ops.gdn_chunked_prefill_packed(qd, kd, vd, bd, gd, cud)
+    out_s, state_s = ops.gdn_recurrent_prefill_sequential(qd, kd, vd, bd, gd, cud)
+    torch.cuda.synchronize()
+    assert _lib.load().b200_wait_timed_out() == 0
+    assert torch.isfinite(out_c.float()).all() and torch.isfinite(state_c).all()
+    assert maxabs(out_c, out_s) <= 1e-2 and maxabs(state_c, state_s) <= 5e-4
