@@ -47,6 +47,16 @@ static_assert(GF_SMEM <= 227 * 1024, "shared memory budget");
 // tensor-memory columns
 constexpr uint32_t TM_D1 = 0, TM_DD = 64, TM_O1 = 128, TM_O2 = 192, TM_S = 256, TM_COLS = 512;
 
+#ifdef B200_GDN_TRACE
+__device__ unsigned long long g_gdn_trace[64];
+#define GDN_TRACE(i)                                                                   \
+  do {                                                                                 \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && (i) < 64) g_gdn_trace[(i)] = global_timer_ns(); \
+  } while (0)
+#else
+#define GDN_TRACE(i)
+#endif
+
 struct GdnFusedParams {
   const float* beta;
   const float* g;
@@ -57,6 +67,62 @@ struct GdnFusedParams {
   int64_t be_t, be_h, g_t, g_h, o_t, o_h;
   int heads;
 };
+
+constexpr int GF_TP = 36;  // fp32 pitch of the merge scratch rows
+
+// One level of the blocked triangular inverse on the 2N x 2N diagonal block at `base`:  P21 = -P22 (L21 P11).
+// merge_a: T = L21 P11, merge_b: P21 = -P22 T; each thread owns one 4x4 tile (N*N/16 tiles).  P11 and P22 are lower
+// triangular, which bounds the k loops; everything is fp32 FMAs.
+template <int N>
+__device__ __forceinline__ void merge_a(const float* Lm, const float* Pm, float* T, int base, int tile) {
+  constexpr int TPR = N / 4;
+  const int r0 = (tile / TPR) * 4, c0 = (tile % TPR) * 4;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  const float* A = Lm + (base + N + r0) * GF_LP + base;
+  const float* B = Pm + base * GF_LP + base + c0;
+#pragma unroll 4
+  for (int k = c0; k < N; ++k) {
+    const float4 bq = *reinterpret_cast<const float4*>(B + k * GF_LP);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float av = A[i * GF_LP + k];
+      acc[i][0] = fmaf(av, bq.x, acc[i][0]);
+      acc[i][1] = fmaf(av, bq.y, acc[i][1]);
+      acc[i][2] = fmaf(av, bq.z, acc[i][2]);
+      acc[i][3] = fmaf(av, bq.w, acc[i][3]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<float4*>(T + (r0 + i) * GF_TP + c0) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+}
+template <int N>
+__device__ __forceinline__ void merge_b(float* Pm, const float* T, int base, int tile) {
+  constexpr int TPR = N / 4;
+  const int r0 = (tile / TPR) * 4, c0 = (tile % TPR) * 4;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  const float* A = Pm + (base + N + r0) * GF_LP + base + N;
+#pragma unroll 4
+  for (int k = 0; k <= r0 + 3; ++k) {
+    const float4 bq = *reinterpret_cast<const float4*>(T + k * GF_TP + c0);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float av = A[i * GF_LP + k];
+      acc[i][0] = fmaf(-av, bq.x, acc[i][0]);
+      acc[i][1] = fmaf(-av, bq.y, acc[i][1]);
+      acc[i][2] = fmaf(-av, bq.z, acc[i][2]);
+      acc[i][3] = fmaf(-av, bq.w, acc[i][3]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    *reinterpret_cast<float4*>(Pm + (base + N + r0 + i) * GF_LP + base + c0) =
+        make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+}
 
 __device__ __forceinline__ void split8(const float (&v)[8], uint4& hi, uint4& lo) {
   uint32_t h[4], l[4];
@@ -117,7 +183,9 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
 
   uint32_t mma_phase = 0;
   bool failed = false;
+  GDN_TRACE(0);
   for (int c = 0; c < num_chunks; ++c) {
+    GDN_TRACE(1 + c * 10);
     const int t0 = tok0 + c * CHUNK;
     const int valid = min(CHUNK, len - c * CHUNK);
     const bool last = c + 1 == num_chunks;
@@ -153,6 +221,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     // ---- Q, K, V of this chunk
     bool ok = mbar_wait_bounded(&bar_load, c & 1);
     if (__syncthreads_or(!ok)) { failed = true; break; }
+    GDN_TRACE(2 + c * 10);
     // ---- D1 = [Q;K] K^T
     if (issuer) {
       tc_fence_after_sync();
@@ -168,6 +237,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     ++mma_phase;
     if (__syncthreads_or(!ok)) { failed = true; break; }
     tc_fence_after_sync();
+    GDN_TRACE(3 + c * 10);
     // ---- D1 -> A (bf16 pair, B operand of the output product) and L (fp32, for the solves)
     {
       const int half = warp >> 2, r = 32 * (warp & 3) + lane;
@@ -209,48 +279,116 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     }
     tc_fence_before_sync();
     __syncthreads();
-    // ---- forward substitution: x_t = rhs_t - sum_{i<t} L[t][i] x_i, one right-hand-side column per thread
-    float x[CHUNK];
-    {
-      const int role = warp >> 2, col = tid & 127;
-      const uint8_t* colbase = smem + (role == 0 ? GF_V : GF_QK + 8192) + (col >> 6) * (role == 0 ? 8192 : 16384) +
-                               (col & 7) * 2;
-      const int ch = (col & 63) >> 3;
-      const float* rs = role == 0 ? s_beta : s_rk;
+    GDN_TRACE(4 + c * 10);
+    // ---- P = (I + L)^-1 in fp32 on the CUDA cores, blocked: the four 16x16 diagonal blocks by forward substitution
+    //      (one thread per column), then two levels of  P21 = -P22 (L21 P11)  with 4x4 register tiles.  P and the
+    //      product scratch live over the delta tiles, which are free until the delta step.
+    float* Pm = reinterpret_cast<float*>(smem + GF_DH);                        // [64][GF_LP]
+    float* Tm = reinterpret_cast<float*>(smem + GF_DH + CHUNK * GF_LP * 4);    // [32][GF_TP]
+    if (tid < 64) {
+      const int blk = tid >> 4, j = tid & 15;
+      const float* lb = Lm + (16 * blk) * GF_LP + 16 * blk;
+      float xx[16];
 #pragma unroll
-      for (int t = 0; t < CHUNK; ++t) {
-        const uint16_t raw = *reinterpret_cast<const uint16_t*>(colbase + t * 128 + ((ch ^ (t & 7)) << 4));
-        float a0 = rs[t] * __uint_as_float(static_cast<uint32_t>(raw) << 16), a1 = 0.f, a2 = 0.f, a3 = 0.f;
-        const float4* lr = reinterpret_cast<const float4*>(Lm + t * GF_LP);
+      for (int r = 0; r < 16; ++r) {
+        float a0 = (r == j) ? 1.f : 0.f, a1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < t; i += 4) {
-          const float4 l = lr[i >> 2];
-          a0 = fmaf(-l.x, x[i], a0);
-          if (i + 1 < t) a1 = fmaf(-l.y, x[i + 1], a1);
-          if (i + 2 < t) a2 = fmaf(-l.z, x[i + 2], a2);
-          if (i + 3 < t) a3 = fmaf(-l.w, x[i + 3], a3);
+        for (int i = 0; i < r; ++i) {
+          if (i & 1) a1 = fmaf(-lb[r * GF_LP + i], xx[i], a1);
+          else a0 = fmaf(-lb[r * GF_LP + i], xx[i], a0);
         }
-        x[t] = (a0 + a1) + (a2 + a3);
-      }
-      if (role == 1) {
-        // w^T row dk = col: 64 token values as a bf16 pair (MN-major B operand of the delta product)
-#pragma unroll
-        for (int cc = 0; cc < 8; ++cc) {
-          float v8[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v8[j] = x[cc * 8 + j];
-          uint4 hi, lo;
-          split8(v8, hi, lo);
-          const uint32_t off = col * 128 + ((cc ^ (col & 7)) << 4);
-          *reinterpret_cast<uint4*>(smem + GF_WH + off) = hi;
-          *reinterpret_cast<uint4*>(smem + GF_WL + off) = lo;
-        }
-        fence_proxy_async();
+        xx[r] = a0 + a1;
+        Pm[(16 * blk + r) * GF_LP + 16 * blk + j] = xx[r];
       }
     }
     __syncthreads();
-    // ---- Dd = S^T w^T (the state is zero before the first chunk)
+    if (tid < 32) merge_a<16>(Lm, Pm, Tm + (tid >> 4) * 16 * GF_TP, 32 * (tid >> 4), tid & 15);
+    __syncthreads();
+    if (tid < 32) merge_b<16>(Pm, Tm + (tid >> 4) * 16 * GF_TP, 32 * (tid >> 4), tid & 15);
+    __syncthreads();
+    if (tid < 64) merge_a<32>(Lm, Pm, Tm, 0, tid);
+    __syncthreads();
+    if (tid < 64) merge_b<32>(Pm, Tm, 0, tid);
+    __syncthreads();
+    GDN_TRACE(5 + c * 10);
+    // ---- B operands of the two right-hand-side products: Pu[t][i] = P[t][i] beta_i, Pw[t][i] = P[t][i] beta_i e^{G_i}
+    //      as bf16 pairs (four [64 t][64 i] tiles over the w tiles, which are written later)
+    {
+      const int t = tid >> 2, i0 = (tid & 3) * 16;
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const float4 p0 = *reinterpret_cast<const float4*>(Pm + t * GF_LP + i0 + cc * 8);
+        const float4 p1 = *reinterpret_cast<const float4*>(Pm + t * GF_LP + i0 + cc * 8 + 4);
+        const float pv[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+        float pu[8], pw[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int i = i0 + cc * 8 + j;
+          const float v1 = (i <= t) ? pv[j] : 0.f;  // blocks above the diagonal were never written
+          pu[j] = v1 * s_beta[i];
+          pw[j] = v1 * s_rk[i];
+        }
+        uint4 hi, lo;
+        const uint32_t off = t * 128 + ((((i0 >> 3) + cc) ^ (t & 7)) << 4);
+        split8(pu, hi, lo);
+        *reinterpret_cast<uint4*>(smem + GF_WH + off) = hi;
+        *reinterpret_cast<uint4*>(smem + GF_WH + 8192 + off) = lo;
+        split8(pw, hi, lo);
+        *reinterpret_cast<uint4*>(smem + GF_WL + off) = hi;
+        *reinterpret_cast<uint4*>(smem + GF_WL + 8192 + off) = lo;
+      }
+      fence_proxy_async();
+    }
+    __syncthreads();
+    // ---- u^T = V^T Pu^T -> Dd,  w^T = K^T Pw^T -> (the O1 columns, free until the output products)
+    if (issuer) {
+      tc_fence_after_sync();
+      const uint32_t idesc = idesc_bf16_f32(128, 64, true, false);
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t a_base = sbase + (which == 0 ? GF_V : GF_QK + 8192);
+        const uint32_t a_lbo = which == 0 ? 8192 : 16384;
+        const uint32_t b_base = sbase + (which == 0 ? GF_WH : GF_WL);
+#pragma unroll
+        for (int grp = 0; grp < 2; ++grp) {
+#pragma unroll
+          for (int kt = 0; kt < 4; ++kt)
+            umma_ss(tmem + (which == 0 ? TM_DD : TM_O1), smem_desc_sw128(a_base + kt * 2048, a_lbo, 1024),
+                    smem_desc_sw128(b_base + grp * 8192 + kt * 32, 16, 1024), idesc, (grp | kt) != 0);
+        }
+      }
+      umma_commit(&bar_mma);
+    }
+    ok = mbar_wait_bounded(&bar_mma, mma_phase & 1);
+    ++mma_phase;
+    if (__syncthreads_or(!ok)) { failed = true; break; }
+    tc_fence_after_sync();
+    // ---- Dd -= S^T w^T: the key threads turn w^T into the MN-major B operand -w^T (bf16 pair); not needed for the
+    //      first chunk, whose state is zero
     if (c > 0) {
+      if (warp >= 4) {
+        const int dk = tid - 128;
+        uint32_t d[32];
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          tmem_ld32(tlane + TM_O1 + hf * 32, d);
+          tmem_ld_wait();
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            float v8[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v8[j] = -__uint_as_float(d[cc * 8 + j]);
+            uint4 hi, lo;
+            split8(v8, hi, lo);
+            const uint32_t off = dk * 128 + (((hf * 4 + cc) ^ (dk & 7)) << 4);
+            *reinterpret_cast<uint4*>(smem + GF_WH + off) = hi;
+            *reinterpret_cast<uint4*>(smem + GF_WL + off) = lo;
+          }
+        }
+        fence_proxy_async();
+      }
+      tc_fence_before_sync();
+      __syncthreads();
       if (issuer) {
         tc_fence_after_sync();
         const uint32_t idesc = idesc_bf16_f32(128, 64, false, true);
@@ -260,7 +398,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             umma_ss(tmem + TM_DD, smem_desc_sw128(sa + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
-                    smem_desc_sw128(wb + ks * 2048, 16384, 1024), idesc, (grp | ks) != 0);
+                    smem_desc_sw128(wb + ks * 2048, 16384, 1024), idesc, true);
           }
         }
         umma_commit(&bar_mma);
@@ -270,36 +408,33 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
       if (__syncthreads_or(!ok)) { failed = true; break; }
       tc_fence_after_sync();
     }
-    // ---- value threads: delta = u - Dd -> delta (pair) and delta' = e^{G_last - G} delta (pair, over the dead w tiles)
-    //      key threads:   decay the state in tensor memory
+    GDN_TRACE(6 + c * 10);
+    // ---- value threads: delta^T (in Dd) -> delta (pair) and delta' = e^{G_last - G} delta (pair, over the dead w
+    //      tiles);  key threads: decay the state in tensor memory
     if (warp < 4) {
       const int dv = tid;
-      if (c > 0) {
-        uint32_t d[32];
+      uint32_t d[32];
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          tmem_ld32(tlane + TM_DD + hf * 32, d);
-          tmem_ld_wait();
+      for (int hf = 0; hf < 2; ++hf) {
+        tmem_ld32(tlane + TM_DD + hf * 32, d);
+        tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) x[hf * 32 + j] -= __uint_as_float(d[j]);
+        for (int cc = 0; cc < 4; ++cc) {
+          float v8[8], s8[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            v8[j] = __uint_as_float(d[cc * 8 + j]);
+            s8[j] = v8[j] * s_dec[hf * 32 + cc * 8 + j];
+          }
+          uint4 hi, lo;
+          const uint32_t off = dv * 128 + (((hf * 4 + cc) ^ (dv & 7)) << 4);
+          split8(v8, hi, lo);
+          *reinterpret_cast<uint4*>(smem + GF_DH + off) = hi;
+          *reinterpret_cast<uint4*>(smem + GF_DL + off) = lo;
+          split8(s8, hi, lo);
+          *reinterpret_cast<uint4*>(smem + GF_WH + off) = hi;
+          *reinterpret_cast<uint4*>(smem + GF_WL + off) = lo;
         }
-      }
-#pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {
-        float v8[8], s8[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          v8[j] = x[cc * 8 + j];
-          s8[j] = v8[j] * s_dec[cc * 8 + j];
-        }
-        uint4 hi, lo;
-        const uint32_t off = dv * 128 + ((cc ^ (dv & 7)) << 4);
-        split8(v8, hi, lo);
-        *reinterpret_cast<uint4*>(smem + GF_DH + off) = hi;
-        *reinterpret_cast<uint4*>(smem + GF_DL + off) = lo;
-        split8(s8, hi, lo);
-        *reinterpret_cast<uint4*>(smem + GF_WH + off) = hi;
-        *reinterpret_cast<uint4*>(smem + GF_WL + off) = lo;
       }
       fence_proxy_async();
     } else if (c > 0) {
@@ -317,6 +452,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     }
     tc_fence_before_sync();
     __syncthreads();
+    GDN_TRACE(7 + c * 10);
     // ---- O1 = S^T q^T, O2 = delta^T A^T, S^T += delta'^T k
     if (issuer) {
       tc_fence_after_sync();
@@ -356,12 +492,14 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     ++mma_phase;
     if (__syncthreads_or(!ok)) { failed = true; break; }
     tc_fence_after_sync();
+    GDN_TRACE(8 + c * 10);
     if (issuer && !last) issue_loads(c + 1);  // every reader of Q, K and V is done
     // ---- value threads: out^T = e^{G_t} O1 + O2;  key threads: export the state (bf16 pair for the next chunk,
     //      fp32 to global memory after the last one)
     if (warp < 4) {
+      // out^T -> [t][dv] bf16 staged in the (now free) delta tile, then whole rows go out as 16-byte stores
       const int dv = tid;
-      __nv_bfloat16* orow = p.out + static_cast<int64_t>(t0) * p.o_t + h * p.o_h + dv;
+      __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(smem + GF_DH);
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         uint32_t o2[32], o1[32];
@@ -373,20 +511,28 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
           const int t = hf * 32 + j;
           float o = __uint_as_float(o2[j]);
           if (c > 0) o = fmaf(s_eG[t], __uint_as_float(o1[j]), o);
-          if (t < valid) orow[static_cast<int64_t>(t) * p.o_t] = __float2bfloat16_rn(o);
+          stage[t * GDN_D + dv] = __float2bfloat16_rn(o);
         }
+      }
+      named_barrier(1, 128);
+      __nv_bfloat16* obase = p.out + static_cast<int64_t>(t0) * p.o_t + h * p.o_h;
+      for (int idx = tid; idx < valid * 16; idx += 128) {
+        const int row = idx >> 4, c16 = idx & 15;
+        *reinterpret_cast<uint4*>(obase + static_cast<int64_t>(row) * p.o_t + c16 * 8) =
+            *reinterpret_cast<const uint4*>(stage + row * GDN_D + c16 * 8);
       }
     } else {
       const int dv = tid - 128;
-      float* srow = p.state + (static_cast<int64_t>(b) * p.heads + h) * GDN_D * GDN_D + dv;
       uint32_t d[32];
 #pragma unroll
       for (int qd = 0; qd < 4; ++qd) {
         tmem_ld32(tlane + TM_S + qd * 32, d);
         tmem_ld_wait();
         if (last) {
+          // final state: fp32 [dk][dv] staged over the (now free) state tiles, stored by one 64 KiB bulk copy
+          float* stage = reinterpret_cast<float*>(smem + GF_SH);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) srow[(qd * 32 + j) * GDN_D] = __uint_as_float(d[j]);
+          for (int j = 0; j < 32; ++j) stage[(qd * 32 + j) * GDN_D + dv] = __uint_as_float(d[j]);
         } else {
 #pragma unroll
           for (int cc = 0; cc < 4; ++cc) {
@@ -402,10 +548,19 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
           }
         }
       }
-      if (!last) fence_proxy_async();
+      fence_proxy_async();
+      if (last) {
+        named_barrier(2, 128);
+        if (tid == 128) {
+          bulk_s2g(p.state + (static_cast<int64_t>(b) * p.heads + h) * GDN_D * GDN_D, smem + GF_SH,
+                   GDN_D * GDN_D * 4);
+          bulk_wait_read();
+        }
+      }
     }
     tc_fence_before_sync();
     __syncthreads();
+    GDN_TRACE(9 + c * 10);
   }
   if (num_chunks == 0 && warp >= 4) {  // empty sequence: zero state
     float* srow = p.state + (static_cast<int64_t>(b) * p.heads + h) * GDN_D * GDN_D + (tid - 128);
@@ -430,6 +585,12 @@ static bool encode_qkv_map(CUtensorMap* map, const void* base, int64_t tokens, i
 
 using namespace b200;
 
+#ifdef B200_GDN_TRACE
+extern "C" int b200_gdn_trace_read(unsigned long long* host64) {
+  return cudaMemcpyFromSymbol(host64, g_gdn_trace, sizeof(unsigned long long) * 64) == cudaSuccess ? 0 : 3;
+}
+#endif
+
 extern "C" int b200_gdn_chunked_prefill_fused(const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k,
                                               int64_t k_stride_t, int64_t k_stride_h, const void* v,
                                               int64_t v_stride_t, int64_t v_stride_h, const float* beta,
@@ -443,6 +604,8 @@ extern "C" int b200_gdn_chunked_prefill_fused(const void* q, int64_t q_stride_t,
   B200_REQUIRE(key_dim == GDN_D && value_dim == GDN_D, "gdn_chunked_prefill_fused: key/value dim must be %d (got %d/%d)",
                GDN_D, key_dim, value_dim);
   B200_REQUIRE(cu_seqlens != nullptr, "gdn_chunked_prefill_fused: cu_seqlens is required");
+  B200_REQUIRE(aligned16(out) && aligned16(state) && out_stride_t % 8 == 0 && out_stride_h % 8 == 0,
+               "gdn_chunked_prefill_fused: out and state must be 16-byte aligned, out strides multiples of 8 elements");
   B200_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && q_stride_t % 8 == 0 && k_stride_t % 8 == 0 &&
                    v_stride_t % 8 == 0 && q_stride_h % 8 == 0 && k_stride_h % 8 == 0 && v_stride_h % 8 == 0,
                "gdn_chunked_prefill_fused: q/k/v must be 16-byte aligned with token and head strides that are "
