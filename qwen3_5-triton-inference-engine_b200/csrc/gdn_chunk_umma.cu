@@ -40,12 +40,12 @@ constexpr int GF_DL = GF_DH + 16384;
 constexpr int GF_AH = GF_DL + 16384;       // A hi [64 t][64 i]
 constexpr int GF_AL = GF_AH + 8192;
 constexpr int GF_L = GF_AL + 8192;         // L fp32 [64][GF_LP]
-constexpr int GF_SC = GF_L + CHUNK * GF_LP * 4;  // per-token scalars, 5 arrays of 64 floats
-constexpr int GF_SMEM = GF_SC + 5 * CHUNK * 4 + 1024;
+constexpr int GF_SC = GF_L + CHUNK * GF_LP * 4;  // per-token scalars, 4 arrays of 64 floats
+constexpr int GF_SMEM = GF_SC + 4 * CHUNK * 4 + 1024;
 static_assert(GF_SMEM <= 227 * 1024, "shared memory budget");
 
 // tensor-memory columns
-constexpr uint32_t TM_D1 = 0, TM_DD = 64, TM_O1 = 128, TM_O2 = 192, TM_S = 256, TM_COLS = 512;
+constexpr uint32_t TM_D1 = 0, TM_DD = 64, TM_O1 = 128, TM_M = 192, TM_O2 = 256, TM_S = 320, TM_COLS = 512;  // O1|M adjacent
 
 #ifdef B200_GDN_TRACE
 __device__ unsigned long long g_gdn_trace[64];
@@ -71,55 +71,62 @@ struct GdnFusedParams {
 constexpr int GF_TP = 36;  // fp32 pitch of the merge scratch rows
 
 // One level of the blocked triangular inverse on the 2N x 2N diagonal block at `base`:  P21 = -P22 (L21 P11).
-// merge_a: T = L21 P11, merge_b: P21 = -P22 T; each thread owns one 4x4 tile (N*N/16 tiles).  P11 and P22 are lower
-// triangular, which bounds the k loops; everything is fp32 FMAs.
-template <int N>
+// merge_a: T = L21 P11, merge_b: P21 = -P22 T; each thread owns one TR x 4 tile (N*N/(4 TR) tiles).  P11 and P22 are
+// lower triangular, which bounds the k range; k runs in unrolled groups of eight so that a group's loads are all in
+// flight before its FMAs.  Everything is fp32.
+template <int N, int TR>
 __device__ __forceinline__ void merge_a(const float* Lm, const float* Pm, float* T, int base, int tile) {
   constexpr int TPR = N / 4;
-  const int r0 = (tile / TPR) * 4, c0 = (tile % TPR) * 4;
-  float acc[4][4];
+  const int r0 = (tile / TPR) * TR, c0 = (tile % TPR) * 4;
+  float acc[TR][4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  for (int i = 0; i < TR; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
   const float* A = Lm + (base + N + r0) * GF_LP + base;
   const float* B = Pm + base * GF_LP + base + c0;
-#pragma unroll 4
-  for (int k = c0; k < N; ++k) {
-    const float4 bq = *reinterpret_cast<const float4*>(B + k * GF_LP);
+  for (int k0 = c0 & ~7; k0 < N; k0 += 8) {  // P11[k][c] = 0 for k < c
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float av = A[i * GF_LP + k];
-      acc[i][0] = fmaf(av, bq.x, acc[i][0]);
-      acc[i][1] = fmaf(av, bq.y, acc[i][1]);
-      acc[i][2] = fmaf(av, bq.z, acc[i][2]);
-      acc[i][3] = fmaf(av, bq.w, acc[i][3]);
+    for (int kk = 0; kk < 8; ++kk) {
+      const int k = k0 + kk;
+      const float4 bq = *reinterpret_cast<const float4*>(B + k * GF_LP);
+#pragma unroll
+      for (int i = 0; i < TR; ++i) {
+        const float av = A[i * GF_LP + k];
+        acc[i][0] = fmaf(av, bq.x, acc[i][0]);
+        acc[i][1] = fmaf(av, bq.y, acc[i][1]);
+        acc[i][2] = fmaf(av, bq.z, acc[i][2]);
+        acc[i][3] = fmaf(av, bq.w, acc[i][3]);
+      }
     }
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < TR; ++i)
     *reinterpret_cast<float4*>(T + (r0 + i) * GF_TP + c0) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
 }
-template <int N>
+template <int N, int TR>
 __device__ __forceinline__ void merge_b(float* Pm, const float* T, int base, int tile) {
   constexpr int TPR = N / 4;
-  const int r0 = (tile / TPR) * 4, c0 = (tile % TPR) * 4;
-  float acc[4][4];
+  const int r0 = (tile / TPR) * TR, c0 = (tile % TPR) * 4;
+  float acc[TR][4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  for (int i = 0; i < TR; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
   const float* A = Pm + (base + N + r0) * GF_LP + base + N;
-#pragma unroll 4
-  for (int k = 0; k <= r0 + 3; ++k) {
-    const float4 bq = *reinterpret_cast<const float4*>(T + k * GF_TP + c0);
+  for (int k0 = 0; k0 <= r0 + TR - 1; k0 += 8) {  // P22[r][k] = 0 for k > r
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float av = A[i * GF_LP + k];
-      acc[i][0] = fmaf(-av, bq.x, acc[i][0]);
-      acc[i][1] = fmaf(-av, bq.y, acc[i][1]);
-      acc[i][2] = fmaf(-av, bq.z, acc[i][2]);
-      acc[i][3] = fmaf(-av, bq.w, acc[i][3]);
+    for (int kk = 0; kk < 8; ++kk) {
+      const int k = k0 + kk;
+      const float4 bq = *reinterpret_cast<const float4*>(T + k * GF_TP + c0);
+#pragma unroll
+      for (int i = 0; i < TR; ++i) {
+        const float av = A[i * GF_LP + k];
+        acc[i][0] = fmaf(-av, bq.x, acc[i][0]);
+        acc[i][1] = fmaf(-av, bq.y, acc[i][1]);
+        acc[i][2] = fmaf(-av, bq.z, acc[i][2]);
+        acc[i][3] = fmaf(-av, bq.w, acc[i][3]);
+      }
     }
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < TR; ++i)
     *reinterpret_cast<float4*>(Pm + (base + N + r0 + i) * GF_LP + base + c0) =
         make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
 }
@@ -141,7 +148,7 @@ __global__ void __launch_bounds__(GF_THREADS, 1)
 gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_constant__ CUtensorMap map_q,
                        const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ uint64_t bar_load, bar_mma;
+  __shared__ uint64_t bar_load, bar_mma, bar_aux;
   __shared__ uint32_t tmem_slot;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* Lm = reinterpret_cast<float*>(smem + GF_L);
@@ -149,7 +156,6 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
   float* s_G = s_beta + CHUNK;                             // G_t
   float* s_eG = s_G + CHUNK;                               // e^{G_t}
   float* s_dec = s_eG + CHUNK;                             // e^{G_last - G_t} (0 for padding)
-  float* s_rk = s_dec + CHUNK;                             // beta_t e^{G_t}
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.x, b = blockIdx.y;
   const int tok0 = p.cu_seqlens[b];
@@ -161,6 +167,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
   if (tid == 0) {
     mbar_init(&bar_load, 1);
     mbar_init(&bar_mma, 1);
+    mbar_init(&bar_aux, 1);
     mbar_fence_init();
   }
   tc_fence_before_sync();
@@ -179,9 +186,22 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     tma_load_4d(smem + GF_QK + 24576, &map_k, 0, t0, 1, h, &bar_load);
     tma_load_4d(smem + GF_V, &map_v, 0, t0, 0, h, &bar_load);
   };
-  if (issuer && num_chunks > 0) issue_loads(0);
+  // g and beta of tokens lane and lane+32 of a chunk (warp 0 only); fetched one chunk ahead
+  float g0 = 0.f, g1 = 0.f, b0 = 0.f, b1 = 0.f;
+  auto fetch_scalars = [&](int c) {
+    const int t0 = tok0 + c * CHUNK, valid = min(CHUNK, len - c * CHUNK);
+    const bool ok0 = lane < valid, ok1 = lane + 32 < valid;
+    g0 = ok0 ? p.g[static_cast<int64_t>(t0 + lane) * p.g_t + h * p.g_h] : 0.f;
+    g1 = ok1 ? p.g[static_cast<int64_t>(t0 + lane + 32) * p.g_t + h * p.g_h] : 0.f;
+    b0 = ok0 ? p.beta[static_cast<int64_t>(t0 + lane) * p.be_t + h * p.be_h] : 0.f;
+    b1 = ok1 ? p.beta[static_cast<int64_t>(t0 + lane + 32) * p.be_t + h * p.be_h] : 0.f;
+  };
+  if (num_chunks > 0) {
+    if (issuer) issue_loads(0);
+    if (warp == 0) fetch_scalars(0);
+  }
 
-  uint32_t mma_phase = 0;
+  uint32_t mma_phase = 0, aux_phase = 0;
   bool failed = false;
   GDN_TRACE(0);
   for (int c = 0; c < num_chunks; ++c) {
@@ -192,10 +212,6 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     // ---- per-token scalars: warp 0 scans g (tokens lane and lane+32)
     if (warp == 0) {
       const bool ok0 = lane < valid, ok1 = lane + 32 < valid;
-      float g0 = ok0 ? p.g[static_cast<int64_t>(t0 + lane) * p.g_t + h * p.g_h] : 0.f;
-      float g1 = ok1 ? p.g[static_cast<int64_t>(t0 + lane + 32) * p.g_t + h * p.g_h] : 0.f;
-      const float b0 = ok0 ? p.beta[static_cast<int64_t>(t0 + lane) * p.be_t + h * p.be_h] : 0.f;
-      const float b1 = ok1 ? p.beta[static_cast<int64_t>(t0 + lane + 32) * p.be_t + h * p.be_h] : 0.f;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const float a = __shfl_up_sync(0xffffffffu, g0, o), bb = __shfl_up_sync(0xffffffffu, g1, o);
@@ -206,17 +222,14 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
       }
       g1 += __shfl_sync(0xffffffffu, g0, 31);
       const float g_last = __shfl_sync(0xffffffffu, g1, 31);
-      const float e0 = expf(g0), e1 = expf(g1);
       s_beta[lane] = b0;
       s_beta[lane + 32] = b1;
       s_G[lane] = g0;
       s_G[lane + 32] = g1;
-      s_eG[lane] = e0;
-      s_eG[lane + 32] = e1;
+      s_eG[lane] = expf(g0);
+      s_eG[lane + 32] = expf(g1);
       s_dec[lane] = ok0 ? expf(g_last - g0) : 0.f;
       s_dec[lane + 32] = ok1 ? expf(g_last - g1) : 0.f;
-      s_rk[lane] = b0 * e0;
-      s_rk[lane + 32] = b1 * e1;
     }
     // ---- Q, K, V of this chunk
     bool ok = mbar_wait_bounded(&bar_load, c & 1);
@@ -238,9 +251,10 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     if (__syncthreads_or(!ok)) { failed = true; break; }
     tc_fence_after_sync();
     GDN_TRACE(3 + c * 10);
-    // ---- D1 -> A (bf16 pair, B operand of the output product) and L (fp32, for the solves)
+    // ---- D1 -> A (bf16 pair, B operand of the output product) and L (fp32, for the inverse)
     {
       const int half = warp >> 2, r = 32 * (warp & 3) + lane;
+      constexpr float LOG2E = 1.4426950408889634f;
       uint32_t d[32];
       tmem_ld32(tlane + TM_D1 + half * 32, d);
       tmem_ld_wait();
@@ -254,7 +268,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const int i = half * 32 + cc * 8 + j;
-            a8[j] = (row_ok && i <= t) ? expf(gt - s_G[i]) * __uint_as_float(d[cc * 8 + j]) : 0.f;
+            a8[j] = (row_ok && i <= t) ? ex2_fast((gt - s_G[i]) * LOG2E) * __uint_as_float(d[cc * 8 + j]) : 0.f;
           }
           uint4 hi, lo;
           split8(a8, hi, lo);
@@ -262,6 +276,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
           *reinterpret_cast<uint4*>(smem + GF_AH + off) = hi;
           *reinterpret_cast<uint4*>(smem + GF_AL + off) = lo;
         }
+        fence_proxy_async();
       } else {
         const int t = r - CHUNK;
         const float gt = s_G[t], bt = s_beta[t];  // beta is 0 on padding rows
@@ -271,7 +286,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const int i = half * 32 + cc * 4 + j;
-            l4[j] = (i < t) ? bt * expf(gt - s_G[i]) * __uint_as_float(d[cc * 4 + j]) : 0.f;
+            l4[j] = (i < t) ? bt * ex2_fast((gt - s_G[i]) * LOG2E) * __uint_as_float(d[cc * 4 + j]) : 0.f;
           }
           *reinterpret_cast<float4*>(Lm + t * GF_LP + half * 32 + cc * 4) = make_float4(l4[0], l4[1], l4[2], l4[3]);
         }
@@ -280,82 +295,142 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     tc_fence_before_sync();
     __syncthreads();
     GDN_TRACE(4 + c * 10);
-    // ---- P = (I + L)^-1 in fp32 on the CUDA cores, blocked: the four 16x16 diagonal blocks by forward substitution
-    //      (one thread per column), then two levels of  P21 = -P22 (L21 P11)  with 4x4 register tiles.  P and the
-    //      product scratch live over the delta tiles, which are free until the delta step.
-    float* Pm = reinterpret_cast<float*>(smem + GF_DH);                        // [64][GF_LP]
-    float* Tm = reinterpret_cast<float*>(smem + GF_DH + CHUNK * GF_LP * 4);    // [32][GF_TP]
-    if (tid < 64) {
-      const int blk = tid >> 4, j = tid & 15;
-      const float* lb = Lm + (16 * blk) * GF_LP + 16 * blk;
-      float xx[16];
+    // ---- warps 0-3: P = (I + L)^-1 in fp32 on the CUDA cores, blocked: the four 16x16 diagonal blocks by forward
+    //      substitution (one thread per column), then two levels of  P21 = -P22 (L21 P11)  with 4x4 register tiles;
+    //      then Pu[t][i] = P[t][i] beta_i as a bf16 pair (B operand of the delta product) over the dead L.
+    //      warps 4-7 meanwhile: R^T[dv][i] = v_i[dv] - e^{G_i} M^T[dv][i] as a bf16 pair (A operand of the delta
+    //      product) over the w tiles, then the decay of the state in tensor memory.
+    if (warp < 4) {
+      float* Pm = reinterpret_cast<float*>(smem + GF_DH);                      // [64][GF_LP] over the delta tiles
+      float* Tm = reinterpret_cast<float*>(smem + GF_DH + CHUNK * GF_LP * 4);  // [32][GF_TP]
+      if (tid < 64) {
+        const int blk = tid >> 4, j = tid & 15;
+        const float* lb = Lm + (16 * blk) * GF_LP + 16 * blk;
+        float xx[16];
 #pragma unroll
-      for (int r = 0; r < 16; ++r) {
-        float a0 = (r == j) ? 1.f : 0.f, a1 = 0.f;
+        for (int r = 0; r < 16; ++r) {
+          float a0 = (r == j) ? 1.f : 0.f, a1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < r; ++i) {
-          if (i & 1) a1 = fmaf(-lb[r * GF_LP + i], xx[i], a1);
-          else a0 = fmaf(-lb[r * GF_LP + i], xx[i], a0);
+          for (int i = 0; i < r; ++i) {
+            if (i & 1) a1 = fmaf(-lb[r * GF_LP + i], xx[i], a1);
+            else a0 = fmaf(-lb[r * GF_LP + i], xx[i], a0);
+          }
+          xx[r] = a0 + a1;
         }
-        xx[r] = a0 + a1;
-        Pm[(16 * blk + r) * GF_LP + 16 * blk + j] = xx[r];
+#pragma unroll
+        for (int r = 0; r < 16; ++r) Pm[(16 * blk + r) * GF_LP + 16 * blk + j] = xx[r];  // after the loop: no aliasing stalls
       }
-    }
-    __syncthreads();
-    if (tid < 32) merge_a<16>(Lm, Pm, Tm + (tid >> 4) * 16 * GF_TP, 32 * (tid >> 4), tid & 15);
-    __syncthreads();
-    if (tid < 32) merge_b<16>(Pm, Tm + (tid >> 4) * 16 * GF_TP, 32 * (tid >> 4), tid & 15);
-    __syncthreads();
-    if (tid < 64) merge_a<32>(Lm, Pm, Tm, 0, tid);
-    __syncthreads();
-    if (tid < 64) merge_b<32>(Pm, Tm, 0, tid);
-    __syncthreads();
-    GDN_TRACE(5 + c * 10);
-    // ---- B operands of the two right-hand-side products: Pu[t][i] = P[t][i] beta_i, Pw[t][i] = P[t][i] beta_i e^{G_i}
-    //      as bf16 pairs (four [64 t][64 i] tiles over the w tiles, which are written later)
-    {
-      const int t = tid >> 2, i0 = (tid & 3) * 16;
+      named_barrier(3, 128);
+      GDN_TRACE(40 + c * 4);
+      if (tid < 64) merge_a<16, 2>(Lm, Pm, Tm + (tid >> 5) * 16 * GF_TP, 32 * (tid >> 5), tid & 31);
+      named_barrier(3, 128);
+      if (tid < 64) merge_b<16, 2>(Pm, Tm + (tid >> 5) * 16 * GF_TP, 32 * (tid >> 5), tid & 31);
+      named_barrier(3, 128);
+      GDN_TRACE(41 + c * 4);
+      merge_a<32, 2>(Lm, Pm, Tm, 0, tid);
+      named_barrier(3, 128);
+      merge_b<32, 2>(Pm, Tm, 0, tid);
+      GDN_TRACE(42 + c * 4);
+      named_barrier(4, 128);
+      GDN_TRACE(5 + c * 10);
+      {
+        const int t = tid >> 1, i0 = (tid & 1) * 32;
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const float4 p0 = *reinterpret_cast<const float4*>(Pm + t * GF_LP + i0 + cc * 8);
-        const float4 p1 = *reinterpret_cast<const float4*>(Pm + t * GF_LP + i0 + cc * 8 + 4);
-        const float pv[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-        float pu[8], pw[8];
+        for (int cc = 0; cc < 4; ++cc) {
+          const float4 p0 = *reinterpret_cast<const float4*>(Pm + t * GF_LP + i0 + cc * 8);
+          const float4 p1 = *reinterpret_cast<const float4*>(Pm + t * GF_LP + i0 + cc * 8 + 4);
+          const float pv[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+          float pu[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int i = i0 + cc * 8 + j;
-          const float v1 = (i <= t) ? pv[j] : 0.f;  // blocks above the diagonal were never written
-          pu[j] = v1 * s_beta[i];
-          pw[j] = v1 * s_rk[i];
+          for (int j = 0; j < 8; ++j) {
+            const int i = i0 + cc * 8 + j;
+            pu[j] = (i <= t) ? pv[j] * s_beta[i] : 0.f;  // blocks above the diagonal were never written
+          }
+          uint4 hi, lo;
+          split8(pu, hi, lo);
+          const uint32_t off = t * 128 + ((((i0 >> 3) + cc) ^ (t & 7)) << 4);
+          *reinterpret_cast<uint4*>(smem + GF_L + off) = hi;
+          *reinterpret_cast<uint4*>(smem + GF_L + 8192 + off) = lo;
         }
-        uint4 hi, lo;
-        const uint32_t off = t * 128 + ((((i0 >> 3) + cc) ^ (t & 7)) << 4);
-        split8(pu, hi, lo);
-        *reinterpret_cast<uint4*>(smem + GF_WH + off) = hi;
-        *reinterpret_cast<uint4*>(smem + GF_WH + 8192 + off) = lo;
-        split8(pw, hi, lo);
-        *reinterpret_cast<uint4*>(smem + GF_WL + off) = hi;
-        *reinterpret_cast<uint4*>(smem + GF_WL + 8192 + off) = lo;
       }
       fence_proxy_async();
+    } else {
+      const int dv = tid - 128;
+      if (c > 0) {
+        // the two products that only need the incoming state, as one N=128 product: [O1 | M^T] = S^T [Q;K]^T
+        if (tid == 128) {
+          tc_fence_after_sync();
+          const uint32_t idesc = idesc_bf16_f32(128, 128, false, false);
+#pragma unroll
+          for (int grp = 0; grp < 2; ++grp) {
+            const uint32_t sa = sbase + (grp == 0 ? GF_SH : GF_SL);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+              const uint32_t o = (ks >> 2) * 16384 + (ks & 3) * 32;
+              umma_ss(tmem + TM_O1, smem_desc_sw128(sa + o, 16, 1024), smem_desc_sw128(sbase + GF_QK + o, 16, 1024),
+                      idesc, (grp | ks) != 0);
+            }
+          }
+          umma_commit(&bar_aux);
+        }
+        ok = mbar_wait_bounded(&bar_aux, aux_phase & 1);
+        tc_fence_after_sync();
+      }
+      const uint8_t* vcol = smem + GF_V + (dv >> 6) * 8192 + (dv & 7) * 2;
+      const int vch = (dv & 63) >> 3;
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        uint32_t d[32];
+        if (c > 0) {
+          tmem_ld32(tlane + TM_M + hf * 32, d);
+          tmem_ld_wait();
+        }
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          float r8[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int i = hf * 32 + cc * 8 + j;
+            const uint16_t raw = *reinterpret_cast<const uint16_t*>(vcol + i * 128 + ((vch ^ (i & 7)) << 4));
+            const float vv = __uint_as_float(static_cast<uint32_t>(raw) << 16);
+            r8[j] = c > 0 ? fmaf(-s_eG[i], __uint_as_float(d[cc * 8 + j]), vv) : vv;
+          }
+          uint4 hi, lo;
+          split8(r8, hi, lo);
+          const uint32_t off = dv * 128 + (((hf * 4 + cc) ^ (dv & 7)) << 4);
+          *reinterpret_cast<uint4*>(smem + GF_WH + off) = hi;
+          *reinterpret_cast<uint4*>(smem + GF_WL + off) = lo;
+        }
+      }
+      fence_proxy_async();
+      if (c > 0) {
+        const float decay = s_eG[CHUNK - 1];
+        uint32_t d[32];
+#pragma unroll
+        for (int qd = 0; qd < 4; ++qd) {
+          tmem_ld32(tlane + TM_S + qd * 32, d);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) d[j] = __float_as_uint(__uint_as_float(d[j]) * decay);
+          tmem_st32(tlane + TM_S + qd * 32, d);
+        }
+        tmem_st_wait();
+      }
     }
-    __syncthreads();
-    // ---- u^T = V^T Pu^T -> Dd,  w^T = K^T Pw^T -> (the O1 columns, free until the output products)
+    if (c > 0) ++aux_phase;
+    tc_fence_before_sync();
+    if (__syncthreads_or(!ok)) { failed = true; break; }
+    // ---- delta^T = R^T Pu^T  (hi*hi + hi*lo + lo*hi)
     if (issuer) {
       tc_fence_after_sync();
-      const uint32_t idesc = idesc_bf16_f32(128, 64, true, false);
+      const uint32_t idesc = idesc_bf16_f32(128, 64, false, false);
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        const uint32_t a_base = sbase + (which == 0 ? GF_V : GF_QK + 8192);
-        const uint32_t a_lbo = which == 0 ? 8192 : 16384;
-        const uint32_t b_base = sbase + (which == 0 ? GF_WH : GF_WL);
+      for (int grp = 0; grp < 3; ++grp) {
+        const uint32_t ra = sbase + (grp == 2 ? GF_WL : GF_WH), pb = sbase + GF_L + (grp == 1 ? 8192 : 0);
 #pragma unroll
-        for (int grp = 0; grp < 2; ++grp) {
-#pragma unroll
-          for (int kt = 0; kt < 4; ++kt)
-            umma_ss(tmem + (which == 0 ? TM_DD : TM_O1), smem_desc_sw128(a_base + kt * 2048, a_lbo, 1024),
-                    smem_desc_sw128(b_base + grp * 8192 + kt * 32, 16, 1024), idesc, (grp | kt) != 0);
-        }
+        for (int ks = 0; ks < 4; ++ks)
+          umma_ss(tmem + TM_DD, smem_desc_sw128(ra + ks * 32, 16, 1024), smem_desc_sw128(pb + ks * 32, 16, 1024), idesc,
+                  (grp | ks) != 0);
       }
       umma_commit(&bar_mma);
     }
@@ -363,112 +438,40 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     ++mma_phase;
     if (__syncthreads_or(!ok)) { failed = true; break; }
     tc_fence_after_sync();
-    // ---- Dd -= S^T w^T: the key threads turn w^T into the MN-major B operand -w^T (bf16 pair); not needed for the
-    //      first chunk, whose state is zero
-    if (c > 0) {
-      if (warp >= 4) {
-        const int dk = tid - 128;
-        uint32_t d[32];
-#pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          tmem_ld32(tlane + TM_O1 + hf * 32, d);
-          tmem_ld_wait();
-#pragma unroll
-          for (int cc = 0; cc < 4; ++cc) {
-            float v8[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v8[j] = -__uint_as_float(d[cc * 8 + j]);
-            uint4 hi, lo;
-            split8(v8, hi, lo);
-            const uint32_t off = dk * 128 + (((hf * 4 + cc) ^ (dk & 7)) << 4);
-            *reinterpret_cast<uint4*>(smem + GF_WH + off) = hi;
-            *reinterpret_cast<uint4*>(smem + GF_WL + off) = lo;
-          }
-        }
-        fence_proxy_async();
-      }
-      tc_fence_before_sync();
-      __syncthreads();
-      if (issuer) {
-        tc_fence_after_sync();
-        const uint32_t idesc = idesc_bf16_f32(128, 64, false, true);
-#pragma unroll
-        for (int grp = 0; grp < 3; ++grp) {
-          const uint32_t sa = sbase + (grp == 2 ? GF_SL : GF_SH), wb = sbase + (grp == 1 ? GF_WL : GF_WH);
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            umma_ss(tmem + TM_DD, smem_desc_sw128(sa + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024),
-                    smem_desc_sw128(wb + ks * 2048, 16384, 1024), idesc, true);
-          }
-        }
-        umma_commit(&bar_mma);
-      }
-      ok = mbar_wait_bounded(&bar_mma, mma_phase & 1);
-      ++mma_phase;
-      if (__syncthreads_or(!ok)) { failed = true; break; }
-      tc_fence_after_sync();
-    }
     GDN_TRACE(6 + c * 10);
-    // ---- value threads: delta^T (in Dd) -> delta (pair) and delta' = e^{G_last - G} delta (pair, over the dead w
-    //      tiles);  key threads: decay the state in tensor memory
-    if (warp < 4) {
-      const int dv = tid;
+    // ---- delta^T -> delta (pair) and delta' = e^{G_last - G} delta (pair, over the dead R tiles); all eight warps,
+    //      32 tokens each
+    {
+      const int dv = tid & 127, hf = warp >> 2;
       uint32_t d[32];
+      tmem_ld32(tlane + TM_DD + hf * 32, d);
+      tmem_ld_wait();
 #pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        tmem_ld32(tlane + TM_DD + hf * 32, d);
-        tmem_ld_wait();
+      for (int cc = 0; cc < 4; ++cc) {
+        float v8[8], s8[8];
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          float v8[8], s8[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            v8[j] = __uint_as_float(d[cc * 8 + j]);
-            s8[j] = v8[j] * s_dec[hf * 32 + cc * 8 + j];
-          }
-          uint4 hi, lo;
-          const uint32_t off = dv * 128 + (((hf * 4 + cc) ^ (dv & 7)) << 4);
-          split8(v8, hi, lo);
-          *reinterpret_cast<uint4*>(smem + GF_DH + off) = hi;
-          *reinterpret_cast<uint4*>(smem + GF_DL + off) = lo;
-          split8(s8, hi, lo);
-          *reinterpret_cast<uint4*>(smem + GF_WH + off) = hi;
-          *reinterpret_cast<uint4*>(smem + GF_WL + off) = lo;
+        for (int j = 0; j < 8; ++j) {
+          v8[j] = __uint_as_float(d[cc * 8 + j]);
+          s8[j] = v8[j] * s_dec[hf * 32 + cc * 8 + j];
         }
+        uint4 hi, lo;
+        const uint32_t off = dv * 128 + (((hf * 4 + cc) ^ (dv & 7)) << 4);
+        split8(v8, hi, lo);
+        *reinterpret_cast<uint4*>(smem + GF_DH + off) = hi;
+        *reinterpret_cast<uint4*>(smem + GF_DL + off) = lo;
+        split8(s8, hi, lo);
+        *reinterpret_cast<uint4*>(smem + GF_WH + off) = hi;
+        *reinterpret_cast<uint4*>(smem + GF_WL + off) = lo;
       }
       fence_proxy_async();
-    } else if (c > 0) {
-      const float decay = s_eG[CHUNK - 1];
-      uint32_t d[32];
-#pragma unroll
-      for (int qd = 0; qd < 4; ++qd) {
-        tmem_ld32(tlane + TM_S + qd * 32, d);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) d[j] = __float_as_uint(__uint_as_float(d[j]) * decay);
-        tmem_st32(tlane + TM_S + qd * 32, d);
-      }
-      tmem_st_wait();
     }
     tc_fence_before_sync();
     __syncthreads();
     GDN_TRACE(7 + c * 10);
-    // ---- O1 = S^T q^T, O2 = delta^T A^T, S^T += delta'^T k
+    // ---- O2 = delta^T A^T, S^T += delta'^T k
     if (issuer) {
       tc_fence_after_sync();
       const uint32_t idesc_kk = idesc_bf16_f32(128, 64, false, false);
-      if (c > 0) {
-#pragma unroll
-        for (int grp = 0; grp < 2; ++grp) {
-          const uint32_t sa = sbase + (grp == 0 ? GF_SH : GF_SL);
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint32_t o = (ks >> 2) * 16384 + (ks & 3) * 32;
-            umma_ss(tmem + TM_O1, smem_desc_sw128(sa + o, 16, 1024), smem_desc_sw128(sbase + GF_QK + o, 16, 1024),
-                    idesc_kk, (grp | ks) != 0);
-          }
-        }
-      }
 #pragma unroll
       for (int grp = 0; grp < 3; ++grp) {
         const uint32_t da = sbase + (grp == 1 ? GF_DL : GF_DH), ab = sbase + (grp == 2 ? GF_AL : GF_AH);
@@ -493,7 +496,10 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     if (__syncthreads_or(!ok)) { failed = true; break; }
     tc_fence_after_sync();
     GDN_TRACE(8 + c * 10);
-    if (issuer && !last) issue_loads(c + 1);  // every reader of Q, K and V is done
+    if (!last) {  // every reader of Q, K and V is done
+      if (issuer) issue_loads(c + 1);
+      if (warp == 0) fetch_scalars(c + 1);
+    }
     // ---- value threads: out^T = e^{G_t} O1 + O2;  key threads: export the state (bf16 pair for the next chunk,
     //      fp32 to global memory after the last one)
     if (warp < 4) {
