@@ -327,6 +327,8 @@ def main():
     ap.add_argument("--sweep-steps", type=int, default=20)
     ap.add_argument("--kernel-only", action="store_true", help="headline timing only (for profiler captures)")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of one CUDA graph")
+    ap.add_argument("--no-model", action="store_true", help="skip the whole-model decode measurement (BASELINE config 5)")
+    ap.add_argument("--model-steps", type=int, default=512)
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gdn"],
                     help="with --kernel-only: which kernel family to run (profiler captures of the other families)")
     args = ap.parse_args()
@@ -464,6 +466,12 @@ def main():
             "peak_kind": f"of {peak_kind}", "kernel": "fused_decode_kernel",
             "algorithmic_bytes_per_launch": w.bytes,
         }
+    if not args.no_model:
+        del w, step, e2e, graph
+        torch.cuda.empty_cache()
+        model = run_whole_model(device, rank, world, dist, args.model_steps, peak)
+        if rank == 0:
+            line["whole_model"] = model
     if world == 1:
         # ---- CPU baseline on a bounded sample (rank 0, N=1 only)
         sample = min(args.batch, args.cpu_sample)
@@ -483,6 +491,70 @@ def main():
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def run_whole_model(device, rank, world, dist, steps, peak, batch=32, prompt_len=128, warm=4):
+    """BASELINE config 5: random-init Qwen3.5-0.8B architecture (seed 4), packed prefill of 32 prompts x 128 random
+    token ids per GPU, then `steps` greedy decode steps replayed from one CUDA graph per step.  Attention and
+    Gated-DeltaNet run on this package's kernels, the rest is PyTorch glue (cuBLAS GEMMs).  Every rank is an independent
+    replica; with more than one rank the sampled ids are all-gathered over NCCL after every step (the only
+    collective).  Reports whole-job tokens/s (max time over ranks) and the fraction of the HBM bound of one step:
+    all weights once + Gated-DeltaNet states in and out + the KV cache of the mean context."""
+    from b200attn import engine as E
+    cfg = E.ModelConfig()
+    weights = E.random_weights(cfg, seed=4, device=device)
+    gen = torch.Generator().manual_seed(4 + rank)
+    prompts = [torch.randint(0, cfg.vocab, (prompt_len,), generator=gen).tolist() for _ in range(batch)]
+    eng = E.Engine(cfg, weights, batch, prompt_len + steps + warm + 2, device, page_seed=rank)
+
+    def sync():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    eng.prefill(prompts)                       # first call: library handles, tensor maps, allocator pools
+    eng.pos.zero_()
+    sync()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    eng.prefill(prompts)
+    end.record()
+    sync()
+    prefill_ms = start.elapsed_time(end)
+    for _ in range(warm):
+        eng.step()
+    eng.capture()
+    gathered = torch.empty(world * batch, dtype=torch.int64, device=device) if dist is not None else None
+    sync()
+    start.record()
+    for _ in range(steps):
+        tok = eng.step()
+        if dist is not None:
+            dist.all_gather_into_tensor(gathered, tok)
+    end.record()
+    sync()
+    ms = start.elapsed_time(end)
+    if dist is not None:
+        t = torch.tensor([ms, prefill_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, prefill_ms = float(t[0]), float(t[1])
+    param_bytes = sum(t.numel() * t.element_size() for t in [weights["embed"], weights["norm"]])
+    for layer in weights["layers"]:
+        param_bytes += sum(t.numel() * t.element_size() for k, t in layer.items()
+                           if isinstance(t, torch.Tensor) and k != "conv")
+    n_gdn = sum(1 for l in weights["layers"] if l["kind"] == "gdn")
+    n_att = cfg.num_layers - n_gdn
+    mean_ctx = prompt_len + warm + steps / 2
+    step_bytes = param_bytes + n_gdn * batch * gdn_decode_bytes(1) + n_att * batch * 2048 * mean_ctx
+    ms_step = ms / steps
+    return {"metric": "whole-model greedy decode tokens/s (random-init Qwen3.5-0.8B architecture, bf16)",
+            "value": world * batch * steps / (ms * 1e-3), "unit": "tok/s", "ms_per_step": ms_step,
+            "batch_per_gpu": batch, "prompt_len": prompt_len, "decode_steps": steps, "n_gpus": world,
+            "prefill_ms": prefill_ms, "prefill_tok_s": world * batch * prompt_len / (prefill_ms * 1e-3),
+            "hbm_bytes_per_step_per_gpu": step_bytes, "hbm_frac": step_bytes / (ms_step * 1e-3) / 1e9 / peak,
+            "launch": "one CUDA graph per decode step; ids all-gathered over NCCL per step" if dist is not None
+                      else "one CUDA graph per decode step"}
 
 
 def run_sweep(ops, ws, device, peak, steps):

@@ -1,0 +1,215 @@
+"""Whole-model stepping around the CUDA operators of this package: a compact mirror of the reference runner's packed
+prefill and batched decode (engine/runner.py:212-571) for the Qwen3.5-0.8B architecture - 24 layers, three
+Gated-DeltaNet layers then one full-attention layer, SwiGLU MLP, tied embedding / LM head.
+
+The attention and Gated-DeltaNet work runs on the fused operators (`fused_prefill_attention`,
+`gdn_chunked_prefill_packed`, `fused_decode_attention`, `gdn_recurrent_decode`); everything else (projections, norms,
+conv, gates, MLP, argmax) is the PyTorch glue of `glue.py`.  State per replica: paged KV pools and one block table
+(engine/cache.py:51-217), conv and recurrent states per Gated-DeltaNet layer, a device-resident `pos`.  Decode can be
+captured into one CUDA graph: every per-step quantity (token ids, positions) lives in device memory.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import glue, ops
+
+
+@dataclass(frozen=True)
+class ModelConfig:
+    hidden: int = 1024
+    num_layers: int = 24
+    full_attention_interval: int = 4      # layers 3, 7, 11, ... are full attention
+    num_q_heads: int = 8
+    num_kv_heads: int = 2
+    head_dim: int = 256
+    rotary_dim: int = 64
+    rope_theta: float = 1e7
+    gdn_heads: int = 16
+    gdn_dim: int = 128
+    intermediate: int = 3584
+    vocab: int = 248320
+    eps: float = 1e-6
+
+    def is_attention(self, layer: int) -> bool:
+        return (layer + 1) % self.full_attention_interval == 0
+
+    @property
+    def gdn_width(self) -> int:
+        return self.gdn_heads * self.gdn_dim
+
+
+def random_weights(cfg: ModelConfig, seed: int, device, std: float = 0.02) -> dict:
+    """Random-init weights of the architecture (N(0, std), bf16; A_log ~ U(0, 2.7) and the gated-norm weight in fp32,
+    as engine/loader.py:82-153 types them).  Projections that share an input are stored fused, as the reference's
+    decode path uses them (loader.py `_fuse_rows`)."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+
+    def rnd(*shape, dtype=torch.bfloat16):
+        return (torch.randn(*shape, generator=gen, device=device, dtype=torch.float32) * std).to(dtype)
+
+    kd = cfg.gdn_width
+    qd, kvd = cfg.num_q_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
+    layers = []
+    for i in range(cfg.num_layers):
+        layer = {"ln1": rnd(cfg.hidden), "ln2": rnd(cfg.hidden),
+                 "gate_up": rnd(2 * cfg.intermediate, cfg.hidden), "down": rnd(cfg.hidden, cfg.intermediate)}
+        if cfg.is_attention(i):
+            layer.update(kind="attention", qkvg=rnd(2 * qd + 2 * kvd, cfg.hidden), q_norm=rnd(cfg.head_dim),
+                         k_norm=rnd(cfg.head_dim), o_proj=rnd(cfg.hidden, qd))
+        else:
+            conv = rnd(3 * kd, 4)
+            layer.update(kind="gdn", in_proj=rnd(4 * kd + 2 * cfg.gdn_heads, cfg.hidden), conv=conv,
+                         conv4=conv.t().contiguous(),
+                         a_log=torch.rand(cfg.gdn_heads, generator=gen, device=device) * 2.7,
+                         dt_bias=rnd(cfg.gdn_heads), norm=1.0 + rnd(cfg.gdn_dim, dtype=torch.float32),
+                         out_proj=rnd(cfg.hidden, kd))
+        layers.append(layer)
+    return {"embed": rnd(cfg.vocab, cfg.hidden), "norm": rnd(cfg.hidden), "layers": layers}
+
+
+class Engine:
+    """One replica: weights, caches and the two entry points `prefill` and `step`."""
+
+    def __init__(self, cfg: ModelConfig, weights: dict, batch: int, max_context: int, device, page_seed: int = 0):
+        self.cfg, self.w, self.batch, self.device = cfg, weights, batch, torch.device(device)
+        pages_per_seq = (max_context + ops.PAGE_SIZE - 1) // ops.PAGE_SIZE
+        num_pages = batch * pages_per_seq
+        perm = torch.randperm(num_pages, generator=torch.Generator().manual_seed(page_seed))
+        self.block_table = perm.view(batch, pages_per_seq).to(torch.int32).to(self.device)
+        self.max_context = pages_per_seq * ops.PAGE_SIZE
+        self.pos = torch.zeros(batch, dtype=torch.int64, device=self.device)
+        self.kv, self.conv_state, self.rec_state = {}, {}, {}
+        for i in range(cfg.num_layers):
+            if cfg.is_attention(i):
+                self.kv[i] = ops.allocate_paged_kv_cache(num_pages, cfg.num_kv_heads, cfg.head_dim, device=self.device)
+            else:
+                self.conv_state[i] = torch.zeros(batch, 4, 3 * cfg.gdn_width, dtype=torch.bfloat16, device=self.device)
+                self.rec_state[i] = torch.zeros(batch, cfg.gdn_heads, cfg.gdn_dim, cfg.gdn_dim, dtype=torch.float32,
+                                                device=self.device)
+        self.workspace = ops.fused_decode_workspace(self.device)
+        r = cfg.rotary_dim
+        self.inv_freq = (1.0 / (cfg.rope_theta ** (torch.arange(0, r, 2, dtype=torch.float32) / r))).to(self.device)
+        self.tok = torch.zeros(batch, dtype=torch.int64, device=self.device)   # input of the next step
+        self.graph = None
+
+    # ------------------------------------------------------------------------------------------------ shared pieces
+    def _mlp(self, x, layer):
+        cfg = self.cfg
+        h = glue.qwen_rmsnorm(x, layer["ln2"], cfg.eps)
+        gate_up = glue.gemm_2d(h, layer["gate_up"])
+        h = glue.swiglu(gate_up[:, : cfg.intermediate], gate_up[:, cfg.intermediate:])
+        return glue.residual_add(glue.gemm_2d(h, layer["down"]), x)
+
+    def _split_gdn(self, fused):
+        kd, heads = self.cfg.gdn_width, self.cfg.gdn_heads
+        return (fused[:, : 3 * kd], fused[:, 3 * kd: 4 * kd], fused[:, 4 * kd: 4 * kd + heads],
+                fused[:, 4 * kd + heads:])
+
+    def _split_attention(self, fused):
+        cfg = self.cfg
+        qd, kvd = cfg.num_q_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
+        n = fused.shape[0]
+        q = glue.qwen_rmsnorm(fused[:, :qd].view(n, cfg.num_q_heads, cfg.head_dim), self._cur["q_norm"], cfg.eps)
+        k = glue.qwen_rmsnorm(fused[:, 2 * qd: 2 * qd + kvd].view(n, cfg.num_kv_heads, cfg.head_dim),
+                              self._cur["k_norm"], cfg.eps)
+        v = fused[:, 2 * qd + kvd:].view(n, cfg.num_kv_heads, cfg.head_dim)
+        return q, k, v, fused[:, qd: 2 * qd]
+
+    def _head(self, x):
+        return glue.lm_head_argmax(glue.qwen_rmsnorm(x, self.w["norm"], self.cfg.eps), self.w["embed"])
+
+    # ------------------------------------------------------------------------------------------------------ prefill
+    @torch.no_grad()
+    def prefill(self, prompts: list[list[int]]) -> torch.Tensor:
+        """Packed varlen prefill of `batch` prompts (engine/runner.py:212-405 with a PackedBatch); fills every cache,
+        sets pos, returns the first generated token of each sequence (int64 [B]) and leaves it in `self.tok`."""
+        cfg = self.cfg
+        assert len(prompts) == self.batch and all(0 < len(p) <= self.max_context for p in prompts)
+        lengths = [len(p) for p in prompts]
+        ids = torch.tensor([t for p in prompts for t in p], dtype=torch.int64).to(self.device)
+        cu, max_len = ops.build_cu_seqlens(lengths, device=self.device)
+        pos_in_seq = torch.cat([torch.arange(n) for n in lengths]).to(torch.int32).to(self.device)
+        total, heads, dim = ids.numel(), cfg.gdn_heads, cfg.gdn_dim
+        x = glue.embedding_gather(ids, self.w["embed"])
+        for i, layer in enumerate(self.w["layers"]):
+            self._cur = layer
+            h = glue.qwen_rmsnorm(x, layer["ln1"], cfg.eps)
+            if layer["kind"] == "gdn":
+                qkv, z, a, b = self._split_gdn(glue.gemm_2d(h, layer["in_proj"]))
+                conv = glue.depthwise_causal_conv4_prefill(qkv, layer["conv"], pos_in_seq)
+                kd = cfg.gdn_width
+                q = conv[:, :kd].view(total, heads, dim)
+                k = conv[:, kd: 2 * kd].view(total, heads, dim)
+                v = conv[:, 2 * kd:].view(total, heads, dim)
+                q_n, k_n, beta, g = glue.gdn_qk_norm_gates(q, k, a, b, layer["a_log"], layer["dt_bias"])
+                core, state = ops.gdn_chunked_prefill_packed(q_n, k_n, v, beta, g, cu)
+                self.rec_state[i].copy_(state)
+                glue.conv_state_from_packed_prefill(self.conv_state[i], qkv, cu)
+                normed = glue.gdn_gated_rmsnorm(core, z.reshape(total, heads, dim), layer["norm"])
+                mixed = glue.gemm_2d(normed.view(total, kd), layer["out_proj"])
+            else:
+                q, k, v, gate = self._split_attention(glue.gemm_2d(h, layer["qkvg"]))
+                k_cache, v_cache = self.kv[i]
+                ctx = ops.fused_prefill_attention(q, k, v, gate, k_cache, v_cache, self.block_table, cu, pos_in_seq,
+                                                  self.inv_freq, cfg.rotary_dim, max_len)
+                mixed = glue.gemm_2d(ctx, layer["o_proj"])
+            x = self._mlp(glue.residual_add(mixed, x), layer)
+        last = x.index_select(0, cu[1:].long() - 1)
+        self.pos.copy_(torch.tensor(lengths, dtype=torch.int64))
+        self.tok.copy_(self._head(last))
+        return self.tok.clone()
+
+    # ------------------------------------------------------------------------------------------------------- decode
+    @torch.no_grad()
+    def _decode(self, tok: torch.Tensor) -> torch.Tensor:
+        """One token per sequence (engine/runner.py:408-571): returns the next token ids and advances pos on the
+        device.  No host value changes from step to step, so the whole call can sit in a CUDA graph."""
+        cfg = self.cfg
+        batch, heads, dim, kd = self.batch, cfg.gdn_heads, cfg.gdn_dim, cfg.gdn_width
+        x = glue.embedding_gather(tok, self.w["embed"])
+        for i, layer in enumerate(self.w["layers"]):
+            self._cur = layer
+            h = glue.qwen_rmsnorm(x, layer["ln1"], cfg.eps)
+            if layer["kind"] == "gdn":
+                qkv, z, a, b = self._split_gdn(glue.gemm_2d(h, layer["in_proj"]))
+                conv = glue.depthwise_causal_conv4_decode(qkv, self.conv_state[i], layer["conv4"])
+                q = conv[:, :kd].view(batch, heads, dim)
+                k = conv[:, kd: 2 * kd].view(batch, heads, dim)
+                v = conv[:, 2 * kd:].view(batch, heads, dim)
+                q_n, k_n, beta, g = glue.gdn_qk_norm_gates(q, k, a, b, layer["a_log"], layer["dt_bias"])
+                core = ops.gdn_recurrent_decode(q_n, k_n, v, beta, g, self.rec_state[i])
+                normed = glue.gdn_gated_rmsnorm(core, z.reshape(batch, heads, dim), layer["norm"])
+                mixed = glue.gemm_2d(normed.view(batch, kd), layer["out_proj"])
+            else:
+                q, k, v, gate = self._split_attention(glue.gemm_2d(h, layer["qkvg"]))
+                k_cache, v_cache = self.kv[i]
+                ctx = ops.fused_decode_attention(q, k, v, gate, k_cache, v_cache, self.block_table, self.pos,
+                                                 self.inv_freq, cfg.rotary_dim, self.workspace)
+                mixed = glue.gemm_2d(ctx, layer["o_proj"])
+            x = self._mlp(glue.residual_add(mixed, x), layer)
+        nxt = self._head(x)
+        self.pos.add_(1)
+        return nxt
+
+    def capture(self) -> None:
+        """Capture one decode step (read self.tok, write the next ids back into self.tok) into a CUDA graph."""
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                self.tok.copy_(self._decode(self.tok))
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        self.graph = graph
+
+    def step(self) -> torch.Tensor:
+        """Advance every sequence by one token; returns the device tensor holding the new ids (valid until the next
+        step)."""
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.tok.copy_(self._decode(self.tok))
+        return self.tok
