@@ -252,6 +252,36 @@ int b200_gdn_chunked_prefill_fused(const void* q, int64_t q_stride_t, int64_t q_
                                    void* out, int64_t out_stride_t, int64_t out_stride_h, int32_t num_heads,
                                    int32_t key_dim, int32_t value_dim, b200_stream_t stream);
 
+/* ------------------------------------------------------------------------------------------------------------------
+ * Row-wise layer operators around the projections (one launch each).  bf16 tensors, fp32 math, one rounding at the
+ * reference's rounding points.
+ *
+ * b200_add_rmsnorm: norm_out[r,:] = s * rsqrt(mean(s^2) + eps) * (1 + weight), s = x[r,:] (+ residual[r,:], rounded
+ * to bf16 first and also written to sum_out when that is non-NULL).  Row r of x lives at
+ * x + (r / inner_count) * x_stride_outer + (r % inner_count) * x_stride_inner (so a [n, H, D] column view of a fused
+ * projection works); residual rows are residual_stride apart; sum_out and norm_out are contiguous [rows, dim].
+ * dim must be a multiple of 256, at most 2048.  Replaces triton_kernels/qwen_rmsnorm.py:98-146 (and
+ * triton_kernels/residual_add.py in front of it).
+ * b200_swiglu: out[r, c] = silu(gate_up[r, c]) * gate_up[r, intermediate + c].  Replaces triton_kernels/swiglu.py.
+ * b200_gdn_decode_prep: one decode token per sequence of a Gated-DeltaNet layer: shifts conv_state [B,4,3*H*128]
+ * left and appends qkv (triton_kernels/depthwise_causal_conv4_decode.py), y = silu(sum_r weight4[r,c] state[r,c])
+ * rounded to bf16, then q_out = l2norm(y_q) * 128^-0.5, k_out = l2norm(y_k), v_out = y_v as contiguous [B,H,128] and
+ * beta = sigmoid(b), g = -exp(a_log) * softplus(a + dt_bias) as fp32 [B,H] (triton_kernels/gdn_qk_norm_gates.py:68-89).
+ * b200_gdn_gated_rmsnorm: out[r,:] = x[r,:] * rsqrt(mean(x^2) + 1e-6) * weight * silu(z[r,:]) for rows r = (n, head);
+ * x and out contiguous [rows, 128], z row (n, head) at z + n * z_stride + head * 128
+ * (triton_kernels/gdn_gated_rmsnorm.py:95-140). */
+int b200_add_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x_stride_inner, int32_t inner_count,
+                     const void* residual, int64_t residual_stride, const void* weight, void* sum_out, void* norm_out,
+                     int32_t rows, int32_t dim, float eps, b200_stream_t stream);
+int b200_swiglu(const void* gate_up, int64_t row_stride, void* out, int32_t rows, int32_t intermediate,
+                b200_stream_t stream);
+int b200_gdn_decode_prep(const void* qkv, int64_t qkv_stride, void* conv_state, const void* weight4, const void* a,
+                         int64_t a_stride, const void* b, int64_t b_stride, const float* a_log, const void* dt_bias,
+                         void* q_out, void* k_out, void* v_out, float* beta, float* g, int32_t batch, int32_t num_heads,
+                         int32_t head_dim, b200_stream_t stream);
+int b200_gdn_gated_rmsnorm(const void* x, const void* z, int64_t z_stride, const float* weight, void* out, int32_t rows,
+                           int32_t num_heads, int32_t head_dim, b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

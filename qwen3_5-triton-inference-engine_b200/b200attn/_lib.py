@@ -5,7 +5,7 @@ There is no fallback: if the shared library is missing or a call returns non-zer
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_int, c_int32, c_int64, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
 from pathlib import Path
 
 PKG_DIR = Path(__file__).resolve().parent.parent
@@ -40,6 +40,10 @@ SIGNATURES: dict[str, list] = {
     "b200_gdn_chunk_output": [P, I64, I64, P, I64, I64, P, P, P, P, I64, I64, I32, I32, I32, I32, P],
     "b200_gdn_chunked_prefill_packed": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I32, I32, I32,
                                         P, P, P, I64, I64, I32, I32, I32, P],
+    "b200_add_rmsnorm": [P, I64, I64, I32, P, I64, P, P, P, I32, I32, c_float, P],
+    "b200_swiglu": [P, I64, P, I32, I32, P],
+    "b200_gdn_decode_prep": [P, I64, P, P, P, I64, P, I64, P, P, P, P, P, P, P, I32, I32, I32, P],
+    "b200_gdn_gated_rmsnorm": [P, P, I64, P, P, I32, I32, I32, P],
     "b200_gdn_chunked_prefill_fused": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I32, I32,
                                        P, P, I64, I64, I32, I32, I32, P],
 }

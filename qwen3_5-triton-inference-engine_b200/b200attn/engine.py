@@ -73,8 +73,12 @@ def random_weights(cfg: ModelConfig, seed: int, device, std: float = 0.02) -> di
 class Engine:
     """One replica: weights, caches and the two entry points `prefill` and `step`."""
 
-    def __init__(self, cfg: ModelConfig, weights: dict, batch: int, max_context: int, device, page_seed: int = 0):
+    def __init__(self, cfg: ModelConfig, weights: dict, batch: int, max_context: int, device, page_seed: int = 0,
+                 fused_glue: bool = True):
+        """fused_glue: run the row-wise operators of a decode step (residual + RMSNorm, SwiGLU, conv + q/k norms +
+        gates, gated RMSNorm) as this package's single-launch kernels; False keeps them as eager PyTorch (glue.py)."""
         self.cfg, self.w, self.batch, self.device = cfg, weights, batch, torch.device(device)
+        self.fused_glue = fused_glue
         pages_per_seq = (max_context + ops.PAGE_SIZE - 1) // ops.PAGE_SIZE
         num_pages = batch * pages_per_seq
         perm = torch.randperm(num_pages, generator=torch.Generator().manual_seed(page_seed))
@@ -167,6 +171,8 @@ class Engine:
     def _decode(self, tok: torch.Tensor) -> torch.Tensor:
         """One token per sequence (engine/runner.py:408-571): returns the next token ids and advances pos on the
         device.  No host value changes from step to step, so the whole call can sit in a CUDA graph."""
+        if self.fused_glue:
+            return self._decode_fused(tok)
         cfg = self.cfg
         batch, heads, dim, kd = self.batch, cfg.gdn_heads, cfg.gdn_dim, cfg.gdn_width
         x = glue.embedding_gather(tok, self.w["embed"])
@@ -191,6 +197,44 @@ class Engine:
                 mixed = glue.gemm_2d(ctx, layer["o_proj"])
             x = self._mlp(glue.residual_add(mixed, x), layer)
         nxt = self._head(x)
+        self.pos.add_(1)
+        return nxt
+
+    def _decode_fused(self, tok: torch.Tensor) -> torch.Tensor:
+        """The same step with every row-wise operator as one launch: about ten launches per layer (four of them
+        cuBLAS GEMMs).  The residual add after a layer's MLP is fused into the next layer's input norm."""
+        cfg = self.cfg
+        batch, heads, kd = self.batch, cfg.gdn_heads, cfg.gdn_width
+        qd, kvd = cfg.num_q_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
+        x = glue.embedding_gather(tok, self.w["embed"])
+        pending = None                                   # MLP output still to be added to the residual stream
+        for i, layer in enumerate(self.w["layers"]):
+            if pending is None:
+                h = ops.add_rmsnorm(x, layer["ln1"], cfg.eps)
+            else:
+                x, h = ops.add_rmsnorm(pending, layer["ln1"], cfg.eps, residual=x)
+            if layer["kind"] == "gdn":
+                fused = glue.gemm_2d(h, layer["in_proj"])
+                q_n, k_n, v, beta, g = ops.gdn_decode_prep(fused[:, : 3 * kd], self.conv_state[i], layer["conv4"],
+                                                           fused[:, 4 * kd: 4 * kd + heads], fused[:, 4 * kd + heads:],
+                                                           layer["a_log"], layer["dt_bias"], heads)
+                core = ops.gdn_recurrent_decode(q_n, k_n, v, beta, g, self.rec_state[i])
+                normed = ops.gdn_gated_rmsnorm_fused(core, fused[:, 3 * kd: 4 * kd], layer["norm"])
+                mixed = glue.gemm_2d(normed, layer["out_proj"])
+            else:
+                fused = glue.gemm_2d(h, layer["qkvg"])
+                q = ops.add_rmsnorm(fused[:, :qd].view(batch, cfg.num_q_heads, cfg.head_dim), layer["q_norm"], cfg.eps)
+                k = ops.add_rmsnorm(fused[:, 2 * qd: 2 * qd + kvd].view(batch, cfg.num_kv_heads, cfg.head_dim),
+                                    layer["k_norm"], cfg.eps)
+                v = fused[:, 2 * qd + kvd:].view(batch, cfg.num_kv_heads, cfg.head_dim)
+                k_cache, v_cache = self.kv[i]
+                ctx = ops.fused_decode_attention(q, k, v, fused[:, qd: 2 * qd], k_cache, v_cache, self.block_table,
+                                                 self.pos, self.inv_freq, cfg.rotary_dim, self.workspace)
+                mixed = glue.gemm_2d(ctx, layer["o_proj"])
+            x, h = ops.add_rmsnorm(mixed, layer["ln2"], cfg.eps, residual=x)
+            pending = glue.gemm_2d(ops.swiglu_fused(glue.gemm_2d(h, layer["gate_up"]), cfg.intermediate), layer["down"])
+        _, h = ops.add_rmsnorm(pending, self.w["norm"], cfg.eps, residual=x)
+        nxt = glue.lm_head_argmax(h, self.w["embed"])
         self.pos.add_(1)
         return nxt
 

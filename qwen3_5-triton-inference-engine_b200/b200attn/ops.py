@@ -17,6 +17,7 @@ from . import _lib
 PAGE_SIZE = 16     # triton_kernels/gqa_attention_decode_paged.py:91
 MAX_SPLITS = 128   # triton_kernels/gqa_attention_decode_paged.py:95
 GDN_CHUNK = 64
+GDN_DIM = 128      # key and value dim the Gated-DeltaNet kernels are specialised for
 
 
 def _stream():
@@ -586,3 +587,79 @@ def gdn_chunked_prefill_packed(q, k, v, beta, g, cu_seqlens, max_seqlen=None, fu
               g.stride(1), _ptr(cu_seqlens.contiguous()), batch, token_num, int(max_seqlen), _ptr(workspace), _ptr(state),
               _ptr(out), out.stride(0), out.stride(1), num_heads, key_dim, value_dim, _stream())
     return out, state
+
+
+# =========================================================================== row-wise layer operators (one launch each)
+def add_rmsnorm(x, weight, eps: float, residual=None):
+    """Qwen RMSNorm `x * rsqrt(mean(x^2) + eps) * (1 + weight)` over the last dim (triton_kernels/qwen_rmsnorm.py:70-73),
+    optionally fused with the residual add in front of it (triton_kernels/residual_add.py).
+    x: [rows, dim] or a [n, H, dim] column view of a fused projection (last dim contiguous).  Returns norm, or
+    (sum, norm) when `residual` [rows, dim] is given (sum = bf16(x + residual), the new residual stream)."""
+    assert x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.is_contiguous()
+    _require_cuda(x, weight)
+    x = _inner_contiguous(x)
+    dim = x.shape[-1]
+    if x.ndim == 3:
+        outer, inner, count = x.stride(0), x.stride(1), x.shape[1]
+        rows = x.shape[0] * x.shape[1]
+    else:
+        assert x.ndim == 2
+        outer, inner, count, rows = x.stride(0), 0, 1, x.shape[0]
+    norm = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    total = None
+    if residual is not None:
+        assert x.ndim == 2 and residual.shape == x.shape and residual.dtype == torch.bfloat16 and residual.stride(1) == 1
+        total = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    _lib.call("b200_add_rmsnorm", _ptr(x), outer, inner, count, _ptr(residual) if residual is not None else None,
+              residual.stride(0) if residual is not None else 0, _ptr(weight), _ptr(total) if total is not None else None,
+              _ptr(norm), rows, dim, float(eps), _stream())
+    return norm if residual is None else (total, norm)
+
+
+def swiglu_fused(gate_up, intermediate: int):
+    """bf16(silu(gate_up[:, :I]) * gate_up[:, I:2I]) from the fused gate/up projection (triton_kernels/swiglu.py)."""
+    assert gate_up.ndim == 2 and gate_up.dtype == torch.bfloat16 and gate_up.stride(1) == 1
+    assert gate_up.shape[1] >= 2 * intermediate
+    _require_cuda(gate_up)
+    out = torch.empty((gate_up.shape[0], intermediate), dtype=torch.bfloat16, device=gate_up.device)
+    _lib.call("b200_swiglu", _ptr(gate_up), gate_up.stride(0), _ptr(out), gate_up.shape[0], int(intermediate), _stream())
+    return out
+
+
+def gdn_decode_prep(qkv, conv_state, weight4, a, b, a_log, dt_bias, num_heads: int):
+    """One decode token per sequence of a Gated-DeltaNet layer: conv state shift + depthwise conv4 + SiLU
+    (triton_kernels/depthwise_causal_conv4_decode.py), q/k L2 norms and the beta / g gates
+    (triton_kernels/gdn_qk_norm_gates.py:68-89) in one launch.  qkv [B, 3*H*128] (row view), conv_state [B,4,3*H*128]
+    (updated in place), weight4 [4, 3*H*128], a/b [B,H] bf16 (row views).
+    Returns q_n, k_n, v [B,H,128] bf16 and beta, g [B,H] fp32."""
+    batch, width = qkv.shape
+    assert width == 3 * num_heads * GDN_DIM and qkv.stride(1) == 1 and qkv.dtype == torch.bfloat16
+    assert conv_state.shape == (batch, 4, width) and conv_state.is_contiguous() and conv_state.dtype == torch.bfloat16
+    assert weight4.shape == (4, width) and weight4.is_contiguous() and weight4.dtype == torch.bfloat16
+    assert a.shape == b.shape == (batch, num_heads) and a.dtype == b.dtype == torch.bfloat16
+    assert a.stride(1) == 1 and b.stride(1) == 1
+    assert a_log.dtype == torch.float32 and a_log.is_contiguous() and dt_bias.dtype == torch.bfloat16
+    _require_cuda(qkv, conv_state, weight4, a, b, a_log, dt_bias)
+    dev = qkv.device
+    q_n = torch.empty((batch, num_heads, GDN_DIM), dtype=torch.bfloat16, device=dev)
+    k_n, v = torch.empty_like(q_n), torch.empty_like(q_n)
+    beta = torch.empty((batch, num_heads), dtype=torch.float32, device=dev)
+    g = torch.empty_like(beta)
+    _lib.call("b200_gdn_decode_prep", _ptr(qkv), qkv.stride(0), _ptr(conv_state), _ptr(weight4), _ptr(a), a.stride(0),
+              _ptr(b), b.stride(0), _ptr(a_log), _ptr(dt_bias.contiguous()), _ptr(q_n), _ptr(k_n), _ptr(v), _ptr(beta),
+              _ptr(g), batch, num_heads, GDN_DIM, _stream())
+    return q_n, k_n, v, beta, g
+
+
+def gdn_gated_rmsnorm_fused(x, z, weight):
+    """x * rsqrt(mean(x^2) + 1e-6) * weight * silu(z) per head (triton_kernels/gdn_gated_rmsnorm.py:54-67).
+    x [n,H,128] contiguous, z [n, H*128] row view, weight [128] fp32 -> [n, H*128] bf16."""
+    n, heads, dim = x.shape
+    assert dim == GDN_DIM and x.is_contiguous() and x.dtype == torch.bfloat16
+    assert z.shape == (n, heads * dim) and z.stride(1) == 1 and z.dtype == torch.bfloat16
+    assert weight.dtype == torch.float32 and weight.shape == (dim,) and weight.is_contiguous()
+    _require_cuda(x, z, weight)
+    out = torch.empty((n, heads * dim), dtype=torch.bfloat16, device=x.device)
+    _lib.call("b200_gdn_gated_rmsnorm", _ptr(x), _ptr(z), z.stride(0), _ptr(weight), _ptr(out), n * heads, heads, dim,
+              _stream())
+    return out

@@ -1,0 +1,220 @@
+// Row-wise operators between the projections and the attention / Gated-DeltaNet kernels of a layer, each one launch
+// where the reference spends one to three and an eager PyTorch restatement a dozen:
+//   b200_add_rmsnorm        <-> triton_kernels/residual_add.py + triton_kernels/qwen_rmsnorm.py:70-73
+//   b200_swiglu             <-> triton_kernels/swiglu.py
+//   b200_gdn_decode_prep    <-> triton_kernels/depthwise_causal_conv4_decode.py + triton_kernels/gdn_qk_norm_gates.py:68-89
+//   b200_gdn_gated_rmsnorm  <-> triton_kernels/gdn_gated_rmsnorm.py:54-67
+// All are HBM/launch bound: 16-byte accesses, one warp per row (or one CTA per (sequence, head)), fp32 math, one
+// rounding to bf16 at the reference's rounding points.
+#include "b200_attn.h"
+#include "common.cuh"
+
+namespace b200 {
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+  f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  return make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+}
+
+// ------------------------------------------------------------------------------------------ (residual +) RMSNorm
+constexpr int RN_MAXV = 8;  // 16-byte vectors per lane: dim <= 2048
+
+__global__ void __launch_bounds__(128)
+add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_outer, int64_t x_inner, int inner_count,
+                   const __nv_bfloat16* __restrict__ residual, int64_t res_stride,
+                   const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ sum_out,
+                   __nv_bfloat16* __restrict__ norm_out, int rows, int dim, float eps) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const __nv_bfloat16* src = x + static_cast<int64_t>(row / inner_count) * x_outer + (row % inner_count) * x_inner;
+  const int nvec = dim >> 8;  // vectors per lane
+  float v[RN_MAXV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < RN_MAXV; ++i) {
+    if (i < nvec) {
+      const int c = (i * 32 + lane) * 8;
+      unpack8(*reinterpret_cast<const uint4*>(src + c), v[i]);
+      if (residual != nullptr) {
+        float r[8];
+        unpack8(*reinterpret_cast<const uint4*>(residual + static_cast<int64_t>(row) * res_stride + c), r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = round_bf16(v[i][j] + r[j]);  // the sum is a bf16 tensor in the reference
+        if (sum_out != nullptr) *reinterpret_cast<uint4*>(sum_out + static_cast<int64_t>(row) * dim + c) = pack8(v[i]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(v[i][j], v[i][j], ss);
+    }
+  }
+  ss = warp_sum(ss);
+  const float rs = rsqrtf(ss / static_cast<float>(dim) + eps);
+#pragma unroll
+  for (int i = 0; i < RN_MAXV; ++i) {
+    if (i < nvec) {
+      const int c = (i * 32 + lane) * 8;
+      float w[8], o[8];
+      unpack8(*reinterpret_cast<const uint4*>(weight + c), w);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = v[i][j] * rs * (1.0f + w[j]);
+      *reinterpret_cast<uint4*>(norm_out + static_cast<int64_t>(row) * dim + c) = pack8(o);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------- SwiGLU
+__global__ void __launch_bounds__(256)
+swiglu_kernel(const __nv_bfloat16* __restrict__ gate_up, int64_t row_stride, __nv_bfloat16* __restrict__ out, int rows,
+              int inter) {
+  const int vec_per_row = inter >> 3;
+  const int64_t total = static_cast<int64_t>(rows) * vec_per_row;
+  for (int64_t idx = blockIdx.x * 256 + threadIdx.x; idx < total; idx += static_cast<int64_t>(gridDim.x) * 256) {
+    const int64_t r = idx / vec_per_row;
+    const int c = static_cast<int>(idx % vec_per_row) * 8;
+    float g[8], u[8], o[8];
+    unpack8(*reinterpret_cast<const uint4*>(gate_up + r * row_stride + c), g);
+    unpack8(*reinterpret_cast<const uint4*>(gate_up + r * row_stride + inter + c), u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.0f + expf(-g[j])) * u[j];
+    *reinterpret_cast<uint4*>(out + r * inter + c) = pack8(o);
+  }
+}
+
+// ------------------------------------------------------------------------------- GDN decode: conv + norms + gates
+// CTA = (head, sequence), thread t = channel t of the head's q, k and v slices of the [3*H*128] conv width.
+__global__ void __launch_bounds__(GDN_D)
+gdn_decode_prep_kernel(const __nv_bfloat16* __restrict__ qkv, int64_t qkv_stride, __nv_bfloat16* __restrict__ conv_state,
+                       const __nv_bfloat16* __restrict__ w4, const __nv_bfloat16* __restrict__ a, int64_t a_stride,
+                       const __nv_bfloat16* __restrict__ b, int64_t b_stride, const float* __restrict__ a_log,
+                       const __nv_bfloat16* __restrict__ dt_bias, __nv_bfloat16* __restrict__ q_out,
+                       __nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ v_out, float* __restrict__ beta,
+                       float* __restrict__ g, int heads) {
+  __shared__ float red[2][4];
+  const int h = blockIdx.x, seq = blockIdx.y, t = threadIdx.x;
+  const int width = 3 * heads * GDN_D;
+  float y[3];
+#pragma unroll
+  for (int part = 0; part < 3; ++part) {
+    const int c = part * heads * GDN_D + h * GDN_D + t;
+    __nv_bfloat16* st = conv_state + static_cast<int64_t>(seq) * 4 * width + c;
+    const __nv_bfloat16 s1 = st[width], s2 = st[2 * width], s3 = st[3 * width];
+    const __nv_bfloat16 xn = qkv[static_cast<int64_t>(seq) * qkv_stride + c];
+    st[0] = s1;
+    st[width] = s2;
+    st[2 * width] = s3;
+    st[3 * width] = xn;
+    float acc = __bfloat162float(w4[c]) * __bfloat162float(s1);
+    acc = fmaf(__bfloat162float(w4[width + c]), __bfloat162float(s2), acc);
+    acc = fmaf(__bfloat162float(w4[2 * width + c]), __bfloat162float(s3), acc);
+    acc = fmaf(__bfloat162float(w4[3 * width + c]), __bfloat162float(xn), acc);
+    y[part] = round_bf16(acc / (1.0f + expf(-acc)));  // the conv output is a bf16 tensor in the reference
+  }
+  float sq = warp_sum(y[0] * y[0]), sk = warp_sum(y[1] * y[1]);
+  if ((t & 31) == 0) {
+    red[0][t >> 5] = sq;
+    red[1][t >> 5] = sk;
+  }
+  __syncthreads();
+  sq = (red[0][0] + red[0][1]) + (red[0][2] + red[0][3]);
+  sk = (red[1][0] + red[1][1]) + (red[1][2] + red[1][3]);
+  const int64_t o = (static_cast<int64_t>(seq) * heads + h) * GDN_D + t;
+  q_out[o] = __float2bfloat16_rn(y[0] * rsqrtf(sq + 1e-6f) * 0.08838834764831845f);  // DK^-0.5, DK = 128
+  k_out[o] = __float2bfloat16_rn(y[1] * rsqrtf(sk + 1e-6f));
+  v_out[o] = __float2bfloat16_rn(y[2]);
+  if (t == 0) {
+    const float av = __bfloat162float(a[static_cast<int64_t>(seq) * a_stride + h]) + __bfloat162float(dt_bias[h]);
+    const float bv = __bfloat162float(b[static_cast<int64_t>(seq) * b_stride + h]);
+    const float sp = av > 20.f ? av : log1pf(expf(av));
+    beta[static_cast<int64_t>(seq) * heads + h] = 1.0f / (1.0f + expf(-bv));
+    g[static_cast<int64_t>(seq) * heads + h] = -expf(a_log[h]) * sp;
+  }
+}
+
+// ------------------------------------------------------------------------------------------- gated RMSNorm (GDN)
+__global__ void __launch_bounds__(128)
+gdn_gated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ z, int64_t z_stride,
+                         const float* __restrict__ weight, __nv_bfloat16* __restrict__ out, int rows, int heads) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int n = row / heads, h = row % heads;
+  const uint2 xv = *reinterpret_cast<const uint2*>(x + static_cast<int64_t>(row) * GDN_D + lane * 4);
+  const uint2 zv = *reinterpret_cast<const uint2*>(z + static_cast<int64_t>(n) * z_stride + h * GDN_D + lane * 4);
+  const float4 wv = *reinterpret_cast<const float4*>(weight + lane * 4);
+  const float xf[4] = {bf16_lo(xv.x), bf16_hi(xv.x), bf16_lo(xv.y), bf16_hi(xv.y)};
+  const float zf[4] = {bf16_lo(zv.x), bf16_hi(zv.x), bf16_lo(zv.y), bf16_hi(zv.y)};
+  const float wf[4] = {wv.x, wv.y, wv.z, wv.w};
+  const float ss = warp_sum((xf[0] * xf[0] + xf[1] * xf[1]) + (xf[2] * xf[2] + xf[3] * xf[3]));
+  const float rs = rsqrtf(ss / static_cast<float>(GDN_D) + 1e-6f);
+  float o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) o[j] = xf[j] * rs * wf[j] * (zf[j] / (1.0f + expf(-zf[j])));
+  *reinterpret_cast<uint2*>(out + static_cast<int64_t>(row) * GDN_D + lane * 4) =
+      make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_add_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x_stride_inner, int32_t inner_count,
+                                const void* residual, int64_t residual_stride, const void* weight, void* sum_out,
+                                void* norm_out, int32_t rows, int32_t dim, float eps, b200_stream_t stream) {
+  B200_REQUIRE(rows > 0 && inner_count > 0 && dim > 0 && dim % 256 == 0 && dim <= 256 * RN_MAXV,
+               "add_rmsnorm: dim must be a multiple of 256 up to %d (got %d)", 256 * RN_MAXV, dim);
+  B200_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(norm_out) && x_stride_outer % 8 == 0 &&
+                   x_stride_inner % 8 == 0,
+               "add_rmsnorm: pointers must be 16-byte aligned and row strides multiples of 8 elements");
+  B200_REQUIRE(residual == nullptr || (aligned16(residual) && residual_stride % 8 == 0 &&
+                                       (sum_out == nullptr || aligned16(sum_out))),
+               "add_rmsnorm: residual / sum_out must be 16-byte aligned with a row stride that is a multiple of 8");
+  add_rmsnorm_kernel<<<(rows + 3) / 4, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), x_stride_outer, x_stride_inner, inner_count,
+      static_cast<const __nv_bfloat16*>(residual), residual_stride, static_cast<const __nv_bfloat16*>(weight),
+      static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), rows, dim, eps);
+  return check_launch("add_rmsnorm");
+}
+
+extern "C" int b200_swiglu(const void* gate_up, int64_t row_stride, void* out, int32_t rows, int32_t intermediate,
+                           b200_stream_t stream) {
+  B200_REQUIRE(rows > 0 && intermediate > 0 && intermediate % 8 == 0 && row_stride % 8 == 0 && aligned16(gate_up) &&
+                   aligned16(out),
+               "swiglu: intermediate and the row stride must be multiples of 8, pointers 16-byte aligned");
+  const int64_t vecs = static_cast<int64_t>(rows) * (intermediate / 8);
+  int blocks = static_cast<int>((vecs + 255) / 256);
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  swiglu_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gate_up), row_stride, static_cast<__nv_bfloat16*>(out), rows, intermediate);
+  return check_launch("swiglu");
+}
+
+extern "C" int b200_gdn_decode_prep(const void* qkv, int64_t qkv_stride, void* conv_state, const void* weight4,
+                                    const void* a, int64_t a_stride, const void* b, int64_t b_stride,
+                                    const float* a_log, const void* dt_bias, void* q_out, void* k_out, void* v_out,
+                                    float* beta, float* g, int32_t batch, int32_t num_heads, int32_t head_dim,
+                                    b200_stream_t stream) {
+  B200_REQUIRE(batch > 0 && batch <= 65535 && num_heads > 0 && head_dim == GDN_D,
+               "gdn_decode_prep: head_dim must be %d (got %d)", GDN_D, head_dim);
+  gdn_decode_prep_kernel<<<dim3(num_heads, batch), GDN_D, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(qkv), qkv_stride, static_cast<__nv_bfloat16*>(conv_state),
+      static_cast<const __nv_bfloat16*>(weight4), static_cast<const __nv_bfloat16*>(a), a_stride,
+      static_cast<const __nv_bfloat16*>(b), b_stride, a_log, static_cast<const __nv_bfloat16*>(dt_bias),
+      static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_out), static_cast<__nv_bfloat16*>(v_out), beta, g,
+      num_heads);
+  return check_launch("gdn_decode_prep");
+}
+
+extern "C" int b200_gdn_gated_rmsnorm(const void* x, const void* z, int64_t z_stride, const float* weight, void* out,
+                                      int32_t rows, int32_t num_heads, int32_t head_dim, b200_stream_t stream) {
+  B200_REQUIRE(rows > 0 && num_heads > 0 && head_dim == GDN_D, "gdn_gated_rmsnorm: head_dim must be %d (got %d)", GDN_D,
+               head_dim);
+  B200_REQUIRE(z_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(x) % 8 == 0) && (reinterpret_cast<uintptr_t>(z) % 8 == 0) &&
+                   (reinterpret_cast<uintptr_t>(out) % 8 == 0) && aligned16(weight),
+               "gdn_gated_rmsnorm: x, z, out must be 8-byte aligned, weight 16-byte aligned, z stride a multiple of 4");
+  gdn_gated_rmsnorm_kernel<<<(rows + 3) / 4, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(z), z_stride, weight,
+      static_cast<__nv_bfloat16*>(out), rows, num_heads);
+  return check_launch("gdn_gated_rmsnorm");
+}

@@ -1,0 +1,90 @@
+"""GPU parity of the single-launch row-wise layer operators (csrc/layer_glue.cu) against the eager PyTorch
+restatements of the reference operators in b200attn/glue.py (same fp32 math and rounding points): at most one bf16
+ulp apart (transcendentals come from different libraries), gates to 1e-6 relative."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def mods():
+    from b200attn import glue, ops
+    return ops, glue
+
+
+def _ulp_close(a, b, ulps=1):
+    a, b = a.float(), b.float()
+    tol = ulps * 2.0 ** -8 * torch.maximum(a.abs(), b.abs()) + 1e-30
+    assert bool(((a - b).abs() <= tol).all()), f"max diff {(a - b).abs().max().item()}"
+
+
+@pytest.mark.parametrize("rows,dim", [(1, 1024), (32, 1024), (257, 256), (5, 2048)])
+def test_add_rmsnorm(mods, rows, dim):
+    ops, glue = mods
+    gen = torch.Generator().manual_seed(rows * 7 + dim)
+    x = torch.randn(rows, dim, generator=gen).to(torch.bfloat16).to(DEV)
+    res = torch.randn(rows, dim, generator=gen).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(dim, generator=gen) * 0.1).to(torch.bfloat16).to(DEV)
+    _ulp_close(ops.add_rmsnorm(x, w, 1e-6), glue.qwen_rmsnorm(x, w, 1e-6))
+    total, norm = ops.add_rmsnorm(x, w, 1e-6, residual=res)
+    ref_total = glue.residual_add(x, res)
+    assert torch.equal(total, ref_total)
+    _ulp_close(norm, glue.qwen_rmsnorm(ref_total, w, 1e-6))
+
+
+def test_rmsnorm_on_head_views(mods):
+    """q / k norms read column views of the fused projection: [n, H, 256] with strides (5120, 256, 1)."""
+    ops, glue = mods
+    gen = torch.Generator().manual_seed(3)
+    fused = torch.randn(9, 5120, generator=gen).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(256, generator=gen) * 0.1).to(torch.bfloat16).to(DEV)
+    for view in (fused[:, :2048].view(9, 8, 256), fused[:, 4096:4608].view(9, 2, 256)):
+        out = ops.add_rmsnorm(view, w, 1e-6)
+        assert out.is_contiguous() and out.shape == view.shape
+        _ulp_close(out, glue.qwen_rmsnorm(view, w, 1e-6))
+
+
+@pytest.mark.parametrize("rows", [1, 32, 300])
+def test_swiglu(mods, rows):
+    ops, glue = mods
+    gen = torch.Generator().manual_seed(rows)
+    inter = 3584
+    gu = (torch.randn(rows, 2 * inter, generator=gen) * 2).to(torch.bfloat16).to(DEV)
+    _ulp_close(ops.swiglu_fused(gu, inter), glue.swiglu(gu[:, :inter], gu[:, inter:]))
+
+
+@pytest.mark.parametrize("batch", [1, 32])
+def test_gdn_decode_prep(mods, batch):
+    ops, glue = mods
+    gen = torch.Generator().manual_seed(50 + batch)
+    heads, kd = 16, 2048
+    fused = torch.randn(batch, 4 * kd + 2 * heads, generator=gen).to(torch.bfloat16).to(DEV)
+    state = torch.randn(batch, 4, 3 * kd, generator=gen).to(torch.bfloat16).to(DEV)
+    w4 = (torch.randn(4, 3 * kd, generator=gen) * 0.5).to(torch.bfloat16).to(DEV)
+    a_log = (torch.rand(heads, generator=gen) * 2.7).to(DEV)
+    dt_bias = (torch.randn(heads, generator=gen) * 0.5).to(torch.bfloat16).to(DEV)
+    qkv, a, b = fused[:, : 3 * kd], fused[:, 4 * kd: 4 * kd + heads], fused[:, 4 * kd + heads:]
+    ref_state = state.clone()
+    conv = glue.depthwise_causal_conv4_decode(qkv, ref_state, w4)
+    rq, rk, rbeta, rg = glue.gdn_qk_norm_gates(conv[:, :kd].view(batch, heads, 128), conv[:, kd: 2 * kd].view(batch, heads, 128),
+                                               a, b, a_log, dt_bias)
+    q_n, k_n, v, beta, g = ops.gdn_decode_prep(qkv, state, w4, a, b, a_log, dt_bias, heads)
+    assert torch.equal(state, ref_state)
+    _ulp_close(v, conv[:, 2 * kd:].view(batch, heads, 128))
+    _ulp_close(q_n, rq, ulps=2)
+    _ulp_close(k_n, rk, ulps=2)
+    assert torch.allclose(beta, rbeta, rtol=1e-5, atol=1e-7) and torch.allclose(g, rg, rtol=1e-5, atol=1e-7)
+
+
+def test_gdn_gated_rmsnorm(mods):
+    ops, glue = mods
+    gen = torch.Generator().manual_seed(8)
+    n, heads = 33, 16
+    x = torch.randn(n, heads, 128, generator=gen).to(torch.bfloat16).to(DEV)
+    fused = torch.randn(n, 8224, generator=gen).to(torch.bfloat16).to(DEV)
+    z = fused[:, 6144:8192]
+    w = (1 + 0.1 * torch.randn(128, generator=gen)).to(DEV)
+    out = ops.gdn_gated_rmsnorm_fused(x, z, w)
+    _ulp_close(out.view(n, heads, 128), glue.gdn_gated_rmsnorm(x, z.reshape(n, heads, 128), w))
