@@ -260,7 +260,7 @@ int b200_gdn_chunked_prefill_fused(const void* q, int64_t q_stride_t, int64_t q_
  * to bf16 first and also written to sum_out when that is non-NULL).  Row r of x lives at
  * x + (r / inner_count) * x_stride_outer + (r % inner_count) * x_stride_inner (so a [n, H, D] column view of a fused
  * projection works); residual rows are residual_stride apart; sum_out and norm_out are contiguous [rows, dim].
- * dim must be a multiple of 256, at most 2048.  Replaces triton_kernels/qwen_rmsnorm.py:98-146 (and
+ * dim must be a multiple of 256, at most 8192.  Replaces triton_kernels/qwen_rmsnorm.py:98-146 (and
  * triton_kernels/residual_add.py in front of it).
  * b200_swiglu: out[r, c] = silu(gate_up[r, c]) * gate_up[r, intermediate + c].  Replaces triton_kernels/swiglu.py.
  * b200_gdn_decode_prep: one decode token per sequence of a Gated-DeltaNet layer: shifts conv_state [B,4,3*H*128]

@@ -100,11 +100,18 @@ class Engine:
         self.graph = None
 
     # ------------------------------------------------------------------------------------------------ shared pieces
+    def _norm(self, x, weight):
+        if self.fused_glue:
+            return ops.add_rmsnorm(x, weight, self.cfg.eps)
+        return glue.qwen_rmsnorm(x, weight, self.cfg.eps)
+
     def _mlp(self, x, layer):
         cfg = self.cfg
-        h = glue.qwen_rmsnorm(x, layer["ln2"], cfg.eps)
-        gate_up = glue.gemm_2d(h, layer["gate_up"])
-        h = glue.swiglu(gate_up[:, : cfg.intermediate], gate_up[:, cfg.intermediate:])
+        gate_up = glue.gemm_2d(self._norm(x, layer["ln2"]), layer["gate_up"])
+        if self.fused_glue:
+            h = ops.swiglu_fused(gate_up, cfg.intermediate)
+        else:
+            h = glue.swiglu(gate_up[:, : cfg.intermediate], gate_up[:, cfg.intermediate:])
         return glue.residual_add(glue.gemm_2d(h, layer["down"]), x)
 
     def _split_gdn(self, fused):
@@ -116,14 +123,13 @@ class Engine:
         cfg = self.cfg
         qd, kvd = cfg.num_q_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
         n = fused.shape[0]
-        q = glue.qwen_rmsnorm(fused[:, :qd].view(n, cfg.num_q_heads, cfg.head_dim), self._cur["q_norm"], cfg.eps)
-        k = glue.qwen_rmsnorm(fused[:, 2 * qd: 2 * qd + kvd].view(n, cfg.num_kv_heads, cfg.head_dim),
-                              self._cur["k_norm"], cfg.eps)
+        q = self._norm(fused[:, :qd].view(n, cfg.num_q_heads, cfg.head_dim), self._cur["q_norm"])
+        k = self._norm(fused[:, 2 * qd: 2 * qd + kvd].view(n, cfg.num_kv_heads, cfg.head_dim), self._cur["k_norm"])
         v = fused[:, 2 * qd + kvd:].view(n, cfg.num_kv_heads, cfg.head_dim)
         return q, k, v, fused[:, qd: 2 * qd]
 
     def _head(self, x):
-        return glue.lm_head_argmax(glue.qwen_rmsnorm(x, self.w["norm"], self.cfg.eps), self.w["embed"])
+        return glue.lm_head_argmax(self._norm(x, self.w["norm"]), self.w["embed"])
 
     # ------------------------------------------------------------------------------------------------------ prefill
     @torch.no_grad()
@@ -140,7 +146,7 @@ class Engine:
         x = glue.embedding_gather(ids, self.w["embed"])
         for i, layer in enumerate(self.w["layers"]):
             self._cur = layer
-            h = glue.qwen_rmsnorm(x, layer["ln1"], cfg.eps)
+            h = self._norm(x, layer["ln1"])
             if layer["kind"] == "gdn":
                 qkv, z, a, b = self._split_gdn(glue.gemm_2d(h, layer["in_proj"]))
                 conv = glue.depthwise_causal_conv4_prefill(qkv, layer["conv"], pos_in_seq)
@@ -152,8 +158,11 @@ class Engine:
                 core, state = ops.gdn_chunked_prefill_packed(q_n, k_n, v, beta, g, cu)
                 self.rec_state[i].copy_(state)
                 glue.conv_state_from_packed_prefill(self.conv_state[i], qkv, cu)
-                normed = glue.gdn_gated_rmsnorm(core, z.reshape(total, heads, dim), layer["norm"])
-                mixed = glue.gemm_2d(normed.view(total, kd), layer["out_proj"])
+                if self.fused_glue:
+                    normed = ops.gdn_gated_rmsnorm_fused(core, z, layer["norm"])
+                else:
+                    normed = glue.gdn_gated_rmsnorm(core, z.reshape(total, heads, dim), layer["norm"]).view(total, kd)
+                mixed = glue.gemm_2d(normed, layer["out_proj"])
             else:
                 q, k, v, gate = self._split_attention(glue.gemm_2d(h, layer["qkvg"]))
                 k_cache, v_cache = self.kv[i]

@@ -38,7 +38,11 @@ def embedding_gather(token_ids: torch.Tensor, table: torch.Tensor) -> torch.Tens
 def lm_head_argmax(hidden: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     """argmax_v <hidden, table[v]> with the tied embedding as the LM head; ties go to the lowest index
     (triton_kernels/vocab_argmax.py).  Returns int64 [B]."""
-    return torch.argmax(F.linear(hidden, table).float(), dim=-1)
+    try:
+        logits = torch.mm(hidden, table.t(), out_dtype=torch.float32)    # fp32 logits straight from the GEMM
+    except (TypeError, RuntimeError):
+        logits = F.linear(hidden, table).float()
+    return torch.argmax(logits, dim=-1)
 
 
 def depthwise_causal_conv4_prefill(x: torch.Tensor, weight: torch.Tensor, pos_in_seq: torch.Tensor | None) -> torch.Tensor:

@@ -20,48 +20,48 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 }
 
 // ------------------------------------------------------------------------------------------ (residual +) RMSNorm
-constexpr int RN_MAXV = 8;  // 16-byte vectors per lane: dim <= 2048
+// CTA = one row, thread = 8 consecutive elements (blockDim = dim / 8, a multiple of 32): every global load of a
+// thread is issued before the first use, so a call costs one memory round trip plus the block reduction.
+constexpr int RN_MAX_DIM = 8192;
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(RN_MAX_DIM / 8)
 add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_outer, int64_t x_inner, int inner_count,
                    const __nv_bfloat16* __restrict__ residual, int64_t res_stride,
                    const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ sum_out,
-                   __nv_bfloat16* __restrict__ norm_out, int rows, int dim, float eps) {
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (row >= rows) return;
+                   __nv_bfloat16* __restrict__ norm_out, int dim, float eps) {
+  __shared__ float red[32];
+  const int row = blockIdx.x, c = threadIdx.x * 8;
   const __nv_bfloat16* src = x + static_cast<int64_t>(row / inner_count) * x_outer + (row % inner_count) * x_inner;
-  const int nvec = dim >> 8;  // vectors per lane
-  float v[RN_MAXV][8];
+  const uint4 xv = *reinterpret_cast<const uint4*>(src + c);
+  const uint4 wv = *reinterpret_cast<const uint4*>(weight + c);
+  uint4 rv = make_uint4(0, 0, 0, 0);
+  if (residual != nullptr) rv = *reinterpret_cast<const uint4*>(residual + static_cast<int64_t>(row) * res_stride + c);
+  float v[8], w[8];
+  unpack8(xv, v);
+  unpack8(wv, w);
+  if (residual != nullptr) {
+    float r[8];
+    unpack8(rv, r);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = round_bf16(v[j] + r[j]);  // the sum is a bf16 tensor in the reference
+    if (sum_out != nullptr) *reinterpret_cast<uint4*>(sum_out + static_cast<int64_t>(row) * dim + c) = pack8(v);
+  }
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < RN_MAXV; ++i) {
-    if (i < nvec) {
-      const int c = (i * 32 + lane) * 8;
-      unpack8(*reinterpret_cast<const uint4*>(src + c), v[i]);
-      if (residual != nullptr) {
-        float r[8];
-        unpack8(*reinterpret_cast<const uint4*>(residual + static_cast<int64_t>(row) * res_stride + c), r);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[i][j] = round_bf16(v[i][j] + r[j]);  // the sum is a bf16 tensor in the reference
-        if (sum_out != nullptr) *reinterpret_cast<uint4*>(sum_out + static_cast<int64_t>(row) * dim + c) = pack8(v[i]);
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) ss = fmaf(v[i][j], v[i][j], ss);
-    }
-  }
+  for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
   ss = warp_sum(ss);
-  const float rs = rsqrtf(ss / static_cast<float>(dim) + eps);
-#pragma unroll
-  for (int i = 0; i < RN_MAXV; ++i) {
-    if (i < nvec) {
-      const int c = (i * 32 + lane) * 8;
-      float w[8], o[8];
-      unpack8(*reinterpret_cast<const uint4*>(weight + c), w);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = v[i][j] * rs * (1.0f + w[j]);
-      *reinterpret_cast<uint4*>(norm_out + static_cast<int64_t>(row) * dim + c) = pack8(o);
-    }
+  const int warps = blockDim.x >> 5;
+  if (warps > 1) {
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    ss = 0.f;
+    for (int i = 0; i < warps; ++i) ss += red[i];
   }
+  const float rs = rsqrtf(ss / static_cast<float>(dim) + eps);
+  float o[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = v[j] * rs * (1.0f + w[j]);
+  *reinterpret_cast<uint4*>(norm_out + static_cast<int64_t>(row) * dim + c) = pack8(o);
 }
 
 // ------------------------------------------------------------------------------------------------------- SwiGLU
@@ -161,18 +161,18 @@ using namespace b200;
 extern "C" int b200_add_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x_stride_inner, int32_t inner_count,
                                 const void* residual, int64_t residual_stride, const void* weight, void* sum_out,
                                 void* norm_out, int32_t rows, int32_t dim, float eps, b200_stream_t stream) {
-  B200_REQUIRE(rows > 0 && inner_count > 0 && dim > 0 && dim % 256 == 0 && dim <= 256 * RN_MAXV,
-               "add_rmsnorm: dim must be a multiple of 256 up to %d (got %d)", 256 * RN_MAXV, dim);
+  B200_REQUIRE(rows > 0 && inner_count > 0 && dim > 0 && dim % 256 == 0 && dim <= RN_MAX_DIM,
+               "add_rmsnorm: dim must be a multiple of 256 up to %d (got %d)", RN_MAX_DIM, dim);
   B200_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(norm_out) && x_stride_outer % 8 == 0 &&
                    x_stride_inner % 8 == 0,
                "add_rmsnorm: pointers must be 16-byte aligned and row strides multiples of 8 elements");
   B200_REQUIRE(residual == nullptr || (aligned16(residual) && residual_stride % 8 == 0 &&
                                        (sum_out == nullptr || aligned16(sum_out))),
                "add_rmsnorm: residual / sum_out must be 16-byte aligned with a row stride that is a multiple of 8");
-  add_rmsnorm_kernel<<<(rows + 3) / 4, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  add_rmsnorm_kernel<<<rows, dim / 8, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), x_stride_outer, x_stride_inner, inner_count,
       static_cast<const __nv_bfloat16*>(residual), residual_stride, static_cast<const __nv_bfloat16*>(weight),
-      static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), rows, dim, eps);
+      static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), dim, eps);
   return check_launch("add_rmsnorm");
 }
 
