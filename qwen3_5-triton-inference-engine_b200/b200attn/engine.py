@@ -129,7 +129,7 @@ class Engine:
         return q, k, v, fused[:, qd: 2 * qd]
 
     def _head(self, x):
-        return glue.lm_head_argmax(self._norm(x, self.w["norm"]), self.w["embed"])
+        return glue.lm_head_argmax(self._norm(x, self.w["norm"]), self.w["embed"], last_only=False)
 
     # ------------------------------------------------------------------------------------------------------ prefill
     @torch.no_grad()
@@ -142,6 +142,7 @@ class Engine:
         ids = torch.tensor([t for p in prompts for t in p], dtype=torch.int64).to(self.device)
         cu, max_len = ops.build_cu_seqlens(lengths, device=self.device)
         pos_in_seq = torch.cat([torch.arange(n) for n in lengths]).to(torch.int32).to(self.device)
+        seq_start = torch.repeat_interleave(cu[:-1], torch.tensor(lengths, device=self.device))  # runner.py:136
         total, heads, dim = ids.numel(), cfg.gdn_heads, cfg.gdn_dim
         x = glue.embedding_gather(ids, self.w["embed"])
         for i, layer in enumerate(self.w["layers"]):
@@ -149,7 +150,7 @@ class Engine:
             h = self._norm(x, layer["ln1"])
             if layer["kind"] == "gdn":
                 qkv, z, a, b = self._split_gdn(glue.gemm_2d(h, layer["in_proj"]))
-                conv = glue.depthwise_causal_conv4_prefill(qkv, layer["conv"], pos_in_seq)
+                conv = glue.depthwise_causal_conv4_prefill(qkv, layer["conv"], seq_start)
                 kd = cfg.gdn_width
                 q = conv[:, :kd].view(total, heads, dim)
                 k = conv[:, kd: 2 * kd].view(total, heads, dim)
@@ -243,7 +244,7 @@ class Engine:
             x, h = ops.add_rmsnorm(mixed, layer["ln2"], cfg.eps, residual=x)
             pending = glue.gemm_2d(ops.swiglu_fused(glue.gemm_2d(h, layer["gate_up"]), cfg.intermediate), layer["down"])
         _, h = ops.add_rmsnorm(pending, self.w["norm"], cfg.eps, residual=x)
-        nxt = glue.lm_head_argmax(h, self.w["embed"])
+        nxt = glue.lm_head_argmax(h, self.w["embed"], last_only=False)
         self.pos.add_(1)
         return nxt
 

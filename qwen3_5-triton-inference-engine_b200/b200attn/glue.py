@@ -35,23 +35,29 @@ def embedding_gather(token_ids: torch.Tensor, table: torch.Tensor) -> torch.Tens
     return table.index_select(0, token_ids.reshape(-1).long())
 
 
-def lm_head_argmax(hidden: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+def lm_head_argmax(hidden: torch.Tensor, table: torch.Tensor, last_only: bool = True) -> torch.Tensor:
     """argmax_v <hidden, table[v]> with the tied embedding as the LM head; ties go to the lowest index
-    (triton_kernels/vocab_argmax.py).  Returns int64 [B]."""
+    (triton_kernels/vocab_argmax.py:141-200).  last_only=True: only the last row of hidden, returns a 0-d tensor
+    (prefill of one sequence); last_only=False: one id per row, int64 [B] (batched decode)."""
+    if last_only:
+        hidden = hidden[-1:]
     try:
         logits = torch.mm(hidden, table.t(), out_dtype=torch.float32)    # fp32 logits straight from the GEMM
     except (TypeError, RuntimeError):
         logits = F.linear(hidden, table).float()
-    return torch.argmax(logits, dim=-1)
+    ids = torch.argmax(logits, dim=-1)
+    return ids[0] if last_only else ids
 
 
-def depthwise_causal_conv4_prefill(x: torch.Tensor, weight: torch.Tensor, pos_in_seq: torch.Tensor | None) -> torch.Tensor:
-    """y[t,c] = silu(sum_{r=0..3} w[c,r] x[t+r-3,c]) over a packed buffer; taps that would reach before the start of
-    the token's own sequence read zero (triton_kernels/depthwise_causal_conv4_prefill.py:18-91).  x [T,C] bf16 (any row
-    stride), weight [C,4] bf16, pos_in_seq [T] = position of each token inside its sequence (None: one sequence)."""
+def depthwise_causal_conv4_prefill(x: torch.Tensor, weight: torch.Tensor,
+                                   seq_start: torch.Tensor | None = None) -> torch.Tensor:
+    """y[t,c] = silu(sum_{r=0..3} w[c,r] x[t+r-3,c]) over a packed buffer; taps that would reach before seq_start[t]
+    (the first token of t's own sequence) read zero (triton_kernels/depthwise_causal_conv4_prefill.py:18-91, :108-123).
+    x [T,C] bf16 (any row stride), weight [C,4] bf16, seq_start [T] int32 or None (one sequence starting at 0)."""
     total = x.shape[0]
-    if pos_in_seq is None:
-        pos_in_seq = torch.arange(total, device=x.device)
+    pos_in_seq = torch.arange(total, device=x.device)
+    if seq_start is not None:
+        pos_in_seq = pos_in_seq - seq_start.to(pos_in_seq.dtype)
     xf = x.float()
     wf = weight.float()
     acc = xf * wf[:, 3]

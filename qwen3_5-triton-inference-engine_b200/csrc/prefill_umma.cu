@@ -21,6 +21,31 @@
 
 namespace b200 {
 
+#ifdef B200_PU_TRACE
+// debug build only: per-stage clock sums of the softmax loop of CTA 0, warp 0
+__device__ long long g_pu_trace[16];
+#define PU_TRACE(i)                                                                              \
+  do {                                                                                           \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {             \
+      const long long now_ = clock64();                                                          \
+      if ((i) > 0) atomicAdd(reinterpret_cast<unsigned long long*>(&g_pu_trace[(i)]), static_cast<unsigned long long>(now_ - pu_last_)); \
+      else atomicAdd(reinterpret_cast<unsigned long long*>(&g_pu_trace[6]), 1ull);               \
+      if ((i) == 0 && pu_last_ != 0) atomicAdd(reinterpret_cast<unsigned long long*>(&g_pu_trace[0]), static_cast<unsigned long long>(now_ - pu_last_)); \
+      pu_last_ = now_;                                                                           \
+    }                                                                                            \
+  } while (0)
+#define PU_TRACE_T0() const long long put0_ = clock64()
+#define PU_TRACE_ADD(i)                                                                          \
+  do {                                                                                           \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0)        \
+      atomicAdd(reinterpret_cast<unsigned long long*>(&g_pu_trace[(i)]), static_cast<unsigned long long>(clock64() - put0_)); \
+  } while (0)
+#else
+#define PU_TRACE(i)
+#define PU_TRACE_T0()
+#define PU_TRACE_ADD(i)
+#endif
+
 constexpr int PU_BQ = 32;
 constexpr int PU_TKV = 64;
 constexpr int PU_THREADS = 192;
@@ -172,39 +197,62 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     }
   } else if (warp == 4) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    {
+      // the whole warp walks the loop (uniform control flow keeps the descriptors in uniform registers); lane 0 issues
+      const bool leader = lane == 0;
       const uint32_t idesc_s = idesc_bf16_f32(128, PU_TKV, false, false);
       const uint32_t idesc_o = idesc_bf16_f32(128, HEAD_DIM, false, true);
       const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
       bool ok = FUSED ? mbar_wait_bounded(&bar_qr, 0) : mbar_wait_bounded(&bar_q, 0);
       auto issue_pv = [&](int jj) {
         const int s = jj & 1;
-        ok = ok && mbar_wait_bounded(&bar_p[s], (jj >> 1) & 1);
-        ok = ok && mbar_wait_bounded(&bar_v[s], (jj >> 1) & 1);
+        {
+          PU_TRACE_T0();
+          ok = ok && mbar_wait_bounded(&bar_p[s], (jj >> 1) & 1);
+          PU_TRACE_ADD(9);
+        }
+        {
+          PU_TRACE_T0();
+          ok = ok && mbar_wait_bounded(&bar_v[s], (jj >> 1) & 1);
+          PU_TRACE_ADD(10);
+        }
         if (!ok) return;
         tc_fence_after_sync();
         const uint32_t v_addr = smem_u32(v_s + s * PU_KV_BYTES);
+        {
+          PU_TRACE_T0();
 #pragma unroll
-        for (int kt = 0; kt < PU_TKV / 16; ++kt)
-          umma_ss(tmem_o, smem_desc_sw128(p_addr + s * PU_P_BYTES + kt * 32, 16, 1024),
-                  smem_desc_sw128(v_addr + kt * 2048, PU_TKV * 128, 1024), idesc_o, (jj > 0) || (kt > 0));
-        umma_commit(&bar_pv[s]);
+          for (int kt = 0; kt < PU_TKV / 16; ++kt)
+            umma_ss_leader(tmem_o, smem_desc_sw128(p_addr + s * PU_P_BYTES + kt * 32, 16, 1024),
+                           smem_desc_sw128(v_addr + kt * 2048, PU_TKV * 128, 1024), idesc_o, (jj > 0) || (kt > 0), leader);
+          umma_commit_leader(&bar_pv[s], leader);
+          PU_TRACE_ADD(12);
+        }
       };
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j & 1;
-        ok = mbar_wait_bounded(&bar_k[s], (j >> 1) & 1);
+        {
+          PU_TRACE_T0();
+          ok = mbar_wait_bounded(&bar_k[s], (j >> 1) & 1);
+          PU_TRACE_ADD(8);
+        }
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t k_addr = smem_u32(k_s + s * PU_KV_BYTES);
+        {
+          PU_TRACE_T0();
 #pragma unroll
-        for (int ks = 0; ks < HEAD_DIM / 16; ++ks)
-          umma_ss(tmem + s * PU_TKV, smem_desc_sw128(q_addr + (ks >> 2) * (128 * 128) + (ks & 3) * 32, 16, 1024),
-                  smem_desc_sw128(k_addr + (ks >> 2) * (PU_TKV * 128) + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
-        umma_commit(&bar_s[s]);
+          for (int ks = 0; ks < HEAD_DIM / 16; ++ks)
+            umma_ss_leader(tmem + s * PU_TKV, smem_desc_sw128(q_addr + (ks >> 2) * (128 * 128) + (ks & 3) * 32, 16, 1024),
+                           smem_desc_sw128(k_addr + (ks >> 2) * (PU_TKV * 128) + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0,
+                           leader);
+          umma_commit_leader(&bar_s[s], leader);
+          PU_TRACE_ADD(11);
+        }
         if (j >= 1) issue_pv(j - 1);
       }
       if (ok) issue_pv(n_tiles - 1);
-      if (!ok) atomicExch(p.err, 1);
+      if (!ok && leader) atomicExch(p.err, 1);
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue, thread = row
@@ -250,15 +298,21 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
       fence_proxy_async();  // the rotated rows must be visible to the tensor core's reads
       mbar_arrive(&bar_qr);
     }
+#ifdef B200_PU_TRACE
+    long long pu_last_ = 0;
+#endif
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int s = j & 1;
+      PU_TRACE(0);
       ok = mbar_wait_bounded(&bar_s[s], (j >> 1) & 1);
       if (!ok) break;
       tc_fence_after_sync();
+      PU_TRACE(1);
       uint32_t r0[32], r1[32];
       tmem_ld32(tmem + lane_base + s * PU_TKV, r0);
       tmem_ld32(tmem + lane_base + s * PU_TKV + 32, r1);
       tmem_ld_wait();
+      PU_TRACE(2);
       // mask (causal and inside the sequence; only tiles on the diagonal or at the sequence end need it) and take
       // the row maximum of the raw scores; the scale (> 0) is folded into the exponent below
       const int lim = min(q_tok, seq_len - 1) - j * PU_TKV;  // last valid column of this tile for this row
@@ -308,6 +362,7 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
           if (!ok) break;
         }
       }
+      PU_TRACE(3);
       // p = 2^(s*scale - m_ref): fp32 for l, bf16 for the PV product, written as row `row` of the swizzled P tile
       float sum0 = 0.f, sum1 = 0.f;
       const float neg_m = -m_ref, sc = p.scale_log2;
@@ -328,9 +383,11 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
       }
       const float sum = sum0 + sum1;
       l_run += sum;
+      PU_TRACE(4);
       fence_proxy_async();      // generic-proxy stores to P before the tensor core (async proxy) reads them
       tc_fence_before_sync();   // this thread's TMEM loads/stores before the arrive
       mbar_arrive(&bar_p[s]);
+      PU_TRACE(5);
     }
     // ---- epilogue: O / l -> bf16 -> staged in shared memory (Q and P are dead) -> coalesced global stores
     if (ok) ok = mbar_wait_bounded(&bar_pv[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
@@ -403,6 +460,17 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
 }  // namespace b200
 
 using namespace b200;
+
+#ifdef B200_PU_TRACE
+extern "C" int b200_pu_trace_read(long long* host8, int reset) {
+  if (cudaMemcpyFromSymbol(host8, g_pu_trace, sizeof(long long) * 16) != cudaSuccess) return 3;
+  if (reset) {
+    long long z[16] = {0};
+    cudaMemcpyToSymbol(g_pu_trace, z, sizeof(z));
+  }
+  return 0;
+}
+#endif
 
 static bool mult8(int64_t x) { return (x & 7) == 0; }
 

@@ -80,6 +80,25 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                : "memory");
 }
 
+// Warp-uniform forms: the WHOLE warp runs the surrounding code (so that the compiler can keep descriptors and loop
+// state in uniform registers instead of converting them per instruction) and only the lane with `leader` set issues.
+__device__ __forceinline__ void umma_ss_leader(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               bool accumulate, bool leader) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate)),
+        "r"(static_cast<uint32_t>(leader))
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_leader(uint64_t* bar, bool leader) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+      ::"r"(smem_u32(bar)), "r"(static_cast<uint32_t>(leader))
+      : "memory");
+}
+
 // 32 consecutive fp32 columns of this thread's TMEM lane (lane = 32 * (warp % 4) + laneid must be encoded in taddr).
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(

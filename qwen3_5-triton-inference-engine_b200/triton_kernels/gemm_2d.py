@@ -1,0 +1,3 @@
+"""Same module and symbol names as the reference's triton_kernels/gemm_2d.py; the operators here are the plain
+PyTorch restatements of b200attn/glue.py (these operators are outside the attention / Gated-DeltaNet path)."""
+from b200attn.glue import gemm_2d  # noqa: F401

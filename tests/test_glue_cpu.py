@@ -31,8 +31,8 @@ def test_packed_conv_matches_per_sequence():
     lengths, chans = [1, 2, 3, 4, 9, 17], 48
     x = torch.randn(sum(lengths), chans, generator=gen).to(torch.bfloat16)
     w = (torch.randn(chans, 4, generator=gen) * 0.5).to(torch.bfloat16)
-    pos = torch.cat([torch.arange(n) for n in lengths])
-    got = glue.depthwise_causal_conv4_prefill(x, w, pos)
+    starts = torch.cat([torch.full((n,), sum(lengths[:i]), dtype=torch.int32) for i, n in enumerate(lengths)])
+    got = glue.depthwise_causal_conv4_prefill(x, w, starts)
     off = 0
     for n in lengths:
         assert torch.equal(got[off: off + n], _conv_one(x[off: off + n], w))
@@ -70,5 +70,7 @@ def test_norms_and_gates_shapes():
     assert torch.allclose(q_n.float().pow(2).sum(-1), torch.full((3, 16), 1 / 128), atol=2e-4)
     y = glue.qwen_rmsnorm(x, torch.zeros(128, dtype=torch.bfloat16), 1e-6)
     assert torch.allclose(y.float().pow(2).mean(-1), torch.ones(3, 16), atol=2e-2)
-    ids = glue.lm_head_argmax(torch.eye(4, dtype=torch.bfloat16), torch.eye(4, dtype=torch.bfloat16).repeat(2, 1))
+    table = torch.eye(4, dtype=torch.bfloat16).repeat(2, 1)
+    ids = glue.lm_head_argmax(torch.eye(4, dtype=torch.bfloat16), table, last_only=False)
     assert ids.tolist() == [0, 1, 2, 3]      # ties go to the lowest index
+    assert int(glue.lm_head_argmax(torch.eye(4, dtype=torch.bfloat16), table)) == 3
