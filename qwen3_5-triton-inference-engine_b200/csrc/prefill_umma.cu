@@ -5,14 +5,18 @@
 //
 // One CTA = one (sequence, kv head, block of 32 query tokens).  The 4 Q heads of the group are stacked into the 128
 // rows of one MMA tile (row = token*4 + head, the stacking idea of gqa_attention_varlen_causal.py:151-160), so every
-// K/V tile is fetched once per group.  Per 64-token KV tile:
-//     S[128 x 64]   = Q[128 x 256] . K^T          tcgen05.mma, both operands K-major in shared memory, D in TMEM
-//     P = exp2(S*scale*log2e - m)                  one softmax thread per row, straight out of TMEM
-//     O[128 x 256] += P[128 x 64] . V[64 x 256]    tcgen05.mma, V as an MN-major operand, O stays in TMEM
-// Roles: warps 0-3 softmax/epilogue (thread = row = TMEM lane), warp 4 issues the MMAs, warp 5 the TMA loads
-// (Q once, K/V double-buffered, 32 KiB per copy, 128-byte swizzle, no multicast).  S is double-buffered in TMEM so
-// that S of tile j+1 is computed while tile j is in the softmax.  O is rescaled in TMEM only when a row maximum
-// grows by more than 2^8 (the running reference maximum may lag; p then stays <= 256, exact for bf16 and fp32 l).
+// K/V tile is fetched once per group.  Per 128-token KV tile:
+//     S[128 x 128]  = Q[128 x 256] . K^T          tcgen05.mma, both operands K-major in shared memory, D in TMEM
+//     P = exp2(S*scale*log2e - m)                  two softmax threads per row (64 columns each), straight out of TMEM
+//     O[128 x 256] += P[128 x 128] . V[128 x 256]  tcgen05.mma, V as an MN-major operand, O stays in TMEM
+// The tile is 128 tokens wide because a tcgen05.mma with M=128 costs at least ~64 cycles whatever its N (measured:
+// N=64 and N=128 both ~69 cycles per instruction, N=256 128 cycles), so N=64 score tiles ran the tensor pipe at half
+// rate.  Roles: warps 0-7 softmax/epilogue (TMEM lane quarter = warp % 4, column half = warp / 4), warp 8 issues the
+// MMAs (the whole warp walks the loop, lane 0 issues), warps 9 and 10 issue the K and V TMA loads (64 KiB per tile,
+// 128-byte swizzle, no multicast; two independent chains so that K of tile j+1 is requested the moment S of tile j
+// is done).  S is double-buffered in TMEM (2 x 128 columns + 256 for O = all 512); Q, K, V and P are single-buffered
+// in the 224 KiB of shared memory.  O is rescaled in TMEM only when a row maximum grows by more than 2^8 (the
+// running reference maximum may lag; p then stays <= 256, exact for bf16 and fp32 l).
 // The reference's rounding points are kept where they matter for the 2e-2 bar: p is rounded to bf16 for the PV
 // product while l sums the fp32 p; scores are scaled in fp32 (the reference pre-scales q and re-rounds it to bf16).
 // Every mbarrier wait is bounded; on expiry the role sets the device error flag and the CTA drains and exits.
@@ -21,41 +25,19 @@
 
 namespace b200 {
 
-#ifdef B200_PU_TRACE
-// debug build only: per-stage clock sums of the softmax loop of CTA 0, warp 0
-__device__ long long g_pu_trace[16];
-#define PU_TRACE(i)                                                                              \
-  do {                                                                                           \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) {             \
-      const long long now_ = clock64();                                                          \
-      if ((i) > 0) atomicAdd(reinterpret_cast<unsigned long long*>(&g_pu_trace[(i)]), static_cast<unsigned long long>(now_ - pu_last_)); \
-      else atomicAdd(reinterpret_cast<unsigned long long*>(&g_pu_trace[6]), 1ull);               \
-      if ((i) == 0 && pu_last_ != 0) atomicAdd(reinterpret_cast<unsigned long long*>(&g_pu_trace[0]), static_cast<unsigned long long>(now_ - pu_last_)); \
-      pu_last_ = now_;                                                                           \
-    }                                                                                            \
-  } while (0)
-#define PU_TRACE_T0() const long long put0_ = clock64()
-#define PU_TRACE_ADD(i)                                                                          \
-  do {                                                                                           \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0)        \
-      atomicAdd(reinterpret_cast<unsigned long long*>(&g_pu_trace[(i)]), static_cast<unsigned long long>(clock64() - put0_)); \
-  } while (0)
-#else
-#define PU_TRACE(i)
-#define PU_TRACE_T0()
-#define PU_TRACE_ADD(i)
-#endif
-
 constexpr int PU_BQ = 32;
-constexpr int PU_TKV = 64;
-constexpr int PU_THREADS = 192;
+constexpr int PU_TKV = 128;
+constexpr int PU_SOFTMAX_THREADS = 256;
+constexpr int PU_THREADS = 352;                     // 8 softmax warps + MMA issuer + K producer + V producer
 constexpr int PU_Q_BYTES = 128 * HEAD_DIM * 2;      // 64 KiB: 4 column blocks of [128 rows][64]
-constexpr int PU_P_BYTES = 128 * PU_TKV * 2;        // 16 KiB: [128 rows][64]
-constexpr int PU_KV_BYTES = PU_TKV * HEAD_DIM * 2;  // 32 KiB: 4 column blocks of [64 rows][64]
-constexpr int PU_SMEM = PU_Q_BYTES + 2 * PU_P_BYTES + 4 * PU_KV_BYTES + 1024;
+constexpr int PU_P_BYTES = 128 * PU_TKV * 2;        // 32 KiB: 2 column blocks of [128 rows][64]
+constexpr int PU_KV_BYTES = PU_TKV * HEAD_DIM * 2;  // 64 KiB: 4 column blocks of [128 rows][64]
+// Q + P + K + V fill 224 KiB; the static part (barriers, exchange arrays) is padded to 3 KiB by the 1024-byte
+// alignment of the dynamic part, which makes the 227 KiB block limit exactly.  No alignment slack: the kernel checks.
+constexpr int PU_SMEM = PU_Q_BYTES + PU_P_BYTES + 2 * PU_KV_BYTES;
 constexpr int PU_OUT_PITCH = HEAD_DIM * 2 + 16;     // staging pitch of the epilogue (bytes)
-static_assert(128 * PU_OUT_PITCH <= PU_Q_BYTES + 2 * PU_P_BYTES, "output staging must fit in the Q + P region");
-constexpr uint32_t PU_TMEM_COLS = 512;              // S0 [0,64) S1 [64,128) O [128,384)
+static_assert(128 * PU_OUT_PITCH <= PU_Q_BYTES + PU_P_BYTES, "output staging must fit in the Q + P region");
+constexpr uint32_t PU_TMEM_COLS = 512;              // S0 [0,128) S1 [128,256) O [256,512)
 constexpr float PU_TAU = 8.0f;                      // lazy-rescale threshold (log2 domain)
 constexpr float PU_LOG2E = 1.4426950408889634f;
 
@@ -138,8 +120,10 @@ __global__ void __launch_bounds__(PU_THREADS, 1)
 varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                           const __grid_constant__ CUtensorMap map_v, const __grid_constant__ PrefillUmmaParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ uint64_t bar_q, bar_qr, bar_k[2], bar_v[2], bar_s[2], bar_p[2], bar_pv[2];
+  __shared__ uint64_t bar_q, bar_qr, bar_k, bar_v, bar_s[2], bar_p, bar_pv;
   __shared__ uint32_t tmem_slot;
+  __shared__ float xm[2][2][128];  // [tile parity][column half][row]: row maxima (at the end: row sums) exchanged
+                                   // between the two threads of a row
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int qb = gridDim.x - 1 - blockIdx.x;  // heaviest blocks first
@@ -151,125 +135,114 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
   const int kv_end = min(q0 + PU_BQ, seq_len);
   const int n_tiles = (kv_end + PU_TKV - 1) / PU_TKV;
 
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem) & 1023u) != 0) {  // swizzled tiles need 1024-byte alignment; never taken with __align__(1024)
+    if (tid == 0) atomicExch(p.err, 1);
+    return;
+  }
   uint8_t* q_s = smem;
   uint8_t* p_s = smem + PU_Q_BYTES;
-  uint8_t* k_s = p_s + 2 * PU_P_BYTES;  // two stages (P is double-buffered too)
-  uint8_t* v_s = k_s + 2 * PU_KV_BYTES;  // two stages
+  uint8_t* k_s = p_s + PU_P_BYTES;
+  uint8_t* v_s = k_s + PU_KV_BYTES;
 
   if (warp == 0) tmem_alloc(&tmem_slot, PU_TMEM_COLS);
   if (tid == 0) {
     mbar_init(&bar_q, 1);
     mbar_init(&bar_qr, 128);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&bar_k[i], 1);
-      mbar_init(&bar_v[i], 1);
-      mbar_init(&bar_s[i], 1);
-      mbar_init(&bar_p[i], 128);
-      mbar_init(&bar_pv[i], 1);
-    }
+    mbar_init(&bar_k, 1);
+    mbar_init(&bar_v, 1);
+    mbar_init(&bar_s[0], 1);
+    mbar_init(&bar_s[1], 1);
+    mbar_init(&bar_p, PU_SOFTMAX_THREADS);
+    mbar_init(&bar_pv, 1);
     mbar_fence_init();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
-  const uint32_t tmem_o = tmem + 128;
+  const uint32_t tmem_o = tmem + 2 * PU_TKV;
 
-  if (warp == 5) {
-    // ------------------------------------------------------------------ TMA producer
+  if (warp == 9) {
+    // ------------------------------------------------------------------ TMA producer: Q once, then the K tiles
     if (lane == 0) {
       bool ok = true;
       mbar_expect_tx(&bar_q, PU_Q_BYTES);
       tma_load_5d(q_s, &map_q, 0, 0, h, seq_start + q0, 0, &bar_q);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j & 1, u = j >> 1;
-        if (j >= 2) ok = mbar_wait_bounded(&bar_s[s], (u - 1) & 1);  // S of tile j-2 done: K stage free
+        if (j >= 1) ok = mbar_wait_bounded(&bar_s[(j - 1) & 1], ((j - 1) >> 1) & 1);  // S of tile j-1 done: K free
         if (!ok) break;
-        mbar_expect_tx(&bar_k[s], PU_KV_BYTES);
-        tma_load_4d(k_s + s * PU_KV_BYTES, &map_k, 0, seq_start + j * PU_TKV, 0, h, &bar_k[s]);
-        if (j >= 2) ok = mbar_wait_bounded(&bar_pv[s], (u - 1) & 1);  // PV of tile j-2 done: V stage free
-        if (!ok) break;
-        mbar_expect_tx(&bar_v[s], PU_KV_BYTES);
-        tma_load_4d(v_s + s * PU_KV_BYTES, &map_v, 0, seq_start + j * PU_TKV, 0, h, &bar_v[s]);
+        mbar_expect_tx(&bar_k, PU_KV_BYTES);
+        tma_load_4d(k_s, &map_k, 0, seq_start + j * PU_TKV, 0, h, &bar_k);
       }
       if (!ok) atomicExch(p.err, 1);
     }
-  } else if (warp == 4) {
+  } else if (warp == 10) {
+    // ------------------------------------------------------------------ TMA producer: the V tiles
+    if (lane == 0) {
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j >= 1) ok = mbar_wait_bounded(&bar_pv, (j - 1) & 1);  // PV of tile j-1 done: V free
+        if (!ok) break;
+        mbar_expect_tx(&bar_v, PU_KV_BYTES);
+        tma_load_4d(v_s, &map_v, 0, seq_start + j * PU_TKV, 0, h, &bar_v);
+      }
+      if (!ok) atomicExch(p.err, 1);
+    }
+  } else if (warp == 8) {
     // ------------------------------------------------------------------ MMA issuer
     {
-      // the whole warp walks the loop (uniform control flow keeps the descriptors in uniform registers); lane 0 issues
+      // the whole warp walks the loop (uniform control flow), lane 0 issues
       const bool leader = lane == 0;
       const uint32_t idesc_s = idesc_bf16_f32(128, PU_TKV, false, false);
       const uint32_t idesc_o = idesc_bf16_f32(128, HEAD_DIM, false, true);
-      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
       bool ok = FUSED ? mbar_wait_bounded(&bar_qr, 0) : mbar_wait_bounded(&bar_q, 0);
       auto issue_pv = [&](int jj) {
-        const int s = jj & 1;
-        {
-          PU_TRACE_T0();
-          ok = ok && mbar_wait_bounded(&bar_p[s], (jj >> 1) & 1);
-          PU_TRACE_ADD(9);
-        }
-        {
-          PU_TRACE_T0();
-          ok = ok && mbar_wait_bounded(&bar_v[s], (jj >> 1) & 1);
-          PU_TRACE_ADD(10);
-        }
+        ok = ok && mbar_wait_bounded(&bar_p, jj & 1);
+        ok = ok && mbar_wait_bounded(&bar_v, jj & 1);
         if (!ok) return;
         tc_fence_after_sync();
-        const uint32_t v_addr = smem_u32(v_s + s * PU_KV_BYTES);
-        {
-          PU_TRACE_T0();
 #pragma unroll
-          for (int kt = 0; kt < PU_TKV / 16; ++kt)
-            umma_ss_leader(tmem_o, smem_desc_sw128(p_addr + s * PU_P_BYTES + kt * 32, 16, 1024),
-                           smem_desc_sw128(v_addr + kt * 2048, PU_TKV * 128, 1024), idesc_o, (jj > 0) || (kt > 0), leader);
-          umma_commit_leader(&bar_pv[s], leader);
-          PU_TRACE_ADD(12);
-        }
+        for (int kt = 0; kt < PU_TKV / 16; ++kt)
+          umma_ss_leader(tmem_o, smem_desc_sw128(p_addr + (kt >> 2) * (128 * 128) + (kt & 3) * 32, 16, 1024),
+                         smem_desc_sw128(v_addr + kt * 2048, PU_TKV * 128, 1024), idesc_o, (jj > 0) || (kt > 0), leader);
+        umma_commit_leader(&bar_pv, leader);
       };
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j & 1;
-        {
-          PU_TRACE_T0();
-          ok = mbar_wait_bounded(&bar_k[s], (j >> 1) & 1);
-          PU_TRACE_ADD(8);
-        }
+        ok = mbar_wait_bounded(&bar_k, j & 1);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t k_addr = smem_u32(k_s + s * PU_KV_BYTES);
-        {
-          PU_TRACE_T0();
 #pragma unroll
-          for (int ks = 0; ks < HEAD_DIM / 16; ++ks)
-            umma_ss_leader(tmem + s * PU_TKV, smem_desc_sw128(q_addr + (ks >> 2) * (128 * 128) + (ks & 3) * 32, 16, 1024),
-                           smem_desc_sw128(k_addr + (ks >> 2) * (PU_TKV * 128) + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0,
-                           leader);
-          umma_commit_leader(&bar_s[s], leader);
-          PU_TRACE_ADD(11);
+        for (int ks = 0; ks < HEAD_DIM / 16; ++ks) {
+          const uint32_t o = (ks >> 2) * (128 * 128) + (ks & 3) * 32;
+          umma_ss_leader(tmem + s * PU_TKV, smem_desc_sw128(q_addr + o, 16, 1024), smem_desc_sw128(k_addr + o, 16, 1024),
+                         idesc_s, ks > 0, leader);
         }
+        umma_commit_leader(&bar_s[s], leader);
         if (j >= 1) issue_pv(j - 1);
       }
       if (ok) issue_pv(n_tiles - 1);
       if (!ok && leader) atomicExch(p.err, 1);
     }
   } else {
-    // ------------------------------------------------------------------ softmax + epilogue, thread = row
-    const int row = tid;                       // TMEM lane; row = token*4 + head
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int row = 32 * (warp & 3) + lane;    // TMEM lane; row = token*4 + head
+    const int half = warp >> 2;                // this thread's 64 of the tile's 128 columns
     const int q_tok = q0 + (row >> 2);
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_base = static_cast<uint32_t>(32 * (warp & 3)) << 16;
+    const int pair_bar = 1 + (warp & 3);       // named barrier of the two warps that share these rows
     float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
-    if (FUSED) {
-      // rotate this thread's Q row in place (dims j and j+32, j < 32, all inside column block 0 of the swizzled
-      // tile).  The 32 angles of a token are shared by its 4 heads = 4 adjacent lanes: each computes 8 of them.
-      const int tok = min(q_tok, seq_len - 1);
-      const int64_t t = seq_start + tok;
+    if (FUSED && half == 0) {
+      // rotary embedding of this row's q in place (dims [0,32) and [32,64) live in column block 0, chunks c, c+4)
+      const int64_t t = seq_start + min(q_tok, seq_len - 1);
       const int64_t pid = p.ids_are_int64 ? static_cast<const int64_t*>(p.position_ids)[t]
                                           : static_cast<int64_t>(static_cast<const int32_t*>(p.position_ids)[t]);
       const float posf = static_cast<float>(pid);
-      float cs[8], sn[8];
+      // the four rows of a token share their angles: each lane of a quad computes 8 of the 32 (sin, cos) pairs
+      float sn[8], cs[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) sincosf(posf * p.inv_freq[(lane & 3) * 8 + i], &sn[i], &cs[i]);
       ok = mbar_wait_bounded(&bar_q, 0);
@@ -298,107 +271,104 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
       fence_proxy_async();  // the rotated rows must be visible to the tensor core's reads
       mbar_arrive(&bar_qr);
     }
-#ifdef B200_PU_TRACE
-    long long pu_last_ = 0;
-#endif
-    for (int j = 0; j < n_tiles && ok; ++j) {
+    // A failed (timed-out) wait clears `ok`; the loop then keeps only its barriers and arrivals, so that the partner
+    // warp and the MMA issuer are never left waiting for this thread.
+    for (int j = 0; j < n_tiles; ++j) {
       const int s = j & 1;
-      PU_TRACE(0);
-      ok = mbar_wait_bounded(&bar_s[s], (j >> 1) & 1);
-      if (!ok) break;
-      tc_fence_after_sync();
-      PU_TRACE(1);
+      if (ok) ok = mbar_wait_bounded(&bar_s[s], (j >> 1) & 1);
       uint32_t r0[32], r1[32];
-      tmem_ld32(tmem + lane_base + s * PU_TKV, r0);
-      tmem_ld32(tmem + lane_base + s * PU_TKV + 32, r1);
-      tmem_ld_wait();
-      PU_TRACE(2);
-      // mask (causal and inside the sequence; only tiles on the diagonal or at the sequence end need it) and take
-      // the row maximum of the raw scores; the scale (> 0) is folded into the exponent below
-      const int lim = min(q_tok, seq_len - 1) - j * PU_TKV;  // last valid column of this tile for this row
-      if (lim < PU_TKV - 1) {
+      float m_half = 0.f;
+      if (ok) {
+        tc_fence_after_sync();
+        tmem_ld32(tmem + lane_base + s * PU_TKV + half * 64, r0);
+        tmem_ld32(tmem + lane_base + s * PU_TKV + half * 64 + 32, r1);
+        tmem_ld_wait();
+        // mask (causal and inside the sequence; only tiles on the diagonal or at the sequence end need it) and take
+        // the row maximum of the raw scores; the scale (> 0) is folded into the exponent below
+        const int lim = min(q_tok, seq_len - 1) - j * PU_TKV - half * 64;  // last valid column of this half
+        if (lim < 63) {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          if (c > lim) r0[c] = 0xff800000u;       // -inf
-          if (c + 32 > lim) r1[c] = 0xff800000u;
-        }
-      }
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        mx0 = fmaxf(mx0, __uint_as_float(r0[c]));
-        mx1 = fmaxf(mx1, __uint_as_float(r0[c + 1]));
-        mx2 = fmaxf(mx2, __uint_as_float(r1[c]));
-        mx3 = fmaxf(mx3, __uint_as_float(r1[c + 1]));
-      }
-      const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
-      const float m_new = fmaxf(m_ref, m_tile);
-      if (j == 0) {
-        m_ref = m_new;
-      } else {
-        const bool need = (m_new - m_ref) > PU_TAU;
-        if (__any_sync(0xffffffffu, need)) {
-          // O must be at rest before it is rescaled: wait for the PV product of tile j-1
-          ok = mbar_wait_bounded(&bar_pv[(j - 1) & 1], ((j - 1) >> 1) & 1);
-          if (!ok) break;
-          tc_fence_after_sync();
-          const float alpha = need ? ex2_fast(m_ref - m_new) : 1.f;
-#pragma unroll 1
-          for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
-            uint32_t o[32];
-            tmem_ld32(tmem_o + lane_base + c0, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-            tmem_st32(tmem_o + lane_base + c0, o);
+          for (int c = 0; c < 32; ++c) {
+            if (c > lim) r0[c] = 0xff800000u;       // -inf
+            if (c + 32 > lim) r1[c] = 0xff800000u;
           }
-          tmem_st_wait();
-          l_run *= alpha;
-          if (need) m_ref = m_new;
         }
-        if (j >= 2) {
-          // this tile's P buffer was last read by the PV product of tile j-2
-          ok = mbar_wait_bounded(&bar_pv[s], ((j - 2) >> 1) & 1);
-          if (!ok) break;
-        }
-      }
-      PU_TRACE(3);
-      // p = 2^(s*scale - m_ref): fp32 for l, bf16 for the PV product, written as row `row` of the swizzled P tile
-      float sum0 = 0.f, sum1 = 0.f;
-      const float neg_m = -m_ref, sc = p.scale_log2;
-      uint8_t* prow = p_s + s * PU_P_BYTES + row * 128;
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) {
-        uint32_t w[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const int c = ch * 8 + k * 2;
-          const float x0 = ex2_fast(fmaf(__uint_as_float(c < 32 ? r0[c] : r1[c - 32]), sc, neg_m));
-          const float x1 = ex2_fast(fmaf(__uint_as_float(c + 1 < 32 ? r0[c + 1] : r1[c + 1 - 32]), sc, neg_m));
-          sum0 += x0;
-          sum1 += x1;
-          w[k] = pack_bf16(x0, x1);
+        for (int c = 0; c < 32; c += 2) {
+          mx0 = fmaxf(mx0, __uint_as_float(r0[c]));
+          mx1 = fmaxf(mx1, __uint_as_float(r0[c + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(r1[c]));
+          mx3 = fmaxf(mx3, __uint_as_float(r1[c + 1]));
         }
-        *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        m_half = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       }
-      const float sum = sum0 + sum1;
-      l_run += sum;
-      PU_TRACE(4);
+      xm[s][half][row] = m_half;
+      named_barrier(pair_bar, 64);
+      // P is single-buffered and O must be at rest before a rescale: wait for the PV product of tile j-1
+      if (ok && j > 0) ok = mbar_wait_bounded(&bar_pv, (j - 1) & 1);
+      if (ok) {
+        const float m_tile = fmaxf(m_half, xm[s][half ^ 1][row]) * p.scale_log2;
+        const float m_new = fmaxf(m_ref, m_tile);  // both threads of a row compute the same value
+        if (j == 0) {
+          m_ref = m_new;
+        } else {
+          const bool need = (m_new - m_ref) > PU_TAU;
+          if (__any_sync(__activemask(), need)) {
+            tc_fence_after_sync();
+            const float alpha = need ? ex2_fast(m_ref - m_new) : 1.f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < HEAD_DIM / 2; c0 += 32) {  // this thread's 128 columns of O
+              uint32_t o[32];
+              tmem_ld32(tmem_o + lane_base + half * (HEAD_DIM / 2) + c0, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+              tmem_st32(tmem_o + lane_base + half * (HEAD_DIM / 2) + c0, o);
+            }
+            tmem_st_wait();
+            l_run *= alpha;
+            if (need) m_ref = m_new;
+          }
+        }
+        // p = 2^(s*scale - m_ref): fp32 for l, bf16 for the PV product, written as this thread's 128 bytes of row
+        // `row` of the swizzled P tile (column block = half)
+        float sum0 = 0.f, sum1 = 0.f;
+        const float neg_m = -m_ref, sc = p.scale_log2;
+        uint8_t* prow = p_s + half * (128 * 128) + row * 128;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          uint32_t w[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int c = ch * 8 + k * 2;
+            const float x0 = ex2_fast(fmaf(__uint_as_float(c < 32 ? r0[c] : r1[c - 32]), sc, neg_m));
+            const float x1 = ex2_fast(fmaf(__uint_as_float(c + 1 < 32 ? r0[c + 1] : r1[c + 1 - 32]), sc, neg_m));
+            sum0 += x0;
+            sum1 += x1;
+            w[k] = pack_bf16(x0, x1);
+          }
+          *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        l_run += sum0 + sum1;
+      }
       fence_proxy_async();      // generic-proxy stores to P before the tensor core (async proxy) reads them
       tc_fence_before_sync();   // this thread's TMEM loads/stores before the arrive
-      mbar_arrive(&bar_p[s]);
-      PU_TRACE(5);
+      mbar_arrive(&bar_p);
     }
     // ---- epilogue: O / l -> bf16 -> staged in shared memory (Q and P are dead) -> coalesced global stores
-    if (ok) ok = mbar_wait_bounded(&bar_pv[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1);
+    if (ok) ok = mbar_wait_bounded(&bar_pv, (n_tiles - 1) & 1);
+    float* xl = &xm[n_tiles & 1][0][0];  // the parity slot the last tile did not use
+    xl[half * 128 + row] = l_run;
+    named_barrier(pair_bar, 64);
     if (ok) {
       tc_fence_after_sync();
-      const float inv_l = 1.f / l_run;
-      uint8_t* orow = smem + row * PU_OUT_PITCH;
+      const float inv_l = 1.f / (l_run + xl[(half ^ 1) * 128 + row]);
+      uint8_t* orow = smem + row * PU_OUT_PITCH + half * HEAD_DIM;  // this half's 128 columns = 256 bytes
 #pragma unroll 1
-      for (int c0 = 0; c0 < HEAD_DIM; c0 += 32) {
+      for (int c0 = 0; c0 < HEAD_DIM / 2; c0 += 32) {
         uint32_t o[32];
-        tmem_ld32(tmem_o + lane_base + c0, o);
+        tmem_ld32(tmem_o + lane_base + half * (HEAD_DIM / 2) + c0, o);
         tmem_ld_wait();
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -412,18 +382,18 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     } else {
       atomicExch(p.err, 1);
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four softmax warps only
+    named_barrier(9, PU_SOFTMAX_THREADS);  // the eight softmax warps only
     if (ok) {
       // 128 rows x 32 sixteen-byte chunks; a warp covers one 512-byte row per step.  The gate rows are fetched
       // eight steps at a time so that their latency is paid once per batch, not once per chunk.
-      constexpr int STEPS = HEAD_DIM / 8;  // 32 iterations of 128 threads
+      constexpr int STEPS = 128 * (HEAD_DIM / 8) / PU_SOFTMAX_THREADS;  // 16 iterations of 256 threads
 #pragma unroll 1
       for (int i0 = 0; i0 < STEPS; i0 += 8) {
         uint4 gv[8];
         if (FUSED) {
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
-            const int i = (i0 + u) * 128 + tid, r = i >> 5, ch = i & 31;
+            const int i = (i0 + u) * PU_SOFTMAX_THREADS + tid, r = i >> 5, ch = i & 31;
             const int tok = min(q0 + (r >> 2), seq_len - 1);
             gv[u] = *reinterpret_cast<const uint4*>(p.gate + static_cast<int64_t>(seq_start + tok) * p.gate_t +
                                                     (h * GROUP + (r & 3)) * HEAD_DIM + ch * 8);
@@ -431,7 +401,7 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-          const int i = (i0 + u) * 128 + tid, r = i >> 5, ch = i & 31;
+          const int i = (i0 + u) * PU_SOFTMAX_THREADS + tid, r = i >> 5, ch = i & 31;
           const int tok = q0 + (r >> 2);
           if (tok < seq_len) {
             uint4 v = *reinterpret_cast<const uint4*>(smem + r * PU_OUT_PITCH + ch * 16);
@@ -460,17 +430,6 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
 }  // namespace b200
 
 using namespace b200;
-
-#ifdef B200_PU_TRACE
-extern "C" int b200_pu_trace_read(long long* host8, int reset) {
-  if (cudaMemcpyFromSymbol(host8, g_pu_trace, sizeof(long long) * 16) != cudaSuccess) return 3;
-  if (reset) {
-    long long z[16] = {0};
-    cudaMemcpyToSymbol(g_pu_trace, z, sizeof(z));
-  }
-  return 0;
-}
-#endif
 
 static bool mult8(int64_t x) { return (x & 7) == 0; }
 
