@@ -44,7 +44,8 @@ int b200_abi_version(void);
 int b200_wait_timed_out(void);
 
 /* Diagnostic: one CTA multiplies two bf16 tiles loaded by tensor-map TMA with tcgen05.mma (accumulator in tensor
- * memory) and writes fp32 C.  mode 0: C[128x64] = A[128x256] . B[64x256]^T;  mode 1: C[128x256] = A[128x64] . B[64x256].
+ * memory) and writes fp32 C.  mode 0: C[128x64] = A[128x256] . B[64x256]^T;  mode 1: C[128x256] = A[128x64] . B[64x256];
+ * mode 2: as mode 1 with A handed to the MMA through tensor memory instead of shared memory.
  * All matrices row-major and contiguous.  No counterpart in the reference; it validates the sm_100a building blocks
  * the prefill kernels use. */
 int b200_selftest_umma(int32_t mode, const void* a, const void* b, float* c, b200_stream_t stream);

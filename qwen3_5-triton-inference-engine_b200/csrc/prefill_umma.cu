@@ -7,15 +7,16 @@
 // rows of one MMA tile (row = token*4 + head, the stacking idea of gqa_attention_varlen_causal.py:151-160), so every
 // K/V tile is fetched once per group.  Per 128-token KV tile:
 //     S[128 x 128]  = Q[128 x 256] . K^T          tcgen05.mma, both operands K-major in shared memory, D in TMEM
-//     P = exp2(S*scale*log2e - m)                  two softmax threads per row (64 columns each), straight out of TMEM
-//     O[128 x 256] += P[128 x 128] . V[128 x 256]  tcgen05.mma, V as an MN-major operand, O stays in TMEM
+//     P = exp2(S*scale*log2e - m)                  two softmax threads per row (64 columns each), TMEM -> TMEM
+//     O[128 x 256] += P[128 x 128] . V[128 x 256]  tcgen05.mma, P from TMEM, V as an MN-major operand, O stays in TMEM
 // The tile is 128 tokens wide because a tcgen05.mma with M=128 costs at least ~64 cycles whatever its N (measured:
 // N=64 and N=128 both ~69 cycles per instruction, N=256 128 cycles), so N=64 score tiles ran the tensor pipe at half
 // rate.  Roles: warps 0-7 softmax/epilogue (TMEM lane quarter = warp % 4, column half = warp / 4), warp 8 issues the
 // MMAs (the whole warp walks the loop, lane 0 issues), warps 9 and 10 issue the K and V TMA loads (64 KiB per tile,
 // 128-byte swizzle, no multicast; two independent chains so that K of tile j+1 is requested the moment S of tile j
-// is done).  S is double-buffered in TMEM (2 x 128 columns + 256 for O = all 512); Q, K, V and P are single-buffered
-// in the 224 KiB of shared memory.  O is rescaled in TMEM only when a row maximum grows by more than 2^8 (the
+// is done).  S is double-buffered in TMEM (2 x 128 columns + 256 for O = all 512) and P never touches shared memory:
+// the softmax threads store it as packed bf16 over the first 64 columns of the S buffer they just read, and the PV
+// product takes its A operand from tensor memory.  Q, K and V are single-buffered in shared memory.  O is rescaled in TMEM only when a row maximum grows by more than 2^8 (the
 // running reference maximum may lag; p then stays <= 256, exact for bf16 and fp32 l).
 // The reference's rounding points are kept where they matter for the 2e-2 bar: p is rounded to bf16 for the PV
 // product while l sums the fp32 p; scores are scaled in fp32 (the reference pre-scales q and re-rounds it to bf16).
@@ -30,14 +31,11 @@ constexpr int PU_TKV = 128;
 constexpr int PU_SOFTMAX_THREADS = 256;
 constexpr int PU_THREADS = 352;                     // 8 softmax warps + MMA issuer + K producer + V producer
 constexpr int PU_Q_BYTES = 128 * HEAD_DIM * 2;      // 64 KiB: 4 column blocks of [128 rows][64]
-constexpr int PU_P_BYTES = 128 * PU_TKV * 2;        // 32 KiB: 2 column blocks of [128 rows][64]
 constexpr int PU_KV_BYTES = PU_TKV * HEAD_DIM * 2;  // 64 KiB: 4 column blocks of [128 rows][64]
-// Q + P + K + V fill 224 KiB; the static part (barriers, exchange arrays) is padded to 3 KiB by the 1024-byte
-// alignment of the dynamic part, which makes the 227 KiB block limit exactly.  No alignment slack: the kernel checks.
-constexpr int PU_SMEM = PU_Q_BYTES + PU_P_BYTES + 2 * PU_KV_BYTES;
+constexpr int PU_SMEM = PU_Q_BYTES + 2 * PU_KV_BYTES;  // 192 KiB; tiles need 1024-byte alignment: the kernel checks
 constexpr int PU_OUT_PITCH = HEAD_DIM * 2 + 16;     // staging pitch of the epilogue (bytes)
-static_assert(128 * PU_OUT_PITCH <= PU_Q_BYTES + PU_P_BYTES, "output staging must fit in the Q + P region");
-constexpr uint32_t PU_TMEM_COLS = 512;              // S0 [0,128) S1 [128,256) O [256,512)
+static_assert(128 * PU_OUT_PITCH <= PU_Q_BYTES + PU_KV_BYTES, "output staging must fit in the Q + K region");
+constexpr uint32_t PU_TMEM_COLS = 512;              // S0 [0,128) S1 [128,256) (P over their first 64) O [256,512)
 constexpr float PU_TAU = 8.0f;                      // lazy-rescale threshold (log2 domain)
 constexpr float PU_LOG2E = 1.4426950408889634f;
 
@@ -120,7 +118,7 @@ __global__ void __launch_bounds__(PU_THREADS, 1)
 varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                           const __grid_constant__ CUtensorMap map_v, const __grid_constant__ PrefillUmmaParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ uint64_t bar_q, bar_qr, bar_k, bar_v, bar_s[2], bar_p, bar_pv;
+  __shared__ uint64_t bar_q, bar_qr, bar_k, bar_v, bar_s[2], bar_p[2], bar_pv;
   __shared__ uint32_t tmem_slot;
   __shared__ float xm[2][2][128];  // [tile parity][column half][row]: row maxima (at the end: row sums) exchanged
                                    // between the two threads of a row
@@ -141,8 +139,7 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     return;
   }
   uint8_t* q_s = smem;
-  uint8_t* p_s = smem + PU_Q_BYTES;
-  uint8_t* k_s = p_s + PU_P_BYTES;
+  uint8_t* k_s = smem + PU_Q_BYTES;
   uint8_t* v_s = k_s + PU_KV_BYTES;
 
   if (warp == 0) tmem_alloc(&tmem_slot, PU_TMEM_COLS);
@@ -153,7 +150,8 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
     mbar_init(&bar_v, 1);
     mbar_init(&bar_s[0], 1);
     mbar_init(&bar_s[1], 1);
-    mbar_init(&bar_p, PU_SOFTMAX_THREADS);
+    mbar_init(&bar_p[0], PU_SOFTMAX_THREADS);  // one per S/P buffer: a warp may be a tile ahead of another
+    mbar_init(&bar_p[1], PU_SOFTMAX_THREADS);
     mbar_init(&bar_pv, 1);
     mbar_fence_init();
   }
@@ -196,22 +194,25 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
       const bool leader = lane == 0;
       const uint32_t idesc_s = idesc_bf16_f32(128, PU_TKV, false, false);
       const uint32_t idesc_o = idesc_bf16_f32(128, HEAD_DIM, false, true);
-      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
+      const uint32_t q_addr = smem_u32(q_s), k_addr = smem_u32(k_s), v_addr = smem_u32(v_s);
       bool ok = FUSED ? mbar_wait_bounded(&bar_qr, 0) : mbar_wait_bounded(&bar_q, 0);
       auto issue_pv = [&](int jj) {
-        ok = ok && mbar_wait_bounded(&bar_p, jj & 1);
+        ok = ok && mbar_wait_bounded(&bar_p[jj & 1], (jj >> 1) & 1);
         ok = ok && mbar_wait_bounded(&bar_v, jj & 1);
         if (!ok) return;
         tc_fence_after_sync();
 #pragma unroll
         for (int kt = 0; kt < PU_TKV / 16; ++kt)
-          umma_ss_leader(tmem_o, smem_desc_sw128(p_addr + (kt >> 2) * (128 * 128) + (kt & 3) * 32, 16, 1024),
+          umma_ts_leader(tmem_o, tmem + (jj & 1) * PU_TKV + kt * 8,  // P: 16 tokens = 8 packed columns per step
                          smem_desc_sw128(v_addr + kt * 2048, PU_TKV * 128, 1024), idesc_o, (jj > 0) || (kt > 0), leader);
         umma_commit_leader(&bar_pv, leader);
       };
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j & 1;
         ok = mbar_wait_bounded(&bar_k, j & 1);
+        // S(j) overwrites the buffer whose first columns hold P(j-2): the PV product that reads them from tensor
+        // memory must have COMPLETED, issue order alone does not protect an operand in tensor memory
+        if (ok && j >= 2) ok = mbar_wait_bounded(&bar_pv, (j - 2) & 1);
         if (!ok) break;
         tc_fence_after_sync();
 #pragma unroll
@@ -305,8 +306,7 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
       }
       xm[s][half][row] = m_half;
       named_barrier(pair_bar, 64);
-      // P is single-buffered and O must be at rest before a rescale: wait for the PV product of tile j-1
-      if (ok && j > 0) ok = mbar_wait_bounded(&bar_pv, (j - 1) & 1);
+      // after this barrier both threads of the row hold their scores in registers: the S buffer may take P
       if (ok) {
         const float m_tile = fmaxf(m_half, xm[s][half ^ 1][row]) * p.scale_log2;
         const float m_new = fmaxf(m_ref, m_tile);  // both threads of a row compute the same value
@@ -315,6 +315,8 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
         } else {
           const bool need = (m_new - m_ref) > PU_TAU;
           if (__any_sync(__activemask(), need)) {
+            // O must be at rest before it is rescaled: wait for the PV product of tile j-1
+            ok = mbar_wait_bounded(&bar_pv, (j - 1) & 1);
             tc_fence_after_sync();
             const float alpha = need ? ex2_fast(m_ref - m_new) : 1.f;
 #pragma unroll 1
@@ -331,32 +333,30 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
             if (need) m_ref = m_new;
           }
         }
-        // p = 2^(s*scale - m_ref): fp32 for l, bf16 for the PV product, written as this thread's 128 bytes of row
-        // `row` of the swizzled P tile (column block = half)
+        // p = 2^(s*scale - m_ref): fp32 for l, bf16 for the PV product, stored as this thread's 32 packed columns of
+        // the P tile (tokens 2c, 2c+1 in column c) over the S buffer
         float sum0 = 0.f, sum1 = 0.f;
         const float neg_m = -m_ref, sc = p.scale_log2;
-        uint8_t* prow = p_s + half * (128 * 128) + row * 128;
+        uint32_t w[32];
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          uint32_t w[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int c = ch * 8 + k * 2;
-            const float x0 = ex2_fast(fmaf(__uint_as_float(c < 32 ? r0[c] : r1[c - 32]), sc, neg_m));
-            const float x1 = ex2_fast(fmaf(__uint_as_float(c + 1 < 32 ? r0[c + 1] : r1[c + 1 - 32]), sc, neg_m));
-            sum0 += x0;
-            sum1 += x1;
-            w[k] = pack_bf16(x0, x1);
-          }
-          *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int c = 0; c < 32; ++c) {
+          const float x0 = ex2_fast(fmaf(__uint_as_float(c < 16 ? r0[2 * c] : r1[2 * c - 32]), sc, neg_m));
+          const float x1 = ex2_fast(fmaf(__uint_as_float(c < 16 ? r0[2 * c + 1] : r1[2 * c - 31]), sc, neg_m));
+          sum0 += x0;
+          sum1 += x1;
+          w[c] = pack_bf16(x0, x1);
         }
         l_run += sum0 + sum1;
+        tmem_st32(tmem + lane_base + s * PU_TKV + half * 32, w);
+        tmem_st_wait();
       }
-      fence_proxy_async();      // generic-proxy stores to P before the tensor core (async proxy) reads them
       tc_fence_before_sync();   // this thread's TMEM loads/stores before the arrive
-      mbar_arrive(&bar_p);
+      mbar_arrive(&bar_p[s]);
     }
-    // ---- epilogue: O / l -> bf16 -> staged in shared memory (Q and P are dead) -> coalesced global stores
+    // ---- epilogue: O / l -> bf16 -> staged in shared memory (Q and K are dead) -> coalesced global stores
+    // A parity wait only tells the two most recent phases apart, and this thread may not have seen the PV product of
+    // tile n-2 complete yet: wait for it first, then for the last one.
+    if (ok && n_tiles >= 2) ok = mbar_wait_bounded(&bar_pv, (n_tiles - 2) & 1);
     if (ok) ok = mbar_wait_bounded(&bar_pv, (n_tiles - 1) & 1);
     float* xl = &xm[n_tiles & 1][0][0];  // the parity slot the last tile did not use
     xl[half * 128 + row] = l_run;

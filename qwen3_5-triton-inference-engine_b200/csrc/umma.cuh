@@ -91,6 +91,17 @@ __device__ __forceinline__ void umma_ss_leader(uint32_t d_tmem, uint64_t a_desc,
         "r"(static_cast<uint32_t>(leader))
       : "memory");
 }
+// A operand in tensor memory: lane = row, each 32-bit column holds two consecutive K elements (bf16, lower index in
+// the low half), so a K=16 step is 8 columns; B from shared memory as usual.
+__device__ __forceinline__ void umma_ts_leader(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                               bool accumulate, bool leader) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate)),
+        "r"(static_cast<uint32_t>(leader))
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit_leader(uint64_t* bar, bool leader) {
   asm volatile(
       "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t"

@@ -2,6 +2,8 @@
 // (128-byte swizzle), multiplies them with tcgen05.mma into tensor memory and writes the fp32 result back.
 //   mode 0: C[128 x 64]  = A[128 x 256] . B[64 x 256]^T     (B is K-major: the QK^T shape of prefill attention)
 //   mode 1: C[128 x 256] = A[128 x 64]  . B[64 x 256]       (B is MN-major: the P.V shape)
+//   mode 2: the same product with A written to TENSOR MEMORY by the threads (two bf16 per 32-bit column) and used as
+//           the MMA's A operand from there (the form in which prefill attention hands P to the PV product)
 // It exists so that descriptor or layout mistakes show up in a 10-microsecond kernel with a known answer instead
 // of inside the attention kernels; tests/test_gpu_umma.py compares it with torch.matmul.
 #include "b200_attn.h"
@@ -66,7 +68,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   uint8_t* b_s = smem + ST_A_BYTES;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n = mode == 0 ? 64 : 256;
-  constexpr uint32_t TMEM_COLS = 256;
+  constexpr uint32_t TMEM_COLS = 512;  // C in [0,256); mode 2 keeps A in [256,288)
 
   if (warp == 0) tmem_alloc(&tmem_slot, TMEM_COLS);
   if (tid == 0) {
@@ -91,6 +93,19 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     }
   }
   bool ok = mbar_wait_bounded(&bar_tma, 0);
+  if (mode == 2) {
+    // row `tid` of A: 64 bf16 = 32 packed words, read from the swizzled tile and stored to TMEM columns [256, 288)
+    uint32_t w[32];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint4 v = *reinterpret_cast<const uint4*>(a_s + tid * 128 + ((c ^ (tid & 7)) << 4));
+      w[c * 4] = v.x; w[c * 4 + 1] = v.y; w[c * 4 + 2] = v.z; w[c * 4 + 3] = v.w;
+    }
+    tmem_st32(tmem + (static_cast<uint32_t>(warp * 32) << 16) + 256, w);
+    tmem_st_wait();
+    tc_fence_before_sync();
+    __syncthreads();
+  }
   if (ok && tid == 0) {
     tc_fence_after_sync();
     if (mode == 0) {
@@ -101,6 +116,11 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const uint32_t b_addr = smem_u32(b_s) + (ks >> 2) * (64 * 128) + (ks & 3) * 32;
         umma_ss(tmem, smem_desc_sw128(a_addr, 16, 1024), smem_desc_sw128(b_addr, 16, 1024), idesc, ks > 0);
       }
+    } else if (mode == 2) {
+      const uint32_t idesc = idesc_bf16_f32(128, 256, false, true);
+      for (int kt = 0; kt < 4; ++kt)
+        umma_ts_leader(tmem, tmem + 256 + kt * 8, smem_desc_sw128(smem_u32(b_s) + kt * 2048, 64 * 128, 1024), idesc,
+                       kt > 0, true);
     } else {
       // K-major A [128 x 64] and MN-major B [64 (K) x 256 (N)]: 4 steps of K=16 rows of B (2048 bytes apart)
       const uint32_t idesc = idesc_bf16_f32(128, 256, false, true);
@@ -136,7 +156,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
 using namespace b200;
 
 extern "C" int b200_selftest_umma(int32_t mode, const void* a, const void* b, float* c, b200_stream_t stream) {
-  B200_REQUIRE(mode == 0 || mode == 1, "selftest_umma: mode must be 0 or 1");
+  B200_REQUIRE(mode >= 0 && mode <= 2, "selftest_umma: mode must be 0, 1 or 2");
   CUtensorMap map_a, map_b;
   bool ok;
   if (mode == 0) {

@@ -70,7 +70,7 @@ def test_varlen_causal_strided_inputs(ops):
     assert rel_to_max(out, exact) < 2e-2
 
 
-@pytest.mark.parametrize("lengths", [[5], [16, 17, 1], [70, 33, 128, 2], [300, 45]])
+@pytest.mark.parametrize("lengths", [[5], [16, 17, 1], [70, 33, 128, 2], [300, 45], [129, 256, 257], [1100]])
 def test_fused_prefill_vs_oracle(ops, lengths):
     gen = torch.Generator().manual_seed(400 + sum(lengths))
     total, batch = sum(lengths), len(lengths)
