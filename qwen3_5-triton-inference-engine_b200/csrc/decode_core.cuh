@@ -1,9 +1,10 @@
 // Warp-level core of paged GQA decode attention (4 Q heads per KV head, head_dim 256, 16-token pages).
 //
 // One warp owns one stream of KV pages.  A page's K tile and V tile are staged separately in shared memory by
-// the TMA engine (cp.async.bulk, one 512-byte copy per token row so that rows sit at a 528-byte pitch and
-// ldmatrix reads eight rows from eight different bank groups), each completing on its own mbarrier, so the
-// score computation of a page starts as soon as its K rows have landed.  Scores use tokens as the MMA M dimension:
+// the TMA engine, each completing on its own mbarrier, so the score computation of a page starts as soon as its K
+// rows have landed.  Two staging layouts (tile_offset<SW>): one tensor-map box per tile with the 128-byte swizzle
+// (the fused kernel; dense caches), or one 512-byte bulk copy per token row at a 528-byte pitch (the drop-in split
+// kernel; any cache strides); both are conflict-free for ldmatrix.  Scores use tokens as the MMA M dimension:
 //   S^T[16 tok x 8]   = K_page[16 x 256] . Q^T[256 x 8]      (Q heads 4..7 are zero padding)
 //   O^T[256 x 8]     += V_page^T[256 x 16] . P^T[16 x 8]
 // so the 4-head group costs an N=8 tile instead of an M=16 one.  Softmax statistics live in registers; only the
