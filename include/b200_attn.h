@@ -271,6 +271,15 @@ int b200_gdn_chunked_prefill_fused(const void* q, int64_t q_stride_t, int64_t q_
  * b200_gdn_gated_rmsnorm: out[r,:] = x[r,:] * rsqrt(mean(x^2) + 1e-6) * weight * silu(z[r,:]) for rows r = (n, head);
  * x and out contiguous [rows, 128], z row (n, head) at z + n * z_stride + head * 128
  * (triton_kernels/gdn_gated_rmsnorm.py:95-140). */
+/* The whole Gated-DeltaNet mixer of ONE decode token per sequence between its two projections, one launch:
+ * b200_gdn_decode_prep -> b200_gdn_recurrent_decode -> b200_gdn_gated_rmsnorm with nothing written in between.
+ * fused: one row per sequence of the input projection, [q | k | v | z | a | b] = [3*H*128 | H*128 | H | H] bf16, rows
+ * fused_stride elements apart; conv_state [B,4,3*H*128] bf16 and state [B,H,128,128] fp32 are updated in place;
+ * weight4 [4,3*H*128] bf16, a_log [H] fp32, dt_bias [H] bf16, norm_weight [128] fp32; out [B, H*128] bf16 contiguous.
+ * Replaces the operator chain of engine/runner.py:431-441. */
+int b200_gdn_decode_fused(const void* fused, int64_t fused_stride, void* conv_state, const void* weight4,
+                          const float* a_log, const void* dt_bias, const float* norm_weight, float* state, void* out,
+                          int32_t batch, int32_t num_heads, int32_t head_dim, b200_stream_t stream);
 int b200_add_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x_stride_inner, int32_t inner_count,
                      const void* residual, int64_t residual_stride, const void* weight, void* sum_out, void* norm_out,
                      int32_t rows, int32_t dim, float eps, b200_stream_t stream);

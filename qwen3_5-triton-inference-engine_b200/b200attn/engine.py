@@ -225,11 +225,8 @@ class Engine:
                 x, h = ops.add_rmsnorm(pending, layer["ln1"], cfg.eps, residual=x)
             if layer["kind"] == "gdn":
                 fused = glue.gemm_2d(h, layer["in_proj"])
-                q_n, k_n, v, beta, g = ops.gdn_decode_prep(fused[:, : 3 * kd], self.conv_state[i], layer["conv4"],
-                                                           fused[:, 4 * kd: 4 * kd + heads], fused[:, 4 * kd + heads:],
-                                                           layer["a_log"], layer["dt_bias"], heads)
-                core = ops.gdn_recurrent_decode(q_n, k_n, v, beta, g, self.rec_state[i])
-                normed = ops.gdn_gated_rmsnorm_fused(core, fused[:, 3 * kd: 4 * kd], layer["norm"])
+                normed = ops.gdn_decode_fused(fused, self.conv_state[i], layer["conv4"], layer["a_log"], layer["dt_bias"],
+                                              layer["norm"], self.rec_state[i], heads)
                 mixed = glue.gemm_2d(normed, layer["out_proj"])
             else:
                 fused = glue.gemm_2d(h, layer["qkvg"])

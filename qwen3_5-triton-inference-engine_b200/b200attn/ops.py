@@ -663,3 +663,23 @@ def gdn_gated_rmsnorm_fused(x, z, weight):
     _lib.call("b200_gdn_gated_rmsnorm", _ptr(x), _ptr(z), z.stride(0), _ptr(weight), _ptr(out), n * heads, heads, dim,
               _stream())
     return out
+
+
+def gdn_decode_fused(fused, conv_state, weight4, a_log, dt_bias, norm_weight, state, num_heads: int):
+    """The Gated-DeltaNet mixer of one decode token per sequence between its projections in ONE launch: conv + SiLU,
+    q/k norms, gates, delta-rule step and gated RMSNorm (engine/runner.py:431-441).  fused [B, 4*H*128 + 2*H] is the
+    row of the fused input projection ([q|k|v|z|a|b]); conv_state [B,4,3*H*128] and state [B,H,128,128] are updated in
+    place.  Returns the normed mixer output [B, H*128] bf16 (the input of out_proj)."""
+    batch = fused.shape[0]
+    kd = num_heads * GDN_DIM
+    assert fused.shape == (batch, 4 * kd + 2 * num_heads) and fused.stride(1) == 1 and fused.dtype == torch.bfloat16
+    assert conv_state.shape == (batch, 4, 3 * kd) and conv_state.is_contiguous() and conv_state.dtype == torch.bfloat16
+    assert weight4.shape == (4, 3 * kd) and weight4.is_contiguous() and weight4.dtype == torch.bfloat16
+    assert a_log.dtype == torch.float32 and a_log.is_contiguous() and dt_bias.dtype == torch.bfloat16
+    assert norm_weight.dtype == torch.float32 and norm_weight.shape == (GDN_DIM,) and norm_weight.is_contiguous()
+    assert state.shape == (batch, num_heads, GDN_DIM, GDN_DIM) and state.is_contiguous() and state.dtype == torch.float32
+    _require_cuda(fused, conv_state, weight4, a_log, dt_bias, norm_weight, state)
+    out = torch.empty((batch, kd), dtype=torch.bfloat16, device=fused.device)
+    _lib.call("b200_gdn_decode_fused", _ptr(fused), fused.stride(0), _ptr(conv_state), _ptr(weight4), _ptr(a_log),
+              _ptr(dt_bias.contiguous()), _ptr(norm_weight), _ptr(state), _ptr(out), batch, num_heads, GDN_DIM, _stream())
+    return out

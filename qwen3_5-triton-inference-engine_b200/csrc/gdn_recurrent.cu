@@ -76,6 +76,80 @@ gdn_decode_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_b, int64_t q_h,
   for (int i = 0; i < GDN_D; ++i) __stcs(sp + i * GDN_D, s[i]);
 }
 
+// The whole Gated-DeltaNet mixer of one decode token between its two projections, in one launch per layer:
+// conv state shift + depthwise conv4 + SiLU (triton_kernels/depthwise_causal_conv4_decode.py), q/k L2 norms and the
+// beta / g gates (triton_kernels/gdn_qk_norm_gates.py:68-89), the delta-rule step above, and the gated RMSNorm
+// (triton_kernels/gdn_gated_rmsnorm.py:54-67).  `fused` is one row of the input projection per sequence:
+// [q | k | v | z | a | b] = [3*H*128 | H*128 | H | H].  Thread t of CTA (sequence, head) owns channel t of the head's q,
+// k, v and z slices and value column t of the state; every intermediate keeps the reference's rounding point (conv
+// output, q_n, k_n and the recurrence output are bf16 tensors there).
+__global__ void __launch_bounds__(GDN_THREADS)
+gdn_decode_fused_kernel(const __nv_bfloat16* __restrict__ fused, int64_t fused_stride,
+                        __nv_bfloat16* __restrict__ conv_state, const __nv_bfloat16* __restrict__ w4,
+                        const float* __restrict__ a_log, const __nv_bfloat16* __restrict__ dt_bias,
+                        const float* __restrict__ norm_w, float* __restrict__ state, __nv_bfloat16* __restrict__ out,
+                        int heads) {
+  __shared__ __align__(16) float kf[GDN_D];
+  __shared__ __align__(16) float qf[GDN_D];
+  __shared__ float red[3][4];
+  __shared__ float gate_s[2];
+  const int b = blockIdx.x / heads, h = blockIdx.x % heads, t = threadIdx.x;
+  const int kd = heads * GDN_D, width = 3 * kd;
+  float* sp = state + (static_cast<int64_t>(b) * heads + h) * GDN_D * GDN_D + t;
+  float s[GDN_D];
+#pragma unroll
+  for (int i = 0; i < GDN_D; ++i) s[i] = __ldcs(sp + i * GDN_D);  // the 64 KiB state: issued first, streamed once
+  const __nv_bfloat16* row = fused + static_cast<int64_t>(b) * fused_stride;
+  float y[3];
+#pragma unroll
+  for (int part = 0; part < 3; ++part) {
+    const int c = part * kd + h * GDN_D + t;
+    __nv_bfloat16* st = conv_state + static_cast<int64_t>(b) * 4 * width + c;
+    const __nv_bfloat16 s1 = st[width], s2 = st[2 * width], s3 = st[3 * width];
+    const __nv_bfloat16 xn = row[c];
+    st[0] = s1;
+    st[width] = s2;
+    st[2 * width] = s3;
+    st[3 * width] = xn;
+    float acc = __bfloat162float(w4[c]) * __bfloat162float(s1);
+    acc = fmaf(__bfloat162float(w4[width + c]), __bfloat162float(s2), acc);
+    acc = fmaf(__bfloat162float(w4[2 * width + c]), __bfloat162float(s3), acc);
+    acc = fmaf(__bfloat162float(w4[3 * width + c]), __bfloat162float(xn), acc);
+    y[part] = round_bf16(acc / (1.0f + expf(-acc)));
+  }
+  const float zv = __bfloat162float(row[width + h * GDN_D + t]);
+  const float wv = norm_w[t];
+  float sq = warp_sum(y[0] * y[0]), sk = warp_sum(y[1] * y[1]);
+  if ((t & 31) == 0) {
+    red[0][t >> 5] = sq;
+    red[1][t >> 5] = sk;
+  }
+  if (t == 0) {
+    const float av = __bfloat162float(row[width + kd + h]) + __bfloat162float(dt_bias[h]);
+    const float bv = __bfloat162float(row[width + kd + heads + h]);
+    const float sp_ = av > 20.f ? av : log1pf(expf(av));
+    gate_s[0] = 1.0f / (1.0f + expf(-bv));              // beta
+    gate_s[1] = __expf(-expf(a_log[h]) * sp_);           // exp(g)
+  }
+  __syncthreads();
+  sq = (red[0][0] + red[0][1]) + (red[0][2] + red[0][3]);
+  sk = (red[1][0] + red[1][1]) + (red[1][2] + red[1][3]);
+  qf[t] = round_bf16(y[0] * rsqrtf(sq + 1e-6f) * 0.08838834764831845f);  // DK^-0.5
+  kf[t] = round_bf16(y[1] * rsqrtf(sk + 1e-6f));
+  __syncthreads();
+  float o;
+  gdn_token_update(s, kf, qf, gate_s[1], gate_s[0], y[2], o);
+#pragma unroll
+  for (int i = 0; i < GDN_D; ++i) __stcs(sp + i * GDN_D, s[i]);
+  // gated RMSNorm over the head's 128 outputs
+  const float x = round_bf16(o);
+  const float ss = warp_sum(x * x);
+  if ((t & 31) == 0) red[2][t >> 5] = ss;
+  __syncthreads();
+  const float rs = rsqrtf(((red[2][0] + red[2][1]) + (red[2][2] + red[2][3])) / static_cast<float>(GDN_D) + 1e-6f);
+  out[(static_cast<int64_t>(b) * heads + h) * GDN_D + t] = __float2bfloat16_rn(x * rs * wv * (zv / (1.0f + expf(-zv))));
+}
+
 constexpr int SEQ_TILE = 16;  // tokens staged in shared memory per step of the prefill loop
 
 __global__ void __launch_bounds__(GDN_THREADS)
@@ -142,6 +216,20 @@ extern "C" int b200_gdn_recurrent_decode(const void* q, int64_t q_stride_b, int6
       g_stride_b, g_stride_h, state, state_stride_b, state_stride_h, static_cast<__nv_bfloat16*>(out), out_stride_b,
       out_stride_h, num_heads);
   return check_launch("gdn_recurrent_decode");
+}
+
+extern "C" int b200_gdn_decode_fused(const void* fused, int64_t fused_stride, void* conv_state, const void* weight4,
+                                     const float* a_log, const void* dt_bias, const float* norm_weight, float* state,
+                                     void* out, int32_t batch, int32_t num_heads, int32_t head_dim,
+                                     b200_stream_t stream) {
+  B200_REQUIRE(batch > 0 && num_heads > 0 && head_dim == GDN_D, "gdn_decode_fused: head_dim must be %d (got %d)", GDN_D,
+               head_dim);
+  gdn_decode_fused_kernel<<<static_cast<unsigned>(batch) * num_heads, GDN_THREADS, 0,
+                            reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(fused), fused_stride, static_cast<__nv_bfloat16*>(conv_state),
+      static_cast<const __nv_bfloat16*>(weight4), a_log, static_cast<const __nv_bfloat16*>(dt_bias), norm_weight, state,
+      static_cast<__nv_bfloat16*>(out), num_heads);
+  return check_launch("gdn_decode_fused");
 }
 
 extern "C" int b200_gdn_recurrent_prefill_sequential(

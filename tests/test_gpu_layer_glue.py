@@ -88,3 +88,29 @@ def test_gdn_gated_rmsnorm(mods):
     w = (1 + 0.1 * torch.randn(128, generator=gen)).to(DEV)
     out = ops.gdn_gated_rmsnorm_fused(x, z, w)
     _ulp_close(out.view(n, heads, 128), glue.gdn_gated_rmsnorm(x, z.reshape(n, heads, 128), w))
+
+
+@pytest.mark.parametrize("batch", [1, 32])
+def test_gdn_decode_fused_equals_chain(mods, batch):
+    """One-launch Gated-DeltaNet decode mixer against prep -> recurrent_decode -> gated RMSNorm over three steps
+    (conv state and recurrent state carried in place)."""
+    ops, glue = mods
+    gen = torch.Generator().manual_seed(90 + batch)
+    heads, kd = 16, 2048
+    w4 = (torch.randn(4, 3 * kd, generator=gen) * 0.5).to(torch.bfloat16).to(DEV)
+    a_log = (torch.rand(heads, generator=gen) * 2.7).to(DEV)
+    dt_bias = (torch.randn(heads, generator=gen) * 0.5).to(torch.bfloat16).to(DEV)
+    norm_w = (1 + 0.1 * torch.randn(128, generator=gen)).to(DEV)
+    conv_a = torch.randn(batch, 4, 3 * kd, generator=gen).to(torch.bfloat16).to(DEV)
+    state_a = (torch.randn(batch, heads, 128, 128, generator=gen) * 0.1).to(DEV)
+    conv_b, state_b = conv_a.clone(), state_a.clone()
+    for step in range(3):
+        fused = torch.randn(batch, 4 * kd + 2 * heads, generator=gen).to(torch.bfloat16).to(DEV)
+        q_n, k_n, v, beta, g = ops.gdn_decode_prep(fused[:, : 3 * kd], conv_a, w4, fused[:, 4 * kd: 4 * kd + heads],
+                                                   fused[:, 4 * kd + heads:], a_log, dt_bias, heads)
+        core = ops.gdn_recurrent_decode(q_n, k_n, v, beta, g, state_a)
+        ref = ops.gdn_gated_rmsnorm_fused(core, fused[:, 3 * kd: 4 * kd], norm_w)
+        out = ops.gdn_decode_fused(fused, conv_b, w4, a_log, dt_bias, norm_w, state_b, heads)
+        assert torch.equal(conv_a, conv_b)
+        assert torch.allclose(state_a, state_b, rtol=1e-5, atol=1e-6)
+        _ulp_close(out, ref, ulps=2)
