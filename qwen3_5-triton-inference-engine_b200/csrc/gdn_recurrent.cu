@@ -96,25 +96,36 @@ gdn_decode_fused_kernel(const __nv_bfloat16* __restrict__ fused, int64_t fused_s
   const int b = blockIdx.x / heads, h = blockIdx.x % heads, t = threadIdx.x;
   const int kd = heads * GDN_D, width = 3 * kd;
   float* sp = state + (static_cast<int64_t>(b) * heads + h) * GDN_D * GDN_D + t;
+  const __nv_bfloat16* row = fused + static_cast<int64_t>(b) * fused_stride;
+  // the small loads go out first so that the conv, norm and gate arithmetic runs while the 64 KiB state streams in
+  __nv_bfloat16 cs[3][3], cx[3], cw[3][4];
+#pragma unroll
+  for (int part = 0; part < 3; ++part) {
+    const int c = part * kd + h * GDN_D + t;
+    const __nv_bfloat16* st = conv_state + static_cast<int64_t>(b) * 4 * width + c;
+    cs[part][0] = st[width];
+    cs[part][1] = st[2 * width];
+    cs[part][2] = st[3 * width];
+    cx[part] = row[c];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) cw[part][r] = w4[r * width + c];
+  }
   float s[GDN_D];
 #pragma unroll
-  for (int i = 0; i < GDN_D; ++i) s[i] = __ldcs(sp + i * GDN_D);  // the 64 KiB state: issued first, streamed once
-  const __nv_bfloat16* row = fused + static_cast<int64_t>(b) * fused_stride;
+  for (int i = 0; i < GDN_D; ++i) s[i] = __ldcs(sp + i * GDN_D);  // streamed once: evict-first
   float y[3];
 #pragma unroll
   for (int part = 0; part < 3; ++part) {
     const int c = part * kd + h * GDN_D + t;
     __nv_bfloat16* st = conv_state + static_cast<int64_t>(b) * 4 * width + c;
-    const __nv_bfloat16 s1 = st[width], s2 = st[2 * width], s3 = st[3 * width];
-    const __nv_bfloat16 xn = row[c];
-    st[0] = s1;
-    st[width] = s2;
-    st[2 * width] = s3;
-    st[3 * width] = xn;
-    float acc = __bfloat162float(w4[c]) * __bfloat162float(s1);
-    acc = fmaf(__bfloat162float(w4[width + c]), __bfloat162float(s2), acc);
-    acc = fmaf(__bfloat162float(w4[2 * width + c]), __bfloat162float(s3), acc);
-    acc = fmaf(__bfloat162float(w4[3 * width + c]), __bfloat162float(xn), acc);
+    st[0] = cs[part][0];
+    st[width] = cs[part][1];
+    st[2 * width] = cs[part][2];
+    st[3 * width] = cx[part];
+    float acc = __bfloat162float(cw[part][0]) * __bfloat162float(cs[part][0]);
+    acc = fmaf(__bfloat162float(cw[part][1]), __bfloat162float(cs[part][1]), acc);
+    acc = fmaf(__bfloat162float(cw[part][2]), __bfloat162float(cs[part][2]), acc);
+    acc = fmaf(__bfloat162float(cw[part][3]), __bfloat162float(cx[part]), acc);
     y[part] = round_bf16(acc / (1.0f + expf(-acc)));
   }
   const float zv = __bfloat162float(row[width + h * GDN_D + t]);
