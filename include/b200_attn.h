@@ -271,20 +271,42 @@ int b200_gdn_chunked_prefill_fused(const void* q, int64_t q_stride_t, int64_t q_
  * b200_gdn_gated_rmsnorm: out[r,:] = x[r,:] * rsqrt(mean(x^2) + 1e-6) * weight * silu(z[r,:]) for rows r = (n, head);
  * x and out contiguous [rows, 128], z row (n, head) at z + n * z_stride + head * 128
  * (triton_kernels/gdn_gated_rmsnorm.py:95-140). */
+/* Overlap flags (programmatic dependent launch) of b200_skinny_gemm, b200_add_rmsnorm, b200_swiglu and
+ * b200_gdn_decode_fused; 0 = plain stream order.
+ *   START    the kernel may begin while the kernel in front of it in the stream still runs; it reads that kernel's
+ *            output, and writes anything, only after that kernel has completed.
+ *   TRIGGER  the kernel lets the NEXT kernel in the stream begin early in the same way.  Pass it only when that next
+ *            kernel is one of these four launched with START: a kernel that does not itself wait for its predecessor
+ *            before finishing (some library initialisation kernels) would break the ordering of everything after it.
+ *   PREFETCH b200_gdn_decode_fused only, see there. */
+#define B200_OVERLAP_START 1
+#define B200_OVERLAP_TRIGGER 2
+#define B200_OVERLAP_PREFETCH 4
+
 /* The whole Gated-DeltaNet mixer of ONE decode token per sequence between its two projections, one launch:
  * b200_gdn_decode_prep -> b200_gdn_recurrent_decode -> b200_gdn_gated_rmsnorm with nothing written in between.
  * fused: one row per sequence of the input projection, [q | k | v | z | a | b] = [3*H*128 | H*128 | H | H] bf16, rows
  * fused_stride elements apart; conv_state [B,4,3*H*128] bf16 and state [B,H,128,128] fp32 are updated in place;
  * weight4 [4,3*H*128] bf16, a_log [H] fp32, dt_bias [H] bf16, norm_weight [128] fp32; out [B, H*128] bf16 contiguous.
- * Replaces the operator chain of engine/runner.py:431-441. */
+ * Replaces the operator chain of engine/runner.py:431-441.  `overlap`: B200_OVERLAP_* flags (below); PREFETCH lets the
+ * kernel load conv_state and state before the kernel in front of it has finished - pass it only when that kernel does
+ * not write them (in a layer stack it is the input projection). */
 int b200_gdn_decode_fused(const void* fused, int64_t fused_stride, void* conv_state, const void* weight4,
                           const float* a_log, const void* dt_bias, const float* norm_weight, float* state, void* out,
-                          int32_t batch, int32_t num_heads, int32_t head_dim, b200_stream_t stream);
+                          int32_t batch, int32_t num_heads, int32_t head_dim, int32_t overlap, b200_stream_t stream);
+/* Y[M,N] = X[M,K] . W[N,K]^T for decode batches (M <= 32), bf16 in/out, fp32 accumulation: W is streamed once by
+ * tensor-map TMA, X staged in shared memory.  N a multiple of 8, K a multiple of 128 up to 1536; x / y rows x_stride /
+ * y_stride elements apart (multiples of 8), weight contiguous [N,K]; all 16-byte aligned.  With
+ * B200_OVERLAP_START the weight tiles are requested before the preceding kernel in the stream has finished, so
+ * `weight` must not be that kernel's output (x may be).
+ * Replaces triton_kernels/gemm_2d.py for the decode-step projections of the hidden state. */
+int b200_skinny_gemm(const void* x, int64_t x_stride, const void* weight, void* y, int64_t y_stride, int32_t m,
+                     int32_t n, int32_t k, int32_t overlap, b200_stream_t stream);
 int b200_add_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x_stride_inner, int32_t inner_count,
                      const void* residual, int64_t residual_stride, const void* weight, void* sum_out, void* norm_out,
-                     int32_t rows, int32_t dim, float eps, b200_stream_t stream);
+                     int32_t rows, int32_t dim, float eps, int32_t overlap, b200_stream_t stream);
 int b200_swiglu(const void* gate_up, int64_t row_stride, void* out, int32_t rows, int32_t intermediate,
-                b200_stream_t stream);
+                int32_t overlap, b200_stream_t stream);
 int b200_gdn_decode_prep(const void* qkv, int64_t qkv_stride, void* conv_state, const void* weight4, const void* a,
                          int64_t a_stride, const void* b, int64_t b_stride, const float* a_log, const void* dt_bias,
                          void* q_out, void* k_out, void* v_out, float* beta, float* g, int32_t batch, int32_t num_heads,

@@ -40,10 +40,11 @@ SIGNATURES: dict[str, list] = {
     "b200_gdn_chunk_output": [P, I64, I64, P, I64, I64, P, P, P, P, I64, I64, I32, I32, I32, I32, P],
     "b200_gdn_chunked_prefill_packed": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I32, I32, I32,
                                         P, P, P, I64, I64, I32, I32, I32, P],
-    "b200_add_rmsnorm": [P, I64, I64, I32, P, I64, P, P, P, I32, I32, c_float, P],
-    "b200_swiglu": [P, I64, P, I32, I32, P],
+    "b200_skinny_gemm": [P, I64, P, P, I64, I32, I32, I32, I32, P],
+    "b200_add_rmsnorm": [P, I64, I64, I32, P, I64, P, P, P, I32, I32, c_float, I32, P],
+    "b200_swiglu": [P, I64, P, I32, I32, I32, P],
     "b200_gdn_decode_prep": [P, I64, P, P, P, I64, P, I64, P, P, P, P, P, P, P, I32, I32, I32, P],
-    "b200_gdn_decode_fused": [P, I64, P, P, P, P, P, P, P, I32, I32, I32, P],
+    "b200_gdn_decode_fused": [P, I64, P, P, P, P, P, P, P, I32, I32, I32, I32, P],
     "b200_gdn_gated_rmsnorm": [P, P, I64, P, P, I32, I32, I32, P],
     "b200_gdn_chunked_prefill_fused": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I32, I32,
                                        P, P, I64, I64, I32, I32, I32, P],

@@ -100,6 +100,17 @@ class Engine:
         self.graph = None
 
     # ------------------------------------------------------------------------------------------------ shared pieces
+    def _streams_weight(self, weight) -> bool:
+        """Whether a projection of `batch` rows by this weight runs on the package's weight-streaming kernel."""
+        return (self.fused_glue and self.batch <= ops.SKINNY_GEMM_MAX_M and weight.shape[1] <= ops.SKINNY_GEMM_MAX_K
+                and weight.shape[1] % 128 == 0 and weight.shape[0] % 8 == 0)
+
+    def _proj(self, x, weight, overlap: int = 0):
+        """Projection of the hidden state: the weight-streaming kernel for decode-sized batches, cuBLAS otherwise."""
+        if x.shape[0] == self.batch and self._streams_weight(weight):
+            return ops.skinny_gemm(x, weight, overlap=overlap)
+        return glue.gemm_2d(x, weight)
+
     def _norm(self, x, weight):
         if self.fused_glue:
             return ops.add_rmsnorm(x, weight, self.cfg.eps)
@@ -211,36 +222,45 @@ class Engine:
         return nxt
 
     def _decode_fused(self, tok: torch.Tensor) -> torch.Tensor:
-        """The same step with every row-wise operator as one launch: about ten launches per layer (four of them
-        cuBLAS GEMMs).  The residual add after a layer's MLP is fused into the next layer's input norm."""
+        """The same step with every row-wise operator as one launch: about nine launches per layer (two or three of
+        them cuBLAS GEMMs).  The residual add after a layer's MLP is fused into the next layer's input norm.  Kernels
+        of this package that follow one another start early (programmatic dependent launch: weights and states stream
+        in while the predecessor finishes); a kernel in front of a cuBLAS or PyTorch kernel never triggers early."""
         cfg = self.cfg
         batch, heads, kd = self.batch, cfg.gdn_heads, cfg.gdn_width
         qd, kvd = cfg.num_q_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
+        start, chain = ops.OVERLAP_START, ops.OVERLAP_START | ops.OVERLAP_TRIGGER
         x = glue.embedding_gather(tok, self.w["embed"])
         pending = None                                   # MLP output still to be added to the residual stream
         for i, layer in enumerate(self.w["layers"]):
+            proj_w = layer["in_proj"] if layer["kind"] == "gdn" else layer["qkvg"]
+            own_proj = self._streams_weight(proj_w)      # the next kernel is this package's projection
             if pending is None:
-                h = ops.add_rmsnorm(x, layer["ln1"], cfg.eps)
+                h = ops.add_rmsnorm(x, layer["ln1"], cfg.eps, overlap=chain if own_proj else start)
             else:
-                x, h = ops.add_rmsnorm(pending, layer["ln1"], cfg.eps, residual=x)
+                x, h = ops.add_rmsnorm(pending, layer["ln1"], cfg.eps, residual=x, overlap=chain if own_proj else start)
+            fused = self._proj(h, proj_w, chain)
             if layer["kind"] == "gdn":
-                fused = glue.gemm_2d(h, layer["in_proj"])
                 normed = ops.gdn_decode_fused(fused, self.conv_state[i], layer["conv4"], layer["a_log"], layer["dt_bias"],
-                                              layer["norm"], self.rec_state[i], heads)
+                                              layer["norm"], self.rec_state[i], heads,
+                                              overlap=start | ops.OVERLAP_PREFETCH)
                 mixed = glue.gemm_2d(normed, layer["out_proj"])
             else:
-                fused = glue.gemm_2d(h, layer["qkvg"])
-                q = ops.add_rmsnorm(fused[:, :qd].view(batch, cfg.num_q_heads, cfg.head_dim), layer["q_norm"], cfg.eps)
+                q = ops.add_rmsnorm(fused[:, :qd].view(batch, cfg.num_q_heads, cfg.head_dim), layer["q_norm"], cfg.eps,
+                                    overlap=chain)
                 k = ops.add_rmsnorm(fused[:, 2 * qd: 2 * qd + kvd].view(batch, cfg.num_kv_heads, cfg.head_dim),
-                                    layer["k_norm"], cfg.eps)
+                                    layer["k_norm"], cfg.eps, overlap=start)
                 v = fused[:, 2 * qd + kvd:].view(batch, cfg.num_kv_heads, cfg.head_dim)
                 k_cache, v_cache = self.kv[i]
                 ctx = ops.fused_decode_attention(q, k, v, fused[:, qd: 2 * qd], k_cache, v_cache, self.block_table,
                                                  self.pos, self.inv_freq, cfg.rotary_dim, self.workspace)
                 mixed = glue.gemm_2d(ctx, layer["o_proj"])
-            x, h = ops.add_rmsnorm(mixed, layer["ln2"], cfg.eps, residual=x)
-            pending = glue.gemm_2d(ops.swiglu_fused(glue.gemm_2d(h, layer["gate_up"]), cfg.intermediate), layer["down"])
-        _, h = ops.add_rmsnorm(pending, self.w["norm"], cfg.eps, residual=x)
+            own_mlp = self._streams_weight(layer["gate_up"])
+            x, h = ops.add_rmsnorm(mixed, layer["ln2"], cfg.eps, residual=x, overlap=chain if own_mlp else start)
+            act = ops.swiglu_fused(self._proj(h, layer["gate_up"], chain), cfg.intermediate,
+                                   overlap=start)
+            pending = glue.gemm_2d(act, layer["down"])
+        _, h = ops.add_rmsnorm(pending, self.w["norm"], cfg.eps, residual=x, overlap=start)
         nxt = glue.lm_head_argmax(h, self.w["embed"], last_only=False)
         self.pos.add_(1)
         return nxt

@@ -590,7 +590,13 @@ def gdn_chunked_prefill_packed(q, k, v, beta, g, cu_seqlens, max_seqlen=None, fu
 
 
 # =========================================================================== row-wise layer operators (one launch each)
-def add_rmsnorm(x, weight, eps: float, residual=None):
+# Overlap flags (programmatic dependent launch, include/b200_attn.h): START = this kernel may begin while the kernel in
+# front of it still runs; TRIGGER = the next kernel may begin early too (only when it is one of these operators called
+# with START); PREFETCH = gdn_decode_fused may load its states before the kernel in front of it has finished.
+OVERLAP_START, OVERLAP_TRIGGER, OVERLAP_PREFETCH = 1, 2, 4
+
+
+def add_rmsnorm(x, weight, eps: float, residual=None, overlap: int = 0):
     """Qwen RMSNorm `x * rsqrt(mean(x^2) + eps) * (1 + weight)` over the last dim (triton_kernels/qwen_rmsnorm.py:70-73),
     optionally fused with the residual add in front of it (triton_kernels/residual_add.py).
     x: [rows, dim] or a [n, H, dim] column view of a fused projection (last dim contiguous).  Returns norm, or
@@ -612,17 +618,18 @@ def add_rmsnorm(x, weight, eps: float, residual=None):
         total = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
     _lib.call("b200_add_rmsnorm", _ptr(x), outer, inner, count, _ptr(residual) if residual is not None else None,
               residual.stride(0) if residual is not None else 0, _ptr(weight), _ptr(total) if total is not None else None,
-              _ptr(norm), rows, dim, float(eps), _stream())
+              _ptr(norm), rows, dim, float(eps), int(overlap), _stream())
     return norm if residual is None else (total, norm)
 
 
-def swiglu_fused(gate_up, intermediate: int):
+def swiglu_fused(gate_up, intermediate: int, overlap: int = 0):
     """bf16(silu(gate_up[:, :I]) * gate_up[:, I:2I]) from the fused gate/up projection (triton_kernels/swiglu.py)."""
     assert gate_up.ndim == 2 and gate_up.dtype == torch.bfloat16 and gate_up.stride(1) == 1
     assert gate_up.shape[1] >= 2 * intermediate
     _require_cuda(gate_up)
     out = torch.empty((gate_up.shape[0], intermediate), dtype=torch.bfloat16, device=gate_up.device)
-    _lib.call("b200_swiglu", _ptr(gate_up), gate_up.stride(0), _ptr(out), gate_up.shape[0], int(intermediate), _stream())
+    _lib.call("b200_swiglu", _ptr(gate_up), gate_up.stride(0), _ptr(out), gate_up.shape[0], int(intermediate),
+              int(overlap), _stream())
     return out
 
 
@@ -665,11 +672,13 @@ def gdn_gated_rmsnorm_fused(x, z, weight):
     return out
 
 
-def gdn_decode_fused(fused, conv_state, weight4, a_log, dt_bias, norm_weight, state, num_heads: int):
+def gdn_decode_fused(fused, conv_state, weight4, a_log, dt_bias, norm_weight, state, num_heads: int, overlap: int = 0):
     """The Gated-DeltaNet mixer of one decode token per sequence between its projections in ONE launch: conv + SiLU,
     q/k norms, gates, delta-rule step and gated RMSNorm (engine/runner.py:431-441).  fused [B, 4*H*128 + 2*H] is the
     row of the fused input projection ([q|k|v|z|a|b]); conv_state [B,4,3*H*128] and state [B,H,128,128] are updated in
-    place.  Returns the normed mixer output [B, H*128] bf16 (the input of out_proj)."""
+    place.  Returns the normed mixer output [B, H*128] bf16 (the input of out_proj).
+    overlap: OVERLAP_* flags; OVERLAP_PREFETCH lets the kernel load conv_state / state while the kernel before it in
+    the stream is still running: only valid when that kernel does not write them."""
     batch = fused.shape[0]
     kd = num_heads * GDN_DIM
     assert fused.shape == (batch, 4 * kd + 2 * num_heads) and fused.stride(1) == 1 and fused.dtype == torch.bfloat16
@@ -681,5 +690,23 @@ def gdn_decode_fused(fused, conv_state, weight4, a_log, dt_bias, norm_weight, st
     _require_cuda(fused, conv_state, weight4, a_log, dt_bias, norm_weight, state)
     out = torch.empty((batch, kd), dtype=torch.bfloat16, device=fused.device)
     _lib.call("b200_gdn_decode_fused", _ptr(fused), fused.stride(0), _ptr(conv_state), _ptr(weight4), _ptr(a_log),
-              _ptr(dt_bias.contiguous()), _ptr(norm_weight), _ptr(state), _ptr(out), batch, num_heads, GDN_DIM, _stream())
+              _ptr(dt_bias.contiguous()), _ptr(norm_weight), _ptr(state), _ptr(out), batch, num_heads, GDN_DIM,
+              int(overlap), _stream())
     return out
+
+
+SKINNY_GEMM_MAX_M, SKINNY_GEMM_MAX_K = 32, 1536
+
+
+def skinny_gemm(x, weight, overlap: int = 0):
+    """y = x @ weight^T for a decode batch (x [M <= 32, K <= 1536] bf16, weight [N, K] bf16 contiguous), the weight
+    streamed once from HBM (triton_kernels/gemm_2d.py for the decode-step projections)."""
+    assert x.ndim == 2 and weight.ndim == 2 and x.shape[1] == weight.shape[1]
+    assert x.dtype == weight.dtype == torch.bfloat16 and weight.is_contiguous() and x.stride(1) == 1
+    m, k = x.shape
+    n = weight.shape[0]
+    _require_cuda(x, weight)
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
+    _lib.call("b200_skinny_gemm", _ptr(x), x.stride(0), _ptr(weight), _ptr(y), y.stride(0), m, n, k, int(overlap),
+              _stream())
+    return y

@@ -142,6 +142,39 @@ __device__ __forceinline__ void named_barrier(int id, int count) {
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// ----------------------------------------------------------------------------- programmatic dependent launch
+// Overlap flags of the entry points that support it (include/b200_attn.h, B200_OVERLAP_*):
+//   START    the kernel is launched with the programmatic-serialization attribute: it may begin while its predecessor
+//            in the stream still runs.  What it does before pdl_wait() (barrier set-up, loads of weights) overlaps
+//            with the predecessor; pdl_wait() returns once the predecessor has completed and its writes are visible;
+//            ALL global writes of the kernel come after it.
+//   TRIGGER  the kernel lets its successor begin in the same way (pdl_trigger() at its start).  Only safe when the
+//            successor is a kernel that itself waits for its predecessor before it finishes - one of this library's
+//            START kernels.  A library kernel launched with the attribute that never waits (an initialisation kernel,
+//            say) would complete early, and everything ordered after it would no longer be ordered after this kernel.
+//   PREFETCH kernel-specific: also load, before pdl_wait(), state that only an earlier step wrote.
+constexpr int OVERLAP_START = 1, OVERLAP_TRIGGER = 2, OVERLAP_PREFETCH = 4;
+// NOTE: data written by the predecessor must not be read through a `const __restrict__` pointer: such loads are
+// invariant to the compiler, which may hoist them above the wait (seen on the device: a stale projection row).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(bool early_start, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = early_start ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ----------------------------------------------------------------------------- warp-level MMA (bf16, fp32 accumulate)
 // D[16x8] += A[16x16] * B[16x8]
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {

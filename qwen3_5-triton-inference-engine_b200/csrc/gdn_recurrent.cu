@@ -84,11 +84,11 @@ gdn_decode_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_b, int64_t q_h,
 // k, v and z slices and value column t of the state; every intermediate keeps the reference's rounding point (conv
 // output, q_n, k_n and the recurrence output are bf16 tensors there).
 __global__ void __launch_bounds__(GDN_THREADS)
-gdn_decode_fused_kernel(const __nv_bfloat16* __restrict__ fused, int64_t fused_stride,
+gdn_decode_fused_kernel(const __nv_bfloat16* fused, int64_t fused_stride,  // no __restrict__: see pdl_wait()
                         __nv_bfloat16* __restrict__ conv_state, const __nv_bfloat16* __restrict__ w4,
                         const float* __restrict__ a_log, const __nv_bfloat16* __restrict__ dt_bias,
                         const float* __restrict__ norm_w, float* __restrict__ state, __nv_bfloat16* __restrict__ out,
-                        int heads) {
+                        int heads, int overlap) {
   __shared__ __align__(16) float kf[GDN_D];
   __shared__ __align__(16) float qf[GDN_D];
   __shared__ float red[3][4];
@@ -97,7 +97,12 @@ gdn_decode_fused_kernel(const __nv_bfloat16* __restrict__ fused, int64_t fused_s
   const int kd = heads * GDN_D, width = 3 * kd;
   float* sp = state + (static_cast<int64_t>(b) * heads + h) * GDN_D * GDN_D + t;
   const __nv_bfloat16* row = fused + static_cast<int64_t>(b) * fused_stride;
-  // the small loads go out first so that the conv, norm and gate arithmetic runs while the 64 KiB state streams in
+  // With the PREFETCH flag the caller guarantees that the conv state and the recurrent state were last written by an
+  // EARLIER kernel than the one directly before this one in the stream (in a layer stack that one is the input
+  // projection): their loads then go out before pdl_wait() and overlap with the projection.  `fused` is read after
+  // the wait; every store comes after it too.
+  if (overlap & OVERLAP_TRIGGER) pdl_trigger();
+  if (!(overlap & OVERLAP_PREFETCH)) pdl_wait();
   __nv_bfloat16 cs[3][3], cx[3], cw[3][4];
 #pragma unroll
   for (int part = 0; part < 3; ++part) {
@@ -106,13 +111,15 @@ gdn_decode_fused_kernel(const __nv_bfloat16* __restrict__ fused, int64_t fused_s
     cs[part][0] = st[width];
     cs[part][1] = st[2 * width];
     cs[part][2] = st[3 * width];
-    cx[part] = row[c];
 #pragma unroll
     for (int r = 0; r < 4; ++r) cw[part][r] = w4[r * width + c];
   }
   float s[GDN_D];
 #pragma unroll
   for (int i = 0; i < GDN_D; ++i) s[i] = __ldcs(sp + i * GDN_D);  // streamed once: evict-first
+  pdl_wait();
+#pragma unroll
+  for (int part = 0; part < 3; ++part) cx[part] = row[part * kd + h * GDN_D + t];
   float y[3];
 #pragma unroll
   for (int part = 0; part < 3; ++part) {
@@ -232,14 +239,15 @@ extern "C" int b200_gdn_recurrent_decode(const void* q, int64_t q_stride_b, int6
 extern "C" int b200_gdn_decode_fused(const void* fused, int64_t fused_stride, void* conv_state, const void* weight4,
                                      const float* a_log, const void* dt_bias, const float* norm_weight, float* state,
                                      void* out, int32_t batch, int32_t num_heads, int32_t head_dim,
-                                     b200_stream_t stream) {
+                                     int32_t overlap, b200_stream_t stream) {
   B200_REQUIRE(batch > 0 && num_heads > 0 && head_dim == GDN_D, "gdn_decode_fused: head_dim must be %d (got %d)", GDN_D,
                head_dim);
-  gdn_decode_fused_kernel<<<static_cast<unsigned>(batch) * num_heads, GDN_THREADS, 0,
-                            reinterpret_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(fused), fused_stride, static_cast<__nv_bfloat16*>(conv_state),
-      static_cast<const __nv_bfloat16*>(weight4), a_log, static_cast<const __nv_bfloat16*>(dt_bias), norm_weight, state,
-      static_cast<__nv_bfloat16*>(out), num_heads);
+  if (launch_pdl((overlap & OVERLAP_START) != 0, gdn_decode_fused_kernel, dim3(static_cast<unsigned>(batch) * num_heads), dim3(GDN_THREADS), 0,
+                 reinterpret_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(fused), fused_stride,
+                 static_cast<__nv_bfloat16*>(conv_state), static_cast<const __nv_bfloat16*>(weight4), a_log,
+                 static_cast<const __nv_bfloat16*>(dt_bias), norm_weight, state, static_cast<__nv_bfloat16*>(out),
+                 num_heads, overlap) != cudaSuccess)
+    return fail(ERR_LAUNCH, "gdn_decode_fused: %s", cudaGetErrorString(cudaGetLastError()));
   return check_launch("gdn_decode_fused");
 }
 

@@ -25,15 +25,17 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 constexpr int RN_MAX_DIM = 8192;
 
 __global__ void __launch_bounds__(RN_MAX_DIM / 8)
-add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_outer, int64_t x_inner, int inner_count,
-                   const __nv_bfloat16* __restrict__ residual, int64_t res_stride,
+add_rmsnorm_kernel(const __nv_bfloat16* x, int64_t x_outer, int64_t x_inner, int inner_count,  // x, residual: no
+                   const __nv_bfloat16* residual, int64_t res_stride,                             // __restrict__ (pdl_wait)
                    const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ sum_out,
-                   __nv_bfloat16* __restrict__ norm_out, int dim, float eps) {
+                   __nv_bfloat16* __restrict__ norm_out, int dim, float eps, int overlap) {
   __shared__ float red[32];
   const int row = blockIdx.x, c = threadIdx.x * 8;
   const __nv_bfloat16* src = x + static_cast<int64_t>(row / inner_count) * x_outer + (row % inner_count) * x_inner;
+  if (overlap & OVERLAP_TRIGGER) pdl_trigger();
+  const uint4 wv = *reinterpret_cast<const uint4*>(weight + c);  // a weight: independent of the predecessor
+  pdl_wait();
   const uint4 xv = *reinterpret_cast<const uint4*>(src + c);
-  const uint4 wv = *reinterpret_cast<const uint4*>(weight + c);
   uint4 rv = make_uint4(0, 0, 0, 0);
   if (residual != nullptr) rv = *reinterpret_cast<const uint4*>(residual + static_cast<int64_t>(row) * res_stride + c);
   float v[8], w[8];
@@ -66,10 +68,12 @@ add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_outer, int64_t
 
 // ------------------------------------------------------------------------------------------------------- SwiGLU
 __global__ void __launch_bounds__(256)
-swiglu_kernel(const __nv_bfloat16* __restrict__ gate_up, int64_t row_stride, __nv_bfloat16* __restrict__ out, int rows,
-              int inter) {
+swiglu_kernel(const __nv_bfloat16* gate_up, int64_t row_stride, __nv_bfloat16* __restrict__ out, int rows,
+              int inter, int overlap) {
   const int vec_per_row = inter >> 3;
   const int64_t total = static_cast<int64_t>(rows) * vec_per_row;
+  if (overlap & OVERLAP_TRIGGER) pdl_trigger();
+  pdl_wait();
   for (int64_t idx = blockIdx.x * 256 + threadIdx.x; idx < total; idx += static_cast<int64_t>(gridDim.x) * 256) {
     const int64_t r = idx / vec_per_row;
     const int c = static_cast<int>(idx % vec_per_row) * 8;
@@ -160,7 +164,7 @@ using namespace b200;
 
 extern "C" int b200_add_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x_stride_inner, int32_t inner_count,
                                 const void* residual, int64_t residual_stride, const void* weight, void* sum_out,
-                                void* norm_out, int32_t rows, int32_t dim, float eps, b200_stream_t stream) {
+                                void* norm_out, int32_t rows, int32_t dim, float eps, int32_t overlap, b200_stream_t stream) {
   B200_REQUIRE(rows > 0 && inner_count > 0 && dim > 0 && dim % 256 == 0 && dim <= RN_MAX_DIM,
                "add_rmsnorm: dim must be a multiple of 256 up to %d (got %d)", RN_MAX_DIM, dim);
   B200_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(norm_out) && x_stride_outer % 8 == 0 &&
@@ -169,15 +173,16 @@ extern "C" int b200_add_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x
   B200_REQUIRE(residual == nullptr || (aligned16(residual) && residual_stride % 8 == 0 &&
                                        (sum_out == nullptr || aligned16(sum_out))),
                "add_rmsnorm: residual / sum_out must be 16-byte aligned with a row stride that is a multiple of 8");
-  add_rmsnorm_kernel<<<rows, dim / 8, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), x_stride_outer, x_stride_inner, inner_count,
-      static_cast<const __nv_bfloat16*>(residual), residual_stride, static_cast<const __nv_bfloat16*>(weight),
-      static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), dim, eps);
+  if (launch_pdl((overlap & OVERLAP_START) != 0, add_rmsnorm_kernel, dim3(rows), dim3(dim / 8), 0, reinterpret_cast<cudaStream_t>(stream),
+                 static_cast<const __nv_bfloat16*>(x), x_stride_outer, x_stride_inner, inner_count,
+                 static_cast<const __nv_bfloat16*>(residual), residual_stride, static_cast<const __nv_bfloat16*>(weight),
+                 static_cast<__nv_bfloat16*>(sum_out), static_cast<__nv_bfloat16*>(norm_out), dim, eps, overlap) != cudaSuccess)
+    return fail(ERR_LAUNCH, "add_rmsnorm: %s", cudaGetErrorString(cudaGetLastError()));
   return check_launch("add_rmsnorm");
 }
 
 extern "C" int b200_swiglu(const void* gate_up, int64_t row_stride, void* out, int32_t rows, int32_t intermediate,
-                           b200_stream_t stream) {
+                           int32_t overlap, b200_stream_t stream) {
   B200_REQUIRE(rows > 0 && intermediate > 0 && intermediate % 8 == 0 && row_stride % 8 == 0 && aligned16(gate_up) &&
                    aligned16(out),
                "swiglu: intermediate and the row stride must be multiples of 8, pointers 16-byte aligned");
@@ -185,8 +190,10 @@ extern "C" int b200_swiglu(const void* gate_up, int64_t row_stride, void* out, i
   int blocks = static_cast<int>((vecs + 255) / 256);
   const int cap = sm_count() * 8;
   if (blocks > cap) blocks = cap;
-  swiglu_kernel<<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(gate_up), row_stride, static_cast<__nv_bfloat16*>(out), rows, intermediate);
+  if (launch_pdl((overlap & OVERLAP_START) != 0, swiglu_kernel, dim3(blocks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+                 static_cast<const __nv_bfloat16*>(gate_up), row_stride, static_cast<__nv_bfloat16*>(out), rows,
+                 intermediate, overlap) != cudaSuccess)
+    return fail(ERR_LAUNCH, "swiglu: %s", cudaGetErrorString(cudaGetLastError()));
   return check_launch("swiglu");
 }
 

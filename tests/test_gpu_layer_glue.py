@@ -90,8 +90,9 @@ def test_gdn_gated_rmsnorm(mods):
     _ulp_close(out.view(n, heads, 128), glue.gdn_gated_rmsnorm(x, z.reshape(n, heads, 128), w))
 
 
+@pytest.mark.parametrize("prefetch", [0, 1 | 4])
 @pytest.mark.parametrize("batch", [1, 32])
-def test_gdn_decode_fused_equals_chain(mods, batch):
+def test_gdn_decode_fused_equals_chain(mods, batch, prefetch):
     """One-launch Gated-DeltaNet decode mixer against prep -> recurrent_decode -> gated RMSNorm over three steps
     (conv state and recurrent state carried in place)."""
     ops, glue = mods
@@ -110,7 +111,79 @@ def test_gdn_decode_fused_equals_chain(mods, batch):
                                                    fused[:, 4 * kd + heads:], a_log, dt_bias, heads)
         core = ops.gdn_recurrent_decode(q_n, k_n, v, beta, g, state_a)
         ref = ops.gdn_gated_rmsnorm_fused(core, fused[:, 3 * kd: 4 * kd], norm_w)
-        out = ops.gdn_decode_fused(fused, conv_b, w4, a_log, dt_bias, norm_w, state_b, heads)
+        out = ops.gdn_decode_fused(fused, conv_b, w4, a_log, dt_bias, norm_w, state_b, heads, overlap=prefetch)
         assert torch.equal(conv_a, conv_b)
         assert torch.allclose(state_a, state_b, rtol=1e-5, atol=1e-6)
         _ulp_close(out, ref, ulps=2)
+
+
+@pytest.mark.parametrize("m,n,k", [(32, 8224, 1024), (1, 5120, 1024), (17, 7168, 1024), (32, 248320, 1024), (8, 512, 256),
+                                   (32, 1024, 1536)])
+def test_skinny_gemm(mods, m, n, k):
+    """Weight-streaming decode GEMM against an fp32 matmul of the same bf16 operands (exact products, fp32
+    accumulation on both sides: only the summation order and the final bf16 rounding differ)."""
+    ops, _ = mods
+    gen = torch.Generator().manual_seed(m * 131 + n)
+    x = torch.randn(m, k, generator=gen).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=gen) * 0.05).to(torch.bfloat16).to(DEV)
+    y = ops.skinny_gemm(x, w)
+    ref = x.float() @ w.float().t()
+    assert y.shape == (m, n)
+    err = (y.float() - ref).abs().max().item()
+    assert err <= 2.0 ** -8 * ref.abs().max().item() + 1e-6, err
+    # a strided input row view (a slice of a wider activation) gives the same result
+    wide = torch.zeros(m, k + 64, dtype=torch.bfloat16, device=DEV)
+    wide[:, :k] = x
+    assert torch.equal(ops.skinny_gemm(wide[:, :k], w), y)
+
+
+def test_overlapped_chain_in_graph_equals_plain(mods):
+    """add_rmsnorm -> skinny_gemm -> gdn_decode_fused launched with every overlap flag (programmatic dependent launch:
+    each kernel starts while its predecessor runs, the mixer pre-loads its states) and replayed from a CUDA graph with
+    a NEW input every replay, against the same chain in plain stream order.  A kernel that read its predecessor's
+    output before it was complete would see the previous replay's values."""
+    ops, _ = mods
+    gen = torch.Generator().manual_seed(7)
+    batch, heads, kd, hidden = 4, 16, 2048, 256
+    w_in = (torch.randn(4 * kd + 2 * heads, hidden, generator=gen) * 0.05).to(torch.bfloat16).to(DEV)
+    w4 = (torch.randn(4, 3 * kd, generator=gen) * 0.5).to(torch.bfloat16).to(DEV)
+    a_log = (torch.rand(heads, generator=gen) * 2.7).to(DEV)
+    dt_bias = (torch.randn(heads, generator=gen) * 0.5).to(torch.bfloat16).to(DEV)
+    norm_w = (1 + 0.1 * torch.randn(128, generator=gen)).to(DEV)
+    ln = (torch.randn(hidden, generator=gen) * 0.1).to(torch.bfloat16).to(DEV)
+    xs = [torch.randn(batch, hidden, generator=gen).to(torch.bfloat16).to(DEV) for _ in range(5)]
+    conv0 = torch.randn(batch, 4, 3 * kd, generator=gen).to(torch.bfloat16).to(DEV)
+    state0 = (torch.randn(batch, heads, 128, 128, generator=gen) * 0.1).to(DEV)
+
+    def run(overlapped: bool):
+        conv, state, x = conv0.clone(), state0.clone(), xs[0].clone()
+        out = torch.zeros(batch, kd, dtype=torch.bfloat16, device=DEV)
+        chain = ops.OVERLAP_START | ops.OVERLAP_TRIGGER if overlapped else 0
+        last = ops.OVERLAP_START | ops.OVERLAP_PREFETCH if overlapped else 0
+
+        def step():
+            h = ops.add_rmsnorm(x, ln, 1e-6, overlap=chain)
+            fused = ops.skinny_gemm(h, w_in, overlap=chain)
+            out.copy_(ops.gdn_decode_fused(fused, conv, w4, a_log, dt_bias, norm_w, state, heads, overlap=last))
+
+        step()
+        outs = [out.clone()]
+        graph = None
+        if overlapped:
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side), torch.cuda.graph(graph, stream=side):
+                step()
+            torch.cuda.current_stream().wait_stream(side)
+        for nxt in xs[1:]:
+            x.copy_(nxt)
+            graph.replay() if graph is not None else step()
+            outs.append(out.clone())
+        torch.cuda.synchronize()
+        return outs, state, conv
+
+    plain, fast = run(False), run(True)
+    for a, b in zip(plain[0], fast[0]):
+        assert torch.equal(a, b)
+    assert torch.equal(plain[1], fast[1]) and torch.equal(plain[2], fast[2])
