@@ -309,6 +309,18 @@ def hbm_peak():
 
 
 # --------------------------------------------------------------------------- main
+def aggregate_over_ranks(ms_local: float, units_local: float, dist, device):
+    """Whole-job figures of a replicated run: (slowest rank's time, units summed over ranks).  `dist` is
+    torch.distributed (initialised) or None for a single process."""
+    if dist is None:
+        return ms_local, units_local
+    t = torch.tensor([ms_local], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    u = torch.tensor([units_local], device=device, dtype=torch.float64)
+    dist.all_reduce(u, op=dist.ReduceOp.SUM)
+    return float(t.item()), float(u.item())
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
@@ -425,15 +437,7 @@ def main():
                 j += 1
             torch.cuda.synchronize()
     clock_info = clocks.summary()
-    if dist is not None:
-        t = torch.tensor([ms_total], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-        tb = torch.tensor([float(w.bytes)], device=device, dtype=torch.float64)
-        dist.all_reduce(tb)
-        total_bytes = float(tb.item())
-    else:
-        total_bytes = float(w.bytes)
+    ms_total, total_bytes = aggregate_over_ranks(ms_total, float(w.bytes), dist, device)
     ms_per_step = ms_total / args.steps
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
 
@@ -458,10 +462,7 @@ def main():
     end.record()
     barrier()
     e2e_ms = max(start.elapsed_time(end), (time.perf_counter() - t0) * 1e3)
-    if dist is not None:
-        t = torch.tensor([e2e_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_ms, _ = aggregate_over_ranks(e2e_ms, 0.0, dist, device)
     e2e_value = total_bytes / (e2e_ms / args.steps * 1e-3) / 1e9
     h2d = args.batch * (4096 + 1024 + 1024 + 4096)
     d2h = args.batch * 4096
