@@ -365,7 +365,7 @@ def main():
     ap.add_argument("--sweep-steps", type=int, default=20)
     ap.add_argument("--kernel-only", action="store_true", help="headline timing only (for profiler captures)")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of one CUDA graph")
-    ap.add_argument("--no-model", action="store_true", help="skip the whole-model decode measurement (BASELINE config 5)")
+    ap.add_argument("--no-model", action="store_true", help="skip the whole-model decode measurement (24-layer random-init model)")
     ap.add_argument("--model-steps", type=int, default=512)
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gdn"],
                     help="with --kernel-only: which kernel family to run (profiler captures of the other families)")
@@ -523,7 +523,7 @@ def main():
 
 
 def run_whole_model(device, rank, world, dist, steps, peak, batch=32, prompt_len=128, warm=4):
-    """BASELINE config 5: random-init Qwen3.5-0.8B architecture (seed 4), packed prefill of 32 prompts x 128 random
+    """Whole-model workload: random-init Qwen3.5-0.8B architecture (seed 4), packed prefill of 32 prompts x 128 random
     token ids per GPU, then `steps` greedy decode steps replayed from one CUDA graph per step.  Attention and
     Gated-DeltaNet run on this package's kernels, the rest is PyTorch glue (cuBLAS GEMMs).  Every rank is an independent
     replica; with more than one rank the sampled ids are all-gathered over NCCL after every step (the only
@@ -626,7 +626,7 @@ def run_sweep(ops, ws, device, peak, steps):
 
 
 def run_prefill_sweep(ops, device, steps, only=None):
-    """Prefill-side operators at the BASELINE shapes: packed varlen causal attention (config 3: B=32, lengths
+    """Prefill-side operators at the benchmark shapes: packed varlen causal attention (B=32, lengths
     ~U[16,512] seed 2, plus a long-prompt shape where the tensor bound applies) and the GDN prefill forms (config 4:
     32 prompts x 128 tokens).  Reported against both rooflines; inputs are regenerated per call site, not rotated
     (every call reads each input once, outputs are larger than the reuse L2 could give)."""

@@ -471,7 +471,7 @@ extern "C" int b200_gdn_chunk_output(const void* q, int64_t q_stride_t, int64_t 
 
 // Packed chunk-64 prefill: the three stages over a batch of sequences packed in one buffer, chunk grid restarting at
 // every cu_seqlens[b], zero state at each sequence start.  The reference has no such call (its chunk path is
-// single-sequence, engine/runner.py:263-267); it is the packed form BASELINE config 4 asks for.
+// single-sequence, engine/runner.py:263-267); it is the packed form a batched prefill (32 prompts in one buffer) needs.
 // Workspace layout (fp32): w | u_base | delta [Nmax,H,64,128] each, g_cumsum [Nmax,H,64], chunk_state [Nmax,H,128,128]
 // with Nmax = total_tokens / 64 + batch (an upper bound of the number of chunks that needs no device read).
 extern "C" int64_t b200_gdn_chunked_prefill_packed_workspace_bytes(int32_t batch, int32_t total_tokens, int32_t num_heads) {

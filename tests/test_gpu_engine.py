@@ -1,4 +1,4 @@
-"""Whole-model stepping (packed prefill, batched decode, CUDA-graph decode) on a reduced-size model of the BASELINE
+"""Whole-model stepping (packed prefill, batched decode, CUDA-graph decode) on a reduced-size model of the benchmark
 architecture against the fp32 full-recomputation restatement of the reference runner (oracle/reference_model.py).
 
 Greedy tokens are compared TEACHER-FORCED (the oracle sees the engine's own history), so one flipped near-tie cannot
