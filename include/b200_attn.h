@@ -109,6 +109,20 @@ int b200_fused_decode_attention(const void* q, int64_t q_stride_b, int64_t q_str
                                 const float* inv_freq, int32_t rotary_dim, void* out, void* workspace, int32_t batch,
                                 int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, b200_stream_t stream);
 
+/* b200_fused_decode_attention with overlap flags (B200_OVERLAP_*, defined below): START lets the kernel begin while the
+ * kernel in front of it still runs; PREFETCH additionally lets it compute the position prefix, gather page ids and
+ * request its first K/V pages before that kernel has finished - pass it only when that kernel writes neither pos, the
+ * block table nor the caches (in a layer stack it is the k-norm).  q, k_new, v_new and gate are always read after it. */
+int b200_fused_decode_attention_overlap(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_new,
+                                        int64_t kn_stride_b, int64_t kn_stride_h, const void* v_new, int64_t vn_stride_b,
+                                        int64_t vn_stride_h, const void* gate, int64_t gate_stride_b, void* k_cache,
+                                        void* v_cache, int64_t kc_stride_p, int64_t kc_stride_h, int64_t kc_stride_s,
+                                        int64_t vc_stride_p, int64_t vc_stride_h, int64_t vc_stride_s, int64_t num_pages,
+                                        const int32_t* block_table, int64_t bt_stride_b, const int64_t* pos,
+                                        const float* inv_freq, int32_t rotary_dim, void* out, void* workspace,
+                                        int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                                        int32_t overlap, b200_stream_t stream);
+
 /* The same fused decode step for callers that cannot allocate device memory (a host that owns the whole GPU and
  * forbids cudaMalloc after start-up, a plugin inside another process, code running under stream capture).  This
  * entry point has NO counterpart in the reference.  Arguments are those of b200_fused_decode_attention without
@@ -271,7 +285,7 @@ int b200_gdn_chunked_prefill_fused(const void* q, int64_t q_stride_t, int64_t q_
  * b200_gdn_gated_rmsnorm: out[r,:] = x[r,:] * rsqrt(mean(x^2) + 1e-6) * weight * silu(z[r,:]) for rows r = (n, head);
  * x and out contiguous [rows, 128], z row (n, head) at z + n * z_stride + head * 128
  * (triton_kernels/gdn_gated_rmsnorm.py:95-140). */
-/* Overlap flags (programmatic dependent launch) of b200_skinny_gemm, b200_add_rmsnorm, b200_swiglu and
+/* Overlap flags (programmatic dependent launch) of b200_(norm_)skinny_gemm, b200_add_rmsnorm, b200_swiglu and
  * b200_gdn_decode_fused; 0 = plain stream order.
  *   START    the kernel may begin while the kernel in front of it in the stream still runs; it reads that kernel's
  *            output, and writes anything, only after that kernel has completed.
@@ -295,13 +309,19 @@ int b200_gdn_decode_fused(const void* fused, int64_t fused_stride, void* conv_st
                           const float* a_log, const void* dt_bias, const float* norm_weight, float* state, void* out,
                           int32_t batch, int32_t num_heads, int32_t head_dim, int32_t overlap, b200_stream_t stream);
 /* Y[M,N] = X[M,K] . W[N,K]^T for decode batches (M <= 32), bf16 in/out, fp32 accumulation: W is streamed once by
- * tensor-map TMA, X staged in shared memory.  N a multiple of 8, K a multiple of 128 up to 1536; x / y rows x_stride /
+ * tensor-map TMA, X staged in shared memory.  N a multiple of 8, K a multiple of 128 up to 1280; x / y rows x_stride /
  * y_stride elements apart (multiples of 8), weight contiguous [N,K]; all 16-byte aligned.  With
  * B200_OVERLAP_START the weight tiles are requested before the preceding kernel in the stream has finished, so
  * `weight` must not be that kernel's output (x may be).
  * Replaces triton_kernels/gemm_2d.py for the decode-step projections of the hidden state. */
 int b200_skinny_gemm(const void* x, int64_t x_stride, const void* weight, void* y, int64_t y_stride, int32_t m,
                      int32_t n, int32_t k, int32_t overlap, b200_stream_t stream);
+/* The gate/up projection of the MLP with its activation folded into the epilogue (one launch instead of two):
+ *   weight = [gate rows | up rows] [2*intermediate, K];  y[:, j] = silu(bf16(x . gate_j)) * bf16(x . up_j)
+ * (triton_kernels/gemm_2d.py on the fused gate/up weight followed by triton_kernels/swiglu.py).  y is
+ * [M, intermediate]; intermediate a multiple of 8; other shapes, alignment and overlap flags as b200_skinny_gemm. */
+int b200_skinny_gemm_swiglu(const void* x, int64_t x_stride, const void* weight, void* y, int64_t y_stride, int32_t m,
+                            int32_t intermediate, int32_t k, int32_t overlap, b200_stream_t stream);
 int b200_add_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x_stride_inner, int32_t inner_count,
                      const void* residual, int64_t residual_stride, const void* weight, void* sum_out, void* norm_out,
                      int32_t rows, int32_t dim, float eps, int32_t overlap, b200_stream_t stream);

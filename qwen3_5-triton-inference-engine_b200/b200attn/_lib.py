@@ -23,6 +23,8 @@ SIGNATURES: dict[str, list] = {
     "b200_paged_decode_combine": [P, P, P, P, P, I32, I32, I32, P],
     "b200_fused_decode_attention": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, P, P, I64, I64, I64, I64, I64, I64,
                                     I64, P, I64, P, P, I32, P, P, I32, I32, I32, I32, P],
+    "b200_fused_decode_attention_overlap": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, P, P, I64, I64, I64, I64, I64,
+                                            I64, I64, P, I64, P, P, I32, P, P, I32, I32, I32, I32, I32, P],
     "b200_fused_decode_attention_static": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, P, P, I64, I64, I64, I64, I64,
                                            I64, I64, P, I64, P, P, I32, P, I32, I32, I32, I32, P],
     "b200_selftest_umma": [I32, P, P, P, P],
@@ -41,6 +43,7 @@ SIGNATURES: dict[str, list] = {
     "b200_gdn_chunked_prefill_packed": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I32, I32, I32,
                                         P, P, P, I64, I64, I32, I32, I32, P],
     "b200_skinny_gemm": [P, I64, P, P, I64, I32, I32, I32, I32, P],
+    "b200_skinny_gemm_swiglu": [P, I64, P, P, I64, I32, I32, I32, I32, P],
     "b200_add_rmsnorm": [P, I64, I64, I32, P, I64, P, P, P, I32, I32, c_float, I32, P],
     "b200_swiglu": [P, I64, P, I32, I32, I32, P],
     "b200_gdn_decode_prep": [P, I64, P, P, P, I64, P, I64, P, P, P, P, P, P, P, I32, I32, I32, P],

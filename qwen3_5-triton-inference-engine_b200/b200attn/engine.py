@@ -222,8 +222,9 @@ class Engine:
         return nxt
 
     def _decode_fused(self, tok: torch.Tensor) -> torch.Tensor:
-        """The same step with every row-wise operator as one launch: about nine launches per layer (two or three of
-        them cuBLAS GEMMs).  The residual add after a layer's MLP is fused into the next layer's input norm.  Kernels
+        """The same step with every row-wise operator as one launch: about eight launches per layer (two of them
+        cuBLAS GEMMs; the SwiGLU is the epilogue of the gate/up projection).  The residual add after a layer's MLP is
+        fused into the next layer's input norm.  Kernels
         of this package that follow one another start early (programmatic dependent launch: weights and states stream
         in while the predecessor finishes); a kernel in front of a cuBLAS or PyTorch kernel never triggers early."""
         cfg = self.cfg
@@ -249,16 +250,19 @@ class Engine:
                 q = ops.add_rmsnorm(fused[:, :qd].view(batch, cfg.num_q_heads, cfg.head_dim), layer["q_norm"], cfg.eps,
                                     overlap=chain)
                 k = ops.add_rmsnorm(fused[:, 2 * qd: 2 * qd + kvd].view(batch, cfg.num_kv_heads, cfg.head_dim),
-                                    layer["k_norm"], cfg.eps, overlap=start)
+                                    layer["k_norm"], cfg.eps, overlap=chain)
                 v = fused[:, 2 * qd + kvd:].view(batch, cfg.num_kv_heads, cfg.head_dim)
                 k_cache, v_cache = self.kv[i]
                 ctx = ops.fused_decode_attention(q, k, v, fused[:, qd: 2 * qd], k_cache, v_cache, self.block_table,
-                                                 self.pos, self.inv_freq, cfg.rotary_dim, self.workspace)
+                                                 self.pos, self.inv_freq, cfg.rotary_dim, self.workspace,
+                                                 overlap=start | ops.OVERLAP_PREFETCH)
                 mixed = glue.gemm_2d(ctx, layer["o_proj"])
-            own_mlp = self._streams_weight(layer["gate_up"])
+            own_mlp = self._streams_weight(layer["gate_up"]) and cfg.intermediate % 8 == 0
             x, h = ops.add_rmsnorm(mixed, layer["ln2"], cfg.eps, residual=x, overlap=chain if own_mlp else start)
-            act = ops.swiglu_fused(self._proj(h, layer["gate_up"], chain), cfg.intermediate,
-                                   overlap=start)
+            if own_mlp:
+                act = ops.skinny_gemm(h, layer["gate_up"], overlap=start, swiglu=True)   # cuBLAS follows: no trigger
+            else:
+                act = ops.swiglu_fused(glue.gemm_2d(h, layer["gate_up"]), cfg.intermediate, overlap=start)
             pending = glue.gemm_2d(act, layer["down"])
         _, h = ops.add_rmsnorm(pending, self.w["norm"], cfg.eps, residual=x, overlap=start)
         nxt = glue.lm_head_argmax(h, self.w["embed"], last_only=False)

@@ -210,9 +210,11 @@ def fused_decode_workspace(device="cuda") -> torch.Tensor:
 
 
 def fused_decode_attention(q, k_new, v_new, gate, k_cache, v_cache, block_table, pos, inv_freq, rotary_dim,
-                           workspace, out=None) -> torch.Tensor:
+                           workspace, out=None, overlap: int = 0) -> torch.Tensor:
     """RoPE(q, k_new) + append + paged attention + sigmoid gate in one launch -> [B, H_q*D] bf16.
-    q [B,H_q,D], k_new/v_new [B,H_kv,D] are the post-norm, PRE-RoPE projections; gate [B, H_q*D]."""
+    q [B,H_q,D], k_new/v_new [B,H_kv,D] are the post-norm, PRE-RoPE projections; gate [B, H_q*D].
+    overlap: OVERLAP_START lets the kernel begin while its predecessor in the stream runs; OVERLAP_PREFETCH also lets it
+    read pos / block_table / cache pages before that predecessor has finished (valid when it writes none of them)."""
     batch, num_q_heads, head_dim = q.shape
     num_kv_heads = k_new.shape[1]
     assert k_new.shape == v_new.shape == (batch, num_kv_heads, head_dim)
@@ -228,12 +230,12 @@ def fused_decode_attention(q, k_new, v_new, gate, k_cache, v_cache, block_table,
     if out is None:
         out = torch.empty((batch, num_q_heads * head_dim), dtype=torch.bfloat16, device=q.device)
     assert out.is_contiguous() and out.shape == (batch, num_q_heads * head_dim)
-    _lib.call("b200_fused_decode_attention", _ptr(q), q.stride(0), q.stride(1), _ptr(k_new), k_new.stride(0),
+    _lib.call("b200_fused_decode_attention_overlap", _ptr(q), q.stride(0), q.stride(1), _ptr(k_new), k_new.stride(0),
               k_new.stride(1), _ptr(v_new), v_new.stride(0), v_new.stride(1), _ptr(gate), gate.stride(0),
               _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), k_cache.stride(1), k_cache.stride(2), v_cache.stride(0),
               v_cache.stride(1), v_cache.stride(2), k_cache.shape[0], _ptr(block_table), block_table.stride(0), _ptr(pos),
               _ptr(inv_freq), int(rotary_dim), _ptr(out), _ptr(workspace), batch, num_q_heads, num_kv_heads, head_dim,
-              _stream())
+              int(overlap), _stream())
     return out
 
 
@@ -695,18 +697,23 @@ def gdn_decode_fused(fused, conv_state, weight4, a_log, dt_bias, norm_weight, st
     return out
 
 
-SKINNY_GEMM_MAX_M, SKINNY_GEMM_MAX_K = 32, 1536
+SKINNY_GEMM_MAX_M, SKINNY_GEMM_MAX_K = 32, 1280
 
 
-def skinny_gemm(x, weight, overlap: int = 0):
-    """y = x @ weight^T for a decode batch (x [M <= 32, K <= 1536] bf16, weight [N, K] bf16 contiguous), the weight
-    streamed once from HBM (triton_kernels/gemm_2d.py for the decode-step projections)."""
+def skinny_gemm(x, weight, overlap: int = 0, swiglu: bool = False):
+    """y = x @ weight^T for a decode batch (x [M <= 32, K <= 1280] bf16, weight [N, K] bf16 contiguous), the weight
+    streamed once from HBM (triton_kernels/gemm_2d.py for the decode-step projections).
+    swiglu=True: weight = [gate rows | up rows] [2*I, K] and the result is silu(bf16(x.gate_j)) * bf16(x.up_j), [M, I]
+    (the fused gate/up projection followed by triton_kernels/swiglu.py, one launch)."""
     assert x.ndim == 2 and weight.ndim == 2 and x.shape[1] == weight.shape[1]
     assert x.dtype == weight.dtype == torch.bfloat16 and weight.is_contiguous() and x.stride(1) == 1
     m, k = x.shape
     n = weight.shape[0]
+    if swiglu:
+        assert n % 2 == 0
+        n //= 2
     _require_cuda(x, weight)
     y = torch.empty((m, n), dtype=torch.bfloat16, device=x.device)
-    _lib.call("b200_skinny_gemm", _ptr(x), x.stride(0), _ptr(weight), _ptr(y), y.stride(0), m, n, k, int(overlap),
-              _stream())
+    _lib.call("b200_skinny_gemm_swiglu" if swiglu else "b200_skinny_gemm", _ptr(x), x.stride(0), _ptr(weight), _ptr(y),
+              y.stride(0), m, n, k, int(overlap), _stream())
     return y

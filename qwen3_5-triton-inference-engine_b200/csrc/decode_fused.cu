@@ -56,7 +56,7 @@ struct FusedDecodeParams {
   float* partials;
   int* counters;
   int* err;
-  int batch, num_kv_heads, rotary_half;
+  int batch, num_kv_heads, rotary_half, overlap;
   float scale;
 };
 
@@ -207,6 +207,10 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
     for (int s = 0; s < FD_RING; ++s) mbar_init(&bars[warp][s], 1);
     mbar_fence_init();
   }
+  // Started early (programmatic dependent launch): with the PREFETCH flag the position prefix, the page-id gathers and
+  // the first K/V page copies below overlap with the predecessor (it must not write pos, the block table or the
+  // caches); q, k_new, v_new and gate are the predecessor's output and are read only after the wait further down.
+  if (!(p.overlap & OVERLAP_PREFETCH)) pdl_wait();
 
   // ---- exclusive prefix of units per sequence: units_b = cdiv(pos[b], 16) + 1
   for (int b = tid; b < batch; b += FD_THREADS) {
@@ -238,7 +242,10 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   const int chunk = max((total + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x), FD_WARPS);
   const int r0 = blockIdx.x * chunk;
   const int r1 = min(r0 + chunk, total);
-  if (r0 >= r1) return;
+  if (r0 >= r1) {
+    pdl_wait();  // an idle CTA still orders the grid after its predecessor
+    return;
+  }
 
   // ---- per-warp issue cursor: walks the same unit sequence as the consumer, FD_RING tiles ahead.
   // Tile sequence of a warp: K(u0), V(u0), K(u1), V(u1), ...; tile n lives in ring slot n % FD_RING.
@@ -326,6 +333,7 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
     }
     finish_store(p, sg.b, sg.h * GROUP + hh, d0, a4, l_fin, gate_bits);
   };
+  pdl_wait();  // from here on the predecessor's q / k_new / v_new / gate are read and global memory is written
   stage_q(q_s, p, seg.b, seg.h, pos_s[seg.b], tid);
   __syncthreads();
   while (seg.start < r1) {
@@ -375,7 +383,9 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
           else decode_accumulate<true>(st, tile, valid, b0, b1, alpha0, alpha1, lane);
         }
         ++consumed;
-        fence_proxy_async();  // generic-proxy writes to this slot (row clears, the appended token) before the next bulk copy
+        // generic-proxy writes to this slot (row clears of a partly filled page, the appended token) are ordered before
+        // the next bulk copy into it; a full page was only read
+        if (valid < PAGE) fence_proxy_async();
         __syncwarp();
         if (!dead) issue_next();
       }
@@ -485,7 +495,7 @@ static const CUtensorMap* cache_tile_map(const void* base, int64_t rows) {
 
 extern "C" int64_t b200_fused_decode_workspace_bytes(void) { return FD_WORKSPACE_BYTES; }
 
-extern "C" int b200_fused_decode_attention(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_new,
+static int fused_decode_impl(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_new,
                                            int64_t kn_stride_b, int64_t kn_stride_h, const void* v_new,
                                            int64_t vn_stride_b, int64_t vn_stride_h, const void* gate,
                                            int64_t gate_stride_b, void* k_cache, void* v_cache, int64_t kc_stride_p,
@@ -494,7 +504,7 @@ extern "C" int b200_fused_decode_attention(const void* q, int64_t q_stride_b, in
                                            const int32_t* block_table, int64_t bt_stride_b, const int64_t* pos,
                                            const float* inv_freq, int32_t rotary_dim, void* out, void* workspace,
                                            int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
-                                           b200_stream_t stream) {
+                                           int32_t overlap, b200_stream_t stream) {
   B200_REQUIRE(batch > 0 && batch <= FD_MAX_BATCH, "fused_decode_attention: batch must be in [1, %d] (got %d)",
                FD_MAX_BATCH, batch);
   B200_REQUIRE(head_dim == HEAD_DIM, "fused_decode_attention: head_dim must be %d (got %d)", HEAD_DIM, head_dim);
@@ -556,10 +566,13 @@ extern "C" int b200_fused_decode_attention(const void* q, int64_t q_stride_b, in
   p.batch = batch;
   p.num_kv_heads = num_kv_heads;
   p.rotary_half = rotary_dim / 2;
+  p.overlap = overlap;
   p.scale = 1.0f / sqrtf(static_cast<float>(head_dim));
   int grid = sm_count();
   if (grid > FD_MAX_CTAS) grid = FD_MAX_CTAS;
-  fused_decode_kernel<<<grid, FD_THREADS, FD_SMEM_TOTAL, reinterpret_cast<cudaStream_t>(stream)>>>(p, *map_k, *map_v);
+  if (launch_pdl((overlap & OVERLAP_START) != 0, fused_decode_kernel, dim3(grid), dim3(FD_THREADS), FD_SMEM_TOTAL,
+                 reinterpret_cast<cudaStream_t>(stream), p, *map_k, *map_v) != cudaSuccess)
+    return fail(ERR_LAUNCH, "fused_decode_attention: %s", cudaGetErrorString(cudaGetLastError()));
   return check_launch("fused_decode_attention");
 }
 
@@ -591,6 +604,35 @@ static void* static_workspace_for_current_device() {
     cached[dev] = ptr;
   }
   return cached[dev];
+}
+
+extern "C" int b200_fused_decode_attention(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_new,
+                                           int64_t kn_stride_b, int64_t kn_stride_h, const void* v_new,
+                                           int64_t vn_stride_b, int64_t vn_stride_h, const void* gate,
+                                           int64_t gate_stride_b, void* k_cache, void* v_cache, int64_t kc_stride_p,
+                                           int64_t kc_stride_h, int64_t kc_stride_s, int64_t vc_stride_p,
+                                           int64_t vc_stride_h, int64_t vc_stride_s, int64_t num_pages,
+                                           const int32_t* block_table, int64_t bt_stride_b, const int64_t* pos,
+                                           const float* inv_freq, int32_t rotary_dim, void* out, void* workspace,
+                                           int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                                           b200_stream_t stream) {
+  return fused_decode_impl(q, q_stride_b, q_stride_h, k_new, kn_stride_b, kn_stride_h, v_new, vn_stride_b, vn_stride_h,
+                           gate, gate_stride_b, k_cache, v_cache, kc_stride_p, kc_stride_h, kc_stride_s, vc_stride_p,
+                           vc_stride_h, vc_stride_s, num_pages, block_table, bt_stride_b, pos, inv_freq, rotary_dim, out,
+                           workspace, batch, num_q_heads, num_kv_heads, head_dim, 0, stream);
+}
+
+extern "C" int b200_fused_decode_attention_overlap(
+    const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_new, int64_t kn_stride_b, int64_t kn_stride_h,
+    const void* v_new, int64_t vn_stride_b, int64_t vn_stride_h, const void* gate, int64_t gate_stride_b, void* k_cache,
+    void* v_cache, int64_t kc_stride_p, int64_t kc_stride_h, int64_t kc_stride_s, int64_t vc_stride_p,
+    int64_t vc_stride_h, int64_t vc_stride_s, int64_t num_pages, const int32_t* block_table, int64_t bt_stride_b,
+    const int64_t* pos, const float* inv_freq, int32_t rotary_dim, void* out, void* workspace, int32_t batch,
+    int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, int32_t overlap, b200_stream_t stream) {
+  return fused_decode_impl(q, q_stride_b, q_stride_h, k_new, kn_stride_b, kn_stride_h, v_new, vn_stride_b, vn_stride_h,
+                           gate, gate_stride_b, k_cache, v_cache, kc_stride_p, kc_stride_h, kc_stride_s, vc_stride_p,
+                           vc_stride_h, vc_stride_s, num_pages, block_table, bt_stride_b, pos, inv_freq, rotary_dim, out,
+                           workspace, batch, num_q_heads, num_kv_heads, head_dim, overlap, stream);
 }
 
 // Same computation and arguments as b200_fused_decode_attention, minus the workspace.

@@ -4,11 +4,17 @@
 // decode step (README-EN.md:116).
 //
 // The product is HBM-bound on W (M is tiny), so the kernel is built like the decode-attention kernels: X is staged once
-// per CTA in shared memory (one bulk copy per row), every warp owns 16 rows of W and streams them through a private
-// ring of 4 KiB tiles (tensor-map TMA box {64 k, 16 rows, 2 k-blocks}, 128-byte swizzle -> conflict-free ldmatrix,
-// one mbarrier per tile, no cluster multicast), and multiplies with mma.sync m16n8k16 taking the W rows as the MMA M dimension and the batch as N
-// (M <= 32 is far too thin for a tcgen05 tile).  A CTA of four warps covers 64 rows of W; CTAs walk the row blocks
-// persistently, so X is read once per CTA however large N is.  Every wait is bounded.
+// per CTA in shared memory (one bulk copy per row), every warp streams rows of W through a private ring of 4 KiB tiles
+// (tensor-map TMA, 128-byte swizzle -> conflict-free ldmatrix, one mbarrier per tile, no cluster multicast), and
+// multiplies with mma.sync m16n8k16 taking the W rows as the MMA M dimension and the batch as N (M <= 32 is far too
+// thin for a tcgen05 tile).  CTAs walk the row blocks persistently, so X is read once per CTA however large N is.
+// Every wait is bounded.
+//
+// Two forms.  Plain: a warp's tile is 16 consecutive rows of W (one box {64 k, 16 rows, 2 k-blocks}), a CTA of four
+// warps covers 64 outputs.  SwiGLU (W = [gate rows | up rows], the fused gate/up projection followed by
+// triton_kernels/swiglu.py): a warp's tile is 8 gate rows stacked on the 8 matching up rows (two boxes of 8 rows), so the
+// accumulator fragment of a thread holds gate_j (row r) and up_j (row r + 8) of the same output j and the activation is
+// applied in registers; a CTA covers 32 outputs.
 #include "b200_attn.h"
 #include "umma.cuh"
 
@@ -16,36 +22,41 @@ namespace b200 {
 
 constexpr int SG_WARPS = 4;
 constexpr int SG_THREADS = SG_WARPS * 32;
-constexpr int SG_ROWS = 16 * SG_WARPS;   // W rows per CTA step
-constexpr int SG_RING = 6;               // 4 KiB tiles in flight per warp
+constexpr int SG_ROWS = 16 * SG_WARPS;   // outputs per CTA step, plain form (8 * SG_WARPS in the SwiGLU form)
 constexpr int SG_TILE_K = 128;           // k elements per tile: two swizzled blocks of [16 rows][64 k] bf16
 constexpr int SG_TILE_BYTES = 2 * 16 * 128;
+constexpr int SG_RING = 8;                        // tiles in flight per warp
+constexpr int SG_RING_BYTES = SG_RING * SG_TILE_BYTES;
 constexpr int SG_MAX_M = 32;
-constexpr int SG_MAX_K = 1536;           // X staging: 32 x (K*2 + 16) bytes
+constexpr int SG_MAX_K = 1280;           // X staging: 32 x (K*2 + 16) bytes next to 128 KiB of weight rings
 
 struct SkinnyGemmParams {
-  const __nv_bfloat16* x;
-  __nv_bfloat16* y;
+  const __nv_bfloat16* x;  // [M, K]
+  __nv_bfloat16* y;        // [M, N]
   int64_t x_stride, y_stride;
   int* err;
-  int m, n, k, row_blocks, overlap;
+  int m, n, k, row_blocks, overlap, up_row0;  // n: outputs; up_row0: first W row of the `up` half (SwiGLU form)
 };
 
+template <bool SWIGLU>
 __global__ void __launch_bounds__(SG_THREADS, 1)
 skinny_gemm_kernel(const __grid_constant__ SkinnyGemmParams p, const __grid_constant__ CUtensorMap map_w) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ uint64_t bars[SG_WARPS][SG_RING];
+  constexpr int SLOT_BYTES = SG_TILE_BYTES;
+  constexpr int RING = SG_RING;
+  constexpr int OUT = SWIGLU ? 8 * SG_WARPS : SG_ROWS;  // outputs per CTA step
+  __shared__ uint64_t bars[SG_WARPS][RING];
   __shared__ uint64_t bar_x;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  uint8_t* ring = smem + warp * (SG_RING * SG_TILE_BYTES);
-  uint8_t* stage = smem + SG_WARPS * SG_RING * SG_TILE_BYTES;          // [32 batch][64 n] bf16 output staging, 4 KiB
+  uint8_t* ring = smem + warp * SG_RING_BYTES;
+  uint8_t* stage = smem + SG_WARPS * SG_RING_BYTES;                    // [32 batch][OUT] bf16 output staging, <= 4 KiB
   uint8_t* xs = stage + SG_MAX_M * SG_ROWS * 2;                        // [32][x_pitch] bf16
   const int x_pitch = p.k * 2 + 16;                                    // bytes; the 16 shift the banks row by row
   const int k_tiles = p.k / SG_TILE_K;
 
   if (lane == 0) {
-    for (int s = 0; s < SG_RING; ++s) mbar_init(&bars[warp][s], 1);
+    for (int s = 0; s < RING; ++s) mbar_init(&bars[warp][s], 1);
     if (warp == 0) mbar_init(&bar_x, 1);
     mbar_fence_init();
   }
@@ -55,25 +66,31 @@ skinny_gemm_kernel(const __grid_constant__ SkinnyGemmParams p, const __grid_cons
   __syncwarp();
   auto issue = [&](int t) {
     const int rb = blockIdx.x + (t / k_tiles) * gridDim.x, kt = t % k_tiles;
-    const int slot = t % SG_RING;
-    mbar_expect_tx(&bars[warp][slot], SG_TILE_BYTES);
-    tma_load_3d(ring + slot * SG_TILE_BYTES, &map_w, 0, rb * SG_ROWS + warp * 16, kt * 2, &bars[warp][slot]);
+    const int slot = t % RING;
+    mbar_expect_tx(&bars[warp][slot], SLOT_BYTES);
+    if (SWIGLU) {  // map_w has 8-row boxes: gate rows to the first half of the tile, up rows to the second
+      tma_load_3d(ring + slot * SLOT_BYTES, &map_w, 0, rb * OUT + warp * 8, kt * 2, &bars[warp][slot]);
+      tma_load_3d(ring + slot * SLOT_BYTES + SG_TILE_BYTES / 2, &map_w, 0, p.up_row0 + rb * OUT + warp * 8, kt * 2,
+                  &bars[warp][slot]);
+    } else {
+      tma_load_3d(ring + slot * SLOT_BYTES, &map_w, 0, rb * OUT + warp * 16, kt * 2, &bars[warp][slot]);
+    }
   };
   if (p.overlap & OVERLAP_TRIGGER) pdl_trigger();
   if (lane == 0) {
-    for (int t = 0; t < SG_RING && t < total_tiles; ++t) issue(t);  // weights: independent of the predecessor
+    for (int t = 0; t < RING && t < total_tiles; ++t) issue(t);  // weights: independent of the predecessor
   }
   pdl_wait();  // X is the predecessor's output
-  // X -> shared memory while the first W tiles are in flight: one bulk copy per row (rows beyond M are zeroed)
+  // X -> shared memory while the first W tiles are in flight (rows beyond M are zeroed)
+  for (int i = tid; i < (SG_MAX_M - p.m) * (p.k >> 3); i += SG_THREADS) {
+    const int r = p.m + i / (p.k >> 3), c = i % (p.k >> 3);
+    *reinterpret_cast<uint4*>(xs + r * x_pitch + c * 16) = make_uint4(0, 0, 0, 0);
+  }
   __syncthreads();  // bar_x is initialised
   if (warp == 0) {
     if (lane == 0) mbar_expect_tx(&bar_x, static_cast<uint32_t>(p.m) * p.k * 2);
     __syncwarp();
     if (lane < p.m) bulk_g2s(xs + lane * x_pitch, p.x + static_cast<int64_t>(lane) * p.x_stride, p.k * 2, &bar_x);
-  }
-  for (int i = tid; i < (SG_MAX_M - p.m) * (p.k >> 3); i += SG_THREADS) {
-    const int r = p.m + i / (p.k >> 3), c = i % (p.k >> 3);
-    *reinterpret_cast<uint4*>(xs + r * x_pitch + c * 16) = make_uint4(0, 0, 0, 0);
   }
   __syncthreads();
   bool ok = mbar_wait_bounded(&bar_x, 0);
@@ -90,61 +107,75 @@ skinny_gemm_kernel(const __grid_constant__ SkinnyGemmParams p, const __grid_cons
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
     for (int kt = 0; kt < k_tiles && ok; ++kt, ++t) {
-      const int slot = t % SG_RING;
-      if (!mbar_wait_bounded(&bars[warp][slot], (t / SG_RING) & 1)) {
+      const int slot = t % RING;
+      if (!mbar_wait_bounded(&bars[warp][slot], (t / RING) & 1)) {
         ok = false;
         break;
       }
-      const uint32_t tile = smem_u32(ring + slot * SG_TILE_BYTES);
+      const uint32_t tile = smem_u32(ring + slot * SLOT_BYTES);
 #pragma unroll
       for (int ks = 0; ks < SG_TILE_K / 16; ++ks) {
         uint32_t a[4], b01[4], b23[4];
-        ldmatrix_x4(a, tile + (ks >> 2) * (16 * 128) + a_row * 128 + ((((ks & 3) * 2 + a_par) ^ (a_row & 7)) << 4));
+        // plain: [k-block][16 rows][128 B]; SwiGLU: [gate | up][k-block][8 rows][128 B]; 16-byte chunks XOR-swizzled by row
+        const uint32_t a_off = (SWIGLU ? (a_row >> 3) * (SG_TILE_BYTES / 2) + (ks >> 2) * (8 * 128) + (a_row & 7) * 128
+                                       : (ks >> 2) * (16 * 128) + a_row * 128) +
+                               ((((ks & 3) * 2 + a_par) ^ (a_row & 7)) << 4);
         const uint32_t xk = xs_base + b_lane + (kt * SG_TILE_K + ks * 16) * 2;
         ldmatrix_x4(b01, xk);                   // batch rows 0-15: (b0, b1) of n8 tiles 0 and 1
         ldmatrix_x4(b23, xk + 16 * x_pitch);    // batch rows 16-31
+        ldmatrix_x4(a, tile + a_off);
         mma_bf16_16816(acc[0], a, b01[0], b01[1]);
         mma_bf16_16816(acc[1], a, b01[2], b01[3]);
         mma_bf16_16816(acc[2], a, b23[0], b23[1]);
         mma_bf16_16816(acc[3], a, b23[2], b23[3]);
       }
-      __syncwarp();  // every lane has read the tile: its slot can take the tile SG_RING ahead
-      if (lane == 0 && t + SG_RING < total_tiles) issue(t + SG_RING);
+      __syncwarp();  // every lane has read the tile: its slot can take the tile RING ahead
+      if (lane == 0 && t + RING < total_tiles) issue(t + RING);
     }
-    // acc[nt]: rows (W row = lane/4, +8), cols (batch = nt*8 + (lane%4)*2, +1)  ->  stage[batch][n] -> Y
+    // acc[nt]: rows (tile row = lane/4, +8), cols (batch = nt*8 + (lane%4)*2, +1)  ->  stage[batch][output] -> Y
     __syncthreads();  // the previous block's staging has been written out
     {
       __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage);
-      const int nr = warp * 16 + (lane >> 2), bc = (lane & 3) * 2;
+      const int bc = (lane & 3) * 2;
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt) {
-        st[(nt * 8 + bc) * SG_ROWS + nr] = __float2bfloat16_rn(acc[nt][0]);
-        st[(nt * 8 + bc + 1) * SG_ROWS + nr] = __float2bfloat16_rn(acc[nt][1]);
-        st[(nt * 8 + bc) * SG_ROWS + nr + 8] = __float2bfloat16_rn(acc[nt][2]);
-        st[(nt * 8 + bc + 1) * SG_ROWS + nr + 8] = __float2bfloat16_rn(acc[nt][3]);
+        if (SWIGLU) {
+          // rows r and r + 8 of the tile are gate_j and up_j; the projection is a bf16 tensor in the reference
+          const int j = warp * 8 + (lane >> 2);
+          const float g0 = round_bf16(acc[nt][0]), g1 = round_bf16(acc[nt][1]);
+          const float u0 = round_bf16(acc[nt][2]), u1 = round_bf16(acc[nt][3]);
+          st[(nt * 8 + bc) * OUT + j] = __float2bfloat16_rn(g0 / (1.0f + expf(-g0)) * u0);
+          st[(nt * 8 + bc + 1) * OUT + j] = __float2bfloat16_rn(g1 / (1.0f + expf(-g1)) * u1);
+        } else {
+          const int nr = warp * 16 + (lane >> 2);
+          st[(nt * 8 + bc) * OUT + nr] = __float2bfloat16_rn(acc[nt][0]);
+          st[(nt * 8 + bc + 1) * OUT + nr] = __float2bfloat16_rn(acc[nt][1]);
+          st[(nt * 8 + bc) * OUT + nr + 8] = __float2bfloat16_rn(acc[nt][2]);
+          st[(nt * 8 + bc + 1) * OUT + nr + 8] = __float2bfloat16_rn(acc[nt][3]);
+        }
       }
     }
     __syncthreads();
-    for (int i = tid; i < SG_MAX_M * (SG_ROWS / 8); i += SG_THREADS) {
-      const int r = i / (SG_ROWS / 8), c = i % (SG_ROWS / 8);
-      const int n0 = rb * SG_ROWS + c * 8;
+    for (int i = tid; i < SG_MAX_M * (OUT / 8); i += SG_THREADS) {
+      const int r = i / (OUT / 8), c = i % (OUT / 8);
+      const int n0 = rb * OUT + c * 8;
       if (r < p.m && n0 < p.n)  // N is a multiple of 8: a 16-byte chunk is inside or outside as a whole
         *reinterpret_cast<uint4*>(p.y + static_cast<int64_t>(r) * p.y_stride + n0) =
-            *reinterpret_cast<const uint4*>(stage + (r * SG_ROWS + c * 8) * 2);
+            *reinterpret_cast<const uint4*>(stage + (r * OUT + c * 8) * 2);
     }
   }
   if (!ok) {
     if (lane == 0) atomicExch(p.err, 1);
     // let this warp's copies in flight land before the shared memory goes away
-    for (int s = 0; s < SG_RING; ++s) mbar_wait_bounded(&bars[warp][s], 0, 1u << 12);
+    for (int s = 0; s < RING; ++s) mbar_wait_bounded(&bars[warp][s], 0, 1u << 12);
   }
 }
 
-static const CUtensorMap* cache_weight_map(const void* base, int64_t n, int64_t k) {
+static const CUtensorMap* cache_weight_map(const void* base, int64_t n, int64_t k, int box_rows) {
   struct Entry {
     const void* base;
     int64_t n, k;
-    int dev;
+    int dev, box_rows;
     CUtensorMap map;
   };
   constexpr int N = 128;  // a model has a fixed set of weight matrices
@@ -153,14 +184,17 @@ static const CUtensorMap* cache_weight_map(const void* base, int64_t n, int64_t 
   int dev = 0;
   cudaGetDevice(&dev);
   for (int i = 0; i < used; ++i)
-    if (entries[i].base == base && entries[i].n == n && entries[i].k == k && entries[i].dev == dev) return &entries[i].map;
+    if (entries[i].base == base && entries[i].n == n && entries[i].k == k && entries[i].dev == dev &&
+        entries[i].box_rows == box_rows)
+      return &entries[i].map;
   Entry& e = entries[next];
-  if (!encode_tile_map(&e.map, base, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(k) * 2, 16, 2))
+  if (!encode_tile_map(&e.map, base, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(k) * 2, box_rows, 2))
     return nullptr;
   e.base = base;
   e.n = n;
   e.k = k;
   e.dev = dev;
+  e.box_rows = box_rows;
   next = (next + 1) % N;
   if (used < N) ++used;
   return &e.map;
@@ -170,43 +204,77 @@ static const CUtensorMap* cache_weight_map(const void* base, int64_t n, int64_t 
 
 using namespace b200;
 
-extern "C" int b200_skinny_gemm(const void* x, int64_t x_stride, const void* weight, void* y, int64_t y_stride,
-                                int32_t m, int32_t n, int32_t k, int32_t overlap, b200_stream_t stream) {
-  B200_REQUIRE(m > 0 && m <= SG_MAX_M, "skinny_gemm: M must be in [1, %d] (got %d)", SG_MAX_M, m);
-  B200_REQUIRE(n > 0 && n % 8 == 0 && k >= SG_TILE_K && k % SG_TILE_K == 0 && k <= SG_MAX_K,
-               "skinny_gemm: N must be a multiple of 8, K a multiple of %d up to %d (got N=%d K=%d)", SG_TILE_K,
-               SG_MAX_K, n, k);
-  B200_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(y) && x_stride % 8 == 0 && y_stride % 8 == 0,
-               "skinny_gemm: pointers must be 16-byte aligned, row strides multiples of 8 elements");
-  const CUtensorMap* map = cache_weight_map(weight, n, k);
-  if (!map) return fail(ERR_RUNTIME, "skinny_gemm: cannot encode the weight tensor map");
-  const int smem = SG_WARPS * SG_RING * SG_TILE_BYTES + SG_MAX_M * SG_ROWS * 2 + SG_MAX_M * (SG_MAX_K * 2 + 16) + 1024;
+template <bool SWIGLU>
+static int launch_skinny(SkinnyGemmParams p, const void* weight, int w_rows, cudaStream_t stream, const char* what) {
+  const CUtensorMap* map = cache_weight_map(weight, w_rows, p.k, SWIGLU ? 8 : 16);
+  if (!map) return fail(ERR_RUNTIME, "%s: cannot encode the weight tensor map", what);
+  constexpr int smem_max = SG_WARPS * SG_RING_BYTES + SG_MAX_M * SG_ROWS * 2 + SG_MAX_M * (SG_MAX_K * 2 + 16) + 1024;
+  static_assert(smem_max <= 227 * 1024, "weight rings + X staging must fit the 227 KiB a CTA may use");
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    if (cudaFuncSetAttribute(skinny_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return fail(ERR_RUNTIME, "skinny_gemm: cannot raise dynamic shared memory to %d", smem);
+    if (cudaFuncSetAttribute(skinny_gemm_kernel<SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max) !=
+        cudaSuccess)
+      return fail(ERR_RUNTIME, "%s: cannot raise dynamic shared memory to %d", what, smem_max);
     configured[dev] = true;
   }
-  SkinnyGemmParams p;
+  p.err = wait_timeout_flag();
+  if (!p.err) return fail(ERR_RUNTIME, "%s: no error flag", what);
+  constexpr int out_per_cta = SWIGLU ? 8 * SG_WARPS : SG_ROWS;
+  p.row_blocks = (p.n + out_per_cta - 1) / out_per_cta;
+  int grid = p.row_blocks;
+  const int sms = sm_count();
+  if (grid > sms) grid = sms;
+  const int dyn = SG_WARPS * SG_RING_BYTES + SG_MAX_M * SG_ROWS * 2 + SG_MAX_M * (p.k * 2 + 16) + 1024;
+  if (launch_pdl((p.overlap & OVERLAP_START) != 0, skinny_gemm_kernel<SWIGLU>, dim3(grid), dim3(SG_THREADS), dyn, stream,
+                 p, *map) != cudaSuccess)
+    return fail(ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(cudaGetLastError()));
+  return check_launch(what);
+}
+
+static int check_skinny_shape(const char* what, int m, int n, int k) {
+  B200_REQUIRE(m > 0 && m <= SG_MAX_M, "%s: M must be in [1, %d] (got %d)", what, SG_MAX_M, m);
+  B200_REQUIRE(n > 0 && n % 8 == 0 && k >= SG_TILE_K && k % SG_TILE_K == 0 && k <= SG_MAX_K,
+               "%s: N must be a multiple of 8, K a multiple of %d up to %d (got N=%d K=%d)", what, SG_TILE_K, SG_MAX_K, n,
+               k);
+  return OK;
+}
+
+extern "C" int b200_skinny_gemm(const void* x, int64_t x_stride, const void* weight, void* y, int64_t y_stride,
+                                int32_t m, int32_t n, int32_t k, int32_t overlap, b200_stream_t stream) {
+  int rc = check_skinny_shape("skinny_gemm", m, n, k);
+  if (rc != OK) return rc;
+  B200_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(y) && x_stride % 8 == 0 && y_stride % 8 == 0,
+               "skinny_gemm: pointers must be 16-byte aligned, row strides multiples of 8 elements");
+  SkinnyGemmParams p = {};
   p.x = static_cast<const __nv_bfloat16*>(x);
   p.y = static_cast<__nv_bfloat16*>(y);
   p.x_stride = x_stride;
   p.y_stride = y_stride;
-  p.err = wait_timeout_flag();
-  if (!p.err) return fail(ERR_RUNTIME, "skinny_gemm: no error flag");
   p.m = m;
   p.n = n;
   p.k = k;
-  p.row_blocks = (n + SG_ROWS - 1) / SG_ROWS;
   p.overlap = overlap;
-  int grid = p.row_blocks;
-  const int sms = sm_count();
-  if (grid > sms) grid = sms;
-  const int dyn = SG_WARPS * SG_RING * SG_TILE_BYTES + SG_MAX_M * SG_ROWS * 2 + SG_MAX_M * (k * 2 + 16) + 1024;
-  if (launch_pdl((overlap & OVERLAP_START) != 0, skinny_gemm_kernel, dim3(grid), dim3(SG_THREADS), dyn, reinterpret_cast<cudaStream_t>(stream), p, *map) !=
-      cudaSuccess)
-    return fail(ERR_LAUNCH, "skinny_gemm: %s", cudaGetErrorString(cudaGetLastError()));
-  return check_launch("skinny_gemm");
+  return launch_skinny<false>(p, weight, n, reinterpret_cast<cudaStream_t>(stream), "skinny_gemm");
+}
+
+extern "C" int b200_skinny_gemm_swiglu(const void* x, int64_t x_stride, const void* weight, void* y, int64_t y_stride,
+                                       int32_t m, int32_t intermediate, int32_t k, int32_t overlap,
+                                       b200_stream_t stream) {
+  int rc = check_skinny_shape("skinny_gemm_swiglu", m, intermediate, k);
+  if (rc != OK) return rc;
+  B200_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(y) && x_stride % 8 == 0 && y_stride % 8 == 0,
+               "skinny_gemm_swiglu: pointers must be 16-byte aligned, row strides multiples of 8 elements");
+  SkinnyGemmParams p = {};
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.y = static_cast<__nv_bfloat16*>(y);
+  p.x_stride = x_stride;
+  p.y_stride = y_stride;
+  p.m = m;
+  p.n = intermediate;
+  p.k = k;
+  p.overlap = overlap;
+  p.up_row0 = intermediate;
+  return launch_skinny<true>(p, weight, 2 * intermediate, reinterpret_cast<cudaStream_t>(stream), "skinny_gemm_swiglu");
 }

@@ -268,3 +268,64 @@ def test_decode_under_cuda_graph(ops):
         assert maxabs(out_s, ref) < TOL, f"step {i}"
     assert torch.equal(pos.cpu(), p)
     no_timeouts()
+
+
+def test_overlapped_decode_attention_in_graph_equals_plain(ops):
+    """q-norm -> k-norm -> fused decode attention launched with the overlap flags (the attention kernel starts while the
+    k-norm runs and requests its first pages before it waits) and replayed from a CUDA graph with new projections every
+    replay, against the same chain in plain stream order: outputs and caches must be the same bytes."""
+    lengths = [30, 3, 200, 1025]
+    steps = 6
+    c = make_paged_case(lengths, seed=78, slack_tokens=steps + 4)
+    d = to_dev(c)
+    inv_d = rope_inv_freq().to(DEV)
+    b = len(lengths)
+    gen = torch.Generator().manual_seed(2)
+    rows = [bf16_randn(b, (8 + 8 + 2 + 2) * 256, gen=gen).to(DEV) for _ in range(steps)]
+    qw = (torch.randn(256, generator=gen) * 0.1).to(torch.bfloat16).to(DEV)
+    kw = (torch.randn(256, generator=gen) * 0.1).to(torch.bfloat16).to(DEV)
+
+    def run(overlapped: bool):
+        fused = rows[0].clone()
+        kc, vc, pos = d["k_cache"].clone(), d["v_cache"].clone(), d["pos"].clone()
+        ws = ops.fused_decode_workspace(DEV)
+        out = torch.empty(b, 2048, dtype=torch.bfloat16, device=DEV)
+        chain = ops.OVERLAP_START | ops.OVERLAP_TRIGGER if overlapped else 0
+        last = ops.OVERLAP_START | ops.OVERLAP_PREFETCH if overlapped else 0
+
+        def step():
+            q = ops.add_rmsnorm(fused[:, :2048].view(b, 8, 256), qw, 1e-6, overlap=chain)
+            k = ops.add_rmsnorm(fused[:, 4096:4608].view(b, 2, 256), kw, 1e-6, overlap=chain)
+            v = fused[:, 4608:].view(b, 2, 256)
+            ops.fused_decode_attention(q, k, v, fused[:, 2048:4096], kc, vc, d["block_table"], pos, inv_d, 64, ws,
+                                       out=out, overlap=last)
+            pos.add_(1)
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        outs = [out.clone()]
+        graph = None
+        if overlapped:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            graph.replay()                       # the capture itself does not execute
+            outs.append(out.clone())
+        else:
+            step()
+            outs.append(out.clone())
+        for nxt in rows[1:]:
+            fused.copy_(nxt)
+            graph.replay() if graph is not None else step()
+            outs.append(out.clone())
+        torch.cuda.synchronize()
+        return outs, kc, vc, pos
+
+    plain, fast = run(False), run(True)
+    no_timeouts()
+    for x, y in zip(plain[0], fast[0]):
+        assert torch.equal(x, y)
+    assert torch.equal(plain[1], fast[1]) and torch.equal(plain[2], fast[2]) and torch.equal(plain[3], fast[3])

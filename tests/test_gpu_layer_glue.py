@@ -118,7 +118,7 @@ def test_gdn_decode_fused_equals_chain(mods, batch, prefetch):
 
 
 @pytest.mark.parametrize("m,n,k", [(32, 8224, 1024), (1, 5120, 1024), (17, 7168, 1024), (32, 248320, 1024), (8, 512, 256),
-                                   (32, 1024, 1536)])
+                                   (32, 1024, 1280)])
 def test_skinny_gemm(mods, m, n, k):
     """Weight-streaming decode GEMM against an fp32 matmul of the same bf16 operands (exact products, fp32
     accumulation on both sides: only the summation order and the final bf16 rounding differ)."""
@@ -187,3 +187,18 @@ def test_overlapped_chain_in_graph_equals_plain(mods):
     for a, b in zip(plain[0], fast[0]):
         assert torch.equal(a, b)
     assert torch.equal(plain[1], fast[1]) and torch.equal(plain[2], fast[2])
+
+
+@pytest.mark.parametrize("m,k,inter", [(32, 1024, 3584), (4, 256, 512), (17, 1280, 1000), (1, 128, 8), (32, 1024, 40)])
+def test_skinny_gemm_swiglu_equals_chain(mods, m, k, inter):
+    """Gate/up projection with the SwiGLU in its epilogue against skinny_gemm -> swiglu: the same products in the same
+    order, the same rounding of the projection to bf16 in between, so the same bytes.  `inter` values that are not a
+    multiple of the 32 outputs a CTA covers exercise the tiles that hang over the end of the gate (and up) rows."""
+    ops, _ = mods
+    gen = torch.Generator().manual_seed(m + k + inter)
+    x = torch.randn(m, k, generator=gen).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(2 * inter, k, generator=gen) * 0.05).to(torch.bfloat16).to(DEV)
+    ref = ops.swiglu_fused(ops.skinny_gemm(x, w), inter)
+    y = ops.skinny_gemm(x, w, swiglu=True)
+    assert y.shape == ref.shape == (m, inter)
+    assert torch.equal(y, ref)
