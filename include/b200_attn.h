@@ -109,19 +109,25 @@ int b200_fused_decode_attention(const void* q, int64_t q_stride_b, int64_t q_str
                                 const float* inv_freq, int32_t rotary_dim, void* out, void* workspace, int32_t batch,
                                 int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, b200_stream_t stream);
 
-/* b200_fused_decode_attention with overlap flags (B200_OVERLAP_*, defined below): START lets the kernel begin while the
- * kernel in front of it still runs; PREFETCH additionally lets it compute the position prefix, gather page ids and
- * request its first K/V pages before that kernel has finished - pass it only when that kernel writes neither pos, the
- * block table nor the caches (in a layer stack it is the k-norm).  q, k_new, v_new and gate are always read after it. */
-int b200_fused_decode_attention_overlap(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_new,
-                                        int64_t kn_stride_b, int64_t kn_stride_h, const void* v_new, int64_t vn_stride_b,
-                                        int64_t vn_stride_h, const void* gate, int64_t gate_stride_b, void* k_cache,
-                                        void* v_cache, int64_t kc_stride_p, int64_t kc_stride_h, int64_t kc_stride_s,
-                                        int64_t vc_stride_p, int64_t vc_stride_h, int64_t vc_stride_s, int64_t num_pages,
-                                        const int32_t* block_table, int64_t bt_stride_b, const int64_t* pos,
-                                        const float* inv_freq, int32_t rotary_dim, void* out, void* workspace,
-                                        int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
-                                        int32_t overlap, b200_stream_t stream);
+/* b200_fused_decode_attention with two optional extensions.
+ * q_norm_weight / k_norm_weight (bf16 [head_dim], or NULL): the per-head Qwen RMSNorm x * rsqrt(mean(x^2) + eps) *
+ *   (1 + weight) of q and k_new (triton_kernels/qwen_rmsnorm.py:70-73 as applied at engine/runner.py:476-489) is computed
+ *   inside the kernel, rounded to bf16 like the reference's q_norm / k_norm output, before the RoPE; q and k_new are
+ *   then the raw projections.  Same bytes as b200_add_rmsnorm followed by the plain call.
+ * overlap (B200_OVERLAP_*, defined below): START lets the kernel begin while the kernel in front of it still runs;
+ *   PREFETCH additionally lets it compute the position prefix, gather page ids and request its first K/V pages before
+ *   that kernel has finished - pass it only when that kernel writes neither pos, the block table nor the caches (in a
+ *   layer stack it is the q/k/v/gate projection).  q, k_new, v_new and gate are always read after it. */
+int b200_fused_decode_attention_ex(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_new,
+                                   int64_t kn_stride_b, int64_t kn_stride_h, const void* v_new, int64_t vn_stride_b,
+                                   int64_t vn_stride_h, const void* gate, int64_t gate_stride_b, void* k_cache,
+                                   void* v_cache, int64_t kc_stride_p, int64_t kc_stride_h, int64_t kc_stride_s,
+                                   int64_t vc_stride_p, int64_t vc_stride_h, int64_t vc_stride_s, int64_t num_pages,
+                                   const int32_t* block_table, int64_t bt_stride_b, const int64_t* pos,
+                                   const float* inv_freq, int32_t rotary_dim, void* out, void* workspace, int32_t batch,
+                                   int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                                   const void* q_norm_weight, const void* k_norm_weight, float eps, int32_t overlap,
+                                   b200_stream_t stream);
 
 /* The same fused decode step for callers that cannot allocate device memory (a host that owns the whole GPU and
  * forbids cudaMalloc after start-up, a plugin inside another process, code running under stream capture).  This

@@ -23,8 +23,8 @@ SIGNATURES: dict[str, list] = {
     "b200_paged_decode_combine": [P, P, P, P, P, I32, I32, I32, P],
     "b200_fused_decode_attention": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, P, P, I64, I64, I64, I64, I64, I64,
                                     I64, P, I64, P, P, I32, P, P, I32, I32, I32, I32, P],
-    "b200_fused_decode_attention_overlap": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, P, P, I64, I64, I64, I64, I64,
-                                            I64, I64, P, I64, P, P, I32, P, P, I32, I32, I32, I32, I32, P],
+    "b200_fused_decode_attention_ex": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, P, P, I64, I64, I64, I64, I64,
+                                       I64, I64, P, I64, P, P, I32, P, P, I32, I32, I32, I32, P, P, c_float, I32, P],
     "b200_fused_decode_attention_static": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, P, P, I64, I64, I64, I64, I64,
                                            I64, I64, P, I64, P, P, I32, P, I32, I32, I32, I32, P],
     "b200_selftest_umma": [I32, P, P, P, P],

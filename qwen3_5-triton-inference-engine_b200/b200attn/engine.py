@@ -247,15 +247,16 @@ class Engine:
                                               overlap=start | ops.OVERLAP_PREFETCH)
                 mixed = glue.gemm_2d(normed, layer["out_proj"])
             else:
-                q = ops.add_rmsnorm(fused[:, :qd].view(batch, cfg.num_q_heads, cfg.head_dim), layer["q_norm"], cfg.eps,
-                                    overlap=chain)
-                k = ops.add_rmsnorm(fused[:, 2 * qd: 2 * qd + kvd].view(batch, cfg.num_kv_heads, cfg.head_dim),
-                                    layer["k_norm"], cfg.eps, overlap=chain)
+                # the q / k head norms run inside the attention kernel, which starts behind the projection
+                q = fused[:, :qd].view(batch, cfg.num_q_heads, cfg.head_dim)
+                k = fused[:, 2 * qd: 2 * qd + kvd].view(batch, cfg.num_kv_heads, cfg.head_dim)
                 v = fused[:, 2 * qd + kvd:].view(batch, cfg.num_kv_heads, cfg.head_dim)
                 k_cache, v_cache = self.kv[i]
                 ctx = ops.fused_decode_attention(q, k, v, fused[:, qd: 2 * qd], k_cache, v_cache, self.block_table,
                                                  self.pos, self.inv_freq, cfg.rotary_dim, self.workspace,
-                                                 overlap=start | ops.OVERLAP_PREFETCH)
+                                                 overlap=(start | ops.OVERLAP_PREFETCH) if own_proj else start,
+                                                 q_norm_weight=layer["q_norm"], k_norm_weight=layer["k_norm"],
+                                                 eps=cfg.eps)
                 mixed = glue.gemm_2d(ctx, layer["o_proj"])
             own_mlp = self._streams_weight(layer["gate_up"]) and cfg.intermediate % 8 == 0
             x, h = ops.add_rmsnorm(mixed, layer["ln2"], cfg.eps, residual=x, overlap=chain if own_mlp else start)

@@ -210,9 +210,12 @@ def fused_decode_workspace(device="cuda") -> torch.Tensor:
 
 
 def fused_decode_attention(q, k_new, v_new, gate, k_cache, v_cache, block_table, pos, inv_freq, rotary_dim,
-                           workspace, out=None, overlap: int = 0) -> torch.Tensor:
+                           workspace, out=None, overlap: int = 0, q_norm_weight=None, k_norm_weight=None,
+                           eps: float = 1e-6) -> torch.Tensor:
     """RoPE(q, k_new) + append + paged attention + sigmoid gate in one launch -> [B, H_q*D] bf16.
     q [B,H_q,D], k_new/v_new [B,H_kv,D] are the post-norm, PRE-RoPE projections; gate [B, H_q*D].
+    q_norm_weight / k_norm_weight (bf16 [D]): q and k_new are the RAW projections and the per-head Qwen RMSNorm
+    (engine/runner.py:476-489) is applied inside the kernel - the same bytes as add_rmsnorm in front of the call.
     overlap: OVERLAP_START lets the kernel begin while its predecessor in the stream runs; OVERLAP_PREFETCH also lets it
     read pos / block_table / cache pages before that predecessor has finished (valid when it writes none of them)."""
     batch, num_q_heads, head_dim = q.shape
@@ -230,12 +233,15 @@ def fused_decode_attention(q, k_new, v_new, gate, k_cache, v_cache, block_table,
     if out is None:
         out = torch.empty((batch, num_q_heads * head_dim), dtype=torch.bfloat16, device=q.device)
     assert out.is_contiguous() and out.shape == (batch, num_q_heads * head_dim)
-    _lib.call("b200_fused_decode_attention_overlap", _ptr(q), q.stride(0), q.stride(1), _ptr(k_new), k_new.stride(0),
+    for w in (q_norm_weight, k_norm_weight):
+        assert w is None or (w.dtype == torch.bfloat16 and w.is_contiguous() and w.numel() == head_dim and w.device == q.device)
+    _lib.call("b200_fused_decode_attention_ex", _ptr(q), q.stride(0), q.stride(1), _ptr(k_new), k_new.stride(0),
               k_new.stride(1), _ptr(v_new), v_new.stride(0), v_new.stride(1), _ptr(gate), gate.stride(0),
               _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), k_cache.stride(1), k_cache.stride(2), v_cache.stride(0),
               v_cache.stride(1), v_cache.stride(2), k_cache.shape[0], _ptr(block_table), block_table.stride(0), _ptr(pos),
               _ptr(inv_freq), int(rotary_dim), _ptr(out), _ptr(workspace), batch, num_q_heads, num_kv_heads, head_dim,
-              int(overlap), _stream())
+              _ptr(q_norm_weight) if q_norm_weight is not None else None,
+              _ptr(k_norm_weight) if k_norm_weight is not None else None, float(eps), int(overlap), _stream())
     return out
 
 

@@ -47,6 +47,7 @@ constexpr int FD_SMEM_TOTAL = FD_SMEM_RING + FD_SMEM_MERGE + FD_SMEM_CUM + FD_SM
 
 struct FusedDecodeParams {
   const __nv_bfloat16 *q, *k_new, *v_new, *gate;
+  const __nv_bfloat16 *q_norm_w, *k_norm_w;  // optional per-head RMSNorm weights [256] applied to q / k_new first
   __nv_bfloat16 *k_cache, *v_cache, *out;
   int64_t q_b, q_h, kn_b, kn_h, vn_b, vn_h, gate_b;
   int64_t kc_p, kc_h, kc_s, vc_p, vc_h, vc_s, bt_b;
@@ -57,7 +58,7 @@ struct FusedDecodeParams {
   int* counters;
   int* err;
   int batch, num_kv_heads, rotary_half, overlap;
-  float scale;
+  float scale, eps;
 };
 
 // Position of a (sequence, kv head) segment on the unit line.  units = old pages + 1 (the appended token).
@@ -88,65 +89,79 @@ __device__ __forceinline__ void segment_advance(Segment& s, const int* cum, int 
   if (s.b < batch) s.end = s.start + (cum[s.b + 1] - cum[s.b]);
 }
 
-// Stage the 4 Q heads of one segment in shared memory, rotated: dims [0, half) pair with [half, 2*half),
-// angles = float(pos) * inv_freq[d] in fp32, full-range sincosf, result rounded to bf16 -- the arithmetic of
-// triton_kernels/partial_rope.py:65-113.  Cooperative over the CTA's 256 threads; the caller synchronises.
-__device__ __forceinline__ void stage_q(__nv_bfloat16* buf, const FusedDecodeParams& p, int b, int h, int pos_b, int tid) {
-  const int half = p.rotary_half;
-  const __nv_bfloat16* q4 = p.q + b * p.q_b + (h * GROUP) * p.q_h;
-  if (tid < GROUP * 32) {
-    // rotary pairs: at most 32 per head (rotary_dim <= 64)
-    const int head = tid >> 5, j = tid & 31;
-    if (j < half) {
-      const float a = __bfloat162float(q4[head * p.q_h + j]), bb = __bfloat162float(q4[head * p.q_h + j + half]);
-      float sn, cs, f, g;
-      sincosf(static_cast<float>(pos_b) * p.inv_freq[j], &sn, &cs);
-      rope_pair(a, bb, sn, cs, f, g);
-      buf[head * FD_Q_PITCH + j] = __float2bfloat16_rn(f);
-      buf[head * FD_Q_PITCH + j + half] = __float2bfloat16_rn(g);
-    }
-  } else {
-    // pass-through dims [2*half, 256) in 16-byte pieces
-    const int per_head = (HEAD_DIM - 2 * half) / 8;
-    for (int i = tid - GROUP * 32; i < GROUP * per_head; i += FD_THREADS - GROUP * 32) {
-      const int head = i / per_head, d = 2 * half + (i % per_head) * 8;
-      *reinterpret_cast<uint4*>(buf + head * FD_Q_PITCH + d) = *reinterpret_cast<const uint4*>(q4 + head * p.q_h + d);
+// One head row of q or k_new, 8 consecutive dims per lane (`w` = 4 packed bf16 pairs).
+//
+// Optional Qwen RMSNorm over the 256 dims, x * rsqrt(mean(x^2) + eps) * (1 + weight), rounded to bf16 as the
+// reference's q_norm / k_norm output is a bf16 tensor (triton_kernels/qwen_rmsnorm.py:70-73, applied at
+// engine/runner.py:476-489); the summation order is the one of add_rmsnorm_kernel, so both give the same bytes.
+__device__ __forceinline__ void norm_row8(uint32_t (&w)[4], const __nv_bfloat16* weight, float eps, int lane) {
+  const uint4 wraw = *reinterpret_cast<const uint4*>(weight + lane * 8);
+  const uint32_t ww[4] = {wraw.x, wraw.y, wraw.z, wraw.w};
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = bf16_lo(w[i]);
+    v[2 * i + 1] = bf16_hi(w[i]);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
+  ss = warp_sum(ss);
+  const float rs = rsqrtf(ss / static_cast<float>(HEAD_DIM) + eps);
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    w[i] = pack_bf16(v[2 * i] * rs * (1.0f + bf16_lo(ww[i])), v[2 * i + 1] * rs * (1.0f + bf16_hi(ww[i])));
+}
+// Partial RoPE of the row at position pos: dims [0, half) pair with [half, 2*half), angles = float(pos) * inv_freq[d] in
+// fp32, full-range sincosf, result rounded to bf16 -- the arithmetic of triton_kernels/partial_rope.py:65-113.  Lanes
+// [0, half/8) hold the first halves, the next half/8 lanes their partners; the other lanes pass through.
+__device__ __forceinline__ void rope_row8(uint32_t (&w)[4], const FusedDecodeParams& p, int64_t pos, int lane) {
+  const int half = p.rotary_half;  // <= 32: one angle per lane
+  if (half == 0) return;
+  // the warp computes the `half` angles once, one sincosf per lane, and hands them round by shuffles
+  float sn = 0.f, cs = 1.f;
+  if (lane < half) sincosf(static_cast<float>(pos) * p.inv_freq[lane], &sn, &cs);
+  const int lanes_half = half / 8;
+  const bool in_rot = lane < 2 * lanes_half;
+  const bool first = lane < lanes_half;
+  const int partner = first ? lane + lanes_half : lane - lanes_half;
+  const int dbase = (in_rot ? (first ? lane : partner) : 0) * 8;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t other = __shfl_sync(0xffffffffu, w[i], in_rot ? partner : lane);
+    const float s0 = __shfl_sync(0xffffffffu, sn, dbase + 2 * i), c0 = __shfl_sync(0xffffffffu, cs, dbase + 2 * i);
+    const float s1 = __shfl_sync(0xffffffffu, sn, dbase + 2 * i + 1), c1 = __shfl_sync(0xffffffffu, cs, dbase + 2 * i + 1);
+    if (in_rot) {
+      const uint32_t fa = first ? w[i] : other;  // first-half values
+      const uint32_t fb = first ? other : w[i];  // second-half values
+      float f0, g0, f1, g1;
+      rope_pair(bf16_lo(fa), bf16_lo(fb), s0, c0, f0, g0);
+      rope_pair(bf16_hi(fa), bf16_hi(fb), s1, c1, f1, g1);
+      w[i] = first ? pack_bf16(f0, f1) : pack_bf16(g0, g1);
     }
   }
 }
 
-// The appended token as a one-row page: the rotated k_new goes to row 0 of `k_tile` and to its slot in the
-// cache.  Each lane owns 8 consecutive dims.
+// Stage the 4 Q heads of one segment in shared memory, normalised (optional) and rotated: warps 0-3 take one head
+// each.  The caller synchronises.
+__device__ __forceinline__ void stage_q(__nv_bfloat16* buf, const FusedDecodeParams& p, int b, int h, int pos_b, int tid) {
+  if (tid >= GROUP * 32) return;
+  const int head = tid >> 5, lane = tid & 31;
+  const uint4 raw = *reinterpret_cast<const uint4*>(p.q + b * p.q_b + (h * GROUP + head) * p.q_h + lane * 8);
+  uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  if (p.q_norm_w != nullptr) norm_row8(w, p.q_norm_w, p.eps, lane);
+  rope_row8(w, p, pos_b, lane);
+  *reinterpret_cast<uint4*>(buf + head * FD_Q_PITCH + lane * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// The appended token as a one-row page: the normalised (optional), rotated k_new goes to row 0 of `k_tile` and to its
+// slot in the cache.  Each lane owns 8 consecutive dims.
 __device__ __forceinline__ void stage_new_k(uint8_t* k_tile, const FusedDecodeParams& p, int b, int h, int64_t pos_b,
                                             int lane) {
   const uint4 kraw = *reinterpret_cast<const uint4*>(p.k_new + b * p.kn_b + h * p.kn_h + lane * 8);
   uint32_t kw[4] = {kraw.x, kraw.y, kraw.z, kraw.w};
-  const int half = p.rotary_half;
-  if (half > 0) {
-    const int lanes_half = half / 8;  // lanes [0, lanes_half) hold the first halves, the next lanes_half the second
-    const bool in_rot = lane < 2 * lanes_half;
-    const bool first = lane < lanes_half;
-    const int partner = first ? lane + lanes_half : lane - lanes_half;
-    uint32_t other[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) other[i] = __shfl_sync(0xffffffffu, kw[i], in_rot ? partner : lane);
-    if (in_rot) {
-      const float posf = static_cast<float>(pos_b);
-      const int dbase = (first ? lane : partner) * 8;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float s0, c0, s1, c1;
-        sincosf(posf * p.inv_freq[dbase + 2 * i], &s0, &c0);
-        sincosf(posf * p.inv_freq[dbase + 2 * i + 1], &s1, &c1);
-        const uint32_t fa = first ? kw[i] : other[i];  // first-half values
-        const uint32_t fb = first ? other[i] : kw[i];  // second-half values
-        float f0, g0, f1, g1;
-        rope_pair(bf16_lo(fa), bf16_lo(fb), s0, c0, f0, g0);
-        rope_pair(bf16_hi(fa), bf16_hi(fb), s1, c1, f1, g1);
-        kw[i] = first ? pack_bf16(f0, f1) : pack_bf16(g0, g1);
-      }
-    }
-  }
+  if (p.k_norm_w != nullptr) norm_row8(kw, p.k_norm_w, p.eps, lane);
+  rope_row8(kw, p, pos_b, lane);
   const uint4 krot = make_uint4(kw[0], kw[1], kw[2], kw[3]);
   *reinterpret_cast<uint4*>(k_tile + tile_offset<true>(0, lane)) = krot;
   const int64_t phys = p.block_table[b * p.bt_b + pos_b / PAGE];
@@ -504,7 +519,10 @@ static int fused_decode_impl(const void* q, int64_t q_stride_b, int64_t q_stride
                                            const int32_t* block_table, int64_t bt_stride_b, const int64_t* pos,
                                            const float* inv_freq, int32_t rotary_dim, void* out, void* workspace,
                                            int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                                           const void* q_norm_weight, const void* k_norm_weight, float eps,
                                            int32_t overlap, b200_stream_t stream) {
+  B200_REQUIRE(aligned16(q_norm_weight) && aligned16(k_norm_weight),
+               "fused_decode_attention: norm weights must be 16-byte aligned");
   B200_REQUIRE(batch > 0 && batch <= FD_MAX_BATCH, "fused_decode_attention: batch must be in [1, %d] (got %d)",
                FD_MAX_BATCH, batch);
   B200_REQUIRE(head_dim == HEAD_DIM, "fused_decode_attention: head_dim must be %d (got %d)", HEAD_DIM, head_dim);
@@ -567,6 +585,9 @@ static int fused_decode_impl(const void* q, int64_t q_stride_b, int64_t q_stride
   p.num_kv_heads = num_kv_heads;
   p.rotary_half = rotary_dim / 2;
   p.overlap = overlap;
+  p.q_norm_w = static_cast<const __nv_bfloat16*>(q_norm_weight);
+  p.k_norm_w = static_cast<const __nv_bfloat16*>(k_norm_weight);
+  p.eps = eps;
   p.scale = 1.0f / sqrtf(static_cast<float>(head_dim));
   int grid = sm_count();
   if (grid > FD_MAX_CTAS) grid = FD_MAX_CTAS;
@@ -619,20 +640,22 @@ extern "C" int b200_fused_decode_attention(const void* q, int64_t q_stride_b, in
   return fused_decode_impl(q, q_stride_b, q_stride_h, k_new, kn_stride_b, kn_stride_h, v_new, vn_stride_b, vn_stride_h,
                            gate, gate_stride_b, k_cache, v_cache, kc_stride_p, kc_stride_h, kc_stride_s, vc_stride_p,
                            vc_stride_h, vc_stride_s, num_pages, block_table, bt_stride_b, pos, inv_freq, rotary_dim, out,
-                           workspace, batch, num_q_heads, num_kv_heads, head_dim, 0, stream);
+                           workspace, batch, num_q_heads, num_kv_heads, head_dim, nullptr, nullptr, 0.f, 0, stream);
 }
 
-extern "C" int b200_fused_decode_attention_overlap(
+extern "C" int b200_fused_decode_attention_ex(
     const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_new, int64_t kn_stride_b, int64_t kn_stride_h,
     const void* v_new, int64_t vn_stride_b, int64_t vn_stride_h, const void* gate, int64_t gate_stride_b, void* k_cache,
     void* v_cache, int64_t kc_stride_p, int64_t kc_stride_h, int64_t kc_stride_s, int64_t vc_stride_p,
     int64_t vc_stride_h, int64_t vc_stride_s, int64_t num_pages, const int32_t* block_table, int64_t bt_stride_b,
     const int64_t* pos, const float* inv_freq, int32_t rotary_dim, void* out, void* workspace, int32_t batch,
-    int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, int32_t overlap, b200_stream_t stream) {
+    int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, const void* q_norm_weight, const void* k_norm_weight,
+    float eps, int32_t overlap, b200_stream_t stream) {
   return fused_decode_impl(q, q_stride_b, q_stride_h, k_new, kn_stride_b, kn_stride_h, v_new, vn_stride_b, vn_stride_h,
                            gate, gate_stride_b, k_cache, v_cache, kc_stride_p, kc_stride_h, kc_stride_s, vc_stride_p,
                            vc_stride_h, vc_stride_s, num_pages, block_table, bt_stride_b, pos, inv_freq, rotary_dim, out,
-                           workspace, batch, num_q_heads, num_kv_heads, head_dim, overlap, stream);
+                           workspace, batch, num_q_heads, num_kv_heads, head_dim, q_norm_weight, k_norm_weight, eps,
+                           overlap, stream);
 }
 
 // Same computation and arguments as b200_fused_decode_attention, minus the workspace.

@@ -271,9 +271,11 @@ def test_decode_under_cuda_graph(ops):
 
 
 def test_overlapped_decode_attention_in_graph_equals_plain(ops):
-    """q-norm -> k-norm -> fused decode attention launched with the overlap flags (the attention kernel starts while the
-    k-norm runs and requests its first pages before it waits) and replayed from a CUDA graph with new projections every
-    replay, against the same chain in plain stream order: outputs and caches must be the same bytes."""
+    """projection -> q-norm -> k-norm -> fused decode attention in plain stream order, against projection -> fused decode
+    attention with the head norms inside the kernel and the overlap flags set (it starts while the projection runs and
+    requests its first pages before it waits), replayed from a CUDA graph with a new input every replay: outputs,
+    caches and positions must be the same bytes.  A kernel that read the projection before it was complete would see
+    the previous replay's values."""
     lengths = [30, 3, 200, 1025]
     steps = 6
     c = make_paged_case(lengths, seed=78, slack_tokens=steps + 4)
@@ -281,24 +283,31 @@ def test_overlapped_decode_attention_in_graph_equals_plain(ops):
     inv_d = rope_inv_freq().to(DEV)
     b = len(lengths)
     gen = torch.Generator().manual_seed(2)
-    rows = [bf16_randn(b, (8 + 8 + 2 + 2) * 256, gen=gen).to(DEV) for _ in range(steps)]
+    xs = [bf16_randn(b, 256, gen=gen).to(DEV) for _ in range(steps)]
+    w = (torch.randn((8 + 8 + 2 + 2) * 256, 256, generator=gen) * 0.08).to(torch.bfloat16).to(DEV)
     qw = (torch.randn(256, generator=gen) * 0.1).to(torch.bfloat16).to(DEV)
     kw = (torch.randn(256, generator=gen) * 0.1).to(torch.bfloat16).to(DEV)
 
     def run(overlapped: bool):
-        fused = rows[0].clone()
+        x = xs[0].clone()
         kc, vc, pos = d["k_cache"].clone(), d["v_cache"].clone(), d["pos"].clone()
         ws = ops.fused_decode_workspace(DEV)
         out = torch.empty(b, 2048, dtype=torch.bfloat16, device=DEV)
-        chain = ops.OVERLAP_START | ops.OVERLAP_TRIGGER if overlapped else 0
-        last = ops.OVERLAP_START | ops.OVERLAP_PREFETCH if overlapped else 0
 
         def step():
-            q = ops.add_rmsnorm(fused[:, :2048].view(b, 8, 256), qw, 1e-6, overlap=chain)
-            k = ops.add_rmsnorm(fused[:, 4096:4608].view(b, 2, 256), kw, 1e-6, overlap=chain)
-            v = fused[:, 4608:].view(b, 2, 256)
-            ops.fused_decode_attention(q, k, v, fused[:, 2048:4096], kc, vc, d["block_table"], pos, inv_d, 64, ws,
-                                       out=out, overlap=last)
+            if overlapped:
+                fused = ops.skinny_gemm(x, w, overlap=ops.OVERLAP_START | ops.OVERLAP_TRIGGER)
+                ops.fused_decode_attention(fused[:, :2048].view(b, 8, 256), fused[:, 4096:4608].view(b, 2, 256),
+                                           fused[:, 4608:].view(b, 2, 256), fused[:, 2048:4096], kc, vc,
+                                           d["block_table"], pos, inv_d, 64, ws, out=out,
+                                           overlap=ops.OVERLAP_START | ops.OVERLAP_PREFETCH,
+                                           q_norm_weight=qw, k_norm_weight=kw, eps=1e-6)
+            else:
+                fused = ops.skinny_gemm(x, w)
+                q = ops.add_rmsnorm(fused[:, :2048].view(b, 8, 256), qw, 1e-6)
+                k = ops.add_rmsnorm(fused[:, 4096:4608].view(b, 2, 256), kw, 1e-6)
+                ops.fused_decode_attention(q, k, fused[:, 4608:].view(b, 2, 256), fused[:, 2048:4096], kc, vc,
+                                           d["block_table"], pos, inv_d, 64, ws, out=out)
             pos.add_(1)
 
         side = torch.cuda.Stream()
@@ -313,12 +322,11 @@ def test_overlapped_decode_attention_in_graph_equals_plain(ops):
             with torch.cuda.graph(graph):
                 step()
             graph.replay()                       # the capture itself does not execute
-            outs.append(out.clone())
         else:
             step()
-            outs.append(out.clone())
-        for nxt in rows[1:]:
-            fused.copy_(nxt)
+        outs.append(out.clone())
+        for nxt in xs[1:]:
+            x.copy_(nxt)
             graph.replay() if graph is not None else step()
             outs.append(out.clone())
         torch.cuda.synchronize()
