@@ -386,6 +386,8 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
+        # stdout carries the one JSON line: NCCL's own messages (its version banner among them) go to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=device)
 
     from b200attn import ops

@@ -328,6 +328,14 @@ int b200_skinny_gemm(const void* x, int64_t x_stride, const void* weight, void* 
  * [M, intermediate]; intermediate a multiple of 8; other shapes, alignment and overlap flags as b200_skinny_gemm. */
 int b200_skinny_gemm_swiglu(const void* x, int64_t x_stride, const void* weight, void* y, int64_t y_stride, int32_t m,
                             int32_t intermediate, int32_t k, int32_t overlap, b200_stream_t stream);
+
+/* ids[r] = argmax over n of logits[r, n] (fp32 [rows, n], row stride in elements), ties to the lowest index: the arg-max
+ * half of triton_kernels/vocab_argmax.py:141-200, for logits produced by a library GEMM.  ids is int64 [rows].
+ * workspace: b200_argmax_rows_workspace_bytes() bytes, 8-byte aligned, zero-filled once (every launch leaves it zero);
+ * rows <= 1024, n and row_stride multiples of 4, logits 16-byte aligned.  overlap: B200_OVERLAP_START only. */
+int64_t b200_argmax_rows_workspace_bytes(void);
+int b200_argmax_rows(const float* logits, int64_t row_stride, int64_t* ids, void* workspace, int32_t rows, int32_t n,
+                     int32_t overlap, b200_stream_t stream);
 int b200_add_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x_stride_inner, int32_t inner_count,
                      const void* residual, int64_t residual_stride, const void* weight, void* sum_out, void* norm_out,
                      int32_t rows, int32_t dim, float eps, int32_t overlap, b200_stream_t stream);

@@ -44,6 +44,7 @@ SIGNATURES: dict[str, list] = {
                                         P, P, P, I64, I64, I32, I32, I32, P],
     "b200_skinny_gemm": [P, I64, P, P, I64, I32, I32, I32, I32, P],
     "b200_skinny_gemm_swiglu": [P, I64, P, P, I64, I32, I32, I32, I32, P],
+    "b200_argmax_rows": [P, I64, P, P, I32, I32, I32, P],
     "b200_add_rmsnorm": [P, I64, I64, I32, P, I64, P, P, P, I32, I32, c_float, I32, P],
     "b200_swiglu": [P, I64, P, I32, I32, I32, P],
     "b200_gdn_decode_prep": [P, I64, P, P, P, I64, P, I64, P, P, P, P, P, P, P, I32, I32, I32, P],
@@ -57,6 +58,7 @@ OTHER = {
     "b200_abi_version": ([], c_int),
     "b200_wait_timed_out": ([], c_int),
     "b200_fused_decode_workspace_bytes": ([], c_int64),
+    "b200_argmax_rows_workspace_bytes": ([], c_int64),
     "b200_gdn_chunked_prefill_packed_workspace_bytes": ([I32, I32, I32], c_int64),
 }
 

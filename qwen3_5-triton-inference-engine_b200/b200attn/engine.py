@@ -94,6 +94,7 @@ class Engine:
                 self.rec_state[i] = torch.zeros(batch, cfg.gdn_heads, cfg.gdn_dim, cfg.gdn_dim, dtype=torch.float32,
                                                 device=self.device)
         self.workspace = ops.fused_decode_workspace(self.device)
+        self.argmax_ws = ops.argmax_workspace(self.device)
         r = cfg.rotary_dim
         self.inv_freq = (1.0 / (cfg.rope_theta ** (torch.arange(0, r, 2, dtype=torch.float32) / r))).to(self.device)
         self.tok = torch.zeros(batch, dtype=torch.int64, device=self.device)   # input of the next step
@@ -266,7 +267,9 @@ class Engine:
                 act = ops.swiglu_fused(glue.gemm_2d(h, layer["gate_up"]), cfg.intermediate, overlap=start)
             pending = glue.gemm_2d(act, layer["down"])
         _, h = ops.add_rmsnorm(pending, self.w["norm"], cfg.eps, residual=x, overlap=start)
-        nxt = glue.lm_head_argmax(h, self.w["embed"], last_only=False)
+        # tied LM head: fp32 logits from cuBLAS, arg-max (lowest index on ties) in one launch
+        nxt = glue.lm_head_argmax(h, self.w["embed"], last_only=False,
+                                  argmax=lambda logits: ops.argmax_rows(logits, self.argmax_ws, overlap=start))
         self.pos.add_(1)
         return nxt
 

@@ -35,17 +35,18 @@ def embedding_gather(token_ids: torch.Tensor, table: torch.Tensor) -> torch.Tens
     return table.index_select(0, token_ids.reshape(-1).long())
 
 
-def lm_head_argmax(hidden: torch.Tensor, table: torch.Tensor, last_only: bool = True) -> torch.Tensor:
+def lm_head_argmax(hidden: torch.Tensor, table: torch.Tensor, last_only: bool = True, argmax=None) -> torch.Tensor:
     """argmax_v <hidden, table[v]> with the tied embedding as the LM head; ties go to the lowest index
     (triton_kernels/vocab_argmax.py:141-200).  last_only=True: only the last row of hidden, returns a 0-d tensor
-    (prefill of one sequence); last_only=False: one id per row, int64 [B] (batched decode)."""
+    (prefill of one sequence); last_only=False: one id per row, int64 [B] (batched decode).
+    argmax: optional callable taking the fp32 logits [rows, V] and returning int64 [rows] (default torch.argmax)."""
     if last_only:
         hidden = hidden[-1:]
     try:
         logits = torch.mm(hidden, table.t(), out_dtype=torch.float32)    # fp32 logits straight from the GEMM
     except (TypeError, RuntimeError):
         logits = F.linear(hidden, table).float()
-    ids = torch.argmax(logits, dim=-1)
+    ids = torch.argmax(logits, dim=-1) if argmax is None else argmax(logits)
     return ids[0] if last_only else ids
 
 

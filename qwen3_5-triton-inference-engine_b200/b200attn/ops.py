@@ -703,6 +703,25 @@ def gdn_decode_fused(fused, conv_state, weight4, a_log, dt_bias, norm_weight, st
     return out
 
 
+def argmax_workspace(device="cuda") -> torch.Tensor:
+    """Zero-filled workspace for `argmax_rows` (one per stream of calls; every call leaves it zero again)."""
+    return torch.zeros(_lib.load().b200_argmax_rows_workspace_bytes(), dtype=torch.uint8, device=device)
+
+
+def argmax_rows(logits, workspace, out=None, overlap: int = 0) -> torch.Tensor:
+    """ids[r] = argmax_n logits[r, n] for fp32 logits [rows, n], ties to the lowest index (the arg-max half of
+    triton_kernels/vocab_argmax.py:141-200; the logits come from a library GEMM).  Returns int64 [rows]."""
+    assert logits.ndim == 2 and logits.dtype == torch.float32 and logits.stride(1) == 1
+    _require_cuda(logits, workspace)
+    rows, n = logits.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int64, device=logits.device)
+    assert out.dtype == torch.int64 and out.is_contiguous() and out.numel() == rows
+    _lib.call("b200_argmax_rows", _ptr(logits), logits.stride(0), _ptr(out), _ptr(workspace), rows, n, int(overlap),
+              _stream())
+    return out
+
+
 SKINNY_GEMM_MAX_M, SKINNY_GEMM_MAX_K = 32, 1280
 
 

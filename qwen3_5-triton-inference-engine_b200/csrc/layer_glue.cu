@@ -4,6 +4,7 @@
 //   b200_swiglu             <-> triton_kernels/swiglu.py
 //   b200_gdn_decode_prep    <-> triton_kernels/depthwise_causal_conv4_decode.py + triton_kernels/gdn_qk_norm_gates.py:68-89
 //   b200_gdn_gated_rmsnorm  <-> triton_kernels/gdn_gated_rmsnorm.py:54-67
+//   b200_argmax_rows        <-> the arg-max half of triton_kernels/vocab_argmax.py:141-200 (fp32 logits in, ids out)
 // All are HBM/launch bound: 16-byte accesses, one warp per row (or one CTA per (sequence, head)), fp32 math, one
 // rounding to bf16 at the reference's rounding points.
 #include "b200_attn.h"
@@ -158,6 +159,64 @@ gdn_gated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
       make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
 }
 
+// ------------------------------------------------------------------------------------------- row arg-max (LM head)
+// ids[r] = argmax_n logits[r, n], ties to the lowest n (triton_kernels/vocab_argmax.py:141-200).  A (value, index)
+// pair is packed into one 64-bit key whose unsigned order is "larger value first, then smaller index"; a CTA reduces
+// one slice of one row (16-byte loads, every thread walks its elements in ascending order), the slices of a row meet
+// in an atomicMax, and the last slice to arrive (a counter per row) unpacks the index and leaves key and counter zero
+// for the next launch.
+constexpr int AM_THREADS = 256;
+constexpr int AM_MAX_ROWS = 1024;
+
+__device__ __forceinline__ unsigned long long argmax_key(float v, uint32_t idx) {
+  uint32_t u = __float_as_uint(v);
+  u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);  // monotone map of the float order onto unsigned integers
+  return (static_cast<unsigned long long>(u) << 32) | (0xffffffffu - idx);
+}
+
+__global__ void __launch_bounds__(AM_THREADS)
+argmax_rows_kernel(const float* logits, int64_t row_stride, int n, int64_t* __restrict__ ids,  // logits: no __restrict__
+                   unsigned long long* keys, int* counters, int overlap) {                    // (read after pdl_wait)
+  __shared__ unsigned long long red[AM_THREADS / 32];
+  const int row = blockIdx.y, splits = gridDim.x;
+  const int vecs = n >> 2;                                       // n is a multiple of 4
+  const int per = (vecs + splits - 1) / splits;
+  const int v0 = blockIdx.x * per, v1 = min(v0 + per, vecs);
+  pdl_wait();
+  const float4* src = reinterpret_cast<const float4*>(logits + static_cast<int64_t>(row) * row_stride);
+  float best = -INFINITY;
+  uint32_t best_i = 0xffffffffu;                                 // "nothing yet": loses every tie
+  for (int i = v0 + threadIdx.x; i < v1; i += AM_THREADS) {
+    const float4 x = __ldcs(src + i);
+    const uint32_t base = static_cast<uint32_t>(i) * 4u;
+    // strict > keeps the first of equal values inside this thread's ascending walk; NaN compares false and is skipped
+    if (x.x > best || best_i == 0xffffffffu) { best = x.x; best_i = base; }
+    if (x.y > best) { best = x.y; best_i = base + 1; }
+    if (x.z > best) { best = x.z; best_i = base + 2; }
+    if (x.w > best) { best = x.w; best_i = base + 3; }
+  }
+  unsigned long long key = best_i == 0xffffffffu ? 0ull : argmax_key(best, best_i);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+    key = other > key ? other : key;
+  }
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = key;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int w = 1; w < AM_THREADS / 32; ++w) key = red[w] > key ? red[w] : key;
+    atomicMax(keys + row, key);
+    __threadfence();
+    if (atomicAdd(counters + row, 1) == splits - 1) {
+      __threadfence();
+      const unsigned long long top = atomicExch(keys + row, 0ull);
+      ids[row] = static_cast<int64_t>(0xffffffffu - static_cast<uint32_t>(top & 0xffffffffull));
+      counters[row] = 0;
+    }
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -224,4 +283,27 @@ extern "C" int b200_gdn_gated_rmsnorm(const void* x, const void* z, int64_t z_st
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(z), z_stride, weight,
       static_cast<__nv_bfloat16*>(out), rows, num_heads);
   return check_launch("gdn_gated_rmsnorm");
+}
+
+extern "C" int64_t b200_argmax_rows_workspace_bytes(void) { return AM_MAX_ROWS * (8 + 4); }
+
+extern "C" int b200_argmax_rows(const float* logits, int64_t row_stride, int64_t* ids, void* workspace, int32_t rows,
+                                int32_t n, int32_t overlap, b200_stream_t stream) {
+  B200_REQUIRE(rows > 0 && rows <= AM_MAX_ROWS && n > 0 && n % 4 == 0 && row_stride % 4 == 0,
+               "argmax_rows: rows must be in [1, %d], n and the row stride multiples of 4 (got %d rows, n=%d)", AM_MAX_ROWS,
+               rows, n);
+  B200_REQUIRE(aligned16(logits) && workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) % 8 == 0) &&
+                   ids != nullptr,
+               "argmax_rows: logits must be 16-byte aligned, the workspace 8-byte aligned");
+  // slices of at least 8192 elements; enough CTAs to fill the machine for a decode batch
+  int splits = sm_count() * 2 / rows;
+  const int max_splits = (n / 4 + 2047) / 2048;
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
+  unsigned long long* keys = static_cast<unsigned long long*>(workspace);
+  int* counters = reinterpret_cast<int*>(keys + AM_MAX_ROWS);
+  if (launch_pdl((overlap & OVERLAP_START) != 0, argmax_rows_kernel, dim3(splits, rows), dim3(AM_THREADS), 0,
+                 reinterpret_cast<cudaStream_t>(stream), logits, row_stride, n, ids, keys, counters, overlap) != cudaSuccess)
+    return fail(ERR_LAUNCH, "argmax_rows: %s", cudaGetErrorString(cudaGetLastError()));
+  return check_launch("argmax_rows");
 }

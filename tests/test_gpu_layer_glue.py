@@ -202,3 +202,29 @@ def test_skinny_gemm_swiglu_equals_chain(mods, m, k, inter):
     y = ops.skinny_gemm(x, w, swiglu=True)
     assert y.shape == ref.shape == (m, inter)
     assert torch.equal(y, ref)
+
+
+@pytest.mark.parametrize("rows,n", [(32, 248320), (1, 8), (5, 1000), (1024, 64), (3, 40004)])
+def test_argmax_rows_equals_torch(mods, rows, n):
+    """Row arg-max of fp32 logits against torch.argmax (first maximal value wins): random rows, rows whose maximum
+    occurs several times (in different slices and inside one 16-byte load), a constant row, a row of -inf, a row view
+    with a larger stride; the workspace must be all zero again after every call."""
+    ops, _ = mods
+    gen = torch.Generator().manual_seed(rows + n)
+    wide = torch.randn(rows, n + 8, generator=gen)
+    logits = wide[:, :n]                               # row stride n + 8
+    top = logits.max(dim=1).values
+    for r in range(0, rows, 3):                        # plant duplicates of the maximum
+        for c in torch.randint(0, n, (4,), generator=gen).tolist():
+            logits[r, c] = top[r]
+        c0 = int(torch.randint(0, n - 1, (1,), generator=gen))
+        logits[r, c0] = logits[r, c0 + 1] = top[r]
+    if rows >= 3:
+        logits[1] = 0.25
+        logits[2] = float("-inf")
+    dev_logits = wide.to(DEV)[:, :n]
+    ws = ops.argmax_workspace(DEV)
+    for _ in range(2):
+        ids = ops.argmax_rows(dev_logits, ws)
+        assert torch.equal(ids.cpu(), torch.argmax(logits, dim=1))
+        assert int(ws.abs().sum()) == 0
