@@ -350,10 +350,30 @@ def run_reference(args, rank, world):
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+def claim_stdout():
+    """stdout is for the one JSON line.  Libraries write there too (NCCL prints its version banner with printf), so the
+    process's descriptor 1 is pointed at stderr for the whole run and the real stdout is kept aside for the result."""
+    sys.stdout.flush()
+    real = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    return real
+
+
+RESULT_OUT = None
+
+
+def emit(obj) -> None:
+    out = RESULT_OUT if RESULT_OUT is not None else sys.stdout
+    out.write(json.dumps(obj) + "\n")
+    out.flush()
 
 
 def main():
+    global RESULT_OUT
+    RESULT_OUT = claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
@@ -386,8 +406,6 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
-        # stdout carries the one JSON line: NCCL's own messages (its version banner among them) go to stderr
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=device)
 
     from b200attn import ops
@@ -395,7 +413,7 @@ def main():
     if args.kernel_only and args.workload != "decode":
         rows = run_prefill_sweep(ops, device, args.steps, only=args.workload)
         if rank == 0:
-            print(json.dumps({"kernel_only": True, "workload": args.workload, "rows": rows}), flush=True)
+            emit({"kernel_only": True, "workload": args.workload, "rows": rows})
         if dist is not None:
             dist.destroy_process_group()
         return
@@ -445,8 +463,8 @@ def main():
 
     if args.kernel_only:
         if rank == 0:
-            print(json.dumps({"metric": METRIC, "value": value, "unit": "GB/s", "ms_per_step": ms_per_step,
-                              "steps": args.steps, "batch": args.batch, "kernel_only": True}), flush=True)
+            emit({"metric": METRIC, "value": value, "unit": "GB/s", "ms_per_step": ms_per_step, "steps": args.steps,
+                  "batch": args.batch, "kernel_only": True})
         if dist is not None:
             dist.destroy_process_group()
         return
@@ -518,7 +536,7 @@ def main():
         if not args.no_sweep:
             line["sweep"] = run_sweep(ops, ws, device, peak, args.sweep_steps)
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
