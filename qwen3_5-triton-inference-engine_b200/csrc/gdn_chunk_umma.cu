@@ -47,16 +47,6 @@ static_assert(GF_SMEM <= 227 * 1024, "shared memory budget");
 // tensor-memory columns
 constexpr uint32_t TM_D1 = 0, TM_DD = 64, TM_O1 = 128, TM_M = 192, TM_O2 = 256, TM_S = 320, TM_COLS = 512;  // O1|M adjacent
 
-#ifdef B200_GDN_TRACE
-__device__ unsigned long long g_gdn_trace[64];
-#define GDN_TRACE(i)                                                                   \
-  do {                                                                                 \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && (i) < 64) g_gdn_trace[(i)] = global_timer_ns(); \
-  } while (0)
-#else
-#define GDN_TRACE(i)
-#endif
-
 struct GdnFusedParams {
   const float* beta;
   const float* g;
@@ -203,9 +193,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
 
   uint32_t mma_phase = 0, aux_phase = 0;
   bool failed = false;
-  GDN_TRACE(0);
   for (int c = 0; c < num_chunks; ++c) {
-    GDN_TRACE(1 + c * 10);
     const int t0 = tok0 + c * CHUNK;
     const int valid = min(CHUNK, len - c * CHUNK);
     const bool last = c + 1 == num_chunks;
@@ -234,7 +222,6 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     // ---- Q, K, V of this chunk
     bool ok = mbar_wait_bounded(&bar_load, c & 1);
     if (__syncthreads_or(!ok)) { failed = true; break; }
-    GDN_TRACE(2 + c * 10);
     // ---- D1 = [Q;K] K^T
     if (issuer) {
       tc_fence_after_sync();
@@ -250,7 +237,6 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     ++mma_phase;
     if (__syncthreads_or(!ok)) { failed = true; break; }
     tc_fence_after_sync();
-    GDN_TRACE(3 + c * 10);
     // ---- D1 -> A (bf16 pair, B operand of the output product) and L (fp32, for the inverse)
     {
       const int half = warp >> 2, r = 32 * (warp & 3) + lane;
@@ -294,7 +280,6 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     }
     tc_fence_before_sync();
     __syncthreads();
-    GDN_TRACE(4 + c * 10);
     // ---- warps 0-3: P = (I + L)^-1 in fp32 on the CUDA cores, blocked: the four 16x16 diagonal blocks by forward
     //      substitution (one thread per column), then two levels of  P21 = -P22 (L21 P11)  with 4x4 register tiles;
     //      then Pu[t][i] = P[t][i] beta_i as a bf16 pair (B operand of the delta product) over the dead L.
@@ -321,18 +306,14 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
         for (int r = 0; r < 16; ++r) Pm[(16 * blk + r) * GF_LP + 16 * blk + j] = xx[r];  // after the loop: no aliasing stalls
       }
       named_barrier(3, 128);
-      GDN_TRACE(40 + c * 4);
       if (tid < 64) merge_a<16, 2>(Lm, Pm, Tm + (tid >> 5) * 16 * GF_TP, 32 * (tid >> 5), tid & 31);
       named_barrier(3, 128);
       if (tid < 64) merge_b<16, 2>(Pm, Tm + (tid >> 5) * 16 * GF_TP, 32 * (tid >> 5), tid & 31);
       named_barrier(3, 128);
-      GDN_TRACE(41 + c * 4);
       merge_a<32, 2>(Lm, Pm, Tm, 0, tid);
       named_barrier(3, 128);
       merge_b<32, 2>(Pm, Tm, 0, tid);
-      GDN_TRACE(42 + c * 4);
       named_barrier(4, 128);
-      GDN_TRACE(5 + c * 10);
       {
         const int t = tid >> 1, i0 = (tid & 1) * 32;
 #pragma unroll
@@ -438,7 +419,6 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     ++mma_phase;
     if (__syncthreads_or(!ok)) { failed = true; break; }
     tc_fence_after_sync();
-    GDN_TRACE(6 + c * 10);
     // ---- delta^T -> delta (pair) and delta' = e^{G_last - G} delta (pair, over the dead R tiles); all eight warps,
     //      32 tokens each
     {
@@ -467,7 +447,6 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     }
     tc_fence_before_sync();
     __syncthreads();
-    GDN_TRACE(7 + c * 10);
     // ---- O2 = delta^T A^T, S^T += delta'^T k
     if (issuer) {
       tc_fence_after_sync();
@@ -495,7 +474,6 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     ++mma_phase;
     if (__syncthreads_or(!ok)) { failed = true; break; }
     tc_fence_after_sync();
-    GDN_TRACE(8 + c * 10);
     if (!last) {  // every reader of Q, K and V is done
       if (issuer) issue_loads(c + 1);
       if (warp == 0) fetch_scalars(c + 1);
@@ -566,7 +544,6 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     }
     tc_fence_before_sync();
     __syncthreads();
-    GDN_TRACE(9 + c * 10);
   }
   if (num_chunks == 0 && warp >= 4) {  // empty sequence: zero state
     float* srow = p.state + (static_cast<int64_t>(b) * p.heads + h) * GDN_D * GDN_D + (tid - 128);
@@ -590,12 +567,6 @@ static bool encode_qkv_map(CUtensorMap* map, const void* base, int64_t tokens, i
 }  // namespace b200
 
 using namespace b200;
-
-#ifdef B200_GDN_TRACE
-extern "C" int b200_gdn_trace_read(unsigned long long* host64) {
-  return cudaMemcpyFromSymbol(host64, g_gdn_trace, sizeof(unsigned long long) * 64) == cudaSuccess ? 0 : 3;
-}
-#endif
 
 extern "C" int b200_gdn_chunked_prefill_fused(const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k,
                                               int64_t k_stride_t, int64_t k_stride_h, const void* v,
