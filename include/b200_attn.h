@@ -315,8 +315,10 @@ int b200_gdn_decode_fused(const void* fused, int64_t fused_stride, void* conv_st
                           const float* a_log, const void* dt_bias, const float* norm_weight, float* state, void* out,
                           int32_t batch, int32_t num_heads, int32_t head_dim, int32_t overlap, b200_stream_t stream);
 /* Y[M,N] = X[M,K] . W[N,K]^T for decode batches (M <= 32), bf16 in/out, fp32 accumulation: W is streamed once by
- * tensor-map TMA, X staged in shared memory.  N a multiple of 8, K a multiple of 128 up to 1280; x / y rows x_stride /
- * y_stride elements apart (multiples of 8), weight contiguous [N,K]; all 16-byte aligned.  With
+ * tensor-map TMA, X staged in shared memory.  N a multiple of 8, K a multiple of 128.  K <= 1280: every warp owns 16
+ * outputs and all of K.  K > 1280 (up to 16384; the projections back to the hidden size): a CTA owns 16 outputs, its
+ * warps split K and X is staged in ceil(K/1024) equal chunks, which must consist of whole 128-k tiles (2048 and 3584
+ * do).  x / y rows x_stride / y_stride elements apart (multiples of 8), weight contiguous [N,K]; all 16-byte aligned.  With
  * B200_OVERLAP_START the weight tiles are requested before the preceding kernel in the stream has finished, so
  * `weight` must not be that kernel's output (x may be).
  * Replaces triton_kernels/gemm_2d.py for the decode-step projections of the hidden state. */

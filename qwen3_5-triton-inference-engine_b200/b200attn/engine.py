@@ -101,10 +101,13 @@ class Engine:
         self.graph = None
 
     # ------------------------------------------------------------------------------------------------ shared pieces
-    def _streams_weight(self, weight) -> bool:
+    def _streams_weight(self, weight, swiglu: bool = False) -> bool:
         """Whether a projection of `batch` rows by this weight runs on the package's weight-streaming kernel."""
-        return (self.fused_glue and self.batch <= ops.SKINNY_GEMM_MAX_M and weight.shape[1] <= ops.SKINNY_GEMM_MAX_K
-                and weight.shape[1] % 128 == 0 and weight.shape[0] % 8 == 0)
+        n = weight.shape[0] // 2 if swiglu else weight.shape[0]
+        # K > 1280 (out / o / down projection) stays on cuBLAS: the kernel's wide-K form takes 6.6 / 11.0 us for
+        # K = 2048 / 3584 where cuBLAS takes 5.8 / 8.6 us, more than starting early behind its neighbours wins back
+        return (self.fused_glue and weight.shape[1] <= ops.SKINNY_GEMM_MAX_K
+                and ops.skinny_gemm_supports(self.batch, n, weight.shape[1], swiglu))
 
     def _proj(self, x, weight, overlap: int = 0):
         """Projection of the hidden state: the weight-streaming kernel for decode-sized batches, cuBLAS otherwise."""
@@ -223,50 +226,55 @@ class Engine:
         return nxt
 
     def _decode_fused(self, tok: torch.Tensor) -> torch.Tensor:
-        """The same step with every row-wise operator as one launch: about eight launches per layer (two of them
-        cuBLAS GEMMs; the SwiGLU is the epilogue of the gate/up projection).  The residual add after a layer's MLP is
-        fused into the next layer's input norm.  Kernels
-        of this package that follow one another start early (programmatic dependent launch: weights and states stream
-        in while the predecessor finishes); a kernel in front of a cuBLAS or PyTorch kernel never triggers early."""
+        """The same step with every row-wise operator as one launch: seven launches per layer (norm, projection, mixer
+        with its head norms inside, output projection, norm, gate/up projection with the SwiGLU as its epilogue, down
+        projection).  The residual add after a layer's MLP is fused into the next layer's input norm.  Kernels of this
+        package that follow one another start early (programmatic dependent launch: weights and states stream in while
+        the predecessor finishes); a kernel in front of a cuBLAS or PyTorch kernel never triggers early."""
         cfg = self.cfg
-        batch, heads, kd = self.batch, cfg.gdn_heads, cfg.gdn_width
+        batch, heads = self.batch, cfg.gdn_heads
         qd, kvd = cfg.num_q_heads * cfg.head_dim, cfg.num_kv_heads * cfg.head_dim
-        start, chain = ops.OVERLAP_START, ops.OVERLAP_START | ops.OVERLAP_TRIGGER
+        start, trigger, prefetch = ops.OVERLAP_START, ops.OVERLAP_TRIGGER, ops.OVERLAP_PREFETCH
+
+        def then(own_next: bool) -> int:                 # flags of a kernel whose successor is (not) one of ours
+            return start | trigger if own_next else start
+
         x = glue.embedding_gather(tok, self.w["embed"])
         pending = None                                   # MLP output still to be added to the residual stream
         for i, layer in enumerate(self.w["layers"]):
-            proj_w = layer["in_proj"] if layer["kind"] == "gdn" else layer["qkvg"]
-            own_proj = self._streams_weight(proj_w)      # the next kernel is this package's projection
+            gdn = layer["kind"] == "gdn"
+            proj_w = layer["in_proj"] if gdn else layer["qkvg"]
+            out_w = layer["out_proj"] if gdn else layer["o_proj"]
+            own_proj, own_out = self._streams_weight(proj_w), self._streams_weight(out_w)
+            own_mlp, own_down = self._streams_weight(layer["gate_up"], swiglu=True), self._streams_weight(layer["down"])
             if pending is None:
-                h = ops.add_rmsnorm(x, layer["ln1"], cfg.eps, overlap=chain if own_proj else start)
+                h = ops.add_rmsnorm(x, layer["ln1"], cfg.eps, overlap=then(own_proj))
             else:
-                x, h = ops.add_rmsnorm(pending, layer["ln1"], cfg.eps, residual=x, overlap=chain if own_proj else start)
-            fused = self._proj(h, proj_w, chain)
-            if layer["kind"] == "gdn":
-                normed = ops.gdn_decode_fused(fused, self.conv_state[i], layer["conv4"], layer["a_log"], layer["dt_bias"],
-                                              layer["norm"], self.rec_state[i], heads,
-                                              overlap=start | ops.OVERLAP_PREFETCH)
-                mixed = glue.gemm_2d(normed, layer["out_proj"])
+                x, h = ops.add_rmsnorm(pending, layer["ln1"], cfg.eps, residual=x, overlap=then(own_proj))
+            fused = self._proj(h, proj_w, then(True))
+            if gdn:
+                mixed_in = ops.gdn_decode_fused(fused, self.conv_state[i], layer["conv4"], layer["a_log"],
+                                                layer["dt_bias"], layer["norm"], self.rec_state[i], heads,
+                                                overlap=then(own_out) | prefetch)
             else:
                 # the q / k head norms run inside the attention kernel, which starts behind the projection
                 q = fused[:, :qd].view(batch, cfg.num_q_heads, cfg.head_dim)
                 k = fused[:, 2 * qd: 2 * qd + kvd].view(batch, cfg.num_kv_heads, cfg.head_dim)
                 v = fused[:, 2 * qd + kvd:].view(batch, cfg.num_kv_heads, cfg.head_dim)
                 k_cache, v_cache = self.kv[i]
-                ctx = ops.fused_decode_attention(q, k, v, fused[:, qd: 2 * qd], k_cache, v_cache, self.block_table,
-                                                 self.pos, self.inv_freq, cfg.rotary_dim, self.workspace,
-                                                 overlap=(start | ops.OVERLAP_PREFETCH) if own_proj else start,
-                                                 q_norm_weight=layer["q_norm"], k_norm_weight=layer["k_norm"],
-                                                 eps=cfg.eps)
-                mixed = glue.gemm_2d(ctx, layer["o_proj"])
-            own_mlp = self._streams_weight(layer["gate_up"]) and cfg.intermediate % 8 == 0
-            x, h = ops.add_rmsnorm(mixed, layer["ln2"], cfg.eps, residual=x, overlap=chain if own_mlp else start)
+                mixed_in = ops.fused_decode_attention(q, k, v, fused[:, qd: 2 * qd], k_cache, v_cache, self.block_table,
+                                                      self.pos, self.inv_freq, cfg.rotary_dim, self.workspace,
+                                                      overlap=then(own_out) | (prefetch if own_proj else 0),
+                                                      q_norm_weight=layer["q_norm"], k_norm_weight=layer["k_norm"],
+                                                      eps=cfg.eps)
+            mixed = self._proj(mixed_in, out_w, then(True))
+            x, h = ops.add_rmsnorm(mixed, layer["ln2"], cfg.eps, residual=x, overlap=then(own_mlp))
             if own_mlp:
-                act = ops.skinny_gemm(h, layer["gate_up"], overlap=start, swiglu=True)   # cuBLAS follows: no trigger
+                act = ops.skinny_gemm(h, layer["gate_up"], overlap=then(own_down), swiglu=True)
             else:
-                act = ops.swiglu_fused(glue.gemm_2d(h, layer["gate_up"]), cfg.intermediate, overlap=start)
-            pending = glue.gemm_2d(act, layer["down"])
-        _, h = ops.add_rmsnorm(pending, self.w["norm"], cfg.eps, residual=x, overlap=start)
+                act = ops.swiglu_fused(glue.gemm_2d(h, layer["gate_up"]), cfg.intermediate, overlap=then(own_down))
+            pending = self._proj(act, layer["down"], then(True))
+        _, h = ops.add_rmsnorm(pending, self.w["norm"], cfg.eps, residual=x, overlap=start)   # cuBLAS follows
         # tied LM head: fp32 logits from cuBLAS, arg-max (lowest index on ties) in one launch
         nxt = glue.lm_head_argmax(h, self.w["embed"], last_only=False,
                                   argmax=lambda logits: ops.argmax_rows(logits, self.argmax_ws, overlap=start))

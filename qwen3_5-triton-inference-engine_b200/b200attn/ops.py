@@ -722,12 +722,27 @@ def argmax_rows(logits, workspace, out=None, overlap: int = 0) -> torch.Tensor:
     return out
 
 
-SKINNY_GEMM_MAX_M, SKINNY_GEMM_MAX_K = 32, 1280
+SKINNY_GEMM_MAX_M, SKINNY_GEMM_MAX_K = 32, 1280      # MAX_K: X staged whole; longer rows take the wide-K form
+SKINNY_GEMM_WIDE_CHUNK, SKINNY_GEMM_WIDE_MAX_K = 1024, 16384
+
+
+def skinny_gemm_supports(m: int, n: int, k: int, swiglu: bool = False) -> bool:
+    """Whether `skinny_gemm` takes an [m, k] x [n, k]^T product (the shape rules of b200_skinny_gemm[_swiglu])."""
+    if not (0 < m <= SKINNY_GEMM_MAX_M and n > 0 and n % 8 == 0 and k >= 128 and k % 128 == 0):
+        return False
+    if k <= SKINNY_GEMM_MAX_K:
+        return True
+    if swiglu or k > SKINNY_GEMM_WIDE_MAX_K:
+        return False
+    chunks = -(-k // SKINNY_GEMM_WIDE_CHUNK)
+    return k % (chunks * 128) == 0
 
 
 def skinny_gemm(x, weight, overlap: int = 0, swiglu: bool = False):
-    """y = x @ weight^T for a decode batch (x [M <= 32, K <= 1280] bf16, weight [N, K] bf16 contiguous), the weight
-    streamed once from HBM (triton_kernels/gemm_2d.py for the decode-step projections).
+    """y = x @ weight^T for a decode batch (x [M <= 32, K] bf16, weight [N, K] bf16 contiguous), the weight streamed
+    once from HBM (triton_kernels/gemm_2d.py for the decode-step projections).  K <= 1280: every warp owns 16 outputs
+    and the whole K; longer rows (the out / o / down projections): a CTA owns 16 outputs and its warps split K
+    (`skinny_gemm_supports` tells which shapes are taken).
     swiglu=True: weight = [gate rows | up rows] [2*I, K] and the result is silu(bf16(x.gate_j)) * bf16(x.up_j), [M, I]
     (the fused gate/up projection followed by triton_kernels/swiglu.py, one launch)."""
     assert x.ndim == 2 and weight.ndim == 2 and x.shape[1] == weight.shape[1]

@@ -222,6 +222,7 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
     for (int s = 0; s < FD_RING; ++s) mbar_init(&bars[warp][s], 1);
     mbar_fence_init();
   }
+  if (p.overlap & OVERLAP_TRIGGER) pdl_trigger();  // the successor may start: it waits for this grid before it reads `out`
   // Started early (programmatic dependent launch): with the PREFETCH flag the position prefix, the page-id gathers and
   // the first K/V page copies below overlap with the predecessor (it must not write pos, the block table or the
   // caches); q, k_new, v_new and gate are the predecessor's output and are read only after the wait further down.

@@ -171,6 +171,181 @@ skinny_gemm_kernel(const __grid_constant__ SkinnyGemmParams p, const __grid_cons
   }
 }
 
+// ------------------------------------------------------------------------------------------------ wide-K form
+// Projections back to the hidden size (out / o / down projection: N = hidden, K = 2048 .. 3584 and more) have few
+// output rows and long ones.  A CTA owns 16 outputs (one MMA M tile) and its four warps split K: warp w streams the
+// 4 KiB tiles kt = w, w + 4, ... of those 16 rows, accumulates its own [16 x 32] product and the four partial sums meet
+// in shared memory (fixed order, so the result is deterministic).  X no longer fits next to the rings, so it is staged
+// in chunks of at most 1024 k, double-buffered: the last warp to leave a chunk (a counter in shared memory, nobody
+// waits) requests the chunk after the next into the buffer that just became free.
+constexpr int WK_RING = 5;                // W tiles in flight per warp
+constexpr int WK_CHUNK_MAX = 1024;        // k elements of X per staged chunk
+constexpr int WK_ROWS = 16;               // outputs per CTA step
+constexpr int WK_MAX_K = 16384;
+constexpr int WK_X_PITCH_MAX = WK_CHUNK_MAX * 2 + 16;
+constexpr int WK_SMEM = SG_WARPS * WK_RING * SG_TILE_BYTES + SG_WARPS * WK_ROWS * SG_MAX_M * 4 +
+                        2 * SG_MAX_M * WK_X_PITCH_MAX + 1024;
+static_assert(WK_SMEM <= 227 * 1024, "weight rings + two X chunks must fit the 227 KiB a CTA may use");
+
+struct WideKParams {
+  const __nv_bfloat16* x;  // [M, K]
+  __nv_bfloat16* y;        // [M, N]
+  int64_t x_stride, y_stride;
+  int* err;
+  int m, n, k, row_blocks, overlap, chunk_k, n_chunks;
+};
+
+__global__ void __launch_bounds__(SG_THREADS, 1)
+skinny_gemm_widek_kernel(const __grid_constant__ WideKParams p, const __grid_constant__ CUtensorMap map_w) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ uint64_t bars[SG_WARPS][WK_RING];
+  __shared__ uint64_t bar_x[2];
+  __shared__ int x_left[2];  // warps that have left the chunk in buffer 0 / 1 (counts up, never reset)
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint8_t* ring = smem + warp * WK_RING * SG_TILE_BYTES;
+  float* red = reinterpret_cast<float*>(smem + SG_WARPS * WK_RING * SG_TILE_BYTES);   // [4 warps][32 batch][16 rows]
+  uint8_t* xs = reinterpret_cast<uint8_t*>(red) + SG_WARPS * WK_ROWS * SG_MAX_M * 4;  // [2][32][x_pitch]
+  const int x_pitch = p.chunk_k * 2 + 16;
+  const int x_buf_bytes = SG_MAX_M * x_pitch;
+  const int k_tiles = p.k / SG_TILE_K, chunk_tiles = p.chunk_k / SG_TILE_K;
+
+  if (tid == 0) {
+    for (int w = 0; w < SG_WARPS; ++w)
+      for (int s = 0; s < WK_RING; ++s) mbar_init(&bars[w][s], 1);
+    mbar_init(&bar_x[0], 1);
+    mbar_init(&bar_x[1], 1);
+    x_left[0] = x_left[1] = 0;
+    mbar_fence_init();
+  }
+  const int my_blocks = (p.row_blocks - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int my_tiles = k_tiles > warp ? (k_tiles - warp + SG_WARPS - 1) / SG_WARPS : 0;  // per row block, this warp
+  const int total_tiles = my_blocks * my_tiles;
+  const int total_chunks = my_blocks * p.n_chunks;
+  __syncthreads();
+  auto issue = [&](int t) {  // lane 0: tile t of this warp = (row block t / my_tiles, k tile warp + 4 * (t % my_tiles))
+    const int rb = blockIdx.x + (t / my_tiles) * gridDim.x, kt = warp + SG_WARPS * (t % my_tiles);
+    const int slot = t % WK_RING;
+    mbar_expect_tx(&bars[warp][slot], SG_TILE_BYTES);
+    tma_load_3d(ring + slot * SG_TILE_BYTES, &map_w, 0, rb * WK_ROWS, kt * 2, &bars[warp][slot]);
+  };
+  // chunk q of this CTA's chunk stream (row block q / n_chunks, k range (q % n_chunks) * chunk_k ...) -> buffer q & 1
+  auto stage_x = [&](int q) {  // a whole warp
+    const int buf = q & 1, c = q % p.n_chunks;
+    if (lane == 0) mbar_expect_tx(&bar_x[buf], static_cast<uint32_t>(p.m) * p.chunk_k * 2);
+    __syncwarp();
+    if (lane < p.m)
+      bulk_g2s(xs + buf * x_buf_bytes + lane * x_pitch, p.x + static_cast<int64_t>(lane) * p.x_stride + c * p.chunk_k,
+               p.chunk_k * 2, &bar_x[buf]);
+  };
+  if (p.overlap & OVERLAP_TRIGGER) pdl_trigger();
+  if (lane == 0) {
+    for (int t = 0; t < WK_RING && t < total_tiles; ++t) issue(t);  // weights: independent of the predecessor
+  }
+  pdl_wait();  // X is the predecessor's output
+  for (int i = tid; i < 2 * (SG_MAX_M - p.m) * (p.chunk_k >> 3); i += SG_THREADS) {  // rows beyond M are zero
+    const int per_buf = (SG_MAX_M - p.m) * (p.chunk_k >> 3);
+    const int buf = i / per_buf, j = i % per_buf;
+    const int r = p.m + j / (p.chunk_k >> 3), c = j % (p.chunk_k >> 3);
+    *reinterpret_cast<uint4*>(xs + buf * x_buf_bytes + r * x_pitch + c * 16) = make_uint4(0, 0, 0, 0);
+  }
+  if (warp == 0) {
+    stage_x(0);
+    if (total_chunks > 1) stage_x(1);
+  }
+  __syncthreads();  // the zero rows are in place
+
+  const int a_row = lane & 15, a_par = lane >> 4;
+  const uint32_t b_lane = static_cast<uint32_t>(((lane & 7) + ((lane >> 4) << 3)) * x_pitch + ((lane >> 3) & 1) * 16);
+  bool ok = true;
+  int t = 0;
+  // leave chunk q: the last of the four warps to do so requests chunk q + 2 into the buffer that is now free
+  auto leave_chunk = [&](int q) {
+    int last = 0;
+    if (lane == 0) last = ((atomicAdd(&x_left[q & 1], 1) & (SG_WARPS - 1)) == SG_WARPS - 1);
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last && q + 2 < total_chunks) stage_x(q + 2);
+  };
+  for (int blk = 0; blk < my_blocks; ++blk) {
+    const int rb = blockIdx.x + blk * gridDim.x;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    int cur = -1;  // chunk (within the row block) whose X this warp is reading
+    for (int kt = warp; kt < k_tiles; kt += SG_WARPS, ++t) {
+      const int c = kt / chunk_tiles;
+      while (cur < c) {  // move on to the chunk of this tile, leaving the ones in between
+        if (cur >= 0) leave_chunk(blk * p.n_chunks + cur);
+        ++cur;
+      }
+      const int q = blk * p.n_chunks + c;
+      if (ok && !mbar_wait_bounded(&bar_x[q & 1], (q >> 1) & 1)) ok = false;
+      const int slot = t % WK_RING;
+      if (ok && !mbar_wait_bounded(&bars[warp][slot], (t / WK_RING) & 1)) ok = false;
+      if (ok) {
+        const uint32_t tile = smem_u32(ring + slot * SG_TILE_BYTES);
+        const uint32_t xk0 = smem_u32(xs + (q & 1) * x_buf_bytes) + b_lane + ((kt - c * chunk_tiles) * SG_TILE_K) * 2;
+#pragma unroll
+        for (int ks = 0; ks < SG_TILE_K / 16; ++ks) {
+          uint32_t a[4], b01[4], b23[4];
+          const uint32_t a_off = (ks >> 2) * (16 * 128) + a_row * 128 + ((((ks & 3) * 2 + a_par) ^ (a_row & 7)) << 4);
+          ldmatrix_x4(b01, xk0 + ks * 32);
+          ldmatrix_x4(b23, xk0 + ks * 32 + 16 * x_pitch);
+          ldmatrix_x4(a, tile + a_off);
+          mma_bf16_16816(acc[0], a, b01[0], b01[1]);
+          mma_bf16_16816(acc[1], a, b01[2], b01[3]);
+          mma_bf16_16816(acc[2], a, b23[0], b23[1]);
+          mma_bf16_16816(acc[3], a, b23[2], b23[3]);
+        }
+      }
+      __syncwarp();  // every lane has read the tile: its slot can take the tile WK_RING ahead
+      if (ok && lane == 0 && t + WK_RING < total_tiles) issue(t + WK_RING);
+    }
+    while (cur < p.n_chunks) {  // leave the remaining chunks of this row block (also those this warp had no tile in)
+      if (cur >= 0) leave_chunk(blk * p.n_chunks + cur);
+      ++cur;
+    }
+    // ---- the four partial [16 x 32] sums meet in shared memory: red[warp][batch][row]
+    {
+      float* mine = red + warp * (WK_ROWS * SG_MAX_M);
+      const int r0 = lane >> 2, bc = (lane & 3) * 2;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        mine[(nt * 8 + bc) * WK_ROWS + r0] = acc[nt][0];
+        mine[(nt * 8 + bc + 1) * WK_ROWS + r0] = acc[nt][1];
+        mine[(nt * 8 + bc) * WK_ROWS + r0 + 8] = acc[nt][2];
+        mine[(nt * 8 + bc + 1) * WK_ROWS + r0 + 8] = acc[nt][3];
+      }
+    }
+    __syncthreads();
+    {
+      // thread -> batch row tid / 4, outputs (tid % 4) * 4 .. + 4: one 8-byte store
+      const int b = tid >> 2, r = (tid & 3) * 4;
+      float o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int idx = b * WK_ROWS + r + j;
+        o[j] = ((red[idx] + red[WK_ROWS * SG_MAX_M + idx]) + red[2 * WK_ROWS * SG_MAX_M + idx]) +
+               red[3 * WK_ROWS * SG_MAX_M + idx];
+      }
+      const int n0 = rb * WK_ROWS + r;
+      if (b < p.m && n0 < p.n)  // N is a multiple of 8 and r of 4: the four outputs are inside or outside together
+        *reinterpret_cast<uint2*>(p.y + static_cast<int64_t>(b) * p.y_stride + n0) =
+            make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
+    }
+    __syncthreads();  // red is free for the next row block
+  }
+  if (!ok) {
+    if (lane == 0) atomicExch(p.err, 1);
+    // let this warp's copies in flight land before the shared memory goes away
+    for (int s = 0; s < WK_RING; ++s) mbar_wait_bounded(&bars[warp][s], 0, 1u << 12);
+    if (warp == 0) {
+      mbar_wait_bounded(&bar_x[0], 0, 1u << 12);
+      mbar_wait_bounded(&bar_x[1], 0, 1u << 12);
+    }
+  }
+}
+
 static const CUtensorMap* cache_weight_map(const void* base, int64_t n, int64_t k, int box_rows) {
   struct Entry {
     const void* base;
@@ -233,6 +408,42 @@ static int launch_skinny(SkinnyGemmParams p, const void* weight, int w_rows, cud
   return check_launch(what);
 }
 
+// Chunking of K for the wide-K form: the fewest equal chunks of whole 128-k tiles that are at most WK_CHUNK_MAX long.
+static bool widek_chunks(int k, int* chunk_k, int* n_chunks) {
+  if (k <= 0 || k % SG_TILE_K != 0 || k > WK_MAX_K) return false;
+  const int n = (k + WK_CHUNK_MAX - 1) / WK_CHUNK_MAX;
+  if (k % (n * SG_TILE_K) != 0) return false;
+  *chunk_k = k / n;
+  *n_chunks = n;
+  return true;
+}
+
+static int launch_widek(WideKParams p, const void* weight, cudaStream_t stream) {
+  const char* what = "skinny_gemm";
+  const CUtensorMap* map = cache_weight_map(weight, p.n, p.k, 16);
+  if (!map) return fail(ERR_RUNTIME, "%s: cannot encode the weight tensor map", what);
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(skinny_gemm_widek_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WK_SMEM) != cudaSuccess)
+      return fail(ERR_RUNTIME, "%s: cannot raise dynamic shared memory to %d", what, WK_SMEM);
+    configured[dev] = true;
+  }
+  p.err = wait_timeout_flag();
+  if (!p.err) return fail(ERR_RUNTIME, "%s: no error flag", what);
+  p.row_blocks = (p.n + WK_ROWS - 1) / WK_ROWS;
+  int grid = p.row_blocks;
+  const int sms = sm_count();
+  if (grid > sms) grid = sms;
+  const int dyn = SG_WARPS * WK_RING * SG_TILE_BYTES + SG_WARPS * WK_ROWS * SG_MAX_M * 4 +
+                  2 * SG_MAX_M * (p.chunk_k * 2 + 16) + 1024;
+  if (launch_pdl((p.overlap & OVERLAP_START) != 0, skinny_gemm_widek_kernel, dim3(grid), dim3(SG_THREADS), dyn, stream, p,
+                 *map) != cudaSuccess)
+    return fail(ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(cudaGetLastError()));
+  return check_launch(what);
+}
+
 static int check_skinny_shape(const char* what, int m, int n, int k) {
   B200_REQUIRE(m > 0 && m <= SG_MAX_M, "%s: M must be in [1, %d] (got %d)", what, SG_MAX_M, m);
   B200_REQUIRE(n > 0 && n % 8 == 0 && k >= SG_TILE_K && k % SG_TILE_K == 0 && k <= SG_MAX_K,
@@ -243,10 +454,25 @@ static int check_skinny_shape(const char* what, int m, int n, int k) {
 
 extern "C" int b200_skinny_gemm(const void* x, int64_t x_stride, const void* weight, void* y, int64_t y_stride,
                                 int32_t m, int32_t n, int32_t k, int32_t overlap, b200_stream_t stream) {
-  int rc = check_skinny_shape("skinny_gemm", m, n, k);
-  if (rc != OK) return rc;
   B200_REQUIRE(aligned16(x) && aligned16(weight) && aligned16(y) && x_stride % 8 == 0 && y_stride % 8 == 0,
                "skinny_gemm: pointers must be 16-byte aligned, row strides multiples of 8 elements");
+  if (k > SG_MAX_K) {  // long rows: K split over the warps of a CTA, X staged in chunks
+    WideKParams wp = {};
+    B200_REQUIRE(m > 0 && m <= SG_MAX_M && n > 0 && n % 8 == 0 && widek_chunks(k, &wp.chunk_k, &wp.n_chunks),
+                 "skinny_gemm: M must be in [1, %d], N a multiple of 8, K > %d a multiple of 128 that splits into equal "
+                 "chunks of whole tiles of at most %d (got M=%d N=%d K=%d)", SG_MAX_M, SG_MAX_K, WK_CHUNK_MAX, m, n, k);
+    wp.x = static_cast<const __nv_bfloat16*>(x);
+    wp.y = static_cast<__nv_bfloat16*>(y);
+    wp.x_stride = x_stride;
+    wp.y_stride = y_stride;
+    wp.m = m;
+    wp.n = n;
+    wp.k = k;
+    wp.overlap = overlap;
+    return launch_widek(wp, weight, reinterpret_cast<cudaStream_t>(stream));
+  }
+  int rc = check_skinny_shape("skinny_gemm", m, n, k);
+  if (rc != OK) return rc;
   SkinnyGemmParams p = {};
   p.x = static_cast<const __nv_bfloat16*>(x);
   p.y = static_cast<__nv_bfloat16*>(y);
