@@ -104,9 +104,9 @@ class Engine:
     def _streams_weight(self, weight, swiglu: bool = False) -> bool:
         """Whether a projection of `batch` rows by this weight runs on the package's weight-streaming kernel."""
         n = weight.shape[0] // 2 if swiglu else weight.shape[0]
-        # K > 1280 (out / o / down projection) stays on cuBLAS: the kernel's wide-K form takes 6.6 / 11.0 us for
-        # K = 2048 / 3584 where cuBLAS takes 5.8 / 8.6 us, more than starting early behind its neighbours wins back
-        return (self.fused_glue and weight.shape[1] <= ops.SKINNY_GEMM_MAX_K
+        # K > 4096 would take the chunked wide-K form, which is slower than cuBLAS (11.0 against 8.6 us at K = 3584
+        # when forced); up to 4096 the CTA-pair form is faster (4.4 / 5.9 against 5.6 / 8.1 us at K = 2048 / 3584)
+        return (self.fused_glue and weight.shape[1] <= ops.SKINNY_GEMM_PAIR_MAX_K
                 and ops.skinny_gemm_supports(self.batch, n, weight.shape[1], swiglu))
 
     def _proj(self, x, weight, overlap: int = 0):

@@ -723,6 +723,7 @@ def argmax_rows(logits, workspace, out=None, overlap: int = 0) -> torch.Tensor:
 
 
 SKINNY_GEMM_MAX_M, SKINNY_GEMM_MAX_K = 32, 1280      # MAX_K: X staged whole; longer rows take the wide-K form
+SKINNY_GEMM_PAIR_MAX_K = 4096                        # up to here long rows are split over a pair of CTAs (K % 256 == 0)
 SKINNY_GEMM_WIDE_CHUNK, SKINNY_GEMM_WIDE_MAX_K = 1024, 16384
 
 
@@ -741,8 +742,8 @@ def skinny_gemm_supports(m: int, n: int, k: int, swiglu: bool = False) -> bool:
 def skinny_gemm(x, weight, overlap: int = 0, swiglu: bool = False):
     """y = x @ weight^T for a decode batch (x [M <= 32, K] bf16, weight [N, K] bf16 contiguous), the weight streamed
     once from HBM (triton_kernels/gemm_2d.py for the decode-step projections).  K <= 1280: every warp owns 16 outputs
-    and the whole K; longer rows (the out / o / down projections): a CTA owns 16 outputs and its warps split K
-    (`skinny_gemm_supports` tells which shapes are taken).
+    and the whole K; longer rows (the out / o / down projections): 16 outputs per step, K split over the warps of a
+    pair of CTAs (K <= 4096) or of one CTA with X staged in chunks (`skinny_gemm_supports` tells which shapes are taken).
     swiglu=True: weight = [gate rows | up rows] [2*I, K] and the result is silu(bf16(x.gate_j)) * bf16(x.up_j), [M, I]
     (the fused gate/up projection followed by triton_kernels/swiglu.py, one launch)."""
     assert x.ndim == 2 and weight.ndim == 2 and x.shape[1] == weight.shape[1]

@@ -346,6 +346,140 @@ skinny_gemm_widek_kernel(const __grid_constant__ WideKParams p, const __grid_con
   }
 }
 
+// ------------------------------------------------------------------------------------------------ pair-K form
+// The same 16-outputs-per-step decomposition for K <= 4096, on a cluster of two CTAs that take one half of K each: twice
+// as many SMs stream W, a CTA stages only its half of X -- once, whole, so there is no chunk pipeline -- and the two
+// partial [16 x 32] sums meet through distributed shared memory (rank 1 stores its sum into rank 0's shared memory,
+// one cluster barrier, rank 0 adds, rounds and writes).  No cluster multicast is used; every CTA loads its own tiles.
+constexpr int PK_RING = 3;                 // W tiles in flight per warp (a warp has K / 1024 tiles per row block)
+constexpr int PK_MAX_K = 4096;
+constexpr int PK_SMEM = SG_WARPS * PK_RING * SG_TILE_BYTES + (SG_WARPS + 1) * WK_ROWS * SG_MAX_M * 4 +
+                        SG_MAX_M * (PK_MAX_K + 16) + 1024;
+static_assert(PK_SMEM <= 227 * 1024, "weight rings + half of X must fit the 227 KiB a CTA may use");
+
+__global__ void __launch_bounds__(SG_THREADS, 1)
+skinny_gemm_pairk_kernel(const __grid_constant__ WideKParams p, const __grid_constant__ CUtensorMap map_w) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ uint64_t bars[SG_WARPS][PK_RING];
+  __shared__ uint64_t bar_x;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  uint8_t* ring = smem + warp * PK_RING * SG_TILE_BYTES;
+  float* red = reinterpret_cast<float*>(smem + SG_WARPS * PK_RING * SG_TILE_BYTES);  // [4 warps + peer][32 batch][16 rows]
+  float* peer = red + SG_WARPS * WK_ROWS * SG_MAX_M;                                 // written by rank 1 into rank 0
+  uint8_t* xs = reinterpret_cast<uint8_t*>(peer + WK_ROWS * SG_MAX_M);               // [32][x_pitch]: this CTA's half of X
+  const int half_k = p.k >> 1;
+  const int x_pitch = half_k * 2 + 16;
+  const int half_tiles = half_k / SG_TILE_K;
+
+  if (tid == 0) {
+    for (int w = 0; w < SG_WARPS; ++w)
+      for (int s = 0; s < PK_RING; ++s) mbar_init(&bars[w][s], 1);
+    mbar_init(&bar_x, 1);
+    mbar_fence_init();
+  }
+  const int my_blocks = (p.row_blocks - pair + pairs - 1) / pairs;
+  const int my_tiles = half_tiles > warp ? (half_tiles - warp + SG_WARPS - 1) / SG_WARPS : 0;  // per row block, this warp
+  const int total_tiles = my_blocks * my_tiles;
+  __syncthreads();
+  auto issue = [&](int t) {  // lane 0: tile t of this warp
+    const int rb = pair + (t / my_tiles) * pairs, kt = static_cast<int>(rank) * half_tiles + warp + SG_WARPS * (t % my_tiles);
+    const int slot = t % PK_RING;
+    mbar_expect_tx(&bars[warp][slot], SG_TILE_BYTES);
+    tma_load_3d(ring + slot * SG_TILE_BYTES, &map_w, 0, rb * WK_ROWS, kt * 2, &bars[warp][slot]);
+  };
+  if (p.overlap & OVERLAP_TRIGGER) pdl_trigger();
+  if (lane == 0) {
+    for (int t = 0; t < PK_RING && t < total_tiles; ++t) issue(t);  // weights: independent of the predecessor
+  }
+  pdl_wait();  // X is the predecessor's output
+  if (warp == 0) {
+    if (lane == 0) mbar_expect_tx(&bar_x, static_cast<uint32_t>(p.m) * half_k * 2);
+    __syncwarp();
+    if (lane < p.m)
+      bulk_g2s(xs + lane * x_pitch, p.x + static_cast<int64_t>(lane) * p.x_stride + rank * half_k, half_k * 2, &bar_x);
+  }
+  for (int i = tid; i < (SG_MAX_M - p.m) * (half_k >> 3); i += SG_THREADS) {  // rows beyond M are zero
+    const int r = p.m + i / (half_k >> 3), c = i % (half_k >> 3);
+    *reinterpret_cast<uint4*>(xs + r * x_pitch + c * 16) = make_uint4(0, 0, 0, 0);
+  }
+  __syncthreads();
+  bool ok = mbar_wait_bounded(&bar_x, 0);
+
+  const int a_row = lane & 15, a_par = lane >> 4;
+  const uint32_t xs_base = smem_u32(xs) + static_cast<uint32_t>(((lane & 7) + ((lane >> 4) << 3)) * x_pitch + ((lane >> 3) & 1) * 16);
+  const uint32_t peer_remote = cluster_map(smem_u32(peer), 0);
+  int t = 0;
+  for (int blk = 0; blk < my_blocks; ++blk) {
+    const int rb = pair + blk * pairs;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    for (int kl = warp; kl < half_tiles; kl += SG_WARPS, ++t) {
+      const int slot = t % PK_RING;
+      if (ok && !mbar_wait_bounded(&bars[warp][slot], (t / PK_RING) & 1)) ok = false;
+      if (ok) {
+        const uint32_t tile = smem_u32(ring + slot * SG_TILE_BYTES);
+        const uint32_t xk0 = xs_base + kl * SG_TILE_K * 2;
+#pragma unroll
+        for (int ks = 0; ks < SG_TILE_K / 16; ++ks) {
+          uint32_t a[4], b01[4], b23[4];
+          const uint32_t a_off = (ks >> 2) * (16 * 128) + a_row * 128 + ((((ks & 3) * 2 + a_par) ^ (a_row & 7)) << 4);
+          ldmatrix_x4(b01, xk0 + ks * 32);
+          ldmatrix_x4(b23, xk0 + ks * 32 + 16 * x_pitch);
+          ldmatrix_x4(a, tile + a_off);
+          mma_bf16_16816(acc[0], a, b01[0], b01[1]);
+          mma_bf16_16816(acc[1], a, b01[2], b01[3]);
+          mma_bf16_16816(acc[2], a, b23[0], b23[1]);
+          mma_bf16_16816(acc[3], a, b23[2], b23[3]);
+        }
+      }
+      __syncwarp();  // every lane has read the tile: its slot can take the tile PK_RING ahead
+      if (ok && lane == 0 && t + PK_RING < total_tiles) issue(t + PK_RING);
+    }
+    // ---- the warps' partial [16 x 32] sums meet in shared memory: red[warp][batch][row]
+    {
+      float* mine = red + warp * (WK_ROWS * SG_MAX_M);
+      const int r0 = lane >> 2, bc = (lane & 3) * 2;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        mine[(nt * 8 + bc) * WK_ROWS + r0] = acc[nt][0];
+        mine[(nt * 8 + bc + 1) * WK_ROWS + r0] = acc[nt][1];
+        mine[(nt * 8 + bc) * WK_ROWS + r0 + 8] = acc[nt][2];
+        mine[(nt * 8 + bc + 1) * WK_ROWS + r0 + 8] = acc[nt][3];
+      }
+    }
+    __syncthreads();
+    // thread -> batch row tid / 4, outputs (tid % 4) * 4 .. + 4
+    const int b = tid >> 2, r = (tid & 3) * 4;
+    float o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int idx = b * WK_ROWS + r + j;
+      o[j] = ((red[idx] + red[WK_ROWS * SG_MAX_M + idx]) + red[2 * WK_ROWS * SG_MAX_M + idx]) +
+             red[3 * WK_ROWS * SG_MAX_M + idx];
+    }
+    if (rank == 1) st_cluster_f32x4(peer_remote + (b * WK_ROWS + r) * 4, o[0], o[1], o[2], o[3]);
+    cluster_sync();  // rank 1's sum is in rank 0's shared memory; red is free again in both CTAs
+    if (rank == 0) {
+      const float4 other = *reinterpret_cast<const float4*>(peer + b * WK_ROWS + r);
+      const int n0 = rb * WK_ROWS + r;
+      if (b < p.m && n0 < p.n)  // N is a multiple of 8 and r of 4: the four outputs are inside or outside together
+        *reinterpret_cast<uint2*>(p.y + static_cast<int64_t>(b) * p.y_stride + n0) =
+            make_uint2(pack_bf16(o[0] + other.x, o[1] + other.y), pack_bf16(o[2] + other.z, o[3] + other.w));
+    }
+    if (blk + 1 < my_blocks) cluster_sync();  // rank 0 has read `peer` before rank 1 writes the next sum
+  }
+  if (!ok) {
+    if (lane == 0) atomicExch(p.err, 1);
+    // let this warp's copies in flight land before the shared memory goes away
+    for (int s = 0; s < PK_RING; ++s) mbar_wait_bounded(&bars[warp][s], 0, 1u << 12);
+    if (warp == 0) mbar_wait_bounded(&bar_x, 0, 1u << 12);
+  }
+}
+
 static const CUtensorMap* cache_weight_map(const void* base, int64_t n, int64_t k, int box_rows) {
   struct Entry {
     const void* base;
@@ -444,6 +578,32 @@ static int launch_widek(WideKParams p, const void* weight, cudaStream_t stream) 
   return check_launch(what);
 }
 
+static int launch_pairk(WideKParams p, const void* weight, cudaStream_t stream) {
+  const char* what = "skinny_gemm";
+  const CUtensorMap* map = cache_weight_map(weight, p.n, p.k, 16);
+  if (!map) return fail(ERR_RUNTIME, "%s: cannot encode the weight tensor map", what);
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(skinny_gemm_pairk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PK_SMEM) != cudaSuccess)
+      return fail(ERR_RUNTIME, "%s: cannot raise dynamic shared memory to %d", what, PK_SMEM);
+    configured[dev] = true;
+  }
+  p.err = wait_timeout_flag();
+  if (!p.err) return fail(ERR_RUNTIME, "%s: no error flag", what);
+  p.row_blocks = (p.n + WK_ROWS - 1) / WK_ROWS;
+  int pairs = p.row_blocks;
+  const int sms = sm_count();
+  if (pairs > sms / 2) pairs = sms / 2;
+  const int dyn = SG_WARPS * PK_RING * SG_TILE_BYTES + (SG_WARPS + 1) * WK_ROWS * SG_MAX_M * 4 +
+                  SG_MAX_M * (p.k + 16) + 1024;
+  if (launch_pdl_cluster((p.overlap & OVERLAP_START) != 0, 2, skinny_gemm_pairk_kernel, dim3(2 * pairs), dim3(SG_THREADS),
+                         dyn, stream, p, *map) != cudaSuccess)
+    return fail(ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(cudaGetLastError()));
+  return check_launch(what);
+}
+
 static int check_skinny_shape(const char* what, int m, int n, int k) {
   B200_REQUIRE(m > 0 && m <= SG_MAX_M, "%s: M must be in [1, %d] (got %d)", what, SG_MAX_M, m);
   B200_REQUIRE(n > 0 && n % 8 == 0 && k >= SG_TILE_K && k % SG_TILE_K == 0 && k <= SG_MAX_K,
@@ -469,6 +629,7 @@ extern "C" int b200_skinny_gemm(const void* x, int64_t x_stride, const void* wei
     wp.n = n;
     wp.k = k;
     wp.overlap = overlap;
+    if (k <= PK_MAX_K && k % (2 * SG_TILE_K) == 0) return launch_pairk(wp, weight, reinterpret_cast<cudaStream_t>(stream));
     return launch_widek(wp, weight, reinterpret_cast<cudaStream_t>(stream));
   }
   int rc = check_skinny_shape("skinny_gemm", m, n, k);
