@@ -10,8 +10,8 @@
 // thin for a tcgen05 tile).  CTAs walk the row blocks persistently, so X is read once per CTA however large N is.
 // Every wait is bounded.
 //
-// Two forms.  Plain: a warp's tile is 16 consecutive rows of W (one box {64 k, 16 rows, 2 k-blocks}), a CTA of four
-// warps covers 64 outputs.  SwiGLU (W = [gate rows | up rows], the fused gate/up projection followed by
+// Two forms.  Plain: a warp's tile is 16 consecutive rows of W (one box {64 k, 16 rows, 2 k-blocks}), a CTA covers 64
+// outputs with four row groups of two warps each (the even and the odd k tiles).  SwiGLU (W = [gate rows | up rows], the fused gate/up projection followed by
 // triton_kernels/swiglu.py): a warp's tile is 8 gate rows stacked on the 8 matching up rows (two boxes of 8 rows), so the
 // accumulator fragment of a thread holds gate_j (row r) and up_j (row r + 8) of the same output j and the activation is
 // applied in registers; a CTA covers 32 outputs.
@@ -27,6 +27,11 @@ constexpr int SG_TILE_K = 128;           // k elements per tile: two swizzled bl
 constexpr int SG_TILE_BYTES = 2 * 16 * 128;
 constexpr int SG_RING = 8;                        // tiles in flight per warp
 constexpr int SG_RING_BYTES = SG_RING * SG_TILE_BYTES;
+constexpr int SG_KSPLIT = 2;                      // K = 1280 or less: warps per row group, alternating k tiles
+constexpr int SG_STD_WARPS = SG_WARPS * SG_KSPLIT;
+constexpr int SG_STD_THREADS = SG_STD_WARPS * 32;
+constexpr int SG_STD_RING = SG_RING / SG_KSPLIT;  // the same bytes in flight per CTA
+constexpr int SG_PART_BYTES = 16 * SG_WARPS * 32 * 4;
 constexpr int SG_MAX_M = 32;
 constexpr int SG_MAX_K = 1280;           // X staging: 32 x (K*2 + 16) bytes next to 128 KiB of weight rings
 
@@ -39,19 +44,23 @@ struct SkinnyGemmParams {
 };
 
 template <bool SWIGLU>
-__global__ void __launch_bounds__(SG_THREADS, 1)
+__global__ void __launch_bounds__(SG_STD_THREADS, 1)
 skinny_gemm_kernel(const __grid_constant__ SkinnyGemmParams p, const __grid_constant__ CUtensorMap map_w) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   constexpr int SLOT_BYTES = SG_TILE_BYTES;
-  constexpr int RING = SG_RING;
+  constexpr int RING = SG_STD_RING;
   constexpr int OUT = SWIGLU ? 8 * SG_WARPS : SG_ROWS;  // outputs per CTA step
-  __shared__ uint64_t bars[SG_WARPS][RING];
+  __shared__ uint64_t bars[SG_STD_WARPS][RING];
   __shared__ uint64_t bar_x;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  uint8_t* ring = smem + warp * SG_RING_BYTES;
+  // warps wr and wr + 4 share the rows of group wr and take the even / the odd k tiles: a warp's k steps are a chain of
+  // dependent ldmatrix + MMA, so two short chains per row group finish in half the time of one long one
+  const int wr = warp & (SG_WARPS - 1), kh = warp / SG_WARPS;
+  uint8_t* ring = smem + warp * (RING * SLOT_BYTES);
   uint8_t* stage = smem + SG_WARPS * SG_RING_BYTES;                    // [32 batch][OUT] bf16 output staging, <= 4 KiB
-  uint8_t* xs = stage + SG_MAX_M * SG_ROWS * 2;                        // [32][x_pitch] bf16
+  float* part = reinterpret_cast<float*>(stage + SG_MAX_M * SG_ROWS * 2);  // [16][4 groups x 32 lanes]: odd-tile sums
+  uint8_t* xs = reinterpret_cast<uint8_t*>(part) + SG_PART_BYTES;      // [32][x_pitch] bf16
   const int x_pitch = p.k * 2 + 16;                                    // bytes; the 16 shift the banks row by row
   const int k_tiles = p.k / SG_TILE_K;
 
@@ -62,37 +71,41 @@ skinny_gemm_kernel(const __grid_constant__ SkinnyGemmParams p, const __grid_cons
   }
   // my tiles: row block rb = blockIdx.x, + gridDim.x, ...; tile index t counts (row block, k tile) pairs
   const int my_blocks = (p.row_blocks - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
-  const int total_tiles = my_blocks * k_tiles;
+  const int my_kt = (k_tiles - kh + SG_KSPLIT - 1) / SG_KSPLIT;  // k tiles kh, kh + 2, ... of every row block
+  const int total_tiles = my_blocks * my_kt;
   __syncwarp();
   auto issue = [&](int t) {
-    const int rb = blockIdx.x + (t / k_tiles) * gridDim.x, kt = t % k_tiles;
+    const int rb = blockIdx.x + (t / my_kt) * gridDim.x, kt = kh + SG_KSPLIT * (t % my_kt);
     const int slot = t % RING;
     mbar_expect_tx(&bars[warp][slot], SLOT_BYTES);
     if (SWIGLU) {  // map_w has 8-row boxes: gate rows to the first half of the tile, up rows to the second
-      tma_load_3d(ring + slot * SLOT_BYTES, &map_w, 0, rb * OUT + warp * 8, kt * 2, &bars[warp][slot]);
-      tma_load_3d(ring + slot * SLOT_BYTES + SG_TILE_BYTES / 2, &map_w, 0, p.up_row0 + rb * OUT + warp * 8, kt * 2,
+      tma_load_3d(ring + slot * SLOT_BYTES, &map_w, 0, rb * OUT + wr * 8, kt * 2, &bars[warp][slot]);
+      tma_load_3d(ring + slot * SLOT_BYTES + SG_TILE_BYTES / 2, &map_w, 0, p.up_row0 + rb * OUT + wr * 8, kt * 2,
                   &bars[warp][slot]);
     } else {
-      tma_load_3d(ring + slot * SLOT_BYTES, &map_w, 0, rb * OUT + warp * 16, kt * 2, &bars[warp][slot]);
+      tma_load_3d(ring + slot * SLOT_BYTES, &map_w, 0, rb * OUT + wr * 16, kt * 2, &bars[warp][slot]);
     }
   };
+  auto stage_x = [&]() {  // warp 0: one bulk copy per row of X
+    if (lane == 0) mbar_expect_tx(&bar_x, static_cast<uint32_t>(p.m) * p.k * 2);
+    __syncwarp();
+    if (lane < p.m) bulk_g2s(xs + lane * x_pitch, p.x + static_cast<int64_t>(lane) * p.x_stride, p.k * 2, &bar_x);
+  };
+  // Started early, the weights are requested while the predecessor runs and X after it.  In plain stream order X goes
+  // first: requested behind 128 KiB of weight tiles it would arrive behind them.
+  const bool early = (p.overlap & OVERLAP_START) != 0;
   if (p.overlap & OVERLAP_TRIGGER) pdl_trigger();
+  if (!early && warp == 0) stage_x();
   if (lane == 0) {
     for (int t = 0; t < RING && t < total_tiles; ++t) issue(t);  // weights: independent of the predecessor
   }
   pdl_wait();  // X is the predecessor's output
-  // X -> shared memory while the first W tiles are in flight (rows beyond M are zeroed)
-  for (int i = tid; i < (SG_MAX_M - p.m) * (p.k >> 3); i += SG_THREADS) {
+  if (early && warp == 0) stage_x();
+  for (int i = tid; i < (SG_MAX_M - p.m) * (p.k >> 3); i += SG_STD_THREADS) {  // rows beyond M are zero
     const int r = p.m + i / (p.k >> 3), c = i % (p.k >> 3);
     *reinterpret_cast<uint4*>(xs + r * x_pitch + c * 16) = make_uint4(0, 0, 0, 0);
   }
-  __syncthreads();  // bar_x is initialised
-  if (warp == 0) {
-    if (lane == 0) mbar_expect_tx(&bar_x, static_cast<uint32_t>(p.m) * p.k * 2);
-    __syncwarp();
-    if (lane < p.m) bulk_g2s(xs + lane * x_pitch, p.x + static_cast<int64_t>(lane) * p.x_stride, p.k * 2, &bar_x);
-  }
-  __syncthreads();
+  __syncthreads();  // bar_x is initialised for everybody, the zero rows are in place
   bool ok = mbar_wait_bounded(&bar_x, 0);
 
   const uint32_t xs_base = smem_u32(xs);
@@ -106,7 +119,7 @@ skinny_gemm_kernel(const __grid_constant__ SkinnyGemmParams p, const __grid_cons
     float acc[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-    for (int kt = 0; kt < k_tiles && ok; ++kt, ++t) {
+    for (int kt = kh; kt < k_tiles && ok; kt += SG_KSPLIT, ++t) {
       const int slot = t % RING;
       if (!mbar_wait_bounded(&bars[warp][slot], (t / RING) & 1)) {
         ok = false;
@@ -132,22 +145,29 @@ skinny_gemm_kernel(const __grid_constant__ SkinnyGemmParams p, const __grid_cons
       __syncwarp();  // every lane has read the tile: its slot can take the tile RING ahead
       if (lane == 0 && t + RING < total_tiles) issue(t + RING);
     }
+    // the odd-tile warps hand their sums to the even-tile warps of the same row group
+    if (kh == 1) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) part[i * (SG_WARPS * 32) + wr * 32 + lane] = acc[i >> 2][i & 3];
+    }
+    __syncthreads();  // (also: the previous block's staging has been written out)
     // acc[nt]: rows (tile row = lane/4, +8), cols (batch = nt*8 + (lane%4)*2, +1)  ->  stage[batch][output] -> Y
-    __syncthreads();  // the previous block's staging has been written out
-    {
+    if (kh == 0) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) acc[i >> 2][i & 3] += part[i * (SG_WARPS * 32) + wr * 32 + lane];
       __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage);
       const int bc = (lane & 3) * 2;
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt) {
         if (SWIGLU) {
           // rows r and r + 8 of the tile are gate_j and up_j; the projection is a bf16 tensor in the reference
-          const int j = warp * 8 + (lane >> 2);
+          const int j = wr * 8 + (lane >> 2);
           const float g0 = round_bf16(acc[nt][0]), g1 = round_bf16(acc[nt][1]);
           const float u0 = round_bf16(acc[nt][2]), u1 = round_bf16(acc[nt][3]);
           st[(nt * 8 + bc) * OUT + j] = __float2bfloat16_rn(g0 / (1.0f + expf(-g0)) * u0);
           st[(nt * 8 + bc + 1) * OUT + j] = __float2bfloat16_rn(g1 / (1.0f + expf(-g1)) * u1);
         } else {
-          const int nr = warp * 16 + (lane >> 2);
+          const int nr = wr * 16 + (lane >> 2);
           st[(nt * 8 + bc) * OUT + nr] = __float2bfloat16_rn(acc[nt][0]);
           st[(nt * 8 + bc + 1) * OUT + nr] = __float2bfloat16_rn(acc[nt][1]);
           st[(nt * 8 + bc) * OUT + nr + 8] = __float2bfloat16_rn(acc[nt][2]);
@@ -156,7 +176,7 @@ skinny_gemm_kernel(const __grid_constant__ SkinnyGemmParams p, const __grid_cons
       }
     }
     __syncthreads();
-    for (int i = tid; i < SG_MAX_M * (OUT / 8); i += SG_THREADS) {
+    for (int i = tid; i < SG_MAX_M * (OUT / 8); i += SG_STD_THREADS) {
       const int r = i / (OUT / 8), c = i % (OUT / 8);
       const int n0 = rb * OUT + c * 8;
       if (r < p.m && n0 < p.n)  // N is a multiple of 8: a 16-byte chunk is inside or outside as a whole
@@ -517,7 +537,8 @@ template <bool SWIGLU>
 static int launch_skinny(SkinnyGemmParams p, const void* weight, int w_rows, cudaStream_t stream, const char* what) {
   const CUtensorMap* map = cache_weight_map(weight, w_rows, p.k, SWIGLU ? 8 : 16);
   if (!map) return fail(ERR_RUNTIME, "%s: cannot encode the weight tensor map", what);
-  constexpr int smem_max = SG_WARPS * SG_RING_BYTES + SG_MAX_M * SG_ROWS * 2 + SG_MAX_M * (SG_MAX_K * 2 + 16) + 1024;
+  constexpr int smem_max =
+      SG_WARPS * SG_RING_BYTES + SG_MAX_M * SG_ROWS * 2 + SG_PART_BYTES + SG_MAX_M * (SG_MAX_K * 2 + 16) + 1024;
   static_assert(smem_max <= 227 * 1024, "weight rings + X staging must fit the 227 KiB a CTA may use");
   static bool configured[64] = {false};
   int dev = 0;
@@ -535,8 +556,8 @@ static int launch_skinny(SkinnyGemmParams p, const void* weight, int w_rows, cud
   int grid = p.row_blocks;
   const int sms = sm_count();
   if (grid > sms) grid = sms;
-  const int dyn = SG_WARPS * SG_RING_BYTES + SG_MAX_M * SG_ROWS * 2 + SG_MAX_M * (p.k * 2 + 16) + 1024;
-  if (launch_pdl((p.overlap & OVERLAP_START) != 0, skinny_gemm_kernel<SWIGLU>, dim3(grid), dim3(SG_THREADS), dyn, stream,
+  const int dyn = SG_WARPS * SG_RING_BYTES + SG_MAX_M * SG_ROWS * 2 + SG_PART_BYTES + SG_MAX_M * (p.k * 2 + 16) + 1024;
+  if (launch_pdl((p.overlap & OVERLAP_START) != 0, skinny_gemm_kernel<SWIGLU>, dim3(grid), dim3(SG_STD_THREADS), dyn, stream,
                  p, *map) != cudaSuccess)
     return fail(ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(cudaGetLastError()));
   return check_launch(what);
