@@ -120,12 +120,18 @@ gdn_decode_fused_kernel(const __nv_bfloat16* fused, int64_t fused_stride,  // no
 #pragma unroll
     for (int r = 0; r < 4; ++r) cw[part][r] = w4[r * width + c];
   }
+  // the weights of the epilogue and of the gates are fetched up front as well: nothing later waits for a first touch
+  const float wv = norm_w[t];
+  const float a_log_h = a_log[h], dt_bias_h = __bfloat162float(dt_bias[h]);
   float s[GDN_D];
 #pragma unroll
   for (int i = 0; i < GDN_D; ++i) s[i] = __ldcs(sp + i * GDN_D);  // streamed once: evict-first
   pdl_wait();
+  // every value of the projection row this thread needs, in one round trip
 #pragma unroll
   for (int part = 0; part < 3; ++part) cx[part] = row[part * kd + h * GDN_D + t];
+  const float zv = __bfloat162float(row[width + h * GDN_D + t]);
+  const float a_raw = __bfloat162float(row[width + kd + h]), b_raw = __bfloat162float(row[width + kd + heads + h]);
   float y[3];
 #pragma unroll
   for (int part = 0; part < 3; ++part) {
@@ -141,19 +147,16 @@ gdn_decode_fused_kernel(const __nv_bfloat16* fused, int64_t fused_stride,  // no
     acc = fmaf(__bfloat162float(cw[part][3]), __bfloat162float(cx[part]), acc);
     y[part] = round_bf16(acc / (1.0f + expf(-acc)));
   }
-  const float zv = __bfloat162float(row[width + h * GDN_D + t]);
-  const float wv = norm_w[t];
   float sq = warp_sum(y[0] * y[0]), sk = warp_sum(y[1] * y[1]);
   if ((t & 31) == 0) {
     red[0][t >> 5] = sq;
     red[1][t >> 5] = sk;
   }
   if (t == 0) {
-    const float av = __bfloat162float(row[width + kd + h]) + __bfloat162float(dt_bias[h]);
-    const float bv = __bfloat162float(row[width + kd + heads + h]);
+    const float av = a_raw + dt_bias_h;
     const float sp_ = av > 20.f ? av : log1pf(expf(av));
-    gate_s[0] = 1.0f / (1.0f + expf(-bv));              // beta
-    gate_s[1] = __expf(-expf(a_log[h]) * sp_);           // exp(g)
+    gate_s[0] = 1.0f / (1.0f + expf(-b_raw));            // beta
+    gate_s[1] = __expf(-expf(a_log_h) * sp_);            // exp(g)
   }
   __syncthreads();
   sq = (red[0][0] + red[0][1]) + (red[0][2] + red[0][3]);
