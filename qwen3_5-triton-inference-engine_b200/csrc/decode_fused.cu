@@ -209,6 +209,7 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   __shared__ uint64_t bars[FD_WARPS][FD_RING];
   __shared__ int s_last;
+  __shared__ int s_max_units;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* merge = reinterpret_cast<float*>(smem + FD_SMEM_RING);
   int* cum = reinterpret_cast<int*>(smem + FD_SMEM_RING + FD_SMEM_MERGE);
@@ -236,10 +237,11 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   }
   __syncthreads();
   if (warp == 0) {
-    int carry = 0;
+    int carry = 0, longest = 0;
     for (int base = 0; base < batch; base += 32) {
       const int idx = base + lane;
       int v = (idx < batch) ? cum[idx + 1] : 0;
+      longest = max(longest, v);
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const int n = __shfl_up_sync(0xffffffffu, v, o);
@@ -248,16 +250,42 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
       if (idx < batch) cum[idx + 1] = v + carry;
       carry += __shfl_sync(0xffffffffu, v, 31);
     }
-    if (lane == 0) cum[0] = 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, o));
+    if (lane == 0) {
+      cum[0] = 0;
+      s_max_units = longest;
+    }
   }
   __syncthreads();
 
-  // equal ranges of units per CTA, but never less than one unit per warp: tiny problems use fewer CTAs and leave
-  // fewer partials to merge
+  // Two ways to cut the work.
+  //  - Stream-K: equal ranges of units per CTA (never less than one unit per warp: tiny problems use fewer CTAs and leave
+  //    fewer partials to merge).  Balanced whatever the context lengths, but a segment cut by a range boundary costs a
+  //    partial, a ticket and a merge, and a CTA that spans several segments stops at every boundary.
+  //  - One whole segment per CTA, when there are no more segments than CTAs: no partials at all, but the longest
+  //    segment sets the time, and an SM alone streams at about 75 GB/s.
+  // The choice compares two time models fitted to measurements of this kernel on B200 (microseconds x 1000, u = units):
+  //    whole   max(0.165, 0.35 * segments / CTAs) * u_longest + 9.5     stream-K   0.35 * u_per_CTA + 16.5
   const int total = heads * cum[batch];
-  const int chunk = max((total + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x), FD_WARPS);
-  const int r0 = blockIdx.x * chunk;
-  const int r1 = min(r0 + chunk, total);
+  const int grid = static_cast<int>(gridDim.x), nseg = batch * heads;
+  const int chunk = max((total + grid - 1) / grid, FD_WARPS);
+  const bool whole_segments =
+      nseg <= grid && max(165, 350 * nseg / grid) * s_max_units + 9500 < 350 * chunk + 16500;
+  int r0, r1;
+  if (whole_segments) {
+    if (static_cast<int>(blockIdx.x) < nseg) {
+      const int sb = blockIdx.x / heads, sh = blockIdx.x % heads;
+      const int units = cum[sb + 1] - cum[sb];
+      r0 = heads * cum[sb] + sh * units;
+      r1 = r0 + units;
+    } else {
+      r0 = r1 = total;
+    }
+  } else {
+    r0 = blockIdx.x * chunk;
+    r1 = min(r0 + chunk, total);
+  }
   if (r0 >= r1) {
     pdl_wait();  // an idle CTA still orders the grid after its predecessor
     return;
