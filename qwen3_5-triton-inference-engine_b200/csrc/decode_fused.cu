@@ -271,7 +271,7 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   const int grid = static_cast<int>(gridDim.x), nseg = batch * heads;
   const int chunk = max((total + grid - 1) / grid, FD_WARPS);
   const bool whole_segments =
-      nseg <= grid && max(165, 350 * nseg / grid) * s_max_units + 9500 < 350 * chunk + 16500;
+      nseg <= grid && 21 * (max(165, 350 * nseg / grid) * s_max_units + 9500) < 20 * (350 * chunk + 16500);  // by 5 %
   int r0, r1;
   if (whole_segments) {
     if (static_cast<int>(blockIdx.x) < nseg) {
