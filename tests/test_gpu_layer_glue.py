@@ -119,7 +119,7 @@ def test_gdn_decode_fused_equals_chain(mods, batch, prefetch):
 
 @pytest.mark.parametrize("m,n,k", [(32, 8224, 1024), (1, 5120, 1024), (17, 7168, 1024), (32, 248320, 1024), (8, 512, 256),
                                    (32, 1024, 1280), (32, 1024, 2048), (32, 1024, 3584), (5, 256, 2048), (17, 40, 1536),
-                                   (32, 4096, 7168), (1, 8, 16384)])
+                                   (32, 4096, 7168), (1, 8, 16384), (32, 4096, 2048), (3, 2400, 4096)])
 def test_skinny_gemm(mods, m, n, k):
     """Weight-streaming decode GEMM against an fp32 matmul of the same bf16 operands (exact products, fp32
     accumulation on both sides: only the summation order and the final bf16 rounding differ)."""
