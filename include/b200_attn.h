@@ -331,6 +331,13 @@ int b200_skinny_gemm(const void* x, int64_t x_stride, const void* weight, void* 
 int b200_skinny_gemm_swiglu(const void* x, int64_t x_stride, const void* weight, void* y, int64_t y_stride, int32_t m,
                             int32_t intermediate, int32_t k, int32_t overlap, b200_stream_t stream);
 
+/* ids[b] = argmax over n of <x[b, :], weight[n, :]> with fp32 accumulation, ties to the lowest n: the LM head with a tied
+ * embedding and its greedy sampling in one launch (triton_kernels/vocab_argmax.py:141-200); the logits are never written.
+ * The decode GEMM above with an arg-max epilogue: x [M <= 32, K <= 1280] bf16, weight [N, K] bf16 contiguous, N a multiple
+ * of 8, ids int64 [M]; workspace as for b200_argmax_rows (zero-filled once, left zero by every launch). */
+int b200_lm_head_argmax(const void* x, int64_t x_stride, const void* weight, int64_t* ids, void* workspace, int32_t m,
+                        int32_t n, int32_t k, int32_t overlap, b200_stream_t stream);
+
 /* ids[r] = argmax over n of logits[r, n] (fp32 [rows, n], row stride in elements), ties to the lowest index: the arg-max
  * half of triton_kernels/vocab_argmax.py:141-200, for logits produced by a library GEMM.  ids is int64 [rows].
  * workspace: b200_argmax_rows_workspace_bytes() bytes, 8-byte aligned, zero-filled once (every launch leaves it zero);

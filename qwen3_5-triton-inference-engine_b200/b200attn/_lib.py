@@ -45,6 +45,7 @@ SIGNATURES: dict[str, list] = {
     "b200_skinny_gemm": [P, I64, P, P, I64, I32, I32, I32, I32, P],
     "b200_skinny_gemm_swiglu": [P, I64, P, P, I64, I32, I32, I32, I32, P],
     "b200_argmax_rows": [P, I64, P, P, I32, I32, I32, P],
+    "b200_lm_head_argmax": [P, I64, P, P, P, I32, I32, I32, I32, P],
     "b200_add_rmsnorm": [P, I64, I64, I32, P, I64, P, P, P, I32, I32, c_float, I32, P],
     "b200_swiglu": [P, I64, P, I32, I32, I32, P],
     "b200_gdn_decode_prep": [P, I64, P, P, P, I64, P, I64, P, P, P, P, P, P, P, I32, I32, I32, P],

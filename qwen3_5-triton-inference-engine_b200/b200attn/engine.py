@@ -274,10 +274,15 @@ class Engine:
             else:
                 act = ops.swiglu_fused(glue.gemm_2d(h, layer["gate_up"]), cfg.intermediate, overlap=then(own_down))
             pending = self._proj(act, layer["down"], then(True))
-        _, h = ops.add_rmsnorm(pending, self.w["norm"], cfg.eps, residual=x, overlap=start)   # cuBLAS follows
-        # tied LM head: fp32 logits from cuBLAS, arg-max (lowest index on ties) in one launch
-        nxt = glue.lm_head_argmax(h, self.w["embed"], last_only=False,
-                                  argmax=lambda logits: ops.argmax_rows(logits, self.argmax_ws, overlap=start))
+        embed = self.w["embed"]
+        own_head = (embed.shape[1] <= ops.SKINNY_GEMM_MAX_K
+                    and ops.skinny_gemm_supports(batch, embed.shape[0], embed.shape[1]))
+        _, h = ops.add_rmsnorm(pending, self.w["norm"], cfg.eps, residual=x, overlap=then(own_head))
+        if own_head:   # tied LM head and greedy sampling in one launch; the logits are never written
+            nxt = ops.lm_head_argmax(h, embed, self.argmax_ws, overlap=start)
+        else:          # fp32 logits from cuBLAS, arg-max (lowest index on ties) in one launch
+            nxt = glue.lm_head_argmax(h, embed, last_only=False,
+                                      argmax=lambda logits: ops.argmax_rows(logits, self.argmax_ws, overlap=start))
         self.pos.add_(1)
         return nxt
 

@@ -722,6 +722,22 @@ def argmax_rows(logits, workspace, out=None, overlap: int = 0) -> torch.Tensor:
     return out
 
 
+def lm_head_argmax(hidden, table, workspace, out=None, overlap: int = 0) -> torch.Tensor:
+    """ids[b] = argmax_v <hidden[b], table[v]> (fp32 accumulation, ties to the lowest id) in one launch: the tied LM head
+    and greedy sampling of triton_kernels/vocab_argmax.py:141-200 without writing the logits.  hidden [M <= 32, K <= 1280]
+    bf16, table [V, K] bf16 contiguous, V a multiple of 8; workspace from `argmax_workspace`.  Returns int64 [M]."""
+    assert hidden.ndim == 2 and table.ndim == 2 and hidden.shape[1] == table.shape[1]
+    assert hidden.dtype == table.dtype == torch.bfloat16 and table.is_contiguous() and hidden.stride(1) == 1
+    _require_cuda(hidden, table, workspace)
+    m, k = hidden.shape
+    if out is None:
+        out = torch.empty(m, dtype=torch.int64, device=hidden.device)
+    assert out.dtype == torch.int64 and out.is_contiguous() and out.numel() == m
+    _lib.call("b200_lm_head_argmax", _ptr(hidden), hidden.stride(0), _ptr(table), _ptr(out), _ptr(workspace), m,
+              table.shape[0], k, int(overlap), _stream())
+    return out
+
+
 SKINNY_GEMM_MAX_M, SKINNY_GEMM_MAX_K = 32, 1280      # MAX_K: X staged whole; longer rows take the wide-K form
 SKINNY_GEMM_PAIR_MAX_K = 4096                        # up to here long rows are split over a pair of CTAs (K % 256 == 0)
 SKINNY_GEMM_WIDE_CHUNK, SKINNY_GEMM_WIDE_MAX_K = 1024, 16384

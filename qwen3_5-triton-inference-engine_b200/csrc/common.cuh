@@ -196,6 +196,14 @@ inline cudaError_t launch_pdl_cluster(bool early_start, unsigned cluster_x, void
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
+// ----------------------------------------------------------------------------- arg-max keys
+// (value, index) as one 64-bit key whose unsigned order is "larger value first, then smaller index"; 0 is below every key.
+__device__ __forceinline__ unsigned long long argmax_key(float v, uint32_t idx) {
+  uint32_t u = __float_as_uint(v);
+  u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);  // monotone map of the float order onto unsigned integers
+  return (static_cast<unsigned long long>(u) << 32) | (0xffffffffu - idx);
+}
+
 // ----------------------------------------------------------------------------- thread-block clusters
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;

@@ -168,12 +168,6 @@ gdn_gated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat1
 constexpr int AM_THREADS = 256;
 constexpr int AM_MAX_ROWS = 1024;
 
-__device__ __forceinline__ unsigned long long argmax_key(float v, uint32_t idx) {
-  uint32_t u = __float_as_uint(v);
-  u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);  // monotone map of the float order onto unsigned integers
-  return (static_cast<unsigned long long>(u) << 32) | (0xffffffffu - idx);
-}
-
 __global__ void __launch_bounds__(AM_THREADS)
 argmax_rows_kernel(const float* logits, int64_t row_stride, int n, int64_t* __restrict__ ids,  // logits: no __restrict__
                    unsigned long long* keys, int* counters, int overlap) {                    // (read after pdl_wait)

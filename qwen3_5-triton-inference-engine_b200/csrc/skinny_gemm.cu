@@ -41,9 +41,13 @@ struct SkinnyGemmParams {
   int64_t x_stride, y_stride;
   int* err;
   int m, n, k, row_blocks, overlap, up_row0;  // n: outputs; up_row0: first W row of the `up` half (SwiGLU form)
+  // arg-max form: ids[b] = argmax_n y[b, n] instead of y (keys / counter: zero-filled workspace, left zero)
+  int64_t* ids;
+  unsigned long long* keys;
+  int* counter;
 };
 
-template <bool SWIGLU>
+template <bool SWIGLU, bool ARGMAX>
 __global__ void __launch_bounds__(SG_STD_THREADS, 1)
 skinny_gemm_kernel(const __grid_constant__ SkinnyGemmParams p, const __grid_constant__ CUtensorMap map_w) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -113,6 +117,14 @@ skinny_gemm_kernel(const __grid_constant__ SkinnyGemmParams p, const __grid_cons
   //                          B (X) row = (lane & 7) + 8 * (lane >> 4) inside a 16-row pair, k half = (lane >> 3) & 1
   const int a_row = lane & 15, a_par = lane >> 4;
   const uint32_t b_lane = static_cast<uint32_t>(((lane & 7) + ((lane >> 4) << 3)) * x_pitch + ((lane >> 3) & 1) * 16);
+  // arg-max form: this thread's running best over its rows, per batch column (8 columns: nt * 2 + (j & 1))
+  float best_v[8];
+  uint32_t best_i[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    best_v[c] = -INFINITY;
+    best_i[c] = 0xffffffffu;
+  }
   int t = 0;
   for (int blk = 0; blk < my_blocks; ++blk) {  // a failed wait clears `ok`; the loop then only keeps its barriers
     const int rb = blockIdx.x + blk * gridDim.x;
@@ -155,6 +167,27 @@ skinny_gemm_kernel(const __grid_constant__ SkinnyGemmParams p, const __grid_cons
     if (kh == 0) {
 #pragma unroll
       for (int i = 0; i < 16; ++i) acc[i >> 2][i & 3] += part[i * (SG_WARPS * 32) + wr * 32 + lane];
+    }
+    if (ARGMAX) {
+      if (kh == 0) {
+        // rows ascend with the row block and, inside it, from fragment row r to r + 8: strict > keeps the lowest index
+        const uint32_t n_lo = static_cast<uint32_t>(rb * OUT + wr * 16 + (lane >> 2));
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int c = nt * 2 + (j & 1);
+            const uint32_t n = n_lo + (j >= 2 ? 8u : 0u);
+            if (n < static_cast<uint32_t>(p.n) && (acc[nt][j] > best_v[c] || best_i[c] == 0xffffffffu)) {
+              best_v[c] = acc[nt][j];
+              best_i[c] = n;
+            }
+          }
+      }
+      __syncthreads();  // `part` may be rewritten by the next row block
+      continue;
+    }
+    if (kh == 0) {
       __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage);
       const int bc = (lane & 3) * 2;
 #pragma unroll
@@ -182,6 +215,44 @@ skinny_gemm_kernel(const __grid_constant__ SkinnyGemmParams p, const __grid_cons
       if (r < p.m && n0 < p.n)  // N is a multiple of 8: a 16-byte chunk is inside or outside as a whole
         *reinterpret_cast<uint4*>(p.y + static_cast<int64_t>(r) * p.y_stride + n0) =
             *reinterpret_cast<const uint4*>(stage + (r * OUT + c * 8) * 2);
+    }
+  }
+  if (ARGMAX) {
+    // lanes that share lane % 4 hold the same batch columns: fold them, then the four row groups, then the CTAs
+    unsigned long long* keybuf = reinterpret_cast<unsigned long long*>(part);  // [4 row groups][32 batch]
+    if (kh == 0) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        unsigned long long key = best_i[c] == 0xffffffffu ? 0ull : argmax_key(best_v[c], best_i[c]);
+#pragma unroll
+        for (int o = 4; o <= 16; o <<= 1) {
+          const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+          key = other > key ? other : key;
+        }
+        if (lane < 4) keybuf[wr * SG_MAX_M + (c >> 1) * 8 + lane * 2 + (c & 1)] = key;
+      }
+    }
+    __syncthreads();
+    if (warp == 0) {
+      if (lane < p.m && ok) {
+        unsigned long long key = keybuf[lane];
+#pragma unroll
+        for (int w = 1; w < SG_WARPS; ++w) key = keybuf[w * SG_MAX_M + lane] > key ? keybuf[w * SG_MAX_M + lane] : key;
+        atomicMax(p.keys + lane, key);
+      }
+      __threadfence();
+      __syncwarp();
+      int last = 0;
+      if (lane == 0) last = (atomicAdd(p.counter, 1) == static_cast<int>(gridDim.x) - 1);
+      last = __shfl_sync(0xffffffffu, last, 0);
+      if (last) {  // every CTA's keys are in: unpack the ids and leave the workspace zero for the next launch
+        __threadfence();
+        if (lane < p.m) {
+          const unsigned long long top = atomicExch(p.keys + lane, 0ull);
+          p.ids[lane] = static_cast<int64_t>(0xffffffffu - static_cast<uint32_t>(top & 0xffffffffull));
+        }
+        if (lane == 0) *p.counter = 0;
+      }
     }
   }
   if (!ok) {
@@ -533,7 +604,7 @@ static const CUtensorMap* cache_weight_map(const void* base, int64_t n, int64_t 
 
 using namespace b200;
 
-template <bool SWIGLU>
+template <bool SWIGLU, bool ARGMAX = false>
 static int launch_skinny(SkinnyGemmParams p, const void* weight, int w_rows, cudaStream_t stream, const char* what) {
   const CUtensorMap* map = cache_weight_map(weight, w_rows, p.k, SWIGLU ? 8 : 16);
   if (!map) return fail(ERR_RUNTIME, "%s: cannot encode the weight tensor map", what);
@@ -544,7 +615,7 @@ static int launch_skinny(SkinnyGemmParams p, const void* weight, int w_rows, cud
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    if (cudaFuncSetAttribute(skinny_gemm_kernel<SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max) !=
+    if (cudaFuncSetAttribute(skinny_gemm_kernel<SWIGLU, ARGMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max) !=
         cudaSuccess)
       return fail(ERR_RUNTIME, "%s: cannot raise dynamic shared memory to %d", what, smem_max);
     configured[dev] = true;
@@ -557,7 +628,7 @@ static int launch_skinny(SkinnyGemmParams p, const void* weight, int w_rows, cud
   const int sms = sm_count();
   if (grid > sms) grid = sms;
   const int dyn = SG_WARPS * SG_RING_BYTES + SG_MAX_M * SG_ROWS * 2 + SG_PART_BYTES + SG_MAX_M * (p.k * 2 + 16) + 1024;
-  if (launch_pdl((p.overlap & OVERLAP_START) != 0, skinny_gemm_kernel<SWIGLU>, dim3(grid), dim3(SG_STD_THREADS), dyn, stream,
+  if (launch_pdl((p.overlap & OVERLAP_START) != 0, skinny_gemm_kernel<SWIGLU, ARGMAX>, dim3(grid), dim3(SG_STD_THREADS), dyn, stream,
                  p, *map) != cudaSuccess)
     return fail(ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(cudaGetLastError()));
   return check_launch(what);
@@ -685,4 +756,25 @@ extern "C" int b200_skinny_gemm_swiglu(const void* x, int64_t x_stride, const vo
   p.overlap = overlap;
   p.up_row0 = intermediate;
   return launch_skinny<true>(p, weight, 2 * intermediate, reinterpret_cast<cudaStream_t>(stream), "skinny_gemm_swiglu");
+}
+
+extern "C" int b200_lm_head_argmax(const void* x, int64_t x_stride, const void* weight, int64_t* ids, void* workspace,
+                                   int32_t m, int32_t n, int32_t k, int32_t overlap, b200_stream_t stream) {
+  int rc = check_skinny_shape("lm_head_argmax", m, n, k);
+  if (rc != OK) return rc;
+  B200_REQUIRE(aligned16(x) && aligned16(weight) && x_stride % 8 == 0 && ids != nullptr && workspace != nullptr &&
+                   (reinterpret_cast<uintptr_t>(workspace) % 8 == 0),
+               "lm_head_argmax: x / weight must be 16-byte aligned, the x row stride a multiple of 8, the workspace "
+               "8-byte aligned");
+  SkinnyGemmParams p = {};
+  p.x = static_cast<const __nv_bfloat16*>(x);
+  p.x_stride = x_stride;
+  p.m = m;
+  p.n = n;
+  p.k = k;
+  p.overlap = overlap;
+  p.ids = ids;
+  p.keys = static_cast<unsigned long long*>(workspace);  // the layout of b200_argmax_rows: 1024 keys, then counters
+  p.counter = reinterpret_cast<int*>(p.keys + 1024);
+  return launch_skinny<false, true>(p, weight, n, reinterpret_cast<cudaStream_t>(stream), "lm_head_argmax");
 }

@@ -74,6 +74,8 @@ def test_greedy_tokens_match_fp32_recomputation(small, monkeypatch):
         return torch.argmax(logits, dim=-1)
 
     monkeypatch.setattr(glue, "lm_head_argmax", head)
+    from b200attn import ops
+    monkeypatch.setattr(ops, "lm_head_argmax", lambda hidden, table, workspace, out=None, overlap=0: head(hidden, table))
     toks, _ = _generate(E, cfg, weights, prompts, STEPS, graph=False)
     torch.cuda.synchronize()
     assert _lib.load().b200_wait_timed_out() == 0

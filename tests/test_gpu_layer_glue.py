@@ -230,3 +230,42 @@ def test_argmax_rows_equals_torch(mods, rows, n):
         ids = ops.argmax_rows(dev_logits, ws)
         assert torch.equal(ids.cpu(), torch.argmax(logits, dim=1))
         assert int(ws.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("m,v,k", [(32, 248320, 1024), (5, 2048, 256), (1, 40, 128), (17, 100000, 1280)])
+def test_lm_head_argmax(mods, m, v, k):
+    """LM head + greedy sampling in one launch against the fp32 logits of the same bf16 operands: the chosen id's
+    logit is the row maximum up to the fp32 summation order; with duplicated table rows (identical logits, computed
+    by identical arithmetic) the lowest id wins; the workspace is zero again afterwards."""
+    ops, _ = mods
+    gen = torch.Generator().manual_seed(m + v + k)
+    h = torch.randn(m, k, generator=gen).to(torch.bfloat16).to(DEV)
+    table = (torch.randn(v, k, generator=gen) * 0.05).to(torch.bfloat16).to(DEV)
+    ws = ops.argmax_workspace(DEV)
+    ids = ops.lm_head_argmax(h, table, ws)
+    logits = h.float() @ table.float().t()
+    top = logits.max(dim=1).values
+    picked = logits.gather(1, ids.view(-1, 1)).squeeze(1)
+    assert ids.dtype == torch.int64 and int(ids.min()) >= 0 and int(ids.max()) < v
+    assert torch.all(picked >= top - 1e-4 * top.abs().clamp_min(1.0)), (picked - top).min().item()
+    assert int(ws.abs().sum()) == 0
+    # ties: copy every row's winner to a few other rows, below and above it
+    table2 = table.clone()
+    expect = []
+    for r in range(m):
+        w = int(ids[r])
+        twins = sorted({w, (w * 7 + 3) % v, (w + v // 2) % v})
+        for tw in twins:
+            table2[tw] = table[w]
+        expect.append(twins)
+    ids2 = ops.lm_head_argmax(h, table2, ws)
+    logits2 = h.float() @ table2.float().t()
+    for r in range(m):
+        best = int(ids2[r])
+        # a copied row of another sequence's winner may beat this row's old maximum: accept any exact-tie set
+        ties = (logits2[r] >= logits2[r, best] - 1e-4 * max(1.0, abs(float(logits2[r, best])))).nonzero().flatten().tolist()
+        assert best in ties
+        same = [t for t in expect[r] if t in ties]
+        if best in expect[r]:
+            assert best == min(same)
+    assert int(ws.abs().sum()) == 0
