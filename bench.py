@@ -16,7 +16,8 @@ Reported on one JSON line:
   roofline   the fused kernel against the measured copy bandwidth of this pool's B200s
   cpu_baseline  the CPU oracle (a port of the reference operators' math, eager PyTorch on the host cores)
   sweep      us/layer and GB/s for B in {1,4,16,32,64,256}, random and fixed-32768 contexts, plus the drop-in
-             3-launch chain and the Gated-DeltaNet decode state update (not part of `value`)
+             3-launch chain, the Gated-DeltaNet decode state update, the decode-step projections and LM head of the
+             whole model (cuBLAS time beside each) and the prefill operators (not part of `value`)
 `--impl reference` times the reference operators' CPU math (the oracle port; the Triton reference itself cannot
 travel to the box) on a bounded sample of the same workload.
 Under torchrun each rank runs its own replica (weak scaling, no data-path collective); the time is the max over ranks.
@@ -387,7 +388,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of one CUDA graph")
     ap.add_argument("--no-model", action="store_true", help="skip the whole-model decode measurement (24-layer random-init model)")
     ap.add_argument("--model-steps", type=int, default=512)
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gdn"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gdn", "gemm"],
                     help="with --kernel-only: which kernel family to run (profiler captures of the other families)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
@@ -411,7 +412,10 @@ def main():
     from b200attn import ops
 
     if args.kernel_only and args.workload != "decode":
-        rows = run_prefill_sweep(ops, device, args.steps, only=args.workload)
+        if args.workload == "gemm":
+            rows = run_gemm_sweep(ops, device, hbm_peak()[0], args.steps)
+        else:
+            rows = run_prefill_sweep(ops, device, args.steps, only=args.workload)
         if rank == 0:
             emit({"kernel_only": True, "workload": args.workload, "rows": rows})
         if dist is not None:
@@ -641,7 +645,44 @@ def run_sweep(ops, ws, device, peak, steps):
                      "frac": nbytes / (ms * 1e-3) / 1e9 / peak})
         del states
         torch.cuda.empty_cache()
+    rows += run_gemm_sweep(ops, device, peak, steps)
     rows += run_prefill_sweep(ops, device, steps)
+    return rows
+
+
+def run_gemm_sweep(ops, device, peak, steps):
+    """The decode-step projections of BASELINE config 5 (32 sequences, hidden 1024): weight-streaming GEMMs, bound by the
+    weight bytes.  Weights rotate over enough copies that no call finds its matrix in L2; the cuBLAS time of the same
+    product (plus torch.argmax for the LM head) is reported beside each."""
+    import torch.nn.functional as F
+    rows = []
+    gen = torch.Generator().manual_seed(5)
+    m = 32
+    shapes = (("input projection (GDN layer)", 8224, 1024, "plain"), ("gate/up projection + SwiGLU", 7168, 1024, "swiglu"),
+              ("output projection", 1024, 2048, "plain"), ("down projection", 1024, 3584, "plain"),
+              ("LM head + arg-max", 248320, 1024, "argmax"))
+    ws_arg = ops.argmax_workspace(device)
+    for tag, n, k, kind in shapes:
+        nbytes = n * k * 2
+        copies = max(2, min(48, cdiv(3 * L2_BYTES, nbytes)))
+        x = torch.randn(m, k, generator=gen).to(torch.bfloat16).to(device)
+        weights = [(torch.randn(n, k, device=device) * 0.03).to(torch.bfloat16) for _ in range(copies)]
+        if kind == "swiglu":
+            own = lambda i: ops.skinny_gemm(x, weights[i % copies], swiglu=True)
+            lib = lambda i: ops.swiglu_fused(F.linear(x, weights[i % copies]), n // 2)
+        elif kind == "argmax":
+            own = lambda i: ops.lm_head_argmax(x, weights[i % copies], ws_arg)
+            lib = lambda i: torch.argmax(torch.mm(x, weights[i % copies].t(), out_dtype=torch.float32), dim=-1)
+        else:
+            own = lambda i: ops.skinny_gemm(x, weights[i % copies])
+            lib = lambda i: F.linear(x, weights[i % copies])
+        ms = time_steps(own, steps, 3)
+        ms_lib = time_steps(lib, steps, 3)
+        rows.append({"op": "decode GEMM: " + tag, "shape": f"[{m},{k}] x [{n},{k}]^T", "us": ms * 1e3,
+                     "gbs": nbytes / (ms * 1e-3) / 1e9, "frac_hbm": nbytes / (ms * 1e-3) / 1e9 / peak,
+                     "cublas_us": ms_lib * 1e3})
+        del weights
+        torch.cuda.empty_cache()
     return rows
 
 
