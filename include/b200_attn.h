@@ -49,6 +49,11 @@ int b200_wait_timed_out(void);
  * All matrices row-major and contiguous.  No counterpart in the reference; it validates the sm_100a building blocks
  * the prefill kernels use. */
 int b200_selftest_umma(int32_t mode, const void* a, const void* b, float* c, b200_stream_t stream);
+/* Diagnostic: one warp waits, with a small poll limit, on a staged-copy barrier that nothing will ever complete.  The
+ * wait gives up, the kernel sets the flag that b200_wait_timed_out() reports, leaves *sentinel (device int32) as it was
+ * and returns; nothing faults or hangs.  It exercises the give-up path that every kernel of this library takes when a
+ * copy it waits for does not arrive.  No counterpart in the reference. */
+int b200_selftest_wait_timeout(int32_t* sentinel, b200_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------ paged KV cache */
 /* cache[block_table[b, pos[b]/16], h, pos[b]%16, :] = new[b, h, :] for K and V.
@@ -117,7 +122,12 @@ int b200_fused_decode_attention(const void* q, int64_t q_stride_b, int64_t q_str
  * overlap (B200_OVERLAP_*, defined below): START lets the kernel begin while the kernel in front of it still runs;
  *   PREFETCH additionally lets it compute the position prefix, gather page ids and request its first K/V pages before
  *   that kernel has finished - pass it only when that kernel writes neither pos, the block table nor the caches (in a
- *   layer stack it is the q/k/v/gate projection).  q, k_new, v_new and gate are always read after it. */
+ *   layer stack it is the q/k/v/gate projection).  q, k_new, v_new and gate are always read after it.
+ * partition: how the KV pages are cut over the CTAs.  0 = the kernel chooses per launch from the lengths in pos[];
+ *   1 = always equal ranges of pages per CTA (segments cut at range boundaries are merged through the workspace);
+ *   2 = always one whole (sequence, kv head) segment per CTA (needs batch * num_kv_heads <= the number of SMs, else the
+ *   call is refused).  The result is the same up to fp32 summation order; 1 and 2 exist so that tests and tuning can
+ *   pin either form. */
 int b200_fused_decode_attention_ex(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_new,
                                    int64_t kn_stride_b, int64_t kn_stride_h, const void* v_new, int64_t vn_stride_b,
                                    int64_t vn_stride_h, const void* gate, int64_t gate_stride_b, void* k_cache,
@@ -127,7 +137,7 @@ int b200_fused_decode_attention_ex(const void* q, int64_t q_stride_b, int64_t q_
                                    const float* inv_freq, int32_t rotary_dim, void* out, void* workspace, int32_t batch,
                                    int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
                                    const void* q_norm_weight, const void* k_norm_weight, float eps, int32_t overlap,
-                                   b200_stream_t stream);
+                                   int32_t partition, b200_stream_t stream);
 
 /* The same fused decode step for callers that cannot allocate device memory (a host that owns the whole GPU and
  * forbids cudaMalloc after start-up, a plugin inside another process, code running under stream capture).  This
@@ -356,6 +366,51 @@ int b200_gdn_decode_prep(const void* qkv, int64_t qkv_stride, void* conv_state, 
                          int32_t head_dim, b200_stream_t stream);
 int b200_gdn_gated_rmsnorm(const void* x, const void* z, int64_t z_stride, const float* weight, void* out, int32_t rows,
                            int32_t num_heads, int32_t head_dim, b200_stream_t stream);
+
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * Element-wise operators of the Gated-DeltaNet input pipeline and of the residual stream (one launch each, any number
+ * of tokens).  bf16 tensors, fp32 math, one rounding where the reference rounds; channel counts are multiples of 8,
+ * pointers 16-byte aligned, row strides multiples of 8 elements unless stated otherwise.
+ *
+ * b200_conv4_prefill: out[t,c] = silu(sum_r weight[c,r] * x[t+r-3, c]) over a packed buffer of `tokens` rows; a tap
+ *   whose row lies before seq_start[t] (int32 [tokens], the first row of t's own sequence; NULL = one sequence starting
+ *   at row 0) reads zero.  weight element (c, r) at weight + c*w_stride_d + r*w_stride_k.
+ *   Replaces wy_lib::depthwise_causal_conv4_prefill, triton_kernels/depthwise_causal_conv4_prefill.py:108-170
+ *   (kernel :18-91).
+ * b200_conv4_decode: one token per sequence.  state [batch,4,channels] (contiguous, the last four conv INPUT rows) is
+ *   shifted up one row, x[b] becomes row 3, out[b,c] = silu(sum_r weight4[r,c] * state[b,r,c]).
+ *   Replaces wy_lib::depthwise_causal_conv4_decode, triton_kernels/depthwise_causal_conv4_decode.py:152-207
+ *   (kernel :78-149).
+ * b200_conv_state_from_packed_prefill: state[b,r,:] = x[cu_seqlens[b+1]-4+r, :] when that row belongs to sequence b,
+ *   else zero.  Replaces wy_lib::conv_state_from_packed_prefill, triton_kernels/depthwise_causal_conv4_decode.py:332-374
+ *   (kernel :254-329).
+ * b200_gdn_qk_norm_gates: q_out = q * rsqrt(sum q^2 + 1e-6) * 128^-0.5 and k_out = k * rsqrt(sum k^2 + 1e-6) as
+ *   contiguous bf16 [tokens,H,128]; beta = sigmoid(b) and g = -exp(a_log) * softplus(a + dt_bias) as fp32 [tokens,H].
+ *   q, k [tokens,H,128] with token / head strides (multiples of 4, 8-byte aligned); a, b [tokens,H] bf16 with a token
+ *   stride.  Replaces wy_lib::gdn_qk_norm_gates, triton_kernels/gdn_qk_norm_gates.py:128-200 (kernel :14-114).
+ * b200_embedding_gather: out[t,:] = table[ids[t],:] (ids int32 or int64 [tokens], table [V,dim] contiguous).
+ *   Replaces wy_lib::embedding_gather, triton_kernels/embedding_gather.py:62-100 (kernel :14-49).
+ * b200_residual_add: out[i] = bf16(x[i] + residual[i]) over `count` contiguous elements.
+ *   Replaces wy_lib::residual_add, triton_kernels/residual_add.py:23-50 (kernel :7-20).
+ * b200_swiglu_pair: b200_swiglu for gate and up given as two [rows,width] matrices with their own row strides
+ *   (triton_kernels/swiglu.py:75-110, kernel :17-59). */
+int b200_conv4_prefill(const void* x, int64_t x_stride_t, const void* weight, int64_t w_stride_d, int64_t w_stride_k,
+                       const int32_t* seq_start, void* out, int64_t out_stride_t, int32_t tokens, int32_t channels,
+                       b200_stream_t stream);
+int b200_conv4_decode(const void* x, int64_t x_stride_b, void* state, const void* weight4, void* out,
+                      int64_t out_stride_b, int32_t batch, int32_t channels, b200_stream_t stream);
+int b200_conv_state_from_packed_prefill(void* state, const void* x, int64_t x_stride_t, const int32_t* cu_seqlens,
+                                        int32_t batch, int32_t channels, b200_stream_t stream);
+int b200_gdn_qk_norm_gates(const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k, int64_t k_stride_t,
+                           int64_t k_stride_h, const void* a, int64_t a_stride_t, const void* b, int64_t b_stride_t,
+                           const float* a_log, const void* dt_bias, void* q_out, void* k_out, float* beta, float* g,
+                           int32_t tokens, int32_t num_heads, int32_t head_dim, b200_stream_t stream);
+int b200_embedding_gather(const void* ids, int32_t ids_are_int64, const void* table, void* out, int32_t tokens,
+                          int32_t dim, b200_stream_t stream);
+int b200_residual_add(const void* x, const void* residual, void* out, int64_t count, b200_stream_t stream);
+int b200_swiglu_pair(const void* gate, int64_t gate_stride, const void* up, int64_t up_stride, void* out, int32_t rows,
+                     int32_t width, b200_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -24,10 +24,11 @@ SIGNATURES: dict[str, list] = {
     "b200_fused_decode_attention": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, P, P, I64, I64, I64, I64, I64, I64,
                                     I64, P, I64, P, P, I32, P, P, I32, I32, I32, I32, P],
     "b200_fused_decode_attention_ex": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, P, P, I64, I64, I64, I64, I64,
-                                       I64, I64, P, I64, P, P, I32, P, P, I32, I32, I32, I32, P, P, c_float, I32, P],
+                                       I64, I64, P, I64, P, P, I32, P, P, I32, I32, I32, I32, P, P, c_float, I32, I32, P],
     "b200_fused_decode_attention_static": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, P, P, I64, I64, I64, I64, I64,
                                            I64, I64, P, I64, P, P, I32, P, I32, I32, I32, I32, P],
     "b200_selftest_umma": [I32, P, P, P, P],
+    "b200_selftest_wait_timeout": [P, P],
     "b200_gqa_varlen_causal": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I32, I32, I32, I32, I32, I32, P],
     "b200_fused_prefill_attention": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, P, P, I64, I64, I64, I64, I64, I64,
                                      P, I64, P, P, I32, P, I32, P, P, I32, I32, I32, I32, I32, I32, P],
@@ -51,6 +52,13 @@ SIGNATURES: dict[str, list] = {
     "b200_gdn_decode_prep": [P, I64, P, P, P, I64, P, I64, P, P, P, P, P, P, P, I32, I32, I32, P],
     "b200_gdn_decode_fused": [P, I64, P, P, P, P, P, P, P, I32, I32, I32, I32, P],
     "b200_gdn_gated_rmsnorm": [P, P, I64, P, P, I32, I32, I32, P],
+    "b200_conv4_prefill": [P, I64, P, I64, I64, P, P, I64, I32, I32, P],
+    "b200_conv4_decode": [P, I64, P, P, P, I64, I32, I32, P],
+    "b200_conv_state_from_packed_prefill": [P, P, I64, P, I32, I32, P],
+    "b200_gdn_qk_norm_gates": [P, I64, I64, P, I64, I64, P, I64, P, I64, P, P, P, P, P, P, I32, I32, I32, P],
+    "b200_embedding_gather": [P, I32, P, P, I32, I32, P],
+    "b200_residual_add": [P, P, P, I64, P],
+    "b200_swiglu_pair": [P, I64, P, I64, P, I32, I32, P],
     "b200_gdn_chunked_prefill_fused": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I32, I32,
                                        P, P, I64, I64, I32, I32, I32, P],
 }

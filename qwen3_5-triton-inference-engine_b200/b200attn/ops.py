@@ -145,7 +145,8 @@ def paged_gqa_attention_decode_combine(m_partial: torch.Tensor, l_partial: torch
     assert pos.dtype == torch.int64 and pos.shape == (batch,)
     _require_cuda(m_partial, l_partial, acc_partial, pos)
     out = torch.empty((batch, num_q_heads, head_dim), dtype=torch.bfloat16, device=acc_partial.device)
-    _lib.call("b200_paged_decode_combine", _ptr(m_partial), _ptr(l_partial), _ptr(acc_partial), _ptr(pos.contiguous()),
+    pos = pos.contiguous()  # kept alive until the launch is enqueued
+    _lib.call("b200_paged_decode_combine", _ptr(m_partial), _ptr(l_partial), _ptr(acc_partial), _ptr(pos),
               _ptr(out), batch, num_q_heads, head_dim, _stream())
     return out
 
@@ -211,13 +212,16 @@ def fused_decode_workspace(device="cuda") -> torch.Tensor:
 
 def fused_decode_attention(q, k_new, v_new, gate, k_cache, v_cache, block_table, pos, inv_freq, rotary_dim,
                            workspace, out=None, overlap: int = 0, q_norm_weight=None, k_norm_weight=None,
-                           eps: float = 1e-6) -> torch.Tensor:
+                           eps: float = 1e-6, partition: int = 0) -> torch.Tensor:
     """RoPE(q, k_new) + append + paged attention + sigmoid gate in one launch -> [B, H_q*D] bf16.
     q [B,H_q,D], k_new/v_new [B,H_kv,D] are the post-norm, PRE-RoPE projections; gate [B, H_q*D].
     q_norm_weight / k_norm_weight (bf16 [D]): q and k_new are the RAW projections and the per-head Qwen RMSNorm
     (engine/runner.py:476-489) is applied inside the kernel - the same bytes as add_rmsnorm in front of the call.
     overlap: OVERLAP_START lets the kernel begin while its predecessor in the stream runs; OVERLAP_PREFETCH also lets it
-    read pos / block_table / cache pages before that predecessor has finished (valid when it writes none of them)."""
+    read pos / block_table / cache pages before that predecessor has finished (valid when it writes none of them).
+    partition: 0 = the kernel picks how the KV pages are cut over the CTAs; 1 = equal page ranges per CTA (segments cut at
+    a range boundary are merged through the workspace); 2 = one whole (sequence, kv head) segment per CTA (needs
+    batch * H_kv <= the number of SMs).  Same result up to fp32 summation order."""
     batch, num_q_heads, head_dim = q.shape
     num_kv_heads = k_new.shape[1]
     assert k_new.shape == v_new.shape == (batch, num_kv_heads, head_dim)
@@ -241,7 +245,8 @@ def fused_decode_attention(q, k_new, v_new, gate, k_cache, v_cache, block_table,
               v_cache.stride(1), v_cache.stride(2), k_cache.shape[0], _ptr(block_table), block_table.stride(0), _ptr(pos),
               _ptr(inv_freq), int(rotary_dim), _ptr(out), _ptr(workspace), batch, num_q_heads, num_kv_heads, head_dim,
               _ptr(q_norm_weight) if q_norm_weight is not None else None,
-              _ptr(k_norm_weight) if k_norm_weight is not None else None, float(eps), int(overlap), _stream())
+              _ptr(k_norm_weight) if k_norm_weight is not None else None, float(eps), int(overlap), int(partition),
+              _stream())
     return out
 
 
@@ -263,9 +268,10 @@ def partial_rope(x: torch.Tensor, position_ids: torch.Tensor, inv_freq: torch.Te
     x = _inner_contiguous(x)
     out = torch.empty_like(x)
     assert out.stride(3) == 1
+    inv_freq = inv_freq.contiguous()  # kept alive until the launch is enqueued
     _lib.call("b200_partial_rope", _ptr(x), x.stride(0), x.stride(1), x.stride(2), _ptr(out), out.stride(0),
               out.stride(1), out.stride(2), _ptr(position_ids), int(position_ids.dtype == torch.int64),
-              position_ids.stride(0), position_ids.stride(1), _ptr(inv_freq.contiguous()), batch_size, num_heads,
+              position_ids.stride(0), position_ids.stride(1), _ptr(inv_freq), batch_size, num_heads,
               token_num, head_dim, int(rotary_dim), _stream())
     return out
 
@@ -396,8 +402,9 @@ def gqa_attention_varlen_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
     q, k, v = map(_inner_contiguous, (q, k, v))
     out = torch.empty_like(q)
     assert out.stride(2) == 1
+    cu_seqlens = cu_seqlens.contiguous()  # kept alive until the launch is enqueued
     _lib.call("b200_gqa_varlen_causal", _ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1), _ptr(v),
-              v.stride(0), v.stride(1), _ptr(out), out.stride(0), out.stride(1), _ptr(cu_seqlens.contiguous()), batch,
+              v.stride(0), v.stride(1), _ptr(out), out.stride(0), out.stride(1), _ptr(cu_seqlens), batch,
               total_tokens, int(max_seqlen), num_q_head, num_kv_head, d_model, _stream())
     return out
 
@@ -556,9 +563,27 @@ def _(q, k, delta, g_cumsum, chunk_state):
     return torch.empty((q.shape[0], q.shape[1], delta.shape[-1]), dtype=q.dtype, device=q.device)
 
 
+_ONE_SEQUENCE_CU: dict = {}
+
+
 def call_gdn_recurrent_prefill_chunked_triton(q, k, v, beta, g):
-    """prepare_wy -> chunk_state -> chunk_output for one sequence; returns (out, final_state).
-    triton_kernels/gdn_recurrent_prefill.py:1026-1047 (name kept for drop-in use; no Triton is involved)."""
+    """Chunk-64 prefill of ONE sequence; returns (out [T,H,DV] bf16, final_state [H,DK,DV] fp32).
+    triton_kernels/gdn_recurrent_prefill.py:1026-1047 (name kept for drop-in use; no Triton is involved).  The caller
+    wants only the output and the final state, so the three stages run as the single tensor-core kernel with
+    cu_seqlens = [0, T] whenever its layout rules hold (128-dim heads, 16-byte aligned q/k/v with strides that are
+    multiples of 8); otherwise as the three reference-shaped operators through their HBM intermediates."""
+    token_num = q.shape[0]
+    fusable = (q.shape[-1] == GDN_DIM and v.shape[-1] == GDN_DIM
+               and all(t.stride(-1) == 1 and t.stride(0) % 8 == 0 and t.stride(1) % 8 == 0 and t.data_ptr() % 16 == 0
+                       for t in (q, k, v)))
+    if fusable:
+        key = (q.device.index, token_num)
+        if key not in _ONE_SEQUENCE_CU:
+            if len(_ONE_SEQUENCE_CU) > 4096:
+                _ONE_SEQUENCE_CU.clear()
+            _ONE_SEQUENCE_CU[key] = torch.tensor([0, token_num], dtype=torch.int32, device=q.device)
+        out, state = gdn_chunked_prefill_packed(q, k, v, beta, g, _ONE_SEQUENCE_CU[key])
+        return out, state[0]
     w, u_base, g_cumsum = gdn_chunk_prepare_wy(k, v, beta, g)
     delta, chunk_state, final_state = gdn_chunk_state(k, w, u_base, g_cumsum)
     out = gdn_chunk_output(q, k, delta, g_cumsum, chunk_state)
@@ -582,17 +607,19 @@ def gdn_chunked_prefill_packed(q, k, v, beta, g, cu_seqlens, max_seqlen=None, fu
     state = torch.empty((batch, num_heads, key_dim, value_dim), dtype=torch.float32, device=q.device)
     out = torch.empty((token_num, num_heads, value_dim), dtype=q.dtype, device=q.device)
     if fused:
+        cu_seqlens = cu_seqlens.contiguous()  # kept alive until the launch is enqueued
         _lib.call("b200_gdn_chunked_prefill_fused", _ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1),
                   _ptr(v), v.stride(0), v.stride(1), _ptr(beta), beta.stride(0), beta.stride(1), _ptr(g), g.stride(0),
-                  g.stride(1), _ptr(cu_seqlens.contiguous()), batch, token_num, _ptr(state), _ptr(out), out.stride(0),
+                  g.stride(1), _ptr(cu_seqlens), batch, token_num, _ptr(state), _ptr(out), out.stride(0),
                   out.stride(1), num_heads, key_dim, value_dim, _stream())
         return out, state
     assert max_seqlen is not None, "the three-stage path needs max_seqlen"
     nbytes = _lib.load().b200_gdn_chunked_prefill_packed_workspace_bytes(batch, token_num, num_heads)
     workspace = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    cu_seqlens = cu_seqlens.contiguous()  # kept alive until the launch is enqueued
     _lib.call("b200_gdn_chunked_prefill_packed", _ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1),
               _ptr(v), v.stride(0), v.stride(1), _ptr(beta), beta.stride(0), beta.stride(1), _ptr(g), g.stride(0),
-              g.stride(1), _ptr(cu_seqlens.contiguous()), batch, token_num, int(max_seqlen), _ptr(workspace), _ptr(state),
+              g.stride(1), _ptr(cu_seqlens), batch, token_num, int(max_seqlen), _ptr(workspace), _ptr(state),
               _ptr(out), out.stride(0), out.stride(1), num_heads, key_dim, value_dim, _stream())
     return out, state
 
@@ -660,8 +687,9 @@ def gdn_decode_prep(qkv, conv_state, weight4, a, b, a_log, dt_bias, num_heads: i
     k_n, v = torch.empty_like(q_n), torch.empty_like(q_n)
     beta = torch.empty((batch, num_heads), dtype=torch.float32, device=dev)
     g = torch.empty_like(beta)
+    dt_bias = dt_bias.contiguous()  # kept alive until the launch is enqueued
     _lib.call("b200_gdn_decode_prep", _ptr(qkv), qkv.stride(0), _ptr(conv_state), _ptr(weight4), _ptr(a), a.stride(0),
-              _ptr(b), b.stride(0), _ptr(a_log), _ptr(dt_bias.contiguous()), _ptr(q_n), _ptr(k_n), _ptr(v), _ptr(beta),
+              _ptr(b), b.stride(0), _ptr(a_log), _ptr(dt_bias), _ptr(q_n), _ptr(k_n), _ptr(v), _ptr(beta),
               _ptr(g), batch, num_heads, GDN_DIM, _stream())
     return q_n, k_n, v, beta, g
 
@@ -697,8 +725,9 @@ def gdn_decode_fused(fused, conv_state, weight4, a_log, dt_bias, norm_weight, st
     assert state.shape == (batch, num_heads, GDN_DIM, GDN_DIM) and state.is_contiguous() and state.dtype == torch.float32
     _require_cuda(fused, conv_state, weight4, a_log, dt_bias, norm_weight, state)
     out = torch.empty((batch, kd), dtype=torch.bfloat16, device=fused.device)
+    dt_bias = dt_bias.contiguous()  # kept alive until the launch is enqueued
     _lib.call("b200_gdn_decode_fused", _ptr(fused), fused.stride(0), _ptr(conv_state), _ptr(weight4), _ptr(a_log),
-              _ptr(dt_bias.contiguous()), _ptr(norm_weight), _ptr(state), _ptr(out), batch, num_heads, GDN_DIM,
+              _ptr(dt_bias), _ptr(norm_weight), _ptr(state), _ptr(out), batch, num_heads, GDN_DIM,
               int(overlap), _stream())
     return out
 

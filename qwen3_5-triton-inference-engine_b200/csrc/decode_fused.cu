@@ -23,6 +23,8 @@
 #include "decode_core.cuh"
 #include "umma.cuh"
 
+#include <mutex>
+
 namespace b200 {
 
 constexpr int FD_WARPS = 8;
@@ -58,6 +60,7 @@ struct FusedDecodeParams {
   int* counters;
   int* err;
   int batch, num_kv_heads, rotary_half, overlap;
+  int partition;  // 0 = the time models below choose, 1 = stream-K, 2 = one whole segment per CTA
   float scale, eps;
 };
 
@@ -270,8 +273,8 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   const int total = heads * cum[batch];
   const int grid = static_cast<int>(gridDim.x), nseg = batch * heads;
   const int chunk = max((total + grid - 1) / grid, FD_WARPS);
-  const bool whole_segments =
-      nseg <= grid && 21 * (max(165, 350 * nseg / grid) * s_max_units + 9500) < 20 * (350 * chunk + 16500);  // by 5 %
+  const bool model_whole = 21 * (max(165, 350 * nseg / grid) * s_max_units + 9500) < 20 * (350 * chunk + 16500);  // by 5 %
+  const bool whole_segments = nseg <= grid && (p.partition == 2 || (p.partition == 0 && model_whole));
   int r0, r1;
   if (whole_segments) {
     if (static_cast<int>(blockIdx.x) < nseg) {
@@ -512,8 +515,12 @@ using namespace b200;
 
 // Tensor maps of the KV pools seen as matrices of token rows [rows][256]; a box is one page of one head
 // ({64 dims, 16 rows, 4 column blocks}).  Encoding costs a few microseconds of host time, so the last few
-// (pointer, rows) pairs are remembered: a model has a fixed set of pools.
-static const CUtensorMap* cache_tile_map(const void* base, int64_t rows) {
+// (pointer, rows) pairs are remembered: a model has a fixed set of pools.  The table is shared by all host threads:
+// it is searched and filled under a mutex and the map is copied out, so a concurrent caller cannot overwrite an entry
+// between the look-up and the launch.
+static bool cache_tile_map(const void* base, int64_t rows, CUtensorMap* out) {
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
   struct Entry {
     const void* base;
     int64_t rows;
@@ -526,15 +533,20 @@ static const CUtensorMap* cache_tile_map(const void* base, int64_t rows) {
   int dev = 0;
   cudaGetDevice(&dev);
   for (int i = 0; i < used; ++i)
-    if (entries[i].base == base && entries[i].rows == rows && entries[i].dev == dev) return &entries[i].map;
+    if (entries[i].base == base && entries[i].rows == rows && entries[i].dev == dev) {
+      *out = entries[i].map;
+      return true;
+    }
   Entry& e = entries[next];
-  if (!encode_tile_map(&e.map, base, static_cast<uint64_t>(rows), HEAD_DIM, HEAD_DIM * 2, PAGE, HEAD_DIM / 64)) return nullptr;
+  e.base = nullptr;  // not a valid entry while it is being rewritten
+  if (!encode_tile_map(&e.map, base, static_cast<uint64_t>(rows), HEAD_DIM, HEAD_DIM * 2, PAGE, HEAD_DIM / 64)) return false;
   e.base = base;
   e.rows = rows;
   e.dev = dev;
   next = (next + 1) % N;
   if (used < N) ++used;
-  return &e.map;
+  *out = e.map;
+  return true;
 }
 
 extern "C" int64_t b200_fused_decode_workspace_bytes(void) { return FD_WORKSPACE_BYTES; }
@@ -549,7 +561,8 @@ static int fused_decode_impl(const void* q, int64_t q_stride_b, int64_t q_stride
                                            const float* inv_freq, int32_t rotary_dim, void* out, void* workspace,
                                            int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
                                            const void* q_norm_weight, const void* k_norm_weight, float eps,
-                                           int32_t overlap, b200_stream_t stream) {
+                                           int32_t overlap, int32_t partition, b200_stream_t stream) {
+  B200_REQUIRE(partition >= 0 && partition <= 2, "fused_decode_attention: partition must be 0, 1 or 2 (got %d)", partition);
   B200_REQUIRE(aligned16(q_norm_weight) && aligned16(k_norm_weight),
                "fused_decode_attention: norm weights must be 16-byte aligned");
   B200_REQUIRE(batch > 0 && batch <= FD_MAX_BATCH, "fused_decode_attention: batch must be in [1, %d] (got %d)",
@@ -576,9 +589,10 @@ static int fused_decode_impl(const void* q, int64_t q_stride_b, int64_t q_stride
   B200_REQUIRE(num_pages > 0 && kc_stride_s == HEAD_DIM && vc_stride_s == HEAD_DIM && kc_stride_h == dense_h &&
                    vc_stride_h == dense_h && kc_stride_p == dense_p && vc_stride_p == dense_p,
                "fused_decode_attention: k_cache / v_cache must be contiguous [num_pages, H_kv, 16, 256]");
-  const CUtensorMap* map_k = cache_tile_map(k_cache, num_pages * num_kv_heads * PAGE);
-  const CUtensorMap* map_v = cache_tile_map(v_cache, num_pages * num_kv_heads * PAGE);
-  if (!map_k || !map_v) return fail(ERR_RUNTIME, "fused_decode_attention: cannot encode the cache tensor maps");
+  CUtensorMap map_k, map_v;
+  if (!cache_tile_map(k_cache, num_pages * num_kv_heads * PAGE, &map_k) ||
+      !cache_tile_map(v_cache, num_pages * num_kv_heads * PAGE, &map_v))
+    return fail(ERR_RUNTIME, "fused_decode_attention: cannot encode the cache tensor maps");
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -620,8 +634,12 @@ static int fused_decode_impl(const void* q, int64_t q_stride_b, int64_t q_stride
   p.scale = 1.0f / sqrtf(static_cast<float>(head_dim));
   int grid = sm_count();
   if (grid > FD_MAX_CTAS) grid = FD_MAX_CTAS;
+  B200_REQUIRE(partition != 2 || batch * num_kv_heads <= grid,
+               "fused_decode_attention: partition 2 (whole segments) needs batch*H_kv <= %d CTAs (got %d)", grid,
+               batch * num_kv_heads);
+  p.partition = partition;
   if (launch_pdl((overlap & OVERLAP_START) != 0, fused_decode_kernel, dim3(grid), dim3(FD_THREADS), FD_SMEM_TOTAL,
-                 reinterpret_cast<cudaStream_t>(stream), p, *map_k, *map_v) != cudaSuccess)
+                 reinterpret_cast<cudaStream_t>(stream), p, map_k, map_v) != cudaSuccess)
     return fail(ERR_LAUNCH, "fused_decode_attention: %s", cudaGetErrorString(cudaGetLastError()));
   return check_launch("fused_decode_attention");
 }
@@ -669,7 +687,7 @@ extern "C" int b200_fused_decode_attention(const void* q, int64_t q_stride_b, in
   return fused_decode_impl(q, q_stride_b, q_stride_h, k_new, kn_stride_b, kn_stride_h, v_new, vn_stride_b, vn_stride_h,
                            gate, gate_stride_b, k_cache, v_cache, kc_stride_p, kc_stride_h, kc_stride_s, vc_stride_p,
                            vc_stride_h, vc_stride_s, num_pages, block_table, bt_stride_b, pos, inv_freq, rotary_dim, out,
-                           workspace, batch, num_q_heads, num_kv_heads, head_dim, nullptr, nullptr, 0.f, 0, stream);
+                           workspace, batch, num_q_heads, num_kv_heads, head_dim, nullptr, nullptr, 0.f, 0, 0, stream);
 }
 
 extern "C" int b200_fused_decode_attention_ex(
@@ -679,12 +697,12 @@ extern "C" int b200_fused_decode_attention_ex(
     int64_t vc_stride_h, int64_t vc_stride_s, int64_t num_pages, const int32_t* block_table, int64_t bt_stride_b,
     const int64_t* pos, const float* inv_freq, int32_t rotary_dim, void* out, void* workspace, int32_t batch,
     int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, const void* q_norm_weight, const void* k_norm_weight,
-    float eps, int32_t overlap, b200_stream_t stream) {
+    float eps, int32_t overlap, int32_t partition, b200_stream_t stream) {
   return fused_decode_impl(q, q_stride_b, q_stride_h, k_new, kn_stride_b, kn_stride_h, v_new, vn_stride_b, vn_stride_h,
                            gate, gate_stride_b, k_cache, v_cache, kc_stride_p, kc_stride_h, kc_stride_s, vc_stride_p,
                            vc_stride_h, vc_stride_s, num_pages, block_table, bt_stride_b, pos, inv_freq, rotary_dim, out,
                            workspace, batch, num_q_heads, num_kv_heads, head_dim, q_norm_weight, k_norm_weight, eps,
-                           overlap, stream);
+                           overlap, partition, stream);
 }
 
 // Same computation and arguments as b200_fused_decode_attention, minus the workspace.

@@ -230,7 +230,8 @@ gdn_decode_stream_kernel(const __grid_constant__ GdnStreamParams p) {
   };
   if (my_items > 0) fetch(0);
   bool ok = true;
-  for (int n = 0; n < my_items; ++n) {
+  int n_done = 0;  // items whose state was loaded, updated and handed to the store engine
+  for (int n = 0; n < my_items && ok; ++n) {
     const int item = blockIdx.x + n * gridDim.x, b = item / p.heads, h = item % p.heads;
     float* buf = bufs + (n % GS_STAGES) * (GDN_D * GDN_D);
     const float eg = __expf(gn), bt = bn, vv = vn;
@@ -238,8 +239,9 @@ gdn_decode_stream_kernel(const __grid_constant__ GdnStreamParams p) {
     kf[t] = kn;
     qf[t] = qn;
     if (n + 1 < my_items) fetch(n + 1);
-    if (ok) ok = mbar_wait_bounded(&full[n % GS_STAGES], (n / GS_STAGES) & 1);
-    __syncthreads();  // kf / qf visible
+    const bool mine = mbar_wait_bounded(&full[n % GS_STAGES], (n / GS_STAGES) & 1);
+    ok = __syncthreads_and(mine);  // kf / qf visible; the CTA agrees on whether the state arrived
+    if (!ok) break;                // a lost copy: this item's state and output stay untouched
     float s[GDN_D];
 #pragma unroll
     for (int i = 0; i < GDN_D; ++i) s[i] = buf[i * GDN_D + t];
@@ -258,10 +260,17 @@ gdn_decode_stream_kernel(const __grid_constant__ GdnStreamParams p) {
       }
       bulk_s2g(state_of(n), buf, GS_STATE_BYTES);
     }
+    n_done = n + 1;
   }
   if (t == 0) {
     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all stores complete before the CTA ends
-    if (!ok) atomicExch(p.err, 1);
+    if (!ok) {
+      atomicExch(p.err, 1);
+      // the loads of items n_done and n_done + 1 may still be in flight into this CTA's shared memory: give them a
+      // bounded time to land before the CTA (and its shared memory) goes away
+      for (int m = n_done; m < min(n_done + 2, my_items); ++m)
+        mbar_wait_bounded(&full[m % GS_STAGES], (m / GS_STAGES) & 1, 1u << 12);
+    }
   }
 }
 

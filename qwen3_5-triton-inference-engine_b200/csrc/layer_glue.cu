@@ -69,8 +69,8 @@ add_rmsnorm_kernel(const __nv_bfloat16* x, int64_t x_outer, int64_t x_inner, int
 
 // ------------------------------------------------------------------------------------------------------- SwiGLU
 __global__ void __launch_bounds__(256)
-swiglu_kernel(const __nv_bfloat16* gate_up, int64_t row_stride, __nv_bfloat16* __restrict__ out, int rows,
-              int inter, int overlap) {
+swiglu_kernel(const __nv_bfloat16* gate, int64_t gate_stride, const __nv_bfloat16* up, int64_t up_stride,
+              __nv_bfloat16* __restrict__ out, int rows, int inter, int overlap) {
   const int vec_per_row = inter >> 3;
   const int64_t total = static_cast<int64_t>(rows) * vec_per_row;
   if (overlap & OVERLAP_TRIGGER) pdl_trigger();
@@ -79,8 +79,8 @@ swiglu_kernel(const __nv_bfloat16* gate_up, int64_t row_stride, __nv_bfloat16* _
     const int64_t r = idx / vec_per_row;
     const int c = static_cast<int>(idx % vec_per_row) * 8;
     float g[8], u[8], o[8];
-    unpack8(*reinterpret_cast<const uint4*>(gate_up + r * row_stride + c), g);
-    unpack8(*reinterpret_cast<const uint4*>(gate_up + r * row_stride + inter + c), u);
+    unpack8(*reinterpret_cast<const uint4*>(gate + r * gate_stride + c), g);
+    unpack8(*reinterpret_cast<const uint4*>(up + r * up_stride + c), u);
 #pragma unroll
     for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.0f + expf(-g[j])) * u[j];
     *reinterpret_cast<uint4*>(out + r * inter + c) = pack8(o);
@@ -244,10 +244,27 @@ extern "C" int b200_swiglu(const void* gate_up, int64_t row_stride, void* out, i
   const int cap = sm_count() * 8;
   if (blocks > cap) blocks = cap;
   if (launch_pdl((overlap & OVERLAP_START) != 0, swiglu_kernel, dim3(blocks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
-                 static_cast<const __nv_bfloat16*>(gate_up), row_stride, static_cast<__nv_bfloat16*>(out), rows,
-                 intermediate, overlap) != cudaSuccess)
+                 static_cast<const __nv_bfloat16*>(gate_up), row_stride,
+                 static_cast<const __nv_bfloat16*>(gate_up) + intermediate, row_stride, static_cast<__nv_bfloat16*>(out),
+                 rows, intermediate, overlap) != cudaSuccess)
     return fail(ERR_LAUNCH, "swiglu: %s", cudaGetErrorString(cudaGetLastError()));
   return check_launch("swiglu");
+}
+
+extern "C" int b200_swiglu_pair(const void* gate, int64_t gate_stride, const void* up, int64_t up_stride, void* out,
+                                int32_t rows, int32_t width, b200_stream_t stream) {
+  B200_REQUIRE(rows > 0 && width > 0 && width % 8 == 0 && gate_stride % 8 == 0 && up_stride % 8 == 0 && aligned16(gate) &&
+                   aligned16(up) && aligned16(out),
+               "swiglu_pair: the width and the row strides must be multiples of 8, pointers 16-byte aligned");
+  const int64_t vecs = static_cast<int64_t>(rows) * (width / 8);
+  int blocks = static_cast<int>((vecs + 255) / 256);
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  if (launch_pdl(false, swiglu_kernel, dim3(blocks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+                 static_cast<const __nv_bfloat16*>(gate), gate_stride, static_cast<const __nv_bfloat16*>(up), up_stride,
+                 static_cast<__nv_bfloat16*>(out), rows, width, 0) != cudaSuccess)
+    return fail(ERR_LAUNCH, "swiglu_pair: %s", cudaGetErrorString(cudaGetLastError()));
+  return check_launch("swiglu_pair");
 }
 
 extern "C" int b200_gdn_decode_prep(const void* qkv, int64_t qkv_stride, void* conv_state, const void* weight4,

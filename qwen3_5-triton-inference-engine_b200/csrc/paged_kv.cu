@@ -6,7 +6,7 @@
 
 namespace b200 {
 
-static char g_error[512] = "";
+static thread_local char g_error[512] = "";  // per host thread: a caller reads the text of its own failed call
 void set_error(const char* fmt, ...) {
   va_list ap;
   va_start(ap, fmt);

@@ -18,6 +18,8 @@
 #include "b200_attn.h"
 #include "umma.cuh"
 
+#include <mutex>
+
 namespace b200 {
 
 constexpr int SG_WARPS = 4;
@@ -571,7 +573,10 @@ skinny_gemm_pairk_kernel(const __grid_constant__ WideKParams p, const __grid_con
   }
 }
 
-static const CUtensorMap* cache_weight_map(const void* base, int64_t n, int64_t k, int box_rows) {
+// Shared by all host threads: searched and filled under a mutex, the map is copied out.
+static bool cache_weight_map(const void* base, int64_t n, int64_t k, int box_rows, CUtensorMap* out) {
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
   struct Entry {
     const void* base;
     int64_t n, k;
@@ -585,11 +590,14 @@ static const CUtensorMap* cache_weight_map(const void* base, int64_t n, int64_t 
   cudaGetDevice(&dev);
   for (int i = 0; i < used; ++i)
     if (entries[i].base == base && entries[i].n == n && entries[i].k == k && entries[i].dev == dev &&
-        entries[i].box_rows == box_rows)
-      return &entries[i].map;
+        entries[i].box_rows == box_rows) {
+      *out = entries[i].map;
+      return true;
+    }
   Entry& e = entries[next];
+  e.base = nullptr;  // not a valid entry while it is being rewritten
   if (!encode_tile_map(&e.map, base, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(k) * 2, box_rows, 2))
-    return nullptr;
+    return false;
   e.base = base;
   e.n = n;
   e.k = k;
@@ -597,7 +605,8 @@ static const CUtensorMap* cache_weight_map(const void* base, int64_t n, int64_t 
   e.box_rows = box_rows;
   next = (next + 1) % N;
   if (used < N) ++used;
-  return &e.map;
+  *out = e.map;
+  return true;
 }
 
 }  // namespace b200
@@ -606,8 +615,8 @@ using namespace b200;
 
 template <bool SWIGLU, bool ARGMAX = false>
 static int launch_skinny(SkinnyGemmParams p, const void* weight, int w_rows, cudaStream_t stream, const char* what) {
-  const CUtensorMap* map = cache_weight_map(weight, w_rows, p.k, SWIGLU ? 8 : 16);
-  if (!map) return fail(ERR_RUNTIME, "%s: cannot encode the weight tensor map", what);
+  CUtensorMap map;
+  if (!cache_weight_map(weight, w_rows, p.k, SWIGLU ? 8 : 16, &map)) return fail(ERR_RUNTIME, "%s: cannot encode the weight tensor map", what);
   constexpr int smem_max =
       SG_WARPS * SG_RING_BYTES + SG_MAX_M * SG_ROWS * 2 + SG_PART_BYTES + SG_MAX_M * (SG_MAX_K * 2 + 16) + 1024;
   static_assert(smem_max <= 227 * 1024, "weight rings + X staging must fit the 227 KiB a CTA may use");
@@ -629,7 +638,7 @@ static int launch_skinny(SkinnyGemmParams p, const void* weight, int w_rows, cud
   if (grid > sms) grid = sms;
   const int dyn = SG_WARPS * SG_RING_BYTES + SG_MAX_M * SG_ROWS * 2 + SG_PART_BYTES + SG_MAX_M * (p.k * 2 + 16) + 1024;
   if (launch_pdl((p.overlap & OVERLAP_START) != 0, skinny_gemm_kernel<SWIGLU, ARGMAX>, dim3(grid), dim3(SG_STD_THREADS), dyn, stream,
-                 p, *map) != cudaSuccess)
+                 p, map) != cudaSuccess)
     return fail(ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(cudaGetLastError()));
   return check_launch(what);
 }
@@ -646,8 +655,8 @@ static bool widek_chunks(int k, int* chunk_k, int* n_chunks) {
 
 static int launch_widek(WideKParams p, const void* weight, cudaStream_t stream) {
   const char* what = "skinny_gemm";
-  const CUtensorMap* map = cache_weight_map(weight, p.n, p.k, 16);
-  if (!map) return fail(ERR_RUNTIME, "%s: cannot encode the weight tensor map", what);
+  CUtensorMap map;
+  if (!cache_weight_map(weight, p.n, p.k, 16, &map)) return fail(ERR_RUNTIME, "%s: cannot encode the weight tensor map", what);
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -665,15 +674,15 @@ static int launch_widek(WideKParams p, const void* weight, cudaStream_t stream) 
   const int dyn = SG_WARPS * WK_RING * SG_TILE_BYTES + SG_WARPS * WK_ROWS * SG_MAX_M * 4 +
                   2 * SG_MAX_M * (p.chunk_k * 2 + 16) + 1024;
   if (launch_pdl((p.overlap & OVERLAP_START) != 0, skinny_gemm_widek_kernel, dim3(grid), dim3(SG_THREADS), dyn, stream, p,
-                 *map) != cudaSuccess)
+                 map) != cudaSuccess)
     return fail(ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(cudaGetLastError()));
   return check_launch(what);
 }
 
 static int launch_pairk(WideKParams p, const void* weight, cudaStream_t stream) {
   const char* what = "skinny_gemm";
-  const CUtensorMap* map = cache_weight_map(weight, p.n, p.k, 16);
-  if (!map) return fail(ERR_RUNTIME, "%s: cannot encode the weight tensor map", what);
+  CUtensorMap map;
+  if (!cache_weight_map(weight, p.n, p.k, 16, &map)) return fail(ERR_RUNTIME, "%s: cannot encode the weight tensor map", what);
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -691,7 +700,7 @@ static int launch_pairk(WideKParams p, const void* weight, cudaStream_t stream) 
   const int dyn = SG_WARPS * PK_RING * SG_TILE_BYTES + (SG_WARPS + 1) * WK_ROWS * SG_MAX_M * 4 +
                   SG_MAX_M * (p.k + 16) + 1024;
   if (launch_pdl_cluster((p.overlap & OVERLAP_START) != 0, 2, skinny_gemm_pairk_kernel, dim3(2 * pairs), dim3(SG_THREADS),
-                         dyn, stream, p, *map) != cudaSuccess)
+                         dyn, stream, p, map) != cudaSuccess)
     return fail(ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(cudaGetLastError()));
   return check_launch(what);
 }

@@ -151,9 +151,36 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   if (warp == 0) tmem_dealloc(tmem, TMEM_COLS);
 }
 
+// The give-up path of every staged copy in this library, exercised on purpose: an mbarrier is armed for bytes that no
+// copy will ever deliver, one warp waits for it with a small poll limit, the wait returns false, the kernel records that
+// in the error word, leaves `sentinel` untouched (what a real kernel does with its outputs on this path) and returns.
+// Nothing is in flight when it ends; the context stays usable.
+__global__ void wait_timeout_selftest_kernel(int* err, int* sentinel, uint32_t polls) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    mbar_expect_tx(&bar, 16);  // the one arrival is made, the 16 bytes never come
+  }
+  __syncwarp();
+  const bool ok = mbar_wait_bounded(&bar, 0, polls);
+  if (threadIdx.x == 0) {
+    if (ok) *sentinel = 1;  // would mean the wait did NOT run out
+    else atomicExch(err, 1);
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_selftest_wait_timeout(int32_t* sentinel, b200_stream_t stream) {
+  int* err = wait_timeout_flag();
+  if (!err) return fail(ERR_RUNTIME, "selftest_wait_timeout: no error flag");
+  B200_REQUIRE(sentinel != nullptr, "selftest_wait_timeout: sentinel is NULL");
+  wait_timeout_selftest_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(err, sentinel, 1u << 10);
+  return check_launch("selftest_wait_timeout");
+}
 
 extern "C" int b200_selftest_umma(int32_t mode, const void* a, const void* b, float* c, b200_stream_t stream) {
   B200_REQUIRE(mode >= 0 && mode <= 2, "selftest_umma: mode must be 0, 1 or 2");

@@ -1,3 +1,12 @@
-"""Same module and symbol names as the reference's triton_kernels/depthwise_causal_conv4_decode.py; the operators here are the plain
-PyTorch restatements of b200attn/glue.py (these operators are outside the attention / Gated-DeltaNet path)."""
-from b200attn.glue import depthwise_causal_conv4_decode, conv_state_from_packed_prefill  # noqa: F401
+"""Same public names as the reference's triton_kernels/depthwise_causal_conv4_decode.py, served by the CUDA operators of b200attn (b200attn/glue_ops.py)."""
+from b200attn.glue_ops import (  # noqa: F401
+    CONV_KERNEL_SIZE,
+    conv_state_from_packed_prefill,
+    conv_state_from_prefill,
+    conv_weight_for_decode,
+    depthwise_causal_conv4_decode,
+)
+
+
+def call_depthwise_causal_conv4_decode_triton(x, state, weight):
+    return depthwise_causal_conv4_decode(x, state, weight)

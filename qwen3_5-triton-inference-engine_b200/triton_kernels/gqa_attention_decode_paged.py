@@ -14,3 +14,5 @@ from b200attn.ops import (  # noqa: F401
     paged_kv_fill_varlen,
     physical_rows,
 )
+
+PAGE = PAGE_SIZE

@@ -1,3 +1,6 @@
-"""Same module and symbol names as the reference's triton_kernels/residual_add.py; the operators here are the plain
-PyTorch restatements of b200attn/glue.py (these operators are outside the attention / Gated-DeltaNet path)."""
-from b200attn.glue import residual_add  # noqa: F401
+"""Same public names as the reference's triton_kernels/residual_add.py, served by the CUDA operators of b200attn (b200attn/glue_ops.py)."""
+from b200attn.glue_ops import residual_add  # noqa: F401
+
+
+def call_residual_add_triton(x, residual):
+    return residual_add(x, residual)

@@ -1,3 +1,6 @@
-"""Same module and symbol names as the reference's triton_kernels/vocab_argmax.py; the operators here are the plain
-PyTorch restatements of b200attn/glue.py (these operators are outside the attention / Gated-DeltaNet path)."""
-from b200attn.glue import lm_head_argmax  # noqa: F401
+"""Same public names as the reference's triton_kernels/vocab_argmax.py, served by the CUDA operators of b200attn (b200attn/glue_ops.py)."""
+from b200attn.glue_ops import lm_head_argmax  # noqa: F401
+
+
+def call_lm_head_argmax_triton(hidden, weight, last_only=True):
+    return lm_head_argmax(hidden, weight, last_only)

@@ -24,6 +24,19 @@ REFERENCE_SCHEMAS = {
     "gdn_chunk_prepare_wy": "wy_lib::gdn_chunk_prepare_wy(Tensor k, Tensor v, Tensor beta, Tensor g) -> (Tensor, Tensor, Tensor)",
     "gdn_chunk_state": "wy_lib::gdn_chunk_state(Tensor k, Tensor w, Tensor u_base, Tensor g_cumsum) -> (Tensor, Tensor, Tensor)",
     "gdn_chunk_output": "wy_lib::gdn_chunk_output(Tensor q, Tensor k, Tensor delta, Tensor g_cumsum, Tensor chunk_state) -> Tensor",
+    # the operators around the path (b200attn/glue_ops.py)
+    "conv_state_from_packed_prefill": "wy_lib::conv_state_from_packed_prefill(Tensor(a0!) state, Tensor x, Tensor cu_seqlens) -> ()",
+    "depthwise_causal_conv4_decode": "wy_lib::depthwise_causal_conv4_decode(Tensor x, Tensor(a1!) state, Tensor weight) -> Tensor",
+    "depthwise_causal_conv4_prefill": "wy_lib::depthwise_causal_conv4_prefill(Tensor x, Tensor weight, Tensor? seq_start=None) -> Tensor",
+    "embedding_gather": "wy_lib::embedding_gather(Tensor input_ids, Tensor weight) -> Tensor",
+    "gdn_gated_rmsnorm": "wy_lib::gdn_gated_rmsnorm(Tensor x, Tensor z, Tensor weight) -> Tensor",
+    "gdn_qk_norm_gates": "wy_lib::gdn_qk_norm_gates(Tensor q, Tensor k, Tensor a, Tensor b, Tensor a_log, Tensor dt_bias) -> (Tensor, Tensor, Tensor, Tensor)",
+    "gemm_2d": "wy_lib::gemm_2d(Tensor x, Tensor weight) -> Tensor",
+    "gqa_attention_without_kvcache_casual": "wy_lib::gqa_attention_without_kvcache_casual(Tensor q, Tensor k, Tensor v) -> Tensor",
+    "lm_head_argmax": "wy_lib::lm_head_argmax(Tensor hidden, Tensor weight, bool last_only=True) -> Tensor",
+    "qwen_rmsnorm": "wy_lib::qwen_rmsnorm(Tensor x, Tensor weight, float eps=9.9999999999999995e-07) -> Tensor",
+    "residual_add": "wy_lib::residual_add(Tensor x, Tensor residual) -> Tensor",
+    "swiglu": "wy_lib::swiglu(Tensor gate, Tensor up) -> Tensor",
 }
 
 
@@ -47,7 +60,7 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_operator_schemas_match_reference():
-    from b200attn import ops  # noqa: F401  (registers the operators)
+    from b200attn import glue_ops, ops  # noqa: F401  (importing registers the operators)
 
     for name, schema in REFERENCE_SCHEMAS.items():
         if not hasattr(torch.ops.wy_lib, name):
