@@ -16,11 +16,12 @@ import torch.nn.functional as F
 from .reference_ops import gdn_step
 
 
-def widen(weights: dict) -> dict:
-    """The engine's weight dictionary on the CPU in fp32."""
+def widen(weights: dict, device="cpu") -> dict:
+    """The engine's weight dictionary in fp32, on the CPU by default (`device` lets a GPU test run the same eager fp32
+    arithmetic on the device when the model is too large for the host to finish in seconds)."""
     def conv(v):
         if isinstance(v, torch.Tensor):
-            return v.detach().float().cpu()
+            return v.detach().float().to(device)
         if isinstance(v, list):
             return [conv(x) for x in v]
         if isinstance(v, dict):
@@ -50,8 +51,8 @@ def _gdn_layer(cfg, layer, h):
     k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)
     beta = torch.sigmoid(b)
     g = -torch.exp(layer["a_log"]).unsqueeze(0) * F.softplus(a + layer["dt_bias"].unsqueeze(0))
-    state = torch.zeros(heads, dim, dim)
-    core = torch.empty(total, heads, dim)
+    state = torch.zeros(heads, dim, dim, device=h.device)
+    core = torch.empty(total, heads, dim, device=h.device)
     for t in range(total):
         state, core[t] = gdn_step(state, q[t], k[t], v[t], beta[t], g[t])
     normed = core * torch.rsqrt(core.pow(2).mean(-1, keepdim=True) + 1e-6) * layer["norm"] * \
@@ -69,8 +70,8 @@ def _attention_layer(cfg, layer, h):
     k = _rms(fused[:, 2 * qd: 2 * qd + kvd].view(total, nkv, d), layer["k_norm"], cfg.eps)
     v = fused[:, 2 * qd + kvd:].view(total, nkv, d)
     half = cfg.rotary_dim // 2
-    inv_freq = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.rotary_dim, 2, dtype=torch.float32) / cfg.rotary_dim))
-    ang = torch.arange(total, dtype=torch.float32).unsqueeze(1) * inv_freq.unsqueeze(0)   # partial_rope.py:56-132
+    inv_freq = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.rotary_dim, 2, dtype=torch.float32, device=h.device) / cfg.rotary_dim))
+    ang = torch.arange(total, dtype=torch.float32, device=h.device).unsqueeze(1) * inv_freq.unsqueeze(0)   # partial_rope.py:56-132
     cos, sin = torch.cos(ang).unsqueeze(1), torch.sin(ang).unsqueeze(1)
 
     def rope(x):
@@ -81,15 +82,29 @@ def _attention_layer(cfg, layer, h):
     k = k.repeat_interleave(nq // nkv, dim=1)
     v = v.repeat_interleave(nq // nkv, dim=1)
     scores = torch.einsum("thd,shd->hts", q, k) * d ** -0.5
-    mask = torch.ones(total, total, dtype=torch.bool).tril()
+    mask = torch.ones(total, total, dtype=torch.bool, device=h.device).tril()
     probs = torch.softmax(scores.masked_fill(~mask, float("-inf")), dim=-1)
     ctx = torch.einsum("hts,shd->thd", probs, v).reshape(total, qd)
     return (ctx * torch.sigmoid(gate)) @ layer["o_proj"].t()                         # attention_gate_pack.py:46-64
 
 
+def all_hidden(cfg, w32: dict, tokens: list[int]) -> torch.Tensor:
+    """Final-norm hidden state [T, hidden] at EVERY position of one sequence (the model is causal: row t depends on
+    tokens[:t+1] only), i.e. what the runner feeds its LM head after consuming token t."""
+    x = w32["embed"][torch.tensor(tokens, dtype=torch.long, device=w32["embed"].device)]
+    for layer in w32["layers"]:
+        h = _rms(x, layer["ln1"], cfg.eps)
+        mixed = _gdn_layer(cfg, layer, h) if layer["kind"] == "gdn" else _attention_layer(cfg, layer, h)
+        x = x + mixed
+        h = _rms(x, layer["ln2"], cfg.eps)
+        gate_up = h @ layer["gate_up"].t()
+        x = x + (F.silu(gate_up[:, : cfg.intermediate]) * gate_up[:, cfg.intermediate:]) @ layer["down"].t()
+    return _rms(x, w32["norm"], cfg.eps)
+
+
 def last_token_logits(cfg, w32: dict, tokens: list[int]) -> torch.Tensor:
     """Logits [vocab] for the token that follows `tokens` (full recomputation)."""
-    x = w32["embed"][torch.tensor(tokens, dtype=torch.long)]
+    x = w32["embed"][torch.tensor(tokens, dtype=torch.long, device=w32["embed"].device)]
     for layer in w32["layers"]:
         h = _rms(x, layer["ln1"], cfg.eps)
         mixed = _gdn_layer(cfg, layer, h) if layer["kind"] == "gdn" else _attention_layer(cfg, layer, h)

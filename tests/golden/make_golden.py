@@ -36,61 +36,14 @@ HERE = Path(__file__).resolve().parent
 
 
 # --------------------------------------------------------------------------- shims
-def install_shims() -> None:
-    import triton
-    import triton.language as tl
-    from triton.runtime import interpreter as interp
-    from triton.runtime.autotuner import Autotuner
-
-    def create_dot(self, a, b, d, input_precision, max_num_imprecise_acc):
-        def widen(h):
-            data = h.data
-            if h.dtype.scalar == tl.bfloat16 or data.dtype == np.uint16:
-                data = (data.astype(np.uint32) << 16).view(np.float32)
-            return data
-
-        out = np.matmul(widen(a), widen(b), dtype=d.data.dtype) + d.data
-        return interp.TensorHandle(out, d.dtype.scalar)
-
-    interp.InterpreterBuilder.create_dot = create_dot
-
-    original_cast = interp.InterpreterBuilder.cast_impl
-
-    def cast_impl(self, src, dst_type):
-        if src.dtype.scalar == tl.float32 and dst_type.scalar == tl.bfloat16:
-            bits = np.ascontiguousarray(src.data).view(np.uint32).astype(np.uint64)
-            rounded = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16).astype(np.uint16)
-            return interp.TensorHandle(rounded, dst_type.scalar)
-        return original_cast(self, src, dst_type)
-
-    interp.InterpreterBuilder.cast_impl = cast_impl
-
-    original_wrap = torch.library.wrap_triton
-
-    def wrap_triton(fn):
-        if isinstance(fn, interp.InterpretedFunction):
-            return fn
-        return original_wrap(fn)
-
-    torch.library.wrap_triton = wrap_triton
-
-    def pin_autotuners():
-        import importlib
-        import pkgutil
-
-        import triton_kernels
-
-        pinned = 0
-        for info in pkgutil.iter_modules(triton_kernels.__path__):
-            mod = importlib.import_module(f"triton_kernels.{info.name}")
-            for name in dir(mod):
-                obj = getattr(mod, name)
-                if isinstance(obj, Autotuner) and len(obj.configs) > 1:
-                    obj.configs = [obj.configs[0]]
-                    pinned += 1
-        return pinned
-
-    return pin_autotuners
+def install_shims():
+    """The four interpreter shims live in baseline/interpreter_shims.py (shared with the CPU-baseline harness)."""
+    import importlib.util
+    path = HERE.parent.parent / "baseline" / "interpreter_shims.py"
+    spec = importlib.util.spec_from_file_location("interpreter_shims", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.install_shims()
 
 
 # --------------------------------------------------------------------------- inputs
@@ -299,6 +252,177 @@ def case_gdn_chunked():
                 seq_out=seq_out, seq_state=seq_state)
 
 
+def case_glue_conv4():
+    """Depthwise conv4: packed prefill with seq_start, single-token decode with a non-zero state, conv-state extraction."""
+    from triton_kernels import depthwise_causal_conv4_decode as dec
+    from triton_kernels import depthwise_causal_conv4_prefill as pre
+
+    gen = torch.Generator().manual_seed(21)
+    chans = 6144
+    lengths = [3, 6, 2]
+    total = sum(lengths)
+    x = bf16_randn(total, chans, gen=gen)
+    w = (torch.randn(chans, 4, generator=gen) * 0.5).to(torch.bfloat16)
+    seq_start = pre.build_seq_start(lengths, device="cpu")
+    cu = torch.tensor([0] + list(np.cumsum(lengths)), dtype=torch.int32)
+    out = {"lengths": torch.tensor(lengths), "x": x, "weight": w, "seq_start": seq_start, "cu_seqlens": cu,
+           "prefill_packed": pre.depthwise_causal_conv4_prefill(x, w, seq_start),
+           "prefill_single": pre.depthwise_causal_conv4_prefill(x[:3], w)}
+    state = bf16_randn(len(lengths), 4, chans, gen=gen)      # non-zero on purpose: every slot must be overwritten
+    out["state_garbage"] = state.clone()
+    dec.conv_state_from_packed_prefill(state, x, cu)
+    out["state_from_packed"] = state.clone()
+    out["state_from_prefill_short"] = dec.conv_state_from_prefill(x[:3])
+    # decode: x is a column slice of a wider projection row, as in the runner
+    batch = 3
+    fused = bf16_randn(batch, 8224, gen=gen)
+    w4 = dec.conv_weight_for_decode(w)
+    st = bf16_randn(batch, 4, chans, gen=gen)
+    out.update({"decode_fused_row": fused, "decode_state_in": st.clone(), "weight4": w4})
+    out["decode_out"] = dec.depthwise_causal_conv4_decode(fused[:, :chans], st, w4)
+    out["decode_state_out"] = st
+    return out
+
+
+def case_glue_norms():
+    """RMSNorm (flat rows and a [B,H,D] column view), q/k L2 norms + gates, gated RMSNorm, SwiGLU, gather."""
+    from triton_kernels import embedding_gather as eg
+    from triton_kernels import gdn_gated_rmsnorm as gn
+    from triton_kernels import gdn_qk_norm_gates as qk
+    from triton_kernels import qwen_rmsnorm as rn
+    from triton_kernels import swiglu as sw
+
+    gen = torch.Generator().manual_seed(22)
+    out = {}
+    x2 = bf16_randn(5, 1024, gen=gen)
+    w1024 = (torch.randn(1024, generator=gen) * 0.1).to(torch.bfloat16)
+    out.update({"rms.x2": x2, "rms.w1024": w1024, "rms.out2": rn.qwen_rmsnorm(x2, w1024, 1e-6)})
+    fused = bf16_randn(3, 5120, gen=gen)
+    w256 = (torch.randn(256, generator=gen) * 0.1).to(torch.bfloat16)
+    out.update({"rms.fused": fused, "rms.w256": w256,
+                "rms.out3": rn.qwen_rmsnorm(fused[:, :2048].view(3, 8, 256), w256, 1e-6)})
+    # q/k norms + gates on strided views of a conv output, a/b as column slices
+    t, h, d = 5, 16, 128
+    conv = bf16_randn(t, 3 * h * d, gen=gen)
+    ab = bf16_randn(t, 2 * h, gen=gen)
+    a_log = torch.rand(h, generator=gen) * 2.7
+    dt_bias = bf16_randn(h, gen=gen)
+    q = conv[:, : h * d].view(t, h, d)
+    k = conv[:, h * d: 2 * h * d].view(t, h, d)
+    q_n, k_n, beta, g = qk.gdn_qk_norm_gates(q, k, ab[:, :h], ab[:, h:], a_log, dt_bias)
+    out.update({"qk.conv": conv, "qk.ab": ab, "qk.a_log": a_log, "qk.dt_bias": dt_bias, "qk.q_n": q_n, "qk.k_n": k_n,
+                "qk.beta": beta, "qk.g": g})
+    core = bf16_randn(t, h, d, gen=gen)
+    z = bf16_randn(t, h * d + 64, gen=gen)
+    wn = 1.0 + torch.randn(d, generator=gen) * 0.1
+    out.update({"gn.x": core, "gn.z_rows": z, "gn.weight": wn,
+                "gn.out": gn.gdn_gated_rmsnorm(core, z[:, : h * d].view(t, h, d), wn)})
+    inter = 3584
+    gate_up = bf16_randn(3, 2 * inter, gen=gen)
+    out.update({"swiglu.gate_up": gate_up, "swiglu.out": sw.swiglu(gate_up[:, :inter], gate_up[:, inter:])})
+    table = bf16_randn(50, 1024, gen=gen)
+    ids = torch.tensor([7, 0, 49, 7, 13], dtype=torch.int32)
+    out.update({"gather.table": table, "gather.ids": ids, "gather.out": eg.embedding_gather(ids, table)})
+    return out
+
+
+def case_glue_matmul():
+    """Projection GEMM and the fused LM-head arg-max (with a tie: two identical vocabulary rows)."""
+    from triton_kernels import gemm_2d as gm
+    from triton_kernels import vocab_argmax as va
+
+    gen = torch.Generator().manual_seed(23)
+    out = {}
+    w = (torch.randn(384, 256, generator=gen) * 0.05).to(torch.bfloat16)
+    for m in (1, 5):
+        x = bf16_randn(m, 256, gen=gen)
+        y = gm.gemm_2d(x, w)
+        assert (y.float() - x.float() @ w.float().t()).abs().max() < 0.05
+        out.update({f"gemm.x{m}": x, f"gemm.y{m}": y})
+    out["gemm.w"] = w
+    vocab, hidden = 2048, 256
+    table = (torch.randn(vocab, hidden, generator=gen) * 0.05).to(torch.bfloat16)
+    rows = bf16_randn(3, hidden, gen=gen)
+    best = torch.argmax(rows.float() @ table.float().t(), dim=-1)
+    table[1900] = table[best[0]]          # a later duplicate of row 0's winner: the lower index must still win
+    table[3] = table[best[1]] if best[1] > 3 else table[3]
+    ids_all = va.lm_head_argmax(rows, table, last_only=False)
+    ids_last = va.lm_head_argmax(rows, table, last_only=True)
+    ref = torch.argmax(rows.float() @ table.float().t(), dim=-1)
+    assert torch.equal(ids_all, ref), (ids_all, ref)
+    out.update({"argmax.rows": rows, "argmax.table": table, "argmax.ids": ids_all, "argmax.last": ids_last})
+    return out
+
+
+def case_glue_gdn_decode_layer():
+    """The Gated-DeltaNet mixer of one decode token between its projections, as the reference runner chains it
+    (engine/runner.py:423-441): conv4 decode -> q/k norms + gates -> delta-rule step -> gated RMSNorm."""
+    from triton_kernels import depthwise_causal_conv4_decode as dec
+    from triton_kernels import gdn_gated_rmsnorm as gn
+    from triton_kernels import gdn_qk_norm_gates as qk
+    from triton_kernels import gdn_recurrent_prefill as rec
+
+    gen = torch.Generator().manual_seed(24)
+    batch, h, d = 3, 4, 128
+    kd = h * d
+    fused = bf16_randn(batch, 4 * kd + 2 * h, gen=gen)
+    conv_state = bf16_randn(batch, 4, 3 * kd, gen=gen)
+    w4 = (torch.randn(4, 3 * kd, generator=gen) * 0.5).to(torch.bfloat16)
+    a_log = torch.rand(h, generator=gen) * 2.7
+    dt_bias = bf16_randn(h, gen=gen)
+    norm_w = 1.0 + torch.randn(d, generator=gen) * 0.1
+    state = torch.randn(batch, h, d, d, generator=gen) * 0.1
+    cs, st = conv_state.clone(), state.clone()
+    conv = dec.depthwise_causal_conv4_decode(fused[:, : 3 * kd], cs, w4)
+    q = conv[:, :kd].view(batch, h, d)
+    k = conv[:, kd: 2 * kd].view(batch, h, d)
+    v = conv[:, 2 * kd:].view(batch, h, d)
+    q_n, k_n, beta, g = qk.gdn_qk_norm_gates(q, k, fused[:, 4 * kd: 4 * kd + h], fused[:, 4 * kd + h:], a_log, dt_bias)
+    core = rec.gdn_recurrent_decode(q_n, k_n, v, beta, g, st)
+    normed = gn.gdn_gated_rmsnorm(core, fused[:, 3 * kd: 4 * kd].view(batch, h, d), norm_w)
+    return dict(fused=fused, conv_state_in=conv_state, weight4=w4, a_log=a_log, dt_bias=dt_bias, norm_weight=norm_w,
+                state_in=state, conv=conv, q_n=q_n, k_n=k_n, beta=beta, g=g, core=core, conv_state_out=cs,
+                state_out=st, out=normed.view(batch, kd))
+
+
+def case_glue_attn_decode_layer():
+    """The attention mixer of one decode token between its projections, as the reference runner chains it
+    (engine/runner.py:464-517): q/k RMSNorm -> partial RoPE -> append + paged attention -> sigmoid gate."""
+    from triton_kernels import attention_gate_pack as gp
+    from triton_kernels import gqa_attention_decode_paged as pa
+    from triton_kernels import partial_rope as pr
+    from triton_kernels import qwen_rmsnorm as rn
+
+    gen = torch.Generator().manual_seed(25)
+    lens = [5, 37, 100]
+    batch, hq, hkv, d, r = len(lens), 8, 2, 256, 64
+    qd, kvd = hq * d, hkv * d
+    fused = bf16_randn(batch, 2 * qd + 2 * kvd, gen=gen)
+    q_w = (torch.randn(d, generator=gen) * 0.1).to(torch.bfloat16)
+    k_w = (torch.randn(d, generator=gen) * 0.1).to(torch.bfloat16)
+    inv_freq = (1.0 / (1e7 ** (torch.arange(0, r, 2, dtype=torch.float32) / r))).contiguous()
+    pps = (max(lens) + 1 + 15) // 16
+    num_pages = batch * pps + 3
+    block_table = shuffled_table(batch, pps, num_pages, gen)
+    k_cache = bf16_randn(num_pages, hkv, 16, d, gen=gen)
+    v_cache = bf16_randn(num_pages, hkv, 16, d, gen=gen)
+    pos = torch.tensor(lens, dtype=torch.int64)
+    kc, vc = k_cache.clone(), v_cache.clone()
+    q = rn.qwen_rmsnorm(fused[:, :qd].view(batch, hq, d), q_w, 1e-6)
+    k = rn.qwen_rmsnorm(fused[:, 2 * qd: 2 * qd + kvd].view(batch, hkv, d), k_w, 1e-6)
+    ids = pos.view(batch, 1)
+    q4 = pr.partial_rope(q.unsqueeze(2), ids, inv_freq, r)
+    k4 = pr.partial_rope(k.unsqueeze(2), ids, inv_freq, r)
+    v_new = fused[:, 2 * qd + kvd:].view(batch, hkv, d).contiguous()
+    ctx = pa.call_paged_gqa_attention_decode_triton(q4[:, :, 0, :].contiguous(), k4[:, :, 0, :].contiguous(), v_new, kc, vc,
+                                                    block_table, pos)
+    gate4 = fused[:, qd: 2 * qd].view(batch, hq, d).permute(1, 0, 2).unsqueeze(0).contiguous()
+    out = gp.attention_gate_pack(ctx.permute(1, 0, 2).unsqueeze(0).contiguous(), gate4)
+    return dict(fused=fused, q_norm_weight=q_w, k_norm_weight=k_w, inv_freq=inv_freq, block_table=block_table,
+                k_cache_in=k_cache, v_cache_in=v_cache, pos=pos, k_cache_out=kc, v_cache_out=vc, q_normed=q,
+                k_normed=k, ctx=ctx, out=out)
+
+
 CASES = {
     "paged_decode_cfg1": case_paged_decode_cfg1,
     "paged_fill_varlen": case_paged_fill_varlen,
@@ -308,6 +432,11 @@ CASES = {
     "gdn_decode": case_gdn_decode,
     "gdn_sequential": case_gdn_sequential,
     "gdn_chunked": case_gdn_chunked,
+    "glue_conv4": case_glue_conv4,
+    "glue_norms": case_glue_norms,
+    "glue_matmul": case_glue_matmul,
+    "glue_gdn_decode_layer": case_glue_gdn_decode_layer,
+    "glue_attn_decode_layer": case_glue_attn_decode_layer,
 }
 
 

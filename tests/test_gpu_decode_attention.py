@@ -177,14 +177,19 @@ def test_nan_in_unowned_slots_is_ignored(ops):
 # --------------------------------------------------------------------------- fused decode kernel
 @pytest.mark.parametrize("lengths", [[0], [1], [16], [37, 64, 100, 128], [0, 15, 16, 17, 31, 32, 33, 1000],
                                      [4096, 512, 33, 2049, 777, 1, 3000, 16], [32768], [600] * 64])
-def test_fused_decode_vs_oracle(ops, lengths):
+@pytest.mark.parametrize("partition", [0, 1, 2])
+def test_fused_decode_vs_oracle(ops, lengths, partition):
+    """partition pins how the kernel cuts the KV pages over its CTAs (1 = equal page ranges with cross-CTA merges,
+    2 = one whole segment per CTA, 0 = the kernel's own choice), so that both forms are checked on every length set."""
+    if partition == 2 and 2 * len(lengths) > torch.cuda.get_device_properties(0).multi_processor_count:
+        pytest.skip("whole segments need no more segments than SMs")
     c = make_paged_case(lengths, seed=300 + len(lengths) + lengths[0])
     inv = rope_inv_freq()
     d = to_dev(c)
     ws = ops.fused_decode_workspace(DEV)
     kc, vc = d["k_cache"].clone(), d["v_cache"].clone()
     out = ops.fused_decode_attention(d["q"], d["k_new"], d["v_new"], d["gate"], kc, vc, d["block_table"], d["pos"],
-                                     inv.to(DEV), 64, ws)
+                                     inv.to(DEV), 64, ws, partition=partition)
     torch.cuda.synchronize()
     no_timeouts()
     assert int(ws[:8192].view(torch.int32).abs().sum()) == 0, "segment counters must return to zero"
@@ -198,7 +203,7 @@ def test_fused_decode_vs_oracle(ops, lengths):
     assert maxabs(out, ref) < TOL
     # same call again on the updated cache and the same workspace: stale partials must not leak
     out2 = ops.fused_decode_attention(d["q"], d["k_new"], d["v_new"], d["gate"], kc, vc, d["block_table"], d["pos"],
-                                      inv.to(DEV), 64, ws)
+                                      inv.to(DEV), 64, ws, partition=partition)
     assert torch.equal(out2, out)
 
 
