@@ -10,12 +10,14 @@
 namespace b200 {
 
 constexpr int SPLIT_WARPS = 4;
-constexpr int SPLIT_TILES = 4;  // ring of K/V tiles per warp (two pages)
+constexpr int SPLIT_TILES = 2;  // K and V tile of one page per warp: 66 KiB per CTA, three CTAs (12 warps) per SM.  With the
+                                // reference's partition a warp owns one or two pages and writes a 4 KiB partial, so
+                                // the launch is bound by per-item latency: resident warps matter more than a deep ring
 constexpr int SPLIT_SMEM = SPLIT_WARPS * SPLIT_TILES * TILE_BYTES + 128;
 
 // One warp per (sequence, kv head, split).  grid.x = B * H_kv * 128 / SPLIT_WARPS: static in B, so the launch
 // is CUDA-graph safe; everything length-dependent comes from pos[] on the device.
-__global__ void __launch_bounds__(SPLIT_WARPS * 32)
+__global__ void __launch_bounds__(SPLIT_WARPS * 32, 3)
 paged_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_b, int64_t q_h,
                           const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
                           int64_t kc_p, int64_t kc_h, int64_t kc_s, int64_t vc_p, int64_t vc_h, int64_t vc_s,

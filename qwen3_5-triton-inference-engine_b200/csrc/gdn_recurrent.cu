@@ -82,6 +82,45 @@ gdn_decode_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_b, int64_t q_h,
   for (int i = 0; i < GDN_D; ++i) __stcs(sp + i * GDN_D, s[i]);
 }
 
+// The same step with a finer grain: CTA = ONE warp = 32 value columns of one (sequence, head).  Four times as many, four
+// times smaller work items than gdn_decode_kernel (eight resident per SM: the same two heads of state in registers,
+// but they retire and start a quarter head at a time), so the SMs stay evenly loaded and the last wave is a
+// quarter as long.  Used while the batch is too small to keep every SM busy for several rounds with whole heads.
+constexpr int GDN_SLICE = 32;
+
+__global__ void __launch_bounds__(GDN_SLICE, 8)
+gdn_decode_slice_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_b, int64_t q_h, const __nv_bfloat16* __restrict__ k,
+                        int64_t k_b, int64_t k_h, const __nv_bfloat16* __restrict__ v, int64_t v_b, int64_t v_h,
+                        const float* __restrict__ beta, int64_t be_b, int64_t be_h, const float* __restrict__ g,
+                        int64_t g_b, int64_t g_h, float* __restrict__ state, int64_t s_b, int64_t s_h,
+                        __nv_bfloat16* __restrict__ out, int64_t o_b, int64_t o_h, int heads) {
+  __shared__ __align__(16) float kf[GDN_D];
+  __shared__ __align__(16) float qf[GDN_D];
+  constexpr int SLICES = GDN_D / GDN_SLICE;
+  const int item = blockIdx.x / SLICES, slice = blockIdx.x % SLICES;
+  const int b = item / heads, h = item % heads, lane = threadIdx.x, col = slice * GDN_SLICE + lane;
+  float* sp = state + b * s_b + h * s_h + col;
+  // k and q of the head: 4 values per lane, widened into shared memory for the broadcast reads of the update
+  {
+    const uint2 kr = *reinterpret_cast<const uint2*>(k + b * k_b + h * k_h + lane * 4);
+    const uint2 qr = *reinterpret_cast<const uint2*>(q + b * q_b + h * q_h + lane * 4);
+    *reinterpret_cast<float4*>(kf + lane * 4) = make_float4(bf16_lo(kr.x), bf16_hi(kr.x), bf16_lo(kr.y), bf16_hi(kr.y));
+    *reinterpret_cast<float4*>(qf + lane * 4) = make_float4(bf16_lo(qr.x), bf16_hi(qr.x), bf16_lo(qr.y), bf16_hi(qr.y));
+  }
+  const float eg = __expf(g[b * g_b + h * g_h]);
+  const float bt = beta[b * be_b + h * be_h];
+  const float vv = __bfloat162float(v[b * v_b + h * v_h + col]);
+  float s[GDN_D];
+#pragma unroll
+  for (int i = 0; i < GDN_D; ++i) s[i] = __ldcs(sp + i * GDN_D);  // streamed once: evict-first
+  __syncwarp();
+  float o;
+  gdn_token_update(s, kf, qf, eg, bt, vv, o);
+  out[b * o_b + h * o_h + col] = __float2bfloat16_rn(o);
+#pragma unroll
+  for (int i = 0; i < GDN_D; ++i) __stcs(sp + i * GDN_D, s[i]);
+}
+
 // The whole Gated-DeltaNet mixer of one decode token between its two projections, in one launch per layer:
 // conv state shift + depthwise conv4 + SiLU (triton_kernels/depthwise_causal_conv4_decode.py), q/k L2 norms and the
 // beta / g gates (triton_kernels/gdn_qk_norm_gates.py:68-89), the delta-rule step above, and the gated RMSNorm
@@ -364,6 +403,19 @@ extern "C" int b200_gdn_recurrent_decode(const void* q, int64_t q_stride_b, int6
     p.heads = num_heads;
     int grid = p.items < sm_count() ? p.items : sm_count();
     gdn_decode_stream_kernel<<<grid, GDN_THREADS, GS_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+    return check_launch("gdn_recurrent_decode");
+  }
+  // Few items (less than about four rounds of whole heads per SM): the one-warp slices keep more state in flight per SM
+  // and shorten the last wave; q and k rows must then allow 8-byte loads.
+  const bool slices_ok = (reinterpret_cast<uintptr_t>(q) % 8 == 0) && (reinterpret_cast<uintptr_t>(k) % 8 == 0) &&
+                         q_stride_b % 4 == 0 && q_stride_h % 4 == 0 && k_stride_b % 4 == 0 && k_stride_h % 4 == 0;
+  if (slices_ok && batch * num_heads < 8 * sm_count()) {
+    gdn_decode_slice_kernel<<<static_cast<unsigned>(batch) * num_heads * (GDN_D / GDN_SLICE), GDN_SLICE, 0,
+                              reinterpret_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(q), q_stride_b, q_stride_h, static_cast<const __nv_bfloat16*>(k), k_stride_b,
+        k_stride_h, static_cast<const __nv_bfloat16*>(v), v_stride_b, v_stride_h, beta, beta_stride_b, beta_stride_h, g,
+        g_stride_b, g_stride_h, state, state_stride_b, state_stride_h, static_cast<__nv_bfloat16*>(out), out_stride_b,
+        out_stride_h, num_heads);
     return check_launch("gdn_recurrent_decode");
   }
   gdn_decode_kernel<<<static_cast<unsigned>(batch) * num_heads, GDN_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
