@@ -126,8 +126,9 @@ int b200_fused_decode_attention(const void* q, int64_t q_stride_b, int64_t q_str
  * partition: how the KV pages are cut over the CTAs.  0 = the kernel chooses per launch from the lengths in pos[];
  *   1 = always equal ranges of pages per CTA (segments cut at range boundaries are merged through the workspace);
  *   2 = always one whole (sequence, kv head) segment per CTA (needs batch * num_kv_heads <= the number of SMs, else the
- *   call is refused).  The result is the same up to fp32 summation order; 1 and 2 exist so that tests and tuning can
- *   pin either form. */
+ *   call is refused); 3 = always one segment per thread-block cluster, whose CTAs share the segment's pages and merge
+ *   through distributed shared memory (needs batch * num_kv_heads <= 64, else refused).  The result is the same up to
+ *   fp32 summation order; 1, 2 and 3 exist so that tests and tuning can pin each form. */
 int b200_fused_decode_attention_ex(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_new,
                                    int64_t kn_stride_b, int64_t kn_stride_h, const void* v_new, int64_t vn_stride_b,
                                    int64_t vn_stride_h, const void* gate, int64_t gate_stride_b, void* k_cache,

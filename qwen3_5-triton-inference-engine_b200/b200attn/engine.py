@@ -14,7 +14,20 @@ from dataclasses import dataclass
 
 import torch
 
-from . import glue, ops
+from . import glue, glue_ops, ops
+
+
+def _raw(op):
+    """The Python body of a registered torch operator: the engine calls its own operators directly, without the
+    dispatcher round trip (tens of microseconds per call) that an outside caller of `wy_lib::*` pays."""
+    return getattr(op, "_init_fn", op)
+
+
+_conv4_prefill = _raw(glue_ops.depthwise_causal_conv4_prefill)
+_qk_norm_gates = _raw(glue_ops.gdn_qk_norm_gates)
+_conv_state_pack = _raw(glue_ops.conv_state_from_packed_prefill)
+_embedding_gather = _raw(glue_ops.embedding_gather)
+_swiglu = _raw(glue_ops.swiglu)
 
 
 @dataclass(frozen=True)
@@ -158,6 +171,50 @@ class Engine:
         cu, max_len = ops.build_cu_seqlens(lengths, device=self.device)
         pos_in_seq = torch.cat([torch.arange(n) for n in lengths]).to(torch.int32).to(self.device)
         seq_start = torch.repeat_interleave(cu[:-1], torch.tensor(lengths, device=self.device))  # runner.py:136
+        total, heads, dim = ids.numel(), cfg.gdn_heads, cfg.gdn_dim
+        if not self.fused_glue:
+            return self._prefill_eager_glue(ids, cu, max_len, pos_in_seq, seq_start, lengths)
+        # every operator between the projections is one launch of this package (cuBLAS for the prompt-sized GEMMs)
+        x = _embedding_gather(ids, self.w["embed"])
+        pending = None                                   # MLP output still to be added to the residual stream
+        for i, layer in enumerate(self.w["layers"]):
+            self._cur = layer
+            if pending is None:
+                h = ops.add_rmsnorm(x, layer["ln1"], cfg.eps)
+            else:
+                x, h = ops.add_rmsnorm(pending, layer["ln1"], cfg.eps, residual=x)
+            if layer["kind"] == "gdn":
+                qkv, z, a, b = self._split_gdn(glue.gemm_2d(h, layer["in_proj"]))
+                conv = _conv4_prefill(qkv, layer["conv"], seq_start)
+                kd = cfg.gdn_width
+                q = conv[:, :kd].view(total, heads, dim)
+                k = conv[:, kd: 2 * kd].view(total, heads, dim)
+                v = conv[:, 2 * kd:].view(total, heads, dim)
+                q_n, k_n, beta, g = _qk_norm_gates(q, k, a, b, layer["a_log"], layer["dt_bias"])
+                core, state = ops.gdn_chunked_prefill_packed(q_n, k_n, v, beta, g, cu)
+                self.rec_state[i].copy_(state)
+                _conv_state_pack(self.conv_state[i], qkv, cu)
+                normed = ops.gdn_gated_rmsnorm_fused(core, z, layer["norm"])
+                mixed = glue.gemm_2d(normed, layer["out_proj"])
+            else:
+                q, k, v, gate = self._split_attention(glue.gemm_2d(h, layer["qkvg"]))
+                k_cache, v_cache = self.kv[i]
+                ctx = ops.fused_prefill_attention(q, k, v, gate, k_cache, v_cache, self.block_table, cu, pos_in_seq,
+                                                  self.inv_freq, cfg.rotary_dim, max_len)
+                mixed = glue.gemm_2d(ctx, layer["o_proj"])
+            x, h = ops.add_rmsnorm(mixed, layer["ln2"], cfg.eps, residual=x)
+            gate_up = glue.gemm_2d(h, layer["gate_up"])
+            pending = glue.gemm_2d(_swiglu(gate_up[:, : cfg.intermediate], gate_up[:, cfg.intermediate:]), layer["down"])
+        x = glue.residual_add(pending, x)
+        last = x.index_select(0, cu[1:].long() - 1)
+        self.pos.copy_(torch.tensor(lengths, dtype=torch.int64))
+        self.tok.copy_(self._head(last))
+        return self.tok.clone()
+
+
+    def _prefill_eager_glue(self, ids, cu, max_len, pos_in_seq, seq_start, lengths):
+        """The same prefill with the operators around the path as eager PyTorch (glue.py); for comparisons."""
+        cfg = self.cfg
         total, heads, dim = ids.numel(), cfg.gdn_heads, cfg.gdn_dim
         x = glue.embedding_gather(ids, self.w["embed"])
         for i, layer in enumerate(self.w["layers"]):

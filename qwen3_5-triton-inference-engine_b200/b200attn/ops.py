@@ -221,7 +221,8 @@ def fused_decode_attention(q, k_new, v_new, gate, k_cache, v_cache, block_table,
     read pos / block_table / cache pages before that predecessor has finished (valid when it writes none of them).
     partition: 0 = the kernel picks how the KV pages are cut over the CTAs; 1 = equal page ranges per CTA (segments cut at
     a range boundary are merged through the workspace); 2 = one whole (sequence, kv head) segment per CTA (needs
-    batch * H_kv <= the number of SMs).  Same result up to fp32 summation order."""
+    batch * H_kv <= the number of SMs); 3 = one segment per thread-block cluster, merged through distributed shared
+    memory (needs batch * H_kv <= 64).  Same result up to fp32 summation order."""
     batch, num_q_heads, head_dim = q.shape
     num_kv_heads = k_new.shape[1]
     assert k_new.shape == v_new.shape == (batch, num_kv_heads, head_dim)

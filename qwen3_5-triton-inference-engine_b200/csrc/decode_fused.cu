@@ -16,6 +16,11 @@
 //   - A segment cut by a range boundary leaves one partial (m, l, acc[4][256]) per CTA in the workspace; the
 //     last CTA to arrive (a counter per segment) merges them and finishes the segment.  No CTA ever waits for
 //     another one, so nothing depends on co-residency.
+// Small batches (up to 64 segments) are launched as thread-block clusters and may give each SEGMENT to one cluster
+// instead: its CTAs split the segment's pages evenly, exchange their online-softmax states through distributed shared
+// memory - every CTA receives one slice of the output dims from all the others, so the exchange is 4 KiB per CTA
+// whatever the cluster size - meet at one cluster barrier and finish their slice.  No global partials, tickets or
+// fences, and no CTA streams more than 1/cluster of the longest segment.
 // The appended token never takes the cross-CTA write-then-read path that makes the reference keep the append
 // in its own launch (gqa_attention_decode_paged.py:332-334): its K/V rows are built in shared memory by the warp
 // that owns the segment's extra unit and stored to the cache from there; page readers mask that slot.
@@ -45,7 +50,12 @@ constexpr int FD_SMEM_CUM = ((FD_MAX_BATCH + 1) * 4 + 15) / 16 * 16;   // exclus
 constexpr int FD_SMEM_POS = FD_MAX_BATCH * 4;                           // pos[] as int32
 constexpr int FD_Q_PITCH = HEAD_DIM + 8;                                // bf16 elements per staged Q row
 constexpr int FD_SMEM_Q = 2 * GROUP * FD_Q_PITCH * 2;                   // rotated Q of this piece and of the next
-constexpr int FD_SMEM_TOTAL = FD_SMEM_RING + FD_SMEM_MERGE + FD_SMEM_CUM + FD_SMEM_POS + FD_SMEM_Q + 1024;
+constexpr int FD_MAX_CLUSTER = 16;                                      // CTAs that may share one segment
+constexpr int FD_SMEM_RECV = FD_TILE_FLOATS * 4 + FD_MAX_CLUSTER * 8 * 4;  // cluster exchange: one accumulator slice per
+                                                                           // source CTA (4 KiB in all) + every (m, l)
+constexpr int FD_SMEM_TOTAL =
+    FD_SMEM_RING + FD_SMEM_MERGE + FD_SMEM_CUM + FD_SMEM_POS + FD_SMEM_Q + FD_SMEM_RECV + 1024;
+static_assert(FD_SMEM_TOTAL <= 227 * 1024, "shared memory budget");
 
 struct FusedDecodeParams {
   const __nv_bfloat16 *q, *k_new, *v_new, *gate;
@@ -60,7 +70,9 @@ struct FusedDecodeParams {
   int* counters;
   int* err;
   int batch, num_kv_heads, rotary_half, overlap;
-  int partition;  // 0 = the time models below choose, 1 = stream-K, 2 = one whole segment per CTA
+  int partition;  // 0 = the time models below choose, 1 = stream-K, 2 = one whole segment per CTA, 3 = one segment
+                  // per thread-block cluster
+  int cluster_size;  // CTAs per cluster of this launch (1 = launched without clusters)
   float scale, eps;
 };
 
@@ -218,6 +230,8 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   int* cum = reinterpret_cast<int*>(smem + FD_SMEM_RING + FD_SMEM_MERGE);
   int* pos_s = reinterpret_cast<int*>(smem + FD_SMEM_RING + FD_SMEM_MERGE + FD_SMEM_CUM);
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem + FD_SMEM_RING + FD_SMEM_MERGE + FD_SMEM_CUM + FD_SMEM_POS);
+  float* recv = reinterpret_cast<float*>(smem + FD_SMEM_RING + FD_SMEM_MERGE + FD_SMEM_CUM + FD_SMEM_POS + FD_SMEM_Q);
+  float* recv_ml = recv + FD_TILE_FLOATS;   // [source rank][m[4], l[4]]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int heads = p.num_kv_heads, batch = p.batch;
@@ -268,15 +282,57 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   //    partial, a ticket and a merge, and a CTA that spans several segments stops at every boundary.
   //  - One whole segment per CTA, when there are no more segments than CTAs: no partials at all, but the longest
   //    segment sets the time, and an SM alone streams at about 75 GB/s.
-  // The choice compares two time models fitted to measurements of this kernel on B200 (microseconds x 1000, u = units):
-  //    whole   max(0.165, 0.35 * segments / CTAs) * u_longest + 9.5     stream-K   0.35 * u_per_CTA + 16.5
+  //  - One segment per CLUSTER (launches with clusters only, when every segment gets a cluster of its own): the CTAs
+  //    of a cluster take equal shares of the segment's units and merge through distributed shared memory.
+  // The choice compares time models fitted to measurements of this kernel on B200 (nanoseconds, u = units of 16 KiB;
+  // every form is also bound by the DRAM rate, 2.64 ns per unit):
+  //    stream-K  max(350 u_per_CTA, 2.64 u_total) + 16500
+  //    whole     max(165, 350 segments / CTAs) u_longest + 9500
+  //    cluster   max(190 u_longest / cluster_size, 2.64 u_total) + 10500
+  // A form is taken over stream-K when its model wins by 5 %.
   const int total = heads * cum[batch];
   const int grid = static_cast<int>(gridDim.x), nseg = batch * heads;
   const int chunk = max((total + grid - 1) / grid, FD_WARPS);
-  const bool model_whole = 21 * (max(165, 350 * nseg / grid) * s_max_units + 9500) < 20 * (350 * chunk + 16500);  // by 5 %
-  const bool whole_segments = nseg <= grid && (p.partition == 2 || (p.partition == 0 && model_whole));
+  const int csize = p.cluster_size;
+  const int dram = total * 66 / 25;  // 2.64 ns per unit
+  const int t_stream = max(350 * chunk, dram) + 16500;
+  const int t_whole = max(165, 350 * nseg / grid) * s_max_units + 9500;
+  const int t_cluster = max(190 * ((s_max_units + csize - 1) / csize), dram) + 10500;
+  const bool cluster_fits = csize > 1 && nseg * csize <= grid;
+  const bool whole_fits = nseg <= grid;
+  int form = 1;  // 1 stream-K, 2 whole segments, 3 cluster per segment
+  if (p.partition != 0) {
+    form = (p.partition == 3 && cluster_fits) ? 3 : (p.partition == 2 && whole_fits) ? 2 : 1;
+  } else {
+    int best = t_stream;
+    if (whole_fits && 21 * t_whole < 20 * best) {
+      form = 2;
+      best = t_whole;
+    }
+    if (cluster_fits && 21 * t_cluster < 20 * t_stream && t_cluster <= best) form = 3;
+  }
+  const bool cluster_mode = form == 3, whole_segments = form == 2;
   int r0, r1;
-  if (whole_segments) {
+  Segment cseg = {0, 0, 0, 0};  // cluster mode: the segment of this CTA's cluster
+  const int rank = csize > 1 ? static_cast<int>(blockIdx.x) % csize : 0;  // == %cluster_ctarank of a 1-D cluster
+  if (cluster_mode) {
+    const int cl = static_cast<int>(blockIdx.x) / csize;
+    if (cl < nseg) {
+      const int sb = cl / heads, sh = cl % heads;
+      const int units = cum[sb + 1] - cum[sb];
+      const int per = (units + csize - 1) / csize;
+      const int start = heads * cum[sb] + sh * units;
+      cseg.b = sb;
+      cseg.h = sh;
+      cseg.start = start;
+      cseg.end = start + units;
+      r0 = min(start + rank * per, start + units);
+      r1 = min(r0 + per, start + units);
+    } else {
+      pdl_wait();  // a cluster without a segment: all its CTAs leave together, nobody waits for them
+      return;
+    }
+  } else if (whole_segments) {
     if (static_cast<int>(blockIdx.x) < nseg) {
       const int sb = blockIdx.x / heads, sh = blockIdx.x % heads;
       const int units = cum[sb + 1] - cum[sb];
@@ -289,14 +345,16 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
     r0 = blockIdx.x * chunk;
     r1 = min(r0 + chunk, total);
   }
-  if (r0 >= r1) {
+  if (r0 >= r1 && !cluster_mode) {
     pdl_wait();  // an idle CTA still orders the grid after its predecessor
     return;
   }
+  // (in cluster mode a CTA without units of its own still takes part in the exchange below: the cluster barrier needs
+  //  every thread of every CTA of the cluster, and this CTA finishes a slice of the output)
 
   // ---- per-warp issue cursor: walks the same unit sequence as the consumer, FD_RING tiles ahead.
   // Tile sequence of a warp: K(u0), V(u0), K(u1), V(u1), ...; tile n lives in ring slot n % FD_RING.
-  Segment iseg = segment_of_unit(r0, cum, batch, heads);
+  Segment iseg = cluster_mode ? cseg : segment_of_unit(r0, cum, batch, heads);
   int iu = r0 + warp;        // unit whose tiles are issued next
   bool i_is_v = false;       // next tile to issue is the V tile of unit iu
   int ii = 0;                // index of unit iu among this warp's units of the current piece
@@ -350,7 +408,7 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   for (int s = 0; s < FD_RING; ++s) issue_next();
 
   // ---- consumer: CTA-uniform loop over the pieces of this range
-  Segment seg = segment_of_unit(r0, cum, batch, heads);
+  Segment seg = cluster_mode ? cseg : segment_of_unit(r0, cum, batch, heads);
   const int hh = tid >> 6, d0 = (tid & 63) * 4;  // element mapping of the merge / finish steps
   int piece = 0;
   bool have_pending = false;
@@ -383,7 +441,7 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   pdl_wait();  // from here on the predecessor's q / k_new / v_new / gate are read and global memory is written
   stage_q(q_s, p, seg.b, seg.h, pos_s[seg.b], tid);
   __syncthreads();
-  while (seg.start < r1) {
+  while (seg.start < r1 || (cluster_mode && piece == 0)) {  // in cluster mode exactly once, also without units
     const int lo = max(seg.start, r0), hi = min(seg.end, r1);
     const int np = seg.end - seg.start - 1;
     const int64_t pos_b = pos_s[seg.b];
@@ -470,7 +528,30 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
       have_pending = false;
     }
     const bool whole = (lo == seg.start) && (hi == seg.end);
-    if (whole) {
+    if (cluster_mode) {
+      // ---- exchange through distributed shared memory.  Output element e = tid (4 dims of one head) is finished by
+      // the CTA of rank e / tpr; every CTA sends each of its 1024 accumulators to the rank that finishes it (slot
+      // [own rank][e % tpr] of that CTA's receive buffer) and its (m, l) to everybody, then all meet at the barrier.
+      const int tpr = FD_THREADS / csize;
+      const uint32_t slot = smem_u32(recv + (rank * tpr + (tid % tpr)) * 4);
+      st_cluster_f32x4(cluster_map(slot, static_cast<uint32_t>(tid / tpr)), acc[0], acc[1], acc[2], acc[3]);
+      if ((tid & 63) == 0) {
+        for (int dst = 0; dst < csize; ++dst) {
+          const uint32_t ml = cluster_map(smem_u32(recv_ml + rank * 8), static_cast<uint32_t>(dst));
+          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ml + hh * 4), "f"(m_all) : "memory");
+          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ml + 16 + hh * 4), "f"(l_all) : "memory");
+        }
+      }
+      cluster_sync();  // release / acquire: every CTA's slices and (m, l) have landed
+      if (tid / tpr == rank) {
+        float m_fin = -INFINITY, l_fin = 0.f;
+        float a4[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int src = 0; src < csize; ++src)
+          merge_state(m_fin, l_fin, a4, recv_ml[src * 8 + hh], recv_ml[src * 8 + 4 + hh],
+                      *reinterpret_cast<const float4*>(recv + (src * tpr + (tid % tpr)) * 4));
+        finish_store(p, seg.b, seg.h * GROUP + hh, d0, a4, l_fin, gate_pf);
+      }
+    } else if (whole) {
       finish_store(p, seg.b, seg.h * GROUP + hh, d0, acc, l_all, gate_pf);
     } else {
       // ---- leave a partial; the last CTA to arrive on this segment merges all of them.  Nobody waits for the
@@ -551,6 +632,41 @@ static bool cache_tile_map(const void* base, int64_t rows, CUtensorMap* out) {
 
 extern "C" int64_t b200_fused_decode_workspace_bytes(void) { return FD_WORKSPACE_BYTES; }
 
+// CTAs of the fused kernel that can be resident at once when launched in clusters of `csize` (asked from the runtime
+// once per device and size; 0 when such clusters cannot be launched).  Sizes above 8 need the kernel's opt-in.
+static int cluster_limit(int csize) {
+  static int cached[64][5];       // [device][log2(csize)]: 0 = unknown, -1 = cannot launch
+  static std::mutex mu;
+  int dev = 0, lg = 0;
+  while ((1 << lg) < csize) ++lg;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || lg > 4) return 0;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev][lg] == 0) {
+    cached[dev][lg] = -1;
+    bool ok = true;
+    if (csize > 8)
+      ok = cudaFuncSetAttribute(fused_decode_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+    if (ok) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(static_cast<unsigned>(csize) * 16);
+      cfg.blockDim = dim3(FD_THREADS);
+      cfg.dynamicSmemBytes = FD_SMEM_TOTAL;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = static_cast<unsigned>(csize);
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, fused_decode_kernel, &cfg) == cudaSuccess && clusters > 0)
+        cached[dev][lg] = clusters * csize;
+    }
+    cudaGetLastError();  // a refused query must not look like a failed launch later
+  }
+  return cached[dev][lg] > 0 ? cached[dev][lg] : 0;
+}
+
 static int fused_decode_impl(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_new,
                                            int64_t kn_stride_b, int64_t kn_stride_h, const void* v_new,
                                            int64_t vn_stride_b, int64_t vn_stride_h, const void* gate,
@@ -562,7 +678,7 @@ static int fused_decode_impl(const void* q, int64_t q_stride_b, int64_t q_stride
                                            int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
                                            const void* q_norm_weight, const void* k_norm_weight, float eps,
                                            int32_t overlap, int32_t partition, b200_stream_t stream) {
-  B200_REQUIRE(partition >= 0 && partition <= 2, "fused_decode_attention: partition must be 0, 1 or 2 (got %d)", partition);
+  B200_REQUIRE(partition >= 0 && partition <= 3, "fused_decode_attention: partition must be 0..3 (got %d)", partition);
   B200_REQUIRE(aligned16(q_norm_weight) && aligned16(k_norm_weight),
                "fused_decode_attention: norm weights must be 16-byte aligned");
   B200_REQUIRE(batch > 0 && batch <= FD_MAX_BATCH, "fused_decode_attention: batch must be in [1, %d] (got %d)",
@@ -634,12 +750,35 @@ static int fused_decode_impl(const void* q, int64_t q_stride_b, int64_t q_stride
   p.scale = 1.0f / sqrtf(static_cast<float>(head_dim));
   int grid = sm_count();
   if (grid > FD_MAX_CTAS) grid = FD_MAX_CTAS;
-  B200_REQUIRE(partition != 2 || batch * num_kv_heads <= grid,
-               "fused_decode_attention: partition 2 (whole segments) needs batch*H_kv <= %d CTAs (got %d)", grid,
-               batch * num_kv_heads);
+  // Up to 64 segments: launch as clusters so that the kernel may give every segment a whole cluster (the largest power
+  // of two that still leaves each segment its own cluster, at most 16).  The cluster size depends on the batch only,
+  // so it is the same for every replay of a captured launch; whether the cluster form is used is decided on the
+  // device from the lengths.  cluster_limit(): how many CTAs of a cluster size can be resident at once.
+  const int nseg = batch * num_kv_heads;
+  int csize = 1;
+  if (nseg <= 64) {
+    csize = FD_MAX_CLUSTER;
+    while (csize > 1 && (nseg * csize > grid || cluster_limit(csize) < nseg * csize)) csize >>= 1;
+  }
+  B200_REQUIRE(partition != 2 || nseg <= grid,
+               "fused_decode_attention: partition 2 (whole segments) needs batch*H_kv <= %d CTAs (got %d)", grid, nseg);
+  B200_REQUIRE(partition != 3 || csize > 1,
+               "fused_decode_attention: partition 3 (a cluster per segment) needs batch*H_kv <= 64 (got %d)", nseg);
   p.partition = partition;
-  if (launch_pdl((overlap & OVERLAP_START) != 0, fused_decode_kernel, dim3(grid), dim3(FD_THREADS), FD_SMEM_TOTAL,
-                 reinterpret_cast<cudaStream_t>(stream), p, map_k, map_v) != cudaSuccess)
+  p.cluster_size = csize;
+  cudaError_t launched;
+  if (csize > 1) {
+    // every CTA of the launch must be resident together with its cluster mates; the other forms work with any grid
+    int cgrid = cluster_limit(csize);
+    if (cgrid > grid / csize * csize) cgrid = grid / csize * csize;
+    launched = launch_pdl_cluster((overlap & OVERLAP_START) != 0, static_cast<unsigned>(csize), fused_decode_kernel,
+                                  dim3(cgrid), dim3(FD_THREADS), FD_SMEM_TOTAL, reinterpret_cast<cudaStream_t>(stream), p,
+                                  map_k, map_v);
+  } else {
+    launched = launch_pdl((overlap & OVERLAP_START) != 0, fused_decode_kernel, dim3(grid), dim3(FD_THREADS), FD_SMEM_TOTAL,
+                          reinterpret_cast<cudaStream_t>(stream), p, map_k, map_v);
+  }
+  if (launched != cudaSuccess)
     return fail(ERR_LAUNCH, "fused_decode_attention: %s", cudaGetErrorString(cudaGetLastError()));
   return check_launch("fused_decode_attention");
 }

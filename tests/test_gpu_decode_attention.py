@@ -177,12 +177,15 @@ def test_nan_in_unowned_slots_is_ignored(ops):
 # --------------------------------------------------------------------------- fused decode kernel
 @pytest.mark.parametrize("lengths", [[0], [1], [16], [37, 64, 100, 128], [0, 15, 16, 17, 31, 32, 33, 1000],
                                      [4096, 512, 33, 2049, 777, 1, 3000, 16], [32768], [600] * 64])
-@pytest.mark.parametrize("partition", [0, 1, 2])
+@pytest.mark.parametrize("partition", [0, 1, 2, 3])
 def test_fused_decode_vs_oracle(ops, lengths, partition):
     """partition pins how the kernel cuts the KV pages over its CTAs (1 = equal page ranges with cross-CTA merges,
-    2 = one whole segment per CTA, 0 = the kernel's own choice), so that both forms are checked on every length set."""
+    2 = one whole segment per CTA, 3 = one segment per thread-block cluster, 0 = the kernel's own choice), so that every
+    form is checked on every length set it can take."""
     if partition == 2 and 2 * len(lengths) > torch.cuda.get_device_properties(0).multi_processor_count:
         pytest.skip("whole segments need no more segments than SMs")
+    if partition == 3 and 2 * len(lengths) > 64:
+        pytest.skip("a cluster per segment needs at most 64 segments")
     c = make_paged_case(lengths, seed=300 + len(lengths) + lengths[0])
     inv = rope_inv_freq()
     d = to_dev(c)

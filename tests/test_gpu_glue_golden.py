@@ -167,7 +167,7 @@ def test_attention_decode_layer_against_reference_chain(mods, golden):
         err = (out.float() - g["out"].float()).abs().max().item()
         assert err <= 2.0 ** -6, f"{tag}: max abs {err}"
 
-    for partition in (0, 1, 2):
+    for partition in (0, 1, 2, 3):
         kc, vc = g["k_cache_in"].clone(), g["v_cache_in"].clone()
         out = ops.fused_decode_attention(q_raw, k_raw, v_raw, gate, kc, vc, g["block_table"], g["pos"], g["inv_freq"], 64,
                                          ws, q_norm_weight=g["q_norm_weight"], k_norm_weight=g["k_norm_weight"],
