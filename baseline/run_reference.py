@@ -4,6 +4,8 @@
                        installed Triton for the local GPU): the thing this repository replaces
     --kernels b200     this repository's drop-in `triton_kernels/` package (the CUDA library) under the SAME
                        reference `engine/runner.py`, `cache.py`, `paging.py`
+    --kernels b200-fast  the same, with the opt-in `b200attn.fast_runner` subclass of the reference runner that takes
+                       the fused decode / packed-prefill entry points
 
 Both operator sets register the same `wy_lib::*` torch operators, so they cannot live in one process: a caller
 (bench.py, the parity test) starts this script once per operator set and reads the result file.
@@ -47,7 +49,7 @@ def setup_paths(kernels: str) -> None:
     """Make `import triton_kernels` resolve to the chosen operator set and `import engine` to the reference copy."""
     if not (REF / "engine" / "runner.py").exists():
         raise SystemExit(f"{REF} is absent: run `python baseline/make_ref.py` where the reference checkout is available")
-    if kernels == "b200":
+    if kernels.startswith("b200"):
         sys.path.insert(0, str(PKG))
         import triton_kernels  # noqa: F401  this repository's drop-in; must be imported before the reference engine
         assert Path(triton_kernels.__file__).resolve().is_relative_to(PKG)
@@ -115,6 +117,15 @@ def text_weights(cfg: dict, tensors: dict):
         head_dim=cfg["head_dim"], linear_num_heads=cfg["gdn_heads"], linear_head_dim=cfg["gdn_dim"])
 
 
+def runner_class(kernels: str):
+    """The reference's `Qwen35Runner`, or this package's opt-in subclass of it."""
+    if kernels == "b200-fast":
+        from b200attn.fast_runner import fast_runner_class
+        return fast_runner_class()
+    from engine.runner import Qwen35Runner
+    return Qwen35Runner
+
+
 def make_prompts(cfg, batch, prompt_len, seed, ragged):
     import torch
     gen = torch.Generator().manual_seed(seed)
@@ -140,12 +151,11 @@ def events_ms(fn, repeat=1):
 def task_parity(args, cfg):
     import torch
     from engine.cache import allocate_caches
-    from engine.runner import Qwen35Runner
     from triton_kernels.vocab_argmax import lm_head_argmax
 
     dev = torch.device("cuda", 0)
     w = text_weights(cfg, random_tensors(cfg, args.seed, dev))
-    runner = Qwen35Runner(w, compile=False)
+    runner = runner_class(args.kernels)(w, compile=False)
     prompts = [p.to(dev) for p in make_prompts(cfg, args.batch, args.prompt_len, args.seed, args.ragged)]
     max_len = max(p.numel() for p in prompts) + args.steps + 8
     caches = allocate_caches(w, max_len, paged=True, batch=args.batch)
@@ -171,12 +181,12 @@ def task_parity(args, cfg):
 def task_model_bench(args, cfg):
     import torch
     from engine.cache import allocate_caches
-    from engine.runner import GraphedDecoder, Qwen35Runner
+    from engine.runner import GraphedDecoder
     from triton_kernels.vocab_argmax import lm_head_argmax
 
     dev = torch.device("cuda", 0)
     w = text_weights(cfg, random_tensors(cfg, args.seed, dev))
-    runner = Qwen35Runner(w, compile=False)
+    runner = runner_class(args.kernels)(w, compile=False)
     prompts = [p.to(dev) for p in make_prompts(cfg, args.batch, args.prompt_len, args.seed, False)]
     max_len = args.prompt_len + args.steps + 24
     caches = allocate_caches(w, max_len, paged=True, batch=args.batch)
@@ -469,7 +479,7 @@ def task_cpu_legs(args, cfg):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--kernels", choices=["triton", "b200"], required=True)
+    ap.add_argument("--kernels", choices=["triton", "b200", "b200-fast"], required=True)
     ap.add_argument("--task", choices=["parity", "model_bench", "op_bench", "cpu_legs"], required=True)
     ap.add_argument("--out", required=True, help="result file: .pt for parity, .json otherwise")
     ap.add_argument("--teacher", default=None)

@@ -652,7 +652,8 @@ def reference_triton_legs(args, sweep, model, value):
         out["headline_step"] = {"us_per_layer": head, "gbs": nbytes / (head * 1e-6) / 1e9,
                                 "launches": 6, "speedup_of_fused_kernel": value / (nbytes / (head * 1e-6) / 1e9)}
     if sweep is not None:
-        alias = {"fused_decode": "decode_chain", "fused_prefill_attention": "prefill_attention_layer_chain"}
+        alias = {"fused_decode": "decode_chain", "fused_prefill_attention": "prefill_attention_layer_chain",
+                 "gdn chunk-64 prefill, one sequence (drop-in entry point)": "gdn chunk-64 pipeline (3 launches)"}
         for row in sweep:
             op = alias.get(row["op"], row["op"])
             us = by_key.get((op, row.get("B"), row.get("ctx"), row.get("shape")))
@@ -664,7 +665,8 @@ def reference_triton_legs(args, sweep, model, value):
     if model is not None:
         extra = ["--batch", str(model["batch_per_gpu"]), "--prompt-len", str(model["prompt_len"]), "--steps",
                  str(min(model["decode_steps"], 256))]
-        for kernels, key in (("triton", "runner_on_triton"), ("b200", "runner_on_dropin_operators")):
+        for kernels, key in (("triton", "runner_on_triton"), ("b200", "runner_on_dropin_operators"),
+                             ("b200-fast", "fast_runner_subclass")):
             r, why = run_reference_task("model_bench", kernels, extra, 900)
             out[key] = {"unavailable": why} if r is None else {k: r[k] for k in ("ms_per_step", "tok_s", "prefill_ms",
                                                                                    "decode_steps", "batch")}
@@ -916,10 +918,19 @@ def run_prefill_sweep(ops, device, steps, only=None):
     ms = time_steps(lambda i: ops.gdn_chunked_prefill_packed(gq, gk, gv, beta, g, cu, 128, fused=False), steps, 3)
     rows.append({"op": "gdn_chunked_prefill_packed (3 launches)", "shape": "cfg4 B=32 x 128", "tokens": total,
                  "us": ms * 1e3, "tflops_fp32": 12.1e6 * 2 * len(lengths) * heads / (ms * 1e-3) / 1e12})
-    one = slice(0, 128)
-    ms = time_steps(lambda i: ops.call_gdn_recurrent_prefill_chunked_triton(gq[one], gk[one], gv[one], beta[one], g[one]),
-                    steps, 3)
-    rows.append({"op": "gdn chunk-64 pipeline (3 launches)", "shape": "1 sequence x 128", "tokens": 128, "us": ms * 1e3})
+    # one sequence through the drop-in entry point the reference runner calls for long prompts (engine/runner.py:272-273)
+    for n_tok in (128, 2048):
+        gen1 = torch.Generator().manual_seed(3)
+        sq = (torch.nn.functional.normalize(torch.randn(n_tok, heads, 128, generator=gen1), dim=-1) * 128 ** -0.5)
+        sk = torch.nn.functional.normalize(torch.randn(n_tok, heads, 128, generator=gen1), dim=-1)
+        sq, sk = sq.to(torch.bfloat16).to(device), sk.to(torch.bfloat16).to(device)
+        sv = torch.randn(n_tok, heads, 128, generator=gen1).to(torch.bfloat16).to(device)
+        sb = torch.sigmoid(torch.randn(n_tok, heads, generator=gen1)).to(device)
+        sg = (-torch.nn.functional.softplus(torch.randn(n_tok, heads, generator=gen1))
+              * torch.exp(torch.rand(heads, generator=gen1) * 2.7)).to(device)
+        ms = time_steps(lambda i: ops.call_gdn_recurrent_prefill_chunked_triton(sq, sk, sv, sb, sg), steps, 3)
+        rows.append({"op": "gdn chunk-64 prefill, one sequence (drop-in entry point)", "shape": f"1 x {n_tok}",
+                     "tokens": n_tok, "us": ms * 1e3})
     return rows
 
 

@@ -87,15 +87,29 @@ class Engine:
     """One replica: weights, caches and the two entry points `prefill` and `step`."""
 
     def __init__(self, cfg: ModelConfig, weights: dict, batch: int, max_context: int, device, page_seed: int = 0,
-                 fused_glue: bool = True):
+                 fused_glue: bool = True, on_demand_pages: bool = False, num_pages: int | None = None):
         """fused_glue: run the row-wise operators of a decode step (residual + RMSNorm, SwiGLU, conv + q/k norms +
-        gates, gated RMSNorm) as this package's single-launch kernels; False keeps them as eager PyTorch (glue.py)."""
+        gates, gated RMSNorm) as this package's single-launch kernels; False keeps them as eager PyTorch (glue.py).
+        on_demand_pages: KV pages come from a shared pool of `num_pages` (default: enough for every slot at
+        `max_context`) as sequences grow (`serving.PageAllocator`), the `batch` sequences are independent SLOTS that
+        `prefill_slots` fills one group at a time, and `set_active` masks the idle ones - what `ContinuousBatcher`
+        drives.  Without it every slot owns its pages from the start, as the reference reserves them
+        (engine/cache.py:154-159)."""
         self.cfg, self.w, self.batch, self.device = cfg, weights, batch, torch.device(device)
         self.fused_glue = fused_glue
         pages_per_seq = (max_context + ops.PAGE_SIZE - 1) // ops.PAGE_SIZE
-        num_pages = batch * pages_per_seq
-        perm = torch.randperm(num_pages, generator=torch.Generator().manual_seed(page_seed))
-        self.block_table = perm.view(batch, pages_per_seq).to(torch.int32).to(self.device)
+        self.pages = None
+        self.active = None
+        if on_demand_pages:
+            from .serving import PageAllocator
+            num_pages = batch * pages_per_seq + 1 if num_pages is None else num_pages
+            self.pages = PageAllocator(num_pages, batch, pages_per_seq, device=self.device)
+            self.block_table = self.pages.block_table
+            self.active = torch.ones(batch, dtype=torch.int64, device=self.device)   # 1 = the slot decodes
+        else:
+            num_pages = batch * pages_per_seq
+            perm = torch.randperm(num_pages, generator=torch.Generator().manual_seed(page_seed))
+            self.block_table = perm.view(batch, pages_per_seq).to(torch.int32).to(self.device)
         self.max_context = pages_per_seq * ops.PAGE_SIZE
         self.pos = torch.zeros(batch, dtype=torch.int64, device=self.device)
         self.kv, self.conv_state, self.rec_state = {}, {}, {}
@@ -112,6 +126,7 @@ class Engine:
         self.inv_freq = (1.0 / (cfg.rope_theta ** (torch.arange(0, r, 2, dtype=torch.float32) / r))).to(self.device)
         self.tok = torch.zeros(batch, dtype=torch.int64, device=self.device)   # input of the next step
         self.graph = None
+        self._warmed = False     # an eager decode step has run (first-call set-up of the kernels is done)
 
     # ------------------------------------------------------------------------------------------------ shared pieces
     def _streams_weight(self, weight, swiglu: bool = False) -> bool:
@@ -164,15 +179,48 @@ class Engine:
     def prefill(self, prompts: list[list[int]]) -> torch.Tensor:
         """Packed varlen prefill of `batch` prompts (engine/runner.py:212-405 with a PackedBatch); fills every cache,
         sets pos, returns the first generated token of each sequence (int64 [B]) and leaves it in `self.tok`."""
+        assert len(prompts) == self.batch
+        if self.pages is not None:
+            for slot, prompt in enumerate(prompts):
+                self.pages.release(slot)
+                self.pages.ensure(slot, len(prompt) + 1)
+        return self._prefill(prompts, None)
+
+    @torch.no_grad()
+    def prefill_slots(self, slots: list[int], prompts: list[list[int]]) -> torch.Tensor:
+        """Packed prefill of `prompts` into the given slots only (their pages must already be there: the caller is the
+        batcher, which calls `pages.ensure` first); the other slots keep their state.  Returns the first generated
+        token of each prompt (int64 [len(slots)]) and leaves them in `self.tok[slots]`."""
+        assert self.pages is not None, "slot-wise prefill needs on_demand_pages=True"
+        assert len(slots) == len(prompts) and len(set(slots)) == len(slots)
+        assert all(0 <= s < self.batch for s in slots)
+        return self._prefill(prompts, torch.tensor(slots, dtype=torch.int64, device=self.device))
+
+    def set_active(self, mask) -> None:
+        """Which slots decode (host list of bools).  An idle slot still rides along in the step's launches - the batch
+        dimension of a captured graph is fixed - but its position is forced back to zero after every step and its page
+        table row points at the spare page, so nothing it writes is ever read."""
+        assert self.active is not None and len(mask) == self.batch
+        self.active.copy_(torch.tensor([1 if m else 0 for m in mask], dtype=torch.int64), non_blocking=True)
+
+    def _prefill(self, prompts: list[list[int]], slots) -> torch.Tensor:
         cfg = self.cfg
-        assert len(prompts) == self.batch and all(0 < len(p) <= self.max_context for p in prompts)
+        assert all(0 < len(p) <= self.max_context for p in prompts)
         lengths = [len(p) for p in prompts]
+        table = self.block_table if slots is None else self.block_table.index_select(0, slots)
+
+        def put(dst, src):          # write a per-sequence result into all slots, or into the chosen ones
+            if slots is None:
+                dst.copy_(src)
+            else:
+                dst.index_copy_(0, slots, src.to(dst.dtype))
         ids = torch.tensor([t for p in prompts for t in p], dtype=torch.int64).to(self.device)
         cu, max_len = ops.build_cu_seqlens(lengths, device=self.device)
         pos_in_seq = torch.cat([torch.arange(n) for n in lengths]).to(torch.int32).to(self.device)
         seq_start = torch.repeat_interleave(cu[:-1], torch.tensor(lengths, device=self.device))  # runner.py:136
         total, heads, dim = ids.numel(), cfg.gdn_heads, cfg.gdn_dim
         if not self.fused_glue:
+            assert slots is None, "slot-wise prefill runs on the single-launch operators only"
             return self._prefill_eager_glue(ids, cu, max_len, pos_in_seq, seq_start, lengths)
         # every operator between the projections is one launch of this package (cuBLAS for the prompt-sized GEMMs)
         x = _embedding_gather(ids, self.w["embed"])
@@ -192,14 +240,20 @@ class Engine:
                 v = conv[:, 2 * kd:].view(total, heads, dim)
                 q_n, k_n, beta, g = _qk_norm_gates(q, k, a, b, layer["a_log"], layer["dt_bias"])
                 core, state = ops.gdn_chunked_prefill_packed(q_n, k_n, v, beta, g, cu)
-                self.rec_state[i].copy_(state)
-                _conv_state_pack(self.conv_state[i], qkv, cu)
+                put(self.rec_state[i], state)
+                if slots is None:
+                    _conv_state_pack(self.conv_state[i], qkv, cu)
+                else:
+                    conv_rows = torch.empty((len(prompts),) + tuple(self.conv_state[i].shape[1:]), dtype=torch.bfloat16,
+                                            device=self.device)
+                    _conv_state_pack(conv_rows, qkv, cu)
+                    put(self.conv_state[i], conv_rows)
                 normed = ops.gdn_gated_rmsnorm_fused(core, z, layer["norm"])
                 mixed = glue.gemm_2d(normed, layer["out_proj"])
             else:
                 q, k, v, gate = self._split_attention(glue.gemm_2d(h, layer["qkvg"]))
                 k_cache, v_cache = self.kv[i]
-                ctx = ops.fused_prefill_attention(q, k, v, gate, k_cache, v_cache, self.block_table, cu, pos_in_seq,
+                ctx = ops.fused_prefill_attention(q, k, v, gate, k_cache, v_cache, table, cu, pos_in_seq,
                                                   self.inv_freq, cfg.rotary_dim, max_len)
                 mixed = glue.gemm_2d(ctx, layer["o_proj"])
             x, h = ops.add_rmsnorm(mixed, layer["ln2"], cfg.eps, residual=x)
@@ -207,9 +261,10 @@ class Engine:
             pending = glue.gemm_2d(_swiglu(gate_up[:, : cfg.intermediate], gate_up[:, cfg.intermediate:]), layer["down"])
         x = glue.residual_add(pending, x)
         last = x.index_select(0, cu[1:].long() - 1)
-        self.pos.copy_(torch.tensor(lengths, dtype=torch.int64))
-        self.tok.copy_(self._head(last))
-        return self.tok.clone()
+        first = self._head(last)
+        put(self.pos, torch.tensor(lengths, dtype=torch.int64, device=self.device))
+        put(self.tok, first)
+        return first.clone()
 
 
     def _prefill_eager_glue(self, ids, cu, max_len, pos_in_seq, seq_start, lengths):
@@ -280,6 +335,8 @@ class Engine:
             x = self._mlp(glue.residual_add(mixed, x), layer)
         nxt = self._head(x)
         self.pos.add_(1)
+        if self.active is not None:
+            self.pos.mul_(self.active)
         return nxt
 
     def _decode_fused(self, tok: torch.Tensor) -> torch.Tensor:
@@ -341,10 +398,15 @@ class Engine:
             nxt = glue.lm_head_argmax(h, embed, last_only=False,
                                       argmax=lambda logits: ops.argmax_rows(logits, self.argmax_ws, overlap=start))
         self.pos.add_(1)
+        if self.active is not None:
+            self.pos.mul_(self.active)       # idle slots stay at position 0 (and on the spare page)
         return nxt
 
     def capture(self) -> None:
-        """Capture one decode step (read self.tok, write the next ids back into self.tok) into a CUDA graph."""
+        """Capture one decode step (read self.tok, write the next ids back into self.tok) into a CUDA graph.
+        At least one eager `step()` must have run before: the first call of several kernels does per-device set-up
+        (shared-memory limits, symbol addresses, workspaces) that must not happen under stream capture."""
+        assert self._warmed, "run one eager step() before capture(): first calls do set-up that cannot be captured"
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
         graph = torch.cuda.CUDAGraph()
@@ -361,4 +423,5 @@ class Engine:
             self.graph.replay()
         else:
             self.tok.copy_(self._decode(self.tok))
+            self._warmed = True
         return self.tok

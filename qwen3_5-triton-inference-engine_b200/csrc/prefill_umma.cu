@@ -66,6 +66,7 @@ rope_scatter_kernel(const __nv_bfloat16* __restrict__ k, int64_t k_t, int64_t k_
                     int rotary_half, __nv_bfloat16* __restrict__ k_rot, int num_kv_heads) {
   const int lp = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_trigger();  // the attention kernel behind this one may start: it waits for this grid before it reads k_rot
   const int seq_start = cu_seqlens[b];
   const int seq_len = cu_seqlens[b + 1] - seq_start;
   if (lp * PAGE >= seq_len) return;
@@ -74,6 +75,8 @@ rope_scatter_kernel(const __nv_bfloat16* __restrict__ k, int64_t k_t, int64_t k_
   const bool in_rot = lane < 2 * lanes_half;
   const bool first = lane < lanes_half;
   const int partner = first ? lane + lanes_half : lane - lanes_half;
+  const int dbase = (in_rot ? (first ? lane : partner) : 0) * 8;
+  const float freq = lane < rotary_half ? inv_freq[lane] : 0.f;  // rotary_half <= 32: one angle per lane
   for (int slot = warp; slot < PAGE; slot += 4) {
     const int tok = lp * PAGE + slot;
     if (tok >= seq_len) break;
@@ -82,21 +85,20 @@ rope_scatter_kernel(const __nv_bfloat16* __restrict__ k, int64_t k_t, int64_t k_
     const uint4 vraw = *reinterpret_cast<const uint4*>(v + t * v_t + h * v_h + lane * 8);
     uint32_t kw[4] = {kraw.x, kraw.y, kraw.z, kraw.w};
     if (rotary_half > 0) {
-      uint32_t other[4];
+      const int64_t pid = ids_are_int64 ? static_cast<const int64_t*>(position_ids)[t]
+                                        : static_cast<int64_t>(static_cast<const int32_t*>(position_ids)[t]);
+      // the warp computes the row's angles once, one sincosf per lane, and hands them round by shuffles (the same
+      // full-range sincosf of float(pos) * inv_freq as before, so the rotated bytes do not change)
+      float sn = 0.f, cs = 1.f;
+      if (lane < rotary_half) sincosf(static_cast<float>(pid) * freq, &sn, &cs);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) other[i] = __shfl_sync(0xffffffffu, kw[i], in_rot ? partner : lane);
-      if (in_rot) {
-        const int64_t pid = ids_are_int64 ? static_cast<const int64_t*>(position_ids)[t]
-                                          : static_cast<int64_t>(static_cast<const int32_t*>(position_ids)[t]);
-        const float posf = static_cast<float>(pid);
-        const int dbase = (first ? lane : partner) * 8;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float s0, c0, s1, c1;
-          sincosf(posf * inv_freq[dbase + 2 * i], &s0, &c0);
-          sincosf(posf * inv_freq[dbase + 2 * i + 1], &s1, &c1);
-          const uint32_t fa = first ? kw[i] : other[i];
-          const uint32_t fb = first ? other[i] : kw[i];
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t other = __shfl_sync(0xffffffffu, kw[i], in_rot ? partner : lane);
+        const float s0 = __shfl_sync(0xffffffffu, sn, dbase + 2 * i), c0 = __shfl_sync(0xffffffffu, cs, dbase + 2 * i);
+        const float s1 = __shfl_sync(0xffffffffu, sn, dbase + 2 * i + 1), c1 = __shfl_sync(0xffffffffu, cs, dbase + 2 * i + 1);
+        if (in_rot) {
+          const uint32_t fa = first ? kw[i] : other;
+          const uint32_t fb = first ? other : kw[i];
           float f0, g0, f1, g1;
           rope_pair(bf16_lo(fa), bf16_lo(fb), s0, c0, f0, g0);
           rope_pair(bf16_hi(fa), bf16_hi(fb), s1, c1, f1, g1);
@@ -129,7 +131,10 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
   const int seq_start = p.cu_seqlens[b];
   const int seq_len = p.cu_seqlens[b + 1] - seq_start;
   const int q0 = qb * PU_BQ;
-  if (q0 >= seq_len) return;
+  if (q0 >= seq_len) {
+    if (FUSED) pdl_wait();  // every CTA orders the grid after the kernel in front of it
+    return;
+  }
   const int kv_end = min(q0 + PU_BQ, seq_len);
   const int n_tiles = (kv_end + PU_TKV - 1) / PU_TKV;
 
@@ -167,6 +172,10 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
       bool ok = true;
       mbar_expect_tx(&bar_q, PU_Q_BYTES);
       tma_load_5d(q_s, &map_q, 0, 0, h, seq_start + q0, 0, &bar_q);
+      // fused form: started while the rope + scatter kernel still runs (programmatic dependent launch).  Everything up
+      // to here - tensor-memory allocation, barriers, the Q tile, and the V tiles of the other producer - overlaps with
+      // it; the rotated K it writes is read only after it has completed.
+      if (FUSED) pdl_wait();
       for (int j = 0; j < n_tiles && ok; ++j) {
         if (j >= 1) ok = mbar_wait_bounded(&bar_s[(j - 1) & 1], ((j - 1) >> 1) & 1);  // S of tile j-1 done: K free
         if (!ok) break;
@@ -472,7 +481,10 @@ static int launch_prefill_umma(const void* q, int64_t q_stride_t, int64_t q_stri
   if (!p.err) return fail(ERR_RUNTIME, "%s: no error flag", what);
   p.scale_log2 = (1.0f / sqrtf(static_cast<float>(HEAD_DIM))) * PU_LOG2E;
   const dim3 grid((max_seqlen + PU_BQ - 1) / PU_BQ, num_kv_heads, batch);
-  varlen_causal_umma_kernel<FUSED><<<grid, PU_THREADS, PU_SMEM, stream>>>(map_q, map_k, map_v, p);
+  // the fused form starts behind its own rope + scatter kernel while that one still runs (see the K producer)
+  if (launch_pdl(FUSED, varlen_causal_umma_kernel<FUSED>, grid, dim3(PU_THREADS), PU_SMEM, stream, map_q, map_k, map_v, p) !=
+      cudaSuccess)
+    return fail(ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(cudaGetLastError()));
   return check_launch(what);
 }
 

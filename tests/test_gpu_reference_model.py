@@ -4,6 +4,7 @@ Three runs see the same weights and the same inputs at every step ("teacher forc
 tokens the reference produced at step t-1):
   1. the reference runner on the reference's own Triton kernels          (child process, baseline/run_reference.py)
   2. the SAME reference runner on this package's drop-in operators        (child process: both sets register wy_lib::*)
+  2b. this package's opt-in subclass of the reference runner (b200attn/fast_runner.py: fused entry points)
   3. this package's fused engine (b200attn/engine.py)                     (this process)
 plus an fp32 recomputation of the whole model (the oracle, eager PyTorch) as the yardstick for what bf16 noise does to
 this random-init model (N(0, 0.02) weights: near-flat logits, top-2 gaps often below the noise of ANY bf16 engine).
@@ -47,7 +48,10 @@ def runs(tmp_path_factory):
         pytest.skip("the reference's Triton kernels did not run here: " + (res.stderr.strip().splitlines() or ["?"])[-1][:300])
     res = run_child("b200", shim_file, teacher=ref_file)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
-    return torch.load(ref_file), torch.load(shim_file)
+    fast_file = tmp / "fast.pt"
+    res = run_child("b200-fast", fast_file, teacher=ref_file)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    return torch.load(ref_file), torch.load(shim_file), torch.load(fast_file)
 
 
 def harness():
@@ -76,7 +80,7 @@ def truth(runs):
     """fp32 recomputation of the whole model (oracle/reference_model.py, eager PyTorch, run on the GPU because the
     full-size model takes minutes on host cores) over the teacher-forced token sequences: hidden [S+1, B, hidden] and
     logits statistics.  It shares nothing with the engines: no caches, pages, chunks or bf16 intermediates."""
-    ref, _ = runs
+    ref = runs[0]
     H = harness()
     from b200attn import engine as E
     from oracle import reference_model as M
@@ -138,13 +142,21 @@ def check(out):
 
 
 def test_dropin_operators_under_the_reference_runner(runs, truth):
-    ref, shim = runs
+    ref, shim, _ = runs
     check(compare("reference runner on the drop-in CUDA operators vs on its Triton kernels (teacher-forced)",
                   shim["tokens"], shim["hidden"], ref, truth))
 
 
+def test_fast_runner_subclass_against_the_reference_runner(runs, truth):
+    """The opt-in subclass of the reference runner (fused decode / packed-prefill entry points, chunk-64 kernel with
+    cu_seqlens for the packed Gated-DeltaNet prefill) under the same comparison."""
+    ref, _, fast = runs
+    check(compare("b200attn.fast_runner subclass of the reference runner vs the reference runner on Triton "
+                  "(teacher-forced)", fast["tokens"], fast["hidden"], ref, truth))
+
+
 def test_fused_engine_against_the_reference_runner(runs, truth):
-    ref, _ = runs
+    ref = runs[0]
     from b200attn import engine as E
     eng = E.Engine(E.ModelConfig(), engine_weights(truth["tensors"]), BATCH, PROMPT + STEPS + 8, DEV)
     teacher = ref["tokens"].to(DEV)
