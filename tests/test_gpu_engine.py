@@ -47,16 +47,21 @@ def test_graph_decode_equals_eager(small):
 
 
 def test_fused_glue_equals_eager_glue(small):
-    """The single-launch row-wise kernels against the same step with eager PyTorch glue: the operators agree to one
-    bf16 ulp, so the greedy tokens may differ only at near-ties (and then diverge: compare up to the first flip)."""
+    """The single-launch row-wise kernels against the same model with eager PyTorch glue, TEACHER-FORCED: the eager-glue
+    engine is fed the tokens the fused engine produced, so one flipped near-tie cannot cascade.  The operators agree to
+    one bf16 ulp; with random-init logits a few per cent of the decisions are near-ties that such a difference flips
+    (the fp32 test below measures the noise), an operator error would flip most of them."""
     E, cfg, weights, prompts = small
     fused, _ = _generate(E, cfg, weights, prompts, STEPS, graph=False, fused_glue=True)
-    eager, _ = _generate(E, cfg, weights, prompts, STEPS, graph=False, fused_glue=False)
-    same_prefix = [int((fused[b] != eager[b]).int().cumsum(0).eq(0).sum()) for b in range(fused.shape[0])]
-    print("tokens identical up to position", same_prefix, "of", fused.shape[1])
-    # random-init logits have top-2 gaps below bf16 noise every few dozen tokens (the fp32 test below measures it), so a
-    # sequence usually flips somewhere; what an operator error would show is flips right at the start
-    assert min(same_prefix) >= 4 and sum(same_prefix) >= 0.6 * fused.numel()
+    eng = E.Engine(cfg, weights, len(prompts), max(PROMPT_LENGTHS) + STEPS + 2, DEV, page_seed=7, fused_glue=False)
+    got = [eng.prefill(prompts).cpu()]
+    for s in range(STEPS):
+        eng.tok.copy_(fused[:, s].to(DEV))
+        got.append(eng.step().cpu().clone())
+    got = torch.stack(got, dim=1)
+    agree = (got == fused).float().mean().item()
+    print(f"teacher-forced agreement fused glue vs eager glue: {agree:.3f} over {got.numel()} decisions")
+    assert agree >= 0.85
 
 
 def test_greedy_tokens_match_fp32_recomputation(small, monkeypatch):
