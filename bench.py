@@ -800,7 +800,7 @@ def run_sweep(ops, ws, device, peak, steps):
 
 
 def run_gemm_sweep(ops, device, peak, steps):
-    """The decode-step projections of BASELINE config 5 (32 sequences, hidden 1024): weight-streaming GEMMs, bound by the
+    """The decode-step projections of the whole-model workload (32 sequences, hidden 1024): weight-streaming GEMMs, bound by the
     weight bytes.  Weights rotate over enough copies that no call finds its matrix in L2; the cuBLAS time of the same
     product (plus torch.argmax for the LM head) is reported beside each."""
     import torch.nn.functional as F

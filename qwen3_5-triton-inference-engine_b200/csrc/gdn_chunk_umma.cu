@@ -14,8 +14,9 @@
 //   S^T [dv x dk]  += delta'^T k           (accumulated in place in tensor memory after the decay scaling)
 // fp32 operands (S, w, delta, A) are fed as a bf16 pair hi + lo with the three cross products hi*hi, hi*lo, lo*hi
 // (two when the other operand is exact), which keeps about 16 mantissa bits: the same order of accuracy as the
-// reference's 3xTF32 products.  The two triangular systems are solved exactly in fp32 on the CUDA cores, one thread
-// per right-hand-side column (128 columns of v, 128 of k), with L broadcast from shared memory.
+// reference's 3xTF32 products.  P = (I + L)^-1 is formed in fp32 on the CUDA cores by a blocked inverse (16 x 16 diagonal
+// blocks by forward substitution, two levels of P21 = -P22 L21 P11 with register tiles); the classical
+// delta = P beta (v - e^G k S) then needs P only as the right-hand operand of one tensor-core product, so w never exists.
 // Q/K/V chunks arrive by tensor-map TMA (128-byte swizzle) straight from the strided [T, H, 128] activations.
 #include "b200_attn.h"
 #include "umma.cuh"
