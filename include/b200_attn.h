@@ -219,6 +219,13 @@ int b200_gdn_recurrent_decode(const void* q, int64_t q_stride_b, int64_t q_strid
                               int64_t out_stride_h, int32_t batch, int32_t num_heads, int32_t key_dim,
                               int32_t value_dim, b200_stream_t stream);
 
+/* Diagnostic: pins the kernel form b200_gdn_recurrent_decode takes, process-wide (0 = chosen from the sizes, the
+ * default; 1 = one CTA per head with the state in registers; 2 = one warp per 32 value columns; 3 = persistent CTAs,
+ * eight per SM, that stream [128 x 16] boxes of the state through a shared-memory ring of three with tensor-map TMA
+ * copies issued by a copy warp).  A form whose layout rules do not hold for a call falls back to 1.  For tests and tuning: every form computes the same step (fp32 summation order
+ * differs).  No counterpart in the reference. */
+int b200_gdn_recurrent_decode_form(int32_t form);
+
 /* Token-serial recurrence over a packed buffer, zero state at every cu_seqlens[b]; cu_seqlens may be NULL
  * (one sequence of total_tokens).  state [batch,H,128,128] fp32 contiguous (written), out [T,H,128] bf16.
  * Replaces wy_lib::gdn_recurrent_prefill_sequential, triton_kernels/gdn_recurrent_prefill.py:1050-1145

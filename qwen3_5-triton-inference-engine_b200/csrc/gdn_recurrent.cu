@@ -9,13 +9,18 @@
 // bytes per state row).  Decode streams the 64 KiB state once in and once out (HBM-bound); prefill keeps it
 // in registers across the whole sequence (fp32-FMA-bound).
 //
-// Decode exists in two forms.  The streaming form (gdn_decode_stream_kernel) is persistent: one CTA per SM walks its
-// (sequence, head) items with a ring of three 64 KiB shared-memory buffers - the TMA engine loads the state of item
-// n+1 (one bulk copy) while item n is updated and the state of item n-1 is being stored (one bulk copy), so the HBM
-// pipe never drains between items.  It needs contiguous, 16-byte aligned 64 KiB state blocks; the per-CTA form
-// (gdn_decode_kernel) takes any strides.
+// Decode exists in three forms, chosen by size (measured on B200, fractions of the measured copy bandwidth):
+//   * gdn_decode_slice_kernel: CTA = one warp = 32 columns of one head, the column in registers.  Best for very many
+//     heads (4096 heads: 0.99) and in the gap around one to three heads per SM.
+//   * gdn_decode_ring_kernel: persistent CTAs with a ring of [128 x 16] boxes moved by tensor-map TMA and a copy warp.
+//     Best (or level) from one head up to about two thousand (512 heads: 0.78, 1024: 0.88, 2048: 0.94): several small
+//     rings per SM stagger the load, update and store phases that one wave of register-resident heads runs in lockstep.
+//     Needs the dense [B, H, 128, 128] state.
+//   * gdn_decode_kernel: CTA = one head, any strides and alignments; the fallback.
 #include "b200_attn.h"
-#include "common.cuh"
+#include "umma.cuh"
+
+#include <atomic>
 
 namespace b200 {
 
@@ -216,101 +221,239 @@ gdn_decode_fused_kernel(const __nv_bfloat16* fused, int64_t fused_stride,  // no
   out[(static_cast<int64_t>(b) * heads + h) * GDN_D + t] = __float2bfloat16_rn(x * rs * wv * (zv / (1.0f + expf(-zv))));
 }
 
-// ---------------------------------------------------------------------------------- streaming decode (persistent)
-constexpr int GS_STAGES = 3;
-constexpr int GS_STATE_BYTES = GDN_D * GDN_D * 4;          // 64 KiB
-constexpr int GS_SMEM = GS_STAGES * GS_STATE_BYTES + 128;  // + alignment slack
-
-struct GdnStreamParams {
+// ------------------------------------------------------------- streaming decode over column boxes (tensor-map TMA)
+// The persistent pipeline with a finer grain and a copy warp of its own.  An item is a [128 rows x COLS columns] fp32 box
+// of one head's state; ONE tensor-map TMA copy brings it into a ring of STAGES buffers and one takes it out.  A CTA is
+// THREADS compute threads plus one copy warp: thread t of the compute part owns rows (t / COLS) * ROWS ... of column
+// t % COLS, the row groups of a column meet through shared memory for k^T S and q^T S, and the copy warp alone waits
+// for stores to drain before it reuses a buffer, so no compute thread ever stalls on a copy that is not its own item.
+// Several such CTAs share an SM (their rings together hold most of its shared memory), which staggers the load,
+// update and store phases that a single wave of register-resident heads runs in lockstep.  Needs the dense
+// [B, H, 128, 128] state.
+struct GdnRingParams {
   const __nv_bfloat16 *q, *k, *v;
   const float *beta, *g;
-  float* state;
   __nv_bfloat16* out;
-  int64_t q_b, q_h, k_b, k_h, v_b, v_h, be_b, be_h, g_b, g_h, s_b, s_h, o_b, o_h;
+  int64_t q_b, q_h, k_b, k_h, v_b, v_h, be_b, be_h, g_b, g_h, o_b, o_h;
   int* err;
-  int items, heads;
+  int items, heads;  // items = batch * heads * (128 / COLS)
 };
 
-__global__ void __launch_bounds__(GDN_THREADS, 1)
-gdn_decode_stream_kernel(const __grid_constant__ GdnStreamParams p) {
-  extern __shared__ __align__(128) uint8_t gs_raw[];
-  __shared__ uint64_t full[GS_STAGES];
+__device__ __forceinline__ void tma_load_2d(void* dst_smem, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst_smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, const void* src_smem) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(src_smem)), "r"(c0), "r"(c1)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+template <int COLS, int THREADS, int STAGES>
+constexpr int gdn_ring_smem() { return STAGES * GDN_D * COLS * 4 + 128; }
+
+template <int COLS, int THREADS, int STAGES, int CTAS>
+__global__ void __launch_bounds__(THREADS + 32, CTAS)
+gdn_decode_ring_kernel(const __grid_constant__ GdnRingParams p, const __grid_constant__ CUtensorMap map_state) {
+  constexpr int GROUPS = THREADS / COLS, ROWS = GDN_D / GROUPS, PER_HEAD = GDN_D / COLS, BOX = GDN_D * COLS;
+  static_assert(THREADS >= GDN_D && THREADS % COLS == 0 && ROWS % 4 == 0, "ring kernel shape");
+  extern __shared__ __align__(128) uint8_t ring_raw[];
+  __shared__ uint64_t full[STAGES], done[STAGES];
   __shared__ __align__(16) float kf[GDN_D];
   __shared__ __align__(16) float qf[GDN_D];
-  float* bufs = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(gs_raw) + 127) & ~uintptr_t(127));
+  __shared__ float vf[COLS];
+  __shared__ float red[2][GROUPS][COLS];  // [k^T S | q^T S][row group][column]
+  __shared__ int failed;
+  float* bufs = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(ring_raw) + 127) & ~uintptr_t(127));
   const int t = threadIdx.x;
-  const int my_items = (p.items - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int stride = static_cast<int>(gridDim.x), first = static_cast<int>(blockIdx.x);
+  const int my_items = (p.items - first + stride - 1) / stride;
   if (t == 0) {
-    for (int s = 0; s < GS_STAGES; ++s) mbar_init(&full[s], 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&done[s], THREADS);
+    }
+    failed = 0;
     mbar_fence_init();
+    prefetch_tensormap(&map_state);
   }
   __syncthreads();
-  auto state_of = [&](int n) {
-    const int item = blockIdx.x + n * gridDim.x;
-    return p.state + static_cast<int64_t>(item / p.heads) * p.s_b + static_cast<int64_t>(item % p.heads) * p.s_h;
-  };
-  auto load = [&](int n) {  // thread 0 only
-    mbar_expect_tx(&full[n % GS_STAGES], GS_STATE_BYTES);
-    bulk_g2s(bufs + (n % GS_STAGES) * (GDN_D * GDN_D), state_of(n), GS_STATE_BYTES, &full[n % GS_STAGES]);
-  };
-  if (t == 0) {
-    load(0);
-    if (my_items > 1) load(1);
+
+  if (t >= THREADS) {
+    // ------------------------------------------------------------------------------------------- copy warp
+    if (t != THREADS) return;
+    auto load = [&](int n) {
+      const int item = first + n * stride;
+      mbar_expect_tx(&full[n % STAGES], BOX * 4);
+      tma_load_2d(bufs + (n % STAGES) * BOX, &map_state, (item % PER_HEAD) * COLS, (item / PER_HEAD) * GDN_D,
+                  &full[n % STAGES]);
+    };
+    const int ahead = min(my_items, STAGES);
+    for (int n = 0; n < ahead; ++n) load(n);
+    int loaded = ahead, n = 0;
+    for (; n < my_items; ++n) {
+      if (!mbar_wait_bounded(&done[n % STAGES], (n / STAGES) & 1)) break;  // the compute part gave up (or is lost)
+      const int item = first + n * stride;
+      tma_store_2d(&map_state, (item % PER_HEAD) * COLS, (item / PER_HEAD) * GDN_D, bufs + (n % STAGES) * BOX);
+      if (n + STAGES < my_items) {
+        bulk_wait_read();  // the store just issued has read its buffer: the box of item n + STAGES may land there
+        load(n + STAGES);
+        loaded = n + STAGES + 1;
+      }
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all stores complete before the CTA ends
+    if (n < my_items) {
+      atomicExch(p.err, 1);
+      // boxes that were requested but never consumed may still be landing in this CTA's shared memory
+      for (int m = n; m < loaded; ++m) mbar_wait_bounded(&full[m % STAGES], (m / STAGES) & 1, 1u << 12);
+    }
+    return;
   }
+
+  // ------------------------------------------------------------------------------------------- compute part
+  // Row group rg owns rows rg * ROWS + i; with boxes narrower than a warp two row groups share a warp and blocked rows
+  // would put them on the same banks, so there the rows are dealt round-robin (row i * GROUPS + rg) and kf / qf are
+  // stored in the matching order.
+  constexpr bool DEALT = COLS < 32;
+  const int c = t % COLS, rg = t / COLS;
+  const int KSLOT = DEALT ? (t % GROUPS) * ROWS + t / GROUPS : t;
   // per-item operands of the NEXT item are fetched while the current one is computed
   float kn = 0.f, qn = 0.f, vn = 0.f, bn = 0.f, gn = 0.f;
   auto fetch = [&](int n) {
-    const int item = blockIdx.x + n * gridDim.x, b = item / p.heads, h = item % p.heads;
-    kn = __bfloat162float(p.k[b * p.k_b + h * p.k_h + t]);
-    qn = __bfloat162float(p.q[b * p.q_b + h * p.q_h + t]);
-    vn = __bfloat162float(p.v[b * p.v_b + h * p.v_h + t]);
+    const int item = first + n * stride, head = item / PER_HEAD, b = head / p.heads, h = head % p.heads;
+    if (t < GDN_D) {
+      kn = __bfloat162float(p.k[b * p.k_b + h * p.k_h + t]);
+      qn = __bfloat162float(p.q[b * p.q_b + h * p.q_h + t]);
+    }
+    if (rg == 0) vn = __bfloat162float(p.v[b * p.v_b + h * p.v_h + (item % PER_HEAD) * COLS + c]);
     bn = p.beta[b * p.be_b + h * p.be_h];
     gn = p.g[b * p.g_b + h * p.g_h];
   };
   if (my_items > 0) fetch(0);
-  bool ok = true;
-  int n_done = 0;  // items whose state was loaded, updated and handed to the store engine
-  for (int n = 0; n < my_items && ok; ++n) {
-    const int item = blockIdx.x + n * gridDim.x, b = item / p.heads, h = item % p.heads;
-    float* buf = bufs + (n % GS_STAGES) * (GDN_D * GDN_D);
-    const float eg = __expf(gn), bt = bn, vv = vn;
-    __syncthreads();  // kf / qf of the previous item are no longer read
-    kf[t] = kn;
-    qf[t] = qn;
+  for (int n = 0; n < my_items; ++n) {
+    const int item = first + n * stride, head = item / PER_HEAD, b = head / p.heads, h = head % p.heads;
+    float* buf = bufs + (n % STAGES) * BOX;
+    const float eg = __expf(gn), bt = bn;
+    // kf / qf / vf / red of the previous item are no longer read: every compute thread has passed that item's last
+    // barrier, and the reads after it (red[1] for the output) are separated from the writes below by two more
+    if (t < GDN_D) {
+      kf[KSLOT] = kn;
+      qf[KSLOT] = qn;
+    }
+    if (rg == 0) vf[c] = vn;
     if (n + 1 < my_items) fetch(n + 1);
-    const bool mine = mbar_wait_bounded(&full[n % GS_STAGES], (n / GS_STAGES) & 1);
-    ok = __syncthreads_and(mine);  // kf / qf visible; the CTA agrees on whether the state arrived
-    if (!ok) break;                // a lost copy: this item's state and output stay untouched
-    float s[GDN_D];
+    if (!mbar_wait_bounded(&full[n % STAGES], (n / STAGES) & 1)) failed = 1;
+    named_barrier(1, THREADS);  // kf / qf / vf visible; the compute part agrees on whether the box arrived
+    if (*reinterpret_cast<volatile int*>(&failed)) break;  // a lost copy: this item's state and output stay untouched
+    float s[ROWS];
+    float* col = DEALT ? buf + rg * COLS + c : buf + (rg * ROWS) * COLS + c;
+    constexpr int RSTEP = DEALT ? GROUPS * COLS : COLS;  // floats between consecutive rows of this thread
+    const float* kh = kf + rg * ROWS;
+    const float* qh = qf + rg * ROWS;
+    float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
 #pragma unroll
-    for (int i = 0; i < GDN_D; ++i) s[i] = buf[i * GDN_D + t];
-    float o;
-    gdn_token_update(s, kf, qf, eg, bt, vv, o);
+    for (int i = 0; i < ROWS; i += 4) {
+      const float4 k4 = *reinterpret_cast<const float4*>(kh + i);
+      s[i] = col[i * RSTEP] * eg;
+      s[i + 1] = col[(i + 1) * RSTEP] * eg;
+      s[i + 2] = col[(i + 2) * RSTEP] * eg;
+      s[i + 3] = col[(i + 3) * RSTEP] * eg;
+      m0 = fmaf(k4.x, s[i], m0);
+      m1 = fmaf(k4.y, s[i + 1], m1);
+      m2 = fmaf(k4.z, s[i + 2], m2);
+      m3 = fmaf(k4.w, s[i + 3], m3);
+    }
+    red[0][rg][c] = (m0 + m1) + (m2 + m3);
+    named_barrier(1, THREADS);
+    float mem = 0.f;
 #pragma unroll
-    for (int i = 0; i < GDN_D; ++i) buf[i * GDN_D + t] = s[i];
-    p.out[b * p.o_b + h * p.o_h + t] = __float2bfloat16_rn(o);
-    fence_proxy_async();  // generic-proxy stores before the bulk store reads them
-    __syncthreads();
-    if (t == 0) {
-      if (n + 2 < my_items) {
-        // buffer (n+2) % 3 holds item n-1, whose store had this item's whole update to finish reading it
-        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        load(n + 2);
-      }
-      bulk_s2g(state_of(n), buf, GS_STATE_BYTES);
+    for (int r = 0; r < GROUPS; ++r) mem += red[0][r][c];
+    const float delta = bt * (vf[c] - mem);
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+    for (int i = 0; i < ROWS; i += 4) {
+      const float4 k4 = *reinterpret_cast<const float4*>(kh + i);
+      const float4 q4 = *reinterpret_cast<const float4*>(qh + i);
+      s[i] = fmaf(k4.x, delta, s[i]);
+      s[i + 1] = fmaf(k4.y, delta, s[i + 1]);
+      s[i + 2] = fmaf(k4.z, delta, s[i + 2]);
+      s[i + 3] = fmaf(k4.w, delta, s[i + 3]);
+      o0 = fmaf(q4.x, s[i], o0);
+      o1 = fmaf(q4.y, s[i + 1], o1);
+      o2 = fmaf(q4.z, s[i + 2], o2);
+      o3 = fmaf(q4.w, s[i + 3], o3);
+      col[i * RSTEP] = s[i];
+      col[(i + 1) * RSTEP] = s[i + 1];
+      col[(i + 2) * RSTEP] = s[i + 2];
+      col[(i + 3) * RSTEP] = s[i + 3];
     }
-    n_done = n + 1;
-  }
-  if (t == 0) {
-    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all stores complete before the CTA ends
-    if (!ok) {
-      atomicExch(p.err, 1);
-      // the loads of items n_done and n_done + 1 may still be in flight into this CTA's shared memory: give them a
-      // bounded time to land before the CTA (and its shared memory) goes away
-      for (int m = n_done; m < min(n_done + 2, my_items); ++m)
-        mbar_wait_bounded(&full[m % GS_STAGES], (m / GS_STAGES) & 1, 1u << 12);
+    red[1][rg][c] = (o0 + o1) + (o2 + o3);
+    fence_proxy_async();          // generic-proxy stores of the box before the TMA store reads them
+    mbar_arrive(&done[n % STAGES]);  // the copy warp stores the box once all THREADS have arrived
+    named_barrier(1, THREADS);
+    if (rg == 0) {
+      float o = 0.f;
+#pragma unroll
+      for (int r = 0; r < GROUPS; ++r) o += red[1][r][c];
+      p.out[b * p.o_b + h * p.o_h + (item % PER_HEAD) * COLS + c] = __float2bfloat16_rn(o);
     }
   }
+}
+
+// fp32 map over the states seen as a matrix [batch * heads * 128 rows][128 columns]; a box is `cols` columns x 128 rows
+static bool encode_state_map(CUtensorMap* map, const float* state, int64_t rows, int cols) {
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static std::atomic<EncodeFn> cached{nullptr};
+  EncodeFn encode = cached.load();
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || fn == nullptr) {
+      cudaGetLastError();
+      return false;
+    }
+    encode = reinterpret_cast<EncodeFn>(fn);
+    cached.store(encode);
+  }
+  const cuuint64_t dims[2] = {GDN_D, static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {GDN_D * 4};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(cols), GDN_D};
+  const cuuint32_t es[2] = {1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(state), dims, strides, box, es,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Which form b200_gdn_recurrent_decode takes: 0 = chosen from the sizes; 1 one CTA per head, 2 one-warp slices, 3 ring of
+// three [128 x 16] boxes, eight CTAs per SM (a form whose layout rules do not hold falls back to 1).
+static std::atomic<int> g_gdn_decode_form{0};
+
+template <int COLS, int THREADS, int STAGES, int CTAS>
+static int launch_ring(GdnRingParams p, const float* state, int heads_total, cudaStream_t stream) {
+  constexpr int SMEM = gdn_ring_smem<COLS, THREADS, STAGES>();
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(gdn_decode_ring_kernel<COLS, THREADS, STAGES, CTAS>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+      return fail(ERR_RUNTIME, "gdn_recurrent_decode: cannot raise dynamic shared memory to %d", SMEM);
+    configured[dev] = true;
+  }
+  CUtensorMap map;
+  if (!encode_state_map(&map, state, static_cast<int64_t>(heads_total) * GDN_D, COLS))
+    return fail(ERR_RUNTIME, "gdn_recurrent_decode: cannot encode the state tensor map");
+  p.items = heads_total * (GDN_D / COLS);
+  const int slots = CTAS * sm_count();
+  const int grid = p.items < slots ? p.items : slots;
+  gdn_decode_ring_kernel<COLS, THREADS, STAGES, CTAS><<<grid, THREADS + 32, SMEM, stream>>>(p, map);
+  return OK;
 }
 
 constexpr int SEQ_TILE = 16;  // tokens staged in shared memory per step of the prefill loop
@@ -373,44 +516,40 @@ extern "C" int b200_gdn_recurrent_decode(const void* q, int64_t q_stride_b, int6
   B200_REQUIRE(batch > 0 && num_heads > 0, "gdn_recurrent_decode: empty shape");
   B200_REQUIRE(key_dim == GDN_D && value_dim == GDN_D, "gdn_recurrent_decode: key/value dim must be %d (got %d/%d)",
                GDN_D, key_dim, value_dim);
-  const bool blocks_ok = (reinterpret_cast<uintptr_t>(state) % 16 == 0) && state_stride_b % 4 == 0 && state_stride_h % 4 == 0 &&
-                         (state_stride_h >= GDN_D * GDN_D || num_heads == 1) && state_stride_b >= state_stride_h;
-  // The streaming form pays off once every SM has several items to pipeline; below that the per-CTA form (two CTAs
-  // per SM, no start-up ring) is as fast or faster (measured: equal at 256 x 16 items, 10 % behind at 32 x 16).
-  if (blocks_ok && batch * num_heads >= 6 * sm_count()) {
-    static bool configured[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-      if (cudaFuncSetAttribute(gdn_decode_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GS_SMEM) != cudaSuccess)
-        return fail(ERR_RUNTIME, "gdn_recurrent_decode: cannot raise dynamic shared memory to %d", GS_SMEM);
-      configured[dev] = true;
-    }
-    GdnStreamParams p;
+  const bool dense = (reinterpret_cast<uintptr_t>(state) % 128 == 0) && state_stride_h == GDN_D * GDN_D &&
+                     state_stride_b == static_cast<int64_t>(num_heads) * GDN_D * GDN_D;
+  const bool slices_ok = (reinterpret_cast<uintptr_t>(q) % 8 == 0) && (reinterpret_cast<uintptr_t>(k) % 8 == 0) &&
+                         q_stride_b % 4 == 0 && q_stride_h % 4 == 0 && k_stride_b % 4 == 0 && k_stride_h % 4 == 0;
+  const int items = batch * num_heads;
+  int form = g_gdn_decode_form.load();
+  if (form == 0) {
+    // Measured on B200 (16 heads per sequence, batch 1 ... 256): the ring wins or ties up to sixteen heads per SM
+    // (batch 128), the one-warp slices beyond (batch 256: 0.99 of the copy bandwidth against 0.87).
+    form = (dense && items <= 16 * sm_count()) ? 3 : (slices_ok ? 2 : 1);
+  }
+  if ((form >= 3 && !dense) || (form == 2 && !slices_ok)) form = 1;
+  if (form >= 3) {
+    GdnRingParams p;
     p.q = static_cast<const __nv_bfloat16*>(q);
     p.k = static_cast<const __nv_bfloat16*>(k);
     p.v = static_cast<const __nv_bfloat16*>(v);
     p.beta = beta;
     p.g = g;
-    p.state = state;
     p.out = static_cast<__nv_bfloat16*>(out);
     p.q_b = q_stride_b; p.q_h = q_stride_h; p.k_b = k_stride_b; p.k_h = k_stride_h; p.v_b = v_stride_b; p.v_h = v_stride_h;
     p.be_b = beta_stride_b; p.be_h = beta_stride_h; p.g_b = g_stride_b; p.g_h = g_stride_h;
-    p.s_b = state_stride_b; p.s_h = state_stride_h; p.o_b = out_stride_b; p.o_h = out_stride_h;
+    p.o_b = out_stride_b; p.o_h = out_stride_h;
     p.err = wait_timeout_flag();
     if (!p.err) return fail(ERR_RUNTIME, "gdn_recurrent_decode: no error flag");
-    p.items = batch * num_heads;
     p.heads = num_heads;
-    int grid = p.items < sm_count() ? p.items : sm_count();
-    gdn_decode_stream_kernel<<<grid, GDN_THREADS, GS_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+    const cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const int rc = launch_ring<16, 128, 3, 8>(p, state, items, st);
+    if (rc != OK) return rc;
     return check_launch("gdn_recurrent_decode");
   }
-  // Few items (less than about four rounds of whole heads per SM): the one-warp slices keep more state in flight per SM
-  // and shorten the last wave; q and k rows must then allow 8-byte loads.
-  const bool slices_ok = (reinterpret_cast<uintptr_t>(q) % 8 == 0) && (reinterpret_cast<uintptr_t>(k) % 8 == 0) &&
-                         q_stride_b % 4 == 0 && q_stride_h % 4 == 0 && k_stride_b % 4 == 0 && k_stride_h % 4 == 0;
-  if (slices_ok && batch * num_heads < 8 * sm_count()) {
-    gdn_decode_slice_kernel<<<static_cast<unsigned>(batch) * num_heads * (GDN_D / GDN_SLICE), GDN_SLICE, 0,
+  // the one-warp slices keep the SMs evenly loaded and shorten the last wave; q and k rows must allow 8-byte loads
+  if (form == 2) {
+    gdn_decode_slice_kernel<<<static_cast<unsigned>(items) * (GDN_D / GDN_SLICE), GDN_SLICE, 0,
                               reinterpret_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(q), q_stride_b, q_stride_h, static_cast<const __nv_bfloat16*>(k), k_stride_b,
         k_stride_h, static_cast<const __nv_bfloat16*>(v), v_stride_b, v_stride_h, beta, beta_stride_b, beta_stride_h, g,
@@ -424,6 +563,12 @@ extern "C" int b200_gdn_recurrent_decode(const void* q, int64_t q_stride_b, int6
       g_stride_b, g_stride_h, state, state_stride_b, state_stride_h, static_cast<__nv_bfloat16*>(out), out_stride_b,
       out_stride_h, num_heads);
   return check_launch("gdn_recurrent_decode");
+}
+
+extern "C" int b200_gdn_recurrent_decode_form(int32_t form) {
+  B200_REQUIRE(form >= 0 && form <= 3, "gdn_recurrent_decode_form: form must be 0..3 (got %d)", form);
+  g_gdn_decode_form.store(form);
+  return OK;
 }
 
 extern "C" int b200_gdn_decode_fused(const void* fused, int64_t fused_stride, void* conv_state, const void* weight4,

@@ -139,6 +139,36 @@ def test_gdn_decode_persistent_kernel_vs_oracle(ops, batch):
     assert maxabs(sd, ref_state2) <= 2e-5
 
 
+@pytest.mark.parametrize("form", [0, 1, 2, 3])
+@pytest.mark.parametrize("batch", [3, 40])
+def test_gdn_decode_every_kernel_form(ops, form, batch):
+    """The operator has three kernel forms (one CTA per head, one warp per 32 columns, a persistent ring of tensor-map
+    TMA boxes) and picks by size (form 0); here each is pinned in turn and checked against the oracle, two steps in a
+    row, with the strided `v` view of the runner."""
+    from b200attn import _lib
+    heads = 16
+    gen = torch.Generator().manual_seed(900 + batch)
+    q, k, v, beta, g = gdn_inputs(batch, heads, gen, v_row_stride=3 * heads * 128)
+    state = torch.randn(batch, heads, 128, 128, generator=gen) * 0.1
+    sd = state.to(DEV)
+    vd = torch.zeros(batch, 6144, dtype=torch.bfloat16, device=DEV)
+    vd[:, 6144 - heads * 128:] = v.reshape(batch, heads * 128).to(DEV)
+    v_view = vd[:, 6144 - heads * 128:].view(batch, heads, 128)
+    _lib.call("b200_gdn_recurrent_decode_form", form)
+    try:
+        out = ops.gdn_recurrent_decode(q.to(DEV), k.to(DEV), v_view, beta.to(DEV), g.to(DEV), sd)
+        ref_state, ref_out = _flat_step(state, q, k, v, beta, g)
+        assert maxabs(out, ref_out) <= TOL and maxabs(sd, ref_state) <= 1e-5
+        q2, k2, v2, beta2, g2 = gdn_inputs(batch, heads, gen)
+        out2 = ops.gdn_recurrent_decode(q2.to(DEV), k2.to(DEV), v2.to(DEV), beta2.to(DEV), g2.to(DEV), sd)
+        ref_state2, ref_out2 = _flat_step(ref_state, q2, k2, v2, beta2, g2)
+        assert maxabs(out2, ref_out2) <= TOL and maxabs(sd, ref_state2) <= 2e-5
+    finally:
+        _lib.call("b200_gdn_recurrent_decode_form", 0)
+    torch.cuda.synchronize()
+    no_timeouts()
+
+
 def test_config4_gdn_layer_prefill_then_512_decode_steps(ops):
     """Chunk-64 prefill over 32 packed prompts of 128 tokens on the tensor cores against the oracle's chunk pipeline,
     then 512 single-token steps at B=32 from that state against the oracle recurrence (fresh inputs per step, seed 3):
