@@ -130,12 +130,12 @@ __device__ __forceinline__ void norm_row8(uint32_t (&w)[4], const __nv_bfloat16*
 // Partial RoPE of the row at position pos: dims [0, half) pair with [half, 2*half), angles = float(pos) * inv_freq[d] in
 // fp32, full-range sincosf, result rounded to bf16 -- the arithmetic of triton_kernels/partial_rope.py:65-113.  Lanes
 // [0, half/8) hold the first halves, the next half/8 lanes their partners; the other lanes pass through.
-__device__ __forceinline__ void rope_row8(uint32_t (&w)[4], const FusedDecodeParams& p, int64_t pos, int lane) {
-  const int half = p.rotary_half;  // <= 32: one angle per lane
+__device__ __forceinline__ void rope_row8(uint32_t (&w)[4], int half, const float* inv_freq, int64_t pos, int lane) {
+  // half <= 32: one angle per lane; inv_freq may be a shared-memory copy
   if (half == 0) return;
   // the warp computes the `half` angles once, one sincosf per lane, and hands them round by shuffles
   float sn = 0.f, cs = 1.f;
-  if (lane < half) sincosf(static_cast<float>(pos) * p.inv_freq[lane], &sn, &cs);
+  if (lane < half) sincosf(static_cast<float>(pos) * inv_freq[lane], &sn, &cs);
   const int lanes_half = half / 8;
   const bool in_rot = lane < 2 * lanes_half;
   const bool first = lane < lanes_half;
@@ -157,36 +157,71 @@ __device__ __forceinline__ void rope_row8(uint32_t (&w)[4], const FusedDecodePar
   }
 }
 
+// Small read-only operands every CTA keeps in shared memory: a global load issued while the page copies saturate the
+// memory system takes microseconds, and these are needed at every segment boundary.
+struct FusedDecodeTables {
+  float inv_freq[32];
+  __align__(16) __nv_bfloat16 q_norm_w[HEAD_DIM];
+  __align__(16) __nv_bfloat16 k_norm_w[HEAD_DIM];
+  __align__(16) uint8_t new_rows[2 * HEAD_DIM * 2];  // k_new row | v_new row of the segment whose end is in this piece
+};
+
 // Stage the 4 Q heads of one segment in shared memory, normalised (optional) and rotated: warps 0-3 take one head
-// each.  The caller synchronises.
-__device__ __forceinline__ void stage_q(__nv_bfloat16* buf, const FusedDecodeParams& p, int b, int h, int pos_b, int tid) {
+// each.  The caller synchronises.  The row is fetched by load_q_row() so that the caller can put the load in front of
+// a burst of page copies (a small load issued behind them waits for the whole burst) and finish the row later.
+__device__ __forceinline__ uint4 load_q_row(const FusedDecodeParams& p, int b, int h, int tid) {
+  if (tid >= GROUP * 32) return make_uint4(0, 0, 0, 0);
+  const int head = tid >> 5, lane = tid & 31;
+  return *reinterpret_cast<const uint4*>(p.q + b * p.q_b + (h * GROUP + head) * p.q_h + lane * 8);
+}
+__device__ __forceinline__ void stage_q_row(__nv_bfloat16* buf, const FusedDecodeParams& p, const FusedDecodeTables& tb,
+                                            const uint4& raw, int pos_b, int tid) {
   if (tid >= GROUP * 32) return;
   const int head = tid >> 5, lane = tid & 31;
-  const uint4 raw = *reinterpret_cast<const uint4*>(p.q + b * p.q_b + (h * GROUP + head) * p.q_h + lane * 8);
   uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-  if (p.q_norm_w != nullptr) norm_row8(w, p.q_norm_w, p.eps, lane);
-  rope_row8(w, p, pos_b, lane);
+  if (p.q_norm_w != nullptr) norm_row8(w, tb.q_norm_w, p.eps, lane);
+  rope_row8(w, p.rotary_half, tb.inv_freq, pos_b, lane);
   *reinterpret_cast<uint4*>(buf + head * FD_Q_PITCH + lane * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ void stage_q(__nv_bfloat16* buf, const FusedDecodeParams& p, const FusedDecodeTables& tb, int b,
+                                        int h, int pos_b, int tid) {
+  stage_q_row(buf, p, tb, load_q_row(p, b, h, tid), pos_b, tid);
+}
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// Asks the L2 for the q rows and the gate row of a segment ahead of their use (one 16-byte piece per thread of warps
+// 0-3 and 8 bytes of gate per thread: the lines they touch cover both rows).
+__device__ __forceinline__ void prefetch_l2(const void* ptr) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
 }
 
 // The appended token as a one-row page: the normalised (optional), rotated k_new goes to row 0 of `k_tile` and to its
-// slot in the cache.  Each lane owns 8 consecutive dims.
-__device__ __forceinline__ void stage_new_k(uint8_t* k_tile, const FusedDecodeParams& p, int b, int h, int64_t pos_b,
-                                            int lane) {
-  const uint4 kraw = *reinterpret_cast<const uint4*>(p.k_new + b * p.kn_b + h * p.kn_h + lane * 8);
+// slot in the cache (physical page `phys`).  Each lane owns 8 consecutive dims.  The raw rows were copied to
+// tb.new_rows by this warp at the start of the piece (fetch_new_rows), so nothing here waits for global memory.
+__device__ __forceinline__ void fetch_new_rows(FusedDecodeTables& tb, const FusedDecodeParams& p, int b, int h, int lane) {
+  cp_async16(tb.new_rows + lane * 16, p.k_new + b * p.kn_b + h * p.kn_h + lane * 8);
+  cp_async16(tb.new_rows + HEAD_DIM * 2 + lane * 16, p.v_new + b * p.vn_b + h * p.vn_h + lane * 8);
+  cp_async_commit();
+}
+__device__ __forceinline__ void stage_new_k(uint8_t* k_tile, const FusedDecodeParams& p, const FusedDecodeTables& tb, int h,
+                                            int64_t pos_b, int64_t phys, int lane) {
+  cp_async_wait_all();
+  __syncwarp();
+  const uint4 kraw = *reinterpret_cast<const uint4*>(tb.new_rows + lane * 16);
   uint32_t kw[4] = {kraw.x, kraw.y, kraw.z, kraw.w};
-  if (p.k_norm_w != nullptr) norm_row8(kw, p.k_norm_w, p.eps, lane);
-  rope_row8(kw, p, pos_b, lane);
+  if (p.k_norm_w != nullptr) norm_row8(kw, tb.k_norm_w, p.eps, lane);
+  rope_row8(kw, p.rotary_half, tb.inv_freq, pos_b, lane);
   const uint4 krot = make_uint4(kw[0], kw[1], kw[2], kw[3]);
   *reinterpret_cast<uint4*>(k_tile + tile_offset<true>(0, lane)) = krot;
-  const int64_t phys = p.block_table[b * p.bt_b + pos_b / PAGE];
   *reinterpret_cast<uint4*>(p.k_cache + phys * p.kc_p + h * p.kc_h + (pos_b % PAGE) * p.kc_s + lane * 8) = krot;
 }
-__device__ __forceinline__ void stage_new_v(uint8_t* v_tile, const FusedDecodeParams& p, int b, int h, int64_t pos_b,
-                                            int lane) {
-  const uint4 vraw = *reinterpret_cast<const uint4*>(p.v_new + b * p.vn_b + h * p.vn_h + lane * 8);
+__device__ __forceinline__ void stage_new_v(uint8_t* v_tile, const FusedDecodeParams& p, const FusedDecodeTables& tb, int h,
+                                            int64_t pos_b, int64_t phys, int lane) {
+  const uint4 vraw = *reinterpret_cast<const uint4*>(tb.new_rows + HEAD_DIM * 2 + lane * 16);
   *reinterpret_cast<uint4*>(v_tile + tile_offset<true>(0, lane)) = vraw;
-  const int64_t phys = p.block_table[b * p.bt_b + pos_b / PAGE];
   *reinterpret_cast<uint4*>(p.v_cache + phys * p.vc_p + h * p.vc_h + (pos_b % PAGE) * p.vc_s + lane * 8) = vraw;
 }
 
@@ -225,6 +260,7 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   __shared__ uint64_t bars[FD_WARPS][FD_RING];
   __shared__ int s_last;
   __shared__ int s_max_units;
+  __shared__ FusedDecodeTables tb;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* merge = reinterpret_cast<float*>(smem + FD_SMEM_RING);
   int* cum = reinterpret_cast<int*>(smem + FD_SMEM_RING + FD_SMEM_MERGE);
@@ -240,12 +276,22 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
     for (int s = 0; s < FD_RING; ++s) mbar_init(&bars[warp][s], 1);
     mbar_fence_init();
   }
+  if (tid == 0) {
+    prefetch_tensormap(&map_k);
+    prefetch_tensormap(&map_v);
+  }
   if (p.overlap & OVERLAP_TRIGGER) pdl_trigger();  // the successor may start: it waits for this grid before it reads `out`
   // Started early (programmatic dependent launch): with the PREFETCH flag the position prefix, the page-id gathers and
   // the first K/V page copies below overlap with the predecessor (it must not write pos, the block table or the
   // caches); q, k_new, v_new and gate are the predecessor's output and are read only after the wait further down.
   if (!(p.overlap & OVERLAP_PREFETCH)) pdl_wait();
 
+  // weights and frequencies are nobody's output: staged before anything else, published by the barrier below
+  if (warp == 7) tb.inv_freq[lane] = lane < p.rotary_half ? p.inv_freq[lane] : 0.f;
+  if (warp == 6 && p.q_norm_w != nullptr)
+    *reinterpret_cast<uint4*>(tb.q_norm_w + lane * 8) = *reinterpret_cast<const uint4*>(p.q_norm_w + lane * 8);
+  if (warp == 5 && p.k_norm_w != nullptr)
+    *reinterpret_cast<uint4*>(tb.k_norm_w + lane * 8) = *reinterpret_cast<const uint4*>(p.k_norm_w + lane * 8);
   // ---- exclusive prefix of units per sequence: units_b = cdiv(pos[b], 16) + 1
   for (int b = tid; b < batch; b += FD_THREADS) {
     const int pb = static_cast<int>(p.pos[b]);
@@ -360,6 +406,8 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   int ii = 0;                // index of unit iu among this warp's units of the current piece
   int win_base = -1;         // first ii covered by the page-id window (-1 = none loaded)
   int win_phys = 0;          // lane L holds the physical page of this warp's (win_base + L)-th unit of the piece
+  int pre_phys = 0;          // the window this warp needs next, asked for when the current one was loaded: a gather
+  int pre_key = -1;          // issued while the page copies saturate memory takes microseconds (key = its first unit)
   int cur_phys = 0;
   int issued = 0, consumed = 0;
   uint32_t phase_bits = 0;
@@ -375,10 +423,26 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
         if (j < np) {
           if (!i_is_v) {
             if (win_base < 0 || ii - win_base >= 32) {
-              // one gather of the next 32 page ids of this warp (stride FD_WARPS in the table row)
+              // one gather of the next 32 page ids of this warp (stride FD_WARPS in the table row) ...
               win_base = ii;
-              const int jl = j + lane * FD_WARPS;
-              win_phys = (iu + lane * FD_WARPS < hi && jl < np) ? p.block_table[iseg.b * p.bt_b + jl] : 0;
+              if (pre_key == iu) {
+                win_phys = pre_phys;
+              } else {
+                const int jl = j + lane * FD_WARPS;
+                win_phys = (iu + lane * FD_WARPS < hi && jl < np) ? p.block_table[iseg.b * p.bt_b + jl] : 0;
+              }
+              // ... and, not waited for, the one after it: the same segment 32 units of this warp further on, or the
+              // warp's first units of the next segment in the range
+              Segment ns = iseg;
+              int nu = iu + 32 * FD_WARPS;
+              if (nu >= hi && iseg.end < r1) {
+                segment_advance(ns, cum, batch, heads);
+                nu = ns.start + warp;
+              }
+              const int nhi = min(ns.end, r1), njl = nu - ns.start + lane * FD_WARPS;
+              pre_key = nu < nhi ? nu : -1;
+              if (pre_key >= 0)
+                pre_phys = (nu + lane * FD_WARPS < nhi && njl < ns.end - ns.start - 1) ? p.block_table[ns.b * p.bt_b + njl] : 0;
             }
             cur_phys = __shfl_sync(0xffffffffu, win_phys, ii - win_base);
           }
@@ -405,6 +469,18 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
     }
   };
   __syncwarp();
+  // The first segment's q rows: fetched BEFORE the burst of page copies when the predecessor has already finished
+  // (behind 148 x 24 copies the load would wait for all of them); with the PREFETCH flag q is not final yet and is read
+  // after the wait below.
+  const Segment seg0 = cluster_mode ? cseg : segment_of_unit(r0, cum, batch, heads);
+  const bool q_early = !(p.overlap & OVERLAP_PREFETCH);
+  uint4 q_raw = make_uint4(0, 0, 0, 0);
+  if (q_early) q_raw = load_q_row(p, seg0.b, seg0.h, tid);
+  if (seg0.end < r1 && tid < GROUP * 32) {  // the second piece's q rows: into the L2 ahead of their staging
+    Segment nxt = seg0;
+    segment_advance(nxt, cum, batch, heads);
+    prefetch_l2(p.q + nxt.b * p.q_b + (nxt.h * GROUP + warp) * p.q_h + lane * 8);
+  }
   for (int s = 0; s < FD_RING; ++s) issue_next();
 
   // ---- consumer: CTA-uniform loop over the pieces of this range
@@ -439,7 +515,8 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
     finish_store(p, sg.b, sg.h * GROUP + hh, d0, a4, l_fin, gate_bits);
   };
   pdl_wait();  // from here on the predecessor's q / k_new / v_new / gate are read and global memory is written
-  stage_q(q_s, p, seg.b, seg.h, pos_s[seg.b], tid);
+  if (!q_early) q_raw = load_q_row(p, seg.b, seg.h, tid);
+  stage_q_row(q_s, p, tb, q_raw, pos_s[seg.b], tid);
   __syncthreads();
   while (seg.start < r1 || (cluster_mode && piece == 0)) {  // in cluster mode exactly once, also without units
     const int lo = max(seg.start, r0), hi = min(seg.end, r1);
@@ -449,10 +526,22 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
     const uint2 gate_pf = *reinterpret_cast<const uint2*>(p.gate + seg.b * p.gate_b +
                                                            static_cast<int64_t>(seg.h * GROUP + hh) * HEAD_DIM + d0);
     // rotated Q of the NEXT piece goes to the other buffer while this piece streams (published by the merge barriers)
+    // (its rows were asked into the L2 one piece earlier: a load that misses there queues behind the page copies)
     if (seg.end < r1) {
       Segment nxt = seg;
       segment_advance(nxt, cum, batch, heads);
-      stage_q(q_s + ((piece + 1) & 1) * GROUP * FD_Q_PITCH, p, nxt.b, nxt.h, pos_s[nxt.b], tid);
+      if (nxt.end < r1 && tid < GROUP * 32) {
+        Segment nn = nxt;
+        segment_advance(nn, cum, batch, heads);
+        prefetch_l2(p.q + nn.b * p.q_b + (nn.h * GROUP + warp) * p.q_h + lane * 8);
+      }
+      stage_q(q_s + ((piece + 1) & 1) * GROUP * FD_Q_PITCH, p, tb, nxt.b, nxt.h, pos_s[nxt.b], tid);
+    }
+    // the appended token's rows and its page: asked for now by the warp that will reach the segment's last unit
+    int64_t new_phys = 0;
+    if (hi == seg.end && hi > lo && warp == (seg.end - 1 - lo) % FD_WARPS) {
+      fetch_new_rows(tb, p, seg.b, seg.h, lane);
+      new_phys = p.block_table[seg.b * p.bt_b + pos_b / PAGE];
     }
     DecodeWarpState st;
     decode_state_init(st);
@@ -479,8 +568,8 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
             }
           }
         } else {
-          if (part == 0) stage_new_k(tile, p, seg.b, seg.h, pos_b, lane);
-          else stage_new_v(tile, p, seg.b, seg.h, pos_b, lane);
+          if (part == 0) stage_new_k(tile, p, tb, seg.h, pos_b, new_phys, lane);
+          else stage_new_v(tile, p, tb, seg.h, pos_b, new_phys, lane);
           __syncwarp();
         }
         if (ready) {

@@ -94,8 +94,19 @@ def test_gdn_gated_rmsnorm(mods):
 @pytest.mark.parametrize("batch", [1, 32])
 def test_gdn_decode_fused_equals_chain(mods, batch, prefetch):
     """One-launch Gated-DeltaNet decode mixer against prep -> recurrent_decode -> gated RMSNorm over three steps
-    (conv state and recurrent state carried in place)."""
+    (conv state and recurrent state carried in place).  The chain's recurrence is pinned to the one-CTA-per-head form,
+    which sums in the fused kernel's order: the comparison is then about the fusion, not about fp32 summation order
+    (an output that nearly cancels moves by more than two bf16 ulps of itself between orders)."""
+    from b200attn import _lib
     ops, glue = mods
+    _lib.call("b200_gdn_recurrent_decode_form", 1)
+    try:
+        _fused_against_chain(ops, batch, prefetch)
+    finally:
+        _lib.call("b200_gdn_recurrent_decode_form", 0)
+
+
+def _fused_against_chain(ops, batch, prefetch):
     gen = torch.Generator().manual_seed(90 + batch)
     heads, kd = 16, 2048
     w4 = (torch.randn(4, 3 * kd, generator=gen) * 0.5).to(torch.bfloat16).to(DEV)
