@@ -50,6 +50,7 @@ constexpr int FD_SMEM_CUM = ((FD_MAX_BATCH + 1) * 4 + 15) / 16 * 16;   // exclus
 constexpr int FD_SMEM_POS = FD_MAX_BATCH * 4;                           // pos[] as int32
 constexpr int FD_Q_PITCH = HEAD_DIM + 8;                                // bf16 elements per staged Q row
 constexpr int FD_SMEM_Q = 2 * GROUP * FD_Q_PITCH * 2;                   // rotated Q of this piece and of the next
+constexpr int FD_GAP = 16;                                              // line positions behind every segment (see Segment)
 constexpr int FD_MAX_CLUSTER = 16;                                      // CTAs that may share one segment
 constexpr int FD_SMEM_RECV = FD_TILE_FLOATS * 4 + FD_MAX_CLUSTER * 8 * 4;  // cluster exchange: one accumulator slice per
                                                                            // source CTA (4 KiB in all) + every (m, l)
@@ -58,6 +59,7 @@ constexpr int FD_SMEM_TOTAL =
 static_assert(FD_SMEM_TOTAL <= 227 * 1024, "shared memory budget");
 
 struct FusedDecodeParams {
+  int gap;  // empty positions behind every segment on the unit line (see Segment)
   const __nv_bfloat16 *q, *k_new, *v_new, *gate;
   const __nv_bfloat16 *q_norm_w, *k_norm_w;  // optional per-head RMSNorm weights [256] applied to q / k_new first
   __nv_bfloat16 *k_cache, *v_cache, *out;
@@ -76,12 +78,17 @@ struct FusedDecodeParams {
   float scale, eps;
 };
 
-// Position of a (sequence, kv head) segment on the unit line.  units = old pages + 1 (the appended token).
+// Position of a (sequence, kv head) segment on the unit line.  units = old pages + 1 (the appended token); [start, end)
+// are its units.  Behind every segment the line has `gap` empty positions: a CTA stops at every segment boundary inside
+// its range (merge of the eight warps, a partial or the output), which costs about as much as streaming `gap` units, so
+// equal ranges of the line are ranges of equal TIME and a CTA with more boundaries gets fewer pages.
 struct Segment {
   int b, h, start, end;
 };
 
-__device__ __forceinline__ Segment segment_of_unit(int u, const int* cum, int batch, int heads) {
+// cum[] is the exclusive prefix of (units + gap) per sequence.  A position inside a gap belongs to the segment before it
+// (then u >= end).
+__device__ __forceinline__ Segment segment_of_unit(int u, const int* cum, int batch, int heads, int gap) {
   int lo = 0, hi = batch - 1;
   while (lo < hi) {
     const int mid = (lo + hi + 1) >> 1;
@@ -89,19 +96,19 @@ __device__ __forceinline__ Segment segment_of_unit(int u, const int* cum, int ba
   }
   Segment s;
   s.b = lo;
-  const int units = cum[lo + 1] - cum[lo];
-  s.h = (u - heads * cum[lo]) / units;
-  s.start = heads * cum[lo] + s.h * units;
-  s.end = s.start + units;
+  const int span = cum[lo + 1] - cum[lo];
+  s.h = (u - heads * cum[lo]) / span;
+  s.start = heads * cum[lo] + s.h * span;
+  s.end = s.start + span - gap;
   return s;
 }
-__device__ __forceinline__ void segment_advance(Segment& s, const int* cum, int batch, int heads) {
-  s.start = s.end;
+__device__ __forceinline__ void segment_advance(Segment& s, const int* cum, int batch, int heads, int gap) {
+  s.start = s.end + gap;
   if (++s.h == heads) {
     s.h = 0;
     ++s.b;
   }
-  if (s.b < batch) s.end = s.start + (cum[s.b + 1] - cum[s.b]);
+  if (s.b < batch) s.end = s.start + (cum[s.b + 1] - cum[s.b]) - gap;
 }
 
 // One head row of q or k_new, 8 consecutive dims per lane (`w` = 4 packed bf16 pairs).
@@ -270,7 +277,7 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   float* recv_ml = recv + FD_TILE_FLOATS;   // [source rank][m[4], l[4]]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int heads = p.num_kv_heads, batch = p.batch;
+  const int heads = p.num_kv_heads, batch = p.batch, gap = p.gap;
   uint8_t* ring = smem + warp * FD_RING * TILE_BYTES_SW;
   if (lane == 0) {
     for (int s = 0; s < FD_RING; ++s) mbar_init(&bars[warp][s], 1);
@@ -296,7 +303,7 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   for (int b = tid; b < batch; b += FD_THREADS) {
     const int pb = static_cast<int>(p.pos[b]);
     pos_s[b] = pb;
-    cum[b + 1] = (pb + PAGE - 1) / PAGE + 1;
+    cum[b + 1] = (pb + PAGE - 1) / PAGE + 1 + gap;
   }
   __syncthreads();
   if (warp == 0) {
@@ -317,7 +324,7 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
     for (int o = 16; o > 0; o >>= 1) longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, o));
     if (lane == 0) {
       cum[0] = 0;
-      s_max_units = longest;
+      s_max_units = longest - gap;
     }
   }
   __syncthreads();
@@ -336,11 +343,11 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   //    whole     max(165, 350 segments / CTAs) u_longest + 9500
   //    cluster   max(190 u_longest / cluster_size, 2.64 u_total) + 10500
   // A form is taken over stream-K when its model wins by 5 %.
-  const int total = heads * cum[batch];
+  const int total = heads * cum[batch];  // length of the line, gaps included
   const int grid = static_cast<int>(gridDim.x), nseg = batch * heads;
   const int chunk = max((total + grid - 1) / grid, FD_WARPS);
   const int csize = p.cluster_size;
-  const int dram = total * 66 / 25;  // 2.64 ns per unit
+  const int dram = (total - nseg * gap) * 66 / 25;  // 2.64 ns per unit
   const int t_stream = max(350 * chunk, dram) + 16500;
   const int t_whole = max(165, 350 * nseg / grid) * s_max_units + 9500;
   const int t_cluster = max(190 * ((s_max_units + csize - 1) / csize), dram) + 10500;
@@ -365,9 +372,9 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
     const int cl = static_cast<int>(blockIdx.x) / csize;
     if (cl < nseg) {
       const int sb = cl / heads, sh = cl % heads;
-      const int units = cum[sb + 1] - cum[sb];
+      const int span = cum[sb + 1] - cum[sb], units = span - gap;
       const int per = (units + csize - 1) / csize;
-      const int start = heads * cum[sb] + sh * units;
+      const int start = heads * cum[sb] + sh * span;
       cseg.b = sb;
       cseg.h = sh;
       cseg.start = start;
@@ -381,9 +388,9 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   } else if (whole_segments) {
     if (static_cast<int>(blockIdx.x) < nseg) {
       const int sb = blockIdx.x / heads, sh = blockIdx.x % heads;
-      const int units = cum[sb + 1] - cum[sb];
-      r0 = heads * cum[sb] + sh * units;
-      r1 = r0 + units;
+      const int span = cum[sb + 1] - cum[sb];
+      r0 = heads * cum[sb] + sh * span;
+      r1 = r0 + span - gap;
     } else {
       r0 = r1 = total;
     }
@@ -397,11 +404,19 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   }
   // (in cluster mode a CTA without units of its own still takes part in the exchange below: the cluster barrier needs
   //  every thread of every CTA of the cluster, and this CTA finishes a slice of the output)
+  Segment seg0 = cluster_mode ? cseg : segment_of_unit(r0, cum, batch, heads, gap);
+  if (!cluster_mode) {
+    if (r0 >= seg0.end) segment_advance(seg0, cum, batch, heads, gap);  // the range starts inside a gap
+    if (seg0.start >= r1) {                                             // ... and ends in it
+      pdl_wait();
+      return;
+    }
+  }
 
   // ---- per-warp issue cursor: walks the same unit sequence as the consumer, FD_RING tiles ahead.
   // Tile sequence of a warp: K(u0), V(u0), K(u1), V(u1), ...; tile n lives in ring slot n % FD_RING.
-  Segment iseg = cluster_mode ? cseg : segment_of_unit(r0, cum, batch, heads);
-  int iu = r0 + warp;        // unit whose tiles are issued next
+  Segment iseg = seg0;
+  int iu = max(r0, seg0.start) + warp;  // unit whose tiles are issued next
   bool i_is_v = false;       // next tile to issue is the V tile of unit iu
   int ii = 0;                // index of unit iu among this warp's units of the current piece
   int win_base = -1;         // first ii covered by the page-id window (-1 = none loaded)
@@ -435,8 +450,8 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
               // warp's first units of the next segment in the range
               Segment ns = iseg;
               int nu = iu + 32 * FD_WARPS;
-              if (nu >= hi && iseg.end < r1) {
-                segment_advance(ns, cum, batch, heads);
+              if (nu >= hi && iseg.end + gap < r1) {
+                segment_advance(ns, cum, batch, heads, gap);
                 nu = ns.start + warp;
               }
               const int nhi = min(ns.end, r1), njl = nu - ns.start + lane * FD_WARPS;
@@ -461,8 +476,8 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
         i_is_v = !i_is_v;
         return;
       }
-      if (iseg.end >= r1) return;  // nothing left in this CTA's range
-      segment_advance(iseg, cum, batch, heads);
+      if (iseg.end + gap >= r1) return;  // no further segment starts inside this CTA's range
+      segment_advance(iseg, cum, batch, heads, gap);
       iu = iseg.start + warp;
       ii = 0;
       win_base = -1;
@@ -472,19 +487,18 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   // The first segment's q rows: fetched BEFORE the burst of page copies when the predecessor has already finished
   // (behind 148 x 24 copies the load would wait for all of them); with the PREFETCH flag q is not final yet and is read
   // after the wait below.
-  const Segment seg0 = cluster_mode ? cseg : segment_of_unit(r0, cum, batch, heads);
   const bool q_early = !(p.overlap & OVERLAP_PREFETCH);
   uint4 q_raw = make_uint4(0, 0, 0, 0);
   if (q_early) q_raw = load_q_row(p, seg0.b, seg0.h, tid);
-  if (seg0.end < r1 && tid < GROUP * 32) {  // the second piece's q rows: into the L2 ahead of their staging
+  if (seg0.end + gap < r1 && tid < GROUP * 32) {  // the second piece's q rows: into the L2 ahead of their staging
     Segment nxt = seg0;
-    segment_advance(nxt, cum, batch, heads);
+    segment_advance(nxt, cum, batch, heads, gap);
     prefetch_l2(p.q + nxt.b * p.q_b + (nxt.h * GROUP + warp) * p.q_h + lane * 8);
   }
   for (int s = 0; s < FD_RING; ++s) issue_next();
 
   // ---- consumer: CTA-uniform loop over the pieces of this range
-  Segment seg = cluster_mode ? cseg : segment_of_unit(r0, cum, batch, heads);
+  Segment seg = seg0;
   const int hh = tid >> 6, d0 = (tid & 63) * 4;  // element mapping of the merge / finish steps
   int piece = 0;
   bool have_pending = false;
@@ -527,12 +541,12 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
                                                            static_cast<int64_t>(seg.h * GROUP + hh) * HEAD_DIM + d0);
     // rotated Q of the NEXT piece goes to the other buffer while this piece streams (published by the merge barriers)
     // (its rows were asked into the L2 one piece earlier: a load that misses there queues behind the page copies)
-    if (seg.end < r1) {
+    if (seg.end + gap < r1) {  // another segment starts inside the range
       Segment nxt = seg;
-      segment_advance(nxt, cum, batch, heads);
-      if (nxt.end < r1 && tid < GROUP * 32) {
+      segment_advance(nxt, cum, batch, heads, gap);
+      if (nxt.end + gap < r1 && tid < GROUP * 32) {
         Segment nn = nxt;
-        segment_advance(nn, cum, batch, heads);
+        segment_advance(nn, cum, batch, heads, gap);
         prefetch_l2(p.q + nn.b * p.q_b + (nn.h * GROUP + warp) * p.q_h + lane * 8);
       }
       stage_q(q_s + ((piece + 1) & 1) * GROUP * FD_Q_PITCH, p, tb, nxt.b, nxt.h, pos_s[nxt.b], tid);
@@ -667,7 +681,7 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
         s_last = last;
       }
     }
-    segment_advance(seg, cum, batch, heads);
+    segment_advance(seg, cum, batch, heads, gap);
     ++piece;
   }
   if (have_pending) {
@@ -767,6 +781,8 @@ static int fused_decode_impl(const void* q, int64_t q_stride_b, int64_t q_stride
                                            int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
                                            const void* q_norm_weight, const void* k_norm_weight, float eps,
                                            int32_t overlap, int32_t partition, b200_stream_t stream) {
+  const int tune_gap = partition >> 8;  // TUNING ONLY
+  partition &= 0xff;
   B200_REQUIRE(partition >= 0 && partition <= 3, "fused_decode_attention: partition must be 0..3 (got %d)", partition);
   B200_REQUIRE(aligned16(q_norm_weight) && aligned16(k_norm_weight),
                "fused_decode_attention: norm weights must be 16-byte aligned");
@@ -854,6 +870,7 @@ static int fused_decode_impl(const void* q, int64_t q_stride_b, int64_t q_stride
   B200_REQUIRE(partition != 3 || csize > 1,
                "fused_decode_attention: partition 3 (a cluster per segment) needs batch*H_kv <= 64 (got %d)", nseg);
   p.partition = partition;
+  p.gap = tune_gap ? tune_gap - 1 : FD_GAP;
   p.cluster_size = csize;
   cudaError_t launched;
   if (csize > 1) {
