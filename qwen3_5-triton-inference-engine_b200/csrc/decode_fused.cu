@@ -50,7 +50,7 @@ constexpr int FD_SMEM_CUM = ((FD_MAX_BATCH + 1) * 4 + 15) / 16 * 16;   // exclus
 constexpr int FD_SMEM_POS = FD_MAX_BATCH * 4;                           // pos[] as int32
 constexpr int FD_Q_PITCH = HEAD_DIM + 8;                                // bf16 elements per staged Q row
 constexpr int FD_SMEM_Q = 2 * GROUP * FD_Q_PITCH * 2;                   // rotated Q of this piece and of the next
-constexpr int FD_GAP = 16;                                              // line positions behind every segment (see Segment)
+constexpr int FD_GAP = 32;                                              // line positions behind every segment (see Segment)
 constexpr int FD_MAX_CLUSTER = 16;                                      // CTAs that may share one segment
 constexpr int FD_SMEM_RECV = FD_TILE_FLOATS * 4 + FD_MAX_CLUSTER * 8 * 4;  // cluster exchange: one accumulator slice per
                                                                            // source CTA (4 KiB in all) + every (m, l)
@@ -329,28 +329,30 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
   }
   __syncthreads();
 
-  // Two ways to cut the work.
-  //  - Stream-K: equal ranges of units per CTA (never less than one unit per warp: tiny problems use fewer CTAs and leave
-  //    fewer partials to merge).  Balanced whatever the context lengths, but a segment cut by a range boundary costs a
-  //    partial, a ticket and a merge, and a CTA that spans several segments stops at every boundary.
+  // Three ways to cut the work.
+  //  - Stream-K: equal ranges of the unit line per CTA (never less than one position per warp: tiny problems use fewer
+  //    CTAs and leave fewer partials to merge).  A segment cut by a range boundary costs a partial, a ticket and a
+  //    merge, and a CTA that spans several segments stops at every boundary; the gap behind every segment on the line
+  //    charges a range for the boundaries inside it, so that the ranges take equal time rather than hold equal pages.
   //  - One whole segment per CTA, when there are no more segments than CTAs: no partials at all, but the longest
   //    segment sets the time, and an SM alone streams at about 75 GB/s.
   //  - One segment per CLUSTER (launches with clusters only, when every segment gets a cluster of its own): the CTAs
   //    of a cluster take equal shares of the segment's units and merge through distributed shared memory.
   // The choice compares time models fitted to measurements of this kernel on B200 (nanoseconds, u = units of 16 KiB;
   // every form is also bound by the DRAM rate, 2.64 ns per unit):
-  //    stream-K  max(350 u_per_CTA, 2.64 u_total) + 16500
-  //    whole     max(165, 350 segments / CTAs) u_longest + 9500
-  //    cluster   max(190 u_longest / cluster_size, 2.64 u_total) + 10500
+  //    stream-K  max(300 line positions per CTA, 2.64 u_total) + 8000 + 180 u_longest / (positions per CTA)
+  //              (the last term: partials the longest segment leaves for its final merge)
+  //    whole     max(165 u_longest, 2.64 u_total) + 8500
+  //    cluster   max(190 u_longest / cluster_size, 2.64 u_total) + 8500
   // A form is taken over stream-K when its model wins by 5 %.
   const int total = heads * cum[batch];  // length of the line, gaps included
   const int grid = static_cast<int>(gridDim.x), nseg = batch * heads;
   const int chunk = max((total + grid - 1) / grid, FD_WARPS);
   const int csize = p.cluster_size;
   const int dram = (total - nseg * gap) * 66 / 25;  // 2.64 ns per unit
-  const int t_stream = max(350 * chunk, dram) + 16500;
-  const int t_whole = max(165, 350 * nseg / grid) * s_max_units + 9500;
-  const int t_cluster = max(190 * ((s_max_units + csize - 1) / csize), dram) + 10500;
+  const int t_stream = max(300 * chunk, dram) + 8000 + 180 * s_max_units / chunk;
+  const int t_whole = max(165 * s_max_units, dram) + 8500;
+  const int t_cluster = max(190 * ((s_max_units + csize - 1) / csize), dram) + 8500;
   const bool cluster_fits = csize > 1 && nseg * csize <= grid;
   const bool whole_fits = nseg <= grid;
   int form = 1;  // 1 stream-K, 2 whole segments, 3 cluster per segment
@@ -781,8 +783,6 @@ static int fused_decode_impl(const void* q, int64_t q_stride_b, int64_t q_stride
                                            int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
                                            const void* q_norm_weight, const void* k_norm_weight, float eps,
                                            int32_t overlap, int32_t partition, b200_stream_t stream) {
-  const int tune_gap = partition >> 8;  // TUNING ONLY
-  partition &= 0xff;
   B200_REQUIRE(partition >= 0 && partition <= 3, "fused_decode_attention: partition must be 0..3 (got %d)", partition);
   B200_REQUIRE(aligned16(q_norm_weight) && aligned16(k_norm_weight),
                "fused_decode_attention: norm weights must be 16-byte aligned");
@@ -870,7 +870,7 @@ static int fused_decode_impl(const void* q, int64_t q_stride_b, int64_t q_stride
   B200_REQUIRE(partition != 3 || csize > 1,
                "fused_decode_attention: partition 3 (a cluster per segment) needs batch*H_kv <= 64 (got %d)", nseg);
   p.partition = partition;
-  p.gap = tune_gap ? tune_gap - 1 : FD_GAP;
+  p.gap = FD_GAP;
   p.cluster_size = csize;
   cudaError_t launched;
   if (csize > 1) {
