@@ -473,7 +473,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of one CUDA graph")
     ap.add_argument("--no-model", action="store_true", help="skip the whole-model decode measurement (24-layer random-init model)")
     ap.add_argument("--model-steps", type=int, default=512)
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gdn", "gemm"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gdn", "gdn_decode", "gemm"],
                     help="with --kernel-only: which kernel family to run (profiler captures of the other families)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
@@ -502,6 +502,8 @@ def main():
     if args.kernel_only and args.workload != "decode":
         if args.workload == "gemm":
             rows = run_gemm_sweep(ops, device, hbm_peak()[0], args.steps)
+        elif args.workload == "gdn_decode":
+            rows = run_gdn_decode_rows(ops, device, hbm_peak()[0], args.steps, (args.batch,))
         else:
             rows = run_prefill_sweep(ops, device, args.steps, only=args.workload)
         if rank == 0:
@@ -778,8 +780,16 @@ def run_sweep(ops, ws, device, peak, steps):
             rows.append(row)
             del w
             torch.cuda.empty_cache()
-    # Gated-DeltaNet decode: fp32 state [B,16,128,128] streamed in and out once per step
-    for b in (1, 32, 256):
+    rows += run_gdn_decode_rows(ops, device, peak, steps, (1, 32, 256))
+    rows += run_gemm_sweep(ops, device, peak, steps)
+    rows += run_prefill_sweep(ops, device, steps)
+    return rows
+
+
+def run_gdn_decode_rows(ops, device, peak, steps, batches):
+    """Gated-DeltaNet decode: fp32 state [B,16,128,128] streamed in and out once per step."""
+    rows = []
+    for b in batches:
         nbytes = gdn_decode_bytes(b)
         sets = max(1, min(32, cdiv(3 * L2_BYTES, nbytes)))
         states = [torch.zeros(b, 16, 128, 128, device=device) for _ in range(sets)]
@@ -794,8 +804,6 @@ def run_sweep(ops, ws, device, peak, steps):
                      "frac": nbytes / (ms * 1e-3) / 1e9 / peak})
         del states
         torch.cuda.empty_cache()
-    rows += run_gemm_sweep(ops, device, peak, steps)
-    rows += run_prefill_sweep(ops, device, steps)
     return rows
 
 
@@ -918,6 +926,25 @@ def run_prefill_sweep(ops, device, steps, only=None):
     ms = time_steps(lambda i: ops.gdn_chunked_prefill_packed(gq, gk, gv, beta, g, cu, 128, fused=False), steps, 3)
     rows.append({"op": "gdn_chunked_prefill_packed (3 launches)", "shape": "cfg4 B=32 x 128", "tokens": total,
                  "us": ms * 1e3, "tflops_fp32": 12.1e6 * 2 * len(lengths) * heads / (ms * 1e-3) / 1e12})
+    # the same kernel where every SM has work for many chunks: 32 prompts x 1024 tokens (512 CTAs x 16 chunks)
+    long_len = [1024] * 32
+    lt = sum(long_len)
+    gen2 = torch.Generator().manual_seed(11)
+    lq = torch.nn.functional.normalize(torch.randn(lt, heads, 128, generator=gen2), dim=-1) * 128 ** -0.5
+    lk = torch.nn.functional.normalize(torch.randn(lt, heads, 128, generator=gen2), dim=-1)
+    lq, lk = lq.to(torch.bfloat16).to(device), lk.to(torch.bfloat16).to(device)
+    lv = torch.randn(lt, heads, 128, generator=gen2).to(torch.bfloat16).to(device)
+    lbeta = torch.sigmoid(torch.randn(lt, heads, generator=gen2)).to(device)
+    lg = (-torch.nn.functional.softplus(torch.randn(lt, heads, generator=gen2))
+          * torch.exp(torch.rand(heads, generator=gen2) * 2.7)).to(device)
+    lcu, _ = ops.build_cu_seqlens(long_len, device=device)
+    ms = time_steps(lambda i: ops.gdn_chunked_prefill_packed(lq, lk, lv, lbeta, lg, lcu), steps, 3)
+    lflops = 12.1e6 * (lt // 64) * heads
+    lbytes = lt * heads * (4 * 128 * 2 + 8) + len(long_len) * heads * 128 * 128 * 4
+    rows.append({"op": "gdn_chunked_prefill_fused (tcgen05, 1 launch)", "shape": "B=32 x 1024", "tokens": lt,
+                 "us": ms * 1e3, "tflops": lflops / (ms * 1e-3) / 1e12, "frac_tensor": lflops / (ms * 1e-3) / 1e12 / tf_peak,
+                 "gbs": lbytes / (ms * 1e-3) / 1e9, "frac_hbm": lbytes / (ms * 1e-3) / 1e9 / hbm})
+    del lq, lk, lv, lbeta, lg
     # one sequence through the drop-in entry point the reference runner calls for long prompts (engine/runner.py:272-273)
     for n_tok in (128, 2048):
         gen1 = torch.Generator().manual_seed(3)
