@@ -43,6 +43,16 @@ int b200_abi_version(void);
  * last call (the flag is cleared), 0 if not, -1 on a runtime error.  For tests and debugging. */
 int b200_wait_timed_out(void);
 
+/* The small operators of a decode step (partial_rope, attention_gate_pack, paged_kv_append, the split / combine pair,
+ * gdn_recurrent_decode, the decode conv, the GDN norms and gates, residual_add, embedding_gather) are each a few
+ * microseconds long and are called one after the other; they are launched for programmatic dependent launch: every such
+ * kernel lets its successor in the stream be scheduled at once and itself touches global memory only after its
+ * predecessor has completed, so the launch latencies overlap instead of adding up (a kernel of another library in
+ * between is unaffected: it starts when its predecessor has finished, as always).  b200_set_chain_overlap(0) launches
+ * them plainly again, process-wide (for comparisons, or under tools that do not model such launches).  No counterpart
+ * in the reference. */
+int b200_set_chain_overlap(int32_t enabled);
+
 /* Diagnostic: one CTA multiplies two bf16 tiles loaded by tensor-map TMA with tcgen05.mma (accumulator in tensor
  * memory) and writes fp32 C.  mode 0: C[128x64] = A[128x256] . B[64x256]^T;  mode 1: C[128x256] = A[128x64] . B[64x256];
  * mode 2: as mode 1 with A handed to the MMA through tensor memory instead of shared memory.

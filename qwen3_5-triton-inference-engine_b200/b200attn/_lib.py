@@ -30,6 +30,7 @@ SIGNATURES: dict[str, list] = {
     "b200_selftest_umma": [I32, P, P, P, P],
     "b200_selftest_wait_timeout": [P, P],
     "b200_gdn_recurrent_decode_form": [I32],
+    "b200_set_chain_overlap": [I32],
     "b200_gqa_varlen_causal": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, I64, P, I32, I32, I32, I32, I32, I32, P],
     "b200_fused_prefill_attention": [P, I64, I64, P, I64, I64, P, I64, I64, P, I64, P, P, I64, I64, I64, I64, I64, I64,
                                      P, I64, P, P, I32, P, I32, P, P, I32, I32, I32, I32, I32, I32, P],

@@ -38,7 +38,7 @@ def gemm_2d(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     n = weight.shape[0]
     if (ops.skinny_gemm_supports(m, n, k) and k <= ops.SKINNY_GEMM_PAIR_MAX_K and weight.is_contiguous()
             and x.stride(1) == 1 and x.stride(0) % 8 == 0 and _aligned16(x, weight)):
-        return ops.skinny_gemm(x, weight)
+        return ops.skinny_gemm(x, weight, overlap=ops.chain_flags())
     return F.linear(x, weight)
 
 
@@ -79,7 +79,7 @@ def lm_head_argmax(hidden: torch.Tensor, weight: torch.Tensor, last_only: bool =
         ids = torch.empty(rows.shape[0], dtype=torch.int64, device=hidden.device)
         for r0 in range(0, rows.shape[0], ops.SKINNY_GEMM_MAX_M):
             r1 = min(r0 + ops.SKINNY_GEMM_MAX_M, rows.shape[0])
-            ops.lm_head_argmax(rows[r0:r1], weight, ws, out=ids[r0:r1])
+            ops.lm_head_argmax(rows[r0:r1], weight, ws, out=ids[r0:r1], overlap=ops.chain_flags())
     else:
         ids = glue.lm_head_argmax(rows, weight, last_only=False)
     return ids[0].clone() if last_only else ids
@@ -107,7 +107,7 @@ def qwen_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6) -> to
     _require_cuda(x, weight)
     strides_ok = all(s % 8 == 0 for s in x.stride()[:-1])
     if d_model % 256 == 0 and d_model <= 8192 and strides_ok and _aligned16(x, weight):
-        return ops.add_rmsnorm(x, weight, eps)
+        return ops.add_rmsnorm(x, weight, eps, overlap=ops.chain_flags())
     return glue.qwen_rmsnorm(x, weight, eps).contiguous()
 
 

@@ -631,6 +631,22 @@ def gdn_chunked_prefill_packed(q, k, v, beta, g, cu_seqlens, max_seqlen=None, fu
 # with START); PREFETCH = gdn_decode_fused may load its states before the kernel in front of it has finished.
 OVERLAP_START, OVERLAP_TRIGGER, OVERLAP_PREFETCH = 1, 2, 4
 
+_chain_enabled = True
+
+
+def set_chain_overlap(enabled: bool) -> None:
+    """Switch the chained launches of the small decode-step operators on or off, process-wide (b200_set_chain_overlap);
+    on by default.  Off, every operator is launched plainly and `chain_flags()` is 0."""
+    global _chain_enabled
+    _chain_enabled = bool(enabled)
+    _lib.call("b200_set_chain_overlap", int(_chain_enabled))
+
+
+def chain_flags() -> int:
+    """Overlap flags for an operator that is called as one link of a chain of this package's kernels by a caller that
+    knows nothing about its neighbours (the drop-in operators): start early, let the successor start early."""
+    return OVERLAP_START | OVERLAP_TRIGGER if _chain_enabled else 0
+
 
 def add_rmsnorm(x, weight, eps: float, residual=None, overlap: int = 0):
     """Qwen RMSNorm `x * rsqrt(mean(x^2) + eps) * (1 + weight)` over the last dim (triton_kernels/qwen_rmsnorm.py:70-73),

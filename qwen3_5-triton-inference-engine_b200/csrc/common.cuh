@@ -31,6 +31,7 @@ int fail(int code, const char* fmt, ...);
 int check_launch(const char* what);
 int sm_count();
 int* wait_timeout_flag();  // device address of the per-device "a bounded wait ran out" word
+bool chain_overlap();      // whether the small decode-step kernels are launched for programmatic dependent launch
 
 #define B200_REQUIRE(cond, ...)                    \
   do {                                             \
@@ -158,6 +159,14 @@ constexpr int OVERLAP_START = 1, OVERLAP_TRIGGER = 2, OVERLAP_PREFETCH = 4;
 // invariant to the compiler, which may hoist them above the wait (seen on the device: a stale projection row).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// First statement of the small decode-step kernels (the operators a runner calls one after the other, each a few
+// microseconds long): the successor in the stream may be scheduled now, and this kernel touches global memory only after
+// its predecessor has completed.  Launched without the attribute (chain_overlap() off) both are no-ops.  The kernels
+// that use it take their inputs through plain pointers, never `const __restrict__` (see the note above).
+__device__ __forceinline__ void pdl_chain() {
+  pdl_trigger();
+  pdl_wait();
+}
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(bool early_start, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,

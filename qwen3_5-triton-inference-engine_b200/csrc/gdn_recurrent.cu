@@ -62,11 +62,12 @@ __device__ __forceinline__ void gdn_token_update(float (&s)[GDN_D], const float*
 }
 
 __global__ void __launch_bounds__(GDN_THREADS)
-gdn_decode_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_b, int64_t q_h, const __nv_bfloat16* __restrict__ k,
-                  int64_t k_b, int64_t k_h, const __nv_bfloat16* __restrict__ v, int64_t v_b, int64_t v_h,
-                  const float* __restrict__ beta, int64_t be_b, int64_t be_h, const float* __restrict__ g, int64_t g_b,
-                  int64_t g_h, float* __restrict__ state, int64_t s_b, int64_t s_h, __nv_bfloat16* __restrict__ out,
+gdn_decode_kernel(const __nv_bfloat16* q, int64_t q_b, int64_t q_h, const __nv_bfloat16* k,
+                  int64_t k_b, int64_t k_h, const __nv_bfloat16* v, int64_t v_b, int64_t v_h,
+                  const float* beta, int64_t be_b, int64_t be_h, const float* g, int64_t g_b,
+                  int64_t g_h, float* state, int64_t s_b, int64_t s_h, __nv_bfloat16* out,
                   int64_t o_b, int64_t o_h, int heads) {
+  pdl_chain();
   __shared__ __align__(16) float kf[GDN_D];
   __shared__ __align__(16) float qf[GDN_D];
   const int b = blockIdx.x / heads, h = blockIdx.x % heads, col = threadIdx.x;
@@ -94,11 +95,12 @@ gdn_decode_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_b, int64_t q_h,
 constexpr int GDN_SLICE = 32;
 
 __global__ void __launch_bounds__(GDN_SLICE, 8)
-gdn_decode_slice_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_b, int64_t q_h, const __nv_bfloat16* __restrict__ k,
-                        int64_t k_b, int64_t k_h, const __nv_bfloat16* __restrict__ v, int64_t v_b, int64_t v_h,
-                        const float* __restrict__ beta, int64_t be_b, int64_t be_h, const float* __restrict__ g,
-                        int64_t g_b, int64_t g_h, float* __restrict__ state, int64_t s_b, int64_t s_h,
-                        __nv_bfloat16* __restrict__ out, int64_t o_b, int64_t o_h, int heads) {
+gdn_decode_slice_kernel(const __nv_bfloat16* q, int64_t q_b, int64_t q_h, const __nv_bfloat16* k,
+                        int64_t k_b, int64_t k_h, const __nv_bfloat16* v, int64_t v_b, int64_t v_h,
+                        const float* beta, int64_t be_b, int64_t be_h, const float* g,
+                        int64_t g_b, int64_t g_h, float* state, int64_t s_b, int64_t s_h,
+                        __nv_bfloat16* out, int64_t o_b, int64_t o_h, int heads) {
+  pdl_chain();
   __shared__ __align__(16) float kf[GDN_D];
   __shared__ __align__(16) float qf[GDN_D];
   constexpr int SLICES = GDN_D / GDN_SLICE;
@@ -258,6 +260,7 @@ constexpr int gdn_ring_smem() { return STAGES * GDN_D * COLS * 4 + 128; }
 template <int COLS, int THREADS, int STAGES, int CTAS>
 __global__ void __launch_bounds__(THREADS + 32, CTAS)
 gdn_decode_ring_kernel(const __grid_constant__ GdnRingParams p, const __grid_constant__ CUtensorMap map_state) {
+  pdl_chain();
   constexpr int GROUPS = THREADS / COLS, ROWS = GDN_D / GROUPS, PER_HEAD = GDN_D / COLS, BOX = GDN_D * COLS;
   static_assert(THREADS >= GDN_D && THREADS % COLS == 0 && ROWS % 4 == 0, "ring kernel shape");
   extern __shared__ __align__(128) uint8_t ring_raw[];
@@ -452,7 +455,8 @@ static int launch_ring(GdnRingParams p, const float* state, int heads_total, cud
   p.items = heads_total * (GDN_D / COLS);
   const int slots = CTAS * sm_count();
   const int grid = p.items < slots ? p.items : slots;
-  gdn_decode_ring_kernel<COLS, THREADS, STAGES, CTAS><<<grid, THREADS + 32, SMEM, stream>>>(p, map);
+  launch_pdl(chain_overlap(), gdn_decode_ring_kernel<COLS, THREADS, STAGES, CTAS>, dim3(grid), dim3(THREADS + 32), SMEM, stream,
+             p, map);
   return OK;
 }
 
@@ -549,15 +553,16 @@ extern "C" int b200_gdn_recurrent_decode(const void* q, int64_t q_stride_b, int6
   }
   // the one-warp slices keep the SMs evenly loaded and shorten the last wave; q and k rows must allow 8-byte loads
   if (form == 2) {
-    gdn_decode_slice_kernel<<<static_cast<unsigned>(items) * (GDN_D / GDN_SLICE), GDN_SLICE, 0,
-                              reinterpret_cast<cudaStream_t>(stream)>>>(
+    launch_pdl(chain_overlap(), gdn_decode_slice_kernel, dim3(static_cast<unsigned>(items) * (GDN_D / GDN_SLICE)), dim3(GDN_SLICE), 0, reinterpret_cast<cudaStream_t>(stream),
+             
         static_cast<const __nv_bfloat16*>(q), q_stride_b, q_stride_h, static_cast<const __nv_bfloat16*>(k), k_stride_b,
         k_stride_h, static_cast<const __nv_bfloat16*>(v), v_stride_b, v_stride_h, beta, beta_stride_b, beta_stride_h, g,
         g_stride_b, g_stride_h, state, state_stride_b, state_stride_h, static_cast<__nv_bfloat16*>(out), out_stride_b,
         out_stride_h, num_heads);
     return check_launch("gdn_recurrent_decode");
   }
-  gdn_decode_kernel<<<static_cast<unsigned>(batch) * num_heads, GDN_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(chain_overlap(), gdn_decode_kernel, dim3(static_cast<unsigned>(batch) * num_heads), dim3(GDN_THREADS), 0, reinterpret_cast<cudaStream_t>(stream),
+             
       static_cast<const __nv_bfloat16*>(q), q_stride_b, q_stride_h, static_cast<const __nv_bfloat16*>(k), k_stride_b,
       k_stride_h, static_cast<const __nv_bfloat16*>(v), v_stride_b, v_stride_h, beta, beta_stride_b, beta_stride_h, g,
       g_stride_b, g_stride_h, state, state_stride_b, state_stride_h, static_cast<__nv_bfloat16*>(out), out_stride_b,

@@ -90,12 +90,13 @@ swiglu_kernel(const __nv_bfloat16* gate, int64_t gate_stride, const __nv_bfloat1
 // ------------------------------------------------------------------------------- GDN decode: conv + norms + gates
 // CTA = (head, sequence), thread t = channel t of the head's q, k and v slices of the [3*H*128] conv width.
 __global__ void __launch_bounds__(GDN_D)
-gdn_decode_prep_kernel(const __nv_bfloat16* __restrict__ qkv, int64_t qkv_stride, __nv_bfloat16* __restrict__ conv_state,
-                       const __nv_bfloat16* __restrict__ w4, const __nv_bfloat16* __restrict__ a, int64_t a_stride,
-                       const __nv_bfloat16* __restrict__ b, int64_t b_stride, const float* __restrict__ a_log,
-                       const __nv_bfloat16* __restrict__ dt_bias, __nv_bfloat16* __restrict__ q_out,
-                       __nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ v_out, float* __restrict__ beta,
-                       float* __restrict__ g, int heads) {
+gdn_decode_prep_kernel(const __nv_bfloat16* qkv, int64_t qkv_stride, __nv_bfloat16* conv_state,
+                       const __nv_bfloat16* w4, const __nv_bfloat16* a, int64_t a_stride,
+                       const __nv_bfloat16* b, int64_t b_stride, const float* a_log,
+                       const __nv_bfloat16* dt_bias, __nv_bfloat16* q_out,
+                       __nv_bfloat16* k_out, __nv_bfloat16* v_out, float* beta,
+                       float* g, int heads) {
+  pdl_chain();
   __shared__ float red[2][4];
   const int h = blockIdx.x, seq = blockIdx.y, t = threadIdx.x;
   const int width = 3 * heads * GDN_D;
@@ -139,8 +140,9 @@ gdn_decode_prep_kernel(const __nv_bfloat16* __restrict__ qkv, int64_t qkv_stride
 
 // ------------------------------------------------------------------------------------------- gated RMSNorm (GDN)
 __global__ void __launch_bounds__(128)
-gdn_gated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ z, int64_t z_stride,
-                         const float* __restrict__ weight, __nv_bfloat16* __restrict__ out, int rows, int heads) {
+gdn_gated_rmsnorm_kernel(const __nv_bfloat16* x, const __nv_bfloat16* z, int64_t z_stride,
+                         const float* weight, __nv_bfloat16* out, int rows, int heads) {
+  pdl_chain();
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (row >= rows) return;
   const int n = row / heads, h = row % heads;
@@ -260,9 +262,10 @@ extern "C" int b200_swiglu_pair(const void* gate, int64_t gate_stride, const voi
   int blocks = static_cast<int>((vecs + 255) / 256);
   const int cap = sm_count() * 8;
   if (blocks > cap) blocks = cap;
-  if (launch_pdl(false, swiglu_kernel, dim3(blocks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+  const bool chain = chain_overlap();
+  if (launch_pdl(chain, swiglu_kernel, dim3(blocks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
                  static_cast<const __nv_bfloat16*>(gate), gate_stride, static_cast<const __nv_bfloat16*>(up), up_stride,
-                 static_cast<__nv_bfloat16*>(out), rows, width, 0) != cudaSuccess)
+                 static_cast<__nv_bfloat16*>(out), rows, width, chain ? OVERLAP_TRIGGER : 0) != cudaSuccess)
     return fail(ERR_LAUNCH, "swiglu_pair: %s", cudaGetErrorString(cudaGetLastError()));
   return check_launch("swiglu_pair");
 }
@@ -274,7 +277,8 @@ extern "C" int b200_gdn_decode_prep(const void* qkv, int64_t qkv_stride, void* c
                                     b200_stream_t stream) {
   B200_REQUIRE(batch > 0 && batch <= 65535 && num_heads > 0 && head_dim == GDN_D,
                "gdn_decode_prep: head_dim must be %d (got %d)", GDN_D, head_dim);
-  gdn_decode_prep_kernel<<<dim3(num_heads, batch), GDN_D, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(chain_overlap(), gdn_decode_prep_kernel, dim3(num_heads, batch), dim3(GDN_D), 0, reinterpret_cast<cudaStream_t>(stream),
+             
       static_cast<const __nv_bfloat16*>(qkv), qkv_stride, static_cast<__nv_bfloat16*>(conv_state),
       static_cast<const __nv_bfloat16*>(weight4), static_cast<const __nv_bfloat16*>(a), a_stride,
       static_cast<const __nv_bfloat16*>(b), b_stride, a_log, static_cast<const __nv_bfloat16*>(dt_bias),
@@ -290,7 +294,8 @@ extern "C" int b200_gdn_gated_rmsnorm(const void* x, const void* z, int64_t z_st
   B200_REQUIRE(z_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(x) % 8 == 0) && (reinterpret_cast<uintptr_t>(z) % 8 == 0) &&
                    (reinterpret_cast<uintptr_t>(out) % 8 == 0) && aligned16(weight),
                "gdn_gated_rmsnorm: x, z, out must be 8-byte aligned, weight 16-byte aligned, z stride a multiple of 4");
-  gdn_gated_rmsnorm_kernel<<<(rows + 3) / 4, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(chain_overlap(), gdn_gated_rmsnorm_kernel, dim3((rows + 3) / 4), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream),
+             
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(z), z_stride, weight,
       static_cast<__nv_bfloat16*>(out), rows, num_heads);
   return check_launch("gdn_gated_rmsnorm");

@@ -2,6 +2,8 @@
 // Pure byte movement: results are bit-exact with the reference's
 // triton_kernels/gqa_attention_decode_paged.py:175-250 (append) and :397-489 (fill).
 #include "b200_attn.h"
+
+#include <atomic>
 #include "common.cuh"
 
 namespace b200 {
@@ -38,6 +40,10 @@ int* wait_timeout_flag() {
   }
   return cached[dev];
 }
+// Process-wide switch for the chained launches of the small decode-step kernels (on unless switched off).
+static std::atomic<int> g_chain_overlap{1};
+bool chain_overlap() { return g_chain_overlap.load(std::memory_order_relaxed) != 0; }
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;
@@ -51,12 +57,13 @@ int sm_count() {
 }
 
 // One CTA per (sequence, kv head).  Row = d bf16 elements, moved as 16-byte words.
-__global__ void paged_kv_append_kernel(__nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+__global__ void paged_kv_append_kernel(__nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
                                        int64_t kc_p, int64_t kc_h, int64_t kc_s, int64_t vc_p, int64_t vc_h,
-                                       int64_t vc_s, const __nv_bfloat16* __restrict__ k_new, int64_t kn_b,
-                                       int64_t kn_h, const __nv_bfloat16* __restrict__ v_new, int64_t vn_b,
-                                       int64_t vn_h, const int32_t* __restrict__ block_table, int64_t bt_b,
-                                       const int64_t* __restrict__ pos, int d, int vec_ok) {
+                                       int64_t vc_s, const __nv_bfloat16* k_new, int64_t kn_b,
+                                       int64_t kn_h, const __nv_bfloat16* v_new, int64_t vn_b,
+                                       int64_t vn_h, const int32_t* block_table, int64_t bt_b,
+                                       const int64_t* pos, int d, int vec_ok) {
+  pdl_chain();
   const int b = blockIdx.x, h = blockIdx.y;
   const int64_t p = pos[b];
   const int64_t lp = p / PAGE, slot = p % PAGE;
@@ -121,6 +128,11 @@ using namespace b200;
 extern "C" const char* b200_last_error(void) { return g_error; }
 extern "C" int b200_abi_version(void) { return B200_ABI_VERSION; }
 
+extern "C" int b200_set_chain_overlap(int32_t enabled) {
+  g_chain_overlap.store(enabled ? 1 : 0);
+  return OK;
+}
+
 extern "C" int b200_wait_timed_out(void) {
   int* flag = wait_timeout_flag();
   if (!flag) return -1;
@@ -142,7 +154,8 @@ extern "C" int b200_paged_kv_append(void* k_cache, void* v_cache, int64_t kc_str
                      mult8(head_dim) && mult8(kc_stride_p) && mult8(kc_stride_h) && mult8(kc_stride_s) &&
                      mult8(vc_stride_p) && mult8(vc_stride_h) && mult8(vc_stride_s) && mult8(kn_stride_b) &&
                      mult8(kn_stride_h) && mult8(vn_stride_b) && mult8(vn_stride_h);
-  paged_kv_append_kernel<<<dim3(batch, num_kv_heads), 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(chain_overlap(), paged_kv_append_kernel, dim3(batch, num_kv_heads), dim3(32), 0, reinterpret_cast<cudaStream_t>(stream),
+             
       static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), kc_stride_p, kc_stride_h,
       kc_stride_s, vc_stride_p, vc_stride_h, vc_stride_s, static_cast<const __nv_bfloat16*>(k_new), kn_stride_b,
       kn_stride_h, static_cast<const __nv_bfloat16*>(v_new), vn_stride_b, vn_stride_h, block_table, bt_stride_b, pos,

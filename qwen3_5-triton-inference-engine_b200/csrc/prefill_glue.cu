@@ -75,9 +75,10 @@ conv4_prefill_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_stride_t, co
 // One token per sequence: state[b] (the last 4 conv INPUT rows) shifts up by one row, x[b] becomes row 3, then the same
 // sum over the 4 rows.  grid = (sequence, 1024-channel block).
 __global__ void __launch_bounds__(CONV_THREADS)
-conv4_decode_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_stride_b, __nv_bfloat16* __restrict__ state,
-                    const __nv_bfloat16* __restrict__ w4, __nv_bfloat16* __restrict__ out, int64_t out_stride_b,
+conv4_decode_kernel(const __nv_bfloat16* x, int64_t x_stride_b, __nv_bfloat16* state,
+                    const __nv_bfloat16* w4, __nv_bfloat16* out, int64_t out_stride_b,
                     int channels) {
+  pdl_chain();
   const int c = (blockIdx.y * CONV_THREADS + threadIdx.x) * 8;
   if (c >= channels) return;
   const int b = blockIdx.x;
@@ -129,12 +130,13 @@ conv_state_pack_kernel(__nv_bfloat16* __restrict__ state, const __nv_bfloat16* _
 // One warp per (token, head) row of 128: q_n = q * rsqrt(sum q^2 + 1e-6) * 128^-0.5, k_n = k * rsqrt(sum k^2 + 1e-6),
 // both rounded to bf16; beta = sigmoid(b), g = -exp(a_log) * softplus(a + dt_bias) in fp32.
 __global__ void __launch_bounds__(128)
-gdn_qk_norm_gates_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_t, int64_t q_h,
-                         const __nv_bfloat16* __restrict__ k, int64_t k_t, int64_t k_h,
-                         const __nv_bfloat16* __restrict__ a, int64_t a_t, const __nv_bfloat16* __restrict__ b,
-                         int64_t b_t, const float* __restrict__ a_log, const __nv_bfloat16* __restrict__ dt_bias,
-                         __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out, float* __restrict__ beta,
-                         float* __restrict__ g, int64_t rows, int heads) {
+gdn_qk_norm_gates_kernel(const __nv_bfloat16* q, int64_t q_t, int64_t q_h,
+                         const __nv_bfloat16* k, int64_t k_t, int64_t k_h,
+                         const __nv_bfloat16* a, int64_t a_t, const __nv_bfloat16* b,
+                         int64_t b_t, const float* a_log, const __nv_bfloat16* dt_bias,
+                         __nv_bfloat16* q_out, __nv_bfloat16* k_out, float* beta,
+                         float* g, int64_t rows, int heads) {
+  pdl_chain();
   const int64_t row = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -168,8 +170,9 @@ gdn_qk_norm_gates_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_t, int64
 // ------------------------------------------------------------------------------------------- gather / residual add
 template <typename IdT>
 __global__ void __launch_bounds__(256)
-embedding_gather_kernel(const IdT* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
-                        __nv_bfloat16* __restrict__ out, int tokens, int dim) {
+embedding_gather_kernel(const IdT* ids, const __nv_bfloat16* table,
+                        __nv_bfloat16* out, int tokens, int dim) {
+  pdl_chain();
   const int vecs = dim >> 3;
   const int64_t total = static_cast<int64_t>(tokens) * vecs;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * 256) {
@@ -181,8 +184,9 @@ embedding_gather_kernel(const IdT* __restrict__ ids, const __nv_bfloat16* __rest
 }
 
 __global__ void __launch_bounds__(256)
-residual_add_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ r,
-                    __nv_bfloat16* __restrict__ out, int64_t n) {
+residual_add_kernel(const __nv_bfloat16* x, const __nv_bfloat16* r,
+                    __nv_bfloat16* out, int64_t n) {
+  pdl_chain();
   const int64_t vecs = n >> 3;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < vecs; i += static_cast<int64_t>(gridDim.x) * 256) {
     float a[8], b[8], o[8];
@@ -233,7 +237,8 @@ extern "C" int b200_conv4_decode(const void* x, int64_t x_stride_b, void* state,
                "conv4_decode: pointers must be 16-byte aligned with row strides that are multiples of 8 elements");
   const dim3 grid(batch, (channels / 8 + CONV_THREADS - 1) / CONV_THREADS);
   B200_REQUIRE(grid.y <= 65535, "conv4_decode: too many channels (%d)", channels);
-  conv4_decode_kernel<<<grid, CONV_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(chain_overlap(), conv4_decode_kernel, dim3(grid), dim3(CONV_THREADS), 0, reinterpret_cast<cudaStream_t>(stream),
+             
       static_cast<const __nv_bfloat16*>(x), x_stride_b, static_cast<__nv_bfloat16*>(state),
       static_cast<const __nv_bfloat16*>(weight4), static_cast<__nv_bfloat16*>(out), out_stride_b, channels);
   return check_launch("conv4_decode");
@@ -265,7 +270,8 @@ extern "C" int b200_gdn_qk_norm_gates(const void* q, int64_t q_stride_t, int64_t
                    q_stride_t % 4 == 0 && q_stride_h % 4 == 0 && k_stride_t % 4 == 0 && k_stride_h % 4 == 0,
                "gdn_qk_norm_gates: q, k and the outputs must be 8-byte aligned with strides that are multiples of 4");
   const int64_t rows = static_cast<int64_t>(tokens) * num_heads;
-  gdn_qk_norm_gates_kernel<<<static_cast<unsigned>((rows + 3) / 4), 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(chain_overlap(), gdn_qk_norm_gates_kernel, dim3(static_cast<unsigned>((rows + 3) / 4)), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream),
+             
       static_cast<const __nv_bfloat16*>(q), q_stride_t, q_stride_h, static_cast<const __nv_bfloat16*>(k), k_stride_t,
       k_stride_h, static_cast<const __nv_bfloat16*>(a), a_stride_t, static_cast<const __nv_bfloat16*>(b), b_stride_t,
       a_log, static_cast<const __nv_bfloat16*>(dt_bias), static_cast<__nv_bfloat16*>(q_out),
@@ -279,11 +285,13 @@ extern "C" int b200_embedding_gather(const void* ids, int32_t ids_are_int64, con
                "embedding_gather: dim must be a multiple of 8 (got %d), table and out 16-byte aligned", dim);
   const int blocks = grid_for(static_cast<int64_t>(tokens) * (dim / 8), 256);
   if (ids_are_int64)
-    embedding_gather_kernel<int64_t><<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+    launch_pdl(chain_overlap(), embedding_gather_kernel<int64_t>, dim3(blocks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+             
         static_cast<const int64_t*>(ids), static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out),
         tokens, dim);
   else
-    embedding_gather_kernel<int32_t><<<blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+    launch_pdl(chain_overlap(), embedding_gather_kernel<int32_t>, dim3(blocks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+             
         static_cast<const int32_t*>(ids), static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out),
         tokens, dim);
   return check_launch("embedding_gather");
@@ -292,7 +300,8 @@ extern "C" int b200_embedding_gather(const void* ids, int32_t ids_are_int64, con
 extern "C" int b200_residual_add(const void* x, const void* residual, void* out, int64_t count, b200_stream_t stream) {
   B200_REQUIRE(count > 0 && aligned16(x) && aligned16(residual) && aligned16(out),
                "residual_add: pointers must be 16-byte aligned");
-  residual_add_kernel<<<grid_for(count / 8 + 1, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(chain_overlap(), residual_add_kernel, dim3(grid_for(count / 8 + 1, 256)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+             
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(out),
       count);
   return check_launch("residual_add");

@@ -9,11 +9,12 @@ namespace b200 {
 
 // One thread per (b, h, t, column-pair or tail element).  Columns [0,R/2) pair with [R/2,R); angles are
 // pos(fp32) * inv_freq in fp32 with full-range sinf/cosf (positions reach 32768 rad at inv_freq = 1).
-__global__ void partial_rope_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_b, int64_t x_h, int64_t x_t,
-                                    __nv_bfloat16* __restrict__ out, int64_t o_b, int64_t o_h, int64_t o_t,
-                                    const void* __restrict__ position_ids, int ids_are_int64, int64_t id_b,
-                                    int64_t id_t, const float* __restrict__ inv_freq, int batch, int heads,
+__global__ void partial_rope_kernel(const __nv_bfloat16* x, int64_t x_b, int64_t x_h, int64_t x_t,
+                                    __nv_bfloat16* out, int64_t o_b, int64_t o_h, int64_t o_t,
+                                    const void* position_ids, int ids_are_int64, int64_t id_b,
+                                    int64_t id_t, const float* inv_freq, int batch, int heads,
                                     int tokens, int d, int r) {
+  pdl_chain();
   const int half = r / 2;
   const int per_row = half + (d - r);  // work items per (b,h,t) row
   const int64_t total = static_cast<int64_t>(batch) * heads * tokens * per_row;
@@ -46,9 +47,10 @@ __global__ void partial_rope_kernel(const __nv_bfloat16* __restrict__ x, int64_t
 }
 
 // out[t, h*D + d] = bf16(x[h,t,d] * sigmoid(gate[h,t,d])) with fp32 math; 8 elements per thread when aligned.
-__global__ void gate_pack_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_h, int64_t x_t,
-                                 const __nv_bfloat16* __restrict__ gate, int64_t g_h, int64_t g_t,
-                                 __nv_bfloat16* __restrict__ out, int heads, int tokens, int d, int vec_ok) {
+__global__ void gate_pack_kernel(const __nv_bfloat16* x, int64_t x_h, int64_t x_t,
+                                 const __nv_bfloat16* gate, int64_t g_h, int64_t g_t,
+                                 __nv_bfloat16* out, int heads, int tokens, int d, int vec_ok) {
+  pdl_chain();
   const int step = vec_ok ? 8 : 1;
   const int per_row = d / step;
   const int64_t total = static_cast<int64_t>(tokens) * heads * per_row;
@@ -96,7 +98,8 @@ extern "C" int b200_partial_rope(const void* x, int64_t x_stride_b, int64_t x_st
   const int threads = 256;
   const int64_t want = (total + threads - 1) / threads;
   const unsigned grid = static_cast<unsigned>(want < 1 ? 1 : (want > 148 * 16 ? 148 * 16 : want));
-  partial_rope_kernel<<<grid, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(chain_overlap(), partial_rope_kernel, dim3(grid), dim3(threads), 0, reinterpret_cast<cudaStream_t>(stream),
+             
       static_cast<const __nv_bfloat16*>(x), x_stride_b, x_stride_h, x_stride_t, static_cast<__nv_bfloat16*>(out),
       out_stride_b, out_stride_h, out_stride_t, position_ids, ids_are_int64, ids_stride_b, ids_stride_t, inv_freq,
       batch, num_heads, num_tokens, head_dim, rotary_dim);
@@ -113,7 +116,8 @@ extern "C" int b200_attention_gate_pack(const void* x, int64_t x_stride_h, int64
   const int threads = 256;
   const int64_t want = (total + threads - 1) / threads;
   const unsigned grid = static_cast<unsigned>(want < 1 ? 1 : (want > 148 * 16 ? 148 * 16 : want));
-  gate_pack_kernel<<<grid, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(chain_overlap(), gate_pack_kernel, dim3(grid), dim3(threads), 0, reinterpret_cast<cudaStream_t>(stream),
+             
       static_cast<const __nv_bfloat16*>(x), x_stride_h, x_stride_t, static_cast<const __nv_bfloat16*>(gate),
       gate_stride_h, gate_stride_t, static_cast<__nv_bfloat16*>(out), num_heads, num_tokens, head_dim, vec_ok);
   return check_launch("attention_gate_pack");

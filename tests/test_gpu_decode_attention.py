@@ -345,3 +345,40 @@ def test_overlapped_decode_attention_in_graph_equals_plain(ops):
     for x, y in zip(plain[0], fast[0]):
         assert torch.equal(x, y)
     assert torch.equal(plain[1], fast[1]) and torch.equal(plain[2], fast[2]) and torch.equal(plain[3], fast[3])
+
+
+def test_chained_launches_change_nothing_but_time(ops):
+    """The small decode-step operators are launched for programmatic dependent launch by default; the same chain with
+    the switch off must give the same bytes (rope x2 -> append -> split -> combine -> gate-pack, three rounds so that
+    every kernel also runs behind a kernel of its own kind)."""
+    lengths = [700, 33, 2100, 512, 16, 1]
+    c = make_paged_case(lengths, seed=77)
+    inv = rope_inv_freq().to(DEV)
+    d = to_dev(c)
+    b = len(lengths)
+    ids = d["pos"].view(b, 1)
+    gate4 = d["gate"].view(b, 8, 256).permute(1, 0, 2).unsqueeze(0)
+
+    def chain(k_cache, v_cache):
+        outs = []
+        for _ in range(3):
+            q4 = ops.partial_rope(d["q"].unsqueeze(2), ids, inv, 64)
+            k4 = ops.partial_rope(d["k_new"].unsqueeze(2), ids, inv, 64)
+            ctx = ops.call_paged_gqa_attention_decode_triton(q4[:, :, 0, :], k4[:, :, 0, :], d["v_new"], k_cache, v_cache,
+                                                             d["block_table"], d["pos"])
+            outs.append(ops.attention_gate_pack(ctx.permute(1, 0, 2).unsqueeze(0), gate4))
+        torch.cuda.synchronize()
+        return outs
+
+    kc1, vc1 = d["k_cache"].clone(), d["v_cache"].clone()
+    chained = chain(kc1, vc1)
+    ops.set_chain_overlap(False)
+    try:
+        kc2, vc2 = d["k_cache"].clone(), d["v_cache"].clone()
+        plain = chain(kc2, vc2)
+    finally:
+        ops.set_chain_overlap(True)
+    for a, p in zip(chained, plain):
+        assert torch.equal(a, p)
+    assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    no_timeouts()
