@@ -169,6 +169,32 @@ def test_gdn_decode_every_kernel_form(ops, form, batch):
     no_timeouts()
 
 
+@pytest.mark.parametrize("form", [0, 2, 3])
+def test_gdn_decode_state_inside_a_larger_buffer(ops, form):
+    """A recurrent state that is a view into a wider allocation (one spare head per sequence) is not the dense layout
+    the ring form needs: the size-based choice takes the one-warp slices, a pinned ring falls back to one CTA per head.
+    The spare heads must stay untouched."""
+    from b200attn import _lib
+    batch, heads = 5, 16
+    gen = torch.Generator().manual_seed(321)
+    q, k, v, beta, g = gdn_inputs(batch, heads, gen)
+    state = torch.randn(batch, heads, 128, 128, generator=gen) * 0.1
+    wide = torch.full((batch, heads + 1, 128, 128), 7.0, device=DEV)
+    wide[:, :heads] = state.to(DEV)
+    view = wide[:, :heads]
+    assert not view.is_contiguous()
+    _lib.call("b200_gdn_recurrent_decode_form", form)
+    try:
+        out = ops.gdn_recurrent_decode(q.to(DEV), k.to(DEV), v.to(DEV), beta.to(DEV), g.to(DEV), view)
+    finally:
+        _lib.call("b200_gdn_recurrent_decode_form", 0)
+    ref_state, ref_out = _flat_step(state, q, k, v, beta, g)
+    assert maxabs(out, ref_out) <= TOL and maxabs(view, ref_state) <= 1e-5
+    assert bool((wide[:, heads] == 7.0).all())
+    torch.cuda.synchronize()
+    no_timeouts()
+
+
 def test_config4_gdn_layer_prefill_then_512_decode_steps(ops):
     """Chunk-64 prefill over 32 packed prompts of 128 tokens on the tensor cores against the oracle's chunk pipeline,
     then 512 single-token steps at B=32 from that state against the oracle recurrence (fresh inputs per step, seed 3):
