@@ -40,6 +40,7 @@ constexpr float PU_TAU = 8.0f;                      // lazy-rescale threshold (l
 constexpr float PU_LOG2E = 1.4426950408889634f;
 
 struct PrefillUmmaParams {
+  int num_kv_heads, batch_wide_order;
   __nv_bfloat16* out;
   int64_t out_t, out_h;
   const int32_t* cu_seqlens;
@@ -77,39 +78,53 @@ rope_scatter_kernel(const __nv_bfloat16* __restrict__ k, int64_t k_t, int64_t k_
   const int partner = first ? lane + lanes_half : lane - lanes_half;
   const int dbase = (in_rot ? (first ? lane : partner) : 0) * 8;
   const float freq = lane < rotary_half ? inv_freq[lane] : 0.f;  // rotary_half <= 32: one angle per lane
-  for (int slot = warp; slot < PAGE; slot += 4) {
+  // a warp's four token rows (slots warp, warp + 4, ...): every row's loads are requested before the first is used
+  constexpr int ROWS = PAGE / 4;
+  uint4 kraw[ROWS], vraw[ROWS];
+  int64_t pid[ROWS];
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) {
+    const int tok = lp * PAGE + warp + 4 * i;
+    if (tok < seq_len) {
+      const int64_t t = seq_start + tok;
+      kraw[i] = *reinterpret_cast<const uint4*>(k + t * k_t + h * k_h + lane * 8);
+      vraw[i] = *reinterpret_cast<const uint4*>(v + t * v_t + h * v_h + lane * 8);
+      pid[i] = rotary_half == 0 ? 0
+               : ids_are_int64 ? static_cast<const int64_t*>(position_ids)[t]
+                               : static_cast<int64_t>(static_cast<const int32_t*>(position_ids)[t]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < ROWS; ++i) {
+    const int slot = warp + 4 * i;
     const int tok = lp * PAGE + slot;
     if (tok >= seq_len) break;
     const int64_t t = seq_start + tok;
-    const uint4 kraw = *reinterpret_cast<const uint4*>(k + t * k_t + h * k_h + lane * 8);
-    const uint4 vraw = *reinterpret_cast<const uint4*>(v + t * v_t + h * v_h + lane * 8);
-    uint32_t kw[4] = {kraw.x, kraw.y, kraw.z, kraw.w};
+    uint32_t kw[4] = {kraw[i].x, kraw[i].y, kraw[i].z, kraw[i].w};
     if (rotary_half > 0) {
-      const int64_t pid = ids_are_int64 ? static_cast<const int64_t*>(position_ids)[t]
-                                        : static_cast<int64_t>(static_cast<const int32_t*>(position_ids)[t]);
       // the warp computes the row's angles once, one sincosf per lane, and hands them round by shuffles (the same
       // full-range sincosf of float(pos) * inv_freq as before, so the rotated bytes do not change)
       float sn = 0.f, cs = 1.f;
-      if (lane < rotary_half) sincosf(static_cast<float>(pid) * freq, &sn, &cs);
+      if (lane < rotary_half) sincosf(static_cast<float>(pid[i]) * freq, &sn, &cs);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t other = __shfl_sync(0xffffffffu, kw[i], in_rot ? partner : lane);
-        const float s0 = __shfl_sync(0xffffffffu, sn, dbase + 2 * i), c0 = __shfl_sync(0xffffffffu, cs, dbase + 2 * i);
-        const float s1 = __shfl_sync(0xffffffffu, sn, dbase + 2 * i + 1), c1 = __shfl_sync(0xffffffffu, cs, dbase + 2 * i + 1);
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t other = __shfl_sync(0xffffffffu, kw[j], in_rot ? partner : lane);
+        const float s0 = __shfl_sync(0xffffffffu, sn, dbase + 2 * j), c0 = __shfl_sync(0xffffffffu, cs, dbase + 2 * j);
+        const float s1 = __shfl_sync(0xffffffffu, sn, dbase + 2 * j + 1), c1 = __shfl_sync(0xffffffffu, cs, dbase + 2 * j + 1);
         if (in_rot) {
-          const uint32_t fa = first ? kw[i] : other;
-          const uint32_t fb = first ? other : kw[i];
+          const uint32_t fa = first ? kw[j] : other;
+          const uint32_t fb = first ? other : kw[j];
           float f0, g0, f1, g1;
           rope_pair(bf16_lo(fa), bf16_lo(fb), s0, c0, f0, g0);
           rope_pair(bf16_hi(fa), bf16_hi(fb), s1, c1, f1, g1);
-          kw[i] = first ? pack_bf16(f0, f1) : pack_bf16(g0, g1);
+          kw[j] = first ? pack_bf16(f0, f1) : pack_bf16(g0, g1);
         }
       }
     }
     const uint4 krot = make_uint4(kw[0], kw[1], kw[2], kw[3]);
     *reinterpret_cast<uint4*>(k_cache + phys * kc_p + h * kc_h + slot * kc_s + lane * 8) = krot;
     *reinterpret_cast<uint4*>(k_rot + (t * num_kv_heads + h) * HEAD_DIM + lane * 8) = krot;
-    *reinterpret_cast<uint4*>(v_cache + phys * vc_p + h * vc_h + slot * vc_s + lane * 8) = vraw;
+    *reinterpret_cast<uint4*>(v_cache + phys * vc_p + h * vc_h + slot * vc_s + lane * 8) = vraw[i];
   }
 }
 
@@ -126,8 +141,15 @@ varlen_causal_umma_kernel(const __grid_constant__ CUtensorMap map_q, const __gri
                                    // between the two threads of a row
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qb = gridDim.x - 1 - blockIdx.x;  // heaviest blocks first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // Two block orders (blocks are scheduled x-fastest).  Batch-wide: grid = (sequences x kv heads, query blocks), so the
+  // whole batch's last (heaviest) query blocks run first, then the ones before them, ... and the one-tile blocks at
+  // the start of every sequence fill the tail: longest-processing-time-first over the launch.  Taken when the K/V of
+  // the whole batch fits the L2 several times over.  Per sequence: grid = (query blocks, kv heads, sequences), heaviest
+  // block of a sequence first; the CTAs that run together then share one or two sequences' K/V tiles in the L2.
+  const bool batch_wide = p.batch_wide_order != 0;
+  const int qb = batch_wide ? gridDim.y - 1 - blockIdx.y : gridDim.x - 1 - blockIdx.x;
+  const int h = batch_wide ? blockIdx.x % p.num_kv_heads : blockIdx.y;
+  const int b = batch_wide ? blockIdx.x / p.num_kv_heads : blockIdx.z;
   const int seq_start = p.cu_seqlens[b];
   const int seq_len = p.cu_seqlens[b + 1] - seq_start;
   const int q0 = qb * PU_BQ;
@@ -480,7 +502,15 @@ static int launch_prefill_umma(const void* q, int64_t q_stride_t, int64_t q_stri
   p.err = wait_timeout_flag();
   if (!p.err) return fail(ERR_RUNTIME, "%s: no error flag", what);
   p.scale_log2 = (1.0f / sqrtf(static_cast<float>(HEAD_DIM))) * PU_LOG2E;
-  const dim3 grid((max_seqlen + PU_BQ - 1) / PU_BQ, num_kv_heads, batch);
+  B200_REQUIRE((max_seqlen + PU_BQ - 1) / PU_BQ <= 65535 && batch <= 65535 && num_kv_heads <= 65535,
+               "%s: max_seqlen must be at most %d, batch and heads at most 65535 (got %d, %d, %d)", what, 65535 * PU_BQ,
+               max_seqlen, batch, num_kv_heads);
+  const int q_blocks = (max_seqlen + PU_BQ - 1) / PU_BQ;
+  // K and V of the batch (bf16): below a quarter of the 126 MB L2 every running CTA finds its tiles there whatever the order
+  p.batch_wide_order = static_cast<int64_t>(total_tokens) * num_kv_heads * HEAD_DIM * 4 <= (32ll << 20) ? 1 : 0;
+  p.num_kv_heads = num_kv_heads;
+  const dim3 grid = p.batch_wide_order ? dim3(static_cast<unsigned>(num_kv_heads) * batch, q_blocks, 1)
+                                       : dim3(q_blocks, num_kv_heads, batch);
   // the fused form starts behind its own rope + scatter kernel while that one still runs (see the K producer)
   if (launch_pdl(FUSED, varlen_causal_umma_kernel<FUSED>, grid, dim3(PU_THREADS), PU_SMEM, stream, map_q, map_k, map_v, p) !=
       cudaSuccess)
