@@ -5,7 +5,8 @@
 // attention part is call_paged_gqa_attention_decode_triton, triton_kernels/gqa_attention_decode_paged.py:963-994).
 //
 // Work decomposition ("stream-K over pages").  A unit is one KV page of one (sequence, kv head) segment, plus
-// one extra unit per segment for the token being appended.  All units of all segments form one line that is
+// one extra unit per segment for the token being appended.  All units of all segments form one line (with a gap
+// behind every segment that stands for the cost of stopping at a segment boundary, see Segment) that is
 // cut into equal ranges, one per CTA; the grid is one CTA per SM whatever the batch or the context lengths,
 // and the cut is recomputed on the device from pos[], so the launch is static and CUDA-graph safe.  Inside a
 // CTA the eight warps take the units of a segment piece round-robin, each with a private ring of three
