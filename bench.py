@@ -473,7 +473,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of one CUDA graph")
     ap.add_argument("--no-model", action="store_true", help="skip the whole-model decode measurement (24-layer random-init model)")
     ap.add_argument("--model-steps", type=int, default=512)
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gdn", "gdn_decode", "gemm"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "chain", "prefill", "gdn", "gdn_decode", "gemm"],
                     help="with --kernel-only: which kernel family to run (profiler captures of the other families)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
@@ -504,6 +504,12 @@ def main():
             rows = run_gemm_sweep(ops, device, hbm_peak()[0], args.steps)
         elif args.workload == "gdn_decode":
             rows = run_gdn_decode_rows(ops, device, hbm_peak()[0], args.steps, (args.batch,))
+        elif args.workload == "chain":   # the drop-in operator chain (rope x2, append, split, combine, gate-pack)
+            lengths = draw_lengths(args.batch, "random")
+            w = Workload(lengths, device, max_sets=32)
+            scratch = ops.allocate_split_scratch(HQ, D, batch=args.batch, device=device)
+            ms = time_steps(chain_step(ops, w, scratch), args.steps, 3)
+            rows = [{"op": "decode_chain", "B": args.batch, "us_per_layer": ms * 1e3, "gbs": w.bytes / (ms * 1e-3) / 1e9}]
         else:
             rows = run_prefill_sweep(ops, device, args.steps, only=args.workload)
         if rank == 0:
