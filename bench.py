@@ -209,7 +209,9 @@ def fused_step(ops, w: Workload, ws):
 
 
 def chain_step(ops, w: Workload, scratch):
-    """The reference's launch structure with our drop-in operators: rope x2, append, split, combine, gate-pack."""
+    """The operator calls of the reference runner's decode attention with our drop-in operators: rope x2, the decode
+    symbol `call_paged_gqa_attention_decode_triton` (one launch by default; append, split, combine with
+    ops.DECODE_CALL_ONE_LAUNCH off), gate-pack."""
     d = w.dev
     b = w.batch
     ids = w.pos.view(b, 1)
@@ -784,6 +786,14 @@ def run_sweep(ops, ws, device, peak, steps):
                 ms_c = time_steps(chain_step(ops, w, scratch), steps, 3)
                 row["chain_us_per_layer"] = ms_c * 1e3
                 row["chain_gbs"] = w.bytes / (ms_c * 1e-3) / 1e9
+                # the same operator calls with the runner's decode symbol forced onto the reference's launch structure
+                # (append -> split -> combine through the scratch tensors) instead of its one-launch form
+                ops.DECODE_CALL_ONE_LAUNCH = False
+                try:
+                    ms_s = time_steps(chain_step(ops, w, scratch), steps, 3)
+                finally:
+                    ops.DECODE_CALL_ONE_LAUNCH = True
+                row["chain_split_combine_us"] = ms_s * 1e3
                 del scratch
             rows.append(row)
             del w

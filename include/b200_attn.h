@@ -109,7 +109,9 @@ int b200_paged_decode_combine(const float* m_partial, const float* l_partial, co
  * One launch replaces the chain partial_rope x2 -> paged_kv_append -> split -> combine -> attention_gate_pack of
  * engine/runner.py:482-517 (call_paged_gqa_attention_decode_triton, gqa_attention_decode_paged.py:963-994).
  * q [B,H_q,256], k_new/v_new [B,H_kv,256], gate [B, H_q*256] (row stride gate_stride_b), out [B, H_q*256] bf16
- * contiguous; inv_freq [rotary_dim/2] fp32; rotary_dim is 64 (the model's) or 0 = no rotation.  The pools must be
+ * contiguous; inv_freq [rotary_dim/2] fp32; rotary_dim is 64 (the model's) or 0 = no rotation; gate may be NULL:
+ * out is then bf16(acc / l), what the reference's combine kernel returns (with rotary_dim 0 the call is
+ * call_paged_gqa_attention_decode_triton itself: append + attention, one launch instead of three).  The pools must be
  * the dense [num_pages, H_kv, 16, 256] layout (pages are fetched by tensor-map TMA, one 8 KiB box per page and head).
  * workspace: b200_fused_decode_workspace_bytes() bytes of device memory, 256-byte aligned, zero-filled ONCE by
  * the caller before the first use (the kernel leaves it zeroed again); calls sharing a workspace must not

@@ -191,9 +191,58 @@ def paged_kv_fill(k_cache, v_cache, k_prefill, v_prefill, block_table) -> None:
     paged_kv_fill_varlen(k_cache, v_cache, k_prefill, v_prefill, block_table.reshape(1, -1), cu, token_num)
 
 
+# How `call_paged_gqa_attention_decode_triton` runs: True = for four sequences or more, one launch of the fused decode
+# kernel without RoPE and gate (append + attention; `scratch` stays untouched); False = always the reference's three
+# launches append -> split -> combine through `scratch` (which one or two sequences always take: three chained 2-5 us
+# launches are quicker there than the fused kernel's cluster launch).
+DECODE_CALL_ONE_LAUNCH = True
+_decode_call_ws: dict = {}   # device index -> workspace of the one-launch form (zero-filled once, left zero by every call)
+
+
+def _one_launch_decode_ok(q, k_new, v_new, k_cache, v_cache, block_table, pos) -> bool:
+    """The shape and layout rules of b200_fused_decode_attention_static."""
+    batch, hq, d = q.shape
+    hkv = k_new.shape[1]
+    return (d == 256 and hq == 4 * hkv and 8 <= batch * hkv <= 2048 and batch <= 512 and k_cache.is_contiguous()
+            and v_cache.is_contiguous() and k_cache.shape[1:] == (hkv, PAGE_SIZE, d) and v_cache.shape == k_cache.shape
+            and q.stride(2) == 1 and k_new.stride(2) == 1 and v_new.stride(2) == 1
+            and all(t.data_ptr() % 16 == 0 for t in (q, k_new, v_new))
+            and all(st % 8 == 0 for t in (q, k_new, v_new) for st in t.stride()[:2])
+            and block_table.stride(1) == 1 and pos.is_contiguous())
+
+
 def call_paged_gqa_attention_decode_triton(q, k_new, v_new, k_cache, v_cache, block_table, pos, scratch=None):
-    """append -> split -> combine, the symbol engine/runner.py:508-510 calls.
-    triton_kernels/gqa_attention_decode_paged.py:963-994 (the name is kept for drop-in use; no Triton is involved)."""
+    """append -> attention over the pos[b]+1 cached tokens, the symbol engine/runner.py:508-510 calls
+    (triton_kernels/gqa_attention_decode_paged.py:963-994; the name is kept for drop-in use, no Triton is involved).
+    q and k_new arrive rotated; returns [B, H_q, D] bf16.  By default this is ONE launch of the fused decode kernel (no
+    RoPE, no gate): the reference's split-K partials (4 KiB written and read per split, a third of the KV bytes at
+    B = 256) never exist.  With DECODE_CALL_ONE_LAUNCH off, or for layouts the fused kernel does not take, it is the
+    reference's three launches append -> split -> combine through `scratch`."""
+    if DECODE_CALL_ONE_LAUNCH and _one_launch_decode_ok(q, k_new, v_new, k_cache, v_cache, block_table, pos):
+        batch, hq, d = q.shape
+        hkv = k_new.shape[1]
+        _require_cuda(q, k_new, v_new, k_cache, v_cache, block_table, pos)
+        assert q.dtype == k_new.dtype == v_new.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
+        assert block_table.dtype == torch.int32 and pos.dtype == torch.int64 and pos.shape == (batch,)
+        out = torch.empty((batch, hq, d), dtype=torch.bfloat16, device=q.device)
+        ws = _decode_call_ws.get(q.device.index)
+        if ws is None and not torch.cuda.is_current_stream_capturing():
+            ws = _decode_call_ws[q.device.index] = fused_decode_workspace(q.device)
+        if ws is None:
+            # first call on this device inside a stream capture: nothing may be allocated, the library's static workspace
+            # (cleared on the stream before the launch) serves instead
+            _lib.call("b200_fused_decode_attention_static", _ptr(q), q.stride(0), q.stride(1), _ptr(k_new),
+                      k_new.stride(0), k_new.stride(1), _ptr(v_new), v_new.stride(0), v_new.stride(1), None, 0,
+                      _ptr(k_cache), _ptr(v_cache), k_cache.stride(0), k_cache.stride(1), k_cache.stride(2),
+                      v_cache.stride(0), v_cache.stride(1), v_cache.stride(2), k_cache.shape[0], _ptr(block_table),
+                      block_table.stride(0), _ptr(pos), None, 0, _ptr(out), batch, hq, hkv, d, _stream())
+            return out
+        _lib.call("b200_fused_decode_attention_ex", _ptr(q), q.stride(0), q.stride(1), _ptr(k_new), k_new.stride(0),
+                  k_new.stride(1), _ptr(v_new), v_new.stride(0), v_new.stride(1), None, 0, _ptr(k_cache), _ptr(v_cache),
+                  k_cache.stride(0), k_cache.stride(1), k_cache.stride(2), v_cache.stride(0), v_cache.stride(1),
+                  v_cache.stride(2), k_cache.shape[0], _ptr(block_table), block_table.stride(0), _ptr(pos), None, 0,
+                  _ptr(out), _ptr(ws), batch, hq, hkv, d, None, None, 1e-6, chain_flags(), 0, _stream())
+        return out
     if scratch is None:
         scratch = allocate_split_scratch(q.shape[1], q.shape[2], batch=q.shape[0], device=q.device)
     m_partial, l_partial, acc_partial = scratch

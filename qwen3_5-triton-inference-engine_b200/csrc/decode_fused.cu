@@ -233,10 +233,16 @@ __device__ __forceinline__ void stage_new_v(uint8_t* v_tile, const FusedDecodePa
   *reinterpret_cast<uint4*>(p.v_cache + phys * p.vc_p + h * p.vc_h + (pos_b % PAGE) * p.vc_s + lane * 8) = vraw;
 }
 
-// out = bf16( bf16(acc / l) * sigmoid(gate) ), 4 consecutive dims of one head per thread.
+// out = bf16( bf16(acc / l) * sigmoid(gate) ), 4 consecutive dims of one head per thread; without a gate (p.gate NULL)
+// out = bf16(acc / l), the output of the reference's combine kernel.
 __device__ __forceinline__ void finish_store(const FusedDecodeParams& p, int b, int hq, int d0, const float (&acc)[4],
                                              float l, uint2 gv) {
   const int64_t col = static_cast<int64_t>(hq) * HEAD_DIM + d0;
+  if (p.gate == nullptr) {
+    const int64_t row = static_cast<int64_t>(p.num_kv_heads) * GROUP * HEAD_DIM;
+    *reinterpret_cast<uint2*>(p.out + b * row + col) = make_uint2(pack_bf16(acc[0] / l, acc[1] / l), pack_bf16(acc[2] / l, acc[3] / l));
+    return;
+  }
   const float inv_l = 1.f / l;
   const float x0 = round_bf16(acc[0] * inv_l), x1 = round_bf16(acc[1] * inv_l);
   const float x2 = round_bf16(acc[2] * inv_l), x3 = round_bf16(acc[3] * inv_l);
@@ -540,8 +546,9 @@ fused_decode_kernel(const __grid_constant__ FusedDecodeParams p, const __grid_co
     const int np = seg.end - seg.start - 1;
     const int64_t pos_b = pos_s[seg.b];
     // the gate row of this segment is only needed at the very end: fetch it now, off the critical path
-    const uint2 gate_pf = *reinterpret_cast<const uint2*>(p.gate + seg.b * p.gate_b +
-                                                           static_cast<int64_t>(seg.h * GROUP + hh) * HEAD_DIM + d0);
+    const uint2 gate_pf = p.gate == nullptr ? make_uint2(0, 0)
+                                            : *reinterpret_cast<const uint2*>(p.gate + seg.b * p.gate_b +
+                                                                              static_cast<int64_t>(seg.h * GROUP + hh) * HEAD_DIM + d0);
     // rotated Q of the NEXT piece goes to the other buffer while this piece streams (published by the merge barriers)
     // (its rows were asked into the L2 one piece earlier: a load that misses there queues behind the page copies)
     if (seg.end + gap < r1) {  // another segment starts inside the range

@@ -30,7 +30,10 @@ def no_timeouts():
 
 
 # --------------------------------------------------------------------------- KV writers (bit-exact)
-def test_append_and_chain_cfg1_golden(ops, golden):
+def test_append_and_chain_cfg1_golden(ops, golden, monkeypatch):
+    """The runner's decode symbol against the reference's own outputs on config 1: in its three-launch form the scratch
+    tensors must hold the reference's partials; in its one-launch form only the result and the caches are compared."""
+    monkeypatch.setattr(ops, "DECODE_CALL_ONE_LAUNCH", False)
     g = golden("paged_decode_cfg1")
     d = to_dev(g)
     kc, vc = d["k_cache_in"].clone(), d["v_cache_in"].clone()
@@ -54,6 +57,15 @@ def test_append_and_chain_cfg1_golden(ops, golden):
     assert maxabs(out, g["out"]) <= 2 ** -7
     exact = O.paged_decode_exact(g["q"], g["k_cache_out"], g["v_cache_out"], g["block_table"], (g["pos"] + 1).tolist())
     assert maxabs(out, exact) < TOL
+    monkeypatch.setattr(ops, "DECODE_CALL_ONE_LAUNCH", True)
+    kc1, vc1 = d["k_cache_in"].clone(), d["v_cache_in"].clone()
+    out1 = ops.call_paged_gqa_attention_decode_triton(d["q"], d["k_new"], d["v_new"], kc1, vc1, d["block_table"], d["pos"],
+                                                      (m, l, acc))
+    torch.cuda.synchronize()
+    no_timeouts()
+    assert torch.equal(kc1.cpu(), g["k_cache_out"]) and torch.equal(vc1.cpu(), g["v_cache_out"])
+    assert maxabs(out1, g["out"]) <= 2 ** -7 and maxabs(out1, exact) < TOL
+    assert torch.equal(m.cpu(), mc) and torch.equal(acc.cpu(), ac)   # the one-launch form leaves the scratch alone
 
 
 @pytest.mark.parametrize("lengths", [[16], [17], [1], [16, 16], [7, 100, 1, 64], [128] * 8, [1, 1, 1, 1000]])
@@ -118,8 +130,13 @@ def test_append_strided_inputs_bit_exact(ops):
 
 
 # --------------------------------------------------------------------------- drop-in split / combine
+@pytest.mark.parametrize("one_launch", [False, True])
 @pytest.mark.parametrize("lengths", [[0], [15], [16], [1, 17, 255, 256, 2047, 2048], [4095, 33, 2100, 512], [6000]])
-def test_decode_chain_vs_oracle(ops, lengths):
+def test_decode_chain_vs_oracle(ops, lengths, one_launch, monkeypatch):
+    """`call_paged_gqa_attention_decode_triton` in both of its forms: the reference's three launches through the scratch
+    tensors (whose contents are then the reference's partial layout) and the single launch of the fused kernel without
+    RoPE and gate (which leaves the scratch alone)."""
+    monkeypatch.setattr(ops, "DECODE_CALL_ONE_LAUNCH", one_launch)
     c = make_paged_case(lengths, seed=100 + len(lengths) + lengths[0])
     d = to_dev(c)
     kc, vc = d["k_cache"].clone(), d["v_cache"].clone()
@@ -133,8 +150,11 @@ def test_decode_chain_vs_oracle(ops, lengths):
     assert torch.equal(kc.cpu(), kr) and torch.equal(vc.cpu(), vr)
     exact = O.paged_decode_exact(c["q"], kr, vr, c["block_table"], (c["pos"] + 1).tolist())
     assert maxabs(out, exact) < TOL
-    # inactive splits hold (-inf, 0, 0), like the reference kernel leaves them
     m, l, acc = (t.cpu() for t in scratch)
+    if one_launch and len(lengths) >= 4:   # one or two sequences always take the three launches
+        assert bool((m == 3.0).all() and (l == 3.0).all() and (acc == 3.0).all())
+        return
+    # inactive splits hold (-inf, 0, 0), like the reference kernel leaves them
     for b, n in enumerate(lengths):
         _, _, _, active = O.split_geometry(n)
         assert torch.isinf(m[b, :, active:]).all() and (l[b, :, active:] == 0).all() and (acc[b, :, active:] == 0).all()
