@@ -367,10 +367,13 @@ def test_overlapped_decode_attention_in_graph_equals_plain(ops):
     assert torch.equal(plain[1], fast[1]) and torch.equal(plain[2], fast[2]) and torch.equal(plain[3], fast[3])
 
 
-def test_chained_launches_change_nothing_but_time(ops):
+@pytest.mark.parametrize("one_launch", [False, True])
+def test_chained_launches_change_nothing_but_time(ops, one_launch, monkeypatch):
     """The small decode-step operators are launched for programmatic dependent launch by default; the same chain with
-    the switch off must give the same bytes (rope x2 -> append -> split -> combine -> gate-pack, three rounds so that
-    every kernel also runs behind a kernel of its own kind)."""
+    the switch off must give the same bytes (rope x2 -> append -> split -> combine -> gate-pack, or rope x2 -> the
+    one-launch decode symbol -> gate-pack; three rounds so that every kernel also runs behind a kernel of its own
+    kind)."""
+    monkeypatch.setattr(ops, "DECODE_CALL_ONE_LAUNCH", one_launch)
     lengths = [700, 33, 2100, 512, 16, 1]
     c = make_paged_case(lengths, seed=77)
     inv = rope_inv_freq().to(DEV)
