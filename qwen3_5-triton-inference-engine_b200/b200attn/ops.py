@@ -217,7 +217,8 @@ def call_paged_gqa_attention_decode_triton(q, k_new, v_new, k_cache, v_cache, bl
     q and k_new arrive rotated; returns [B, H_q, D] bf16.  By default this is ONE launch of the fused decode kernel (no
     RoPE, no gate): the reference's split-K partials (4 KiB written and read per split, a third of the KV bytes at
     B = 256) never exist.  With DECODE_CALL_ONE_LAUNCH off, or for layouts the fused kernel does not take, it is the
-    reference's three launches append -> split -> combine through `scratch`."""
+    reference's three launches append -> split -> combine through `scratch`.  The one-launch form keeps one workspace
+    per device: like the reference's runner, call it from one stream at a time."""
     if DECODE_CALL_ONE_LAUNCH and _one_launch_decode_ok(q, k_new, v_new, k_cache, v_cache, block_table, pos):
         batch, hq, d = q.shape
         hkv = k_new.shape[1]
