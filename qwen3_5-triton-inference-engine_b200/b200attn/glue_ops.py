@@ -485,3 +485,10 @@ def call_gqa_attention_decode_split_triton(q, k_new, v_new, k_cache, v_cache, pa
         q.unsqueeze(0), k_new.unsqueeze(0), v_new.unsqueeze(0), kc, vc, table, pos.view(1),
         (m_partial.unsqueeze(0), l_partial.unsqueeze(0), acc_partial.unsqueeze(0)))
     return out[0]
+
+
+# eager callers reach the implementations directly; the registered operators stay available as `<name>.op` and under
+# torch.ops.wy_lib (see _direct.py)
+from ._direct import rebind as _rebind  # noqa: E402
+
+_rebind(globals())

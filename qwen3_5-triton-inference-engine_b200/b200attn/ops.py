@@ -20,7 +20,12 @@ GDN_CHUNK = 64
 GDN_DIM = 128      # key and value dim the Gated-DeltaNet kernels are specialised for
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)   # the handle without building a Stream object
+
+
 def _stream():
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -870,3 +875,10 @@ def skinny_gemm(x, weight, overlap: int = 0, swiglu: bool = False):
     _lib.call("b200_skinny_gemm_swiglu" if swiglu else "b200_skinny_gemm", _ptr(x), x.stride(0), _ptr(weight), _ptr(y),
               y.stride(0), m, n, k, int(overlap), _stream())
     return y
+
+
+# eager callers reach the implementations directly; the registered operators stay available as `<name>.op` and under
+# torch.ops.wy_lib (see _direct.py)
+from ._direct import rebind as _rebind  # noqa: E402
+
+_rebind(globals())
