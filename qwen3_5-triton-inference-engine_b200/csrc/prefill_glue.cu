@@ -20,56 +20,72 @@ __device__ __forceinline__ void unpack8g(const uint4& v, float (&f)[8]) {
 __device__ __forceinline__ uint4 pack8g(const float (&f)[8]) {
   return make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
 }
-__device__ __forceinline__ float silu_ref(float a) { return a * (1.0f / (1.0f + expf(-a))); }  // acc * sigmoid(acc)
+// acc * sigmoid(acc).  exp through ex2.approx and the division through rcp.approx (2 ulp each - what the reference's
+// Triton kernel itself compiles to on a GPU): the result is rounded to bf16 (8 bits), which these 22-bit-accurate steps
+// move for about one element in a thousand, by one bf16 ulp.
+__device__ __forceinline__ float silu_ref(float a) { return __fdividef(a, 1.0f + __expf(-a)); }
 
 // ---------------------------------------------------------------------------------------- depthwise conv4 + SiLU
 // y[t,c] = silu(sum_r w[c,r] * x[t+r-3, c]); a tap whose row lies before seq_start[t] (the first row of t's own
-// sequence in the packed buffer) reads zero.  CTA = CONV_TOKENS consecutive tokens x 1024 channels; a thread keeps the
-// last three rows of its 8 channels in registers, so every input row is read once per CTA (plus 3 rows of halo).
+// sequence in the packed buffer) reads zero.  One thread = 8 channels of ONE token: it fetches its four input rows
+// itself (the three earlier ones are other threads' current rows and come from the L1 / L2), so there is no loop over
+// tokens, few registers and ~40 resident warps per SM - the arithmetic (34 instructions per element, two of them on the
+// special-function unit) is what the kernel then runs at, not the latency of a token-by-token window.  A warp is one
+// token x 256 channels (512 contiguous bytes per row), a CTA four consecutive tokens.
 constexpr int CONV_THREADS = 128;
-constexpr int CONV_TOKENS = 16;
+constexpr int CONV_TOKENS = CONV_THREADS / 32;  // tokens per CTA (prefill kernel)
 
 __global__ void __launch_bounds__(CONV_THREADS)
 conv4_prefill_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_stride_t, const __nv_bfloat16* __restrict__ w,
                      int64_t w_stride_d, int64_t w_stride_k, const int32_t* __restrict__ seq_start,
                      __nv_bfloat16* __restrict__ out, int64_t out_stride_t, int tokens, int channels) {
-  const int c = (blockIdx.y * CONV_THREADS + threadIdx.x) * 8;
-  if (c >= channels) return;
-  const int t0 = blockIdx.x * CONV_TOKENS;
+  const int t = blockIdx.x * CONV_TOKENS + (threadIdx.x >> 5);
+  const int c = (blockIdx.y * 32 + (threadIdx.x & 31)) * 8;
+  if (t >= tokens || c >= channels) return;
+  const int lower = seq_start != nullptr ? seq_start[t] : 0;
+  uint4 rows[4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int tr = t - 3 + r;
+    rows[r] = tr >= lower ? *reinterpret_cast<const uint4*>(x + static_cast<int64_t>(tr) * x_stride_t + c)
+                          : make_uint4(0, 0, 0, 0);
+  }
   float wt[4][8];
+  if (w_stride_k == 1 && w_stride_d == 4 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+    // [channels, 4] contiguous: the 32 taps of this thread are 64 consecutive bytes
+    const uint4* wp = reinterpret_cast<const uint4*>(w + static_cast<int64_t>(c) * 4);
 #pragma unroll
-  for (int r = 0; r < 4; ++r)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) wt[r][j] = __bfloat162float(w[(c + j) * w_stride_d + r * w_stride_k]);
-  float win[3][8];  // rows t-3, t-2, t-1
-#pragma unroll
-  for (int r = 0; r < 3; ++r) {
-    const int t = t0 - 3 + r;
-    if (t >= 0) unpack8g(*reinterpret_cast<const uint4*>(x + t * x_stride_t + c), win[r]);
-    else
-#pragma unroll
-      for (int j = 0; j < 8; ++j) win[r][j] = 0.f;
-  }
-  const int t1 = min(t0 + CONV_TOKENS, tokens);
-  for (int t = t0; t < t1; ++t) {
-    float cur[8], o[8];
-    unpack8g(*reinterpret_cast<const uint4*>(x + static_cast<int64_t>(t) * x_stride_t + c), cur);
-    const int lower = seq_start != nullptr ? seq_start[t] : 0;
-    const bool ok0 = t - 3 >= lower, ok1 = t - 2 >= lower, ok2 = t - 1 >= lower;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      // the reference sums the four products in tap order
-      float acc = __fmul_rn(ok0 ? win[0][j] : 0.f, wt[0][j]);
-      acc = __fadd_rn(acc, __fmul_rn(ok1 ? win[1][j] : 0.f, wt[1][j]));
-      acc = __fadd_rn(acc, __fmul_rn(ok2 ? win[2][j] : 0.f, wt[2][j]));
-      acc = __fadd_rn(acc, __fmul_rn(cur[j], wt[3][j]));
-      o[j] = silu_ref(acc);
-      win[0][j] = win[1][j];
-      win[1][j] = win[2][j];
-      win[2][j] = cur[j];
+    for (int q = 0; q < 4; ++q) {  // two channels per 16 bytes
+      const uint4 v = wp[q];
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+      wt[0][2 * q] = bf16_lo(u[0]);
+      wt[1][2 * q] = bf16_hi(u[0]);
+      wt[2][2 * q] = bf16_lo(u[1]);
+      wt[3][2 * q] = bf16_hi(u[1]);
+      wt[0][2 * q + 1] = bf16_lo(u[2]);
+      wt[1][2 * q + 1] = bf16_hi(u[2]);
+      wt[2][2 * q + 1] = bf16_lo(u[3]);
+      wt[3][2 * q + 1] = bf16_hi(u[3]);
     }
-    *reinterpret_cast<uint4*>(out + static_cast<int64_t>(t) * out_stride_t + c) = pack8g(o);
+  } else {
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) wt[r][j] = __bfloat162float(w[(c + j) * w_stride_d + r * w_stride_k]);
   }
+  float xr[4][8], o[8];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) unpack8g(rows[r], xr[r]);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    // the reference sums the four products in tap order (its compiled kernel contracts them into fused multiply-adds)
+    float acc = xr[0][j] * wt[0][j];
+    acc = fmaf(xr[1][j], wt[1][j], acc);
+    acc = fmaf(xr[2][j], wt[2][j], acc);
+    acc = fmaf(xr[3][j], wt[3][j], acc);
+    o[j] = silu_ref(acc);
+  }
+  *reinterpret_cast<uint4*>(out + static_cast<int64_t>(t) * out_stride_t + c) = pack8g(o);
 }
 
 // One token per sequence: state[b] (the last 4 conv INPUT rows) shifts up by one row, x[b] becomes row 3, then the same
@@ -220,7 +236,7 @@ extern "C" int b200_conv4_prefill(const void* x, int64_t x_stride_t, const void*
                channels);
   B200_REQUIRE(aligned16(x) && aligned16(out) && x_stride_t % 8 == 0 && out_stride_t % 8 == 0,
                "conv4_prefill: x and out must be 16-byte aligned with row strides that are multiples of 8 elements");
-  const dim3 grid((tokens + CONV_TOKENS - 1) / CONV_TOKENS, (channels / 8 + CONV_THREADS - 1) / CONV_THREADS);
+  const dim3 grid((tokens + CONV_TOKENS - 1) / CONV_TOKENS, (channels / 8 + 31) / 32);
   B200_REQUIRE(grid.y <= 65535, "conv4_prefill: too many channels (%d)", channels);
   conv4_prefill_kernel<<<grid, CONV_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), x_stride_t, static_cast<const __nv_bfloat16*>(weight), w_stride_d, w_stride_k,
