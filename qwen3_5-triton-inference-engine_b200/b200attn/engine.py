@@ -239,11 +239,12 @@ class Engine:
                 k = conv[:, kd: 2 * kd].view(total, heads, dim)
                 v = conv[:, 2 * kd:].view(total, heads, dim)
                 q_n, k_n, beta, g = _qk_norm_gates(q, k, a, b, layer["a_log"], layer["dt_bias"])
-                core, state = ops.gdn_chunked_prefill_packed(q_n, k_n, v, beta, g, cu)
-                put(self.rec_state[i], state)
-                if slots is None:
+                if slots is None:                        # every slot: the kernel writes the cache's own states
+                    core, _ = ops.gdn_chunked_prefill_packed(q_n, k_n, v, beta, g, cu, state_out=self.rec_state[i])
                     _conv_state_pack(self.conv_state[i], qkv, cu)
                 else:
+                    core, state = ops.gdn_chunked_prefill_packed(q_n, k_n, v, beta, g, cu)
+                    put(self.rec_state[i], state)
                     conv_rows = torch.empty((len(prompts),) + tuple(self.conv_state[i].shape[1:]), dtype=torch.bfloat16,
                                             device=self.device)
                     _conv_state_pack(conv_rows, qkv, cu)

@@ -646,21 +646,27 @@ def call_gdn_recurrent_prefill_chunked_triton(q, k, v, beta, g):
     return out, final_state
 
 
-def gdn_chunked_prefill_packed(q, k, v, beta, g, cu_seqlens, max_seqlen=None, fused=True):
+def gdn_chunked_prefill_packed(q, k, v, beta, g, cu_seqlens, max_seqlen=None, fused=True, state_out=None):
     """Chunk-64 Gated-DeltaNet prefill over a PACKED batch (chunks restart at every cu_seqlens[b], zero state at each
     sequence start).  Returns (out [T,H,DV] bf16, state [B,H,DK,DV] fp32).  The reference's chunk path is
     single-sequence only (engine/runner.py:263-267); this is its packed form, equal to
     gdn_recurrent_prefill_sequential(..., cu_seqlens) up to fp32 rounding.
     fused=True: one tcgen05 kernel, state resident in tensor memory, no workspace (q/k/v need token and head strides
     that are multiples of 8 elements).  fused=False: the three reference-shaped stages through a workspace;
-    `max_seqlen` (host int) sizes their grid."""
+    `max_seqlen` (host int) sizes their grid.  `state_out` (contiguous fp32 [B,H,DK,DV]) receives the final states in
+    place of a fresh tensor, e.g. a cache's own state buffer."""
     _check_gdn(q, k, v, beta, g)
     assert cu_seqlens.dtype == torch.int32 and cu_seqlens.ndim == 1 and cu_seqlens.is_cuda
     token_num, num_heads, key_dim = q.shape
     value_dim = v.shape[-1]
     batch = cu_seqlens.numel() - 1
     q, k, v = map(_inner_contiguous, (q, k, v))
-    state = torch.empty((batch, num_heads, key_dim, value_dim), dtype=torch.float32, device=q.device)
+    if state_out is None:
+        state = torch.empty((batch, num_heads, key_dim, value_dim), dtype=torch.float32, device=q.device)
+    else:
+        assert state_out.shape == (batch, num_heads, key_dim, value_dim) and state_out.dtype == torch.float32
+        assert state_out.is_contiguous() and state_out.device == q.device
+        state = state_out
     out = torch.empty((token_num, num_heads, value_dim), dtype=q.dtype, device=q.device)
     if fused:
         cu_seqlens = cu_seqlens.contiguous()  # kept alive until the launch is enqueued

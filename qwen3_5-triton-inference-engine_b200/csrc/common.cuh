@@ -50,6 +50,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+// Row count from which the row-wise operators switch to their prompt-sized forms (more bytes in flight per thread;
+// below it the one-round-trip forms of the decode step have the shorter latency).
+constexpr int GLUE_WIDE_ROWS = 1024;
+// SiLU for the prompt-sized element-wise kernels, whose exact exponential and division would cost as many issue slots
+// as their memory traffic takes time: fast exponential and reciprocal, a few fp32 ulp before the rounding to bf16.
+__device__ __forceinline__ float silu_fast(float a) { return __fdividef(a, 1.0f + __expf(-a)); }
 
 // One RoPE pair with a fixed operation order, so every kernel that rotates produces the same bits.
 __device__ __forceinline__ void rope_pair(float a, float b, float sn, float cs, float& first, float& second) {

@@ -67,6 +67,59 @@ add_rmsnorm_kernel(const __nv_bfloat16* x, int64_t x_outer, int64_t x_inner, int
   *reinterpret_cast<uint4*>(norm_out + static_cast<int64_t>(row) * dim + c) = pack8(o);
 }
 
+// Prompt-sized form: one warp per row, four rows per CTA, lane = VPL 16-byte vectors 32 vectors apart (dim = VPL * 256);
+// no shared memory and no block barrier, and a CTA keeps up to 12 * VPL loads per lane in flight.
+template <int VPL>
+__global__ void __launch_bounds__(128)
+add_rmsnorm_rows_kernel(const __nv_bfloat16* x, int64_t x_outer, int64_t x_inner, int inner_count,
+                        const __nv_bfloat16* residual, int64_t res_stride,
+                        const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ sum_out,
+                        __nv_bfloat16* __restrict__ norm_out, int rows, float eps, int overlap) {
+  constexpr int DIM = VPL * 256;
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (overlap & OVERLAP_TRIGGER) pdl_trigger();
+  uint4 wv[VPL];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) wv[j] = *reinterpret_cast<const uint4*>(weight + (lane + 32 * j) * 8);
+  pdl_wait();
+  if (row >= rows) return;
+  const __nv_bfloat16* src = x + static_cast<int64_t>(row / inner_count) * x_outer + (row % inner_count) * x_inner;
+  uint4 xv[VPL], rv[VPL];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) xv[j] = *reinterpret_cast<const uint4*>(src + (lane + 32 * j) * 8);
+  if (residual != nullptr) {
+#pragma unroll
+    for (int j = 0; j < VPL; ++j)
+      rv[j] = *reinterpret_cast<const uint4*>(residual + static_cast<int64_t>(row) * res_stride + (lane + 32 * j) * 8);
+  }
+  float v[VPL][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    unpack8(xv[j], v[j]);
+    if (residual != nullptr) {
+      float r[8];
+      unpack8(rv[j], r);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[j][e] = round_bf16(v[j][e] + r[e]);  // the sum is a bf16 tensor in the reference
+      if (sum_out != nullptr)
+        *reinterpret_cast<uint4*>(sum_out + static_cast<int64_t>(row) * DIM + (lane + 32 * j) * 8) = pack8(v[j]);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss = fmaf(v[j][e], v[j][e], ss);
+  }
+  ss = warp_sum(ss);
+  const float rs = rsqrtf(ss / static_cast<float>(DIM) + eps);
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    float w[8], o[8];
+    unpack8(wv[j], w);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = v[j][e] * rs * (1.0f + w[e]);
+    *reinterpret_cast<uint4*>(norm_out + static_cast<int64_t>(row) * DIM + (lane + 32 * j) * 8) = pack8(o);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------------- SwiGLU
 __global__ void __launch_bounds__(256)
 swiglu_kernel(const __nv_bfloat16* gate, int64_t gate_stride, const __nv_bfloat16* up, int64_t up_stride,
@@ -84,6 +137,38 @@ swiglu_kernel(const __nv_bfloat16* gate, int64_t gate_stride, const __nv_bfloat1
 #pragma unroll
     for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.0f + expf(-g[j])) * u[j];
     *reinterpret_cast<uint4*>(out + r * inter + c) = pack8(o);
+  }
+}
+
+// Prompt-sized form: thread = one 8-wide column vector of SW_ROWS consecutive rows, every load issued before the first
+// use; no index division; fast exponential and reciprocal.
+constexpr int SW_ROWS = 4;
+constexpr int SW_THREADS = 64;
+
+__global__ void __launch_bounds__(SW_THREADS)
+swiglu_rows_kernel(const __nv_bfloat16* gate, int64_t gate_stride, const __nv_bfloat16* up, int64_t up_stride,
+                   __nv_bfloat16* __restrict__ out, int rows, int inter, int overlap) {
+  if (overlap & OVERLAP_TRIGGER) pdl_trigger();
+  pdl_wait();
+  const int c = (blockIdx.x * SW_THREADS + threadIdx.x) * 8;
+  if (c >= inter) return;
+  const int r0 = blockIdx.y * SW_ROWS;
+  uint4 gv[SW_ROWS], uv[SW_ROWS];
+#pragma unroll
+  for (int j = 0; j < SW_ROWS; ++j) {
+    const int64_t r = min(r0 + j, rows - 1);
+    gv[j] = *reinterpret_cast<const uint4*>(gate + r * gate_stride + c);
+    uv[j] = *reinterpret_cast<const uint4*>(up + r * up_stride + c);
+  }
+#pragma unroll
+  for (int j = 0; j < SW_ROWS; ++j) {
+    if (r0 + j >= rows) break;
+    float g[8], u[8], o[8];
+    unpack8(gv[j], g);
+    unpack8(uv[j], u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = silu_fast(g[e]) * u[e];
+    *reinterpret_cast<uint4*>(out + static_cast<int64_t>(r0 + j) * inter + c) = pack8(o);
   }
 }
 
@@ -161,6 +246,35 @@ gdn_gated_rmsnorm_kernel(const __nv_bfloat16* x, const __nv_bfloat16* z, int64_t
       make_uint2(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]));
 }
 
+// Prompt-sized form (16-byte aligned rows): 16 lanes x 8 elements per row, eight rows per CTA, fast SiLU.
+__global__ void __launch_bounds__(128)
+gdn_gated_rmsnorm_wide_kernel(const __nv_bfloat16* x, const __nv_bfloat16* z, int64_t z_stride,
+                              const float* weight, __nv_bfloat16* out, int rows, int heads) {
+  pdl_chain();
+  const int sub = threadIdx.x & 15;
+  const int row_raw = blockIdx.x * 8 + (threadIdx.x >> 4);
+  const bool live = row_raw < rows;
+  const int row = live ? row_raw : rows - 1;  // a dead half-warp repeats the last row and stores nothing
+  const int n = row / heads, h = row % heads;
+  const uint4 xv = *reinterpret_cast<const uint4*>(x + static_cast<int64_t>(row) * GDN_D + sub * 8);
+  const uint4 zv = *reinterpret_cast<const uint4*>(z + static_cast<int64_t>(n) * z_stride + h * GDN_D + sub * 8);
+  const float4 w0 = *reinterpret_cast<const float4*>(weight + sub * 8);
+  const float4 w1 = *reinterpret_cast<const float4*>(weight + sub * 8 + 4);
+  const float wf[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+  float xf[8], zf[8], o[8];
+  unpack8(xv, xf);
+  unpack8(zv, zf);
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ss = fmaf(xf[j], xf[j], ss);
+#pragma unroll
+  for (int s = 8; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+  const float rs = rsqrtf(ss / static_cast<float>(GDN_D) + 1e-6f);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = xf[j] * rs * wf[j] * silu_fast(zf[j]);
+  if (live) *reinterpret_cast<uint4*>(out + static_cast<int64_t>(row) * GDN_D + sub * 8) = pack8(o);
+}
+
 // ------------------------------------------------------------------------------------------- row arg-max (LM head)
 // ids[r] = argmax_n logits[r, n], ties to the lowest n (triton_kernels/vocab_argmax.py:141-200).  A (value, index)
 // pair is packed into one 64-bit key whose unsigned order is "larger value first, then smaller index"; a CTA reduces
@@ -228,6 +342,17 @@ extern "C" int b200_add_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x
   B200_REQUIRE(residual == nullptr || (aligned16(residual) && residual_stride % 8 == 0 &&
                                        (sum_out == nullptr || aligned16(sum_out))),
                "add_rmsnorm: residual / sum_out must be 16-byte aligned with a row stride that is a multiple of 8");
+  if (rows >= GLUE_WIDE_ROWS && (dim == 256 || dim == 512 || dim == 1024 || dim == 2048)) {
+    const auto kernel = dim == 256 ? add_rmsnorm_rows_kernel<1> : dim == 512 ? add_rmsnorm_rows_kernel<2>
+                      : dim == 1024 ? add_rmsnorm_rows_kernel<4> : add_rmsnorm_rows_kernel<8>;
+    if (launch_pdl((overlap & OVERLAP_START) != 0, kernel, dim3((rows + 3) / 4), dim3(128), 0,
+                   reinterpret_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(x), x_stride_outer,
+                   x_stride_inner, inner_count, static_cast<const __nv_bfloat16*>(residual), residual_stride,
+                   static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(sum_out),
+                   static_cast<__nv_bfloat16*>(norm_out), rows, eps, overlap) != cudaSuccess)
+      return fail(ERR_LAUNCH, "add_rmsnorm: %s", cudaGetErrorString(cudaGetLastError()));
+    return check_launch("add_rmsnorm");
+  }
   if (launch_pdl((overlap & OVERLAP_START) != 0, add_rmsnorm_kernel, dim3(rows), dim3(dim / 8), 0, reinterpret_cast<cudaStream_t>(stream),
                  static_cast<const __nv_bfloat16*>(x), x_stride_outer, x_stride_inner, inner_count,
                  static_cast<const __nv_bfloat16*>(residual), residual_stride, static_cast<const __nv_bfloat16*>(weight),
@@ -236,19 +361,31 @@ extern "C" int b200_add_rmsnorm(const void* x, int64_t x_stride_outer, int64_t x
   return check_launch("add_rmsnorm");
 }
 
+// Decode-sized calls take the flat one-vector-per-thread kernel, prompt-sized ones the row-blocked kernel.
+static cudaError_t launch_swiglu(bool start_early, const __nv_bfloat16* gate, int64_t gate_stride, const __nv_bfloat16* up,
+                                 int64_t up_stride, __nv_bfloat16* out, int rows, int width, int overlap,
+                                 b200_stream_t stream) {
+  const int row_blocks = (rows + SW_ROWS - 1) / SW_ROWS;
+  if (rows >= GLUE_WIDE_ROWS && row_blocks <= 65535)
+    return launch_pdl(start_early, swiglu_rows_kernel, dim3((width / 8 + SW_THREADS - 1) / SW_THREADS, row_blocks),
+                      dim3(SW_THREADS), 0, reinterpret_cast<cudaStream_t>(stream), gate, gate_stride, up, up_stride, out,
+                      rows, width, overlap);
+  const int64_t vecs = static_cast<int64_t>(rows) * (width / 8);
+  int blocks = static_cast<int>((vecs + 255) / 256);
+  const int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  return launch_pdl(start_early, swiglu_kernel, dim3(blocks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), gate,
+                    gate_stride, up, up_stride, out, rows, width, overlap);
+}
+
 extern "C" int b200_swiglu(const void* gate_up, int64_t row_stride, void* out, int32_t rows, int32_t intermediate,
                            int32_t overlap, b200_stream_t stream) {
   B200_REQUIRE(rows > 0 && intermediate > 0 && intermediate % 8 == 0 && row_stride % 8 == 0 && aligned16(gate_up) &&
                    aligned16(out),
                "swiglu: intermediate and the row stride must be multiples of 8, pointers 16-byte aligned");
-  const int64_t vecs = static_cast<int64_t>(rows) * (intermediate / 8);
-  int blocks = static_cast<int>((vecs + 255) / 256);
-  const int cap = sm_count() * 8;
-  if (blocks > cap) blocks = cap;
-  if (launch_pdl((overlap & OVERLAP_START) != 0, swiglu_kernel, dim3(blocks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
-                 static_cast<const __nv_bfloat16*>(gate_up), row_stride,
-                 static_cast<const __nv_bfloat16*>(gate_up) + intermediate, row_stride, static_cast<__nv_bfloat16*>(out),
-                 rows, intermediate, overlap) != cudaSuccess)
+  if (launch_swiglu((overlap & OVERLAP_START) != 0, static_cast<const __nv_bfloat16*>(gate_up), row_stride,
+                    static_cast<const __nv_bfloat16*>(gate_up) + intermediate, row_stride,
+                    static_cast<__nv_bfloat16*>(out), rows, intermediate, overlap, stream) != cudaSuccess)
     return fail(ERR_LAUNCH, "swiglu: %s", cudaGetErrorString(cudaGetLastError()));
   return check_launch("swiglu");
 }
@@ -258,14 +395,10 @@ extern "C" int b200_swiglu_pair(const void* gate, int64_t gate_stride, const voi
   B200_REQUIRE(rows > 0 && width > 0 && width % 8 == 0 && gate_stride % 8 == 0 && up_stride % 8 == 0 && aligned16(gate) &&
                    aligned16(up) && aligned16(out),
                "swiglu_pair: the width and the row strides must be multiples of 8, pointers 16-byte aligned");
-  const int64_t vecs = static_cast<int64_t>(rows) * (width / 8);
-  int blocks = static_cast<int>((vecs + 255) / 256);
-  const int cap = sm_count() * 8;
-  if (blocks > cap) blocks = cap;
   const bool chain = chain_overlap();
-  if (launch_pdl(chain, swiglu_kernel, dim3(blocks), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
-                 static_cast<const __nv_bfloat16*>(gate), gate_stride, static_cast<const __nv_bfloat16*>(up), up_stride,
-                 static_cast<__nv_bfloat16*>(out), rows, width, chain ? OVERLAP_TRIGGER : 0) != cudaSuccess)
+  if (launch_swiglu(chain, static_cast<const __nv_bfloat16*>(gate), gate_stride, static_cast<const __nv_bfloat16*>(up),
+                    up_stride, static_cast<__nv_bfloat16*>(out), rows, width, chain ? OVERLAP_TRIGGER : 0,
+                    stream) != cudaSuccess)
     return fail(ERR_LAUNCH, "swiglu_pair: %s", cudaGetErrorString(cudaGetLastError()));
   return check_launch("swiglu_pair");
 }
@@ -294,8 +427,9 @@ extern "C" int b200_gdn_gated_rmsnorm(const void* x, const void* z, int64_t z_st
   B200_REQUIRE(z_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(x) % 8 == 0) && (reinterpret_cast<uintptr_t>(z) % 8 == 0) &&
                    (reinterpret_cast<uintptr_t>(out) % 8 == 0) && aligned16(weight),
                "gdn_gated_rmsnorm: x, z, out must be 8-byte aligned, weight 16-byte aligned, z stride a multiple of 4");
-  launch_pdl(chain_overlap(), gdn_gated_rmsnorm_kernel, dim3((rows + 3) / 4), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream),
-             
+  const bool wide = rows >= GLUE_WIDE_ROWS && z_stride % 8 == 0 && aligned16(x) && aligned16(z) && aligned16(out);
+  launch_pdl(chain_overlap(), wide ? gdn_gated_rmsnorm_wide_kernel : gdn_gated_rmsnorm_kernel,
+             dim3(wide ? (rows + 7) / 8 : (rows + 3) / 4), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream),
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(z), z_stride, weight,
       static_cast<__nv_bfloat16*>(out), rows, num_heads);
   return check_launch("gdn_gated_rmsnorm");

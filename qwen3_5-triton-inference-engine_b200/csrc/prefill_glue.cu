@@ -23,32 +23,40 @@ __device__ __forceinline__ uint4 pack8g(const float (&f)[8]) {
 // acc * sigmoid(acc).  exp through ex2.approx and the division through rcp.approx (2 ulp each - what the reference's
 // Triton kernel itself compiles to on a GPU): the result is rounded to bf16 (8 bits), which these 22-bit-accurate steps
 // move for about one element in a thousand, by one bf16 ulp.
-__device__ __forceinline__ float silu_ref(float a) { return __fdividef(a, 1.0f + __expf(-a)); }
+__device__ __forceinline__ float silu_ref(float a) { return silu_fast(a); }
 
 // ---------------------------------------------------------------------------------------- depthwise conv4 + SiLU
 // y[t,c] = silu(sum_r w[c,r] * x[t+r-3, c]); a tap whose row lies before seq_start[t] (the first row of t's own
-// sequence in the packed buffer) reads zero.  One thread = 8 channels of ONE token: it fetches its four input rows
-// itself (the three earlier ones are other threads' current rows and come from the L1 / L2), so there is no loop over
-// tokens, few registers and ~40 resident warps per SM - the arithmetic (34 instructions per element, two of them on the
-// special-function unit) is what the kernel then runs at, not the latency of a token-by-token window.  A warp is one
-// token x 256 channels (512 contiguous bytes per row), a CTA four consecutive tokens.
+// sequence in the packed buffer) reads zero.  One thread = 8 channels of CONV_TPT consecutive tokens: it issues its
+// CONV_TPT + 3 row loads and its weight loads before the first use and keeps no loop-carried window, so a thread costs
+// 11 16-byte loads per 4 outputs, the 32 taps are unpacked once per 4 tokens, and ~20 warps per SM stay resident.  A
+// warp is 4 tokens x 256 channels (512 contiguous bytes per row), a CTA 16 consecutive tokens, whose warps find each
+// other's rows in the L1.  Only a thread whose four tokens belong to two sequences takes the masked path.
 constexpr int CONV_THREADS = 128;
-constexpr int CONV_TOKENS = CONV_THREADS / 32;  // tokens per CTA (prefill kernel)
+constexpr int CONV_TPT = 4;                               // tokens per thread (prefill kernel)
+constexpr int CONV_TOKENS = CONV_THREADS / 32 * CONV_TPT;  // tokens per CTA (prefill kernel)
 
 __global__ void __launch_bounds__(CONV_THREADS)
 conv4_prefill_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_stride_t, const __nv_bfloat16* __restrict__ w,
                      int64_t w_stride_d, int64_t w_stride_k, const int32_t* __restrict__ seq_start,
                      __nv_bfloat16* __restrict__ out, int64_t out_stride_t, int tokens, int channels) {
-  const int t = blockIdx.x * CONV_TOKENS + (threadIdx.x >> 5);
+  const int t0 = (blockIdx.x * (CONV_THREADS / 32) + (threadIdx.x >> 5)) * CONV_TPT;
   const int c = (blockIdx.y * 32 + (threadIdx.x & 31)) * 8;
-  if (t >= tokens || c >= channels) return;
-  const int lower = seq_start != nullptr ? seq_start[t] : 0;
-  uint4 rows[4];
+  if (t0 >= tokens || c >= channels) return;
+  int lower[CONV_TPT];
+  int lowest = tokens, highest = 0;
 #pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    const int tr = t - 3 + r;
-    rows[r] = tr >= lower ? *reinterpret_cast<const uint4*>(x + static_cast<int64_t>(tr) * x_stride_t + c)
-                          : make_uint4(0, 0, 0, 0);
+  for (int j = 0; j < CONV_TPT; ++j) {
+    lower[j] = seq_start != nullptr ? max(seq_start[min(t0 + j, tokens - 1)], 0) : 0;
+    lowest = min(lowest, lower[j]);
+    highest = max(highest, lower[j]);
+  }
+  uint4 rows[CONV_TPT + 3];
+#pragma unroll
+  for (int r = 0; r < CONV_TPT + 3; ++r) {
+    const int tr = t0 - 3 + r;
+    rows[r] = (tr >= lowest && tr < tokens) ? *reinterpret_cast<const uint4*>(x + static_cast<int64_t>(tr) * x_stride_t + c)
+                                            : make_uint4(0, 0, 0, 0);
   }
   float wt[4][8];
   if (w_stride_k == 1 && w_stride_d == 4 && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
@@ -73,19 +81,40 @@ conv4_prefill_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_stride_t, co
 #pragma unroll
       for (int j = 0; j < 8; ++j) wt[r][j] = __bfloat162float(w[(c + j) * w_stride_d + r * w_stride_k]);
   }
-  float xr[4][8], o[8];
+  float xr[CONV_TPT + 3][8];
 #pragma unroll
-  for (int r = 0; r < 4; ++r) unpack8g(rows[r], xr[r]);
+  for (int r = 0; r < CONV_TPT + 3; ++r) unpack8g(rows[r], xr[r]);
+  // rows below `lowest` were zeroed as they were loaded, which is the whole mask when all of this thread's tokens belong
+  // to one sequence
+  const bool inside = highest == lowest;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    // the reference sums the four products in tap order (its compiled kernel contracts them into fused multiply-adds)
-    float acc = xr[0][j] * wt[0][j];
-    acc = fmaf(xr[1][j], wt[1][j], acc);
-    acc = fmaf(xr[2][j], wt[2][j], acc);
-    acc = fmaf(xr[3][j], wt[3][j], acc);
-    o[j] = silu_ref(acc);
+  for (int j = 0; j < CONV_TPT; ++j) {
+    const int t = t0 + j;
+    if (t >= tokens) break;
+    float o[8];
+    if (inside) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        // the reference sums the four products in tap order (its compiled kernel contracts them into fused multiply-adds)
+        float acc = xr[j][e] * wt[0][e];
+        acc = fmaf(xr[j + 1][e], wt[1][e], acc);
+        acc = fmaf(xr[j + 2][e], wt[2][e], acc);
+        acc = fmaf(xr[j + 3][e], wt[3][e], acc);
+        o[e] = silu_ref(acc);
+      }
+    } else {
+      const int first = lower[j] - (t - 3);  // taps below `first` lie before the token's own sequence
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float acc = (first <= 0 ? xr[j][e] : 0.f) * wt[0][e];
+        acc = fmaf(first <= 1 ? xr[j + 1][e] : 0.f, wt[1][e], acc);
+        acc = fmaf(first <= 2 ? xr[j + 2][e] : 0.f, wt[2][e], acc);
+        acc = fmaf(first <= 3 ? xr[j + 3][e] : 0.f, wt[3][e], acc);
+        o[e] = silu_ref(acc);
+      }
+    }
+    *reinterpret_cast<uint4*>(out + static_cast<int64_t>(t) * out_stride_t + c) = pack8g(o);
   }
-  *reinterpret_cast<uint4*>(out + static_cast<int64_t>(t) * out_stride_t + c) = pack8g(o);
 }
 
 // One token per sequence: state[b] (the last 4 conv INPUT rows) shifts up by one row, x[b] becomes row 3, then the same
@@ -180,6 +209,68 @@ gdn_qk_norm_gates_kernel(const __nv_bfloat16* q, int64_t q_t, int64_t q_h,
     const float sp = fmaxf(sp_in, 0.f) + logf(1.0f + expf(-fabsf(sp_in)));
     beta[row] = 1.0f / (1.0f + expf(-bv));
     g[row] = -expf(a_log[h]) * sp;
+  }
+}
+
+// The same for prompt-sized inputs (16-byte aligned rows): 16 lanes x 8 elements per row, eight rows per CTA, so each
+// thread has two 16-byte loads in flight; the gates of the CTA's eight rows are computed by its first eight threads,
+// whose a / b loads are issued with the row loads.
+__global__ void __launch_bounds__(128)
+gdn_qk_norm_gates_wide_kernel(const __nv_bfloat16* q, int64_t q_t, int64_t q_h,
+                              const __nv_bfloat16* k, int64_t k_t, int64_t k_h,
+                              const __nv_bfloat16* a, int64_t a_t, const __nv_bfloat16* b,
+                              int64_t b_t, const float* a_log, const __nv_bfloat16* dt_bias,
+                              __nv_bfloat16* q_out, __nv_bfloat16* k_out, float* beta,
+                              float* g, int64_t rows, int heads) {
+  pdl_chain();
+  const int sub = threadIdx.x & 15;
+  const int64_t row_raw = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 4);
+  const bool live = row_raw < rows;
+  const int64_t row = live ? row_raw : rows - 1;  // a dead half-warp repeats the last row and stores nothing
+  const int64_t t = row / heads;
+  const int h = static_cast<int>(row % heads);
+  const uint4 qv = *reinterpret_cast<const uint4*>(q + t * q_t + h * q_h + sub * 8);
+  const uint4 kv = *reinterpret_cast<const uint4*>(k + t * k_t + h * k_h + sub * 8);
+  const int64_t gate_row = static_cast<int64_t>(blockIdx.x) * 8 + threadIdx.x;
+  const bool gate_thread = threadIdx.x < 8 && gate_row < rows;
+  float bv = 0.f, sp_in = 0.f, decay = 0.f;
+  if (gate_thread) {
+    const int64_t gt = gate_row / heads;
+    const int gh = static_cast<int>(gate_row % heads);
+    bv = __bfloat162float(b[gt * b_t + gh]);
+    sp_in = __bfloat162float(a[gt * a_t + gh]) + __bfloat162float(dt_bias[gh]);
+    decay = a_log[gh];
+  }
+  float qf[8], kf[8];
+  unpack8g(qv, qf);
+  unpack8g(kv, kf);
+  float sq = 0.f, sk = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    sq = fmaf(qf[j], qf[j], sq);
+    sk = fmaf(kf[j], kf[j], sk);
+  }
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) {
+    sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    sk += __shfl_xor_sync(0xffffffffu, sk, o);
+  }
+  const float rq = rsqrtf(sq + 1e-6f), rk = rsqrtf(sk + 1e-6f);
+  constexpr float Q_SCALE = 0.08838834764831845f;  // 128^-0.5
+  float qo[8], ko[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    qo[j] = __fmul_rn(__fmul_rn(qf[j], rq), Q_SCALE);
+    ko[j] = __fmul_rn(kf[j], rk);
+  }
+  if (live) {
+    *reinterpret_cast<uint4*>(q_out + row * GDN_D + sub * 8) = pack8g(qo);
+    *reinterpret_cast<uint4*>(k_out + row * GDN_D + sub * 8) = pack8g(ko);
+  }
+  if (gate_thread) {
+    const float sp = fmaxf(sp_in, 0.f) + logf(1.0f + expf(-fabsf(sp_in)));
+    beta[gate_row] = 1.0f / (1.0f + expf(-bv));
+    g[gate_row] = -expf(decay) * sp;
   }
 }
 
@@ -286,8 +377,12 @@ extern "C" int b200_gdn_qk_norm_gates(const void* q, int64_t q_stride_t, int64_t
                    q_stride_t % 4 == 0 && q_stride_h % 4 == 0 && k_stride_t % 4 == 0 && k_stride_h % 4 == 0,
                "gdn_qk_norm_gates: q, k and the outputs must be 8-byte aligned with strides that are multiples of 4");
   const int64_t rows = static_cast<int64_t>(tokens) * num_heads;
-  launch_pdl(chain_overlap(), gdn_qk_norm_gates_kernel, dim3(static_cast<unsigned>((rows + 3) / 4)), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream),
-             
+  const bool wide = rows >= GLUE_WIDE_ROWS && aligned16(q) && aligned16(k) && aligned16(q_out) && aligned16(k_out) &&
+                    q_stride_t % 8 == 0 && q_stride_h % 8 == 0 && k_stride_t % 8 == 0 && k_stride_h % 8 == 0;
+  const auto kernel = wide ? gdn_qk_norm_gates_wide_kernel : gdn_qk_norm_gates_kernel;
+  const int per_cta = wide ? 8 : 4;
+  launch_pdl(chain_overlap(), kernel, dim3(static_cast<unsigned>((rows + per_cta - 1) / per_cta)), dim3(128), 0,
+             reinterpret_cast<cudaStream_t>(stream),
       static_cast<const __nv_bfloat16*>(q), q_stride_t, q_stride_h, static_cast<const __nv_bfloat16*>(k), k_stride_t,
       k_stride_h, static_cast<const __nv_bfloat16*>(a), a_stride_t, static_cast<const __nv_bfloat16*>(b), b_stride_t,
       a_log, static_cast<const __nv_bfloat16*>(dt_bias), static_cast<__nv_bfloat16*>(q_out),

@@ -20,6 +20,16 @@ def _ulp_close(a, b, ulps=1):
     assert bool(((a - b).abs() <= tol).all()), f"max diff {(a - b).abs().max().item()}"
 
 
+def _prompt_close(a, b, what):
+    """Prompt-sized forms (1024 rows and more): a million elements meet bf16 rounding boundaries that a different
+    summation order or the fast exponential moves, so: never more than one bf16 ulp (2^-7 relative) apart, and at most
+    1 % of the elements different at all."""
+    assert a.shape == b.shape and a.dtype == b.dtype
+    _ulp_close(a, b, ulps=2)
+    differing = (a != b).float().mean().item()
+    assert differing <= 0.01, f"{what}: {differing:.4f} of the elements differ"
+
+
 @pytest.mark.parametrize("rows,dim", [(1, 1024), (32, 1024), (257, 256), (5, 2048)])
 def test_add_rmsnorm(mods, rows, dim):
     ops, glue = mods
@@ -32,6 +42,26 @@ def test_add_rmsnorm(mods, rows, dim):
     ref_total = glue.residual_add(x, res)
     assert torch.equal(total, ref_total)
     _ulp_close(norm, glue.qwen_rmsnorm(ref_total, w, 1e-6))
+
+
+@pytest.mark.parametrize("rows,dim", [(1027, 1024), (4096, 256), (1025, 2048), (1030, 512), (1024, 768)])
+def test_add_rmsnorm_prompt_sized(mods, rows, dim):
+    """From 1024 rows the operator runs its warp-per-row form (dims 256 / 512 / 1024 / 2048; 768 stays on the
+    CTA-per-row form): the sum stays bit-exact, the norm within one bf16 ulp."""
+    ops, glue = mods
+    gen = torch.Generator().manual_seed(rows * 7 + dim)
+    x = torch.randn(rows, dim, generator=gen).to(torch.bfloat16).to(DEV)
+    res = torch.randn(rows, dim, generator=gen).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(dim, generator=gen) * 0.1).to(torch.bfloat16).to(DEV)
+    _prompt_close(ops.add_rmsnorm(x, w, 1e-6), glue.qwen_rmsnorm(x, w, 1e-6), "norm")
+    total, norm = ops.add_rmsnorm(x, w, 1e-6, residual=res)
+    ref_total = glue.residual_add(x, res)
+    assert torch.equal(total, ref_total)
+    _prompt_close(norm, glue.qwen_rmsnorm(ref_total, w, 1e-6), "add + norm")
+    fused = torch.randn(131, 5120, generator=gen).to(torch.bfloat16).to(DEV)   # head views: 1048 rows of 256
+    w256 = (torch.randn(256, generator=gen) * 0.1).to(torch.bfloat16).to(DEV)
+    view = fused[:, :2048].view(131, 8, 256)
+    _prompt_close(ops.add_rmsnorm(view, w256, 1e-6), glue.qwen_rmsnorm(view, w256, 1e-6), "head views")
 
 
 def test_rmsnorm_on_head_views(mods):
@@ -53,6 +83,67 @@ def test_swiglu(mods, rows):
     inter = 3584
     gu = (torch.randn(rows, 2 * inter, generator=gen) * 2).to(torch.bfloat16).to(DEV)
     _ulp_close(ops.swiglu_fused(gu, inter), glue.swiglu(gu[:, :inter], gu[:, inter:]))
+
+
+@pytest.mark.parametrize("rows,inter", [(1027, 3584), (1024, 40), (2050, 1000)])
+def test_swiglu_prompt_sized(mods, rows, inter):
+    """From 1024 rows: the row-blocked form with the fast exponential, on the fused [rows, 2*inter] layout and on two
+    separate column views."""
+    ops, glue = mods
+    from b200attn import glue_ops
+    gen = torch.Generator().manual_seed(rows + inter)
+    gu = (torch.randn(rows, 2 * inter, generator=gen) * 2).to(torch.bfloat16).to(DEV)
+    gu[0, :8] = torch.tensor([-200.0, -90.0, -88.0, -30.0, 0.0, 30.0, 90.0, 200.0], dtype=torch.bfloat16)
+    ref = glue.swiglu(gu[:, :inter], gu[:, inter:])
+    _prompt_close(ops.swiglu_fused(gu, inter), ref, "fused layout")
+    _prompt_close(glue_ops.swiglu(gu[:, :inter], gu[:, inter:]), ref, "column views")
+    assert bool(torch.isfinite(ops.swiglu_fused(gu, inter).float()).all())
+
+
+@pytest.mark.parametrize("lengths", [[1, 2, 3, 5, 64, 7, 1, 130], [4] * 9 + [3], [1] * 13, [258], [2, 1]])
+@pytest.mark.parametrize("channels", [6144, 40])
+def test_conv4_prefill_ragged(mods, lengths, channels):
+    """A thread of the packed conv covers four consecutive tokens: sequences shorter than that window, sequence starts
+    at every offset inside it and a token count that is not a multiple of four, against the eager restatement of the
+    reference operator (one bf16 ulp: the kernel uses the fast exponential)."""
+    _, glue = mods
+    from b200attn import glue_ops
+    gen = torch.Generator().manual_seed(sum(lengths) + channels)
+    total = sum(lengths)
+    x = torch.randn(total, channels, generator=gen).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(channels, 4, generator=gen) * 0.5).to(torch.bfloat16).to(DEV)
+    starts = torch.tensor([s for s, n in zip(torch.tensor([0] + lengths[:-1]).cumsum(0).tolist(), lengths)
+                           for _ in range(n)], dtype=torch.int32, device=DEV)
+    ref = glue.depthwise_causal_conv4_prefill(x, w, starts)
+    _prompt_close(glue_ops.depthwise_causal_conv4_prefill(x, w, starts), ref, "packed conv")
+    _prompt_close(glue_ops.depthwise_causal_conv4_prefill(x, w.t().contiguous().t(), starts), ref, "[4,D] weight")
+    if len(lengths) == 1:
+        _prompt_close(glue_ops.depthwise_causal_conv4_prefill(x, w), ref, "no seq_start")
+
+
+@pytest.mark.parametrize("tokens,heads", [(67, 16), (343, 3), (4096, 16)])
+def test_gdn_row_operators_prompt_sized(mods, tokens, heads):
+    """q/k norms + gates and the gated RMSNorm from 1024 (token, head) rows on: 16 lanes per row, eight rows per CTA,
+    including a row count that leaves the last CTA partly empty (343 x 3 = 1029)."""
+    ops, glue = mods
+    from b200attn import glue_ops
+    gen = torch.Generator().manual_seed(tokens + heads)
+    kd = heads * 128
+    fused = torch.randn(tokens, 4 * kd + 32, generator=gen).to(torch.bfloat16).to(DEV)   # rows stay 16-byte aligned
+    a_log = (torch.rand(heads, generator=gen) * 2.7).to(DEV)
+    dt_bias = (torch.randn(heads, generator=gen) * 0.5).to(torch.bfloat16).to(DEV)
+    q, k = fused[:, :kd].view(tokens, heads, 128), fused[:, kd: 2 * kd].view(tokens, heads, 128)
+    a, b = fused[:, 4 * kd: 4 * kd + heads], fused[:, 4 * kd + heads: 4 * kd + 2 * heads]
+    rq, rk, rbeta, rg = glue.gdn_qk_norm_gates(q, k, a, b, a_log, dt_bias)
+    q_n, k_n, beta, g = glue_ops.gdn_qk_norm_gates(q, k, a, b, a_log, dt_bias)
+    _prompt_close(q_n, rq, "q_n")
+    _prompt_close(k_n, rk, "k_n")
+    assert torch.allclose(beta, rbeta, rtol=1e-5, atol=1e-7) and torch.allclose(g, rg, rtol=1e-5, atol=1e-7)
+    x = torch.randn(tokens, heads, 128, generator=gen).to(torch.bfloat16).to(DEV)
+    z = fused[:, 3 * kd: 4 * kd]
+    w = (1 + 0.1 * torch.randn(128, generator=gen)).to(DEV)
+    out = ops.gdn_gated_rmsnorm_fused(x, z, w)
+    _prompt_close(out.view(tokens, heads, 128), glue.gdn_gated_rmsnorm(x, z.reshape(tokens, heads, 128), w), "gated norm")
 
 
 @pytest.mark.parametrize("batch", [1, 32])
