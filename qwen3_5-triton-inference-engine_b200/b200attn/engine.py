@@ -12,6 +12,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import numpy as np
 import torch
 
 from . import glue, glue_ops, ops
@@ -214,10 +215,16 @@ class Engine:
                 dst.copy_(src)
             else:
                 dst.index_copy_(0, slots, src.to(dst.dtype))
-        ids = torch.tensor([t for p in prompts for t in p], dtype=torch.int64).to(self.device)
+        # ids, position inside the sequence and first packed row of the sequence (runner.py:136) for every token, built
+        # on the host and sent as one int32 [3, T] array
+        lens = np.asarray(lengths, dtype=np.int64)
+        first_row = np.repeat(np.cumsum(lens) - lens, lens)
+        host = np.empty((3, int(lens.sum())), dtype=np.int32)
+        host[0] = np.fromiter((t for p in prompts for t in p), dtype=np.int64, count=host.shape[1])
+        host[1] = np.arange(host.shape[1]) - first_row
+        host[2] = first_row
+        ids, pos_in_seq, seq_start = torch.from_numpy(host).to(self.device).unbind(0)
         cu, max_len = ops.build_cu_seqlens(lengths, device=self.device)
-        pos_in_seq = torch.cat([torch.arange(n) for n in lengths]).to(torch.int32).to(self.device)
-        seq_start = torch.repeat_interleave(cu[:-1], torch.tensor(lengths, device=self.device))  # runner.py:136
         total, heads, dim = ids.numel(), cfg.gdn_heads, cfg.gdn_dim
         if not self.fused_glue:
             assert slots is None, "slot-wise prefill runs on the single-launch operators only"
