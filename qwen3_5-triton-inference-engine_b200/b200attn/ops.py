@@ -622,28 +622,33 @@ def _(q, k, delta, g_cumsum, chunk_state):
 _ONE_SEQUENCE_CU: dict = {}
 
 
+# One sequence walks its chunks serially: the single kernel spends ~9 us per chunk on 16 CTAs, the three stages ~3.3 us
+# per chunk in the state stage plus two chunk-parallel stages, which is the shorter way from about 16 chunks on.
+CHUNKED_THREE_STAGE_FROM = 1024
+
+
 def call_gdn_recurrent_prefill_chunked_triton(q, k, v, beta, g):
     """Chunk-64 prefill of ONE sequence; returns (out [T,H,DV] bf16, final_state [H,DK,DV] fp32).
     triton_kernels/gdn_recurrent_prefill.py:1026-1047 (name kept for drop-in use; no Triton is involved).  The caller
-    wants only the output and the final state, so the three stages run as the single tensor-core kernel with
-    cu_seqlens = [0, T] whenever its layout rules hold (128-dim heads, 16-byte aligned q/k/v with strides that are
-    multiples of 8); otherwise as the three reference-shaped operators through their HBM intermediates."""
+    wants only the output and the final state, so up to CHUNKED_THREE_STAGE_FROM tokens the three stages run as the
+    single tcgen05 kernel with cu_seqlens = [0, T] whenever its layout rules hold (128-dim heads, 16-byte aligned
+    q/k/v with strides that are multiples of 8); longer sequences, and inputs outside those rules, take the three
+    reference-shaped stages (tensor-core products, HBM intermediates in one workspace) in one call."""
     token_num = q.shape[0]
     fusable = (q.shape[-1] == GDN_DIM and v.shape[-1] == GDN_DIM
                and all(t.stride(-1) == 1 and t.stride(0) % 8 == 0 and t.stride(1) % 8 == 0 and t.data_ptr() % 16 == 0
                        for t in (q, k, v)))
-    if fusable:
-        key = (q.device.index, token_num)
-        if key not in _ONE_SEQUENCE_CU:
-            if len(_ONE_SEQUENCE_CU) > 4096:
-                _ONE_SEQUENCE_CU.clear()
-            _ONE_SEQUENCE_CU[key] = torch.tensor([0, token_num], dtype=torch.int32, device=q.device)
+    key = (q.device.index, token_num)
+    if key not in _ONE_SEQUENCE_CU:
+        if len(_ONE_SEQUENCE_CU) > 4096:
+            _ONE_SEQUENCE_CU.clear()
+        _ONE_SEQUENCE_CU[key] = torch.tensor([0, token_num], dtype=torch.int32, device=q.device)
+    if fusable and token_num < CHUNKED_THREE_STAGE_FROM:
         out, state = gdn_chunked_prefill_packed(q, k, v, beta, g, _ONE_SEQUENCE_CU[key])
-        return out, state[0]
-    w, u_base, g_cumsum = gdn_chunk_prepare_wy(k, v, beta, g)
-    delta, chunk_state, final_state = gdn_chunk_state(k, w, u_base, g_cumsum)
-    out = gdn_chunk_output(q, k, delta, g_cumsum, chunk_state)
-    return out, final_state
+    else:
+        out, state = gdn_chunked_prefill_packed(q, k, v, beta, g, _ONE_SEQUENCE_CU[key], max_seqlen=token_num,
+                                                fused=False)
+    return out, state[0]
 
 
 def gdn_chunked_prefill_packed(q, k, v, beta, g, cu_seqlens, max_seqlen=None, fused=True, state_out=None):

@@ -6,17 +6,18 @@
 //   L[t,i] = beta_t exp(G_t - G_i) <k_t,k_i> (i<t);  P = (I+L)^-1;  u = P (beta v);  w = P (beta exp(G) k)
 //   delta = u - w S_in;  S_out = exp(G_last) S_in + sum_t k_t (exp(G_last - G_t) delta_t)^T
 //   o_t = exp(G_t) q_t^T S_in + sum_{i<=t} <q_t,k_i> exp(G_t - G_i) delta_i
-// All products are true fp32 FMAs here (the reference needs 3xTF32 to hold its 5e-4 state tolerance; plain fp32
-// is at least as accurate).  These kernels keep the reference's data flow through HBM so that each operator can be
-// swapped individually.
+// The products run on the tensor cores (mma.sync m16n8k16, bf16 inputs, fp32 accumulation): exact bf16 operands for
+// k k^T and q k^T, bf16 pairs hi + lo for every fp32 operand (the reference holds its 5e-4 state tolerance with 3xTF32
+// products of the same accuracy); only the 64 x 64 triangular inverse stays on the CUDA cores.  These kernels keep the
+// reference's data flow through HBM so that each operator can be swapped individually.
 #include "b200_attn.h"
 #include "common.cuh"
+#include "gdn_inverse.cuh"
 
 namespace b200 {
 
 constexpr int GC_THREADS = 256;
-constexpr int GC_PITCH = GDN_D + 4;   // fp32 row pitch of [64][128] tiles (16-byte aligned rows, banks shifted by 4)
-constexpr int GC_LP = CHUNK + 1;      // pitch of [64][64] tiles
+constexpr int GC_LP = INV_LP;         // fp32 pitch of the [64][64] L and inverse tiles
 
 // Where a CTA's chunk lives.  Single sequence (cu_seqlens == nullptr): chunk = blockIdx.x of `token_num` tokens.
 // Packed batch: blockIdx.z = sequence, blockIdx.x = chunk inside it; chunks of all sequences are numbered
@@ -47,8 +48,97 @@ __device__ __forceinline__ ChunkPos locate_chunk(const int32_t* cu_seqlens, int 
   return c;
 }
 
+// ------------------------------------------------------------------------------------------- tensor-core plumbing
+// Every product below is mma.sync m16n8k16 (bf16 inputs, fp32 accumulation) on bf16 tiles in shared memory.  q, k and v
+// are bf16 already, so a product of two of them is exact up to the fp32 accumulation; an fp32 operand (the inverse, w,
+// delta, the state, the decayed attention) is fed as a bf16 pair hi + lo with the cross products hi*hi + hi*lo + lo*hi
+// (hi*hi + lo*hi when the other operand is exact), about 16 mantissa bits per factor - the order of the reference's
+// 3xTF32 products.
+constexpr int GC_P128 = GDN_D + 8;  // bf16 pitch of [rows][128] tiles: 272-byte rows, conflict-free fragment loads
+constexpr int GC_P64 = CHUNK + 8;   // bf16 pitch of [rows][64] tiles
+
+__device__ __forceinline__ uint32_t ld_pair(const __nv_bfloat16* p) { return *reinterpret_cast<const uint32_t*>(p); }
+__device__ __forceinline__ void split_pair(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat16 h0 = __float2bfloat16_rn(x0), h1 = __float2bfloat16_rn(x1);
+  hi = static_cast<uint32_t>(__bfloat16_as_ushort(h0)) | (static_cast<uint32_t>(__bfloat16_as_ushort(h1)) << 16);
+  lo = pack_bf16(x0 - __bfloat162float(h0), x1 - __bfloat162float(h1));
+}
+// A fragment (rows m0..m0+15, k0..k0+15) of a tile stored [M][K], K contiguous
+__device__ __forceinline__ void frag_a(uint32_t (&a)[4], const __nv_bfloat16* A, int pitch, int m0, int k0, int lane) {
+  const __nv_bfloat16* p = A + (m0 + (lane >> 2)) * pitch + k0 + (lane & 3) * 2;
+  a[0] = ld_pair(p);
+  a[1] = ld_pair(p + 8 * pitch);
+  a[2] = ld_pair(p + 8);
+  a[3] = ld_pair(p + 8 * pitch + 8);
+}
+// A fragment of A = T^T for a tile T stored [K][M], M contiguous (transposing ldmatrix)
+__device__ __forceinline__ void frag_a_t(uint32_t (&a)[4], const __nv_bfloat16* T, int pitch, int m0, int k0, int lane) {
+  const int j = lane >> 3, r = lane & 7;
+  ldmatrix_x4_trans(a, smem_u32(T + (k0 + (j >> 1) * 8 + r) * pitch + m0 + (j & 1) * 8));
+}
+// B fragment (k0..k0+15, columns n0..n0+7) of a tile stored [N][K], K contiguous
+__device__ __forceinline__ void frag_b_nk(uint32_t (&b)[2], const __nv_bfloat16* Bt, int pitch, int n0, int k0, int lane) {
+  const __nv_bfloat16* p = Bt + (n0 + (lane >> 2)) * pitch + k0 + (lane & 3) * 2;
+  b[0] = ld_pair(p);
+  b[1] = ld_pair(p + 8);
+}
+// B fragments of the two column tiles n0..n0+7 (b[0], b[1]) and n0+8..n0+15 (b[2], b[3]) of a tile stored [K][N],
+// N contiguous (transposing ldmatrix)
+__device__ __forceinline__ void frag_b_kn(uint32_t (&b)[4], const __nv_bfloat16* B, int pitch, int k0, int n0, int lane) {
+  const int j = lane >> 3, r = lane & 7;
+  ldmatrix_x4_trans(b, smem_u32(B + (k0 + (j & 1) * 8 + r) * pitch + n0 + (j >> 1) * 8));
+}
+
+// 64 rows x 128 bf16 of one head from a strided [T, H, 128] activation into a [64][GC_P128] tile; rows from `t_end` on
+// are zero.  16-byte loads when the row addresses allow it.
+__device__ __forceinline__ void load_rows_bf16(__nv_bfloat16* tile, const __nv_bfloat16* src, int64_t stride_t, int64_t t0,
+                                               int64_t t_end, int tid) {
+  const bool vec = (reinterpret_cast<uintptr_t>(src) & 15) == 0 && (stride_t & 7) == 0;
+  if (vec) {
+    for (int i = tid; i < CHUNK * (GDN_D / 8); i += GC_THREADS) {
+      const int r = i >> 4, c8 = (i & 15) * 8;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (t0 + r < t_end) val = *reinterpret_cast<const uint4*>(src + (t0 + r) * stride_t + c8);
+      *reinterpret_cast<uint4*>(tile + r * GC_P128 + c8) = val;
+    }
+  } else {
+    for (int i = tid; i < CHUNK * GDN_D; i += GC_THREADS) {
+      const int r = i >> 7, c = i & 127;
+      tile[r * GC_P128 + c] = t0 + r < t_end ? src[(t0 + r) * stride_t + c] : __float2bfloat16_rn(0.f);
+    }
+  }
+}
+// C[64 x 64] = X K^T over the 128 dims for the column tiles that can hold a causal entry (column <= row): warp =
+// (16-row tile mt, 32-column half nh); acc[nt] is the 16 x 8 tile at columns nh*32 + nt*8.
+__device__ __forceinline__ void causal_scores(float (&acc)[4][4], const __nv_bfloat16* X, const __nv_bfloat16* K, int mt,
+                                              int nh, int lane) {
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+  if (nh * 32 > mt * 16 + 15) return;
+#pragma unroll
+  for (int ks = 0; ks < GDN_D / 16; ++ks) {
+    uint32_t a[4];
+    frag_a(a, X, GC_P128, mt * 16, ks * 16, lane);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      if (nh * 32 + nt * 8 > mt * 16 + 15) continue;
+      uint32_t b[2];
+      frag_b_nk(b, K, GC_P128, nh * 32 + nt * 8, ks * 16, lane);
+      mma_bf16_16816(acc[nt], a, b[0], b[1]);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------- prepare_wy
-constexpr int PW_SMEM = (2 * CHUNK * GC_PITCH + 2 * CHUNK * GC_LP + 4 * CHUNK) * 4;
+// shared memory: k, v tiles (bf16) | lower, inv (fp32) | (inv beta) and (inv beta e^G) as bf16 pairs | scalars
+constexpr int PW_KB = 0;
+constexpr int PW_VB = PW_KB + CHUNK * GC_P128 * 2;
+constexpr int PW_LOWER = PW_VB + CHUNK * GC_P128 * 2;
+constexpr int PW_INV = PW_LOWER + CHUNK * GC_LP * 4;
+constexpr int PW_PAIR = PW_INV + CHUNK * GC_LP * 4;      // four [64][GC_P64] bf16 tiles; first the inverse's scratch
+constexpr int PW_SC = PW_PAIR + 4 * CHUNK * GC_P64 * 2;
+static_assert(INV_SCRATCH_FLOATS * 4 <= 4 * CHUNK * GC_P64 * 2, "the merge scratch lies over the pair tiles");
+constexpr int PW_SMEM = PW_SC + 3 * CHUNK * 4;
 
 __global__ void __launch_bounds__(GC_THREADS)
 gdn_chunk_prepare_wy_kernel(const __nv_bfloat16* __restrict__ k, int64_t k_t, int64_t k_h,
@@ -57,27 +147,26 @@ gdn_chunk_prepare_wy_kernel(const __nv_bfloat16* __restrict__ k, int64_t k_t, in
                             int64_t g_t, int64_t g_h, float* __restrict__ w, float* __restrict__ u_base,
                             float* __restrict__ g_cumsum, int token_num, int heads,
                             const int32_t* __restrict__ cu_seqlens) {
-  extern __shared__ __align__(16) float sm[];
+  extern __shared__ __align__(16) uint8_t smem_pw[];
   const ChunkPos pos = locate_chunk(cu_seqlens, token_num);
   if (!pos.valid) return;
   token_num = pos.t_end;
-  float* kf = sm;                            // [64][GC_PITCH]
-  float* vf = kf + CHUNK * GC_PITCH;         // [64][GC_PITCH]
-  float* lower = vf + CHUNK * GC_PITCH;      // [64][GC_LP]
-  float* inv = lower + CHUNK * GC_LP;        // [64][GC_LP]
-  float* gs = inv + CHUNK * GC_LP;           // g, then G
-  float* bs = gs + CHUNK;                    // beta
-  float* es = bs + CHUNK;                    // exp(G)
-  const int chunk = pos.chunk, h = blockIdx.y, tid = threadIdx.x;
+  __nv_bfloat16* kb = reinterpret_cast<__nv_bfloat16*>(smem_pw + PW_KB);   // [64][GC_P128]
+  __nv_bfloat16* vb = reinterpret_cast<__nv_bfloat16*>(smem_pw + PW_VB);   // [64][GC_P128]
+  float* lower = reinterpret_cast<float*>(smem_pw + PW_LOWER);             // [64][GC_LP]
+  float* inv = reinterpret_cast<float*>(smem_pw + PW_INV);                 // [64][GC_LP]
+  __nv_bfloat16* pu_hi = reinterpret_cast<__nv_bfloat16*>(smem_pw + PW_PAIR);  // inv[t][i] beta_i
+  __nv_bfloat16* pu_lo = pu_hi + CHUNK * GC_P64;
+  __nv_bfloat16* pw_hi = pu_lo + CHUNK * GC_P64;                               // inv[t][i] beta_i e^{G_i}
+  __nv_bfloat16* pw_lo = pw_hi + CHUNK * GC_P64;
+  float* gs = reinterpret_cast<float*>(smem_pw + PW_SC);  // g, then G
+  float* bs = gs + CHUNK;                                 // beta
+  float* es = bs + CHUNK;                                 // exp(G)
+  const int chunk = pos.chunk, h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int t0 = pos.t0;
 
-  for (int i = tid; i < CHUNK * GDN_D; i += GC_THREADS) {
-    const int r = i / GDN_D, c = i % GDN_D;
-    const int64_t t = t0 + r;
-    const bool ok = t < token_num;
-    kf[r * GC_PITCH + c] = ok ? __bfloat162float(k[t * k_t + h * k_h + c]) : 0.f;
-    vf[r * GC_PITCH + c] = ok ? __bfloat162float(v[t * v_t + h * v_h + c]) : 0.f;
-  }
+  load_rows_bf16(kb, k + h * k_h, k_t, t0, token_num, tid);
+  load_rows_bf16(vb, v + h * v_h, v_t, t0, token_num, tid);
   if (tid < CHUNK) {
     const int64_t t = t0 + tid;
     const bool ok = t < token_num;
@@ -97,97 +186,147 @@ gdn_chunk_prepare_wy_kernel(const __nv_bfloat16* __restrict__ k, int64_t k_t, in
     g_cumsum[(static_cast<int64_t>(chunk) * heads + h) * CHUNK + tid] = gs[tid];
     es[tid] = expf(gs[tid]);
   }
-  // ---- lower[t][i] = beta_t exp(G_t - G_i) <k_t, k_i> for i < t, both tokens valid
+  // ---- lower[t][i] = beta_t exp(G_t - G_i) <k_t, k_i> for i < t, both tokens valid (k k^T on the tensor cores)
+  const int mt = warp & 3, nh = warp >> 2, gr = lane >> 2, tg = (lane & 3) * 2;
   {
-    const int t = tid >> 2, ig = (tid & 3) * 16;
-    const float4* kt = reinterpret_cast<const float4*>(kf + t * GC_PITCH);
-    for (int ii = 0; ii < 16; ++ii) {
-      const int i = ig + ii;
-      float val = 0.f;
-      if (i < t && t0 + t < token_num) {
-        const float4* ki = reinterpret_cast<const float4*>(kf + i * GC_PITCH);
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll 8
-        for (int d = 0; d < GDN_D / 4; ++d) {
-          const float4 x = kt[d], y = ki[d];
-          a0 = fmaf(x.x, y.x, a0);
-          a1 = fmaf(x.y, y.y, a1);
-          a2 = fmaf(x.z, y.z, a2);
-          a3 = fmaf(x.w, y.w, a3);
-        }
-        val = bs[t] * expf(gs[t] - gs[i]) * ((a0 + a1) + (a2 + a3));
+    float acc[4][4];
+    causal_scores(acc, kb, kb, mt, nh, lane);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int t = mt * 16 + gr + (e >> 1) * 8, i = nh * 32 + nt * 8 + tg + (e & 1);
+        lower[t * GC_LP + i] = (i < t && t0 + t < token_num) ? bs[t] * expf(gs[t] - gs[i]) * acc[nt][e] : 0.f;
       }
-      lower[t * GC_LP + i] = val;
+  }
+  __syncthreads();
+  // ---- inv = (I + lower)^-1, blocked, by the first four warps (blocks above the block diagonal are not written)
+  if (tid < 128) blocked_inverse64(lower, inv, reinterpret_cast<float*>(smem_pw + PW_PAIR), tid);
+  __syncthreads();
+  // ---- the right-hand scalings move into the inverse: u = (inv diag(beta)) v, w = (inv diag(beta e^G)) k, so that the
+  //      right operands stay the exact bf16 inputs
+  for (int idx = tid; idx < CHUNK * CHUNK / 2; idx += GC_THREADS) {
+    const int t = idx >> 5, i = (idx & 31) * 2;
+    const float p0 = i <= t ? inv[t * GC_LP + i] * bs[i] : 0.f;
+    const float p1 = i + 1 <= t ? inv[t * GC_LP + i + 1] * bs[i + 1] : 0.f;
+    uint32_t hi, lo;
+    split_pair(p0, p1, hi, lo);
+    *reinterpret_cast<uint32_t*>(pu_hi + t * GC_P64 + i) = hi;
+    *reinterpret_cast<uint32_t*>(pu_lo + t * GC_P64 + i) = lo;
+    split_pair(p0 * es[i], p1 * es[i + 1], hi, lo);
+    *reinterpret_cast<uint32_t*>(pw_hi + t * GC_P64 + i) = hi;
+    *reinterpret_cast<uint32_t*>(pw_lo + t * GC_P64 + i) = lo;
+  }
+  __syncthreads();
+  // ---- u and w: warp = (16-row tile mt, 64-column half nh); inv is lower triangular, so k steps past the row tile
+  //      contribute nothing
+  const int64_t out_base = (static_cast<int64_t>(chunk) * heads + h) * CHUNK * GDN_D;
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    const __nv_bfloat16* a_hi = which == 0 ? pu_hi : pw_hi;
+    const __nv_bfloat16* a_lo = which == 0 ? pu_lo : pw_lo;
+    const __nv_bfloat16* rhs = which == 0 ? vb : kb;
+    float acc[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    for (int ks = 0; ks <= mt; ++ks) {
+      uint32_t ah[4], al[4];
+      frag_a(ah, a_hi, GC_P64, mt * 16, ks * 16, lane);
+      frag_a(al, a_lo, GC_P64, mt * 16, ks * 16, lane);
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t b[4];
+        frag_b_kn(b, rhs, GC_P128, ks * 16, nh * 64 + np * 16, lane);
+        mma_bf16_16816(acc[2 * np], ah, b[0], b[1]);
+        mma_bf16_16816(acc[2 * np], al, b[0], b[1]);
+        mma_bf16_16816(acc[2 * np + 1], ah, b[2], b[3]);
+        mma_bf16_16816(acc[2 * np + 1], al, b[2], b[3]);
+      }
     }
-  }
-  __syncthreads();
-  // ---- inv = (I + lower)^-1 by forward substitution; thread j owns column j (columns are independent)
-  if (tid < CHUNK) {
-    const int j = tid;
-    for (int row = 0; row < CHUNK; ++row) {
-      float val;
-      if (row < j) val = 0.f;
-      else if (row == j) val = 1.f;
-      else {
-        float a0 = 0.f, a1 = 0.f;
-        int i = j;
-        for (; i + 1 < row; i += 2) {
-          a0 = fmaf(lower[row * GC_LP + i], inv[i * GC_LP + j], a0);
-          a1 = fmaf(lower[row * GC_LP + i + 1], inv[(i + 1) * GC_LP + j], a1);
-        }
-        if (i < row) a0 = fmaf(lower[row * GC_LP + i], inv[i * GC_LP + j], a0);
-        val = -(a0 + a1);
-      }
-      inv[row * GC_LP + j] = val;
-    }
-  }
-  // ---- right-hand sides in place: vf <- beta v, kf <- beta exp(G) k
-  __syncthreads();
-  for (int i = tid; i < CHUNK * GDN_D; i += GC_THREADS) {
-    const int r = i / GDN_D, c = i % GDN_D;
-    vf[r * GC_PITCH + c] *= bs[r];
-    kf[r * GC_PITCH + c] *= bs[r] * es[r];
-  }
-  __syncthreads();
-  // ---- u = inv @ vf, w = inv @ kf : warp = 8 rows, lane = 4 columns
-  {
-    const int r0 = (tid >> 5) * 8, c0 = (tid & 31) * 4;
-    const int64_t out_base = (static_cast<int64_t>(chunk) * heads + h) * CHUNK * GDN_D;
+    float* dst = (which == 0 ? u_base : w) + out_base;
 #pragma unroll
-    for (int which = 0; which < 2; ++which) {
-      const float* rhs = which == 0 ? vf : kf;
-      float acc[8][4];
-#pragma unroll
-      for (int r = 0; r < 8; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
-      for (int i = 0; i < r0 + 8; ++i) {  // inv is lower triangular: columns past the last row of the group are zero
-        const float4 b = *reinterpret_cast<const float4*>(rhs + i * GC_PITCH + c0);
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-          const float a = inv[(r0 + r) * GC_LP + i];
-          acc[r][0] = fmaf(a, b.x, acc[r][0]);
-          acc[r][1] = fmaf(a, b.y, acc[r][1]);
-          acc[r][2] = fmaf(a, b.z, acc[r][2]);
-          acc[r][3] = fmaf(a, b.w, acc[r][3]);
-        }
-      }
-      float* dst = (which == 0 ? u_base : w) + out_base;
-#pragma unroll
-      for (int r = 0; r < 8; ++r)
-        *reinterpret_cast<float4*>(dst + (r0 + r) * GDN_D + c0) = make_float4(acc[r][0], acc[r][1], acc[r][2], acc[r][3]);
+    for (int nt = 0; nt < 8; ++nt) {
+      const int c = nh * 64 + nt * 8 + tg;
+      *reinterpret_cast<float2*>(dst + (mt * 16 + gr) * GDN_D + c) = make_float2(acc[nt][0], acc[nt][1]);
+      *reinterpret_cast<float2*>(dst + (mt * 16 + gr + 8) * GDN_D + c) = make_float2(acc[nt][2], acc[nt][3]);
     }
   }
 }
 
 // ---------------------------------------------------------------------------------------------------- chunk_state
-constexpr int CS_BV = 16;  // value columns per CTA
-constexpr int CS_SMEM = (2 * CHUNK * GC_PITCH + GDN_D * CS_BV + 2 * CHUNK * CS_BV + 2 * CHUNK) * 4;
+constexpr int CS_BV = 32;           // value columns per CTA
+constexpr int GC_PV = CS_BV + 8;    // bf16 pitch of [rows][CS_BV] tiles
+// shared memory: w pair [64][GC_P128] x 2 | k [64][GC_P128] | state pair [128][GC_PV] x 2 | decayed delta pair
+// [64][GC_PV] x 2 | G, decay
+constexpr int CS_WH = 0;
+constexpr int CS_WL = CS_WH + CHUNK * GC_P128 * 2;
+constexpr int CS_KB = CS_WL + CHUNK * GC_P128 * 2;
+constexpr int CS_SH = CS_KB + CHUNK * GC_P128 * 2;
+constexpr int CS_SL = CS_SH + GDN_D * GC_PV * 2;
+constexpr int CS_DH = CS_SL + GDN_D * GC_PV * 2;
+constexpr int CS_DL = CS_DH + CHUNK * GC_PV * 2;
+constexpr int CS_SC = CS_DL + CHUNK * GC_PV * 2;
+constexpr int CS_SMEM = CS_SC + 2 * CHUNK * 4;
+constexpr int CS_W_PER_THREAD = CHUNK * GDN_D / 4 / GC_THREADS;  // float4 of w per thread and chunk (8)
+constexpr int CS_K_PER_THREAD = CHUNK * GDN_D / 8 / GC_THREADS;  // 16-byte pieces of k per thread and chunk (4)
+
+// The w and k rows of one chunk, fetched into registers one chunk ahead so that their latency hides behind the
+// products of the chunk in front.
+struct ChunkOperands {
+  float4 w[CS_W_PER_THREAD];
+  uint4 k[CS_K_PER_THREAD];
+};
+__device__ __forceinline__ void fetch_operands(ChunkOperands& r, const float* w_chunk, const __nv_bfloat16* k_head,
+                                               int64_t k_t, int64_t t0, int64_t t_end, bool k_vec, int tid) {
+#pragma unroll
+  for (int j = 0; j < CS_W_PER_THREAD; ++j) {
+    const int i = tid + j * GC_THREADS;
+    r.w[j] = *reinterpret_cast<const float4*>(w_chunk + static_cast<int64_t>(i >> 5) * GDN_D + (i & 31) * 4);
+  }
+#pragma unroll
+  for (int j = 0; j < CS_K_PER_THREAD; ++j) {
+    const int i = tid + j * GC_THREADS, row = i >> 4, c8 = (i & 15) * 8;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (t0 + row < t_end) {
+      const __nv_bfloat16* src = k_head + (t0 + row) * k_t + c8;
+      if (k_vec) {
+        val = *reinterpret_cast<const uint4*>(src);
+      } else {
+        uint32_t u[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          u[e] = static_cast<uint32_t>(__bfloat16_as_ushort(src[2 * e])) |
+                 (static_cast<uint32_t>(__bfloat16_as_ushort(src[2 * e + 1])) << 16);
+        val = make_uint4(u[0], u[1], u[2], u[3]);
+      }
+    }
+    r.k[j] = val;
+  }
+}
+__device__ __forceinline__ void stage_operands(const ChunkOperands& r, __nv_bfloat16* wh, __nv_bfloat16* wl,
+                                               __nv_bfloat16* kb, int tid) {
+#pragma unroll
+  for (int j = 0; j < CS_W_PER_THREAD; ++j) {
+    const int i = tid + j * GC_THREADS, row = i >> 5, c4 = (i & 31) * 4;
+    uint32_t h0, l0, h1, l1;
+    split_pair(r.w[j].x, r.w[j].y, h0, l0);
+    split_pair(r.w[j].z, r.w[j].w, h1, l1);
+    *reinterpret_cast<uint2*>(wh + row * GC_P128 + c4) = make_uint2(h0, h1);
+    *reinterpret_cast<uint2*>(wl + row * GC_P128 + c4) = make_uint2(l0, l1);
+  }
+#pragma unroll
+  for (int j = 0; j < CS_K_PER_THREAD; ++j) {
+    const int i = tid + j * GC_THREADS;
+    *reinterpret_cast<uint4*>(kb + (i >> 4) * GC_P128 + (i & 15) * 8) = r.k[j];
+  }
+}
 
 __global__ void __launch_bounds__(GC_THREADS)
 gdn_chunk_state_kernel(const __nv_bfloat16* __restrict__ k, int64_t k_t, int64_t k_h, const float* __restrict__ w,
                        const float* __restrict__ u_base, const float* __restrict__ g_cumsum, float* __restrict__ delta,
                        float* __restrict__ chunk_state, float* __restrict__ final_state, int token_num, int num_chunks,
                        int heads, const int32_t* __restrict__ cu_seqlens) {
-  extern __shared__ __align__(16) float sm[];
+  extern __shared__ __align__(16) uint8_t smem_cs[];
   // packed batch: blockIdx.z = sequence; its chunks are [chunk_base, chunk_base + num_chunks)
   int chunk_base = 0, tok_base = 0;
   if (cu_seqlens != nullptr) {
@@ -197,92 +336,148 @@ gdn_chunk_state_kernel(const __nv_bfloat16* __restrict__ k, int64_t k_t, int64_t
     token_num = cu_seqlens[b + 1] - tok_base;
     num_chunks = (token_num + CHUNK - 1) / CHUNK;
   }
-  float* wf = sm;                           // [64][GC_PITCH]
-  float* kf = wf + CHUNK * GC_PITCH;        // [64][GC_PITCH]
-  float* st = kf + CHUNK * GC_PITCH;        // [128][16]
-  float* dl = st + GDN_D * CS_BV;           // delta [64][16]
-  float* de = dl + CHUNK * CS_BV;           // delta * exp(G_last - G) [64][16]
-  float* gs = de + CHUNK * CS_BV;           // G [64]
-  float* dec = gs + CHUNK;                  // exp(G_last - G) (0 for padded tokens)
-  const int h = blockIdx.x, v0 = blockIdx.y * CS_BV, tid = threadIdx.x;
+  __nv_bfloat16* wh = reinterpret_cast<__nv_bfloat16*>(smem_cs + CS_WH);
+  __nv_bfloat16* wl = reinterpret_cast<__nv_bfloat16*>(smem_cs + CS_WL);
+  __nv_bfloat16* kb = reinterpret_cast<__nv_bfloat16*>(smem_cs + CS_KB);
+  __nv_bfloat16* sh = reinterpret_cast<__nv_bfloat16*>(smem_cs + CS_SH);
+  __nv_bfloat16* sl = reinterpret_cast<__nv_bfloat16*>(smem_cs + CS_SL);
+  __nv_bfloat16* dh = reinterpret_cast<__nv_bfloat16*>(smem_cs + CS_DH);
+  __nv_bfloat16* dl = reinterpret_cast<__nv_bfloat16*>(smem_cs + CS_DL);
+  float* gs = reinterpret_cast<float*>(smem_cs + CS_SC);  // G [64]
+  float* dec = gs + CHUNK;                                // exp(G_last - G) (0 for padded tokens)
+  const int h = blockIdx.x, v0 = blockIdx.y * CS_BV, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gr = lane >> 2, tg = (lane & 3) * 2;
+  const __nv_bfloat16* k_head = k + h * k_h;
+  const bool k_vec = (reinterpret_cast<uintptr_t>(k_head) & 15) == 0 && (k_t & 7) == 0;
+  const int64_t seq_end = static_cast<int64_t>(tok_base) + token_num;
 
-  for (int i = tid; i < GDN_D * CS_BV; i += GC_THREADS) st[i] = 0.f;
-  __syncthreads();
+  // the state slice [128 dk][32 dv] lives in accumulator registers: warp = key rows 16*warp .. +15, st[nt] = the
+  // 16 x 8 tile at value columns nt*8
+  float st[CS_BV / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < CS_BV / 8; ++nt) st[nt][0] = st[nt][1] = st[nt][2] = st[nt][3] = 0.f;
+
+  ChunkOperands ops_next;
+  if (num_chunks > 0)
+    fetch_operands(ops_next, w + (static_cast<int64_t>(chunk_base) * heads + h) * CHUNK * GDN_D, k_head, k_t, tok_base,
+                   seq_end, k_vec, tid);
   for (int c = 0; c < num_chunks; ++c) {
     const int64_t ch = static_cast<int64_t>(chunk_base + c) * heads + h;
-    // state entering the chunk
-    for (int i = tid; i < GDN_D * CS_BV / 4; i += GC_THREADS) {
-      const int kk = i / (CS_BV / 4), q4 = i % (CS_BV / 4);
-      *reinterpret_cast<float4*>(chunk_state + (ch * GDN_D + kk) * GDN_D + v0 + q4 * 4) =
-          *reinterpret_cast<const float4*>(st + kk * CS_BV + q4 * 4);
-    }
-    for (int i = tid; i < CHUNK * GDN_D / 4; i += GC_THREADS) {
-      const int r = i / (GDN_D / 4), c4 = i % (GDN_D / 4);
-      *reinterpret_cast<float4*>(wf + r * GC_PITCH + c4 * 4) =
-          *reinterpret_cast<const float4*>(w + (ch * CHUNK + r) * GDN_D + c4 * 4);
-    }
-    for (int i = tid; i < CHUNK * GDN_D; i += GC_THREADS) {
-      const int r = i / GDN_D, cc = i % GDN_D;
-      const int64_t t = static_cast<int64_t>(c) * CHUNK + r;
-      kf[r * GC_PITCH + cc] = t < token_num ? __bfloat162float(k[(tok_base + t) * k_t + h * k_h + cc]) : 0.f;
-    }
-    if (tid < CHUNK) gs[tid] = g_cumsum[ch * CHUNK + tid];
-    __syncthreads();
-    const float g_last = gs[CHUNK - 1];
-    if (tid < CHUNK) dec[tid] = (c * CHUNK + tid < token_num) ? expf(g_last - gs[tid]) : 0.f;
-    // delta[t][v] = u[t][v] - sum_k w[t][k] S[k][v]: thread = (t, 4 columns)
-    {
-      const int t = tid >> 2, c4 = (tid & 3) * 4;
-      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-      const float* wr = wf + t * GC_PITCH;
-#pragma unroll 8
-      for (int kk = 0; kk < GDN_D; ++kk) {
-        const float a = wr[kk];
-        const float4 s4 = *reinterpret_cast<const float4*>(st + kk * CS_BV + c4);
-        a0 = fmaf(a, s4.x, a0);
-        a1 = fmaf(a, s4.y, a1);
-        a2 = fmaf(a, s4.z, a2);
-        a3 = fmaf(a, s4.w, a3);
+    // state entering the chunk: fp32 to global memory, bf16 pair to shared memory (right operand of w S)
+#pragma unroll
+    for (int nt = 0; nt < CS_BV / 8; ++nt)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int kk = warp * 16 + gr + half * 8, col = nt * 8 + tg;
+        const float s0 = st[nt][2 * half], s1 = st[nt][2 * half + 1];
+        *reinterpret_cast<float2*>(chunk_state + (ch * GDN_D + kk) * GDN_D + v0 + col) = make_float2(s0, s1);
+        uint32_t hi, lo;
+        split_pair(s0, s1, hi, lo);
+        *reinterpret_cast<uint32_t*>(sh + kk * GC_PV + col) = hi;
+        *reinterpret_cast<uint32_t*>(sl + kk * GC_PV + col) = lo;
       }
-      const float4 u4 = *reinterpret_cast<const float4*>(u_base + (ch * CHUNK + t) * GDN_D + v0 + c4);
-      const float4 d4 = make_float4(u4.x - a0, u4.y - a1, u4.z - a2, u4.w - a3);
-      *reinterpret_cast<float4*>(delta + (ch * CHUNK + t) * GDN_D + v0 + c4) = d4;
-      *reinterpret_cast<float4*>(dl + t * CS_BV + c4) = d4;
+    stage_operands(ops_next, wh, wl, kb, tid);
+    if (tid < CHUNK) {
+      const float gv = g_cumsum[ch * CHUNK + tid];
+      const float g_last_v = g_cumsum[ch * CHUNK + CHUNK - 1];
+      gs[tid] = gv;
+      dec[tid] = (c * CHUNK + tid < token_num) ? expf(g_last_v - gv) : 0.f;
     }
     __syncthreads();
-    for (int i = tid; i < CHUNK * CS_BV; i += GC_THREADS) de[i] = dl[i] * dec[i / CS_BV];
-    __syncthreads();
-    // S[k][v] = exp(G_last) S[k][v] + sum_t k[t][k] de[t][v]: thread = (k, 8 columns)
+    if (c + 1 < num_chunks)
+      fetch_operands(ops_next, w + (ch + heads) * CHUNK * GDN_D, k_head, k_t,
+                     static_cast<int64_t>(tok_base) + static_cast<int64_t>(c + 1) * CHUNK, seq_end, k_vec, tid);
+    const float g_last = gs[CHUNK - 1];
+    // delta[t][v] = u[t][v] - sum_k w[t][k] S[k][v]: warp = (16-token tile mt, 16-column pair np)
     {
-      const int kk = tid >> 1, c8 = (tid & 1) * 8;
-      float acc[8];
+      const int mt = warp & 3, np = warp >> 2;
+      float2 u2[2][2];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half)
+          u2[nt][half] = *reinterpret_cast<const float2*>(u_base + (ch * CHUNK + mt * 16 + gr + half * 8) * GDN_D + v0 +
+                                                          np * 16 + nt * 8 + tg);
+      float acc[2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < GDN_D / 16; ++ks) {
+        uint32_t ah[4], al[4], bh[4], bl[4];
+        frag_a(ah, wh, GC_P128, mt * 16, ks * 16, lane);
+        frag_a(al, wl, GC_P128, mt * 16, ks * 16, lane);
+        frag_b_kn(bh, sh, GC_PV, ks * 16, np * 16, lane);
+        frag_b_kn(bl, sl, GC_PV, ks * 16, np * 16, lane);
+        mma_bf16_16816(acc[0], ah, bh[0], bh[1]);
+        mma_bf16_16816(acc[0], ah, bl[0], bl[1]);
+        mma_bf16_16816(acc[0], al, bh[0], bh[1]);
+        mma_bf16_16816(acc[1], ah, bh[2], bh[3]);
+        mma_bf16_16816(acc[1], ah, bl[2], bl[3]);
+        mma_bf16_16816(acc[1], al, bh[2], bh[3]);
+      }
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int t = mt * 16 + gr + half * 8, col = np * 16 + nt * 8 + tg;
+          const float d0 = u2[nt][half].x - acc[nt][2 * half], d1 = u2[nt][half].y - acc[nt][2 * half + 1];
+          *reinterpret_cast<float2*>(delta + (ch * CHUNK + t) * GDN_D + v0 + col) = make_float2(d0, d1);
+          uint32_t hi, lo;
+          split_pair(d0 * dec[t], d1 * dec[t], hi, lo);
+          *reinterpret_cast<uint32_t*>(dh + t * GC_PV + col) = hi;
+          *reinterpret_cast<uint32_t*>(dl + t * GC_PV + col) = lo;
+        }
+    }
+    __syncthreads();
+    // S[k][v] = exp(G_last) S[k][v] + sum_t k[t][k] (delta[t][v] exp(G_last - G_t)): A = k^T through the transposing
+    // ldmatrix, exact in bf16
+    {
       const float eg = expf(g_last);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = eg * st[kk * CS_BV + c8 + j];
-#pragma unroll 4
-      for (int t = 0; t < CHUNK; ++t) {
-        const float a = kf[t * GC_PITCH + kk];
-        const float4 x = *reinterpret_cast<const float4*>(de + t * CS_BV + c8);
-        const float4 y = *reinterpret_cast<const float4*>(de + t * CS_BV + c8 + 4);
-        acc[0] = fmaf(a, x.x, acc[0]); acc[1] = fmaf(a, x.y, acc[1]); acc[2] = fmaf(a, x.z, acc[2]); acc[3] = fmaf(a, x.w, acc[3]);
-        acc[4] = fmaf(a, y.x, acc[4]); acc[5] = fmaf(a, y.y, acc[5]); acc[6] = fmaf(a, y.z, acc[6]); acc[7] = fmaf(a, y.w, acc[7]);
-      }
-      __syncthreads();  // every thread has read the old state
+      for (int nt = 0; nt < CS_BV / 8; ++nt)
 #pragma unroll
-      for (int j = 0; j < 8; ++j) st[kk * CS_BV + c8 + j] = acc[j];
+        for (int e = 0; e < 4; ++e) st[nt][e] *= eg;
+#pragma unroll
+      for (int ks = 0; ks < CHUNK / 16; ++ks) {
+        uint32_t a[4];
+        frag_a_t(a, kb, GC_P128, warp * 16, ks * 16, lane);
+#pragma unroll
+        for (int np = 0; np < CS_BV / 16; ++np) {
+          uint32_t bh[4], bl[4];
+          frag_b_kn(bh, dh, GC_PV, ks * 16, np * 16, lane);
+          frag_b_kn(bl, dl, GC_PV, ks * 16, np * 16, lane);
+          mma_bf16_16816(st[2 * np], a, bh[0], bh[1]);
+          mma_bf16_16816(st[2 * np], a, bl[0], bl[1]);
+          mma_bf16_16816(st[2 * np + 1], a, bh[2], bh[3]);
+          mma_bf16_16816(st[2 * np + 1], a, bl[2], bl[3]);
+        }
+      }
     }
-    __syncthreads();
+    __syncthreads();  // the tiles are rewritten by the next chunk
   }
-  for (int i = tid; i < GDN_D * CS_BV / 4; i += GC_THREADS) {
-    const int kk = i / (CS_BV / 4), q4 = i % (CS_BV / 4);
-    *reinterpret_cast<float4*>(final_state + ((static_cast<int64_t>(blockIdx.z) * heads + h) * GDN_D + kk) * GDN_D + v0 +
-                               q4 * 4) =
-        *reinterpret_cast<const float4*>(st + kk * CS_BV + q4 * 4);
-  }
+#pragma unroll
+  for (int nt = 0; nt < CS_BV / 8; ++nt)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int kk = warp * 16 + gr + half * 8, col = nt * 8 + tg;
+      *reinterpret_cast<float2*>(final_state + ((static_cast<int64_t>(blockIdx.z) * heads + h) * GDN_D + kk) * GDN_D + v0 +
+                                 col) = make_float2(st[nt][2 * half], st[nt][2 * half + 1]);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------- chunk_output
-constexpr int CO_SMEM = (2 * CHUNK * GC_PITCH + CHUNK * GC_LP + GDN_D * GC_PITCH + 2 * CHUNK) * 4;
+// shared memory: q, k [64][GC_P128] | state pair [128][GC_P128] x 2 | delta pair [64][GC_P128] x 2 | attention pair
+// [64][GC_P64] x 2 | G, exp(G)
+constexpr int CO_QB = 0;
+constexpr int CO_KB = CO_QB + CHUNK * GC_P128 * 2;
+constexpr int CO_SH = CO_KB + CHUNK * GC_P128 * 2;
+constexpr int CO_SL = CO_SH + GDN_D * GC_P128 * 2;
+constexpr int CO_DH = CO_SL + GDN_D * GC_P128 * 2;
+constexpr int CO_DL = CO_DH + CHUNK * GC_P128 * 2;
+constexpr int CO_AH = CO_DL + CHUNK * GC_P128 * 2;
+constexpr int CO_AL = CO_AH + CHUNK * GC_P64 * 2;
+constexpr int CO_SC = CO_AL + CHUNK * GC_P64 * 2;
+constexpr int CO_SMEM = CO_SC + 2 * CHUNK * 4;
 
 __global__ void __launch_bounds__(GC_THREADS)
 gdn_chunk_output_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_t, int64_t q_h,
@@ -290,109 +485,132 @@ gdn_chunk_output_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_t, int64_
                         const float* __restrict__ g_cumsum, const float* __restrict__ chunk_state,
                         __nv_bfloat16* __restrict__ out, int64_t o_t, int64_t o_h, int token_num, int heads,
                         const int32_t* __restrict__ cu_seqlens) {
-  extern __shared__ __align__(16) float sm[];
+  extern __shared__ __align__(16) uint8_t smem_co[];
   const ChunkPos pos = locate_chunk(cu_seqlens, token_num);
   if (!pos.valid) return;
   token_num = pos.t_end;
-  float* qf = sm;                           // [64][GC_PITCH]
-  float* kd = qf + CHUNK * GC_PITCH;        // k, later delta [64][GC_PITCH]
-  float* att = kd + CHUNK * GC_PITCH;       // [64][GC_LP]
-  float* sf = att + CHUNK * GC_LP;          // state_in [128][GC_PITCH]
-  float* gs = sf + GDN_D * GC_PITCH;        // G
-  float* es = gs + CHUNK;                   // exp(G)
-  const int chunk = pos.chunk, h = blockIdx.y, tid = threadIdx.x;
+  __nv_bfloat16* qb = reinterpret_cast<__nv_bfloat16*>(smem_co + CO_QB);
+  __nv_bfloat16* kb = reinterpret_cast<__nv_bfloat16*>(smem_co + CO_KB);
+  __nv_bfloat16* sh = reinterpret_cast<__nv_bfloat16*>(smem_co + CO_SH);
+  __nv_bfloat16* sl = reinterpret_cast<__nv_bfloat16*>(smem_co + CO_SL);
+  __nv_bfloat16* dh = reinterpret_cast<__nv_bfloat16*>(smem_co + CO_DH);
+  __nv_bfloat16* dl = reinterpret_cast<__nv_bfloat16*>(smem_co + CO_DL);
+  __nv_bfloat16* ah_t = reinterpret_cast<__nv_bfloat16*>(smem_co + CO_AH);
+  __nv_bfloat16* al_t = reinterpret_cast<__nv_bfloat16*>(smem_co + CO_AL);
+  float* gs = reinterpret_cast<float*>(smem_co + CO_SC);  // G
+  float* es = gs + CHUNK;                                 // exp(G)
+  const int chunk = pos.chunk, h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int t0 = pos.t0;
   const int64_t ch = static_cast<int64_t>(chunk) * heads + h;
 
-  for (int i = tid; i < CHUNK * GDN_D; i += GC_THREADS) {
-    const int r = i / GDN_D, c = i % GDN_D;
-    const int64_t t = t0 + r;
-    const bool ok = t < token_num;
-    qf[r * GC_PITCH + c] = ok ? __bfloat162float(q[t * q_t + h * q_h + c]) : 0.f;
-    kd[r * GC_PITCH + c] = ok ? __bfloat162float(k[t * k_t + h * k_h + c]) : 0.f;
+  // the fp32 operands (incoming state, delta) go to registers first: their latency hides behind the q/k staging and
+  // the q k^T product, and they are split into bf16 pairs afterwards
+  constexpr int S_PER_THREAD = GDN_D * GDN_D / 4 / GC_THREADS, D_PER_THREAD = CHUNK * GDN_D / 4 / GC_THREADS;
+  float4 s_regs[S_PER_THREAD], d_regs[D_PER_THREAD];
+  {
+    const float4* s_src = reinterpret_cast<const float4*>(chunk_state + ch * GDN_D * GDN_D);
+    const float4* d_src = reinterpret_cast<const float4*>(delta + ch * CHUNK * GDN_D);
+#pragma unroll
+    for (int j = 0; j < S_PER_THREAD; ++j) s_regs[j] = s_src[tid + j * GC_THREADS];
+#pragma unroll
+    for (int j = 0; j < D_PER_THREAD; ++j) d_regs[j] = d_src[tid + j * GC_THREADS];
   }
-  for (int i = tid; i < GDN_D * GDN_D / 4; i += GC_THREADS) {
-    const int r = i / (GDN_D / 4), c4 = i % (GDN_D / 4);
-    *reinterpret_cast<float4*>(sf + r * GC_PITCH + c4 * 4) =
-        *reinterpret_cast<const float4*>(chunk_state + (ch * GDN_D + r) * GDN_D + c4 * 4);
-  }
+  load_rows_bf16(qb, q + h * q_h, q_t, t0, token_num, tid);
+  load_rows_bf16(kb, k + h * k_h, k_t, t0, token_num, tid);
   if (tid < CHUNK) {
     gs[tid] = g_cumsum[ch * CHUNK + tid];
     es[tid] = expf(gs[tid]);
   }
   __syncthreads();
-  // ---- att[t][i] = <q_t, k_i> exp(G_t - G_i) for i <= t, both tokens valid
+  const int mt = warp & 3, nh = warp >> 2, gr = lane >> 2, tg = (lane & 3) * 2;
+  // ---- att[t][i] = <q_t, k_i> exp(G_t - G_i) for i <= t, both tokens valid; kept as a bf16 pair (left operand of
+  //      att @ delta)
   {
-    const int t = tid >> 2, ig = (tid & 3) * 16;
-    const float4* qt = reinterpret_cast<const float4*>(qf + t * GC_PITCH);
-    for (int ii = 0; ii < 16; ++ii) {
-      const int i = ig + ii;
-      float val = 0.f;
-      if (i <= t && t0 + t < token_num) {
-        const float4* ki = reinterpret_cast<const float4*>(kd + i * GC_PITCH);
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
-#pragma unroll 8
-        for (int d = 0; d < GDN_D / 4; ++d) {
-          const float4 x = qt[d], y = ki[d];
-          a0 = fmaf(x.x, y.x, a0);
-          a1 = fmaf(x.y, y.y, a1);
-          a2 = fmaf(x.z, y.z, a2);
-          a3 = fmaf(x.w, y.w, a3);
-        }
-        val = ((a0 + a1) + (a2 + a3)) * expf(gs[t] - gs[i]);
+    float acc[4][4];
+    causal_scores(acc, qb, kb, mt, nh, lane);
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int t = mt * 16 + gr + half * 8, i = nh * 32 + nt * 8 + tg;
+        const bool row_ok = t0 + t < token_num;
+        const float a0 = (row_ok && i <= t) ? acc[nt][2 * half] * expf(gs[t] - gs[i]) : 0.f;
+        const float a1 = (row_ok && i + 1 <= t) ? acc[nt][2 * half + 1] * expf(gs[t] - gs[i + 1]) : 0.f;
+        uint32_t hi, lo;
+        split_pair(a0, a1, hi, lo);
+        *reinterpret_cast<uint32_t*>(ah_t + t * GC_P64 + i) = hi;
+        *reinterpret_cast<uint32_t*>(al_t + t * GC_P64 + i) = lo;
       }
-      att[t * GC_LP + i] = val;
-    }
+  }
+  {
+    auto stage = [&](const float4& x, __nv_bfloat16* hi, __nv_bfloat16* lo, int i) {  // i = float4 index in [rows][128]
+      uint32_t h0, l0, h1, l1;
+      split_pair(x.x, x.y, h0, l0);
+      split_pair(x.z, x.w, h1, l1);
+      *reinterpret_cast<uint2*>(hi + (i >> 5) * GC_P128 + (i & 31) * 4) = make_uint2(h0, h1);
+      *reinterpret_cast<uint2*>(lo + (i >> 5) * GC_P128 + (i & 31) * 4) = make_uint2(l0, l1);
+    };
+#pragma unroll
+    for (int j = 0; j < S_PER_THREAD; ++j) stage(s_regs[j], sh, sl, tid + j * GC_THREADS);
+#pragma unroll
+    for (int j = 0; j < D_PER_THREAD; ++j) stage(d_regs[j], dh, dl, tid + j * GC_THREADS);
   }
   __syncthreads();
-  // k is no longer needed: its buffer takes delta
-  for (int i = tid; i < CHUNK * GDN_D / 4; i += GC_THREADS) {
-    const int r = i / (GDN_D / 4), c4 = i % (GDN_D / 4);
-    *reinterpret_cast<float4*>(kd + r * GC_PITCH + c4 * 4) =
-        *reinterpret_cast<const float4*>(delta + (ch * CHUNK + r) * GDN_D + c4 * 4);
+  // ---- out = exp(G) (q @ S_in) + att @ delta: warp = (16-row tile mt, 64-column half nh)
+  float acc[8][4];
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+#pragma unroll 2
+  for (int ks = 0; ks < GDN_D / 16; ++ks) {
+    uint32_t a[4];
+    frag_a(a, qb, GC_P128, mt * 16, ks * 16, lane);
+#pragma unroll
+    for (int np = 0; np < 4; ++np) {
+      uint32_t bh[4], bl[4];
+      frag_b_kn(bh, sh, GC_P128, ks * 16, nh * 64 + np * 16, lane);
+      frag_b_kn(bl, sl, GC_P128, ks * 16, nh * 64 + np * 16, lane);
+      mma_bf16_16816(acc[2 * np], a, bh[0], bh[1]);
+      mma_bf16_16816(acc[2 * np], a, bl[0], bl[1]);
+      mma_bf16_16816(acc[2 * np + 1], a, bh[2], bh[3]);
+      mma_bf16_16816(acc[2 * np + 1], a, bl[2], bl[3]);
+    }
   }
-  __syncthreads();
-  // ---- out = exp(G) (q @ S_in) + att @ delta : warp = 8 rows, lane = 4 columns
   {
-    const int r0 = (tid >> 5) * 8, c0 = (tid & 31) * 4;
-    float acc[8][4];
+    const float e0 = es[mt * 16 + gr], e1 = es[mt * 16 + gr + 8];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
-    for (int kk = 0; kk < GDN_D; ++kk) {
-      const float4 b = *reinterpret_cast<const float4*>(sf + kk * GC_PITCH + c0);
-#pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const float a = qf[(r0 + r) * GC_PITCH + kk];
-        acc[r][0] = fmaf(a, b.x, acc[r][0]);
-        acc[r][1] = fmaf(a, b.y, acc[r][1]);
-        acc[r][2] = fmaf(a, b.z, acc[r][2]);
-        acc[r][3] = fmaf(a, b.w, acc[r][3]);
-      }
+    for (int nt = 0; nt < 8; ++nt) {
+      acc[nt][0] *= e0;
+      acc[nt][1] *= e0;
+      acc[nt][2] *= e1;
+      acc[nt][3] *= e1;
     }
+  }
+  for (int ks = 0; ks <= mt; ++ks) {  // att is lower triangular
+    uint32_t ah[4], al[4];
+    frag_a(ah, ah_t, GC_P64, mt * 16, ks * 16, lane);
+    frag_a(al, al_t, GC_P64, mt * 16, ks * 16, lane);
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      const float e = es[r0 + r];
-      acc[r][0] *= e; acc[r][1] *= e; acc[r][2] *= e; acc[r][3] *= e;
+    for (int np = 0; np < 4; ++np) {
+      uint32_t bh[4], bl[4];
+      frag_b_kn(bh, dh, GC_P128, ks * 16, nh * 64 + np * 16, lane);
+      frag_b_kn(bl, dl, GC_P128, ks * 16, nh * 64 + np * 16, lane);
+      mma_bf16_16816(acc[2 * np], ah, bh[0], bh[1]);
+      mma_bf16_16816(acc[2 * np], ah, bl[0], bl[1]);
+      mma_bf16_16816(acc[2 * np], al, bh[0], bh[1]);
+      mma_bf16_16816(acc[2 * np + 1], ah, bh[2], bh[3]);
+      mma_bf16_16816(acc[2 * np + 1], ah, bl[2], bl[3]);
+      mma_bf16_16816(acc[2 * np + 1], al, bh[2], bh[3]);
     }
-    for (int i = 0; i < r0 + 8; ++i) {  // att is lower triangular
-      const float4 b = *reinterpret_cast<const float4*>(kd + i * GC_PITCH + c0);
+  }
 #pragma unroll
-      for (int r = 0; r < 8; ++r) {
-        const float a = att[(r0 + r) * GC_LP + i];
-        acc[r][0] = fmaf(a, b.x, acc[r][0]);
-        acc[r][1] = fmaf(a, b.y, acc[r][1]);
-        acc[r][2] = fmaf(a, b.z, acc[r][2]);
-        acc[r][3] = fmaf(a, b.w, acc[r][3]);
-      }
-    }
+  for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      const int64_t t = t0 + r0 + r;
+    for (int half = 0; half < 2; ++half) {
+      const int64_t t = t0 + mt * 16 + gr + half * 8;
       if (t < token_num)
-        *reinterpret_cast<uint2*>(out + t * o_t + h * o_h + c0) =
-            make_uint2(pack_bf16(acc[r][0], acc[r][1]), pack_bf16(acc[r][2], acc[r][3]));
+        *reinterpret_cast<uint32_t*>(out + t * o_t + h * o_h + nh * 64 + nt * 8 + tg) =
+            pack_bf16(acc[nt][2 * half], acc[nt][2 * half + 1]);
     }
-  }
 }
 
 template <typename K>

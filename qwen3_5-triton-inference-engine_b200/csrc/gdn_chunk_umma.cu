@@ -19,6 +19,7 @@
 // delta = P beta (v - e^G k S) then needs P only as the right-hand operand of one tensor-core product, so w never exists.
 // Q/K/V chunks arrive by tensor-map TMA (128-byte swizzle) straight from the strided [T, H, 128] activations.
 #include "b200_attn.h"
+#include "gdn_inverse.cuh"
 #include "umma.cuh"
 
 namespace b200 {
@@ -27,7 +28,7 @@ namespace b200 {
 // loads and the MMAs.  Eight warps = two per scheduler, so every thread may hold up to 255 registers (the solve
 // keeps a 64-entry column in registers); a ninth warp would cut that to 168.
 constexpr int GF_THREADS = 256;
-constexpr int GF_LP = 68;         // fp32 pitch of L rows: float4 rows, conflict-free for row-per-lane stores
+constexpr int GF_LP = INV_LP;     // fp32 pitch of L rows: float4 rows, conflict-free for row-per-lane stores
 
 // shared-memory map (bytes from a 1024-aligned base); every operand tile is a swizzled [rows][128 B] block set
 constexpr int GF_SH = 0;                   // S^T hi [128 dv][128 dk]: 2 blocks x 16 KiB
@@ -58,69 +59,6 @@ struct GdnFusedParams {
   int64_t be_t, be_h, g_t, g_h, o_t, o_h;
   int heads;
 };
-
-constexpr int GF_TP = 36;  // fp32 pitch of the merge scratch rows
-
-// One level of the blocked triangular inverse on the 2N x 2N diagonal block at `base`:  P21 = -P22 (L21 P11).
-// merge_a: T = L21 P11, merge_b: P21 = -P22 T; each thread owns one TR x 4 tile (N*N/(4 TR) tiles).  P11 and P22 are
-// lower triangular, which bounds the k range; k runs in unrolled groups of eight so that a group's loads are all in
-// flight before its FMAs.  Everything is fp32.
-template <int N, int TR>
-__device__ __forceinline__ void merge_a(const float* Lm, const float* Pm, float* T, int base, int tile) {
-  constexpr int TPR = N / 4;
-  const int r0 = (tile / TPR) * TR, c0 = (tile % TPR) * 4;
-  float acc[TR][4];
-#pragma unroll
-  for (int i = 0; i < TR; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-  const float* A = Lm + (base + N + r0) * GF_LP + base;
-  const float* B = Pm + base * GF_LP + base + c0;
-  for (int k0 = c0 & ~7; k0 < N; k0 += 8) {  // P11[k][c] = 0 for k < c
-#pragma unroll
-    for (int kk = 0; kk < 8; ++kk) {
-      const int k = k0 + kk;
-      const float4 bq = *reinterpret_cast<const float4*>(B + k * GF_LP);
-#pragma unroll
-      for (int i = 0; i < TR; ++i) {
-        const float av = A[i * GF_LP + k];
-        acc[i][0] = fmaf(av, bq.x, acc[i][0]);
-        acc[i][1] = fmaf(av, bq.y, acc[i][1]);
-        acc[i][2] = fmaf(av, bq.z, acc[i][2]);
-        acc[i][3] = fmaf(av, bq.w, acc[i][3]);
-      }
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < TR; ++i)
-    *reinterpret_cast<float4*>(T + (r0 + i) * GF_TP + c0) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-}
-template <int N, int TR>
-__device__ __forceinline__ void merge_b(float* Pm, const float* T, int base, int tile) {
-  constexpr int TPR = N / 4;
-  const int r0 = (tile / TPR) * TR, c0 = (tile % TPR) * 4;
-  float acc[TR][4];
-#pragma unroll
-  for (int i = 0; i < TR; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-  const float* A = Pm + (base + N + r0) * GF_LP + base + N;
-  for (int k0 = 0; k0 <= r0 + TR - 1; k0 += 8) {  // P22[r][k] = 0 for k > r
-#pragma unroll
-    for (int kk = 0; kk < 8; ++kk) {
-      const int k = k0 + kk;
-      const float4 bq = *reinterpret_cast<const float4*>(T + k * GF_TP + c0);
-#pragma unroll
-      for (int i = 0; i < TR; ++i) {
-        const float av = A[i * GF_LP + k];
-        acc[i][0] = fmaf(-av, bq.x, acc[i][0]);
-        acc[i][1] = fmaf(-av, bq.y, acc[i][1]);
-        acc[i][2] = fmaf(-av, bq.z, acc[i][2]);
-        acc[i][3] = fmaf(-av, bq.w, acc[i][3]);
-      }
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < TR; ++i)
-    *reinterpret_cast<float4*>(Pm + (base + N + r0 + i) * GF_LP + base + c0) =
-        make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-}
 
 __device__ __forceinline__ void split8(const float (&v)[8], uint4& hi, uint4& lo) {
   uint32_t h[4], l[4];
@@ -288,32 +226,8 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     //      product) over the w tiles, then the decay of the state in tensor memory.
     if (warp < 4) {
       float* Pm = reinterpret_cast<float*>(smem + GF_DH);                      // [64][GF_LP] over the delta tiles
-      float* Tm = reinterpret_cast<float*>(smem + GF_DH + CHUNK * GF_LP * 4);  // [32][GF_TP]
-      if (tid < 64) {
-        const int blk = tid >> 4, j = tid & 15;
-        const float* lb = Lm + (16 * blk) * GF_LP + 16 * blk;
-        float xx[16];
-#pragma unroll
-        for (int r = 0; r < 16; ++r) {
-          float a0 = (r == j) ? 1.f : 0.f, a1 = 0.f;
-#pragma unroll
-          for (int i = 0; i < r; ++i) {
-            if (i & 1) a1 = fmaf(-lb[r * GF_LP + i], xx[i], a1);
-            else a0 = fmaf(-lb[r * GF_LP + i], xx[i], a0);
-          }
-          xx[r] = a0 + a1;
-        }
-#pragma unroll
-        for (int r = 0; r < 16; ++r) Pm[(16 * blk + r) * GF_LP + 16 * blk + j] = xx[r];  // after the loop: no aliasing stalls
-      }
-      named_barrier(3, 128);
-      if (tid < 64) merge_a<16, 2>(Lm, Pm, Tm + (tid >> 5) * 16 * GF_TP, 32 * (tid >> 5), tid & 31);
-      named_barrier(3, 128);
-      if (tid < 64) merge_b<16, 2>(Pm, Tm + (tid >> 5) * 16 * GF_TP, 32 * (tid >> 5), tid & 31);
-      named_barrier(3, 128);
-      merge_a<32, 2>(Lm, Pm, Tm, 0, tid);
-      named_barrier(3, 128);
-      merge_b<32, 2>(Pm, Tm, 0, tid);
+      float* Tm = reinterpret_cast<float*>(smem + GF_DH + CHUNK * GF_LP * 4);  // merge scratch, [32][INV_TP]
+      blocked_inverse64(Lm, Pm, Tm, tid);
       named_barrier(4, 128);
       {
         const int t = tid >> 1, i0 = (tid & 1) * 32;
