@@ -977,7 +977,7 @@ def run_prefill_sweep(ops, device, steps, only=None):
                  "gbs": cbytes / (ms * 1e-3) / 1e9, "frac_hbm": cbytes / (ms * 1e-3) / 1e9 / hbm})
     ms = time_steps(lambda i: ops.gdn_chunked_prefill_packed(gq, gk, gv, beta, g, cu, 128, fused=False), steps, 3)
     rows.append({"op": "gdn_chunked_prefill_packed (3 launches)", "shape": "cfg4 B=32 x 128", "tokens": total,
-                 "us": ms * 1e3, "tflops_fp32": 12.1e6 * 2 * len(lengths) * heads / (ms * 1e-3) / 1e12})
+                 "us": ms * 1e3, "tflops": cflops / (ms * 1e-3) / 1e12, "frac_tensor": cflops / (ms * 1e-3) / 1e12 / tf_peak})
     # the same kernel where every SM has work for many chunks: 32 prompts x 1024 tokens (512 CTAs x 16 chunks)
     long_len = [1024] * 32
     lt = sum(long_len)
