@@ -460,6 +460,261 @@ static int launch_ring(GdnRingParams p, const float* state, int heads_total, cud
   return OK;
 }
 
+// ----------------------------------------------------------------- the whole mixer over the ring (large batches)
+// gdn_decode_fused_kernel keeps a head's state in 128 registers per thread: two CTAs per SM, so 512 heads (B = 32) run
+// as two waves that each load, compute and store in lockstep.  This form streams the state through the ring above
+// instead: a CTA (128 compute threads + the copy warp) takes WHOLE heads - the head-wide steps (q/k norms, gated
+// RMSNorm) stay inside it - as eight [128 x 16] boxes each; four CTAs with six boxes in flight share an SM, every head
+// of a 32-sequence batch is resident at once, and a head's conv / norm / gate chain runs while its first boxes are on
+// their way.  The arithmetic of a box is that of gdn_decode_ring_kernel<16, 128, ...> (same summation order); the
+// operands of the NEXT head of a CTA are fetched while the current head's boxes are worked on.
+struct GdnMixerParams {
+  const __nv_bfloat16* fused;  // read after pdl_wait(): no __restrict__ anywhere on this path
+  int64_t fused_stride;
+  __nv_bfloat16* conv_state;
+  const __nv_bfloat16* w4;
+  const float* a_log;
+  const __nv_bfloat16* dt_bias;
+  const float* norm_w;
+  __nv_bfloat16* out;
+  int* err;
+  int heads_total, heads, overlap;
+};
+
+constexpr int MX_COLS = 16, MX_THREADS = GDN_D, MX_GROUPS = MX_THREADS / MX_COLS, MX_ROWS = GDN_D / MX_GROUPS;
+constexpr int MX_PER_HEAD = GDN_D / MX_COLS, MX_BOX = GDN_D * MX_COLS;
+
+template <int STAGES, int CTAS>
+__global__ void __launch_bounds__(MX_THREADS + 32, CTAS)
+gdn_mixer_ring_kernel(const __grid_constant__ GdnMixerParams p, const __grid_constant__ CUtensorMap map_state) {
+  extern __shared__ __align__(128) uint8_t ring_raw[];
+  __shared__ uint64_t full[STAGES], done[STAGES];
+  __shared__ __align__(16) float kf[GDN_D];
+  __shared__ __align__(16) float qf[GDN_D];
+  __shared__ float vf[GDN_D];
+  __shared__ float of[GDN_D];                      // the head's recurrence output, value column by value column
+  __shared__ float red[2][MX_GROUPS][MX_COLS];     // [k^T S | q^T S][row group][column]
+  __shared__ float nred[3][4];                     // per-warp sums of the three head-wide norms
+  __shared__ float gate_s[2];
+  __shared__ int failed;
+  float* bufs = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(ring_raw) + 127) & ~uintptr_t(127));
+  const int t = threadIdx.x;
+  const int stride = static_cast<int>(gridDim.x), first = static_cast<int>(blockIdx.x);
+  const int my_heads = (p.heads_total - first + stride - 1) / stride;
+  const int my_items = my_heads * MX_PER_HEAD;
+  const bool prefetch = (p.overlap & OVERLAP_PREFETCH) != 0;
+  if (t == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&done[s], MX_THREADS);
+    }
+    failed = 0;
+    mbar_fence_init();
+    prefetch_tensormap(&map_state);
+  }
+  __syncthreads();
+  if (p.overlap & OVERLAP_TRIGGER) pdl_trigger();
+  // Without PREFETCH nothing is read before the kernel in front has finished.  With it the caller guarantees that the
+  // conv state and the recurrent state were last written by an EARLIER kernel, so their loads go out first; `fused` is
+  // read, and everything is stored, after the wait.
+  if (!prefetch) pdl_wait();
+
+  if (t >= MX_THREADS) {
+    // ------------------------------------------------------------------------------------------- copy warp
+    if (t != MX_THREADS) return;
+    auto coords = [&](int n, int& x, int& y) {
+      x = (n % MX_PER_HEAD) * MX_COLS;
+      y = (first + (n / MX_PER_HEAD) * stride) * GDN_D;
+    };
+    auto load = [&](int n) {
+      int x, y;
+      coords(n, x, y);
+      mbar_expect_tx(&full[n % STAGES], MX_BOX * 4);
+      tma_load_2d(bufs + (n % STAGES) * MX_BOX, &map_state, x, y, &full[n % STAGES]);
+    };
+    const int ahead = min(my_items, STAGES);
+    for (int n = 0; n < ahead; ++n) load(n);
+    if (prefetch) pdl_wait();  // before the first store
+    int loaded = ahead, n = 0;
+    for (; n < my_items; ++n) {
+      if (!mbar_wait_bounded(&done[n % STAGES], (n / STAGES) & 1)) break;  // the compute part gave up (or is lost)
+      int x, y;
+      coords(n, x, y);
+      tma_store_2d(&map_state, x, y, bufs + (n % STAGES) * MX_BOX);
+      if (n + STAGES < my_items) {
+        bulk_wait_read();  // the store just issued has read its buffer: the box of item n + STAGES may land there
+        load(n + STAGES);
+        loaded = n + STAGES + 1;
+      }
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all stores complete before the CTA ends
+    if (n < my_items) {
+      atomicExch(p.err, 1);
+      for (int m = n; m < loaded; ++m) mbar_wait_bounded(&full[m % STAGES], (m / STAGES) & 1, 1u << 12);
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------------------------------------- compute part
+  // thread t = channel t of the head's q, k, v and z slices in the head-wide steps; in a box it is column t % 16 of row
+  // group t / 16, rows dealt round-robin (row i * 8 + group), kf / qf stored in the matching order
+  const int c = t % MX_COLS, rg = t / MX_COLS;
+  const int kslot = (t % MX_GROUPS) * MX_ROWS + t / MX_GROUPS;
+  const int kd = p.heads * GDN_D, width = 3 * kd;
+  const float wv = p.norm_w[t];
+  // operands of one head in registers: the three earlier conv rows, the four taps, then (after the wait) the new row
+  __nv_bfloat16 cs[3][3], cw[3][4], cx[3], zraw, araw, braw;
+  float a_log_h = 0.f, dt_bias_h = 0.f;
+  auto fetch_state_side = [&](int head) {  // nothing the kernel in front writes
+    const int b = head / p.heads, h = head % p.heads;
+#pragma unroll
+    for (int part = 0; part < 3; ++part) {
+      const int ch = part * kd + h * GDN_D + t;
+      const __nv_bfloat16* st = p.conv_state + static_cast<int64_t>(b) * 4 * width + ch;
+      cs[part][0] = st[width];
+      cs[part][1] = st[2 * width];
+      cs[part][2] = st[3 * width];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) cw[part][r] = p.w4[r * width + ch];
+    }
+    a_log_h = p.a_log[h];
+    dt_bias_h = __bfloat162float(p.dt_bias[h]);
+  };
+  auto fetch_row_side = [&](int head) {  // the projection row: only after the wait
+    const int b = head / p.heads, h = head % p.heads;
+    const __nv_bfloat16* row = p.fused + static_cast<int64_t>(b) * p.fused_stride;
+#pragma unroll
+    for (int part = 0; part < 3; ++part) cx[part] = row[part * kd + h * GDN_D + t];
+    zraw = row[width + h * GDN_D + t];
+    araw = row[width + kd + h];
+    braw = row[width + kd + p.heads + h];
+  };
+  if (my_heads > 0) fetch_state_side(first);
+  if (prefetch) pdl_wait();
+  if (my_heads > 0) fetch_row_side(first);
+
+  for (int j = 0; j < my_heads; ++j) {
+    const int head = first + j * stride, b = head / p.heads, h = head % p.heads;
+    // ---- conv state shift + conv4 + SiLU, q/k L2 norms, gates (the fused kernel's arithmetic, rounding point by
+    //      rounding point)
+    float y[3];
+#pragma unroll
+    for (int part = 0; part < 3; ++part) {
+      const int ch = part * kd + h * GDN_D + t;
+      __nv_bfloat16* st = p.conv_state + static_cast<int64_t>(b) * 4 * width + ch;
+      st[0] = cs[part][0];
+      st[width] = cs[part][1];
+      st[2 * width] = cs[part][2];
+      st[3 * width] = cx[part];
+      float acc = __bfloat162float(cw[part][0]) * __bfloat162float(cs[part][0]);
+      acc = fmaf(__bfloat162float(cw[part][1]), __bfloat162float(cs[part][1]), acc);
+      acc = fmaf(__bfloat162float(cw[part][2]), __bfloat162float(cs[part][2]), acc);
+      acc = fmaf(__bfloat162float(cw[part][3]), __bfloat162float(cx[part]), acc);
+      y[part] = round_bf16(acc / (1.0f + expf(-acc)));
+    }
+    const float zv = __bfloat162float(zraw);
+    float sq = warp_sum(y[0] * y[0]), sk = warp_sum(y[1] * y[1]);
+    if ((t & 31) == 0) {
+      nred[0][t >> 5] = sq;
+      nred[1][t >> 5] = sk;
+    }
+    if (t == 0) {
+      const float av = __bfloat162float(araw) + dt_bias_h;
+      const float sp_ = av > 20.f ? av : log1pf(expf(av));
+      gate_s[0] = 1.0f / (1.0f + expf(-__bfloat162float(braw)));  // beta
+      gate_s[1] = __expf(-expf(a_log_h) * sp_);                    // exp(g)
+    }
+    // the next head's operands start their way now and are used after this head's boxes
+    if (j + 1 < my_heads) {
+      fetch_state_side(head + stride);
+      fetch_row_side(head + stride);
+    }
+    named_barrier(2, MX_THREADS);
+    sq = (nred[0][0] + nred[0][1]) + (nred[0][2] + nred[0][3]);
+    sk = (nred[1][0] + nred[1][1]) + (nred[1][2] + nred[1][3]);
+    // kf / qf / vf of the previous head are no longer read: every compute thread has passed its last box's barriers
+    qf[kslot] = round_bf16(y[0] * rsqrtf(sq + 1e-6f) * 0.08838834764831845f);  // DK^-0.5
+    kf[kslot] = round_bf16(y[1] * rsqrtf(sk + 1e-6f));
+    vf[t] = y[2];
+    const float eg = gate_s[1], bt = gate_s[0];
+
+    bool lost = false;
+    for (int box = 0; box < MX_PER_HEAD; ++box) {
+      const int n = j * MX_PER_HEAD + box;
+      float* buf = bufs + (n % STAGES) * MX_BOX;
+      if (!mbar_wait_bounded(&full[n % STAGES], (n / STAGES) & 1)) failed = 1;
+      named_barrier(1, MX_THREADS);  // kf / qf / vf visible; the compute part agrees on whether the box arrived
+      if (*reinterpret_cast<volatile int*>(&failed)) {
+        lost = true;
+        break;  // a lost copy: this box's state and the head's output stay untouched
+      }
+      float s[MX_ROWS];
+      float* col = buf + rg * MX_COLS + c;
+      constexpr int RSTEP = MX_GROUPS * MX_COLS;  // floats between consecutive rows of this thread
+      const float* kh = kf + rg * MX_ROWS;
+      const float* qh = qf + rg * MX_ROWS;
+      float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < MX_ROWS; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kh + i);
+        s[i] = col[i * RSTEP] * eg;
+        s[i + 1] = col[(i + 1) * RSTEP] * eg;
+        s[i + 2] = col[(i + 2) * RSTEP] * eg;
+        s[i + 3] = col[(i + 3) * RSTEP] * eg;
+        m0 = fmaf(k4.x, s[i], m0);
+        m1 = fmaf(k4.y, s[i + 1], m1);
+        m2 = fmaf(k4.z, s[i + 2], m2);
+        m3 = fmaf(k4.w, s[i + 3], m3);
+      }
+      red[0][rg][c] = (m0 + m1) + (m2 + m3);
+      named_barrier(1, MX_THREADS);
+      float mem = 0.f;
+#pragma unroll
+      for (int r = 0; r < MX_GROUPS; ++r) mem += red[0][r][c];
+      const float delta = bt * (vf[box * MX_COLS + c] - mem);
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < MX_ROWS; i += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kh + i);
+        const float4 q4 = *reinterpret_cast<const float4*>(qh + i);
+        s[i] = fmaf(k4.x, delta, s[i]);
+        s[i + 1] = fmaf(k4.y, delta, s[i + 1]);
+        s[i + 2] = fmaf(k4.z, delta, s[i + 2]);
+        s[i + 3] = fmaf(k4.w, delta, s[i + 3]);
+        o0 = fmaf(q4.x, s[i], o0);
+        o1 = fmaf(q4.y, s[i + 1], o1);
+        o2 = fmaf(q4.z, s[i + 2], o2);
+        o3 = fmaf(q4.w, s[i + 3], o3);
+        col[i * RSTEP] = s[i];
+        col[(i + 1) * RSTEP] = s[i + 1];
+        col[(i + 2) * RSTEP] = s[i + 2];
+        col[(i + 3) * RSTEP] = s[i + 3];
+      }
+      red[1][rg][c] = (o0 + o1) + (o2 + o3);
+      fence_proxy_async();             // generic-proxy stores of the box before the TMA store reads them
+      mbar_arrive(&done[n % STAGES]);  // the copy warp stores the box once all compute threads have arrived
+      named_barrier(1, MX_THREADS);
+      if (rg == 0) {
+        float o = 0.f;
+#pragma unroll
+        for (int r = 0; r < MX_GROUPS; ++r) o += red[1][r][c];
+        of[box * MX_COLS + c] = o;
+      }
+    }
+    if (lost) break;
+    // ---- gated RMSNorm over the head's 128 outputs
+    named_barrier(2, MX_THREADS);  // `of` complete
+    const float x = round_bf16(of[t]);
+    const float ss = warp_sum(x * x);
+    if ((t & 31) == 0) nred[2][t >> 5] = ss;
+    named_barrier(2, MX_THREADS);
+    const float rs = rsqrtf(((nred[2][0] + nred[2][1]) + (nred[2][2] + nred[2][3])) / static_cast<float>(GDN_D) + 1e-6f);
+    p.out[(static_cast<int64_t>(b) * p.heads + h) * GDN_D + t] = __float2bfloat16_rn(x * rs * wv * (zv / (1.0f + expf(-zv))));
+  }
+}
+
+constexpr int MX_STAGES = 6, MX_CTAS = 4;
+
 constexpr int SEQ_TILE = 16;  // tokens staged in shared memory per step of the prefill loop
 
 __global__ void __launch_bounds__(GDN_THREADS)
@@ -582,6 +837,46 @@ extern "C" int b200_gdn_decode_fused(const void* fused, int64_t fused_stride, vo
                                      int32_t overlap, b200_stream_t stream) {
   B200_REQUIRE(batch > 0 && num_heads > 0 && head_dim == GDN_D, "gdn_decode_fused: head_dim must be %d (got %d)", GDN_D,
                head_dim);
+  // More heads than two register-resident CTAs per SM can hold at once: the ring form (b200_gdn_recurrent_decode_form
+  // 1 / 3 force either form here too).
+  const int64_t heads_total = static_cast<int64_t>(batch) * num_heads;
+  const int form = g_gdn_decode_form.load();
+  const bool ring_ok = aligned16(state) && heads_total * GDN_D < (1LL << 31);
+  if (ring_ok && (form == 3 || (form != 1 && heads_total > 2 * sm_count()))) {
+    constexpr int SMEM = MX_STAGES * MX_BOX * 4 + 128;
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+      if (cudaFuncSetAttribute(gdn_mixer_ring_kernel<MX_STAGES, MX_CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               SMEM) != cudaSuccess)
+        return fail(ERR_RUNTIME, "gdn_decode_fused: cannot raise dynamic shared memory to %d", SMEM);
+      configured[dev] = true;
+    }
+    CUtensorMap map;
+    if (!encode_state_map(&map, state, heads_total * GDN_D, MX_COLS))
+      return fail(ERR_RUNTIME, "gdn_decode_fused: cannot encode the state tensor map");
+    GdnMixerParams p;
+    p.fused = static_cast<const __nv_bfloat16*>(fused);
+    p.fused_stride = fused_stride;
+    p.conv_state = static_cast<__nv_bfloat16*>(conv_state);
+    p.w4 = static_cast<const __nv_bfloat16*>(weight4);
+    p.a_log = a_log;
+    p.dt_bias = static_cast<const __nv_bfloat16*>(dt_bias);
+    p.norm_w = norm_weight;
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.err = wait_timeout_flag();
+    if (!p.err) return fail(ERR_RUNTIME, "gdn_decode_fused: no error flag");
+    p.heads_total = static_cast<int>(heads_total);
+    p.heads = num_heads;
+    p.overlap = overlap;
+    const int slots = MX_CTAS * sm_count();
+    const int grid = heads_total < slots ? static_cast<int>(heads_total) : slots;
+    if (launch_pdl((overlap & OVERLAP_START) != 0, gdn_mixer_ring_kernel<MX_STAGES, MX_CTAS>, dim3(grid),
+                   dim3(MX_THREADS + 32), SMEM, reinterpret_cast<cudaStream_t>(stream), p, map) != cudaSuccess)
+      return fail(ERR_LAUNCH, "gdn_decode_fused: %s", cudaGetErrorString(cudaGetLastError()));
+    return check_launch("gdn_decode_fused");
+  }
   if (launch_pdl((overlap & OVERLAP_START) != 0, gdn_decode_fused_kernel, dim3(static_cast<unsigned>(batch) * num_heads), dim3(GDN_THREADS), 0,
                  reinterpret_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(fused), fused_stride,
                  static_cast<__nv_bfloat16*>(conv_state), static_cast<const __nv_bfloat16*>(weight4), a_log,

@@ -182,19 +182,53 @@ def test_gdn_gated_rmsnorm(mods):
 
 
 @pytest.mark.parametrize("prefetch", [0, 1 | 4])
-@pytest.mark.parametrize("batch", [1, 32])
-def test_gdn_decode_fused_equals_chain(mods, batch, prefetch):
+@pytest.mark.parametrize("batch,form", [(1, 1), (32, 1), (1, 3), (32, 3), (40, 3)])
+def test_gdn_decode_fused_equals_chain(mods, batch, form, prefetch):
     """One-launch Gated-DeltaNet decode mixer against prep -> recurrent_decode -> gated RMSNorm over three steps
-    (conv state and recurrent state carried in place).  The chain's recurrence is pinned to the one-CTA-per-head form,
-    which sums in the fused kernel's order: the comparison is then about the fusion, not about fp32 summation order
-    (an output that nearly cancels moves by more than two bf16 ulps of itself between orders)."""
+    (conv state and recurrent state carried in place), in both of its forms: 1 = a head's state in registers, 3 = the
+    state streamed through the ring of [128 x 16] boxes (40 sequences x 16 heads are more heads than CTAs fit the GPU,
+    so some CTAs take a second head).  The chain's recurrence is pinned to the same form, which sums in the fused
+    kernel's order: the comparison is then about the fusion, not about fp32 summation order (an output that nearly
+    cancels moves by more than two bf16 ulps of itself between orders)."""
     from b200attn import _lib
     ops, glue = mods
-    _lib.call("b200_gdn_recurrent_decode_form", 1)
+    _lib.call("b200_gdn_recurrent_decode_form", form)
     try:
         _fused_against_chain(ops, batch, prefetch)
     finally:
         _lib.call("b200_gdn_recurrent_decode_form", 0)
+
+
+def test_gdn_decode_fused_forms_agree(mods):
+    """The form the sizes choose (ring from more than two heads per SM on) against the register form on the same
+    inputs: conv state bit-equal, recurrent state and output to summation-order accuracy."""
+    from b200attn import _lib
+    ops, _ = mods
+    gen = torch.Generator().manual_seed(17)
+    batch, heads, kd = 48, 16, 2048
+    w4 = (torch.randn(4, 3 * kd, generator=gen) * 0.5).to(torch.bfloat16).to(DEV)
+    a_log = (torch.rand(heads, generator=gen) * 2.7).to(DEV)
+    dt_bias = (torch.randn(heads, generator=gen) * 0.5).to(torch.bfloat16).to(DEV)
+    norm_w = (1 + 0.1 * torch.randn(128, generator=gen)).to(DEV)
+    conv = torch.randn(batch, 4, 3 * kd, generator=gen).to(torch.bfloat16).to(DEV)
+    state = (torch.randn(batch, heads, 128, 128, generator=gen) * 0.1).to(DEV)
+    fused = torch.randn(batch, 4 * kd + 2 * heads, generator=gen).to(torch.bfloat16).to(DEV)
+    results = []
+    for form in (1, 0):
+        _lib.call("b200_gdn_recurrent_decode_form", form)
+        try:
+            c, s = conv.clone(), state.clone()
+            out = ops.gdn_decode_fused(fused, c, w4, a_log, dt_bias, norm_w, s, heads)
+            results.append((c, s, out))
+        finally:
+            _lib.call("b200_gdn_recurrent_decode_form", 0)
+    torch.cuda.synchronize()
+    assert _lib.load().b200_wait_timed_out() == 0
+    assert torch.equal(results[0][0], results[1][0])
+    assert torch.allclose(results[0][1], results[1][1], rtol=1e-5, atol=1e-6)
+    close = ((results[0][2].float() - results[1][2].float()).abs()
+             <= 2.0 ** -6 * results[0][2].float().abs() + 2e-3)
+    assert close.float().mean().item() > 0.999
 
 
 def _fused_against_chain(ops, batch, prefetch):
