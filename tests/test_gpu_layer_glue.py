@@ -186,15 +186,17 @@ def test_gdn_gated_rmsnorm(mods):
 def test_gdn_decode_fused_equals_chain(mods, batch, form, prefetch):
     """One-launch Gated-DeltaNet decode mixer against prep -> recurrent_decode -> gated RMSNorm over three steps
     (conv state and recurrent state carried in place), in both of its forms: 1 = a head's state in registers, 3 = the
-    state streamed through the ring of [128 x 16] boxes (40 sequences x 16 heads are more heads than CTAs fit the GPU,
-    so some CTAs take a second head).  The chain's recurrence is pinned to the same form, which sums in the fused
-    kernel's order: the comparison is then about the fusion, not about fp32 summation order (an output that nearly
-    cancels moves by more than two bf16 ulps of itself between orders)."""
+    state streamed through a ring of [128 x 32] boxes (40 sequences x 16 heads are more heads than CTAs fit the GPU,
+    so some CTAs take a second head).  In form 1 the chain's recurrence sums in the fused kernel's order and the
+    outputs agree to two bf16 ulps: the comparison is then about the fusion, not about fp32 summation order.  The ring
+    mixer sums a column in four row groups, the ring recurrence of the chain in eight: an output that nearly cancels
+    moves by more than two bf16 ulps of itself between orders, so there the output bar is two ulps of a value of
+    order one plus a small absolute term; conv state (bit-exact) and recurrent state (1e-5) keep their bars."""
     from b200attn import _lib
     ops, glue = mods
     _lib.call("b200_gdn_recurrent_decode_form", form)
     try:
-        _fused_against_chain(ops, batch, prefetch)
+        _fused_against_chain(ops, batch, prefetch, same_order=form == 1)
     finally:
         _lib.call("b200_gdn_recurrent_decode_form", 0)
 
@@ -231,7 +233,7 @@ def test_gdn_decode_fused_forms_agree(mods):
     assert close.float().mean().item() > 0.999
 
 
-def _fused_against_chain(ops, batch, prefetch):
+def _fused_against_chain(ops, batch, prefetch, same_order=True):
     gen = torch.Generator().manual_seed(90 + batch)
     heads, kd = 16, 2048
     w4 = (torch.randn(4, 3 * kd, generator=gen) * 0.5).to(torch.bfloat16).to(DEV)
@@ -250,7 +252,10 @@ def _fused_against_chain(ops, batch, prefetch):
         out = ops.gdn_decode_fused(fused, conv_b, w4, a_log, dt_bias, norm_w, state_b, heads, overlap=prefetch)
         assert torch.equal(conv_a, conv_b)
         assert torch.allclose(state_a, state_b, rtol=1e-5, atol=1e-6)
-        _ulp_close(out, ref, ulps=2)
+        if same_order:
+            _ulp_close(out, ref, ulps=2)
+        else:
+            assert torch.allclose(out.float(), ref.float(), rtol=2.0 ** -6, atol=4e-3)
 
 
 @pytest.mark.parametrize("m,n,k", [(32, 8224, 1024), (1, 5120, 1024), (17, 7168, 1024), (32, 248320, 1024), (8, 512, 256),
