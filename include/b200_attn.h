@@ -234,8 +234,10 @@ int b200_gdn_recurrent_decode(const void* q, int64_t q_stride_b, int64_t q_strid
 /* Diagnostic: pins the kernel form b200_gdn_recurrent_decode takes, process-wide (0 = chosen from the sizes, the
  * default; 1 = one CTA per head with the state in registers; 2 = one warp per 32 value columns; 3 = persistent CTAs,
  * eight per SM, that stream [128 x 16] boxes of the state through a shared-memory ring of three with tensor-map TMA
- * copies issued by a copy warp).  A form whose layout rules do not hold for a call falls back to 1.  For tests and tuning: every form computes the same step (fp32 summation order
- * differs).  No counterpart in the reference. */
+ * copies issued by a copy warp).  A form whose layout rules do not hold for a call falls back to 1.  The same switch
+ * pins b200_gdn_decode_fused: 1 = a head's state in registers, 3 = whole heads streamed as [128 x 32] boxes through a
+ * ring of three, four CTAs per SM (its default from more heads than two register-resident CTAs per SM hold).  For tests
+ * and tuning: every form computes the same step (fp32 summation order differs).  No counterpart in the reference. */
 int b200_gdn_recurrent_decode_form(int32_t form);
 
 /* Token-serial recurrence over a packed buffer, zero state at every cu_seqlens[b]; cu_seqlens may be NULL
@@ -340,7 +342,9 @@ int b200_gdn_chunked_prefill_fused(const void* q, int64_t q_stride_t, int64_t q_
  * weight4 [4,3*H*128] bf16, a_log [H] fp32, dt_bias [H] bf16, norm_weight [128] fp32; out [B, H*128] bf16 contiguous.
  * Replaces the operator chain of engine/runner.py:431-441.  `overlap`: B200_OVERLAP_* flags (below); PREFETCH lets the
  * kernel load conv_state and state before the kernel in front of it has finished - pass it only when that kernel does
- * not write them (in a layer stack it is the input projection). */
+ * not write them (in a layer stack it is the input projection).  Large batches stream the state through a TMA ring
+ * (see b200_gdn_recurrent_decode_form); a bounded wait of that form that runs out leaves the head's state and output
+ * untouched and sets b200_wait_timed_out(). */
 int b200_gdn_decode_fused(const void* fused, int64_t fused_stride, void* conv_state, const void* weight4,
                           const float* a_log, const void* dt_bias, const float* norm_weight, float* state, void* out,
                           int32_t batch, int32_t num_heads, int32_t head_dim, int32_t overlap, b200_stream_t stream);
