@@ -854,7 +854,21 @@ def run_gdn_decode_rows(ops, device, peak, steps, batches):
         ms = time_steps(lambda i: ops.gdn_recurrent_decode(q, k, v, beta, g, states[i % sets]), steps, 3)
         rows.append({"op": "gdn_recurrent_decode", "B": b, "us_per_layer": ms * 1e3, "gbs": nbytes / (ms * 1e-3) / 1e9,
                      "frac": nbytes / (ms * 1e-3) / 1e9 / peak})
-        del states
+        # the whole mixer of a layer in one launch (conv + SiLU, norms, gates, the step above, gated RMSNorm): the same
+        # state bytes plus the conv state [B, 4, 6144] bf16 in and out
+        kd = 16 * 128
+        w4 = (torch.randn(4, 3 * kd, generator=gen) * 0.5).to(torch.bfloat16).to(device)
+        a_log = (torch.rand(16, generator=gen) * 2.7).to(device)
+        dt_bias = (torch.randn(16, generator=gen) * 0.5).to(torch.bfloat16).to(device)
+        norm_w = (1 + 0.1 * torch.randn(128, generator=gen)).to(device)
+        convs = [torch.zeros(b, 4, 3 * kd, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+        row_in = torch.randn(b, 4 * kd + 32, generator=gen).to(torch.bfloat16).to(device)
+        ms = time_steps(lambda i: ops.gdn_decode_fused(row_in, convs[i % sets], w4, a_log, dt_bias, norm_w,
+                                                       states[i % sets], 16), steps, 3)
+        mbytes = nbytes + 2 * b * 4 * 3 * kd * 2
+        rows.append({"op": "gdn_decode_fused (mixer, one launch)", "B": b, "us_per_layer": ms * 1e3,
+                     "gbs": mbytes / (ms * 1e-3) / 1e9, "frac": mbytes / (ms * 1e-3) / 1e9 / peak})
+        del states, convs
         torch.cuda.empty_cache()
     return rows
 
