@@ -201,13 +201,15 @@ def test_gdn_decode_fused_equals_chain(mods, batch, form, prefetch):
         _lib.call("b200_gdn_recurrent_decode_form", 0)
 
 
-def test_gdn_decode_fused_forms_agree(mods):
-    """The form the sizes choose (ring from more than two heads per SM on) against the register form on the same
-    inputs: conv state bit-equal, recurrent state and output to summation-order accuracy."""
+@pytest.mark.parametrize("batch", [48, 256])
+def test_gdn_decode_fused_forms_agree(mods, batch):
+    """The form the sizes choose (ring from more than two heads per SM on; at 256 sequences every CTA walks seven
+    heads) against the register form on the same inputs: conv state bit-equal, recurrent state and output to
+    summation-order accuracy."""
     from b200attn import _lib
     ops, _ = mods
     gen = torch.Generator().manual_seed(17)
-    batch, heads, kd = 48, 16, 2048
+    heads, kd = 16, 2048
     w4 = (torch.randn(4, 3 * kd, generator=gen) * 0.5).to(torch.bfloat16).to(DEV)
     a_log = (torch.rand(heads, generator=gen) * 2.7).to(DEV)
     dt_bias = (torch.randn(heads, generator=gen) * 0.5).to(torch.bfloat16).to(DEV)
