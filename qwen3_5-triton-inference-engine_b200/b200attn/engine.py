@@ -361,7 +361,7 @@ class Engine:
         def then(own_next: bool) -> int:                 # flags of a kernel whose successor is (not) one of ours
             return start | trigger if own_next else start
 
-        x = glue.embedding_gather(tok, self.w["embed"])
+        x = _embedding_gather(tok, self.w["embed"])      # this package's kernel: the norm behind it may start early
         pending = None                                   # MLP output still to be added to the residual stream
         for i, layer in enumerate(self.w["layers"]):
             gdn = layer["kind"] == "gdn"
@@ -401,7 +401,10 @@ class Engine:
                     and ops.skinny_gemm_supports(batch, embed.shape[0], embed.shape[1]))
         _, h = ops.add_rmsnorm(pending, self.w["norm"], cfg.eps, residual=x, overlap=then(own_head))
         if own_head:   # tied LM head and greedy sampling in one launch; the logits are never written
-            nxt = ops.lm_head_argmax(h, embed, self.argmax_ws, overlap=start)
+            # the ids go straight into `tok` when it is the engine's own token buffer (read only by the gather at the
+            # top of the step): no copy kernel behind the step
+            in_place = tok.data_ptr() == self.tok.data_ptr() and tok.dtype == torch.int64 and tok.is_contiguous()
+            nxt = ops.lm_head_argmax(h, embed, self.argmax_ws, out=tok if in_place else None, overlap=start)
         else:          # fp32 logits from cuBLAS, arg-max (lowest index on ties) in one launch
             nxt = glue.lm_head_argmax(h, embed, last_only=False,
                                       argmax=lambda logits: ops.argmax_rows(logits, self.argmax_ws, overlap=start))
@@ -420,7 +423,7 @@ class Engine:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(side):
             with torch.cuda.graph(graph, stream=side):
-                self.tok.copy_(self._decode(self.tok))
+                self._advance()
         torch.cuda.current_stream(self.device).wait_stream(side)
         self.graph = graph
 
@@ -430,6 +433,11 @@ class Engine:
         if self.graph is not None:
             self.graph.replay()
         else:
-            self.tok.copy_(self._decode(self.tok))
+            self._advance()
             self._warmed = True
         return self.tok
+
+    def _advance(self) -> None:
+        nxt = self._decode(self.tok)
+        if nxt.data_ptr() != self.tok.data_ptr():        # a step that did not write the ids in place
+            self.tok.copy_(nxt)
