@@ -274,7 +274,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
       }
       const uint8_t* vcol = smem + GF_V + (dv >> 6) * 8192 + (dv & 7) * 2;
       const int vch = (dv & 63) >> 3;
-#pragma unroll
+#pragma unroll 1  // rolled: the phase's code stays a half / a quarter as long (instruction cache)
       for (int hf = 0; hf < 2; ++hf) {
         uint32_t d[32];
         if (c > 0) {
@@ -302,7 +302,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
       if (c > 0) {
         const float decay = s_eG[CHUNK - 1];
         uint32_t d[32];
-#pragma unroll
+#pragma unroll 1  // rolled: the phase's code stays a half / a quarter as long (instruction cache)
         for (int qd = 0; qd < 4; ++qd) {
           tmem_ld32(tlane + TM_S + qd * 32, d);
           tmem_ld_wait();
@@ -399,7 +399,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
       // out^T -> [t][dv] bf16 staged in the (now free) delta tile, then whole rows go out as 16-byte stores
       const int dv = tid;
       __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(smem + GF_DH);
-#pragma unroll
+#pragma unroll 1  // rolled: the phase's code stays a half / a quarter as long (instruction cache)
       for (int hf = 0; hf < 2; ++hf) {
         uint32_t o2[32], o1[32];
         tmem_ld32(tlane + TM_O2 + hf * 32, o2);
@@ -423,7 +423,7 @@ gdn_chunk_fused_kernel(const __grid_constant__ GdnFusedParams p, const __grid_co
     } else {
       const int dv = tid - 128;
       uint32_t d[32];
-#pragma unroll
+#pragma unroll 1  // rolled: the phase's code stays a half / a quarter as long (instruction cache)
       for (int qd = 0; qd < 4; ++qd) {
         tmem_ld32(tlane + TM_S + qd * 32, d);
         tmem_ld_wait();
