@@ -2,7 +2,11 @@
 
 With the `triton_kernels` drop-in alone the reference runner runs unchanged, operator by operator.  This subclass keeps
 the runner, its caches (`engine/cache.py`), its page table (`engine/paging.py`) and its CUDA-graph decoder, and
-replaces only the four mixer methods where one launch of this package does the work of a chain of operators:
+replaces only the decode step's layer loop and the four mixer methods where one launch of this package does the work of a
+chain of operators:
+
+    decode_step        the layer loop of engine/runner.py:520-571 on the row-wise one-launch operators (residual add +
+                       RMSNorm, projection with SwiGLU epilogue) with early starts between this package's kernels
 
     _attention_decode  fused_decode_attention: q/k head norms + partial RoPE + KV append + paged attention + gate
                        (engine/runner.py:444-518 is eleven operator calls)
@@ -37,6 +41,71 @@ def fast_runner_class():
             self._fused_ws = ops.fused_decode_workspace(self.device)
 
         # ------------------------------------------------------------------------------------------- decode
+        def decode_step(self, token_id, caches, trace=None):
+            """engine/runner.py:520-571 with seven launches per layer instead of about fourteen: the residual add
+            rides in the RMSNorm behind it, the SwiGLU is the epilogue of the gate/up projection, the mixers are the
+            one-launch forms, and kernels of this package that follow one another start early (programmatic dependent
+            launch).  Traced calls and contiguous (unpaged) caches take the reference's method."""
+            paged = caches.block_table is not None and all(
+                c is None or c.is_contiguous() for c in list(caches.k_caches) + list(caches.v_caches))
+            if trace is not None or not paged:
+                return super().decode_step(token_id, caches, trace)
+            start, trigger, prefetch = ops.OVERLAP_START, ops.OVERLAP_TRIGGER, ops.OVERLAP_PREFETCH
+            batch = token_id.shape[0]
+            nh, nkv, d = self.w.num_attention_heads, self.w.num_key_value_heads, self.w.head_dim
+            qd, kvd = nh * d, nkv * d
+
+            def own(weight, swiglu=False):   # does this projection run on the package's weight-streaming kernel?
+                n = weight.shape[0] // 2 if swiglu else weight.shape[0]
+                return (weight.shape[1] <= ops.SKINNY_GEMM_PAIR_MAX_K
+                        and ops.skinny_gemm_supports(batch, n, weight.shape[1], swiglu))
+
+            def then(own_next):              # only a kernel of this package in front may be told to let its successor in
+                return start | trigger if own_next else start
+
+            def proj(x, weight, flags):
+                return ops.skinny_gemm(x, weight, overlap=flags) if own(weight) else gemm_2d(x, weight)
+
+            x = R.embedding_gather(token_id, self.w.embed_tokens)
+            pending = None                   # MLP output still to be added to the residual stream
+            for i, layer in enumerate(self.w.layers):
+                gdn = isinstance(layer, R.GDNLayerWeights)
+                proj_w = layer.in_proj_fused if gdn else layer.qkvg_fused
+                out_w = layer.out_proj if gdn else layer.o_proj
+                own_proj, own_out = own(proj_w), own(out_w)
+                own_mlp, own_down = own(layer.mlp.gate_up, True), own(layer.mlp.down_proj)
+                if pending is None:
+                    h = ops.add_rmsnorm(x, layer.input_layernorm, self.eps, overlap=then(own_proj))
+                else:
+                    x, h = ops.add_rmsnorm(pending, layer.input_layernorm, self.eps, residual=x, overlap=then(own_proj))
+                fused = proj(h, proj_w, then(True))
+                if gdn:
+                    mixed_in = ops.gdn_decode_fused(fused, caches.conv_states[i], layer.conv1d_decode, layer.a_log,
+                                                    layer.dt_bias, layer.norm, caches.recurrent_states[i],
+                                                    self.w.linear_num_heads, overlap=then(own_out) | prefetch)
+                else:
+                    q = fused[:, :qd].view(batch, nh, d)
+                    k = fused[:, 2 * qd: 2 * qd + kvd].view(batch, nkv, d)
+                    v = fused[:, 2 * qd + kvd:].view(batch, nkv, d)
+                    mixed_in = ops.fused_decode_attention(q, k, v, fused[:, qd: 2 * qd], caches.k_caches[i],
+                                                          caches.v_caches[i], caches.block_table, caches.pos,
+                                                          self.inv_freq, self.w.rotary_dim, self._fused_ws,
+                                                          overlap=then(own_out) | (prefetch if own_proj else 0),
+                                                          q_norm_weight=layer.q_norm, k_norm_weight=layer.k_norm,
+                                                          eps=self.eps)
+                mixed = proj(mixed_in, out_w, then(True))
+                x, h = ops.add_rmsnorm(mixed, layer.post_attention_layernorm, self.eps, residual=x,
+                                       overlap=then(own_mlp))
+                if own_mlp:
+                    act = ops.skinny_gemm(h, layer.mlp.gate_up, overlap=then(own_down), swiglu=True)
+                else:
+                    gate_up = gemm_2d(h, layer.mlp.gate_up)
+                    inter = layer.mlp.down_proj.shape[1]
+                    act = R.swiglu(gate_up[:, :inter], gate_up[:, inter:])
+                pending = proj(act, layer.mlp.down_proj, then(True))
+            _, h = ops.add_rmsnorm(pending, self.w.norm, self.eps, residual=x, overlap=start)
+            return h
+
         def _attention_decode(self, h, w, k_cache, v_cache, pos, scratch, block_table=None):
             if block_table is None or not (k_cache.is_contiguous() and v_cache.is_contiguous()):
                 return super()._attention_decode(h, w, k_cache, v_cache, pos, scratch, block_table)
