@@ -8,6 +8,8 @@ chain of operators:
     decode_step        the layer loop of engine/runner.py:520-571 on the row-wise one-launch operators (residual add +
                        RMSNorm, projection with SwiGLU epilogue) with early starts between this package's kernels
 
+    _forward           the prefill layer loop of engine/runner.py:602-666 with the residual adds inside the RMSNorms and
+                       one gate/up projection (untraced calls)
     _attention_decode  fused_decode_attention: q/k head norms + partial RoPE + KV append + paged attention + gate
                        (engine/runner.py:444-518 is eleven operator calls)
     _gdn_decode        gdn_decode_fused: conv step + q/k norms + gates + delta-rule step + gated norm
@@ -130,6 +132,43 @@ def fast_runner_class():
             return gemm_2d(mixed, w.out_proj)
 
         # ------------------------------------------------------------------------------------------ prefill
+        def _forward(self, input_ids, pos, trace, trace_layers, caches=None, seq=0, packed=None):
+            """engine/runner.py:602-666 for untraced calls: the residual adds ride in the RMSNorms behind them, gate and
+            up are one projection and the SwiGLU reads its two halves in place; the mixers are the runner's own methods
+            (overridden below for packed batches)."""
+            if trace is not None:
+                return super()._forward(input_ids, pos, trace, trace_layers, caches=caches, seq=seq, packed=packed)
+            x = R.embedding_gather(input_ids, self.w.embed_tokens)
+            pending = None                   # MLP output still to be added to the residual stream
+            for i, layer in enumerate(self.w.layers):
+                tag = f"layer{i:02d}"
+                if pending is None:
+                    h = ops.add_rmsnorm(x, layer.input_layernorm, self.eps)
+                else:
+                    x, h = ops.add_rmsnorm(pending, layer.input_layernorm, self.eps, residual=x)
+                if isinstance(layer, R.GDNLayerWeights):
+                    if caches is None:
+                        gdn_fill = None
+                    elif packed is None:
+                        gdn_fill = (caches.conv_states[i][seq], caches.recurrent_states[i][seq])
+                    else:
+                        gdn_fill = (caches.conv_states[i], caches.recurrent_states[i])
+                    h = self._gdn(h, layer, None, tag, fill=gdn_fill, packed=packed)
+                else:
+                    h = self._attention(
+                        h, layer, pos, None, tag,
+                        fill=None if caches is None else (caches.k_caches[i], caches.v_caches[i]),
+                        block_table=None if caches is None or not caches.paged
+                        else (caches.block_table if packed is not None else caches.block_table[seq]),
+                        packed=packed,
+                    )
+                x, h = ops.add_rmsnorm(h, layer.post_attention_layernorm, self.eps, residual=x)
+                inter = layer.mlp.down_proj.shape[1]
+                act = ops.swiglu_fused(gemm_2d(h, layer.mlp.gate_up), inter)
+                pending = gemm_2d(act, layer.mlp.down_proj)
+            _, x = ops.add_rmsnorm(pending, self.w.norm, self.eps, residual=x)
+            return x
+
         def _attention(self, h, w, pos, trace, tag, fill=None, block_table=None, packed=None):
             if packed is None or fill is None or block_table is None or trace is not None:
                 return super()._attention(h, w, pos, trace, tag, fill=fill, block_table=block_table, packed=packed)
