@@ -107,3 +107,28 @@ def test_fused_chunk_prefill_long(ops, lengths):
     assert _lib.load().b200_wait_timed_out() == 0
     assert torch.isfinite(out_c.float()).all() and torch.isfinite(state_c).all()
     assert maxabs(out_c, out_s) <= 1e-2 and maxabs(state_c, state_s) <= 5e-4
+
+
+@pytest.mark.parametrize("token_num", [65, 200, 1100])
+def test_chunk_stages_on_unaligned_views(ops, token_num):
+    """q/k/v as column views of a buffer whose row stride is not a multiple of 8 elements and whose columns start two
+    elements in: the three stages then stage their rows element by element (no 16-byte loads), the single-sequence
+    entry point routes such inputs to them at every length, and the results still match the token-serial kernel."""
+    gen = torch.Generator().manual_seed(7000 + token_num)
+    heads = 16
+    q, k, v, beta, g = gdn_inputs(token_num, heads, gen)
+    width = 3 * heads * 128
+    storage = torch.zeros(token_num, width + 6, dtype=torch.bfloat16, device=DEV)
+    storage[:, 2: 2 + width] = torch.cat([q.reshape(token_num, -1), k.reshape(token_num, -1),
+                                          v.reshape(token_num, -1)], dim=1).to(DEV)
+    qd = storage[:, 2: 2 + heads * 128].view(token_num, heads, 128)
+    kd = storage[:, 2 + heads * 128: 2 + 2 * heads * 128].view(token_num, heads, 128)
+    vd = storage[:, 2 + 2 * heads * 128: 2 + width].view(token_num, heads, 128)
+    assert qd.stride(0) % 8 != 0 and qd.data_ptr() % 16 != 0
+    out_c, state_c = ops.call_gdn_recurrent_prefill_chunked_triton(qd, kd, vd, beta.to(DEV), g.to(DEV))
+    out_s, state_s = ops.gdn_recurrent_prefill_sequential(qd, kd, vd, beta.to(DEV), g.to(DEV))
+    assert torch.isfinite(out_c.float()).all() and torch.isfinite(state_c).all()
+    assert maxabs(out_c, out_s) <= 1e-2 and maxabs(state_c, state_s) <= 5e-4
+    w, u, gcs = ops.gdn_chunk_prepare_wy(kd, vd, beta.to(DEV), g.to(DEV))
+    w2, u2, gcs2 = ops.gdn_chunk_prepare_wy(k.to(DEV), v.to(DEV), beta.to(DEV), g.to(DEV))
+    assert torch.equal(w, w2) and torch.equal(u, u2) and torch.equal(gcs, gcs2)

@@ -201,15 +201,15 @@ def test_gdn_decode_fused_equals_chain(mods, batch, form, prefetch):
         _lib.call("b200_gdn_recurrent_decode_form", 0)
 
 
-@pytest.mark.parametrize("batch", [48, 256])
-def test_gdn_decode_fused_forms_agree(mods, batch):
+@pytest.mark.parametrize("batch,heads", [(48, 16), (256, 16), (100, 4), (37, 9)])
+def test_gdn_decode_fused_forms_agree(mods, batch, heads):
     """The form the sizes choose (ring from more than two heads per SM on; at 256 sequences every CTA walks seven
-    heads) against the register form on the same inputs: conv state bit-equal, recurrent state and output to
-    summation-order accuracy."""
+    heads; head counts other than sixteen) against the register form on the same inputs: conv state bit-equal,
+    recurrent state and output to summation-order accuracy."""
     from b200attn import _lib
     ops, _ = mods
     gen = torch.Generator().manual_seed(17)
-    heads, kd = 16, 2048
+    kd = heads * 128
     w4 = (torch.randn(4, 3 * kd, generator=gen) * 0.5).to(torch.bfloat16).to(DEV)
     a_log = (torch.rand(heads, generator=gen) * 2.7).to(DEV)
     dt_bias = (torch.randn(heads, generator=gen) * 0.5).to(torch.bfloat16).to(DEV)
